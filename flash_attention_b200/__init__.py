@@ -1,0 +1,12 @@
+"""B200 (sm_100a) NVFP4 fused attention forward behind the ``flash_attn.cute`` call surface.
+
+Public names follow the reference's ``flash_attn/cute/__init__.py:11-18``.
+"""
+from ._lib import build, lib, LIB_PATH
+from .interface import (flash_attn_func, flash_attn_fp4_func, check_status, VARIANT_AUTO,
+                        VARIANT_SERIAL, VARIANT_WS)
+from .quant import NVFP4Tensor, quantize_qkv, quantize_lastdim, dequantize_lastdim, sf_to_tiled
+
+__all__ = ["flash_attn_func", "flash_attn_fp4_func", "check_status", "NVFP4Tensor", "quantize_qkv",
+           "quantize_lastdim", "dequantize_lastdim", "sf_to_tiled", "build", "lib", "LIB_PATH",
+           "VARIANT_AUTO", "VARIANT_SERIAL", "VARIANT_WS"]

@@ -1,0 +1,115 @@
+"""ctypes binding of libfa4_nvfp4.so (the C ABI declared in include/fa4_nvfp4.h).
+
+The library is built in-tree by ``build()`` with a plain ``nvcc`` command (no JIT cache, no
+torch extension machinery) and loaded lazily.  There is no fallback: if the library is missing
+or cannot be loaded, every operator of this package raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import shutil
+import subprocess
+import threading
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libfa4_nvfp4.so")
+CSRC = os.path.join(_HERE, "csrc")
+SOURCES = ["api.cu"]
+HEADERS = ["ptx.cuh", "softmax.cuh", "attn_common.cuh", "attn_serial.cuh", "attn_ws.cuh",
+           "aux_kernels.cuh"]
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+              "--shared", "-Xcompiler", "-fPIC"]
+
+ERROR_NAMES = {1: "null pointer", 2: "unsupported shape", 3: "bad stride", 4: "misaligned pointer",
+               5: "unknown variant", 6: "tensor map rejected", 7: "struct size mismatch",
+               8: "problem too large for this entry point"}
+
+
+class Params(ctypes.Structure):
+    """Mirror of ``fa4_nvfp4_params``."""
+    _fields_ = [
+        ("struct_size", ctypes.c_uint32), ("variant", ctypes.c_int32),
+        ("q", ctypes.c_void_p), ("k", ctypes.c_void_p), ("v", ctypes.c_void_p),
+        ("q_sf", ctypes.c_void_p), ("k_sf", ctypes.c_void_p), ("v_sf", ctypes.c_void_p),
+        ("out", ctypes.c_void_p), ("lse", ctypes.c_void_p), ("status", ctypes.c_void_p),
+        ("q_stride_b", ctypes.c_int64), ("q_stride_s", ctypes.c_int64), ("q_stride_h", ctypes.c_int64),
+        ("k_stride_b", ctypes.c_int64), ("k_stride_s", ctypes.c_int64), ("k_stride_h", ctypes.c_int64),
+        ("v_stride_b", ctypes.c_int64), ("v_stride_h", ctypes.c_int64), ("v_stride_d", ctypes.c_int64),
+        ("o_stride_b", ctypes.c_int64), ("o_stride_s", ctypes.c_int64), ("o_stride_h", ctypes.c_int64),
+        ("B", ctypes.c_int32), ("Sq", ctypes.c_int32), ("Sk", ctypes.c_int32), ("Hq", ctypes.c_int32),
+        ("Hkv", ctypes.c_int32), ("D", ctypes.c_int32), ("Dv", ctypes.c_int32),
+        ("causal", ctypes.c_int32),
+        ("q_scale", ctypes.c_float), ("k_scale", ctypes.c_float), ("v_scale", ctypes.c_float),
+        ("softmax_scale", ctypes.c_float),
+        ("wait_budget_ns", ctypes.c_uint64),
+    ]
+
+
+def _needs_build() -> bool:
+    if not os.path.exists(LIB_PATH):
+        return True
+    t = os.path.getmtime(LIB_PATH)
+    deps = [os.path.join(CSRC, f) for f in SOURCES + HEADERS]
+    deps.append(os.path.join(_HERE, "..", "include", "fa4_nvfp4.h"))
+    return any(os.path.exists(d) and os.path.getmtime(d) > t for d in deps)
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    """Compile the CUDA library for sm_100a (cross-compiles without a GPU)."""
+    if not force and not _needs_build():
+        return LIB_PATH
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + \
+          ["-o", LIB_PATH] + [os.path.join(CSRC, s) for s in SOURCES]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
+    if verbose:
+        print(res.stderr)
+    return LIB_PATH
+
+
+_lib = None
+_lock = threading.Lock()
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded library.  Raises if it is absent (built on demand only when nvcc is present)."""
+    global _lib
+    with _lock:
+        if _lib is None:
+            if _needs_build():
+                if shutil.which("nvcc") or os.path.exists("/usr/local/cuda/bin/nvcc"):
+                    build()
+                elif not os.path.exists(LIB_PATH):
+                    raise RuntimeError(f"{LIB_PATH} is missing and nvcc is not available; "
+                                       "run flash_attention_b200.build() first")
+            L = ctypes.CDLL(LIB_PATH)
+            L.fa4_nvfp4_fwd.argtypes = [ctypes.POINTER(Params), ctypes.c_void_p]
+            L.fa4_nvfp4_fwd.restype = ctypes.c_int
+            L.fa4_nvfp4_sf_linear_to_tiled.argtypes = [
+                ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
+                ctypes.c_int32, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p]
+            L.fa4_nvfp4_sf_linear_to_tiled.restype = ctypes.c_int
+            L.fa4_nvfp4_query.argtypes = [ctypes.c_int32]
+            L.fa4_nvfp4_query.restype = ctypes.c_int
+            L.fa4_nvfp4_debug_qk_tile.argtypes = [ctypes.c_void_p] * 5 + [
+                ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]
+            L.fa4_nvfp4_debug_qk_tile.restype = ctypes.c_int
+            L.fa4_nvfp4_debug_wait_expiry.argtypes = [ctypes.c_void_p, ctypes.c_uint64, ctypes.c_void_p]
+            L.fa4_nvfp4_debug_wait_expiry.restype = ctypes.c_int
+            _lib = L
+        return _lib
+
+
+EXPORTS = ["fa4_nvfp4_fwd", "fa4_nvfp4_sf_linear_to_tiled", "fa4_nvfp4_query",
+           "fa4_nvfp4_debug_qk_tile", "fa4_nvfp4_debug_wait_expiry"]
+
+
+def check(rc: int, what: str) -> None:
+    if rc == 0:
+        return
+    if rc < 0:
+        raise ValueError(f"{what}: argument rejected ({ERROR_NAMES.get(-rc, rc)})")
+    raise RuntimeError(f"{what}: CUDA error {rc}")

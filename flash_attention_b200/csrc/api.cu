@@ -1,0 +1,193 @@
+// C ABI of the NVFP4 attention forward (see include/fa4_nvfp4.h): argument validation, TMA
+// tensor maps, launch configuration.  Host code only; the kernels live in the .cuh files.
+#include "../../include/fa4_nvfp4.h"
+
+#include "attn_common.cuh"
+#include "attn_serial.cuh"
+#include "attn_ws.cuh"
+#include "aux_kernels.cuh"
+
+#include <cudaTypedefs.h>
+#include <mutex>
+
+namespace {
+
+using namespace fa4;
+
+constexpr uint64_t kDefaultBudgetNs = 2000ull * 1000 * 1000;
+
+PFN_cuTensorMapEncodeTiled_v12000 get_encode() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+    }
+  });
+  return fn;
+}
+
+// Byte tensor of rank 4, innermost dimension contiguous; box = {box0, box1, box2, box3} bytes /
+// rows; 64-byte swizzle when the innermost box is 64 bytes.
+bool encode_u8_4d(CUtensorMap* m, const void* base, const uint64_t (&dims)[4],
+                  const uint64_t (&strides)[3], const uint32_t (&box)[4], CUtensorMapSwizzle sw) {
+  auto fn = get_encode();
+  if (fn == nullptr) return false;
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), dims, strides,
+                        box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+template <class Kernel>
+int ensure_smem(Kernel kernel, uint32_t bytes) {
+  const cudaError_t e =
+      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  return e == cudaSuccess ? 0 : (int)e;
+}
+
+}  // namespace
+
+extern "C" int fa4_nvfp4_query(int32_t what) {
+  static const int dims[] = {128};
+  switch (what) {
+    case 0: return FA4_NVFP4_ABI_VERSION;
+    case 1: return (int)(sizeof(dims) / sizeof(dims[0]));
+    case 100: return (int)fa4::ws::kSmemRequest;
+    default:
+      if (what >= 2 && what < 2 + (int)(sizeof(dims) / sizeof(dims[0]))) return dims[what - 2];
+      return -FA4_E_SHAPE;
+  }
+}
+
+extern "C" int fa4_nvfp4_fwd(const fa4_nvfp4_params* p, void* cuda_stream) {
+  if (p == nullptr) return -FA4_E_NULL;
+  if (p->struct_size != sizeof(fa4_nvfp4_params)) return -FA4_E_STRUCT;
+  if (!p->q || !p->k || !p->v || !p->q_sf || !p->k_sf || !p->v_sf || !p->out) return -FA4_E_NULL;
+  if (p->B <= 0 || p->Sq <= 0 || p->Sk <= 0 || p->Hq <= 0 || p->Hkv <= 0) return -FA4_E_SHAPE;
+  if (p->Hq % p->Hkv != 0) return -FA4_E_SHAPE;
+  if (p->D != 128 || p->Dv != 128) return -FA4_E_SHAPE;
+  if (p->Sq % kBlockM != 0 || p->Sk % kBlockN != 0) return -FA4_E_SHAPE;
+  if (p->Sq / kBlockM * (int64_t)p->Hq * p->B > 0x7fffffffLL) return -FA4_E_SHAPE;
+  if (!(p->softmax_scale > 0.f) || !(p->q_scale > 0.f) || !(p->k_scale > 0.f)) return -FA4_E_SHAPE;
+  const void* ptrs[] = {p->q, p->k, p->v, p->q_sf, p->k_sf, p->v_sf, p->out};
+  for (const void* q : ptrs)
+    if (!aligned16(q)) return -FA4_E_ALIGN;
+  const int64_t bstr[] = {p->q_stride_b, p->q_stride_s, p->q_stride_h, p->k_stride_b, p->k_stride_s,
+                          p->k_stride_h, p->v_stride_b, p->v_stride_h, p->v_stride_d};
+  for (int64_t s : bstr)
+    if (s <= 0 || (s & 15) != 0) return -FA4_E_STRIDE;
+  if ((p->o_stride_b & 7) || (p->o_stride_s & 7) || (p->o_stride_h & 7)) return -FA4_E_STRIDE;
+  int variant = p->variant == FA4_VARIANT_AUTO ? FA4_VARIANT_WS : p->variant;
+  if (variant != FA4_VARIANT_SERIAL && variant != FA4_VARIANT_WS) return -FA4_E_VARIANT;
+
+  CUtensorMap tm_q, tm_k, tm_v;
+  {
+    const uint64_t dq[4] = {(uint64_t)p->D / 2, (uint64_t)p->Hq, (uint64_t)p->Sq, (uint64_t)p->B};
+    const uint64_t sq[3] = {(uint64_t)p->q_stride_h, (uint64_t)p->q_stride_s, (uint64_t)p->q_stride_b};
+    const uint32_t bq[4] = {64, 1, (uint32_t)kBlockM, 1};
+    const uint64_t dk[4] = {(uint64_t)p->D / 2, (uint64_t)p->Hkv, (uint64_t)p->Sk, (uint64_t)p->B};
+    const uint64_t sk[3] = {(uint64_t)p->k_stride_h, (uint64_t)p->k_stride_s, (uint64_t)p->k_stride_b};
+    const uint32_t bk[4] = {64, 1, (uint32_t)kBlockN, 1};
+    const uint64_t dv[4] = {(uint64_t)p->Sk / 2, (uint64_t)p->Dv, (uint64_t)p->Hkv, (uint64_t)p->B};
+    const uint64_t sv[3] = {(uint64_t)p->v_stride_d, (uint64_t)p->v_stride_h, (uint64_t)p->v_stride_b};
+    const uint32_t bv[4] = {64, 128, 1, 1};
+    if (!encode_u8_4d(&tm_q, p->q, dq, sq, bq, CU_TENSOR_MAP_SWIZZLE_64B) ||
+        !encode_u8_4d(&tm_k, p->k, dk, sk, bk, CU_TENSOR_MAP_SWIZZLE_64B) ||
+        !encode_u8_4d(&tm_v, p->v, dv, sv, bv, CU_TENSOR_MAP_SWIZZLE_64B))
+      return -FA4_E_TENSORMAP;
+  }
+
+  KernelParams kp;
+  kp.q_sf = static_cast<const uint8_t*>(p->q_sf);
+  kp.k_sf = static_cast<const uint8_t*>(p->k_sf);
+  kp.v_sf = static_cast<const uint8_t*>(p->v_sf);
+  kp.out = static_cast<__nv_bfloat16*>(p->out);
+  kp.lse = p->lse;
+  kp.status = p->status;
+  kp.o_stride_b = p->o_stride_b;
+  kp.o_stride_s = p->o_stride_s;
+  kp.o_stride_h = p->o_stride_h;
+  kp.B = p->B; kp.Sq = p->Sq; kp.Sk = p->Sk; kp.Hq = p->Hq; kp.Hkv = p->Hkv;
+  kp.group = p->Hq / p->Hkv;
+  kp.num_m_blocks = p->Sq / kBlockM;
+  kp.num_n_blocks = p->Sk / kBlockN;
+  kp.causal = p->causal ? 1 : 0;
+  // tiled scale factors: (B, H, row tiles, col tiles, 512)
+  kp.qsf_stride_h = (int64_t)kp.num_m_blocks * (p->D / 64) * 512;
+  kp.qsf_stride_b = kp.qsf_stride_h * p->Hq;
+  kp.ksf_stride_h = (int64_t)kp.num_n_blocks * (p->D / 64) * 512;
+  kp.ksf_stride_b = kp.ksf_stride_h * p->Hkv;
+  kp.vsf_stride_h = (int64_t)((p->Dv + 127) / 128) * (p->Sk / 64) * 512;
+  kp.vsf_stride_b = kp.vsf_stride_h * p->Hkv;
+  kp.sl2 = p->softmax_scale * p->q_scale * p->k_scale * 1.4426950408889634f;
+  kp.out_scale = p->v_scale;
+  kp.budget_ns = p->wait_budget_ns ? p->wait_budget_ns : kDefaultBudgetNs;
+
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  const unsigned grid = (unsigned)(kp.num_m_blocks * p->Hq * p->B);
+  if (variant == FA4_VARIANT_SERIAL) {
+    if (int e = ensure_smem(attn_fwd_serial_kernel, serial::kSmemRequest)) return e;
+    attn_fwd_serial_kernel<<<grid, 128, serial::kSmemRequest, stream>>>(tm_q, tm_k, tm_v, kp);
+  } else {
+    if (int e = ensure_smem(attn_fwd_ws_kernel, ws::kSmemRequest)) return e;
+    attn_fwd_ws_kernel<<<grid, ws::kThreads, ws::kSmemRequest, stream>>>(tm_q, tm_k, tm_v, kp);
+  }
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : (int)e;
+}
+
+extern "C" int fa4_nvfp4_sf_linear_to_tiled(const void* src, void* dst, int32_t n_outer,
+                                            int32_t n_inner, int32_t rows, int32_t cols,
+                                            int64_t stride_outer, int64_t stride_inner,
+                                            int64_t stride_row, void* cuda_stream) {
+  if (!src || !dst) return -FA4_E_NULL;
+  if (n_outer <= 0 || n_inner <= 0 || rows <= 0 || cols <= 0) return -FA4_E_SHAPE;
+  if (!aligned16(dst)) return -FA4_E_ALIGN;
+  const int64_t total = (int64_t)n_outer * n_inner * ((rows + 127) / 128) * ((cols + 3) / 4) * 32;
+  int64_t blocks = (total + 255) / 256;
+  const int64_t cap = 148 * 16;  // grid-stride beyond a few waves
+  if (blocks > cap) blocks = cap;
+  sf_linear_to_tiled_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+      static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), n_outer, n_inner, rows, cols,
+      stride_outer, stride_inner, stride_row);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : (int)e;
+}
+
+extern "C" int fa4_nvfp4_debug_qk_tile(const void* q, const void* k, const void* q_sf,
+                                       const void* k_sf, float* s_out, int32_t D, int32_t mode,
+                                       uint32_t* status, void* cuda_stream) {
+  if (!q || !k || !q_sf || !k_sf || !s_out) return -FA4_E_NULL;
+  if (D != 128) return -FA4_E_SHAPE;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(q_sf) || !aligned16(k_sf)) return -FA4_E_ALIGN;
+  CUtensorMap tm_q, tm_k;
+  const uint64_t d[4] = {64, 1, 128, 1};
+  const uint64_t s[3] = {64, 64, 64 * 128};
+  const uint32_t b[4] = {64, 1, 128, 1};
+  if (!encode_u8_4d(&tm_q, q, d, s, b, CU_TENSOR_MAP_SWIZZLE_64B) ||
+      !encode_u8_4d(&tm_k, k, d, s, b, CU_TENSOR_MAP_SWIZZLE_64B))
+    return -FA4_E_TENSORMAP;
+  if (int e = ensure_smem(qk_tile_probe_kernel, serial::kSmemRequest)) return e;
+  qk_tile_probe_kernel<<<1, 128, serial::kSmemRequest, static_cast<cudaStream_t>(cuda_stream)>>>(
+      tm_q, tm_k, static_cast<const uint8_t*>(q), static_cast<const uint8_t*>(k),
+      static_cast<const uint8_t*>(q_sf), static_cast<const uint8_t*>(k_sf), s_out, mode, status,
+      kDefaultBudgetNs);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : (int)e;
+}
+
+extern "C" int fa4_nvfp4_debug_wait_expiry(uint32_t* status, uint64_t budget_ns, void* cuda_stream) {
+  if (!status) return -FA4_E_NULL;
+  if (budget_ns == 0 || budget_ns > kDefaultBudgetNs) return -FA4_E_SHAPE;
+  wait_expiry_kernel<<<1, 32, 0, static_cast<cudaStream_t>(cuda_stream)>>>(status, budget_ns);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : (int)e;
+}

@@ -1,0 +1,94 @@
+// Parameters and tile bookkeeping shared by the attention kernels (head dim 128 family).
+#pragma once
+#include "ptx.cuh"
+#include "softmax.cuh"
+#include <cuda_bf16.h>
+
+namespace fa4 {
+
+constexpr int kBlockM = 128;  // query rows per CTA tile (= tensor-memory lanes)
+constexpr int kBlockN = 128;  // keys per K/V block
+
+struct KernelParams {
+  const uint8_t* q_sf;  // tiled scale factors, see fa4_nvfp4.h
+  const uint8_t* k_sf;
+  const uint8_t* v_sf;
+  __nv_bfloat16* out;
+  float* lse;
+  uint32_t* status;
+  int64_t o_stride_b, o_stride_s, o_stride_h;  // elements
+  int64_t qsf_stride_b, qsf_stride_h;          // bytes between batches / heads of tiled SFs
+  int64_t ksf_stride_b, ksf_stride_h;
+  int64_t vsf_stride_b, vsf_stride_h;
+  int B, Sq, Sk, Hq, Hkv, group;
+  int num_m_blocks, num_n_blocks;
+  int causal;
+  float sl2;        // softmax_scale * q_scale * k_scale * log2(e)
+  float out_scale;  // v_scale
+  uint64_t budget_ns;
+};
+
+// Work tile of a CTA.  Tiles are ordered so that, for causal problems, the m-blocks with the
+// most K/V blocks come first (longest-processing-time-first, the idea of the reference's
+// SingleTileLPTScheduler, flash_attn/cute/tile_scheduler.py:386-618) and the query heads of one
+// kv head are neighbours, so that their K/V tiles are shared through L2.
+struct Tile {
+  int m_blk, h, b, hk;
+  int n_blocks;  // number of K/V blocks this tile visits (0: every row is fully masked)
+};
+
+__device__ __forceinline__ Tile decode_tile(const KernelParams& p, int tile_idx) {
+  Tile t;
+  const int per_m = p.Hq * p.B;
+  const int m_rev = tile_idx / per_m;
+  const int rem = tile_idx - m_rev * per_m;
+  t.b = rem / p.Hq;
+  t.h = rem - t.b * p.Hq;
+  t.hk = t.h / p.group;
+  t.m_blk = p.causal ? (p.num_m_blocks - 1 - m_rev) : m_rev;
+  int n = p.num_n_blocks;
+  if (p.causal) {
+    // last visible key of the tile's last row: (m_blk + 1) * 128 - 1 + Sk - Sq
+    // (block range of flash_attn/cute/block_info.py:23-55, bottom-right aligned)
+    const int last = (t.m_blk + 1) * kBlockM + p.Sk - p.Sq;  // exclusive
+    int nb = (last + kBlockN - 1) / kBlockN;
+    if (last <= 0) nb = 0;
+    n = nb < n ? nb : n;
+  }
+  t.n_blocks = n;
+  return t;
+}
+
+// In-block index of the last visible key for query row `row_in_tile` of tile t in K/V block
+// `nb`, or >= 127 when the block needs no mask for that row.
+__device__ __forceinline__ int causal_limit(const KernelParams& p, const Tile& t, int row_in_tile,
+                                            int nb) {
+  return t.m_blk * kBlockM + row_in_tile + p.Sk - p.Sq - nb * kBlockN;
+}
+__device__ __forceinline__ bool block_needs_mask(const KernelParams& p, const Tile& t, int nb) {
+  return p.causal && (nb * kBlockN + kBlockN - 1 > t.m_blk * kBlockM + p.Sk - p.Sq);
+}
+
+// Final scaling and bf16 store of 32 consecutive output columns of one row.
+__device__ __forceinline__ void store_out_32(__nv_bfloat16* dst, const uint32_t (&acc)[32],
+                                             float scale) {
+  uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {
+    uint4 w;
+    w.x = pack_bf16x2(__uint_as_float(acc[8 * v + 0]) * scale, __uint_as_float(acc[8 * v + 1]) * scale);
+    w.y = pack_bf16x2(__uint_as_float(acc[8 * v + 2]) * scale, __uint_as_float(acc[8 * v + 3]) * scale);
+    w.z = pack_bf16x2(__uint_as_float(acc[8 * v + 4]) * scale, __uint_as_float(acc[8 * v + 5]) * scale);
+    w.w = pack_bf16x2(__uint_as_float(acc[8 * v + 6]) * scale, __uint_as_float(acc[8 * v + 7]) * scale);
+    d4[v] = w;
+  }
+}
+
+// Natural-log LSE of the scaled scores from the reference maximum (raw units) and the sum of
+// p' = 2^kShift * p (flash_attn/cute/flash_fwd_sm100.py:2481-2501).
+__device__ __forceinline__ float finish_lse(float m_ref, float l_sum, float sl2) {
+  if (!(l_sum > 0.f) || m_ref == kNegInf) return kNegInf;
+  return (m_ref * sl2 + lg2_approx(l_sum) - static_cast<float>(kShift)) * 0.6931471805599453f;
+}
+
+}  // namespace fa4

@@ -1,0 +1,409 @@
+// Warp-specialised variant: the production kernel.
+//
+// Roles of the 10 warps of a CTA (one CTA per SM, one 128-row query tile per CTA):
+//   warps 0-3  softmax warpgroup 0: K/V blocks 0, 2, 4, ... of the tile (visit order)
+//   warps 4-7  softmax warpgroup 1: K/V blocks 1, 3, 5, ...
+//   warp  8    TMA producer: Q once, then K and V tiles with their scale factors into two rings
+//   warp  9    tensor-core issuer: tcgen05.cp of scale factors, block-scaled tcgen05.mma for
+//              S = Q K^T (two S buffers in tensor memory) and O += P V; owns tensor memory
+//
+// The reference kernel (flash_attn/cute/flash_fwd_sm100.py:216-222) keeps two 128-row query
+// stages with S and O for both in tensor memory (4 x 128 columns = all of it).  The block-scaled
+// instruction needs tensor-memory columns for the scale factors as well, so this kernel keeps ONE
+// query stage with S double-buffered across K/V blocks (S0, S1, O = 384 columns + 56 columns of
+// scales) and lets the two softmax warpgroups alternate over K/V blocks.  The running row
+// maximum is handed from the warpgroup of block i-1 to the warpgroup of block i through shared
+// memory, so the exponentials of consecutive blocks overlap while the maxima stay ordered.
+//
+// The correction step (rescale O when the reference maximum moves; separate warps in the
+// reference, flash_fwd_sm100.py:2230-2351) is done by the softmax warpgroup that moved the
+// maximum: with the lazy threshold it is rare after the first block.
+//
+// Barriers (all mbarriers, every wait bounded):
+//   q_full            producer -> issuer      Q tile + scales landed
+//   k_full/k_empty[]  producer <-> issuer     K ring (k_empty by tcgen05.commit after QK^T)
+//   v_full/v_empty[]  producer <-> issuer     V ring (v_empty by tcgen05.commit after PV)
+//   s_full[2]         issuer -> softmax WG    S buffer holds block i          (commit)
+//   s_free[2]         softmax WG -> issuer    S buffer copied to registers     (128 arrivals)
+//   p_full[2]         softmax WG -> issuer    P block + its scales in shared memory (128 arrivals)
+//   pv_done[2]        issuer -> softmax WGs   PV of block i complete: P buffer free, O stable
+//   max_ready[2]      softmax WG -> other WG  reference maximum of block i published
+//   fin               both WGs                row sums published for the final combine
+//   drain             issuer                  tensor-core work drained on the abort path
+#pragma once
+#include "attn_common.cuh"
+#include "attn_serial.cuh"  // tensor-memory map, tile byte sizes
+
+namespace fa4 {
+namespace ws {
+
+constexpr int kStagesK = 4;
+constexpr int kStagesV = 4;
+constexpr int kThreads = 320;
+constexpr int kProducerWarp = 8;
+constexpr int kIssuerWarp = 9;
+
+// shared-memory map (offsets from a 1024-byte aligned base)
+constexpr uint32_t kOffQ = 0;                                  // 8 KB
+constexpr uint32_t kOffK = kOffQ + kTileBytes;                 // kStagesK x 8 KB
+constexpr uint32_t kOffV = kOffK + kStagesK * kTileBytes;      // kStagesV x 8 KB
+constexpr uint32_t kOffP = kOffV + kStagesV * kTileBytes;      // 2 x 8 KB
+constexpr uint32_t kOffSFQ = kOffP + 2 * kTileBytes;           // 1 KB
+constexpr uint32_t kOffSFK = kOffSFQ + kSfBytes;               // kStagesK x 1 KB
+constexpr uint32_t kOffSFV = kOffSFK + kStagesK * kSfBytes;    // kStagesV x 1 KB
+constexpr uint32_t kOffSFP = kOffSFV + kStagesV * kSfBytes;    // 2 x 1 KB
+constexpr uint32_t kOffMax = kOffSFP + 2 * kSfBytes;           // 2 x 128 floats
+constexpr uint32_t kOffFin = kOffMax + 2 * 128 * 4;            // 2 x 128 x (sum, ref) floats
+constexpr uint32_t kOffBar = kOffFin + 2 * 128 * 8;
+constexpr int kNumBars = 1 + 2 * kStagesK + 2 * kStagesV + 2 * 5 + 2;
+constexpr uint32_t kOffMisc = kOffBar + 8 * kNumBars;          // tmem slot, abort flag
+constexpr uint32_t kSmemUsed = kOffMisc + 16;
+constexpr uint32_t kSmemRequest = kSmemUsed + 1024 > 120 * 1024 ? kSmemUsed + 1024 : 120 * 1024;
+
+enum Site {
+  kSiteQFull = 10, kSiteKEmpty, kSiteVEmpty, kSiteKFull, kSiteVFull, kSiteSFull, kSiteSFree,
+  kSitePFull, kSitePvDone, kSiteMaxReady, kSiteFin, kSiteFinalO
+};
+
+struct Bars {
+  uint32_t q_full, k_full, k_empty, v_full, v_empty, s_full, s_free, p_full, pv_done, max_ready, fin,
+      drain;
+  __device__ explicit Bars(uint32_t b) {
+    q_full = b;
+    k_full = q_full + 8;
+    k_empty = k_full + 8 * kStagesK;
+    v_full = k_empty + 8 * kStagesK;
+    v_empty = v_full + 8 * kStagesV;
+    s_full = v_empty + 8 * kStagesV;
+    s_free = s_full + 16;
+    p_full = s_free + 16;
+    pv_done = p_full + 16;
+    max_ready = pv_done + 16;
+    fin = max_ready + 16;
+    drain = fin + 8;
+  }
+};
+
+}  // namespace ws
+
+__global__ void __launch_bounds__(ws::kThreads, 1)
+attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
+                   const __grid_constant__ CUtensorMap tm_k,
+                   const __grid_constant__ CUtensorMap tm_v, const KernelParams p) {
+  using namespace ws;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gbase = smem_raw + (base - smem_u32(smem_raw));
+  const Bars bars(base + kOffBar);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + kOffMisc);
+  volatile uint32_t* s_abort = reinterpret_cast<volatile uint32_t*>(gbase + kOffMisc + 4);
+  volatile float* s_max = reinterpret_cast<volatile float*>(gbase + kOffMax);   // [2][128]
+  volatile float* s_fin = reinterpret_cast<volatile float*>(gbase + kOffFin);   // [2][128][2]
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const WaitCtx wc{s_abort, p.status, p.budget_ns};
+
+  if (tid == 0) {
+    *s_abort = 0u;
+    mbar_init(bars.q_full, 1);
+    for (int s = 0; s < kStagesK; ++s) {
+      mbar_init(bars.k_full + 8 * s, 1);
+      mbar_init(bars.k_empty + 8 * s, 1);
+    }
+    for (int s = 0; s < kStagesV; ++s) {
+      mbar_init(bars.v_full + 8 * s, 1);
+      mbar_init(bars.v_empty + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bars.s_full + 8 * b, 1);
+      mbar_init(bars.s_free + 8 * b, 128);
+      mbar_init(bars.p_full + 8 * b, 128);
+      mbar_init(bars.pv_done + 8 * b, 1);
+      mbar_init(bars.max_ready + 8 * b, 128);
+    }
+    mbar_init(bars.fin, 256);
+    mbar_init(bars.drain, 1);
+    fence_barrier_init();
+  }
+  if (warp == kProducerWarp && lane == 0) {
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+  }
+  if (warp == kIssuerWarp) {
+    tmem_alloc(base + kOffMisc, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+  const bool poisoned =
+      (p.status != nullptr) && (*reinterpret_cast<volatile uint32_t*>(p.status) != 0u);
+
+  const Tile t = decode_tile(p, blockIdx.x);
+  const int n = poisoned ? 0 : t.n_blocks;
+  constexpr uint32_t idesc = make_idesc_nvf4(128, 128);
+
+  if (warp == kProducerWarp) {
+    // =========================================== TMA producer ===================================
+    if (lane == 0 && n > 0) {
+      mbar_arrive_expect_tx(bars.q_full, kTileBytes + kSfBytes);
+      tma_load_4d(base + kOffQ, &tm_q, bars.q_full, 0, t.h, t.m_blk * kBlockM, t.b);
+      bulk_load(base + kOffSFQ,
+                p.q_sf + t.b * p.qsf_stride_b + t.h * p.qsf_stride_h + (int64_t)t.m_blk * kSfBytes,
+                kSfBytes, bars.q_full);
+      const uint8_t* ksf = p.k_sf + t.b * p.ksf_stride_b + t.hk * p.ksf_stride_h;
+      const uint8_t* vsf = p.v_sf + t.b * p.vsf_stride_b + t.hk * p.vsf_stride_h;
+      bool ok = true;
+      int issued_k = 0, issued_v = 0;
+      // K runs two blocks ahead of V: QK^T of block i+2 is issued before PV of block i.
+      for (int step = 0; ok && step < n + 2; ++step) {
+        const int ik = step, iv = step - 2;
+        if (ik < n) {
+          const int st = ik % kStagesK, nb = n - 1 - ik;
+          ok = mbar_wait(bars.k_empty + 8 * st, ((ik / kStagesK) & 1) ^ 1, wc, kSiteKEmpty);
+          if (!ok) break;
+          mbar_arrive_expect_tx(bars.k_full + 8 * st, kTileBytes + kSfBytes);
+          tma_load_4d(base + kOffK + st * kTileBytes, &tm_k, bars.k_full + 8 * st, 0, t.hk,
+                      nb * kBlockN, t.b);
+          bulk_load(base + kOffSFK + st * kSfBytes, ksf + (int64_t)nb * kSfBytes, kSfBytes,
+                    bars.k_full + 8 * st);
+          issued_k = ik + 1;
+        }
+        if (iv >= 0 && iv < n) {
+          const int st = iv % kStagesV, nb = n - 1 - iv;
+          ok = mbar_wait(bars.v_empty + 8 * st, ((iv / kStagesV) & 1) ^ 1, wc, kSiteVEmpty);
+          if (!ok) break;
+          mbar_arrive_expect_tx(bars.v_full + 8 * st, kTileBytes + kSfBytes);
+          tma_load_4d(base + kOffV + st * kTileBytes, &tm_v, bars.v_full + 8 * st,
+                      nb * (kBlockN / 2), 0, t.hk, t.b);
+          bulk_load(base + kOffSFV + st * kSfBytes, vsf + (int64_t)nb * kSfBytes, kSfBytes,
+                    bars.v_full + 8 * st);
+          issued_v = iv + 1;
+        }
+      }
+      if (!ok) {
+        // bounded drain: let the copies already issued land before the CTA's memory is released
+        const uint64_t t0 = globaltimer_ns();
+        const uint64_t lim = 50ull * 1000 * 1000;
+        for (int i = issued_k > kStagesK ? issued_k - kStagesK : 0; i < issued_k; ++i) {
+          while (!mbar_try_wait(bars.k_full + 8 * (i % kStagesK), (i / kStagesK) & 1) &&
+                 globaltimer_ns() - t0 < lim) {}
+        }
+        for (int i = issued_v > kStagesV ? issued_v - kStagesV : 0; i < issued_v; ++i) {
+          while (!mbar_try_wait(bars.v_full + 8 * (i % kStagesV), (i / kStagesV) & 1) &&
+                 globaltimer_ns() - t0 < lim) {}
+        }
+        while (!mbar_try_wait(bars.q_full, 0) && globaltimer_ns() - t0 < lim) {}
+      }
+    }
+  } else if (warp == kIssuerWarp) {
+    // =========================================== tensor-core issuer =============================
+    if (lane == 0 && n > 0) {
+      bool ok = mbar_wait(bars.q_full, 0, wc, kSiteQFull);
+      if (ok) {
+        tc_fence_after_sync();
+        tc_cp_sf(tmem + kTmSFQ, base + kOffSFQ);
+        tc_cp_sf(tmem + kTmSFQ + 4, base + kOffSFQ + 512);
+      }
+      // S[i % 2] = Q K_i^T
+      auto issue_qk = [&](int i) -> bool {
+        const int st = i % kStagesK, b = i & 1;
+        if (!mbar_wait(bars.k_full + 8 * st, (i / kStagesK) & 1, wc, kSiteKFull)) return false;
+        tc_fence_after_sync();
+        const uint32_t sfk = tmem + kTmSFK + 8 * b;
+        tc_cp_sf(sfk, base + kOffSFK + st * kSfBytes);
+        tc_cp_sf(sfk + 4, base + kOffSFK + st * kSfBytes + 512);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const uint64_t da = make_smem_desc(base + kOffQ + 32 * j, 16, 512, kSwizzle64);
+          const uint64_t db =
+              make_smem_desc(base + kOffK + st * kTileBytes + 32 * j, 16, 512, kSwizzle64);
+          mma_nvf4(tmem + (b ? kTmS1 : kTmS0), da, db, idesc, tmem + kTmSFQ + 4 * j, sfk + 4 * j, j);
+        }
+        tc_commit(bars.s_full + 8 * b);
+        tc_commit(bars.k_empty + 8 * st);
+        return true;
+      };
+      if (ok) ok = issue_qk(0);
+      if (ok && n > 1) ok = issue_qk(1);
+      for (int i = 0; ok && i < n; ++i) {
+        const int b = i & 1, u = i >> 1;
+        if (i + 2 < n) {
+          // S buffer b is free once the softmax warpgroup has copied block i to registers
+          ok = mbar_wait(bars.s_free + 8 * b, u & 1, wc, kSiteSFree);
+          if (!ok) break;
+          tc_fence_after_sync();
+          ok = issue_qk(i + 2);
+          if (!ok) break;
+        }
+        const int st = i % kStagesV;
+        ok = mbar_wait(bars.p_full + 8 * b, u & 1, wc, kSitePFull);
+        if (!ok) break;
+        ok = mbar_wait(bars.v_full + 8 * st, (i / kStagesV) & 1, wc, kSiteVFull);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t sfp = tmem + kTmSFP + 8 * b, sfv = tmem + kTmSFV + 8 * b;
+        tc_cp_sf(sfp, base + kOffSFP + b * kSfBytes);
+        tc_cp_sf(sfp + 4, base + kOffSFP + b * kSfBytes + 512);
+        tc_cp_sf(sfv, base + kOffSFV + st * kSfBytes);
+        tc_cp_sf(sfv + 4, base + kOffSFV + st * kSfBytes + 512);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const uint64_t da =
+              make_smem_desc(base + kOffP + b * kTileBytes + 32 * j, 16, 512, kSwizzle64);
+          const uint64_t db =
+              make_smem_desc(base + kOffV + st * kTileBytes + 32 * j, 16, 512, kSwizzle64);
+          mma_nvf4(tmem + kTmO, da, db, idesc, sfp + 4 * j, sfv + 4 * j, (i > 0 || j > 0) ? 1u : 0u);
+        }
+        tc_commit(bars.pv_done + 8 * b);
+        tc_commit(bars.v_empty + 8 * st);
+      }
+      if (!ok) {
+        // bounded drain of the tensor-core work already issued, before tensor memory is freed
+        const uint64_t t0 = globaltimer_ns();
+        tc_commit(bars.drain);
+        while (!mbar_try_wait(bars.drain, 0) && globaltimer_ns() - t0 < 50ull * 1000 * 1000) {}
+      }
+    }
+  } else {
+    // =========================================== softmax warpgroups =============================
+    const int g = warp >> 2;        // warpgroup 0 / 1
+    const int row = tid & 127;      // tile row == tensor-memory lane
+    const uint32_t lane_addr = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+    float m_ref = kNegInf, l_sum = 0.f;
+    bool ok = true;
+
+    for (int i = g; ok && i < n; i += 2) {
+      const int u = i >> 1;
+      const int nb = n - 1 - i;
+      ok = __all_sync(0xffffffffu, mbar_wait(bars.s_full + 8 * g, u & 1, wc, kSiteSFull));
+      if (!ok) break;
+      tc_fence_after_sync();
+      float s[128];
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        tmem_ld32(lane_addr + (g ? kTmS1 : kTmS0) + 32 * c, reinterpret_cast<uint32_t*>(&s[32 * c]));
+      tc_wait_ld();
+      tc_fence_before_sync();
+      mbar_arrive(bars.s_free + 8 * g);
+
+      if (block_needs_mask(p, t, nb)) mask_row(s, causal_limit(p, t, row, nb));
+      float bm[8];
+      const float m_loc = row_block_max(s, bm);
+
+      // reference maximum handed over by the warpgroup of block i-1
+      float m_prev = kNegInf;
+      if (i > 0) {
+        ok = __all_sync(0xffffffffu,
+                        mbar_wait(bars.max_ready + 8 * (g ^ 1), ((i - 1) >> 1) & 1, wc, kSiteMaxReady));
+        if (!ok) break;
+        m_prev = s_max[(g ^ 1) * 128 + row];
+      }
+      const float m_new = next_reference(m_prev, m_loc, p.sl2);
+      s_max[g * 128 + row] = m_new;
+      mbar_arrive(bars.max_ready + 8 * g);
+
+      // own partial row sum follows the reference
+      if (m_new != m_ref) l_sum *= reference_factor(m_ref, m_new, p.sl2);
+      m_ref = m_new;
+
+      // correction: O holds blocks 0..i-1 relative to m_prev
+      if (i > 0 && __any_sync(0xffffffffu, m_new != m_prev)) {
+        ok = __all_sync(0xffffffffu,
+                        mbar_wait(bars.pv_done + 8 * (g ^ 1), ((i - 1) >> 1) & 1, wc, kSitePvDone));
+        if (!ok) break;
+        tc_fence_after_sync();
+        const float f = (m_new != m_prev) ? reference_factor(m_prev, m_new, p.sl2) : 1.f;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[32];
+          tmem_ld32(lane_addr + kTmO + 32 * c, o);
+          tc_wait_ld();
+#pragma unroll
+          for (int x = 0; x < 32; ++x) o[x] = __float_as_uint(__uint_as_float(o[x]) * f);
+          tmem_st32(lane_addr + kTmO + 32 * c, o);
+        }
+        tc_wait_st();
+      }
+
+      uint32_t pk[16], sfw[2];
+      l_sum += quantize_row(s, bm, m_ref, p.sl2, pk, sfw);
+
+      // P buffer g is free once PV of block i-2 has completed
+      if (u > 0) {
+        ok = __all_sync(0xffffffffu,
+                        mbar_wait(bars.pv_done + 8 * g, (u - 1) & 1, wc, kSitePvDone));
+        if (!ok) break;
+      }
+      uint8_t* sp = gbase + kOffP + g * kTileBytes;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        *reinterpret_cast<uint4*>(sp + sw64_offset(row, c)) =
+            make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+      }
+      uint8_t* ssf = gbase + kOffSFP + g * kSfBytes;
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        *reinterpret_cast<uint32_t*>(ssf + 512 * j + (row & 31) * 16 + (row >> 5) * 4) = sfw[j];
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();  // orders the O rescale stores before the issuer's next MMA
+      mbar_arrive(bars.p_full + 8 * g);
+    }
+
+    // ---- final combine of the two partial row sums ------------------------------------------------
+    if (ok && n > 0) {
+      s_fin[(g * 128 + row) * 2] = l_sum;
+      s_fin[(g * 128 + row) * 2 + 1] = m_ref;
+      mbar_arrive(bars.fin);
+      ok = __all_sync(0xffffffffu, mbar_wait(bars.fin, 0, wc, kSiteFin));
+      if (ok) {
+        const float l_other = s_fin[((g ^ 1) * 128 + row) * 2];
+        const float m_other = s_fin[((g ^ 1) * 128 + row) * 2 + 1];
+        const float m_fin = fmaxf(m_ref, m_other);
+        const float l_tot = l_sum * reference_factor(m_ref, m_fin, p.sl2) +
+                            l_other * reference_factor(m_other, m_fin, p.sl2);
+        l_sum = (m_fin == kNegInf) ? 0.f : l_tot;
+        m_ref = m_fin;
+        ok = __all_sync(0xffffffffu, mbar_wait(bars.pv_done + 8 * ((n - 1) & 1), ((n - 1) >> 1) & 1, wc,
+                                               kSiteFinalO));
+        tc_fence_after_sync();
+      }
+    }
+
+    // ---- epilogue: warpgroup g stores output columns [64 g, 64 g + 64) ------------------------------
+    if (ok && !poisoned) {
+      const int q_idx = t.m_blk * kBlockM + row;
+      __nv_bfloat16* orow =
+          p.out + t.b * p.o_stride_b + (int64_t)q_idx * p.o_stride_s + t.h * p.o_stride_h;
+      const bool empty = (n == 0) || !(l_sum > 0.f);
+      const float scale = empty ? 0.f : p.out_scale / l_sum;
+#pragma unroll 1
+      for (int c = 2 * g; c < 2 * g + 2; ++c) {
+        uint32_t o[32];
+        if (n > 0) {
+          tmem_ld32(lane_addr + kTmO + 32 * c, o);
+          tc_wait_ld();
+        }
+        if (empty) {
+#pragma unroll
+          for (int x = 0; x < 32; ++x) o[x] = 0u;
+        }
+        store_out_32(orow + 32 * c, o, scale);
+      }
+      if (g == 0 && p.lse != nullptr) {
+        p.lse[((int64_t)t.b * p.Hq + t.h) * p.Sq + q_idx] = finish_lse(m_ref, l_sum, p.sl2);
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == kIssuerWarp) tmem_dealloc(tmem, kTmemCols);
+}
+
+}  // namespace fa4

@@ -1,0 +1,164 @@
+// Small kernels around the attention forward: scale-factor layout conversion, the
+// hardware-contract probe (one Q K^T tile) and the bounded-wait self test.
+#pragma once
+#include "attn_serial.cuh"
+
+namespace fa4 {
+
+// ---------------------------------------------------------------------------------------------
+// Scale factors, linear (rows x cols bytes, row stride given) -> 128 x 4 tiles of 512 bytes.
+// One thread writes one 16-byte row of a tile chunk: destination offset (r % 32) * 16 holds
+// the scales of rows r, r + 32, r + 64, r + 96 (4 bytes each = 4 consecutive columns).
+// Grid: x = 32-row-group index over all tiles of all matrices; HBM-bound byte shuffling,
+// reads are 4-byte per row (the linear layout offers no more), writes are 16-byte coalesced.
+// ---------------------------------------------------------------------------------------------
+__global__ void sf_linear_to_tiled_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
+                                          int n_outer, int n_inner, int rows, int cols,
+                                          int64_t stride_outer, int64_t stride_inner,
+                                          int64_t stride_row) {
+  const int row_tiles = (rows + 127) / 128;
+  const int col_tiles = (cols + 3) / 4;
+  const int64_t total = (int64_t)n_outer * n_inner * row_tiles * col_tiles * 32;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int l = (int)(idx & 31);
+    int64_t tile = idx >> 5;
+    const int ct = (int)(tile % col_tiles);
+    tile /= col_tiles;
+    const int rt = (int)(tile % row_tiles);
+    tile /= row_tiles;
+    const int mi = (int)(tile % n_inner);
+    const int mo = (int)(tile / n_inner);
+    const uint8_t* m = src + mo * stride_outer + mi * stride_inner;
+    uint32_t w[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int r = rt * 128 + c * 32 + l;
+      uint32_t v = 0;
+      if (r < rows) {
+        const uint8_t* pr = m + (int64_t)r * stride_row + ct * 4;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          if (ct * 4 + k < cols) v |= (uint32_t)pr[k] << (8 * k);
+        }
+      }
+      w[c] = v;
+    }
+    reinterpret_cast<uint4*>(dst)[idx] = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Probe: S (128 x 128 fp32) = Q tile x K tile^T, head dim 128, through exactly the descriptors
+// the attention kernels use.  mode bit 0 = stage operands with plain stores (the path P takes)
+// instead of TMA.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128, 1)
+qk_tile_probe_kernel(const __grid_constant__ CUtensorMap tm_q,
+                     const __grid_constant__ CUtensorMap tm_k, const uint8_t* q, const uint8_t* k,
+                     const uint8_t* q_sf, const uint8_t* k_sf, float* s_out, int mode,
+                     uint32_t* status, uint64_t budget_ns) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gbase = smem_raw + (base - smem_u32(smem_raw));
+  constexpr uint32_t kOffQ = 0, kOffK = 8192, kOffSFQ = 16384, kOffSFK = 17408, kOffBar = 18432;
+  const uint32_t bar_load = base + kOffBar, bar_mma = base + kOffBar + 8;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + kOffBar + 16);
+  volatile uint32_t* s_abort = reinterpret_cast<volatile uint32_t*>(gbase + kOffBar + 20);
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const WaitCtx wc{s_abort, status, budget_ns};
+
+  if (tid == 0) {
+    *s_abort = 0u;
+    mbar_init(bar_load, 1);
+    mbar_init(bar_mma, 1);
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(base + kOffBar + 16, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+  bool ok = true;
+
+  if (mode & 1) {
+    // plain stores in the swizzled layout + scale chunks copied verbatim
+    for (int c = 0; c < 4; ++c) {
+      *reinterpret_cast<uint4*>(gbase + kOffQ + sw64_offset(tid, c)) =
+          *reinterpret_cast<const uint4*>(q + tid * 64 + c * 16);
+      *reinterpret_cast<uint4*>(gbase + kOffK + sw64_offset(tid, c)) =
+          *reinterpret_cast<const uint4*>(k + tid * 64 + c * 16);
+    }
+    if (tid < 64) {
+      *reinterpret_cast<uint4*>(gbase + kOffSFQ + tid * 16) = reinterpret_cast<const uint4*>(q_sf)[tid];
+      *reinterpret_cast<uint4*>(gbase + kOffSFK + tid * 16) = reinterpret_cast<const uint4*>(k_sf)[tid];
+    }
+    fence_proxy_async_smem();
+  } else {
+    if (tid == 0) {
+      mbar_arrive_expect_tx(bar_load, 2 * (kTileBytes + kSfBytes));
+      tma_load_4d(base + kOffQ, &tm_q, bar_load, 0, 0, 0, 0);
+      tma_load_4d(base + kOffK, &tm_k, bar_load, 0, 0, 0, 0);
+      bulk_load(base + kOffSFQ, q_sf, kSfBytes, bar_load);
+      bulk_load(base + kOffSFK, k_sf, kSfBytes, bar_load);
+    }
+    ok = __all_sync(0xffffffffu, mbar_wait(bar_load, 0, wc, 1));
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (ok) {
+    if (tid == 0) {
+      tc_fence_after_sync();
+      tc_cp_sf(tmem + kTmSFQ, base + kOffSFQ);
+      tc_cp_sf(tmem + kTmSFQ + 4, base + kOffSFQ + 512);
+      tc_cp_sf(tmem + kTmSFK, base + kOffSFK);
+      tc_cp_sf(tmem + kTmSFK + 4, base + kOffSFK + 512);
+      constexpr uint32_t idesc = make_idesc_nvf4(128, 128);
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const uint64_t da = make_smem_desc(base + kOffQ + 32 * j, 16, 512, kSwizzle64);
+        const uint64_t db = make_smem_desc(base + kOffK + 32 * j, 16, 512, kSwizzle64);
+        mma_nvf4(tmem + kTmS0, da, db, idesc, tmem + kTmSFQ + 4 * j, tmem + kTmSFK + 4 * j, j);
+      }
+      tc_commit(bar_mma);
+    }
+    ok = __all_sync(0xffffffffu, mbar_wait(bar_mma, 0, wc, 2));
+    if (ok) {
+      tc_fence_after_sync();
+      const uint32_t lane_addr = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld32(lane_addr + kTmS0 + 32 * c, r);
+        tc_wait_ld();
+#pragma unroll
+        for (int x = 0; x < 32; ++x) s_out[tid * 128 + 32 * c + x] = __uint_as_float(r[x]);
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, kTmemCols);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Bounded-wait self test: a barrier nothing arrives at.
+// ---------------------------------------------------------------------------------------------
+__global__ void wait_expiry_kernel(uint32_t* status, uint64_t budget_ns) {
+  __shared__ uint64_t bar;
+  __shared__ uint32_t abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0u;
+    mbar_init(smem_u32(&bar), 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+  const WaitCtx wc{&abort_flag, status, budget_ns};
+  (void)mbar_wait(smem_u32(&bar), 0, wc, 99);
+  __syncthreads();
+}
+
+}  // namespace fa4

@@ -1,0 +1,220 @@
+"""Python call surface of the NVFP4 attention forward.
+
+Mirrors ``flash_attn.cute.flash_attn_func`` of the reference
+(flash_attn/cute/interface.py:1753-1792 -> FlashAttnFunc.forward :1576-1633 -> _flash_attn_fwd
+:279-813): same positional surface, same tensor conventions ((batch, seqlen, heads, head_dim),
+GQA map ``h_kv = h // (Hq // Hkv)``, ``softmax_scale=None -> 1/sqrt(D)``, bottom-right aligned
+``causal``, returns ``(out, lse)`` with ``lse`` fp32 ``(B, Hq, Sq)`` or ``None``), same error
+behaviour (``AssertionError`` for malformed tensors, ``NotImplementedError`` for features that are
+not built), launch on the current CUDA stream with no host synchronisation.
+
+The reference asserts fp16/bf16 inputs (interface.py:370); this module is the branch an NVFP4
+overload takes before that assert.  Operands arrive either as :class:`NVFP4Tensor` triples through
+:func:`flash_attn_func`, or as raw tensors through :func:`flash_attn_fp4_func` whose scale
+arguments follow the descale convention of the reference's FP8 path
+(hopper/flash_attn_interface.py:81-83).  Output is bf16, as for the reference's quantised inputs
+(hopper/flash_api.cpp:859-863).
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Callable, Optional, Tuple
+
+import torch
+
+from . import _lib
+from .quant import NVFP4Tensor, sf_to_tiled
+
+VARIANT_AUTO, VARIANT_SERIAL, VARIANT_WS = 0, 1, 2
+
+
+def _validate_tensor(t, name, expected_shape, expected_dtype, expected_device):
+    # same checks and messages as flash_attn/cute/interface.py:231-236
+    assert t.shape == expected_shape, f"{name} shape {t.shape} != expected {expected_shape}"
+    assert t.dtype == expected_dtype, f"{name} dtype {t.dtype} != expected {expected_dtype}"
+    assert t.device == expected_device, f"{name} device {t.device} != expected {expected_device}"
+    assert t.is_cuda, f"{name} must be on CUDA"
+
+
+def _as_u8(t: torch.Tensor, name: str) -> torch.Tensor:
+    if t.dtype == torch.uint8:
+        return t
+    if t.dtype in (torch.float8_e4m3fn, getattr(torch, "float4_e2m1fn_x2", torch.uint8)):
+        return t.view(torch.uint8)
+    raise AssertionError(f"{name} must be uint8 / float8_e4m3fn / float4_e2m1fn_x2, got {t.dtype}")
+
+
+def _scalar(x, name: str) -> float:
+    if isinstance(x, torch.Tensor):
+        assert x.numel() == 1, f"{name} must be a python float or a 1-element tensor"
+        return float(x)  # reads the value (synchronises if it lives on the device)
+    return float(x)
+
+
+class DeviceStatus:
+    """One device word per CUDA device that the kernels report bounded-wait expiry into.
+
+    The word is checked lazily: :func:`check_status` reads it back (one small copy, which
+    synchronises) and raises if a kernel gave up; the attention call itself never synchronises.
+    """
+    _words = {}
+
+    @classmethod
+    def word(cls, device: torch.device) -> torch.Tensor:
+        idx = device.index if device.index is not None else torch.cuda.current_device()
+        w = cls._words.get(idx)
+        if w is None:
+            w = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+            cls._words[idx] = w
+        return w
+
+
+def check_status(device=None) -> None:
+    """Raise ``RuntimeError`` if a kernel on ``device`` recorded a failure since the last check."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    w = DeviceStatus.word(device)
+    v = int(w.item()) & 0xFFFFFFFF
+    if v != 0:
+        w.zero_()
+        code, site, blk = v >> 24, (v >> 16) & 0xFF, v & 0xFFFF
+        raise RuntimeError(f"fa4_nvfp4 kernel failure: code {code} (1 = bounded wait expired), "
+                           f"wait site {site}, block {blk}")
+
+
+def flash_attn_fp4_func(
+    q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+    q_sf: torch.Tensor, k_sf: torch.Tensor, v_sf: torch.Tensor,
+    q_scale, k_scale, v_scale,
+    softmax_scale: Optional[float] = None,
+    causal: bool = False,
+    return_lse: bool = False,
+    out: Optional[torch.Tensor] = None,
+    lse: Optional[torch.Tensor] = None,
+    sf_layout: str = "linear",
+    variant: int = VARIANT_AUTO,
+) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    """NVFP4 attention forward.
+
+    q (B,Sq,Hq,D/2), k (B,Sk,Hkv,D/2), v (B,Hkv,Dv,Sk/2): packed e2m1 bytes (V key-contiguous).
+    *_sf: e4m3 block scales, ``sf_layout="linear"``: (B,S,H,D/16) / (B,Hkv,Dv,Sk/16), converted
+    to the tiled layout by a small kernel; ``"tiled"``: already (B,H,ceil(rows/128),cols/4,512).
+    *_scale: fp32 per-tensor scales.  Returns ``(out bf16 (B,Sq,Hq,Dv), lse fp32 (B,Hq,Sq) | None)``.
+
+    Built so far: D = Dv = 128; Sq and Sk multiples of 128.  Anything else raises
+    ``NotImplementedError`` before a launch.
+    """
+    q, k, v = _as_u8(q, "q"), _as_u8(k, "k"), _as_u8(v, "v")
+    q_sf, k_sf, v_sf = _as_u8(q_sf, "q_sf"), _as_u8(k_sf, "k_sf"), _as_u8(v_sf, "v_sf")
+    assert q.dim() == 4 and k.dim() == 4 and v.dim() == 4, "q, k, v must be 4-D"
+    assert q.is_cuda and k.is_cuda and v.is_cuda, "inputs must be on CUDA"
+    q, k, v = (t if t.stride(-1) == 1 else t.contiguous() for t in (q, k, v))
+    B, Sq, Hq, Dh = q.shape
+    Bk, Sk, Hkv, Dhk = k.shape
+    Bv, Hv, Dv, Skh = v.shape
+    D = 2 * Dh
+    assert Bk == B and Bv == B, "batch size mismatch"
+    assert Dhk == Dh, "q and k head dims differ"
+    assert Hv == Hkv and Skh * 2 == Sk, f"v must be (B, Hkv, Dv, Sk/2), got {tuple(v.shape)}"
+    assert Hq % Hkv == 0, "num_head must be divisible by num_head_kv"
+    if D != 128 or Dv != 128:
+        raise NotImplementedError(f"head dims (D={D}, Dv={Dv}) not built; supported: (128, 128)")
+    if Sq % 128 != 0 or Sk % 128 != 0:
+        raise NotImplementedError("seqlen_q and seqlen_k must be multiples of 128")
+    device = q.device
+    if softmax_scale is None:
+        softmax_scale = 1.0 / math.sqrt(D)
+    if sf_layout == "linear":
+        _validate_tensor(q_sf, "q_sf", (B, Sq, Hq, D // 16), torch.uint8, device)
+        _validate_tensor(k_sf, "k_sf", (B, Sk, Hkv, D // 16), torch.uint8, device)
+        _validate_tensor(v_sf, "v_sf", (B, Hkv, Dv, Sk // 16), torch.uint8, device)
+        q_sf, k_sf, v_sf = (t if t.stride(-1) == 1 else t.contiguous() for t in (q_sf, k_sf, v_sf))
+        q_sf, k_sf, v_sf = sf_to_tiled(q_sf, 1, 2), sf_to_tiled(k_sf, 1, 2), sf_to_tiled(v_sf, 2, 1)
+    elif sf_layout == "tiled":
+        _validate_tensor(q_sf, "q_sf", (B, Hq, Sq // 128, D // 64, 512), torch.uint8, device)
+        _validate_tensor(k_sf, "k_sf", (B, Hkv, Sk // 128, D // 64, 512), torch.uint8, device)
+        _validate_tensor(v_sf, "v_sf", (B, Hkv, Dv // 128, Sk // 64, 512), torch.uint8, device)
+        assert q_sf.is_contiguous() and k_sf.is_contiguous() and v_sf.is_contiguous()
+    else:
+        raise ValueError(f"sf_layout must be 'linear' or 'tiled', got {sf_layout!r}")
+
+    if out is None:
+        out = torch.empty(B, Sq, Hq, Dv, dtype=torch.bfloat16, device=device)
+    else:
+        _validate_tensor(out, "out", (B, Sq, Hq, Dv), torch.bfloat16, device)
+        assert out.stride(-1) == 1
+    if lse is None:
+        lse = torch.empty(B, Hq, Sq, dtype=torch.float32, device=device) if return_lse else None
+    else:
+        _validate_tensor(lse, "lse", (B, Hq, Sq), torch.float32, device)
+        assert lse.is_contiguous()
+
+    p = _lib.Params()
+    p.struct_size = ctypes.sizeof(_lib.Params)
+    p.variant = int(variant)
+    p.q, p.k, p.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
+    p.q_sf, p.k_sf, p.v_sf = q_sf.data_ptr(), k_sf.data_ptr(), v_sf.data_ptr()
+    p.out = out.data_ptr()
+    p.lse = lse.data_ptr() if lse is not None else None
+    p.status = DeviceStatus.word(device).data_ptr()
+    p.q_stride_b, p.q_stride_s, p.q_stride_h = q.stride(0), q.stride(1), q.stride(2)
+    p.k_stride_b, p.k_stride_s, p.k_stride_h = k.stride(0), k.stride(1), k.stride(2)
+    p.v_stride_b, p.v_stride_h, p.v_stride_d = v.stride(0), v.stride(1), v.stride(2)
+    p.o_stride_b, p.o_stride_s, p.o_stride_h = out.stride(0), out.stride(1), out.stride(2)
+    p.B, p.Sq, p.Sk, p.Hq, p.Hkv, p.D, p.Dv = B, Sq, Sk, Hq, Hkv, D, Dv
+    p.causal = 1 if causal else 0
+    p.q_scale, p.k_scale, p.v_scale = (_scalar(q_scale, "q_scale"), _scalar(k_scale, "k_scale"),
+                                       _scalar(v_scale, "v_scale"))
+    p.softmax_scale = float(softmax_scale)
+    p.wait_budget_ns = 0
+    with torch.cuda.device(device):
+        stream = torch.cuda.current_stream(device).cuda_stream
+        rc = _lib.lib().fa4_nvfp4_fwd(ctypes.byref(p), stream)
+    _lib.check(rc, "fa4_nvfp4_fwd")
+    return out, lse
+
+
+def flash_attn_func(
+    q, k, v,
+    softmax_scale: Optional[float] = None,
+    causal: bool = False,
+    window_size: Tuple[Optional[int], Optional[int]] = (None, None),
+    learnable_sink: Optional[torch.Tensor] = None,
+    softcap: float = 0.0,
+    num_splits: int = 1,
+    pack_gqa: Optional[bool] = None,
+    deterministic: bool = False,
+    mask_mod: Optional[Callable] = None,
+    full_block_cnt: Optional[torch.Tensor] = None,
+    full_block_idx: Optional[torch.Tensor] = None,
+    mask_block_cnt: Optional[torch.Tensor] = None,
+    mask_block_idx: Optional[torch.Tensor] = None,
+    block_size: Optional[Tuple[int, int]] = None,
+    return_lse: bool = False,
+):
+    """Same signature as the reference's ``flash_attn_func`` (interface.py:1753-1772); q, k, v are
+    :class:`NVFP4Tensor`.  Keyword arguments of features that are not built raise
+    ``NotImplementedError``; ``pack_gqa`` and ``deterministic`` are accepted and ignored (the
+    forward is deterministic, and query heads of a kv head share K/V through L2 instead of being
+    packed into one tile)."""
+    if not all(isinstance(t, NVFP4Tensor) for t in (q, k, v)):
+        raise TypeError("flash_attn_func of this package takes NVFP4Tensor operands; "
+                        "see quantize_qkv()")
+    if window_size != (None, None) and tuple(window_size) != (None, 0 if causal else None):
+        raise NotImplementedError("sliding-window attention is not built")
+    if learnable_sink is not None:
+        raise NotImplementedError("learnable_sink is not built")
+    if softcap not in (0.0, None):
+        raise NotImplementedError("softcap is not built")
+    if num_splits != 1:
+        raise NotImplementedError("split-KV is not built (num_splits must be 1)")
+    if mask_mod is not None or any(t is not None for t in (full_block_cnt, full_block_idx,
+                                                           mask_block_cnt, mask_block_idx)):
+        raise NotImplementedError("mask_mod / block sparsity is not built")
+    layouts = {t.tiled for t in (q, k, v)}
+    if len(layouts) != 1:
+        q, k, v = (NVFP4Tensor(t.data, t.tiled_sf(), t.scale, True, t.is_v) for t in (q, k, v))
+    return flash_attn_fp4_func(
+        q.data, k.data, v.data, q.sf, k.sf, v.sf, q.scale, k.scale, v.scale,
+        softmax_scale=softmax_scale, causal=causal, return_lse=return_lse,
+        sf_layout="tiled" if q.tiled else "linear")

@@ -1,0 +1,123 @@
+"""NVFP4 quantisation of attention operands (torch ops; runs on whatever device the input is on).
+
+Format: e2m1 elements (two per byte, even index in the low nibble), one e4m3 scale per 16
+consecutive elements, one fp32 scale per tensor:
+    per-tensor scale = amax / (6 * 448)
+    block scale      = e4m3(block_amax / 6 / per-tensor scale)
+    element          = e2m1 round-to-nearest-even of x / (block scale * per-tensor scale)
+Q and K are blocked along the head dimension, V along the key axis (V is stored transposed,
+(B, Hkv, Dv, Sk), because 4-bit tensor-core operands must be contiguous along the contraction).
+
+The reference has no quantiser for this path (flash_attn/cute/interface.py:370 rejects anything
+but fp16/bf16); the nearest precedent is the FP8 path of the Hopper generation, which takes
+per-(batch, kv-head) descale factors (hopper/flash_attn_interface.py:81-83).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+_MID = (0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0)
+_TIE_UP = (False, True, False, True, False, True, False)
+
+
+def _e2m1_codes(x: torch.Tensor) -> torch.Tensor:
+    mag = x.abs()
+    code = torch.zeros_like(x, dtype=torch.uint8)
+    for mid, up in zip(_MID, _TIE_UP):
+        code += (mag >= mid).to(torch.uint8) if up else (mag > mid).to(torch.uint8)
+    sign = ((x < 0) & (code > 0)).to(torch.uint8)
+    return code | (sign << 3)
+
+
+def quantize_lastdim(x: torch.Tensor, scale: Optional[float] = None):
+    """x (..., n) float -> (packed uint8 (..., n/2), sf uint8-viewed e4m3 (..., n/16), scale)."""
+    assert x.shape[-1] % 16 == 0, "NVFP4 blocks are 16 elements"
+    xf = x.float()
+    if scale is None:
+        amax = float(xf.abs().max())
+        scale = amax / (6.0 * 448.0) if amax > 0 else 1.0
+    scale = float(torch.tensor(scale, dtype=torch.float32))  # round to fp32 once
+    xb = xf.reshape(*xf.shape[:-1], xf.shape[-1] // 16, 16)
+    bmax = xb.abs().amax(dim=-1)
+    sf8 = (bmax / 6.0 / scale).clamp(max=448.0).to(torch.float8_e4m3fn)
+    denom = (sf8.float() * scale).unsqueeze(-1)
+    scaled = torch.where(denom > 0, xb / denom, torch.zeros_like(xb))
+    codes = _e2m1_codes(scaled).reshape(xf.shape)
+    packed = codes[..., 0::2] | (codes[..., 1::2] << 4)
+    return packed.contiguous(), sf8.view(torch.uint8).contiguous(), scale
+
+
+_E2M1 = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+
+
+def dequantize_lastdim(packed: torch.Tensor, sf: torch.Tensor, scale: float) -> torch.Tensor:
+    """Inverse of quantize_lastdim, fp32."""
+    lut = torch.tensor(_E2M1 + tuple(-v for v in _E2M1), dtype=torch.float32, device=packed.device)
+    codes = torch.stack([packed & 0xF, packed >> 4], dim=-1).reshape(*packed.shape[:-1], -1)
+    vals = lut[codes.long()]
+    sff = sf.view(torch.float8_e4m3fn).float() * scale
+    vb = vals.reshape(*vals.shape[:-1], vals.shape[-1] // 16, 16) * sff.unsqueeze(-1)
+    return vb.reshape(vals.shape)
+
+
+def sf_to_tiled(sf: torch.Tensor, rows_dim: int, head_dim: Optional[int]) -> torch.Tensor:
+    """Linear block scales -> the tiled layout the kernel reads (see include/fa4_nvfp4.h).
+
+    ``sf`` is (B, S, H, C) with ``rows_dim=1, head_dim=2`` (Q, K) or (B, H, R, C) with
+    ``rows_dim=2, head_dim=1`` (V).  Returns uint8 (B, H, ceil(rows/128), ceil(C/4), 512).
+    Runs the library's conversion kernel on CUDA tensors; the result is scratch the attention
+    call reads.
+    """
+    assert sf.dim() == 4 and sf.dtype == torch.uint8 and sf.stride(-1) == 1
+    B = sf.shape[0]
+    H, R, C = sf.shape[head_dim], sf.shape[rows_dim], sf.shape[3]
+    out = torch.empty(B, H, (R + 127) // 128, (C + 3) // 4, 512, dtype=torch.uint8, device=sf.device)
+    if not sf.is_cuda:
+        raise RuntimeError("sf_to_tiled needs CUDA tensors (the conversion is a CUDA kernel)")
+    stream = torch.cuda.current_stream(sf.device).cuda_stream
+    rc = _lib.lib().fa4_nvfp4_sf_linear_to_tiled(
+        sf.data_ptr(), out.data_ptr(), B, H, R, C, sf.stride(0), sf.stride(head_dim),
+        sf.stride(rows_dim), stream)
+    _lib.check(rc, "fa4_nvfp4_sf_linear_to_tiled")
+    return out
+
+
+@dataclass
+class NVFP4Tensor:
+    """One quantised attention operand.
+
+    data   uint8, packed e2m1: (B, S, H, D/2) for q/k, (B, Hkv, Dv, Sk/2) for v
+    sf     uint8 (e4m3 bits): linear (B, S, H, D/16) / (B, Hkv, Dv, Sk/16), or tiled
+    scale  fp32 per-tensor scale
+    tiled  whether ``sf`` is already in the tiled layout
+    """
+    data: torch.Tensor
+    sf: torch.Tensor
+    scale: float
+    tiled: bool = False
+    is_v: bool = False
+
+    def tiled_sf(self) -> torch.Tensor:
+        if self.tiled:
+            return self.sf
+        return sf_to_tiled(self.sf, 2, 1) if self.is_v else sf_to_tiled(self.sf, 1, 2)
+
+    def dequantize(self) -> torch.Tensor:
+        """fp32 values in the reference layout (B, S, H, D) (linear scale factors only)."""
+        assert not self.tiled
+        x = dequantize_lastdim(self.data, self.sf, self.scale)
+        return x.permute(0, 3, 1, 2).contiguous() if self.is_v else x
+
+
+def quantize_qkv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor):
+    """bf16/fp32 (B,S,H,D) tensors in the reference layout -> three NVFP4Tensor (linear scales)."""
+    qd, qs, qg = quantize_lastdim(q)
+    kd, ks, kg = quantize_lastdim(k)
+    vt = v.permute(0, 2, 3, 1)  # (B, Hkv, Dv, Sk): blocks along the key axis
+    vd, vs, vg = quantize_lastdim(vt)
+    return (NVFP4Tensor(qd, qs, qg), NVFP4Tensor(kd, ks, kg), NVFP4Tensor(vd, vs, vg, is_v=True))

@@ -1,0 +1,163 @@
+/*
+ * fa4_nvfp4.h -- C ABI of the B200 (sm_100a) NVFP4 fused attention forward.
+ *
+ * One shared library (libfa4_nvfp4.so), plain C types only.  Every buffer is
+ * owned by the caller and lives in device memory unless stated otherwise; the
+ * library allocates nothing per call.  All entry points return 0 on success,
+ * a negative FA4_E_* code when an argument is rejected on the host (nothing is
+ * launched), or a positive CUDA error code (cudaError_t) when a CUDA runtime
+ * call fails.  Device-side failures (a bounded wait that ran out) are reported
+ * through the caller's `status` word, see fa4_nvfp4_params::status.
+ *
+ * Reference interface this boundary replaces (paths inside the reference
+ * project, graphcore-research/flash-attention):
+ *   flash_attn/cute/interface.py:279-813   _flash_attn_fwd  (validation, output
+ *       conventions, launch on the current stream)
+ *   flash_attn/cute/interface.py:785-803   the compiled-kernel call
+ *       fn(q, k, v, out, lse, softmax_scale, ...)  -> fa4_nvfp4_fwd
+ *   flash_attn/cute/flash_fwd_sm100.py:336-728  FlashAttentionForwardSm100.__call__
+ *       (TMA descriptors, grid, shared-memory opt-in) -> done inside fa4_nvfp4_fwd
+ * The reference has no NVFP4 signature (inputs are asserted fp16/bf16 at
+ * interface.py:370), so the operand formats below are defined here.
+ *
+ * Operand formats
+ *   q   (B, Sq, Hq,  D/2)  bytes, two e2m1 values per byte, low nibble = even index
+ *   k   (B, Sk, Hkv, D/2)  bytes
+ *   v   (B, Hkv, Dv, Sk/2) bytes: V is stored key-contiguous ("V transposed")
+ *                           because 4-bit tensor-core operands must be K-major
+ *   *_sf  e4m3 (unsigned use: scales are >= 0) scale of each block of 16
+ *         consecutive elements (along D for q and k, along the key axis for v),
+ *         in the 128x4 TILED layout described at fa4_nvfp4_sf_linear_to_tiled
+ *   q_scale, k_scale, v_scale  fp32 per-tensor scales; a value is
+ *         e2m1 * e4m3_block_scale * per_tensor_scale
+ *   out (B, Sq, Hq, Dv) bf16;  lse (B, Hq, Sq) fp32, natural log of the sum of
+ *         exp(softmax_scale * q.k) over the visible keys, -inf for a row that
+ *         sees no key (same conventions as interface.py:413-433 and
+ *         flash_fwd_sm100.py:2481-2501)
+ *   causal: key j visible to query i iff j <= i + Sk - Sq (bottom-right aligned,
+ *         flash_attn/cute/testing.py:276)
+ *   GQA: query head h reads kv head h / (Hq / Hkv)  (testing.py:362-363)
+ */
+#ifndef FA4_NVFP4_H_
+#define FA4_NVFP4_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FA4_NVFP4_ABI_VERSION 1
+
+/* host-side argument errors (returned negated) */
+enum {
+  FA4_E_NULL = 1,        /* a required pointer is NULL */
+  FA4_E_SHAPE = 2,       /* unsupported shape or divisibility */
+  FA4_E_STRIDE = 3,      /* stride not a multiple of 16 bytes / not contiguous where required */
+  FA4_E_ALIGN = 4,       /* base pointer not 16-byte aligned */
+  FA4_E_VARIANT = 5,     /* unknown kernel variant */
+  FA4_E_TENSORMAP = 6,   /* the driver rejected a TMA tensor map */
+  FA4_E_STRUCT = 7,      /* struct_size does not match this ABI */
+  FA4_E_TOO_LARGE = 8    /* problem exceeds a fixed capacity of the entry point */
+};
+
+/* device status word: 0 = ok; otherwise (code << 24) | (site << 16) | (blockIdx.x & 0xffff) */
+enum {
+  FA4_S_OK = 0,
+  FA4_S_WAIT_EXPIRED = 1 /* a bounded mbarrier wait ran out; `site` names the wait */
+};
+
+/* kernel variants */
+enum {
+  FA4_VARIANT_AUTO = 0,
+  FA4_VARIANT_SERIAL = 1, /* one warpgroup does every step in turn (bring-up / cross-check) */
+  FA4_VARIANT_WS = 2      /* warp-specialised load / MMA / softmax pipeline */
+};
+
+typedef struct fa4_nvfp4_params {
+  uint32_t struct_size;   /* = sizeof(fa4_nvfp4_params) */
+  int32_t variant;        /* FA4_VARIANT_* */
+
+  const void* q;          /* packed e2m1 */
+  const void* k;
+  const void* v;
+  const void* q_sf;       /* e4m3, tiled: (B, Hq,  ceil(Sq/128), D/64,  512) bytes */
+  const void* k_sf;       /* e4m3, tiled: (B, Hkv, ceil(Sk/128), D/64,  512) bytes */
+  const void* v_sf;       /* e4m3, tiled: (B, Hkv, ceil(Dv/128), Sk/64, 512) bytes */
+  void* out;              /* bf16 (B, Sq, Hq, Dv) */
+  float* lse;             /* fp32 (B, Hq, Sq) or NULL */
+  uint32_t* status;       /* one device word, zeroed by the caller; NULL = not reported */
+
+  /* strides in BYTES for the packed operands, in ELEMENTS for out */
+  int64_t q_stride_b, q_stride_s, q_stride_h;    /* innermost (D/2 bytes) is contiguous */
+  int64_t k_stride_b, k_stride_s, k_stride_h;
+  int64_t v_stride_b, v_stride_h, v_stride_d;    /* innermost (Sk/2 bytes) is contiguous */
+  int64_t o_stride_b, o_stride_s, o_stride_h;    /* innermost (Dv) is contiguous */
+
+  int32_t B, Sq, Sk, Hq, Hkv, D, Dv;
+  int32_t causal;
+  float q_scale, k_scale, v_scale;
+  float softmax_scale;
+  uint64_t wait_budget_ns; /* limit of every device-side wait; 0 = default (2 s) */
+} fa4_nvfp4_params;
+
+/*
+ * NVFP4 attention forward.  Replaces the compiled-kernel call of the reference
+ * (flash_attn/cute/interface.py:785-803).  Asynchronous on `cuda_stream`
+ * (a cudaStream_t; NULL = legacy default stream), no host synchronisation.
+ */
+int fa4_nvfp4_fwd(const fa4_nvfp4_params* p, void* cuda_stream);
+
+/*
+ * Scale-factor layout conversion, linear -> tiled.
+ *   src: rows x cols e4m3 bytes; element (r, c) of matrix m at
+ *        src + m_outer*stride_outer + m_inner*stride_inner + r*stride_row + c
+ *        (n_outer x n_inner matrices; for q_sf given as (B, S, H, D/16):
+ *        outer = batch, inner = head, stride_row = H*D/16)
+ *   dst: (n_outer, n_inner, ceil(rows/128), ceil(cols/4), 512) bytes; inside a
+ *        512-byte tile the scale of row r, column c sits at
+ *        (r % 32) * 16 + (r / 32) * 4 + c   -- the 32x4x4 chunk that one
+ *        `tcgen05.cp 32x128b.warpx4` moves to tensor memory.  Padding rows and
+ *        columns are written as zero.
+ * The reference has no scale-factor operand at all; this layout is the one the
+ * block-scaled tensor-core instruction consumes (flash_attn/cute/mma_sm100_desc.py
+ * documents only the non-scaled kinds).
+ */
+int fa4_nvfp4_sf_linear_to_tiled(const void* src, void* dst,
+                                 int32_t n_outer, int32_t n_inner,
+                                 int32_t rows, int32_t cols,
+                                 int64_t stride_outer, int64_t stride_inner,
+                                 int64_t stride_row, void* cuda_stream);
+
+/*
+ * Version / capability query (host only, never touches a GPU).
+ *   what = 0: ABI version; 1: number of supported head dims; 2+i: i-th supported
+ *   head dim; 100: default dynamic shared memory per CTA of the WS variant.
+ * Mirrors the head-dim validation of flash_attn/cute/interface.py:84-99.
+ */
+int fa4_nvfp4_query(int32_t what);
+
+/*
+ * Hardware-contract probe: one 128x128xD block-scaled tile S = A * B^T with
+ * A = q tile, B = k tile (same operand formats as above, one head, one batch,
+ * Sq = Sk = 128), written as fp32 (128,128) to `s_out`.  `mode` bit 0: stage the
+ * operands with plain shared-memory stores instead of TMA.  Used by the GPU
+ * tests to pin the descriptor and scale-factor layouts; no counterpart in the
+ * reference (its tests never look inside a tile).
+ */
+int fa4_nvfp4_debug_qk_tile(const void* q, const void* k, const void* q_sf,
+                            const void* k_sf, float* s_out, int32_t D,
+                            int32_t mode, uint32_t* status, void* cuda_stream);
+
+/*
+ * Bounded-wait self test: launches one CTA that waits on a barrier nothing
+ * arrives at, with a limit of `budget_ns`; the kernel must give up, record
+ * FA4_S_WAIT_EXPIRED in *status and return normally.  No counterpart in the
+ * reference, whose device waits are unbounded (flash_attn/cute/blackwell_helpers.py:519-526).
+ */
+int fa4_nvfp4_debug_wait_expiry(uint32_t* status, uint64_t budget_ns, void* cuda_stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FA4_NVFP4_H_ */
