@@ -1,0 +1,351 @@
+#!/usr/bin/env python
+"""Benchmark of the NVFP4 attention forward on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg2] [--impl ours|reference]
+
+One "step" is one forward over the whole workload held by a rank.  At N = 1 the workload is the
+causal GQA prefill configuration (B=4, Hq=32, Hkv=8, S=8192, D=128, the one the 50 %-of-FP4-peak
+target is quoted on).  With N > 1 (launched by torch.distributed.run, one rank per GPU) every rank
+holds one such workload -- the (batch, kv-head) units of a global batch of 4 N -- and nothing is
+exchanged on the data path: weak scaling, value = total FLOPs of all ranks / max-over-ranks time.
+
+Rank 0 prints ONE JSON line.  ``value`` is measured with inputs resident in HBM (scale factors
+already tiled, one kernel launch per step, CUDA events around each launch, L2 flushed between
+launches).  ``e2e`` is the same metric through the public Python API with HOST buffers: pinned
+host -> device copies of the packed operands and linear scale factors, the scale-factor tiling
+kernels, the attention kernel, and the device -> host copy of O and LSE, all inside the timed
+region.  ``cpu_baseline`` / ``--impl reference`` time the CPU restatement of the reference's
+``attention_ref`` (oracle/nvfp4_oracle.py) on a bounded sample of the same workload.
+"""
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (B, Hq, Hkv, S, D, causal, v_std, outlier_frac)
+    "cfg0": (1, 4, 4, 256, 128, False, 1.0, 0.0),
+    "cfg1": (4, 32, 32, 4096, 128, False, 1.0, 0.0),
+    "cfg2": (4, 32, 8, 8192, 128, True, 0.5, 0.0),
+    "cfg3": (1, 64, 8, 32768, 128, True, 1.0, 0.01),
+}
+FP4_NOMINAL_TFLOPS = 9000.0   # B200 dense FP4 (4 x the 2.25 PFLOP/s dense bf16)
+
+
+def parse_workload(name):
+    if name in WORKLOADS:
+        return WORKLOADS[name]
+    if name.startswith("sweep:"):  # sweep:D,S,causal(0/1)  with B*H = 128 (H = 16, B = 8)
+        d, s, c = (int(x) for x in name[6:].split(","))
+        return (8, 16, 16, s, d, bool(c), 1.0, 0.0)
+    raise SystemExit(f"unknown workload {name}")
+
+
+def flops_of(B, Hq, S, D, causal):
+    avg = S / 2 if causal else S                  # flash_attn/cute/bench_utils.py:15-38, Sq == Sk
+    return B * Hq * 2 * S * avg * (D + D)
+
+
+def algorithmic_bytes(B, Hq, Hkv, S, D):
+    per = lambda h: B * S * h * (D // 2 + D // 16)          # packed values + block scales
+    return per(Hq) + 2 * per(Hkv) + B * S * Hq * D * 2 + B * Hq * S * 4
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return {"bf16_tflops": d["bf16_tflops"], "hbm_gbs": d["hbm_gbs"], "source": "measured"}
+    return {"bf16_tflops": 1590.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU arm: the oracle's restatement of attention_ref on a bounded sample
+# ------------------------------------------------------------------------------------------------
+def cpu_sample_inputs(wl, seed=0):
+    B, Hq, Hkv, S, D, causal, v_std, _ = wl
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(1, S, 1, D, generator=g).bfloat16()
+    k = torch.randn(1, S, 1, D, generator=g).bfloat16()
+    v = (torch.randn(1, S, 1, D, generator=g) * v_std).bfloat16()
+    from flash_attention_b200 import quantize_qkv
+    Q, K, V = quantize_qkv(q, k, v)
+    return Q.dequantize(), K.dequantize(), V.dequantize()
+
+
+def cpu_reference_step(qd, kd, vd, causal):
+    from oracle import nvfp4_oracle as orc
+    return orc.attention_oracle_a(qd, kd, vd, causal=causal)
+
+
+def time_cpu(wl, steps, warmup):
+    """One step = one (batch, query-head) pair of the workload at full sequence length."""
+    B, Hq, Hkv, S, D, causal, _, _ = wl
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    qd, kd, vd = cpu_sample_inputs(wl)
+    for _ in range(warmup):
+        cpu_reference_step(qd, kd, vd, causal)
+    ts = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        cpu_reference_step(qd, kd, vd, causal)
+        ts.append(time.perf_counter() - t0)
+    fl = flops_of(1, 1, S, D, causal)
+    mean = sum(ts) / len(ts)
+    return {"value": fl / mean / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"1 of {B * Hq} (batch, query-head) pairs at full S={S}, D={D}, "
+                      f"causal={causal}; {steps} timed passes after {warmup} warm-up; "
+                      f"fp32 attention_ref restatement on dequantised NVFP4 inputs",
+            "ms_per_pass": mean * 1e3}
+
+
+def run_reference_arm(args, wl, rank, world):
+    if rank != 0:
+        return
+    B, Hq, Hkv, S, D, causal, _, _ = wl
+    steps = max(1, args.steps)
+    cb = time_cpu(wl, steps, args.warmup)
+    line = {
+        "impl": "reference", "metric": "nvfp4_attn_fwd_tflops", "value": cb["value"], "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup, "ms_per_step": cb["ms_per_pass"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": workload_config(args.workload, wl, world),
+        "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": cb["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "tokens_per_s": S / (cb["ms_per_pass"] * 1e-3) / Hq,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(name, wl, world):
+    B, Hq, Hkv, S, D, causal, v_std, outl = wl
+    return {"workload": f"{name}: NVFP4 attention forward, B={B} per GPU (global batch {B * world}), "
+                        f"Hq={Hq}, Hkv={Hkv}, Sq=Sk={S}, D={D}, causal={causal}",
+            "B_per_gpu": B, "global_batch": B * world, "Hq": Hq, "Hkv": Hkv, "seq_len": S, "head_dim": D,
+            "causal": causal, "v_std": v_std, "outlier_frac": outl,
+            "sharding": f"(batch, kv-head) units, {B * Hkv} per GPU, no collective on the data path",
+            "l2": "L2 flushed between timed launches (256 MiB write)"}
+
+
+# ------------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.p = None
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", f"--id={gpu_index}", f"--query-gpu={self.QUERY}",
+                                       "--format=csv,noheader,nounits", "-lms", "100"],
+                                      stdout=self.f, stderr=subprocess.DEVNULL)
+        except OSError:
+            pass
+
+    def stop(self):
+        if self.p is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.p.terminate()
+        try:
+            self.p.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.p.kill()
+        self.f.flush()
+        rows = [r.strip().split(", ") for r in open(self.f.name) if r.strip()]
+        os.unlink(self.f.name)
+        sm, mx, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1])); mx.append(float(r[2])); power.append(float(r[3]))
+            except ValueError:
+                continue
+            for nm, val in zip(names, r[5:9]):
+                if val.strip().lower() == "active":
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm),
+                "reasons": sorted(reasons)}
+
+
+def run_gpu_arm(args, wl, rank, local_rank, world):
+    import torch.distributed as dist
+    import flash_attention_b200 as fa
+    B, Hq, Hkv, S, D, causal, v_std, outl = wl
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    # ---- synthetic inputs of this rank's shard (global batch = B * world; this rank's B batches)
+    g = torch.Generator(device=dev).manual_seed(1000 + rank)
+    q = torch.randn(B, S, Hq, D, generator=g, device=dev, dtype=torch.bfloat16)
+    k = torch.randn(B, S, Hkv, D, generator=g, device=dev, dtype=torch.bfloat16)
+    v = (torch.randn(B, S, Hkv, D, generator=g, device=dev) * v_std).bfloat16()
+    if outl > 0:
+        n = max(1, int(round(outl * D)))
+        for t in (q, k):
+            idx = torch.randperm(D, generator=g, device=dev)[:n]
+            t[..., idx] *= 20.0
+    Q, K, V = fa.quantize_qkv(q, k, v)
+    del q, k, v
+    Qt, Kt, Vt = (fa.NVFP4Tensor(t.data, t.tiled_sf(), t.scale, True, t.is_v) for t in (Q, K, V))
+    out = torch.empty(B, S, Hq, D, dtype=torch.bfloat16, device=dev)
+    lse = torch.empty(B, Hq, S, dtype=torch.float32, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def step():
+        fa.flash_attn_fp4_func(Qt.data, Kt.data, Vt.data, Qt.sf, Kt.sf, Vt.sf, Qt.scale, Kt.scale,
+                               Vt.scale, causal=causal, return_lse=True, out=out, lse=lse,
+                               sf_layout="tiled")
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    fa.check_status(dev)
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+           for _ in range(args.steps)]
+    barrier()
+    t_wall0 = time.perf_counter()
+    for e0, e1 in evs:
+        flush.zero_()
+        e0.record()
+        step()
+        e1.record()
+    barrier()
+    t_wall = time.perf_counter() - t_wall0
+    dev_ms = sum(e0.elapsed_time(e1) for e0, e1 in evs)
+    fa.check_status(dev)
+
+    # ---- end to end through the public API with host buffers
+    host_in = [t.cpu().pin_memory() for t in (Q.data, K.data, V.data, Q.sf, K.sf, V.sf)]
+    host_out = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+    host_lse = torch.empty(lse.shape, dtype=lse.dtype).pin_memory()
+    h2d = sum(t.numel() * t.element_size() for t in host_in)
+    d2h = host_out.numel() * 2 + host_lse.numel() * 4
+
+    def e2e_step():
+        qd, kd, vd, qs, ks, vs = (t.to(dev, non_blocking=True) for t in host_in)
+        o, l = fa.flash_attn_func(fa.NVFP4Tensor(qd, qs, Q.scale), fa.NVFP4Tensor(kd, ks, K.scale),
+                                  fa.NVFP4Tensor(vd, vs, V.scale, is_v=True), causal=causal,
+                                  return_lse=True)
+        host_out.copy_(o, non_blocking=True)
+        host_lse.copy_(l, non_blocking=True)
+
+    e2e_steps = max(2, min(args.steps, 5))
+    e2e_step()
+    torch.cuda.synchronize()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+    clocks = sampler.stop() if sampler else None
+    fa.check_status(dev)
+
+    times = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    dev_ms, e2e_ms = (float(x) for x in times.cpu())
+
+    if rank == 0:
+        fl_rank = flops_of(B, Hq, S, D, causal)
+        ms_per_step = dev_ms / args.steps
+        tflops_total = fl_rank * world / (ms_per_step * 1e-3) / 1e12
+        tflops_gpu = tflops_total / world
+        peaks = measured_peaks()
+        fp4_peak = 4.0 * peaks["bf16_tflops"]
+        line = {
+            "metric": "nvfp4_attn_fwd_tflops", "value": tflops_total, "unit": "TFLOP/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "nvfp4", "data": "synthetic",
+            "config": workload_config(args.workload, wl, world),
+            "tflops_per_gpu": tflops_gpu,
+            "tokens_per_s": B * S * world / (ms_per_step * 1e-3),
+            "pct_fp4_peak_nominal": 100.0 * tflops_gpu / FP4_NOMINAL_TFLOPS,
+            "roofline": {
+                "bound": "tensor", "achieved": tflops_gpu, "peak": fp4_peak, "unit": "TFLOP/s",
+                "frac": tflops_gpu / fp4_peak,
+                "peak_note": f"4 x the {peaks['source']} cuBLAS bf16 burst figure "
+                             f"({peaks['bf16_tflops']} TFLOP/s): block-scaled e2m1 MMAs issue at 4x the "
+                             f"bf16 rate; nominal dense FP4 is {FP4_NOMINAL_TFLOPS} TFLOP/s",
+                "traffic": TRAFFIC_BYTES.get(args.workload),
+                "algorithmic_bytes": algorithmic_bytes(B, Hq, Hkv, S, D),
+                "hbm_gbs_achieved": algorithmic_bytes(B, Hq, Hkv, S, D) / (ms_per_step * 1e-3) / 1e9,
+            },
+            "e2e": {"value": fl_rank * world / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
+                    "launches_per_step": 4},
+            "gpu_launches": args.steps,
+            "wall_ms_timed_region": t_wall * 1e3,
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu:
+            cb = time_cpu(wl, 3, 1)
+            line["cpu_baseline"] = {k2: cb[k2] for k2 in ("value", "unit", "cores", "kind", "sample")}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the attention kernel,
+# from the ncu captures summarised under profiles/; None until captured.
+TRAFFIC_BYTES = {}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="cfg2")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    wl = parse_workload(args.workload)
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.gpus > 1 and world == 1:
+        # not under a launcher: start one rank per GPU ourselves
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
+               f"--nproc-per-node={args.gpus}", "--master-addr", "127.0.0.1", "--master-port", "29517",
+               os.path.abspath(__file__)] + sys.argv[1:]
+        raise SystemExit(subprocess.call(cmd))
+    if args.impl == "reference":
+        run_reference_arm(args, wl, rank, world)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (no CPU fallback); use --impl reference for the CPU arm")
+    run_gpu_arm(args, wl, rank, local_rank, world)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,79 @@
+"""Generate the golden fixtures in this directory from the REFERENCE's own code.
+
+Run once, in a container that has the reference checkout (it is not needed to run the tests):
+
+    python tests/golden/make_golden.py /path/to/reference
+
+What it pins: the CPU oracle's ``attention_oracle_a`` (oracle/nvfp4_oracle.py) against the
+reference's ``attention_ref`` (flash_attn/cute/testing.py:323-434, imported by file path so
+that ``flash_attn/__init__`` and its compiled extensions are not needed), on NVFP4-dequantised
+inputs: MHA / GQA / MQA head mapping, bottom-right aligned causal masks with Sq < Sk and
+Sq > Sk (fully masked rows), ragged lengths.  The LSE fixture is computed the way the
+reference's tests compute it (tests/cute/test_flash_attn.py:1534-1539: logsumexp of the masked,
+scaled scores, mask = triu(diagonal = Sk - Sq + 1)).
+
+Each fixture stores the quantised operands (packed e2m1 bytes, e4m3 block scales, fp32 tensor
+scale) and the reference's fp32 output; inputs are N(0,1) bf16 draws from the stated seed,
+quantised by oracle.nvfp4_oracle.quantize_nvfp4.
+"""
+import importlib.util
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+from oracle import nvfp4_oracle as orc  # noqa: E402
+
+CASES = [
+    # name, B, Sq, Sk, Hq, Hkv, D, causal, seed
+    ("mha_noncausal", 1, 128, 128, 2, 2, 128, False, 0),
+    ("gqa_causal_sq_lt_sk", 2, 64, 192, 4, 2, 128, True, 1),
+    ("mqa_causal_sq_gt_sk", 1, 160, 96, 2, 1, 128, True, 2),
+    ("mqa_noncausal_ragged", 1, 113, 208, 3, 1, 64, False, 3),
+]
+
+
+def load_reference_testing(ref_root):
+    path = os.path.join(ref_root, "flash_attn", "cute", "testing.py")
+    spec = importlib.util.spec_from_file_location("ref_cute_testing", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def main():
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref = load_reference_testing(ref_root)
+    torch.set_num_threads(4)
+    for name, B, Sq, Sk, Hq, Hkv, D, causal, seed in CASES:
+        g = torch.Generator().manual_seed(seed)
+        q = torch.randn(B, Sq, Hq, D, generator=g).bfloat16().float().numpy()
+        k = torch.randn(B, Sk, Hkv, D, generator=g).bfloat16().float().numpy()
+        v = torch.randn(B, Sk, Hkv, D, generator=g).bfloat16().float().numpy()
+        Q, K = orc.quantize_nvfp4(q), orc.quantize_nvfp4(k)
+        V = orc.quantize_nvfp4(np.ascontiguousarray(np.transpose(v, (0, 2, 3, 1))))  # (B,Hkv,Dv,Sk)
+        qd = torch.from_numpy(orc.dequantize_nvfp4(Q))
+        kd = torch.from_numpy(orc.dequantize_nvfp4(K))
+        vd = torch.from_numpy(np.ascontiguousarray(np.transpose(orc.dequantize_nvfp4(V), (0, 3, 1, 2))))
+        out_ref, _ = ref.attention_ref(qd, kd, vd, causal=causal, upcast=True)
+        kk = kd.repeat_interleave(Hq // Hkv, dim=2)
+        qk = torch.einsum("bshd,bthd->bhst", qd, kk) / (D ** 0.5)
+        if causal:
+            mask = torch.triu(torch.ones(Sq, Sk, dtype=torch.bool), diagonal=Sk - Sq + 1)
+            qk = qk.masked_fill(mask, float("-inf"))
+        lse_ref = torch.logsumexp(qk, dim=-1)
+        np.savez_compressed(
+            os.path.join(HERE, f"{name}.npz"),
+            q_data=Q.data, q_sf=Q.sf, q_scale=np.float32(Q.scale),
+            k_data=K.data, k_sf=K.sf, k_scale=np.float32(K.scale),
+            v_data=V.data, v_sf=V.sf, v_scale=np.float32(V.scale),
+            out_ref=out_ref.numpy().astype(np.float32), lse_ref=lse_ref.numpy().astype(np.float32),
+            causal=np.bool_(causal), seed=np.int64(seed))
+        print(name, out_ref.shape, float(out_ref.abs().max()))
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,187 @@
+"""CPU tests of the host side: the C ABI library loads and exports what include/fa4_nvfp4.h
+declares, rejects bad arguments before touching a GPU, the Python surface mirrors the reference's
+error behaviour, the product quantiser is bit-identical to the oracle's, and the sharding plan."""
+import ctypes
+import os
+import re
+import subprocess
+import sys
+import tempfile
+
+import numpy as np
+import pytest
+import torch
+
+import flash_attention_b200 as fa
+from flash_attention_b200 import _lib, shard
+from oracle import nvfp4_oracle as orc
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "fa4_nvfp4.h")
+
+
+def test_library_exports_every_declared_symbol():
+    L = fa.lib()
+    text = open(HEADER).read()
+    declared = set(re.findall(r"^int\s+(fa4_nvfp4_\w+)\s*\(", text, flags=re.M))
+    assert declared, "no declarations found in the header"
+    assert declared == set(_lib.EXPORTS) or declared >= set(_lib.EXPORTS)
+    for name in declared:
+        assert hasattr(L, name), f"{name} is declared but not exported"
+
+
+def test_params_struct_matches_header():
+    """sizeof / offsets of the ctypes mirror equal the C compiler's view of the header."""
+    src = r'''
+#include <stdio.h>
+#include <stddef.h>
+#include "fa4_nvfp4.h"
+int main(void) {
+  printf("%zu %zu %zu %zu %zu %zu\n", sizeof(fa4_nvfp4_params), offsetof(fa4_nvfp4_params, q),
+         offsetof(fa4_nvfp4_params, q_stride_b), offsetof(fa4_nvfp4_params, B),
+         offsetof(fa4_nvfp4_params, q_scale), offsetof(fa4_nvfp4_params, wait_budget_ns));
+  return 0;
+}'''
+    with tempfile.TemporaryDirectory() as d:
+        c = os.path.join(d, "t.c")
+        open(c, "w").write(src)
+        exe = os.path.join(d, "t")
+        subprocess.run(["gcc", "-std=c99", "-I", os.path.join(ROOT, "include"), c, "-o", exe], check=True)
+        got = [int(x) for x in subprocess.run([exe], capture_output=True, text=True, check=True).stdout.split()]
+    P = _lib.Params
+    assert got == [ctypes.sizeof(P), P.q.offset, P.q_stride_b.offset, P.B.offset, P.q_scale.offset,
+                   P.wait_budget_ns.offset]
+
+
+def test_query():
+    L = fa.lib()
+    assert L.fa4_nvfp4_query(0) == 1
+    n = L.fa4_nvfp4_query(1)
+    assert n >= 1 and 128 in [L.fa4_nvfp4_query(2 + i) for i in range(n)]
+    assert L.fa4_nvfp4_query(100) <= 227 * 1024
+
+
+def _good_params():
+    p = _lib.Params()
+    p.struct_size = ctypes.sizeof(_lib.Params)
+    for f in ("q", "k", "v", "q_sf", "k_sf", "v_sf", "out"):
+        setattr(p, f, 0x1000)
+    p.B, p.Sq, p.Sk, p.Hq, p.Hkv, p.D, p.Dv = 1, 128, 128, 2, 1, 128, 128
+    p.q_stride_b, p.q_stride_s, p.q_stride_h = 128 * 2 * 64, 2 * 64, 64
+    p.k_stride_b, p.k_stride_s, p.k_stride_h = 128 * 64, 64, 64
+    p.v_stride_b, p.v_stride_h, p.v_stride_d = 128 * 64, 128 * 64, 64
+    p.o_stride_b, p.o_stride_s, p.o_stride_h = 128 * 2 * 128, 2 * 128, 128
+    p.q_scale = p.k_scale = p.v_scale = 1.0
+    p.softmax_scale = 0.088
+    return p
+
+
+@pytest.mark.parametrize("mutate,code", [
+    (lambda p: setattr(p, "struct_size", 8), 7),
+    (lambda p: setattr(p, "q", None), 1),
+    (lambda p: setattr(p, "out", None), 1),
+    (lambda p: (setattr(p, "Hq", 3), setattr(p, "Hkv", 2)), 2),   # Hq not a multiple of Hkv
+    (lambda p: setattr(p, "D", 96), 2),
+    (lambda p: setattr(p, "Sq", 100), 2),
+    (lambda p: setattr(p, "Sk", 0), 2),
+    (lambda p: setattr(p, "softmax_scale", 0.0), 2),
+    (lambda p: setattr(p, "k", 0x1008), 4),
+    (lambda p: setattr(p, "q_stride_s", 72), 3),
+    (lambda p: setattr(p, "o_stride_h", 4), 3),
+    (lambda p: setattr(p, "variant", 9), 5),
+])
+def test_fwd_rejects_bad_arguments_on_host(mutate, code):
+    """Every rejection happens before any CUDA call, so this runs without a GPU."""
+    p = _good_params()
+    mutate(p)
+    assert fa.lib().fa4_nvfp4_fwd(ctypes.byref(p), None) == -code
+    assert fa.lib().fa4_nvfp4_fwd(None, None) == -1
+
+
+def test_aux_entry_points_reject_bad_arguments():
+    L = fa.lib()
+    assert L.fa4_nvfp4_sf_linear_to_tiled(None, 0x1000, 1, 1, 1, 1, 1, 1, 1, None) == -1
+    assert L.fa4_nvfp4_sf_linear_to_tiled(0x1000, 0x1000, 1, 1, 0, 1, 1, 1, 1, None) == -2
+    assert L.fa4_nvfp4_sf_linear_to_tiled(0x1000, 0x1004, 1, 1, 1, 1, 1, 1, 1, None) == -4
+    assert L.fa4_nvfp4_debug_qk_tile(0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 64, 0, None, None) == -2
+    assert L.fa4_nvfp4_debug_wait_expiry(None, 1000, None) == -1
+    assert L.fa4_nvfp4_debug_wait_expiry(0x1000, 0, None) == -2
+
+
+def test_python_surface_errors_before_launch():
+    q = torch.zeros(1, 128, 2, 64, dtype=torch.uint8)
+    sf = torch.zeros(1, 128, 2, 8, dtype=torch.uint8)
+    v = torch.zeros(1, 2, 128, 64, dtype=torch.uint8)
+    vsf = torch.zeros(1, 2, 128, 8, dtype=torch.uint8)
+    with pytest.raises(AssertionError, match="CUDA"):
+        fa.flash_attn_fp4_func(q, q, v, sf, sf, vsf, 1.0, 1.0, 1.0)
+    with pytest.raises(AssertionError):
+        fa.flash_attn_fp4_func(q.float(), q, v, sf, sf, vsf, 1.0, 1.0, 1.0)
+    with pytest.raises(TypeError):
+        fa.flash_attn_func(q, q, v)
+    Q = fa.NVFP4Tensor(q, sf, 1.0)
+    V = fa.NVFP4Tensor(v, vsf, 1.0, is_v=True)
+    for kw in ({"window_size": (128, 0)}, {"softcap": 30.0}, {"num_splits": 2},
+               {"learnable_sink": torch.zeros(2)}, {"mask_mod": lambda *a: True}):
+        with pytest.raises(NotImplementedError):
+            fa.flash_attn_func(Q, Q, V, **kw)
+
+
+def test_product_quantiser_is_bit_identical_to_oracle():
+    rng = np.random.default_rng(1)
+    x = (rng.standard_normal((2, 48, 3, 128)) * rng.choice([0.1, 1.0, 30.0], size=(2, 48, 3, 1))).astype(np.float32)
+    x[0, 0, 0, :16] = 0.0
+    a = orc.quantize_nvfp4(x)
+    d, s, g = fa.quantize_lastdim(torch.from_numpy(x))
+    assert np.array_equal(a.data, d.numpy()) and np.array_equal(a.sf, s.numpy()) and a.scale == g
+    assert np.array_equal(orc.dequantize_nvfp4(a), fa.dequantize_lastdim(d, s, g).numpy())
+    q, k, v = (torch.from_numpy(x), torch.from_numpy(x[:, :, :1]), torch.from_numpy(x[:, :, :1] * 0.5))
+    Q, K, V = fa.quantize_qkv(q, k, v)
+    assert V.data.shape == (2, 1, 128, 24) and V.sf.shape == (2, 1, 128, 3) and V.is_v
+    assert V.dequantize().shape == (2, 48, 1, 128)
+
+
+def test_shard_plan_covers_every_unit_once():
+    for B, Hkv, world in [(4, 8, 1), (4, 8, 2), (4, 8, 4), (4, 8, 8), (1, 8, 8), (8, 16, 8), (4, 8, 16)]:
+        seen = np.zeros((B, Hkv), dtype=int)
+        for r in range(world):
+            s = shard.plan_shard(B, Hkv, world, r)
+            seen[s.b0:s.b1, s.h0:s.h1] += 1
+            assert s.units == B * Hkv // world
+        assert (seen == 1).all()
+    with pytest.raises(ValueError):
+        shard.plan_shard(3, 8, 5, 0)
+    with pytest.raises(ValueError):
+        shard.plan_shard(2, 6, 3, 0)     # 4 units per rank straddles a batch boundary
+
+
+def _gloo_worker(rank, world, port, tmp):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    sys.path.insert(0, ROOT)
+    from tests.helpers import make_qkv
+    B, Sq, Sk, Hq, Hkv, D = 2, 128, 128, 4, 2, 128
+    q, k, v = make_qkv(B, Sq, Sk, Hq, Hkv, D, seed=5)
+    Q, K, V = fa.quantize_qkv(q, k, v)                      # scales from the WHOLE tensors
+    s = shard.plan_shard(B, Hkv, world, rank)
+    Qs, Ks, Vs = shard.shard_operands(Q, K, V, s)
+    # stand-in for the kernel on CPU ranks: the oracle on this rank's slice
+    o, l = orc.attention_oracle_a(Qs.dequantize(), Ks.dequantize(), Vs.dequantize(), causal=True)
+    full_o, full_l = shard.gather_output(o, l, s, B, Hq, Hkv)
+    ref_o, ref_l = orc.attention_oracle_a(Q.dequantize(), K.dequantize(), V.dequantize(), causal=True)
+    ok = torch.equal(full_o, ref_o) and torch.equal(full_l, ref_l)
+    open(os.path.join(tmp, f"ok{rank}"), "w").write(str(ok))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_sharded_run_equals_unsharded_gloo_world2():
+    """World size 2 on CPU (gloo): shard -> per-rank attention -> all-gather reproduces the
+    single-rank result bit for bit (per-tensor scales are global)."""
+    import torch.multiprocessing as mp
+    with tempfile.TemporaryDirectory() as tmp:
+        port = 29500 + (os.getpid() % 2000)
+        mp.spawn(_gloo_worker, args=(2, port, tmp), nprocs=2, join=True)
+        assert [open(os.path.join(tmp, f"ok{r}")).read() for r in range(2)] == ["True", "True"]
