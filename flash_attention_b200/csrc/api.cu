@@ -191,3 +191,87 @@ extern "C" int fa4_nvfp4_debug_wait_expiry(uint32_t* status, uint64_t budget_ns,
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : (int)e;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Forward from LINEAR scale factors without any allocation.
+//
+// The regular route for linear scale factors needs scratch memory: three tiled copies of the
+// scales that the caller (the Python wrapper) allocates before calling
+// fa4_nvfp4_sf_linear_to_tiled and fa4_nvfp4_fwd.  Some hosts cannot do that: a serving
+// process that handed every byte of device memory to its own arena at start-up, or a
+// steady-state loop that runs under a "no cudaMalloc" rule because the call synchronises the
+// device.  For them the scratch lives in the library image instead: one fixed array per GPU,
+// resident from the moment the library is loaded on that GPU until the process exits.
+//
+// The array name below is only a host-side handle; the device address is looked up once per
+// device with cudaGetSymbolAddress and cached.
+// ---------------------------------------------------------------------------------------------
+#define FA4_STATIC_SCRATCH_BYTES (16u << 20)
+static __device__ __align__(256) uint8_t g_sf_scratch[FA4_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_scratch_mutex;
+uint8_t* g_scratch_addr[kMaxDevices] = {};
+
+// Device address of g_sf_scratch on the CURRENT device (looked up on first use per device).
+int scratch_address(uint8_t** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return -FA4_E_SHAPE;
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (g_scratch_addr[dev] == nullptr) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_sf_scratch);
+    if (e != cudaSuccess) return (int)e;
+    g_scratch_addr[dev] = static_cast<uint8_t*>(ptr);
+  }
+  *out = g_scratch_addr[dev];
+  return 0;
+}
+
+inline int64_t tiled_sf_bytes(int64_t n_mats, int64_t rows, int64_t cols) {
+  return n_mats * ((rows + 127) / 128) * ((cols + 3) / 4) * 512;
+}
+}  // namespace
+
+extern "C" int fa4_nvfp4_fwd_linear_sf_noalloc(const fa4_nvfp4_params* p, void* cuda_stream) {
+  if (p == nullptr) return -FA4_E_NULL;
+  if (p->struct_size != sizeof(fa4_nvfp4_params)) return -FA4_E_STRUCT;
+  if (!p->q_sf || !p->k_sf || !p->v_sf) return -FA4_E_NULL;
+  if (p->B <= 0 || p->Sq <= 0 || p->Sk <= 0 || p->Hq <= 0 || p->Hkv <= 0 || p->D <= 0 || p->Dv <= 0)
+    return -FA4_E_SHAPE;
+  if (p->D % 16 != 0 || p->Sk % 16 != 0) return -FA4_E_SHAPE;
+  const int64_t q_bytes = tiled_sf_bytes((int64_t)p->B * p->Hq, p->Sq, p->D / 16);
+  const int64_t k_bytes = tiled_sf_bytes((int64_t)p->B * p->Hkv, p->Sk, p->D / 16);
+  const int64_t v_bytes = tiled_sf_bytes((int64_t)p->B * p->Hkv, p->Dv, p->Sk / 16);
+  if (q_bytes + k_bytes + v_bytes > (int64_t)FA4_STATIC_SCRATCH_BYTES) return -FA4_E_TOO_LARGE;
+
+  uint8_t* scratch = nullptr;
+  if (int e = scratch_address(&scratch)) return e;
+  uint8_t* q_t = scratch;
+  uint8_t* k_t = q_t + q_bytes;   // multiples of 512: every region stays 256-byte aligned
+  uint8_t* v_t = k_t + k_bytes;
+
+  const int64_t cq = p->D / 16, cv = p->Sk / 16;
+  // q_sf (B, Sq, Hq, D/16) and k_sf (B, Sk, Hkv, D/16): matrix (b, h) has row stride H * D/16
+  if (int e = fa4_nvfp4_sf_linear_to_tiled(p->q_sf, q_t, p->B, p->Hq, p->Sq, (int)cq,
+                                           (int64_t)p->Sq * p->Hq * cq, cq, (int64_t)p->Hq * cq,
+                                           cuda_stream))
+    return e;
+  if (int e = fa4_nvfp4_sf_linear_to_tiled(p->k_sf, k_t, p->B, p->Hkv, p->Sk, (int)cq,
+                                           (int64_t)p->Sk * p->Hkv * cq, cq, (int64_t)p->Hkv * cq,
+                                           cuda_stream))
+    return e;
+  // v_sf (B, Hkv, Dv, Sk/16): matrix (b, h) is contiguous
+  if (int e = fa4_nvfp4_sf_linear_to_tiled(p->v_sf, v_t, p->B, p->Hkv, p->Dv, (int)cv,
+                                           (int64_t)p->Hkv * p->Dv * cv, (int64_t)p->Dv * cv, cv,
+                                           cuda_stream))
+    return e;
+  fa4_nvfp4_params tiled = *p;
+  tiled.q_sf = q_t;
+  tiled.k_sf = k_t;
+  tiled.v_sf = v_t;
+  return fa4_nvfp4_fwd(&tiled, cuda_stream);
+}

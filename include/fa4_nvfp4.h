@@ -157,6 +157,32 @@ int fa4_nvfp4_debug_qk_tile(const void* q, const void* k, const void* q_sf,
  */
 int fa4_nvfp4_debug_wait_expiry(uint32_t* status, uint64_t budget_ns, void* cuda_stream);
 
+/*
+ * Forward from LINEAR scale factors for hosts that cannot allocate device memory.
+ * No counterpart in the reference (which allocates its outputs with torch and has no scale
+ * factors at all).
+ *
+ * Same contract as fa4_nvfp4_fwd except that p->q_sf, p->k_sf, p->v_sf are the linear, fully
+ * contiguous layouts (B, Sq, Hq, D/16), (B, Sk, Hkv, D/16), (B, Hkv, Dv, Sk/16).  The tiled copies
+ * the kernel reads are staged in a fixed 16 MiB array that is part of the library image on every
+ * GPU the library is loaded on (FA4_NVFP4_STATIC_SCRATCH_BYTES), so the call performs no
+ * cudaMalloc / cudaFree and needs no workspace argument.  Meant for callers whose device memory
+ * is entirely owned by their own arena, or whose steady-state loop must not call the allocator.
+ *
+ * Limits and rules:
+ *  - the three tiled scale-factor tensors together must fit: sum over q, k, v of
+ *    matrices * ceil(rows/128) * ceil(cols/4) * 512 bytes <= 16 MiB, else -FA4_E_TOO_LARGE
+ *    (B=4, Hq=32, Hkv=8, S=8192, D=128 needs 12 MiB);
+ *  - the first call on a device looks the array's device address up (cudaGetSymbolAddress, with
+ *    that device current); make that first call outside any stream capture;
+ *  - all calls on a device share the one array, and it keeps whatever the previous call left
+ *    there.  Each call rewrites every byte it later reads (padding included), so nothing has to
+ *    be cleared, but two calls that overlap on the GPU (different streams without an ordering
+ *    between them) race on it: serialise them.
+ */
+#define FA4_NVFP4_STATIC_SCRATCH_BYTES (16u << 20)
+int fa4_nvfp4_fwd_linear_sf_noalloc(const fa4_nvfp4_params* p, void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif

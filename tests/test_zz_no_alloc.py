@@ -1,0 +1,81 @@
+"""The allocation-free entry point, fa4_nvfp4_fwd_linear_sf_noalloc, against the regular one.
+
+Some hosts of this library may not allocate device memory while they run (their own arena owns
+all of it, or their steady-state loop forbids the allocator because cudaMalloc synchronises the
+device).  For them the scratch that the linear-scale-factor route needs sits in a fixed array
+inside the library.  This file checks, through the C ABI, that the entry point gives exactly the
+bits of the regular route, twice in a row with different problems (the array keeps the previous
+call's contents, so the second call would show stale data if anything were left unwritten), and
+that it refuses a problem whose scale factors exceed the array.
+
+Named test_zz_* so that pytest collects it last."""
+import ctypes
+
+import pytest
+import torch
+
+import flash_attention_b200 as fa
+from flash_attention_b200 import _lib
+from flash_attention_b200.interface import DeviceStatus
+from tests.helpers import make_qkv
+
+pytestmark = pytest.mark.gpu
+
+
+def _params(Q, K, V, out, lse, causal, status):
+    B, Sq, Hq, _ = Q.data.shape
+    _, Sk, Hkv, _ = K.data.shape
+    p = _lib.Params()
+    p.struct_size = ctypes.sizeof(_lib.Params)
+    p.variant = 0
+    p.q, p.k, p.v = Q.data.data_ptr(), K.data.data_ptr(), V.data.data_ptr()
+    p.q_sf, p.k_sf, p.v_sf = Q.sf.data_ptr(), K.sf.data_ptr(), V.sf.data_ptr()
+    p.out, p.lse, p.status = out.data_ptr(), lse.data_ptr(), status.data_ptr()
+    p.q_stride_b, p.q_stride_s, p.q_stride_h = Q.data.stride(0), Q.data.stride(1), Q.data.stride(2)
+    p.k_stride_b, p.k_stride_s, p.k_stride_h = K.data.stride(0), K.data.stride(1), K.data.stride(2)
+    p.v_stride_b, p.v_stride_h, p.v_stride_d = V.data.stride(0), V.data.stride(1), V.data.stride(2)
+    p.o_stride_b, p.o_stride_s, p.o_stride_h = out.stride(0), out.stride(1), out.stride(2)
+    p.B, p.Sq, p.Sk, p.Hq, p.Hkv, p.D, p.Dv = B, Sq, Sk, Hq, Hkv, 128, 128
+    p.causal = 1 if causal else 0
+    p.q_scale, p.k_scale, p.v_scale = Q.scale, K.scale, V.scale
+    p.softmax_scale = 128 ** -0.5
+    return p
+
+
+def test_noalloc_entry_matches_regular_entry_twice_in_a_row(cuda_device):
+    dev = cuda_device
+    L = fa.lib()
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    # the larger problem first, so that the second call finds the array full of other data
+    for (B, Sq, Sk, Hq, Hkv, causal, seed) in [(2, 512, 384, 4, 2, True, 21), (1, 128, 256, 2, 1, False, 22)]:
+        q, k, v = make_qkv(B, Sq, Sk, Hq, Hkv, 128, seed=seed, device=dev)
+        Q, K, V = fa.quantize_qkv(q, k, v)
+        assert Q.sf.is_contiguous() and K.sf.is_contiguous() and V.sf.is_contiguous()
+        want_o, want_l = fa.flash_attn_fp4_func(Q.data, K.data, V.data, Q.sf, K.sf, V.sf, Q.scale,
+                                                K.scale, V.scale, causal=causal, return_lse=True)
+        out = torch.full((B, Sq, Hq, 128), float("nan"), dtype=torch.bfloat16, device=dev)
+        lse = torch.full((B, Hq, Sq), float("nan"), dtype=torch.float32, device=dev)
+        status = DeviceStatus.word(dev)
+        p = _params(Q, K, V, out, lse, causal, status)
+        before = torch.cuda.memory_allocated(dev)
+        rc = L.fa4_nvfp4_fwd_linear_sf_noalloc(ctypes.byref(p), stream)
+        assert rc == 0
+        assert torch.cuda.memory_allocated(dev) == before      # nothing came from torch's allocator
+        torch.cuda.synchronize()
+        fa.check_status(dev)
+        # same kernels on the same bytes: tolerance zero
+        assert torch.equal(out, want_o) and torch.equal(lse, want_l)
+
+
+def test_noalloc_entry_rejects_what_does_not_fit():
+    """Host-side checks only: no GPU work is started for a rejected call."""
+    L = fa.lib()
+    p = _lib.Params()
+    p.struct_size = ctypes.sizeof(_lib.Params)
+    for f in ("q", "k", "v", "q_sf", "k_sf", "v_sf", "out"):
+        setattr(p, f, 0x1000)
+    p.B, p.Sq, p.Sk, p.Hq, p.Hkv, p.D, p.Dv = 8, 8192, 8192, 32, 8, 128, 128   # 24 MiB of scales
+    assert L.fa4_nvfp4_fwd_linear_sf_noalloc(ctypes.byref(p), None) == -8
+    p.struct_size = 4
+    assert L.fa4_nvfp4_fwd_linear_sf_noalloc(ctypes.byref(p), None) == -7
+    assert L.fa4_nvfp4_fwd_linear_sf_noalloc(None, None) == -1
