@@ -159,13 +159,8 @@ attn_fwd_serial_kernel(const __grid_constant__ CUtensorMap tm_q,
         l_sum *= f;
       }
       m_ref = m_new;
-      uint32_t pk[16], sfw[2];
-      l_sum += quantize_row(s, bm, m_ref, p.sl2, pk, sfw);
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        *reinterpret_cast<uint4*>(gbase + kOffP + sw64_offset(row, c)) =
-            make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-      }
+      uint32_t sfw[2];
+      l_sum += quantize_row(s, bm, m_ref, p.sl2, gbase + kOffP, row, sfw);
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         *reinterpret_cast<uint32_t*>(gbase + kOffSFP + 512 * j + (row & 31) * 16 + (row >> 5) * 4) =

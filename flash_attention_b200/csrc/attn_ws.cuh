@@ -1,11 +1,15 @@
 // Warp-specialised variant: the production kernel.
 //
-// Roles of the 10 warps of a CTA (one CTA per SM, one 128-row query tile per CTA):
+// Roles of the 12 warps of a CTA (one CTA per SM, one 128-row query tile per CTA):
 //   warps 0-3  softmax warpgroup 0: K/V blocks 0, 2, 4, ... of the tile (visit order)
 //   warps 4-7  softmax warpgroup 1: K/V blocks 1, 3, 5, ...
 //   warp  8    TMA producer: Q once, then K and V tiles with their scale factors into two rings
 //   warp  9    tensor-core issuer: tcgen05.cp of scale factors, block-scaled tcgen05.mma for
 //              S = Q K^T (two S buffers in tensor memory) and O += P V; owns tensor memory
+//   warps 10-11 idle: they complete the third warpgroup so that registers can be moved from it
+//              to the softmax warpgroups with setmaxnreg (40 vs 232 per thread, the split the
+//              reference uses between its load/MMA warps and softmax warps,
+//              flash_fwd_sm100.py:273-292)
 //
 // The reference kernel (flash_attn/cute/flash_fwd_sm100.py:216-222) keeps two 128-row query
 // stages with S and O for both in tensor memory (4 x 128 columns = all of it).  The block-scaled
@@ -39,7 +43,9 @@ namespace ws {
 
 constexpr int kStagesK = 4;
 constexpr int kStagesV = 4;
-constexpr int kThreads = 320;
+constexpr int kThreads = 384;
+constexpr int kRegsSoftmax = 232;
+constexpr int kRegsOther = 40;
 constexpr int kProducerWarp = 8;
 constexpr int kIssuerWarp = 9;
 
@@ -147,6 +153,9 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
   const int n = poisoned ? 0 : t.n_blocks;
   constexpr uint32_t idesc = make_idesc_nvf4(128, 128);
 
+  if (warp >= 8) {
+    // registers move from this warpgroup to the softmax warpgroups
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
   if (warp == kProducerWarp) {
     // =========================================== TMA producer ===================================
     if (lane == 0 && n > 0) {
@@ -269,8 +278,10 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         while (!mbar_try_wait(bars.drain, 0) && globaltimer_ns() - t0 < 50ull * 1000 * 1000) {}
       }
     }
+  }
   } else {
     // =========================================== softmax warpgroups =============================
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
     const int g = warp >> 2;        // warpgroup 0 / 1
     const int row = tid & 127;      // tile row == tensor-memory lane
     const uint32_t lane_addr = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
@@ -330,21 +341,14 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         tc_wait_st();
       }
 
-      uint32_t pk[16], sfw[2];
-      l_sum += quantize_row(s, bm, m_ref, p.sl2, pk, sfw);
-
       // P buffer g is free once PV of block i-2 has completed
       if (u > 0) {
         ok = __all_sync(0xffffffffu,
                         mbar_wait(bars.pv_done + 8 * g, (u - 1) & 1, wc, kSitePvDone));
         if (!ok) break;
       }
-      uint8_t* sp = gbase + kOffP + g * kTileBytes;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        *reinterpret_cast<uint4*>(sp + sw64_offset(row, c)) =
-            make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-      }
+      uint32_t sfw[2];
+      l_sum += quantize_row(s, bm, m_ref, p.sl2, gbase + kOffP + g * kTileBytes, row, sfw);
       uint8_t* ssf = gbase + kOffSFP + g * kSfBytes;
 #pragma unroll
       for (int j = 0; j < 2; ++j) {

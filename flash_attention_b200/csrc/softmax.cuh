@@ -6,6 +6,7 @@
 // Behaviour kept from the reference's SoftmaxSm100 (flash_attn/cute/softmax.py:169-279):
 //   * the running row maximum is kept in raw score units and the scale
 //     (softmax_scale * log2 e) is applied inside one FMA      (softmax.py:222-235)
+//   * packed two-wide fp32 FMA / ADD for the scale and the row sum (softmax.py:231)
 //   * lazy rescale: the reference maximum only moves when the new maximum exceeds it by more
 //     than a threshold in log2 units                          (softmax.py:203-209)
 //   * a row that has seen no key uses 0 in place of -inf      (softmax.py:197-204)
@@ -14,9 +15,15 @@
 // New here (the reference converts P to bf16/fp16, flash_fwd_sm100.py:2194-2196): P becomes
 // e2m1 with one ue4m3 scale per 16 consecutive keys, the operand format of the block-scaled
 // P.V tensor-core instruction.  The scale of a block is a power of two, 2^e with
-//   e = clamp(ceil(log2(block max of p') - log2 6), -9, 8),    p' = 2^kShift * p,
+//   e = clamp(ceil(log2(block max of p') - log2 6), kEMin, 8),    p' = 2^kShift * p,
 // so that the block maximum lands in (3, 6] of the e2m1 grid, and p'/2^e is produced directly
 // by the exponential (the exponent offset absorbs e), i.e. the quantisation costs no multiply.
+//
+// Pipe budget per 128x128 block on one SM (measured instruction rates on B200): 16 384
+// ex2.approx at 16/clk = 1024 clk and 8192 cvt.e2m1x2 at 16/clk = 512 clk share the XU pipe;
+// everything else is arranged to stay well below that on the FMA / ALU pipes and in issue
+// slots (packed f32x2 arithmetic, 3-input max, block scales derived with a magic-number
+// rounding instead of cvt / ceil, which would also land on the XU pipe).
 #pragma once
 #include "ptx.cuh"
 #include <math.h>
@@ -24,27 +31,52 @@
 namespace fa4 {
 
 // Lazy-rescale threshold and the constant up-shift of P, both in log2 units.  A stale reference
-// maximum lets p reach 2^kLazy; block scales are ue4m3 (max 448 >= 2^8), block maxima sit at
-// <= 6 * 2^e, hence kLazy + kShift <= 10.  The smallest non-zero p is 2^-(10 + kShift)
+// maximum lets p reach 2^kLazy; block scales are ue4m3 normals 2^kEMin .. 2^8, block maxima sit
+// at <= 6 * 2^e, hence kLazy + kShift <= 10.  The smallest non-zero p is 2^(kEMin - 2 - kShift)
 // relative to the reference maximum.
 constexpr int kLazy = 4;
 constexpr int kShift = 6;
+constexpr int kEMin = -6;
 constexpr float kLog2Of6 = 2.5849625007f;
 static_assert(kLazy + kShift <= 10, "P block scales would overflow ue4m3");
 
 constexpr float kNegInf = -INFINITY;
 
+// ---- packed two-wide fp32 arithmetic (one issue slot for two lanes) ---------------------------
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
 // Block maxima (8 blocks of 16 keys) and the row maximum of one 128-key row.
 __device__ __forceinline__ float row_block_max(const float (&s)[128], float (&bm)[8]) {
 #pragma unroll
   for (int b = 0; b < 8; ++b) {
-    float m = fmax3(s[16 * b], s[16 * b + 1], s[16 * b + 2]);
-#pragma unroll
-    for (int j = 3; j < 15; j += 2) m = fmax3(m, s[16 * b + j], s[16 * b + j + 1]);
-    bm[b] = fmaxf(m, s[16 * b + 15]);
+    float m0 = fmax3(s[16 * b], s[16 * b + 1], s[16 * b + 2]);
+    float m1 = fmax3(s[16 * b + 3], s[16 * b + 4], s[16 * b + 5]);
+    m0 = fmax3(m0, s[16 * b + 6], s[16 * b + 7]);
+    m1 = fmax3(m1, s[16 * b + 8], s[16 * b + 9]);
+    m0 = fmax3(m0, s[16 * b + 10], s[16 * b + 11]);
+    m1 = fmax3(m1, s[16 * b + 12], s[16 * b + 13]);
+    m0 = fmax3(m0, s[16 * b + 14], s[16 * b + 15]);
+    bm[b] = fmaxf(m0, m1);
   }
-  float m01 = fmax3(bm[0], bm[1], bm[2]);
-  float m23 = fmax3(bm[3], bm[4], bm[5]);
+  const float m01 = fmax3(bm[0], bm[1], bm[2]);
+  const float m23 = fmax3(bm[3], bm[4], bm[5]);
   return fmax3(fmaxf(m01, m23), bm[6], bm[7]);
 }
 
@@ -60,37 +92,71 @@ __device__ __forceinline__ float reference_factor(float m_from, float m_to, floa
   return (m_from == kNegInf) ? 0.f : ex2_approx((m_from - m_to) * sl2);
 }
 
-// Quantise one row of 128 scores against reference m_ref.
-//   pk[16]  packed e2m1, 8 values per word, key order
+// Quantise one row of 128 scores against reference m_ref and store it as one row of the P tile.
+//   p_tile  shared-memory P tile (K-major, 64-byte rows, 64-byte swizzle); each 16-byte chunk
+//           (32 keys = 2 blocks) is stored as soon as it is complete, to keep registers free
 //   sfw[2]  the 8 block scales as ue4m3 bytes, 4 per word (one word per 64-key MMA step)
 //   returns the row's sum of p' (un-rounded), to be added to the running sum
+//
+// Block exponent without cvt / ceil: u = t + (1.5 * 2^23 + 127) rounds t to the nearest integer
+// (t already carries the +0.5 that turns rounding into ceil) and leaves e + 127 in the low byte
+// of u's bit pattern; u << 23 is then the fp32 bit pattern of 2^e, and (low byte - 120) << 3 the
+// ue4m3 encoding of 2^e.
 __device__ __forceinline__ float quantize_row(const float (&s)[128], const float (&bm)[8],
-                                              float m_ref, float sl2, uint32_t (&pk)[16],
+                                              float m_ref, float sl2, uint8_t* p_tile, uint32_t row,
                                               uint32_t (&sfw)[2]) {
+  constexpr float kMagic = 12582912.f + 127.f;  // 1.5 * 2^23 + exponent bias
   const float msc = (m_ref == kNegInf) ? 0.f : m_ref * sl2;
+  // t' = log2(block max of p') - log2 6 + (0.5 - tiny)
+  const float c_t = static_cast<float>(kShift) - kLog2Of6 + 0.4999995f - msc;
+  const float c_off = static_cast<float>(kShift) - msc;  // -off = c_off - e
+  const uint64_t sl2_2 = f2_pack(sl2, sl2);
   float acc = 0.f;
-  sfw[0] = 0u;
-  sfw[1] = 0u;
+  uint32_t ubits[8];
 #pragma unroll
-  for (int b = 0; b < 8; ++b) {
-    // log2 of the block maximum of p'
-    const float t = fmaf(bm[b], sl2, -msc) + static_cast<float>(kShift);
-    const float ef = fminf(fmaxf(ceilf(t - kLog2Of6), -9.f), 8.f);
-    const int e = static_cast<int>(ef);
-    const float off = msc - static_cast<float>(kShift) + ef;
-    float p[16];
-    float sum = 0.f;
+  for (int c = 0; c < 4; ++c) {
+    uint32_t pk[4];
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      p[j] = ex2_approx(fmaf(s[16 * b + j], sl2, -off));
-      sum += p[j];
+    for (int h = 0; h < 2; ++h) {
+      const int b = 2 * c + h;
+      float t = fmaf(bm[b], sl2, c_t);
+      t = fmaxf(t, static_cast<float>(kEMin) - 0.4f);  // also catches -inf (fully masked block)
+      const float u = t + kMagic;
+      ubits[b] = __float_as_uint(u);
+      const float noff = c_off - (u - kMagic);
+      const uint64_t noff2 = f2_pack(noff, noff);
+      float p[16];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint64_t x2 = f2_fma(f2_pack(s[16 * b + 2 * j], s[16 * b + 2 * j + 1]), sl2_2, noff2);
+        float x0, x1;
+        f2_unpack(x2, x0, x1);
+        p[2 * j] = ex2_approx(x0);
+        p[2 * j + 1] = ex2_approx(x1);
+      }
+      uint64_t sum2 = f2_add(f2_pack(p[0], p[1]), f2_pack(p[2], p[3]));
+      uint64_t sum3 = f2_add(f2_pack(p[4], p[5]), f2_pack(p[6], p[7]));
+      sum2 = f2_add(sum2, f2_pack(p[8], p[9]));
+      sum3 = f2_add(sum3, f2_pack(p[10], p[11]));
+      sum2 = f2_add(sum2, f2_pack(p[12], p[13]));
+      sum3 = f2_add(sum3, f2_pack(p[14], p[15]));
+      sum2 = f2_add(sum2, sum3);
+      pk[2 * h] = pack8_e2m1(p[0], p[1], p[2], p[3], p[4], p[5], p[6], p[7]);
+      pk[2 * h + 1] = pack8_e2m1(p[8], p[9], p[10], p[11], p[12], p[13], p[14], p[15]);
+      float s0, s1;
+      f2_unpack(sum2, s0, s1);
+      acc = fmaf(s0 + s1, __uint_as_float(ubits[b] << 23), acc);
     }
-    pk[2 * b] = pack8_e2m1(p[0], p[1], p[2], p[3], p[4], p[5], p[6], p[7]);
-    pk[2 * b + 1] = pack8_e2m1(p[8], p[9], p[10], p[11], p[12], p[13], p[14], p[15]);
-    acc = fmaf(sum, __int_as_float((e + 127) << 23), acc);
-    // ue4m3 encoding of 2^e: normal for e >= -6 (exponent field e + 7), subnormal below
-    const uint32_t byte = (e >= -6) ? (static_cast<uint32_t>(e + 7) << 3) : (1u << (e + 9));
-    sfw[b >> 2] |= byte << (8 * (b & 3));
+    *reinterpret_cast<uint4*>(p_tile + sw64_offset(row, c)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+  }
+  // ue4m3 bytes: gather the low bytes (e + 127), subtract 120, shift into the exponent field
+#pragma unroll
+  for (int w = 0; w < 2; ++w) {
+    uint32_t lo, hi, all;
+    asm("prmt.b32 %0, %1, %2, 0x0040;" : "=r"(lo) : "r"(ubits[4 * w]), "r"(ubits[4 * w + 1]));
+    asm("prmt.b32 %0, %1, %2, 0x0040;" : "=r"(hi) : "r"(ubits[4 * w + 2]), "r"(ubits[4 * w + 3]));
+    asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(all) : "r"(lo), "r"(hi));
+    sfw[w] = (all - 0x78787878u) << 3;
   }
   return acc;
 }

@@ -44,6 +44,7 @@ _E2M1_TIE_UP = np.array([False, True, False, True, False, True, False])  # tie r
 LOG2_6 = math.log2(6.0)
 P_SHIFT = 6          # constant up-shift of P in log2 units (kernel: kShift)
 P_LAZY = 4           # lazy-rescale threshold in log2 units (kernel: kLazy)
+P_EMIN = -6          # smallest block-scale exponent (kernel: kEMin; ue4m3 normals only)
 BLOCK = 16
 
 
@@ -178,8 +179,8 @@ def quantize_p_block_model(x: torch.Tensor, m_ref: torch.Tensor):
     xb = x.reshape(x.shape[:-1] + (8, BLOCK))
     bmax = xb.amax(dim=-1, keepdim=True)
     t = bmax - m_ref[..., None] + P_SHIFT
-    e = torch.clamp(torch.ceil(t - LOG2_6), -9.0, 8.0)
-    e = torch.where(torch.isfinite(t), e, torch.full_like(e, -9.0))
+    e = torch.clamp(torch.ceil(t - LOG2_6), float(P_EMIN), 8.0)
+    e = torch.where(torch.isfinite(t), e, torch.full_like(e, float(P_EMIN)))
     p_scaled = torch.exp2(xb - (m_ref[..., None] - P_SHIFT + e))          # in [0, 6]
     codes = e2m1_encode(p_scaled.numpy())
     p_hat = torch.from_numpy(e2m1_decode(codes)) * torch.exp2(e)
