@@ -275,3 +275,13 @@ extern "C" int fa4_nvfp4_fwd_linear_sf_noalloc(const fa4_nvfp4_params* p, void* 
   tiled.v_sf = v_t;
   return fa4_nvfp4_fwd(&tiled, cuda_stream);
 }
+
+#ifdef FA4_TRACE
+// Timeline capture for one CTA (build with -DFA4_TRACE; not part of the shipped library).
+extern "C" int fa4_nvfp4_debug_set_trace(void* buf, int cta) {
+  unsigned long long* b = static_cast<unsigned long long*>(buf);
+  cudaError_t e = cudaMemcpyToSymbol(fa4::g_trace_buf, &b, sizeof(b));
+  if (e == cudaSuccess) e = cudaMemcpyToSymbol(fa4::g_trace_cta, &cta, sizeof(cta));
+  return (int)e;
+}
+#endif

@@ -4,12 +4,15 @@
 //   warps 0-3  softmax warpgroup 0: K/V blocks 0, 2, 4, ... of the tile (visit order)
 //   warps 4-7  softmax warpgroup 1: K/V blocks 1, 3, 5, ...
 //   warp  8    TMA producer: Q once, then K and V tiles with their scale factors into two rings
-//   warp  9    tensor-core issuer: tcgen05.cp of scale factors, block-scaled tcgen05.mma for
-//              S = Q K^T (two S buffers in tensor memory) and O += P V; owns tensor memory
-//   warps 10-11 idle: they complete the third warpgroup so that registers can be moved from it
-//              to the softmax warpgroups with setmaxnreg (40 vs 232 per thread, the split the
-//              reference uses between its load/MMA warps and softmax warps,
-//              flash_fwd_sm100.py:273-292)
+//   warp  9    QK^T issuer: tcgen05.cp of the Q/K scale factors and the block-scaled tcgen05.mma
+//              for S = Q K^T (two S buffers in tensor memory); owns tensor memory
+//   warp 10    PV issuer: tcgen05.cp of the P/V scale factors and tcgen05.mma for O += P V.
+//              Two issuing threads because one thread needs on the order of 100 clocks per
+//              tcgen05 instruction or barrier wait next to the busy softmax warps, and a block
+//              needs 18 of them; split in two they stay below the softmax time of a block.
+//   warp 11    idle: it completes the third warpgroup so that registers can be moved from it to
+//              the softmax warpgroups with setmaxnreg (the split the reference uses between its
+//              load/MMA warps and softmax warps, flash_fwd_sm100.py:273-292)
 //
 // The reference kernel (flash_attn/cute/flash_fwd_sm100.py:216-222) keeps two 128-row query
 // stages with S and O for both in tensor memory (4 x 128 columns = all of it).  The block-scaled
@@ -25,20 +28,44 @@
 //
 // Barriers (all mbarriers, every wait bounded):
 //   q_full            producer -> issuer      Q tile + scales landed
-//   k_full/k_empty[]  producer <-> issuer     K ring (k_empty by tcgen05.commit after QK^T)
-//   v_full/v_empty[]  producer <-> issuer     V ring (v_empty by tcgen05.commit after PV)
-//   s_full[2]         issuer -> softmax WG    S buffer holds block i          (commit)
+//   k_full[], v_full[] producer -> issuers    K / V tile + scales landed in ring stage
+//   s_full[2]         issuer -> softmax WG    S buffer holds block i (commit); also tells the
+//                                             producer that the K stage of block i is free
 //   s_free[2]         softmax WG -> issuer    S buffer copied to registers     (128 arrivals)
 //   p_full[2]         softmax WG -> issuer    P block + its scales in shared memory (128 arrivals)
-//   pv_done[2]        issuer -> softmax WGs   PV of block i complete: P buffer free, O stable
+//   pv_done[2]        issuer -> softmax WGs   PV of block i complete: P buffer free, O stable;
+//                                             also tells the producer that the V stage is free
 //   max_ready[2]      softmax WG -> other WG  reference maximum of block i published
 //   fin               both WGs                row sums published for the final combine
-//   drain             issuer                  tensor-core work drained on the abort path
+//   drain[2]          issuers                 tensor-core work drained on the abort path
 #pragma once
 #include "attn_common.cuh"
 #include "attn_serial.cuh"  // tensor-memory map, tile byte sizes
 
 namespace fa4 {
+
+// Optional per-role timeline (compile with -DFA4_TRACE): lane 0 of every warp of ONE CTA appends
+// (event, block index, clock64) records to a global buffer set by fa4_nvfp4_debug_set_trace.
+#ifdef FA4_TRACE
+__device__ unsigned long long* g_trace_buf = nullptr;   // [12 warps][kTraceCap][2]
+__device__ int g_trace_cta = 0;
+constexpr int kTraceCap = 1024;
+#define FA4_TRACE_DECL int trace_n = 0;
+#define FA4_TRACE_EV(ev, idx)                                                                  \
+  do {                                                                                         \
+    if (g_trace_buf != nullptr && (int)blockIdx.x == g_trace_cta && (threadIdx.x & 31) == 0 && \
+        trace_n < kTraceCap) {                                                                 \
+      unsigned long long* r_ = g_trace_buf + ((threadIdx.x >> 5) * kTraceCap + trace_n) * 2;   \
+      r_[0] = ((unsigned long long)(ev) << 32) | (unsigned)(idx);                              \
+      r_[1] = clock64();                                                                       \
+      ++trace_n;                                                                               \
+    }                                                                                          \
+  } while (0)
+#else
+#define FA4_TRACE_DECL
+#define FA4_TRACE_EV(ev, idx) do {} while (0)
+#endif
+
 namespace ws {
 
 constexpr int kStagesK = 4;
@@ -47,7 +74,8 @@ constexpr int kThreads = 384;
 constexpr int kRegsSoftmax = 232;
 constexpr int kRegsOther = 40;
 constexpr int kProducerWarp = 8;
-constexpr int kIssuerWarp = 9;
+constexpr int kIssuerWarp = 9;    // QK^T issuer, owns tensor memory
+constexpr int kPvIssuerWarp = 10;
 
 // shared-memory map (offsets from a 1024-byte aligned base)
 constexpr uint32_t kOffQ = 0;                                  // 8 KB
@@ -61,7 +89,7 @@ constexpr uint32_t kOffSFP = kOffSFV + kStagesV * kSfBytes;    // 2 x 1 KB
 constexpr uint32_t kOffMax = kOffSFP + 2 * kSfBytes;           // 2 x 128 floats
 constexpr uint32_t kOffFin = kOffMax + 2 * 128 * 4;            // 2 x 128 x (sum, ref) floats
 constexpr uint32_t kOffBar = kOffFin + 2 * 128 * 8;
-constexpr int kNumBars = 1 + 2 * kStagesK + 2 * kStagesV + 2 * 5 + 2;
+constexpr int kNumBars = 1 + 2 * kStagesK + 2 * kStagesV + 2 * 3 + 3;
 constexpr uint32_t kOffMisc = kOffBar + 8 * kNumBars;          // tmem slot, abort flag
 constexpr uint32_t kSmemUsed = kOffMisc + 16;
 constexpr uint32_t kSmemRequest = kSmemUsed + 1024 > 120 * 1024 ? kSmemUsed + 1024 : 120 * 1024;
@@ -72,19 +100,16 @@ enum Site {
 };
 
 struct Bars {
-  uint32_t q_full, k_full, k_empty, v_full, v_empty, s_full, s_free, p_full, pv_done, max_ready, fin,
-      drain;
+  uint32_t q_full, k_full, v_full, s_full, s_free, p_full, pv_done, max_ready, fin, drain;
   __device__ explicit Bars(uint32_t b) {
     q_full = b;
     k_full = q_full + 8;
-    k_empty = k_full + 8 * kStagesK;
-    v_full = k_empty + 8 * kStagesK;
-    v_empty = v_full + 8 * kStagesV;
-    s_full = v_empty + 8 * kStagesV;
-    s_free = s_full + 16;
+    v_full = k_full + 8 * kStagesK;
+    s_full = v_full + 8 * kStagesV;   // kStagesK barriers, indexed by block % kStagesK
+    s_free = s_full + 8 * kStagesK;
     p_full = s_free + 16;
-    pv_done = p_full + 16;
-    max_ready = pv_done + 16;
+    pv_done = p_full + 16;            // kStagesV barriers, indexed by block % kStagesV
+    max_ready = pv_done + 8 * kStagesV;
     fin = max_ready + 16;
     drain = fin + 8;
   }
@@ -114,23 +139,18 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
   if (tid == 0) {
     *s_abort = 0u;
     mbar_init(bars.q_full, 1);
-    for (int s = 0; s < kStagesK; ++s) {
-      mbar_init(bars.k_full + 8 * s, 1);
-      mbar_init(bars.k_empty + 8 * s, 1);
-    }
-    for (int s = 0; s < kStagesV; ++s) {
-      mbar_init(bars.v_full + 8 * s, 1);
-      mbar_init(bars.v_empty + 8 * s, 1);
-    }
+    for (int s = 0; s < kStagesK; ++s) mbar_init(bars.k_full + 8 * s, 1);
+    for (int s = 0; s < kStagesV; ++s) mbar_init(bars.v_full + 8 * s, 1);
+    for (int s = 0; s < kStagesK; ++s) mbar_init(bars.s_full + 8 * s, 1);
+    for (int s = 0; s < kStagesV; ++s) mbar_init(bars.pv_done + 8 * s, 1);
     for (int b = 0; b < 2; ++b) {
-      mbar_init(bars.s_full + 8 * b, 1);
       mbar_init(bars.s_free + 8 * b, 128);
       mbar_init(bars.p_full + 8 * b, 128);
-      mbar_init(bars.pv_done + 8 * b, 1);
       mbar_init(bars.max_ready + 8 * b, 128);
     }
     mbar_init(bars.fin, 256);
     mbar_init(bars.drain, 1);
+    mbar_init(bars.drain + 8, 1);
     fence_barrier_init();
   }
   if (warp == kProducerWarp && lane == 0) {
@@ -152,6 +172,8 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
   const Tile t = decode_tile(p, blockIdx.x);
   const int n = poisoned ? 0 : t.n_blocks;
   constexpr uint32_t idesc = make_idesc_nvf4(128, 128);
+  FA4_TRACE_DECL
+  FA4_TRACE_EV(0, 0);
 
   if (warp >= 8) {
     // registers move from this warpgroup to the softmax warpgroups
@@ -173,8 +195,12 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         const int ik = step, iv = step - 2;
         if (ik < n) {
           const int st = ik % kStagesK, nb = n - 1 - ik;
-          ok = mbar_wait(bars.k_empty + 8 * st, ((ik / kStagesK) & 1) ^ 1, wc, kSiteKEmpty);
-          if (!ok) break;
+          // stage st is free once QK^T of block ik - kStagesK has completed (its s_full phase)
+          if (ik >= kStagesK) {
+            const int j = ik - kStagesK;
+            ok = mbar_wait(bars.s_full + 8 * (j % kStagesK), (j / kStagesK) & 1, wc, kSiteKEmpty);
+            if (!ok) break;
+          }
           mbar_arrive_expect_tx(bars.k_full + 8 * st, kTileBytes + kSfBytes);
           tma_load_4d(base + kOffK + st * kTileBytes, &tm_k, bars.k_full + 8 * st, 0, t.hk,
                       nb * kBlockN, t.b);
@@ -184,8 +210,11 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         }
         if (iv >= 0 && iv < n) {
           const int st = iv % kStagesV, nb = n - 1 - iv;
-          ok = mbar_wait(bars.v_empty + 8 * st, ((iv / kStagesV) & 1) ^ 1, wc, kSiteVEmpty);
-          if (!ok) break;
+          if (iv >= kStagesV) {
+            const int j = iv - kStagesV;
+            ok = mbar_wait(bars.pv_done + 8 * (j % kStagesV), (j / kStagesV) & 1, wc, kSiteVEmpty);
+            if (!ok) break;
+          }
           mbar_arrive_expect_tx(bars.v_full + 8 * st, kTileBytes + kSfBytes);
           tma_load_4d(base + kOffV + st * kTileBytes, &tm_v, bars.v_full + 8 * st,
                       nb * (kBlockN / 2), 0, t.hk, t.b);
@@ -210,7 +239,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
       }
     }
   } else if (warp == kIssuerWarp) {
-    // =========================================== tensor-core issuer =============================
+    // =========================================== QK^T issuer ====================================
     if (lane == 0 && n > 0) {
       bool ok = mbar_wait(bars.q_full, 0, wc, kSiteQFull);
       if (ok) {
@@ -218,64 +247,64 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         tc_cp_sf(tmem + kTmSFQ, base + kOffSFQ);
         tc_cp_sf(tmem + kTmSFQ + 4, base + kOffSFQ + 512);
       }
-      // S[i % 2] = Q K_i^T
-      auto issue_qk = [&](int i) -> bool {
+      const uint64_t dq0 = make_desc_sw64(base + kOffQ), dq1 = make_desc_sw64(base + kOffQ + 32);
+      for (int i = 0; ok && i < n; ++i) {
         const int st = i % kStagesK, b = i & 1;
-        if (!mbar_wait(bars.k_full + 8 * st, (i / kStagesK) & 1, wc, kSiteKFull)) return false;
+        if (i >= 2) {
+          // S buffer b is free once the softmax warpgroup has copied block i-2 to registers
+          ok = mbar_wait(bars.s_free + 8 * b, ((i - 2) >> 1) & 1, wc, kSiteSFree);
+          if (!ok) break;
+        }
+        FA4_TRACE_EV(21, i);
+        ok = mbar_wait(bars.k_full + 8 * st, (i / kStagesK) & 1, wc, kSiteKFull);
+        if (!ok) break;
+        FA4_TRACE_EV(20, i);
         tc_fence_after_sync();
         const uint32_t sfk = tmem + kTmSFK + 8 * b;
-        tc_cp_sf(sfk, base + kOffSFK + st * kSfBytes);
-        tc_cp_sf(sfk + 4, base + kOffSFK + st * kSfBytes + 512);
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          const uint64_t da = make_smem_desc(base + kOffQ + 32 * j, 16, 512, kSwizzle64);
-          const uint64_t db =
-              make_smem_desc(base + kOffK + st * kTileBytes + 32 * j, 16, 512, kSwizzle64);
-          mma_nvf4(tmem + (b ? kTmS1 : kTmS0), da, db, idesc, tmem + kTmSFQ + 4 * j, sfk + 4 * j, j);
-        }
-        tc_commit(bars.s_full + 8 * b);
-        tc_commit(bars.k_empty + 8 * st);
-        return true;
-      };
-      if (ok) ok = issue_qk(0);
-      if (ok && n > 1) ok = issue_qk(1);
-      for (int i = 0; ok && i < n; ++i) {
-        const int b = i & 1, u = i >> 1;
-        if (i + 2 < n) {
-          // S buffer b is free once the softmax warpgroup has copied block i to registers
-          ok = mbar_wait(bars.s_free + 8 * b, u & 1, wc, kSiteSFree);
-          if (!ok) break;
-          tc_fence_after_sync();
-          ok = issue_qk(i + 2);
-          if (!ok) break;
-        }
-        const int st = i % kStagesV;
-        ok = mbar_wait(bars.p_full + 8 * b, u & 1, wc, kSitePFull);
-        if (!ok) break;
-        ok = mbar_wait(bars.v_full + 8 * st, (i / kStagesV) & 1, wc, kSiteVFull);
-        if (!ok) break;
-        tc_fence_after_sync();
-        const uint32_t sfp = tmem + kTmSFP + 8 * b, sfv = tmem + kTmSFV + 8 * b;
-        tc_cp_sf(sfp, base + kOffSFP + b * kSfBytes);
-        tc_cp_sf(sfp + 4, base + kOffSFP + b * kSfBytes + 512);
-        tc_cp_sf(sfv, base + kOffSFV + st * kSfBytes);
-        tc_cp_sf(sfv + 4, base + kOffSFV + st * kSfBytes + 512);
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          const uint64_t da =
-              make_smem_desc(base + kOffP + b * kTileBytes + 32 * j, 16, 512, kSwizzle64);
-          const uint64_t db =
-              make_smem_desc(base + kOffV + st * kTileBytes + 32 * j, 16, 512, kSwizzle64);
-          mma_nvf4(tmem + kTmO, da, db, idesc, sfp + 4 * j, sfv + 4 * j, (i > 0 || j > 0) ? 1u : 0u);
-        }
-        tc_commit(bars.pv_done + 8 * b);
-        tc_commit(bars.v_empty + 8 * st);
+        const uint32_t ksf = base + kOffSFK + st * kSfBytes, kt = base + kOffK + st * kTileBytes;
+        tc_cp_sf(sfk, ksf);
+        tc_cp_sf(sfk + 4, ksf + 512);
+        const uint32_t s_tm = tmem + (b ? kTmS1 : kTmS0);
+        mma_nvf4(s_tm, dq0, make_desc_sw64(kt), idesc, tmem + kTmSFQ, sfk, 0u);
+        mma_nvf4(s_tm, dq1, make_desc_sw64(kt + 32), idesc, tmem + kTmSFQ + 4, sfk + 4, 1u);
+        tc_commit(bars.s_full + 8 * st);
+        FA4_TRACE_EV(27, i);
       }
       if (!ok) {
         // bounded drain of the tensor-core work already issued, before tensor memory is freed
         const uint64_t t0 = globaltimer_ns();
         tc_commit(bars.drain);
         while (!mbar_try_wait(bars.drain, 0) && globaltimer_ns() - t0 < 50ull * 1000 * 1000) {}
+      }
+    }
+  } else if (warp == kPvIssuerWarp) {
+    // =========================================== PV issuer ======================================
+    if (lane == 0 && n > 0) {
+      bool ok = true;
+      for (int i = 0; ok && i < n; ++i) {
+        const int st = i % kStagesV, b = i & 1;
+        ok = mbar_wait(bars.v_full + 8 * st, (i / kStagesV) & 1, wc, kSiteVFull);
+        if (!ok) break;
+        ok = mbar_wait(bars.p_full + 8 * b, (i >> 1) & 1, wc, kSitePFull);
+        if (!ok) break;
+        FA4_TRACE_EV(22, i);
+        tc_fence_after_sync();
+        const uint32_t sfp = tmem + kTmSFP + 8 * b, sfv = tmem + kTmSFV + 8 * b;
+        const uint32_t psf = base + kOffSFP + b * kSfBytes, vsf = base + kOffSFV + st * kSfBytes;
+        const uint32_t pt = base + kOffP + b * kTileBytes, vt = base + kOffV + st * kTileBytes;
+        tc_cp_sf(sfp, psf);
+        tc_cp_sf(sfv, vsf);
+        mma_nvf4(tmem + kTmO, make_desc_sw64(pt), make_desc_sw64(vt), idesc, sfp, sfv, i > 0 ? 1u : 0u);
+        tc_cp_sf(sfp + 4, psf + 512);
+        tc_cp_sf(sfv + 4, vsf + 512);
+        mma_nvf4(tmem + kTmO, make_desc_sw64(pt + 32), make_desc_sw64(vt + 32), idesc, sfp + 4, sfv + 4, 1u);
+        tc_commit(bars.pv_done + 8 * st);
+        FA4_TRACE_EV(23, i);
+      }
+      if (!ok) {
+        const uint64_t t0 = globaltimer_ns();
+        tc_commit(bars.drain + 8);
+        while (!mbar_try_wait(bars.drain + 8, 0) && globaltimer_ns() - t0 < 50ull * 1000 * 1000) {}
       }
     }
   }
@@ -291,8 +320,10 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
     for (int i = g; ok && i < n; i += 2) {
       const int u = i >> 1;
       const int nb = n - 1 - i;
-      ok = __all_sync(0xffffffffu, mbar_wait(bars.s_full + 8 * g, u & 1, wc, kSiteSFull));
+      FA4_TRACE_EV(1, i);
+      ok = __all_sync(0xffffffffu, mbar_wait(bars.s_full + 8 * (i % kStagesK), (i / kStagesK) & 1, wc, kSiteSFull));
       if (!ok) break;
+      FA4_TRACE_EV(2, i);
       tc_fence_after_sync();
       float s[128];
 #pragma unroll
@@ -301,10 +332,13 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
       tc_wait_ld();
       tc_fence_before_sync();
       mbar_arrive(bars.s_free + 8 * g);
+      FA4_TRACE_EV(3, i);
 
       if (block_needs_mask(p, t, nb)) mask_row(s, causal_limit(p, t, row, nb));
       float bm[8];
       const float m_loc = row_block_max(s, bm);
+      FA4_TRACE_EV(4, i);
+      FA4_TRACE_EV(40, i);   // calibration: cost of one trace record
 
       // reference maximum handed over by the warpgroup of block i-1
       float m_prev = kNegInf;
@@ -312,20 +346,24 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         ok = __all_sync(0xffffffffu,
                         mbar_wait(bars.max_ready + 8 * (g ^ 1), ((i - 1) >> 1) & 1, wc, kSiteMaxReady));
         if (!ok) break;
+        FA4_TRACE_EV(41, i);
         m_prev = s_max[(g ^ 1) * 128 + row];
       }
       const float m_new = next_reference(m_prev, m_loc, p.sl2);
+      FA4_TRACE_EV(42, i);
       s_max[g * 128 + row] = m_new;
       mbar_arrive(bars.max_ready + 8 * g);
+      FA4_TRACE_EV(5, i);
 
       // own partial row sum follows the reference
       if (m_new != m_ref) l_sum *= reference_factor(m_ref, m_new, p.sl2);
       m_ref = m_new;
 
+      FA4_TRACE_EV(43, i);
       // correction: O holds blocks 0..i-1 relative to m_prev
       if (i > 0 && __any_sync(0xffffffffu, m_new != m_prev)) {
         ok = __all_sync(0xffffffffu,
-                        mbar_wait(bars.pv_done + 8 * (g ^ 1), ((i - 1) >> 1) & 1, wc, kSitePvDone));
+                        mbar_wait(bars.pv_done + 8 * ((i - 1) % kStagesV), ((i - 1) / kStagesV) & 1, wc, kSitePvDone));
         if (!ok) break;
         tc_fence_after_sync();
         const float f = (m_new != m_prev) ? reference_factor(m_prev, m_new, p.sl2) : 1.f;
@@ -341,22 +379,28 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         tc_wait_st();
       }
 
+      FA4_TRACE_EV(44, i);
       // P buffer g is free once PV of block i-2 has completed
       if (u > 0) {
         ok = __all_sync(0xffffffffu,
-                        mbar_wait(bars.pv_done + 8 * g, (u - 1) & 1, wc, kSitePvDone));
+                        mbar_wait(bars.pv_done + 8 * ((i - 2) % kStagesV), ((i - 2) / kStagesV) & 1, wc, kSitePvDone));
         if (!ok) break;
       }
       uint32_t sfw[2];
+      FA4_TRACE_EV(6, i);
       l_sum += quantize_row(s, bm, m_ref, p.sl2, gbase + kOffP + g * kTileBytes, row, sfw);
+      FA4_TRACE_EV(7, i);
       uint8_t* ssf = gbase + kOffSFP + g * kSfBytes;
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         *reinterpret_cast<uint32_t*>(ssf + 512 * j + (row & 31) * 16 + (row >> 5) * 4) = sfw[j];
       }
+      FA4_TRACE_EV(45, i);
       fence_proxy_async_smem();
+      FA4_TRACE_EV(46, i);
       tc_fence_before_sync();  // orders the O rescale stores before the issuer's next MMA
       mbar_arrive(bars.p_full + 8 * g);
+      FA4_TRACE_EV(8, i);
     }
 
     // ---- final combine of the two partial row sums ------------------------------------------------
@@ -373,7 +417,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
                             l_other * reference_factor(m_other, m_fin, p.sl2);
         l_sum = (m_fin == kNegInf) ? 0.f : l_tot;
         m_ref = m_fin;
-        ok = __all_sync(0xffffffffu, mbar_wait(bars.pv_done + 8 * ((n - 1) & 1), ((n - 1) >> 1) & 1, wc,
+        ok = __all_sync(0xffffffffu, mbar_wait(bars.pv_done + 8 * ((n - 1) % kStagesV), ((n - 1) / kStagesV) & 1, wc,
                                                kSiteFinalO));
         tc_fence_after_sync();
       }

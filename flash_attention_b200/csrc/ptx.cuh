@@ -163,6 +163,16 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_
   return d;
 }
 
+// The same descriptor for the tiles the attention kernels use (K-major rows of 64 bytes, 64-byte
+// swizzle, 8-row groups 512 bytes apart): only the address field varies, the upper word is fixed.
+__device__ __forceinline__ uint64_t make_desc_sw64(uint32_t saddr) {
+  constexpr uint32_t hi = (512u >> 4) | (1u << 14) | (kSwizzle64 << 29);
+  const uint32_t lo = ((saddr >> 4) & 0x3fffu) | (1u << 16);
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+  return d;
+}
+
 // Instruction descriptor of kind::mxf4nvf4 (e2m1 x e2m1, ue4m3 scales of 16-element blocks,
 // fp32 accumulate, both operands K-major, K = 64 per instruction):
 //   [7,10) A format (1 = e2m1), [10,13) B format, [15] A major, [16] B major (0 = K),
@@ -191,7 +201,9 @@ __device__ __forceinline__ void mma_nvf4(uint32_t d_tmem, uint64_t a_desc, uint6
 // Copy one 32-row x 16-byte scale-factor chunk (512 contiguous bytes of shared memory) into
 // 4 tensor-memory columns, replicated over the four 32-lane quadrants.
 __device__ __forceinline__ void tc_cp_sf(uint32_t taddr, uint32_t saddr) {
-  const uint64_t desc = make_smem_desc(saddr, 0, 128, kSwizzleNone);
+  constexpr uint32_t hi = (128u >> 4) | (1u << 14);
+  uint64_t desc;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(desc) : "r"((saddr >> 4) & 0x3fffu), "r"(hi));
   asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc)
                : "memory");
 }
