@@ -159,8 +159,11 @@ attn_fwd_serial_kernel(const __grid_constant__ CUtensorMap tm_q,
         l_sum *= f;
       }
       m_ref = m_new;
-      uint32_t sfw[2];
-      l_sum += quantize_row(s, bm, m_ref, p.sl2, gbase + kOffP, row, sfw);
+      float noff[8];
+      uint32_t ue[2];
+      block_exponents(bm, m_ref, p.sl2, noff, ue);
+      l_sum += quantize_row(s, noff, ue, p.sl2, gbase + kOffP, row);
+      const uint32_t sfw[2] = {block_scale_bytes(ue[0]), block_scale_bytes(ue[1])};
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         *reinterpret_cast<uint32_t*>(gbase + kOffSFP + 512 * j + (row & 31) * 16 + (row >> 5) * 4) =

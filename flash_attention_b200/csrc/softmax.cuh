@@ -92,39 +92,60 @@ __device__ __forceinline__ float reference_factor(float m_from, float m_to, floa
   return (m_from == kNegInf) ? 0.f : ex2_approx((m_from - m_to) * sl2);
 }
 
-// Quantise one row of 128 scores against reference m_ref and store it as one row of the P tile.
-//   p_tile  shared-memory P tile (K-major, 64-byte rows, 64-byte swizzle); each 16-byte chunk
-//           (32 keys = 2 blocks) is stored as soon as it is complete, to keep registers free
-//   sfw[2]  the 8 block scales as ue4m3 bytes, 4 per word (one word per 64-key MMA step)
-//   returns the row's sum of p' (un-rounded), to be added to the running sum
+// Per-block exponents of one row (8 blocks of 16 keys) from the block maxima.
+//   noff[b]  the exponent offset of block b:  p'/2^e = 2^(s * sl2 + noff[b])
+//   ue[w]    4 bytes per word, byte k = e + 127 of block 4 w + k (e = block scale exponent)
 //
-// Block exponent without cvt / ceil: u = t + (1.5 * 2^23 + 127) rounds t to the nearest integer
-// (t already carries the +0.5 that turns rounding into ceil) and leaves e + 127 in the low byte
-// of u's bit pattern; u << 23 is then the fp32 bit pattern of 2^e, and (low byte - 120) << 3 the
-// ue4m3 encoding of 2^e.
-__device__ __forceinline__ float quantize_row(const float (&s)[128], const float (&bm)[8],
-                                              float m_ref, float sl2, uint8_t* p_tile, uint32_t row,
-                                              uint32_t (&sfw)[2]) {
+// No cvt / ceil (both would sit on the XU pipe next to the exponentials): u = t + (1.5 * 2^23 +
+// 127) rounds t to the nearest integer (t already carries the +0.5 that turns rounding into
+// ceil) and leaves e + 127 in the low byte of u's bit pattern.
+__device__ __forceinline__ void block_exponents(const float (&bm)[8], float m_ref, float sl2,
+                                                float (&noff)[8], uint32_t (&ue)[2]) {
   constexpr float kMagic = 12582912.f + 127.f;  // 1.5 * 2^23 + exponent bias
   const float msc = (m_ref == kNegInf) ? 0.f : m_ref * sl2;
   // t' = log2(block max of p') - log2 6 + (0.5 - tiny)
   const float c_t = static_cast<float>(kShift) - kLog2Of6 + 0.4999995f - msc;
-  const float c_off = static_cast<float>(kShift) - msc;  // -off = c_off - e
+  const float c_off = static_cast<float>(kShift) - msc;  // noff = c_off - e
+  uint32_t ubits[8];
+#pragma unroll
+  for (int b = 0; b < 8; ++b) {
+    float t = fmaf(bm[b], sl2, c_t);
+    t = fmaxf(t, static_cast<float>(kEMin) - 0.4f);  // also catches -inf (fully masked block)
+    const float u = t + kMagic;
+    ubits[b] = __float_as_uint(u);
+    noff[b] = c_off - (u - kMagic);
+  }
+#pragma unroll
+  for (int w = 0; w < 2; ++w) {
+    uint32_t lo, hi;
+    asm("prmt.b32 %0, %1, %2, 0x0040;" : "=r"(lo) : "r"(ubits[4 * w]), "r"(ubits[4 * w + 1]));
+    asm("prmt.b32 %0, %1, %2, 0x0040;" : "=r"(hi) : "r"(ubits[4 * w + 2]), "r"(ubits[4 * w + 3]));
+    asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(ue[w]) : "r"(lo), "r"(hi));
+  }
+}
+
+// ue4m3 bytes of the block scales 2^e from the packed (e + 127) bytes: (e + 7) << 3.
+__device__ __forceinline__ uint32_t block_scale_bytes(uint32_t ue_word) {
+  return (ue_word - 0x78787878u) << 3;
+}
+
+// Quantise one row of 128 scores with the exponents from block_exponents() and store it as one
+// row of the P tile.
+//   p_tile  shared-memory P tile (K-major, 64-byte rows, 64-byte swizzle); each 16-byte chunk
+//           (32 keys = 2 blocks) is stored as soon as it is complete, to keep registers free
+//   returns the row's sum of p' (un-rounded), to be added to the running sum
+__device__ __forceinline__ float quantize_row(const float (&s)[128], const float (&noff)[8],
+                                              const uint32_t (&ue)[2], float sl2, uint8_t* p_tile,
+                                              uint32_t row) {
   const uint64_t sl2_2 = f2_pack(sl2, sl2);
   float acc = 0.f;
-  uint32_t ubits[8];
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
     uint32_t pk[4];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       const int b = 2 * c + h;
-      float t = fmaf(bm[b], sl2, c_t);
-      t = fmaxf(t, static_cast<float>(kEMin) - 0.4f);  // also catches -inf (fully masked block)
-      const float u = t + kMagic;
-      ubits[b] = __float_as_uint(u);
-      const float noff = c_off - (u - kMagic);
-      const uint64_t noff2 = f2_pack(noff, noff);
+      const uint64_t noff2 = f2_pack(noff[b], noff[b]);
       float p[16];
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
@@ -145,18 +166,11 @@ __device__ __forceinline__ float quantize_row(const float (&s)[128], const float
       pk[2 * h + 1] = pack8_e2m1(p[8], p[9], p[10], p[11], p[12], p[13], p[14], p[15]);
       float s0, s1;
       f2_unpack(sum2, s0, s1);
-      acc = fmaf(s0 + s1, __uint_as_float(ubits[b] << 23), acc);
+      // 2^e as fp32: byte (e + 127) moved into the exponent field
+      const uint32_t eb = __byte_perm(ue[b >> 2], 0u, 0x4440u + (b & 3));
+      acc = fmaf(s0 + s1, __uint_as_float(eb << 23), acc);
     }
     *reinterpret_cast<uint4*>(p_tile + sw64_offset(row, c)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-  }
-  // ue4m3 bytes: gather the low bytes (e + 127), subtract 120, shift into the exponent field
-#pragma unroll
-  for (int w = 0; w < 2; ++w) {
-    uint32_t lo, hi, all;
-    asm("prmt.b32 %0, %1, %2, 0x0040;" : "=r"(lo) : "r"(ubits[4 * w]), "r"(ubits[4 * w + 1]));
-    asm("prmt.b32 %0, %1, %2, 0x0040;" : "=r"(hi) : "r"(ubits[4 * w + 2]), "r"(ubits[4 * w + 3]));
-    asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(all) : "r"(lo), "r"(hi));
-    sfw[w] = (all - 0x78787878u) << 3;
   }
   return acc;
 }
