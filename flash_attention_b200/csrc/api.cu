@@ -132,11 +132,17 @@ extern "C" int fa4_nvfp4_fwd(const fa4_nvfp4_params* p, void* cuda_stream) {
   kp.budget_ns = p->wait_budget_ns ? p->wait_budget_ns : kDefaultBudgetNs;
 
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
-  const unsigned grid = (unsigned)(kp.num_m_blocks * p->Hq * p->B);
+  const unsigned tiles = (unsigned)(kp.num_m_blocks * p->Hq * p->B);
   if (variant == FA4_VARIANT_SERIAL) {
     if (int e = ensure_smem(attn_fwd_serial_kernel, serial::kSmemRequest)) return e;
-    attn_fwd_serial_kernel<<<grid, 128, serial::kSmemRequest, stream>>>(tm_q, tm_k, tm_v, kp);
+    attn_fwd_serial_kernel<<<tiles, 128, serial::kSmemRequest, stream>>>(tm_q, tm_k, tm_v, kp);
   } else {
+    // persistent: one CTA per SM walks the tile list
+    int dev = 0, sms = 0;
+    cudaError_t ce = cudaGetDevice(&dev);
+    if (ce == cudaSuccess) ce = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (ce != cudaSuccess) return (int)ce;
+    const unsigned grid = tiles < (unsigned)sms ? tiles : (unsigned)sms;
     if (int e = ensure_smem(attn_fwd_ws_kernel, ws::kSmemRequest)) return e;
     attn_fwd_ws_kernel<<<grid, ws::kThreads, ws::kSmemRequest, stream>>>(tm_q, tm_k, tm_v, kp);
   }

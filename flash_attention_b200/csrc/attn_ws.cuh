@@ -1,52 +1,65 @@
-// Warp-specialised variant: the production kernel.
+// Warp-specialised, persistent variant: the production kernel.
 //
-// Roles of the 16 warps of a CTA (one CTA per SM, one 128-row query tile per CTA):
-//   warps 0-3   softmax warpgroup 0: K/V blocks 0, 2, 4, ... of the tile (visit order)
-//   warps 4-7   softmax warpgroup 1: K/V blocks 1, 3, 5, ...
-//               one thread = one query row: exponentials, P -> e2m1, row sums, O correction
-//   warp  8     TMA producer: Q once, then K and V tiles with their scale factors into two rings
-//   warp  9     QK^T issuer: tcgen05.cp of the Q/K scale factors and the block-scaled tcgen05.mma
+// One CTA per SM walks a static list of 128-row query tiles (longest first, snake order over
+// the CTAs).  Roles of its 24 warps:
+//   warps 0-15  softmax: four warpgroups, one thread = HALF a query row of one K/V block
+//               (64 keys).  warpgroup k = warp / 4:  column half = k & 1 (keys 0-63 / 64-127),
+//               block parity = k >> 1 (blocks 0,2,4,.. / 1,3,5,.. of a tile in visit order,
+//               so that the summation order of a row depends on its tile only).
+//               exponentials, P -> e2m1, row sums, O correction, epilogue
+//   warps 16-19 statistics warpgroup: for EVERY block, in order, reads S from tensor memory in
+//               32-column chunks, keeps the running reference maximum of each row and publishes
+//               the per-block exponents (softmax.cuh block_exponents) in shared memory
+//   warp 20     TMA producer: Q (double buffered across tiles), K and V rings, scale factors
+//   warp 21     QK^T issuer: tcgen05.cp of the Q/K scale factors and the block-scaled tcgen05.mma
 //               for S = Q K^T (two S buffers in tensor memory); owns tensor memory
-//   warp 10     PV issuer: tcgen05.cp of the P/V scale factors and tcgen05.mma for O += P V.
-//               Two issuing threads because one thread needs on the order of 100 clocks per
-//               tcgen05 instruction or barrier wait next to the busy softmax warps, and a block
-//               needs 18 of them; split in two they stay below the softmax time of a block.
-//   warp 11     idle (completes the warpgroup for setmaxnreg)
-//   warps 12-15 statistics warpgroup: for EVERY block, in order, reads S from tensor memory in
-//               64-column halves, keeps the running reference maximum of each row and publishes
-//               the per-block exponents (softmax.cuh block_exponents) in shared memory.
+//   warp 22     PV issuer: tcgen05.cp of the P/V scale factors and tcgen05.mma for O += P V
+//   warp 23     idle (completes the warpgroup for setmaxnreg)
 //
-// Why a statistics warpgroup: the exponentials of a block (1024 clocks of the XU pipe per SM)
-// can only start once the row maximum of the whole block is known.  With the maximum computed
-// by the softmax threads themselves, every block paid load -> max -> hand-over -> exp in
-// sequence, and with two softmax warps per scheduler the non-exp part (about as long as the exp
-// part, all latency) could not be hidden.  Moving the maxima to their own warps shortens the
-// softmax threads' serial part to load -> exp and keeps the running maximum in one thread per
-// row, so no hand-over between the two softmax warpgroups is needed.
+// Why this shape (measured on B200, see the timeline facility below):
+//  * The exponentials of a block cost 1024 clocks of the XU pipe per SM (16 ex2/clk), far more
+//    than its tensor-core time (256 clocks), so the kernel is organised around keeping the XU
+//    pipe busy.
+//  * ex2 can only start once the row maximum of the whole block is known.  The statistics
+//    warpgroup takes the maxima (and the running maximum, one thread per row, no hand-over) off
+//    the exponentiating threads, whose serial part shrinks to load -> exp.
+//  * Everything around the exponentials is latency (barrier probes, tensor-memory loads, shared
+//    memory), roughly as long as the exponentials themselves.  Two warps per scheduler could not
+//    hide it; with the maxima gone a thread no longer needs the whole row in registers, so the
+//    row is split in two halves and four softmax warps per scheduler overlap each other.
+//  * One thread needs on the order of 100 clocks per tcgen05 instruction or barrier wait next to
+//    the busy softmax warps and a block needs 18 of them: two issuing threads.
+//  * Prologue and epilogue of a tile (first loads, last PV, O to global memory) were a fifth of
+//    a tile's time: the CTA is persistent, the producer and the QK^T issuer run ahead into the
+//    next tile while the softmax warps finish the current one (Q is double buffered; only
+//    the first PV of a tile waits until O has been read out of tensor memory).
 //
 // The reference kernel (flash_attn/cute/flash_fwd_sm100.py:216-222) keeps two 128-row query
 // stages with S and O for both in tensor memory (4 x 128 columns = all of it).  The block-scaled
 // instruction needs tensor-memory columns for the scale factors as well, so this kernel keeps ONE
 // query stage with S double-buffered across K/V blocks (S0, S1, O = 384 columns + 56 columns of
-// scales) and lets the two softmax warpgroups alternate over K/V blocks.
+// scales).  The correction step (rescale O when the reference maximum moves; separate warps in
+// the reference, flash_fwd_sm100.py:2230-2351) is done by the softmax warpgroups of the block
+// that moved the maximum: with the lazy threshold it is rare after the first block.
 //
-// The correction step (rescale O when the reference maximum moves; separate warps in the
-// reference, flash_fwd_sm100.py:2230-2351) is done by the softmax warpgroup of the block that
-// moved the maximum: with the lazy threshold it is rare after the first block.
+// Block indices: i = index inside the tile (0 = last visible K/V block, the reference's visit
+// order), G = blocks_before_this_tile + i = running index that picks ring stages, S/P buffers
+// and barrier phases, so that the pipeline never drains between tiles.
 //
 // Barriers (all mbarriers, every wait bounded):
-//   q_full             producer -> QK issuer   Q tile + scales landed
-//   k_full[], v_full[] producer -> issuers     K / V tile + scales landed in ring stage
-//   s_full[stage]      QK issuer -> stats, softmax: S buffer holds block i (tcgen05.commit); also
-//                                              tells the producer that the K stage is free
-//   s_free[2]          stats + softmax -> QK issuer: S buffer read by both (256 arrivals)
-//   st_ready[2]        stats -> softmax WG     exponents of block i published (128 arrivals)
-//   st_free[2]         softmax WG -> stats     exponents slot consumed (128 arrivals)
-//   p_full[2]          softmax WG -> PV issuer P block + its scales in shared memory (128 arrivals)
-//   pv_done[stage]     PV issuer -> softmax, producer: PV of block i complete: P buffer and V
-//                                              stage free, O stable (tcgen05.commit)
-//   fin                both softmax WGs        row sums published for the final combine
-//   drain[2]           issuers                 tensor-core work drained on the abort path
+//   q_full[2]/q_empty[2] producer <-> QK issuer  Q tile + scales of a tile (q_empty by commit)
+//   k_full[], v_full[]   producer -> issuers     K / V tile + scales landed in ring stage
+//   s_full[stage]        QK issuer -> stats      S buffer holds block G (tcgen05.commit); also
+//                                                tells the producer that the K stage is free
+//   s_free[2]            stats + softmax -> QK issuer: S buffer read by all (384 arrivals)
+//   st_ready[2]          stats -> softmax        exponents of block G published (128 arrivals)
+//   st_free[2]           softmax -> stats        exponents slot consumed (256 arrivals)
+//   p_full[2]            softmax -> PV issuer    P block + its scales in shared memory (256)
+//   pv_done[stage]       PV issuer -> softmax, producer: PV of block G complete: P buffer and V
+//                                                stage free, O stable (tcgen05.commit)
+//   fin                  softmax warpgroups      partial row sums published (512, once per tile)
+//   o_free               softmax -> PV issuer    O copied to registers (512, once per tile)
+//   drain[2]             issuers                 tensor-core work drained on the abort path
 #pragma once
 #include "attn_common.cuh"
 #include "attn_serial.cuh"  // tensor-memory map, tile byte sizes
@@ -56,7 +69,7 @@ namespace fa4 {
 // Optional per-role timeline (compile with -DFA4_TRACE): lane 0 of every warp of ONE CTA appends
 // (event, block index, clock64) records to a global buffer set by fa4_nvfp4_debug_set_trace.
 #ifdef FA4_TRACE
-__device__ unsigned long long* g_trace_buf = nullptr;   // [16 warps][kTraceCap][2]
+__device__ unsigned long long* g_trace_buf = nullptr;   // [24 warps][kTraceCap][2]
 __device__ int g_trace_cta = 0;
 constexpr int kTraceCap = 1024;
 #define FA4_TRACE_DECL int trace_n = 0;
@@ -79,15 +92,15 @@ namespace ws {
 
 constexpr int kStagesK = 4;
 constexpr int kStagesV = 4;
-constexpr int kThreads = 512;
-constexpr int kProducerWarp = 8;
-constexpr int kIssuerWarp = 9;    // QK^T issuer, owns tensor memory
-constexpr int kPvIssuerWarp = 10;
-constexpr int kStatsWarp0 = 12;
-// registers per thread after setmaxnreg: 256 * 200 + 128 * 40 + 128 * 72 = 65536
-constexpr int kRegsSoftmax = 200;
+constexpr int kThreads = 768;
+constexpr int kStatsWarp0 = 16;
+constexpr int kProducerWarp = 20;
+constexpr int kIssuerWarp = 21;    // QK^T issuer, owns tensor memory
+constexpr int kPvIssuerWarp = 22;
+// registers per thread after setmaxnreg: 512 * 96 + 128 * 56 + 128 * 40 = 61440 = 768 * 80
+constexpr int kRegsSoftmax = 96;
+constexpr int kRegsStats = 56;
 constexpr int kRegsOther = 40;
-constexpr int kRegsStats = 72;
 
 // per-row record the statistics warpgroup publishes for one block
 struct alignas(16) RowStats {
@@ -96,52 +109,105 @@ struct alignas(16) RowStats {
   float m_prev;    // reference maximum before this block (raw units)
   float m_new;     // reference maximum from this block on
 };
-static_assert(sizeof(RowStats) == 48, "RowStats is read with three 16-byte loads");
+static_assert(sizeof(RowStats) == 48, "RowStats is read with 16-byte loads");
 
 // shared-memory map (offsets from a 1024-byte aligned base)
-constexpr uint32_t kOffQ = 0;                                  // 8 KB
-constexpr uint32_t kOffK = kOffQ + kTileBytes;                 // kStagesK x 8 KB
+constexpr uint32_t kOffQ = 0;                                  // 2 x 8 KB
+constexpr uint32_t kOffK = kOffQ + 2 * kTileBytes;             // kStagesK x 8 KB
 constexpr uint32_t kOffV = kOffK + kStagesK * kTileBytes;      // kStagesV x 8 KB
 constexpr uint32_t kOffP = kOffV + kStagesV * kTileBytes;      // 2 x 8 KB
-constexpr uint32_t kOffSFQ = kOffP + 2 * kTileBytes;           // 1 KB
-constexpr uint32_t kOffSFK = kOffSFQ + kSfBytes;               // kStagesK x 1 KB
+constexpr uint32_t kOffSFQ = kOffP + 2 * kTileBytes;           // 2 x 1 KB
+constexpr uint32_t kOffSFK = kOffSFQ + 2 * kSfBytes;           // kStagesK x 1 KB
 constexpr uint32_t kOffSFV = kOffSFK + kStagesK * kSfBytes;    // kStagesV x 1 KB
 constexpr uint32_t kOffSFP = kOffSFV + kStagesV * kSfBytes;    // 2 x 1 KB
 constexpr uint32_t kOffStats = kOffSFP + 2 * kSfBytes;         // 2 x 128 x RowStats
-constexpr uint32_t kOffFin = kOffStats + 2 * 128 * 48;         // 2 x 128 x (sum, ref) floats
-constexpr uint32_t kOffBar = kOffFin + 2 * 128 * 8;
-constexpr int kNumBars = 1 + 2 * kStagesK + 2 * kStagesV + 2 * 4 + 3;
+constexpr uint32_t kOffFin = kOffStats + 2 * 128 * 48;         // 2 tiles x 4 WGs x 128 x (sum, ref)
+constexpr uint32_t kOffBar = kOffFin + 2 * 4 * 128 * 8;
+constexpr int kNumBars = 4 + 2 * kStagesK + 2 * kStagesV + 2 * 4 + 4;
 constexpr uint32_t kOffMisc = kOffBar + 8 * kNumBars;          // tmem slot, abort flag
 constexpr uint32_t kSmemUsed = kOffMisc + 16;
-constexpr uint32_t kSmemRequest = kSmemUsed + 1024 > 120 * 1024 ? kSmemUsed + 1024 : 120 * 1024;
+constexpr uint32_t kSmemRequest = kSmemUsed + 1024;
+static_assert(kSmemRequest > 114 * 1024, "one CTA per SM: every CTA allocates all of tensor memory");
 
 enum Site {
-  kSiteQFull = 10, kSiteKEmpty, kSiteVEmpty, kSiteKFull, kSiteVFull, kSiteSFull, kSiteSFree,
-  kSitePFull, kSitePvDone, kSiteStReady, kSiteStFree, kSiteFin, kSiteFinalO
+  kSiteQFull = 10, kSiteQEmpty, kSiteKEmpty, kSiteVEmpty, kSiteKFull, kSiteVFull, kSiteSFull,
+  kSiteSFree, kSitePFull, kSitePvDone, kSiteStReady, kSiteStFree, kSiteFin, kSiteFinalO, kSiteOFree
 };
 
+// barrier indices (8 bytes each from the barrier base); kept as constants so that only the base
+// address lives in a register
 struct Bars {
-  uint32_t q_full, k_full, v_full, s_full, s_free, st_ready, st_free, p_full, pv_done, fin, drain;
-  __device__ explicit Bars(uint32_t b) {
-    q_full = b;
-    k_full = q_full + 8;
-    v_full = k_full + 8 * kStagesK;
-    s_full = v_full + 8 * kStagesV;   // kStagesK barriers, indexed by block % kStagesK
-    pv_done = s_full + 8 * kStagesK;  // kStagesV barriers, indexed by block % kStagesV
-    s_free = pv_done + 8 * kStagesV;
-    st_ready = s_free + 16;
-    st_free = st_ready + 16;
-    p_full = st_free + 16;
-    fin = p_full + 16;
-    drain = fin + 8;
-  }
+  uint32_t base;
+  static constexpr uint32_t kQFull = 0, kQEmpty = 2, kKFull = 4, kVFull = kKFull + kStagesK,
+                            kSFull = kVFull + kStagesV, kPvDone = kSFull + kStagesK,
+                            kSFree = kPvDone + kStagesV, kStReady = kSFree + 2, kStFree = kStReady + 2,
+                            kPFull = kStFree + 2, kFin = kPFull + 2, kOFree = kFin + 1,
+                            kDrain = kOFree + 1, kCount = kDrain + 2;
+  __device__ explicit Bars(uint32_t b) : base(b) {}
+  __device__ __forceinline__ uint32_t at(uint32_t idx) const { return base + 8u * idx; }
 };
+static_assert(Bars::kCount <= kNumBars, "barrier area too small");
 
 // Probe first, block (bounded) only if the probe failed; result is warp-uniform.
 __device__ __forceinline__ bool wait_probed(bool probed, uint32_t bar, uint32_t parity,
                                             const WaitCtx& wc, uint32_t site) {
   if (__all_sync(0xffffffffu, probed)) return true;
   return __all_sync(0xffffffffu, mbar_wait(bar, parity, wc, site));
+}
+
+// O[:, 32 * nchunks columns from taddr] *= f for this thread's row.  Rare (the reference maximum
+// moved by more than the lazy threshold), so it is kept out of line: its 32 registers would
+// otherwise be added to the pressure of the exponential loop.
+__device__ __noinline__ void rescale_accumulator(uint32_t taddr, float f, int nchunks) {
+  for (int c = 0; c < nchunks; ++c) {
+    uint32_t o[32];
+    tmem_ld32(taddr + 32 * c, o);
+    tc_wait_ld();
+#pragma unroll
+    for (int x = 0; x < 32; ++x) o[x] = __float_as_uint(__uint_as_float(o[x]) * f);
+    tmem_st32(taddr + 32 * c, o);
+  }
+}
+
+// Keys with in-chunk index > limit of this thread's 64 scores at taddr become -inf.  Only on
+// diagonal blocks; out of line like the rescale.
+__device__ __noinline__ void mask_scores_in_tmem(uint32_t taddr, int limit) {
+  for (int c = 0; c < 2; ++c) {
+    // tcgen05.ld / st are warp-collective: the skip must be decided by the whole warp
+    if (__all_sync(0xffffffffu, limit >= 32 * c + 31)) continue;  // chunk fully visible
+    uint32_t v[32];
+    tmem_ld32(taddr + 32 * c, v);
+    tc_wait_ld();
+#pragma unroll
+    for (int x = 0; x < 32; ++x) v[x] = (32 * c + x <= limit) ? v[x] : 0xff800000u;
+    tmem_st32(taddr + 32 * c, v);
+  }
+  tc_wait_st();
+}
+
+// Tile end: 32 accumulator columns of this thread's row -> registers (then the accumulator may be
+// overwritten: arrive on o_free_bar), scaled, rounded to bf16 and stored.  o_free_bar == 0: the
+// tile had no visible key, nothing to read, zeros are stored.
+__device__ __noinline__ void store_accumulator_chunk(uint32_t taddr, __nv_bfloat16* dst, float scale,
+                                                     uint32_t o_free_bar) {
+  uint32_t o[32];
+  if (o_free_bar != 0u) {
+    tmem_ld32(taddr, o);
+    tc_wait_ld();
+    tc_fence_before_sync();
+    mbar_arrive(o_free_bar);
+  }
+  if (!(scale != 0.f)) {
+#pragma unroll
+    for (int x = 0; x < 32; ++x) o[x] = 0u;
+  }
+  store_out_32(dst, o, scale);
+}
+
+// Tile visited by CTA `cta` in round `it`: rounds alternate direction so that, with tiles sorted
+// by decreasing work, every CTA gets about the same total.
+__device__ __forceinline__ int tile_of_round(int it, int cta, int ncta) {
+  return it * ncta + ((it & 1) ? (ncta - 1 - cta) : cta);
 }
 
 }  // namespace ws
@@ -158,29 +224,32 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + kOffMisc);
   volatile uint32_t* s_abort = reinterpret_cast<volatile uint32_t*>(gbase + kOffMisc + 4);
   RowStats* s_stats = reinterpret_cast<RowStats*>(gbase + kOffStats);            // [2][128]
-  volatile float* s_fin = reinterpret_cast<volatile float*>(gbase + kOffFin);    // [2][128][2]
+  volatile float* s_fin = reinterpret_cast<volatile float*>(gbase + kOffFin);    // [2][4][128][2]
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
   const WaitCtx wc{s_abort, p.status, p.budget_ns};
+  const int num_tiles = p.num_m_blocks * p.Hq * p.B;
+  const int ncta = gridDim.x, cta = blockIdx.x;
 
   if (tid == 0) {
     *s_abort = 0u;
-    mbar_init(bars.q_full, 1);
-    for (int s = 0; s < kStagesK; ++s) mbar_init(bars.k_full + 8 * s, 1);
-    for (int s = 0; s < kStagesV; ++s) mbar_init(bars.v_full + 8 * s, 1);
-    for (int s = 0; s < kStagesK; ++s) mbar_init(bars.s_full + 8 * s, 1);
-    for (int s = 0; s < kStagesV; ++s) mbar_init(bars.pv_done + 8 * s, 1);
     for (int b = 0; b < 2; ++b) {
-      mbar_init(bars.s_free + 8 * b, 256);
-      mbar_init(bars.st_ready + 8 * b, 128);
-      mbar_init(bars.st_free + 8 * b, 128);
-      mbar_init(bars.p_full + 8 * b, 128);
+      mbar_init(bars.at(Bars::kQFull + b), 1);
+      mbar_init(bars.at(Bars::kQEmpty + b), 1);
+      mbar_init(bars.at(Bars::kSFree + b), 384);
+      mbar_init(bars.at(Bars::kStReady + b), 128);
+      mbar_init(bars.at(Bars::kStFree + b), 256);
+      mbar_init(bars.at(Bars::kPFull + b), 256);
+      mbar_init(bars.at(Bars::kDrain + b), 1);
     }
-    mbar_init(bars.fin, 256);
-    mbar_init(bars.drain, 1);
-    mbar_init(bars.drain + 8, 1);
+    for (int s = 0; s < kStagesK; ++s) mbar_init(bars.at(Bars::kKFull + s), 1);
+    for (int s = 0; s < kStagesV; ++s) mbar_init(bars.at(Bars::kVFull + s), 1);
+    for (int s = 0; s < kStagesK; ++s) mbar_init(bars.at(Bars::kSFull + s), 1);
+    for (int s = 0; s < kStagesV; ++s) mbar_init(bars.at(Bars::kPvDone + s), 1);
+    mbar_init(bars.at(Bars::kFin), 512);
+    mbar_init(bars.at(Bars::kOFree), 512);
     fence_barrier_init();
   }
   if (warp == kProducerWarp && lane == 0) {
@@ -196,162 +265,129 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
-  const bool poisoned =
-      (p.status != nullptr) && (*reinterpret_cast<volatile uint32_t*>(p.status) != 0u);
-
-  const Tile t = decode_tile(p, blockIdx.x);
-  const int n = poisoned ? 0 : t.n_blocks;
   constexpr uint32_t idesc = make_idesc_nvf4(128, 128);
   FA4_TRACE_DECL
   FA4_TRACE_EV(0, 0);
 
-  if (warp >= kStatsWarp0) {
-    // =========================================== statistics warpgroup ===========================
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsStats));
-    const int row = tid & 127;
-    const uint32_t lane_addr = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
-    float m_run = kNegInf;
-    bool ok = true;
-    for (int i = 0; ok && i < n; ++i) {
-      const int b = i & 1, nb = n - 1 - i;
-      const uint32_t bar_s = bars.s_full + 8 * (i % kStagesK), par_s = (i / kStagesK) & 1;
-      const uint32_t bar_f = bars.st_free + 8 * b, par_f = ((i - 2) >> 1) & 1;
-      const bool r_s = mbar_try_wait(bar_s, par_s);
-      const bool r_f = (i >= 2) ? mbar_try_wait(bar_f, par_f) : true;
-      ok = wait_probed(r_s, bar_s, par_s, wc, kSiteSFull);
-      if (!ok) break;
-      FA4_TRACE_EV(30, i);
-      tc_fence_after_sync();
-      const bool masked = block_needs_mask(p, t, nb);
-      const int limit = causal_limit(p, t, row, nb);
-      float bm[8];
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        float s[64];
-        tmem_ld32(lane_addr + (b ? kTmS1 : kTmS0) + 64 * h, reinterpret_cast<uint32_t*>(&s[0]));
-        tmem_ld32(lane_addr + (b ? kTmS1 : kTmS0) + 64 * h + 32, reinterpret_cast<uint32_t*>(&s[32]));
-        tc_wait_ld();
-        if (masked) {
-#pragma unroll
-          for (int c = 0; c < 64; ++c) s[c] = (64 * h + c <= limit) ? s[c] : kNegInf;
-        }
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          float m0 = fmax3(s[16 * q], s[16 * q + 1], s[16 * q + 2]);
-          float m1 = fmax3(s[16 * q + 3], s[16 * q + 4], s[16 * q + 5]);
-          m0 = fmax3(m0, s[16 * q + 6], s[16 * q + 7]);
-          m1 = fmax3(m1, s[16 * q + 8], s[16 * q + 9]);
-          m0 = fmax3(m0, s[16 * q + 10], s[16 * q + 11]);
-          m1 = fmax3(m1, s[16 * q + 12], s[16 * q + 13]);
-          m0 = fmax3(m0, s[16 * q + 14], s[16 * q + 15]);
-          bm[4 * h + q] = fmaxf(m0, m1);
-        }
-      }
-      tc_fence_before_sync();
-      mbar_arrive(bars.s_free + 8 * b);
-      const float m01 = fmax3(bm[0], bm[1], bm[2]);
-      const float m23 = fmax3(bm[3], bm[4], bm[5]);
-      const float m_loc = fmax3(fmaxf(m01, m23), bm[6], bm[7]);
-      const float m_new = next_reference(m_run, m_loc, p.sl2);
-      RowStats rs;
-      block_exponents(bm, m_new, p.sl2, rs.noff, rs.ue);
-      rs.m_prev = m_run;
-      rs.m_new = m_new;
-      m_run = m_new;
-      // the slot is free once the softmax warpgroup of block i-2 has read it
-      ok = wait_probed(r_f, bar_f, par_f, wc, kSiteStFree);
-      if (!ok) break;
-      uint4* dst = reinterpret_cast<uint4*>(&s_stats[b * 128 + row]);
-      const uint4* src = reinterpret_cast<const uint4*>(&rs);
-      dst[0] = src[0];
-      dst[1] = src[1];
-      dst[2] = src[2];
-      mbar_arrive(bars.st_ready + 8 * b);
-      FA4_TRACE_EV(31, i);
-    }
-  } else if (warp >= 8) {
-    // registers move from this warpgroup to the softmax warpgroups
+  // Every role walks the same tile list with the same counters:
+  //   gb = number of K/V blocks of the tiles before the current one, ti = number of non-empty
+  //   tiles before the current one.  A failure recorded by any CTA stops all of them at their
+  //   next tile.
+#define FA4_FOR_EACH_TILE                                                                        \
+  uint32_t gb = 0, ti = 0;                                                                       \
+  bool ok = true;                                                                                \
+  for (int it = 0, tile = tile_of_round(0, cta, ncta); ok && tile < num_tiles;                   \
+       ++it, tile = tile_of_round(it, cta, ncta))
+
+  if (warp >= kProducerWarp) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
-    if (warp == kProducerWarp) {
+    if (warp == kProducerWarp && lane == 0) {
       // ========================================= TMA producer ===================================
-      if (lane == 0 && n > 0) {
-        mbar_arrive_expect_tx(bars.q_full, kTileBytes + kSfBytes);
-        tma_load_4d(base + kOffQ, &tm_q, bars.q_full, 0, t.h, t.m_blk * kBlockM, t.b);
-        bulk_load(base + kOffSFQ,
+      uint32_t issued_k = 0, issued_v = 0, issued_q = 0;
+      FA4_FOR_EACH_TILE {
+        const Tile t = decode_tile(p, tile);
+        const int n = t.n_blocks;
+        if (n == 0) continue;
+        if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
+          *s_abort = 1u;  // another CTA failed: stop this one quickly
+          break;
+        }
+        const uint32_t qb = ti & 1;
+        if (ti >= 2) {
+          ok = mbar_wait(bars.at(Bars::kQEmpty + qb), ((ti - 2) >> 1) & 1, wc, kSiteQEmpty);
+          if (!ok) break;
+        }
+        mbar_arrive_expect_tx(bars.at(Bars::kQFull + qb), kTileBytes + kSfBytes);
+        tma_load_4d(base + kOffQ + qb * kTileBytes, &tm_q, bars.at(Bars::kQFull + qb), 0, t.h,
+                    t.m_blk * kBlockM, t.b);
+        bulk_load(base + kOffSFQ + qb * kSfBytes,
                   p.q_sf + t.b * p.qsf_stride_b + t.h * p.qsf_stride_h + (int64_t)t.m_blk * kSfBytes,
-                  kSfBytes, bars.q_full);
+                  kSfBytes, bars.at(Bars::kQFull + qb));
+        issued_q = ti + 1;
         const uint8_t* ksf = p.k_sf + t.b * p.ksf_stride_b + t.hk * p.ksf_stride_h;
         const uint8_t* vsf = p.v_sf + t.b * p.vsf_stride_b + t.hk * p.vsf_stride_h;
-        bool ok = true;
-        int issued_k = 0, issued_v = 0;
         // K runs two blocks ahead of V: QK^T of block i+2 is issued before PV of block i.
         for (int step = 0; ok && step < n + 2; ++step) {
           const int ik = step, iv = step - 2;
           if (ik < n) {
-            const int st = ik % kStagesK, nb = n - 1 - ik;
-            // stage st is free once QK^T of block ik - kStagesK has completed (its s_full phase)
-            if (ik >= kStagesK) {
-              const int j = ik - kStagesK;
-              ok = mbar_wait(bars.s_full + 8 * (j % kStagesK), (j / kStagesK) & 1, wc, kSiteKEmpty);
+            const uint32_t G = gb + ik, st = G % kStagesK;
+            const int nb = n - 1 - ik;
+            // stage st is free once QK^T of block G - kStagesK has completed (its s_full phase)
+            if (G >= kStagesK) {
+              const uint32_t j = G - kStagesK;
+              ok = mbar_wait(bars.at(Bars::kSFull + (j % kStagesK)), (j / kStagesK) & 1, wc, kSiteKEmpty);
               if (!ok) break;
             }
-            mbar_arrive_expect_tx(bars.k_full + 8 * st, kTileBytes + kSfBytes);
-            tma_load_4d(base + kOffK + st * kTileBytes, &tm_k, bars.k_full + 8 * st, 0, t.hk,
+            mbar_arrive_expect_tx(bars.at(Bars::kKFull + st), kTileBytes + kSfBytes);
+            tma_load_4d(base + kOffK + st * kTileBytes, &tm_k, bars.at(Bars::kKFull + st), 0, t.hk,
                         nb * kBlockN, t.b);
             bulk_load(base + kOffSFK + st * kSfBytes, ksf + (int64_t)nb * kSfBytes, kSfBytes,
-                      bars.k_full + 8 * st);
-            issued_k = ik + 1;
+                      bars.at(Bars::kKFull + st));
+            issued_k = G + 1;
           }
           if (iv >= 0 && iv < n) {
-            const int st = iv % kStagesV, nb = n - 1 - iv;
-            if (iv >= kStagesV) {
-              const int j = iv - kStagesV;
-              ok = mbar_wait(bars.pv_done + 8 * (j % kStagesV), (j / kStagesV) & 1, wc, kSiteVEmpty);
+            const uint32_t G = gb + iv, st = G % kStagesV;
+            const int nb = n - 1 - iv;
+            if (G >= kStagesV) {
+              const uint32_t j = G - kStagesV;
+              ok = mbar_wait(bars.at(Bars::kPvDone + (j % kStagesV)), (j / kStagesV) & 1, wc, kSiteVEmpty);
               if (!ok) break;
             }
-            mbar_arrive_expect_tx(bars.v_full + 8 * st, kTileBytes + kSfBytes);
-            tma_load_4d(base + kOffV + st * kTileBytes, &tm_v, bars.v_full + 8 * st,
+            mbar_arrive_expect_tx(bars.at(Bars::kVFull + st), kTileBytes + kSfBytes);
+            tma_load_4d(base + kOffV + st * kTileBytes, &tm_v, bars.at(Bars::kVFull + st),
                         nb * (kBlockN / 2), 0, t.hk, t.b);
             bulk_load(base + kOffSFV + st * kSfBytes, vsf + (int64_t)nb * kSfBytes, kSfBytes,
-                      bars.v_full + 8 * st);
-            issued_v = iv + 1;
+                      bars.at(Bars::kVFull + st));
+            issued_v = G + 1;
           }
         }
-        if (!ok) {
-          // bounded drain: let the copies already issued land before the CTA's memory is released
-          const uint64_t t0 = globaltimer_ns();
-          const uint64_t lim = 50ull * 1000 * 1000;
-          for (int i = issued_k > kStagesK ? issued_k - kStagesK : 0; i < issued_k; ++i) {
-            while (!mbar_try_wait(bars.k_full + 8 * (i % kStagesK), (i / kStagesK) & 1) &&
-                   globaltimer_ns() - t0 < lim) {}
-          }
-          for (int i = issued_v > kStagesV ? issued_v - kStagesV : 0; i < issued_v; ++i) {
-            while (!mbar_try_wait(bars.v_full + 8 * (i % kStagesV), (i / kStagesV) & 1) &&
-                   globaltimer_ns() - t0 < lim) {}
-          }
-          while (!mbar_try_wait(bars.q_full, 0) && globaltimer_ns() - t0 < lim) {}
+        gb += n;
+        ti += 1;
+      }
+      if (!ok) {
+        // bounded drain: let the copies already issued land before the CTA's memory is released
+        const uint64_t t0 = globaltimer_ns();
+        const uint64_t lim = 50ull * 1000 * 1000;
+        for (uint32_t i = issued_k > kStagesK ? issued_k - kStagesK : 0; i < issued_k; ++i) {
+          while (!mbar_try_wait(bars.at(Bars::kKFull + (i % kStagesK)), (i / kStagesK) & 1) &&
+                 globaltimer_ns() - t0 < lim) {}
+        }
+        for (uint32_t i = issued_v > kStagesV ? issued_v - kStagesV : 0; i < issued_v; ++i) {
+          while (!mbar_try_wait(bars.at(Bars::kVFull + (i % kStagesV)), (i / kStagesV) & 1) &&
+                 globaltimer_ns() - t0 < lim) {}
+        }
+        for (uint32_t i = issued_q > 2 ? issued_q - 2 : 0; i < issued_q; ++i) {
+          while (!mbar_try_wait(bars.at(Bars::kQFull + (i & 1)), (i >> 1) & 1) && globaltimer_ns() - t0 < lim) {}
         }
       }
-    } else if (warp == kIssuerWarp) {
+    } else if (warp == kIssuerWarp && lane == 0) {
       // ========================================= QK^T issuer ====================================
-      if (lane == 0 && n > 0) {
-        bool ok = mbar_wait(bars.q_full, 0, wc, kSiteQFull);
-        if (ok) {
-          tc_fence_after_sync();
-          tc_cp_sf(tmem + kTmSFQ, base + kOffSFQ);
-          tc_cp_sf(tmem + kTmSFQ + 4, base + kOffSFQ + 512);
+      FA4_FOR_EACH_TILE {
+        const Tile t = decode_tile(p, tile);
+        const int n = t.n_blocks;
+        if (n == 0) continue;
+        if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
+          *s_abort = 1u;  // another CTA failed: stop this one quickly
+          break;
         }
-        const uint64_t dq0 = make_desc_sw64(base + kOffQ), dq1 = make_desc_sw64(base + kOffQ + 32);
-        for (int i = 0; ok && i < n; ++i) {
-          const int st = i % kStagesK, b = i & 1;
-          if (i >= 2) {
-            // S buffer b is free once block i-2 has been read by the stats and softmax warps
-            ok = mbar_wait(bars.s_free + 8 * b, ((i - 2) >> 1) & 1, wc, kSiteSFree);
+        const uint32_t qb = ti & 1;
+        ok = mbar_wait(bars.at(Bars::kQFull + qb), (ti >> 1) & 1, wc, kSiteQFull);
+        if (!ok) break;
+        tc_fence_after_sync();
+        tc_cp_sf(tmem + kTmSFQ, base + kOffSFQ + qb * kSfBytes);
+        tc_cp_sf(tmem + kTmSFQ + 4, base + kOffSFQ + qb * kSfBytes + 512);
+        const uint64_t dq0 = make_desc_sw64(base + kOffQ + qb * kTileBytes);
+        const uint64_t dq1 = make_desc_sw64(base + kOffQ + qb * kTileBytes + 32);
+        for (int i = 0; i < n; ++i) {
+          const uint32_t G = gb + i, st = G % kStagesK, b = G & 1;
+          if (G >= 2) {
+            // S buffer b is free once block G-2 has been read by the stats and softmax warps
+            ok = mbar_wait(bars.at(Bars::kSFree + b), ((G - 2) >> 1) & 1, wc, kSiteSFree);
             if (!ok) break;
           }
-          ok = mbar_wait(bars.k_full + 8 * st, (i / kStagesK) & 1, wc, kSiteKFull);
+          ok = mbar_wait(bars.at(Bars::kKFull + st), (G / kStagesK) & 1, wc, kSiteKFull);
           if (!ok) break;
-          FA4_TRACE_EV(20, i);
+          FA4_TRACE_EV(20, G);
           tc_fence_after_sync();
           const uint32_t sfk = tmem + kTmSFK + 8 * b;
           const uint32_t ksf = base + kOffSFK + st * kSfBytes, kt = base + kOffK + st * kTileBytes;
@@ -360,27 +396,42 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
           const uint32_t s_tm = tmem + (b ? kTmS1 : kTmS0);
           mma_nvf4(s_tm, dq0, make_desc_sw64(kt), idesc, tmem + kTmSFQ, sfk, 0u);
           mma_nvf4(s_tm, dq1, make_desc_sw64(kt + 32), idesc, tmem + kTmSFQ + 4, sfk + 4, 1u);
-          tc_commit(bars.s_full + 8 * st);
-          FA4_TRACE_EV(27, i);
+          tc_commit(bars.at(Bars::kSFull + st));
+          FA4_TRACE_EV(27, G);
         }
-        if (!ok) {
-          // bounded drain of the tensor-core work already issued, before tensor memory is freed
-          const uint64_t t0 = globaltimer_ns();
-          tc_commit(bars.drain);
-          while (!mbar_try_wait(bars.drain, 0) && globaltimer_ns() - t0 < 50ull * 1000 * 1000) {}
-        }
+        if (!ok) break;
+        tc_commit(bars.at(Bars::kQEmpty + qb));  // the Q buffer is free once the tile's QK^T have run
+        gb += n;
+        ti += 1;
       }
-    } else if (warp == kPvIssuerWarp) {
+      if (!ok) {
+        // bounded drain of the tensor-core work already issued, before tensor memory is freed
+        const uint64_t t0 = globaltimer_ns();
+        tc_commit(bars.at(Bars::kDrain));
+        while (!mbar_try_wait(bars.at(Bars::kDrain), 0) && globaltimer_ns() - t0 < 50ull * 1000 * 1000) {}
+      }
+    } else if (warp == kPvIssuerWarp && lane == 0) {
       // ========================================= PV issuer ======================================
-      if (lane == 0 && n > 0) {
-        bool ok = true;
-        for (int i = 0; ok && i < n; ++i) {
-          const int st = i % kStagesV, b = i & 1;
-          ok = mbar_wait(bars.v_full + 8 * st, (i / kStagesV) & 1, wc, kSiteVFull);
+      FA4_FOR_EACH_TILE {
+        const Tile t = decode_tile(p, tile);
+        const int n = t.n_blocks;
+        if (n == 0) continue;
+        if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
+          *s_abort = 1u;  // another CTA failed: stop this one quickly
+          break;
+        }
+        for (int i = 0; i < n; ++i) {
+          const uint32_t G = gb + i, st = G % kStagesV, b = G & 1;
+          ok = mbar_wait(bars.at(Bars::kVFull + st), (G / kStagesV) & 1, wc, kSiteVFull);
           if (!ok) break;
-          ok = mbar_wait(bars.p_full + 8 * b, (i >> 1) & 1, wc, kSitePFull);
+          ok = mbar_wait(bars.at(Bars::kPFull + b), (G >> 1) & 1, wc, kSitePFull);
           if (!ok) break;
-          FA4_TRACE_EV(22, i);
+          if (i == 0 && ti >= 1) {
+            // O of the previous tile must have been copied out of tensor memory
+            ok = mbar_wait(bars.at(Bars::kOFree), (ti - 1) & 1, wc, kSiteOFree);
+            if (!ok) break;
+          }
+          FA4_TRACE_EV(22, G);
           tc_fence_after_sync();
           const uint32_t sfp = tmem + kTmSFP + 8 * b, sfv = tmem + kTmSFV + 8 * b;
           const uint32_t psf = base + kOffSFP + b * kSfBytes, vsf = base + kOffSFV + st * kSfBytes;
@@ -393,144 +444,225 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
           tc_cp_sf(sfv + 4, vsf + 512);
           mma_nvf4(tmem + kTmO, make_desc_sw64(pt + 32), make_desc_sw64(vt + 32), idesc, sfp + 4,
                    sfv + 4, 1u);
-          tc_commit(bars.pv_done + 8 * st);
-          FA4_TRACE_EV(23, i);
+          tc_commit(bars.at(Bars::kPvDone + st));
+          FA4_TRACE_EV(23, G);
         }
-        if (!ok) {
-          const uint64_t t0 = globaltimer_ns();
-          tc_commit(bars.drain + 8);
-          while (!mbar_try_wait(bars.drain + 8, 0) && globaltimer_ns() - t0 < 50ull * 1000 * 1000) {}
-        }
+        if (!ok) break;
+        gb += n;
+        ti += 1;
       }
+      if (!ok) {
+        const uint64_t t0 = globaltimer_ns();
+        tc_commit(bars.at(Bars::kDrain + 1));
+        while (!mbar_try_wait(bars.at(Bars::kDrain + 1), 0) && globaltimer_ns() - t0 < 50ull * 1000 * 1000) {}
+      }
+    }
+  } else if (warp >= kStatsWarp0) {
+    // =========================================== statistics warpgroup ===========================
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsStats));
+    const int row = tid & 127;
+    const uint32_t lane_addr = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+    FA4_FOR_EACH_TILE {
+      const Tile t = decode_tile(p, tile);
+      const int n = t.n_blocks;
+      if (n == 0) continue;
+      if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
+          *s_abort = 1u;  // another CTA failed: stop this one quickly
+          break;
+        }
+      float m_run = kNegInf;
+      for (int i = 0; i < n; ++i) {
+        const uint32_t G = gb + i, b = G & 1;
+        const int nb = n - 1 - i;
+        const uint32_t bar_s = bars.at(Bars::kSFull + (G % kStagesK)), par_s = (G / kStagesK) & 1;
+        const uint32_t bar_f = bars.at(Bars::kStFree + b), par_f = ((G - 2) >> 1) & 1;
+        const bool r_s = mbar_try_wait(bar_s, par_s);
+        const bool r_f = (G >= 2) ? mbar_try_wait(bar_f, par_f) : true;
+        ok = wait_probed(r_s, bar_s, par_s, wc, kSiteSFull);
+        if (!ok) break;
+        FA4_TRACE_EV(30, G);
+        tc_fence_after_sync();
+        const bool masked = block_needs_mask(p, t, nb);
+        const int limit = causal_limit(p, t, row, nb);
+        float bm[8];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          float s[32];
+          tmem_ld32(lane_addr + (b ? kTmS1 : kTmS0) + 32 * c, reinterpret_cast<uint32_t*>(&s[0]));
+          tc_wait_ld();
+          if (masked) {
+#pragma unroll
+            for (int x = 0; x < 32; ++x) s[x] = (32 * c + x <= limit) ? s[x] : kNegInf;
+          }
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            float m0 = fmax3(s[16 * q], s[16 * q + 1], s[16 * q + 2]);
+            float m1 = fmax3(s[16 * q + 3], s[16 * q + 4], s[16 * q + 5]);
+            m0 = fmax3(m0, s[16 * q + 6], s[16 * q + 7]);
+            m1 = fmax3(m1, s[16 * q + 8], s[16 * q + 9]);
+            m0 = fmax3(m0, s[16 * q + 10], s[16 * q + 11]);
+            m1 = fmax3(m1, s[16 * q + 12], s[16 * q + 13]);
+            m0 = fmax3(m0, s[16 * q + 14], s[16 * q + 15]);
+            bm[2 * c + q] = fmaxf(m0, m1);
+          }
+        }
+        tc_fence_before_sync();
+        mbar_arrive(bars.at(Bars::kSFree + b));
+        const float m01 = fmax3(bm[0], bm[1], bm[2]);
+        const float m23 = fmax3(bm[3], bm[4], bm[5]);
+        const float m_loc = fmax3(fmaxf(m01, m23), bm[6], bm[7]);
+        const float m_new = next_reference(m_run, m_loc, p.sl2);
+        RowStats rs;
+        block_exponents(bm, m_new, p.sl2, rs.noff, rs.ue);
+        rs.m_prev = m_run;
+        rs.m_new = m_new;
+        m_run = m_new;
+        // the slot is free once the softmax warpgroups of block G-2 have read it
+        ok = wait_probed(r_f, bar_f, par_f, wc, kSiteStFree);
+        if (!ok) break;
+        uint4* dst = reinterpret_cast<uint4*>(&s_stats[b * 128 + row]);
+        const uint4* src = reinterpret_cast<const uint4*>(&rs);
+        dst[0] = src[0];
+        dst[1] = src[1];
+        dst[2] = src[2];
+        mbar_arrive(bars.at(Bars::kStReady + b));
+        FA4_TRACE_EV(31, G);
+      }
+      if (!ok) break;
+      gb += n;
+      ti += 1;
     }
   } else {
     // =========================================== softmax warpgroups =============================
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
-    const int g = warp >> 2;        // warpgroup 0 / 1
-    const int row = tid & 127;      // tile row == tensor-memory lane
+    const int wg = warp >> 2;          // 0..3
+    const int half = wg & 1;           // key columns [64 half, 64 half + 64) of a block
+    const int g = wg >> 1;             // takes the blocks of a tile with (index in tile) % 2 == g
+    const int row = (warp & 3) * 32 + lane;  // tile row == tensor-memory lane
     const uint32_t lane_addr = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
-    float m_ref = kNegInf, l_sum = 0.f;
-    bool ok = true;
 
-    for (int i = g; ok && i < n; i += 2) {
-      const int u = i >> 1, nb = n - 1 - i;
-      FA4_TRACE_EV(1, i);
-      // Probe both barriers this block depends on back to back so that their latencies overlap;
-      // the blocking (bounded) wait only runs for a probe that failed.  st_ready implies s_full.
-      const uint32_t bar_r = bars.st_ready + 8 * g, par_r = u & 1;
-      const uint32_t bar_p = bars.pv_done + 8 * ((i - 2) % kStagesV), par_p = ((i - 2) / kStagesV) & 1;
-      const bool r_r = mbar_try_wait(bar_r, par_r);
-      const bool r_p = (i >= 2) ? mbar_try_wait(bar_p, par_p) : true;
-      ok = wait_probed(r_r, bar_r, par_r, wc, kSiteStReady);
-      if (!ok) break;
-      tc_fence_after_sync();
-      float s[128];
-#pragma unroll
-      for (int c = 0; c < 4; ++c)
-        tmem_ld32(lane_addr + (g ? kTmS1 : kTmS0) + 32 * c, reinterpret_cast<uint32_t*>(&s[32 * c]));
-      // this row's exponents (read while the tensor-memory load is in flight)
-      RowStats rs;
-      {
-        const uint4* src = reinterpret_cast<const uint4*>(&s_stats[g * 128 + row]);
-        uint4* dst = reinterpret_cast<uint4*>(&rs);
-        dst[0] = src[0];
-        dst[1] = src[1];
-        dst[2] = src[2];
+    FA4_FOR_EACH_TILE {
+      const Tile t = decode_tile(p, tile);
+      const int n = t.n_blocks;
+      const bool poisoned =
+          (p.status != nullptr) && (*reinterpret_cast<volatile uint32_t*>(p.status) != 0u);
+      if (poisoned) {
+        *s_abort = 1u;
+        break;
       }
-      tc_wait_ld();
-      tc_fence_before_sync();
-      mbar_arrive(bars.s_free + 8 * g);
-      mbar_arrive(bars.st_free + 8 * g);
+      float m_ref = kNegInf, l_sum = 0.f;
 
-      if (block_needs_mask(p, t, nb)) mask_row(s, causal_limit(p, t, row, nb));
-
-      // own partial row sum follows the reference
-      if (rs.m_new != m_ref) l_sum *= reference_factor(m_ref, rs.m_new, p.sl2);
-      m_ref = rs.m_new;
-
-      // correction: O holds blocks 0..i-1 relative to m_prev
-      if (i > 0 && __any_sync(0xffffffffu, rs.m_new != rs.m_prev)) {
-        ok = __all_sync(0xffffffffu,
-                        mbar_wait(bars.pv_done + 8 * ((i - 1) % kStagesV), ((i - 1) / kStagesV) & 1, wc,
-                                  kSitePvDone));
+      for (int i = g; i < n; i += 2) {
+        const uint32_t G = gb + i, b = G & 1;  // b: S / P / stats buffer of this block
+        const int nb = n - 1 - i;
+        FA4_TRACE_EV(1, G);
+        // Probe both barriers this block depends on back to back so that their latencies
+        // overlap; the blocking (bounded) wait only runs for a probe that failed.
+        // st_ready implies s_full.
+        const uint32_t bar_r = bars.at(Bars::kStReady + b), par_r = (G >> 1) & 1;
+        const uint32_t bar_p = bars.at(Bars::kPvDone + ((G - 2) % kStagesV)), par_p = ((G - 2) / kStagesV) & 1;
+        const bool r_r = mbar_try_wait(bar_r, par_r);
+        const bool r_p = (G >= 2) ? mbar_try_wait(bar_p, par_p) : true;
+        ok = wait_probed(r_r, bar_r, par_r, wc, kSiteStReady);
         if (!ok) break;
         tc_fence_after_sync();
-        const float f = (rs.m_new != rs.m_prev) ? reference_factor(rs.m_prev, rs.m_new, p.sl2) : 1.f;
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t o[32];
-          tmem_ld32(lane_addr + kTmO + 32 * c, o);
-          tc_wait_ld();
-#pragma unroll
-          for (int x = 0; x < 32; ++x) o[x] = __float_as_uint(__uint_as_float(o[x]) * f);
-          tmem_st32(lane_addr + kTmO + 32 * c, o);
+        // this row's exponents
+        const uint4* st_row = reinterpret_cast<const uint4*>(&s_stats[b * 128 + row]);
+        const uint4 v_noff = st_row[half];
+        const uint4 v_misc = st_row[2];
+        const float m_prev = __uint_as_float(v_misc.z), m_new = __uint_as_float(v_misc.w);
+        const uint32_t ue = half ? v_misc.y : v_misc.x;
+
+        // own partial row sum follows the reference
+        if (m_new != m_ref) l_sum *= reference_factor(m_ref, m_new, p.sl2);
+        m_ref = m_new;
+
+        // The two rare steps come BEFORE the scores are loaded, so that no large register array is
+        // live across their out-of-line calls.
+        // correction: O holds blocks 0..i-1 relative to m_prev; this warpgroup rescales its
+        // 64 columns of O
+        if (i > 0 && __any_sync(0xffffffffu, m_new != m_prev)) {
+          ok = __all_sync(0xffffffffu, mbar_wait(bars.at(Bars::kPvDone + ((G - 1) % kStagesV)),
+                                                 ((G - 1) / kStagesV) & 1, wc, kSitePvDone));
+          if (!ok) break;
+          tc_fence_after_sync();
+          const float f = (m_new != m_prev) ? reference_factor(m_prev, m_new, p.sl2) : 1.f;
+          rescale_accumulator(lane_addr + kTmO + 64 * half, f, 2);
+          tc_wait_st();
         }
-        tc_wait_st();
-      }
+        const uint32_t s_addr = lane_addr + (b ? kTmS1 : kTmS0) + 64 * half;
+        // diagonal block: the statistics warps are done with S (st_ready), so this thread may
+        // overwrite the masked keys of its own half row in tensor memory before loading it
+        if (block_needs_mask(p, t, nb)) mask_scores_in_tmem(s_addr, causal_limit(p, t, row, nb) - 64 * half);
 
-      // P buffer g is free once PV of block i-2 has completed
-      ok = wait_probed(r_p, bar_p, par_p, wc, kSitePvDone);
+        float s[64];
+        tmem_ld32(s_addr, reinterpret_cast<uint32_t*>(&s[0]));
+        tmem_ld32(s_addr + 32, reinterpret_cast<uint32_t*>(&s[32]));
+        tc_wait_ld();
+        tc_fence_before_sync();
+        mbar_arrive(bars.at(Bars::kSFree + b));
+        mbar_arrive(bars.at(Bars::kStFree + b));
+
+        // P buffer g is free once PV of block G-2 has completed
+        ok = wait_probed(r_p, bar_p, par_p, wc, kSitePvDone);
+        if (!ok) break;
+        FA4_TRACE_EV(6, G);
+        uint8_t* p_tile = gbase + kOffP + b * kTileBytes;
+        uint4 chunk;
+        l_sum += quantize_pair(&s[0], __uint_as_float(v_noff.x), __uint_as_float(v_noff.y),
+                               __byte_perm(ue, 0u, 0x4440u), __byte_perm(ue, 0u, 0x4441u), p.sl2, chunk);
+        *reinterpret_cast<uint4*>(p_tile + sw64_offset(row, 2 * half)) = chunk;
+        l_sum += quantize_pair(&s[32], __uint_as_float(v_noff.z), __uint_as_float(v_noff.w),
+                               __byte_perm(ue, 0u, 0x4442u), __byte_perm(ue, 0u, 0x4443u), p.sl2, chunk);
+        *reinterpret_cast<uint4*>(p_tile + sw64_offset(row, 2 * half + 1)) = chunk;
+        FA4_TRACE_EV(7, G);
+        // scales of this half: one 64-key MMA step = scale word `half`
+        *reinterpret_cast<uint32_t*>(gbase + kOffSFP + b * kSfBytes + 512 * half + (row & 31) * 16 +
+                                     (row >> 5) * 4) = block_scale_bytes(ue);
+        fence_proxy_async_smem();
+        tc_fence_before_sync();  // orders the O rescale stores before the issuer's next MMA
+        mbar_arrive(bars.at(Bars::kPFull + b));
+      }
       if (!ok) break;
-      FA4_TRACE_EV(6, i);
-      l_sum += quantize_row(s, rs.noff, rs.ue, p.sl2, gbase + kOffP + g * kTileBytes, row);
-      FA4_TRACE_EV(7, i);
-      uint8_t* ssf = gbase + kOffSFP + g * kSfBytes;
-#pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        *reinterpret_cast<uint32_t*>(ssf + 512 * j + (row & 31) * 16 + (row >> 5) * 4) =
-            block_scale_bytes(rs.ue[j]);
-      }
-      fence_proxy_async_smem();
-      tc_fence_before_sync();  // orders the O rescale stores before the issuer's next MMA
-      mbar_arrive(bars.p_full + 8 * g);
-    }
 
-    // ---- final combine of the two partial row sums ------------------------------------------------
-    if (ok && n > 0) {
-      s_fin[(g * 128 + row) * 2] = l_sum;
-      s_fin[(g * 128 + row) * 2 + 1] = m_ref;
-      mbar_arrive(bars.fin);
-      ok = __all_sync(0xffffffffu, mbar_wait(bars.fin, 0, wc, kSiteFin));
-      if (ok) {
-        const float l_other = s_fin[((g ^ 1) * 128 + row) * 2];
-        const float m_other = s_fin[((g ^ 1) * 128 + row) * 2 + 1];
-        const float m_fin = fmaxf(m_ref, m_other);
-        const float l_tot = l_sum * reference_factor(m_ref, m_fin, p.sl2) +
-                            l_other * reference_factor(m_other, m_fin, p.sl2);
-        l_sum = (m_fin == kNegInf) ? 0.f : l_tot;
-        m_ref = m_fin;
-        ok = __all_sync(0xffffffffu,
-                        mbar_wait(bars.pv_done + 8 * ((n - 1) % kStagesV), ((n - 1) / kStagesV) & 1, wc,
-                                  kSiteFinalO));
-        tc_fence_after_sync();
-      }
-    }
-
-    // ---- epilogue: warpgroup g stores output columns [64 g, 64 g + 64) ------------------------------
-    if (ok && !poisoned) {
+      // ---- tile end: combine the four partial row sums, read O, store ---------------------------
       const int q_idx = t.m_blk * kBlockM + row;
       __nv_bfloat16* orow =
-          p.out + t.b * p.o_stride_b + (int64_t)q_idx * p.o_stride_s + t.h * p.o_stride_h;
-      const bool empty = (n == 0) || !(l_sum > 0.f);
-      const float scale = empty ? 0.f : p.out_scale / l_sum;
-#pragma unroll 1
-      for (int c = 2 * g; c < 2 * g + 2; ++c) {
-        uint32_t o[32];
-        if (n > 0) {
-          tmem_ld32(lane_addr + kTmO + 32 * c, o);
-          tc_wait_ld();
-        }
-        if (empty) {
+          p.out + t.b * p.o_stride_b + (int64_t)q_idx * p.o_stride_s + t.h * p.o_stride_h + 32 * wg;
+      float scale = 0.f, m_fin = kNegInf, l_tot = 0.f;
+      if (n > 0) {
+        volatile float* fin_slot = s_fin + (ti & 1) * (4 * 128 * 2);
+        fin_slot[(wg * 128 + row) * 2] = l_sum;
+        fin_slot[(wg * 128 + row) * 2 + 1] = m_ref;
+        mbar_arrive(bars.at(Bars::kFin));
+        ok = __all_sync(0xffffffffu, mbar_wait(bars.at(Bars::kFin), ti & 1, wc, kSiteFin));
+        if (!ok) break;
+        float lw[4], mw[4];
 #pragma unroll
-          for (int x = 0; x < 32; ++x) o[x] = 0u;
+        for (int w = 0; w < 4; ++w) {
+          lw[w] = fin_slot[(w * 128 + row) * 2];
+          mw[w] = fin_slot[(w * 128 + row) * 2 + 1];
+          m_fin = fmaxf(m_fin, mw[w]);
         }
-        store_out_32(orow + 32 * c, o, scale);
+#pragma unroll
+        for (int w = 0; w < 4; ++w) l_tot += lw[w] * reference_factor(mw[w], m_fin, p.sl2);
+        if (m_fin == kNegInf) l_tot = 0.f;
+        const uint32_t Gl = gb + n - 1;
+        ok = __all_sync(0xffffffffu,
+                        mbar_wait(bars.at(Bars::kPvDone + (Gl % kStagesV)), (Gl / kStagesV) & 1, wc, kSiteFinalO));
+        if (!ok) break;
+        tc_fence_after_sync();
+        scale = (l_tot > 0.f) ? p.out_scale / l_tot : 0.f;
       }
-      if (g == 0 && p.lse != nullptr) {
-        p.lse[((int64_t)t.b * p.Hq + t.h) * p.Sq + q_idx] = finish_lse(m_ref, l_sum, p.sl2);
+      store_accumulator_chunk(lane_addr + kTmO + 32 * wg, orow, scale, n > 0 ? bars.at(Bars::kOFree) : 0u);
+      if (wg == 0 && p.lse != nullptr) {
+        p.lse[((int64_t)t.b * p.Hq + t.h) * p.Sq + q_idx] = finish_lse(m_fin, l_tot, p.sl2);
       }
+      gb += n;
+      ti += (n > 0) ? 1u : 0u;
     }
   }
+#undef FA4_FOR_EACH_TILE
 
   tc_fence_before_sync();
   __syncthreads();

@@ -42,24 +42,12 @@ static_assert(kLazy + kShift <= 10, "P block scales would overflow ue4m3");
 
 constexpr float kNegInf = -INFINITY;
 
-// ---- packed two-wide fp32 arithmetic (one issue slot for two lanes) ---------------------------
+// ---- packed two-wide fp32 arithmetic (one issue slot for two lanes): the sm_100 intrinsics
+// __ffma2_rn / __fadd2_rn on float2 values.
 __device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
   uint64_t r;
   asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
   return r;
-}
-__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
-  uint64_t d;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-  return d;
-}
-__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
-  uint64_t d;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-  return d;
 }
 
 // Block maxima (8 blocks of 16 keys) and the row maximum of one 128-key row.
@@ -129,48 +117,55 @@ __device__ __forceinline__ uint32_t block_scale_bytes(uint32_t ue_word) {
   return (ue_word - 0x78787878u) << 3;
 }
 
+// Quantise two neighbouring key blocks (32 scores) of one row: the unit one 16-byte chunk of the
+// P tile holds.  noff0/noff1 and e0/e1 (bytes e + 127) come from block_exponents().
+//   out   packed e2m1 of the 32 values, key order
+//   returns the sum of p' (un-rounded) over the 32 keys
+__device__ __forceinline__ float quantize_pair(const float* s, float noff0, float noff1, uint32_t e0,
+                                               uint32_t e1, float sl2, uint4& out) {
+  float acc = 0.f;
+  uint32_t pk[4];
+  const float2 sl2_2 = make_float2(sl2, sl2);
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const float noff = h ? noff1 : noff0;
+    const float2 noff2 = make_float2(noff, noff);
+    float2 p[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float2 x = __ffma2_rn(make_float2(s[16 * h + 2 * j], s[16 * h + 2 * j + 1]), sl2_2, noff2);
+      p[j] = make_float2(ex2_approx(x.x), ex2_approx(x.y));
+    }
+    float2 sum_a = __fadd2_rn(p[0], p[1]);
+    float2 sum_b = __fadd2_rn(p[2], p[3]);
+    sum_a = __fadd2_rn(sum_a, p[4]);
+    sum_b = __fadd2_rn(sum_b, p[5]);
+    sum_a = __fadd2_rn(sum_a, p[6]);
+    sum_b = __fadd2_rn(sum_b, p[7]);
+    sum_a = __fadd2_rn(sum_a, sum_b);
+    pk[2 * h] = pack8_e2m1(p[0].x, p[0].y, p[1].x, p[1].y, p[2].x, p[2].y, p[3].x, p[3].y);
+    pk[2 * h + 1] = pack8_e2m1(p[4].x, p[4].y, p[5].x, p[5].y, p[6].x, p[6].y, p[7].x, p[7].y);
+    // 2^e as fp32: byte (e + 127) moved into the exponent field
+    acc = fmaf(sum_a.x + sum_a.y, __uint_as_float((h ? e1 : e0) << 23), acc);
+  }
+  out = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+  return acc;
+}
+
 // Quantise one row of 128 scores with the exponents from block_exponents() and store it as one
-// row of the P tile.
-//   p_tile  shared-memory P tile (K-major, 64-byte rows, 64-byte swizzle); each 16-byte chunk
-//           (32 keys = 2 blocks) is stored as soon as it is complete, to keep registers free
-//   returns the row's sum of p' (un-rounded), to be added to the running sum
+// row of the P tile (K-major, 64-byte rows, 64-byte swizzle), one 16-byte chunk at a time.
+// Returns the row's sum of p' (un-rounded), to be added to the running sum.
 __device__ __forceinline__ float quantize_row(const float (&s)[128], const float (&noff)[8],
                                               const uint32_t (&ue)[2], float sl2, uint8_t* p_tile,
                                               uint32_t row) {
-  const uint64_t sl2_2 = f2_pack(sl2, sl2);
   float acc = 0.f;
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
-    uint32_t pk[4];
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const int b = 2 * c + h;
-      const uint64_t noff2 = f2_pack(noff[b], noff[b]);
-      float p[16];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const uint64_t x2 = f2_fma(f2_pack(s[16 * b + 2 * j], s[16 * b + 2 * j + 1]), sl2_2, noff2);
-        float x0, x1;
-        f2_unpack(x2, x0, x1);
-        p[2 * j] = ex2_approx(x0);
-        p[2 * j + 1] = ex2_approx(x1);
-      }
-      uint64_t sum2 = f2_add(f2_pack(p[0], p[1]), f2_pack(p[2], p[3]));
-      uint64_t sum3 = f2_add(f2_pack(p[4], p[5]), f2_pack(p[6], p[7]));
-      sum2 = f2_add(sum2, f2_pack(p[8], p[9]));
-      sum3 = f2_add(sum3, f2_pack(p[10], p[11]));
-      sum2 = f2_add(sum2, f2_pack(p[12], p[13]));
-      sum3 = f2_add(sum3, f2_pack(p[14], p[15]));
-      sum2 = f2_add(sum2, sum3);
-      pk[2 * h] = pack8_e2m1(p[0], p[1], p[2], p[3], p[4], p[5], p[6], p[7]);
-      pk[2 * h + 1] = pack8_e2m1(p[8], p[9], p[10], p[11], p[12], p[13], p[14], p[15]);
-      float s0, s1;
-      f2_unpack(sum2, s0, s1);
-      // 2^e as fp32: byte (e + 127) moved into the exponent field
-      const uint32_t eb = __byte_perm(ue[b >> 2], 0u, 0x4440u + (b & 3));
-      acc = fmaf(s0 + s1, __uint_as_float(eb << 23), acc);
-    }
-    *reinterpret_cast<uint4*>(p_tile + sw64_offset(row, c)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+    uint4 chunk;
+    acc += quantize_pair(&s[32 * c], noff[2 * c], noff[2 * c + 1],
+                         __byte_perm(ue[c >> 1], 0u, 0x4440u + ((2 * c) & 3)),
+                         __byte_perm(ue[c >> 1], 0u, 0x4440u + ((2 * c + 1) & 3)), sl2, chunk);
+    *reinterpret_cast<uint4*>(p_tile + sw64_offset(row, c)) = chunk;
   }
   return acc;
 }
