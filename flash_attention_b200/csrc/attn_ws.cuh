@@ -556,54 +556,48 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         const uint32_t G = gb + i, b = G & 1;  // b: S / P / stats buffer of this block
         const int nb = n - 1 - i;
         FA4_TRACE_EV(1, G);
-        // Probe both barriers this block depends on back to back so that their latencies
+        // Probe the three barriers this block depends on back to back so that their latencies
         // overlap; the blocking (bounded) wait only runs for a probe that failed.
-        // st_ready implies s_full.
+        const uint32_t bar_s = bars.at(Bars::kSFull + (G % kStagesK)), par_s = (G / kStagesK) & 1;
         const uint32_t bar_r = bars.at(Bars::kStReady + b), par_r = (G >> 1) & 1;
         const uint32_t bar_p = bars.at(Bars::kPvDone + ((G - 2) % kStagesV)), par_p = ((G - 2) / kStagesV) & 1;
+        const bool r_s = mbar_try_wait(bar_s, par_s);
         const bool r_r = mbar_try_wait(bar_r, par_r);
         const bool r_p = (G >= 2) ? mbar_try_wait(bar_p, par_p) : true;
-        ok = wait_probed(r_r, bar_r, par_r, wc, kSiteStReady);
+
+        // 1. scores: copied to registers as soon as the MMA has written them, so that the S buffer
+        //    goes back to the QK^T issuer without waiting for the statistics (the buffer's cycle
+        //    MMA -> readers -> MMA bounds the block rate)
+        ok = wait_probed(r_s, bar_s, par_s, wc, kSiteSFull);
         if (!ok) break;
         tc_fence_after_sync();
-        // this row's exponents
-        const uint4* st_row = reinterpret_cast<const uint4*>(&s_stats[b * 128 + row]);
-        const uint4 v_noff = st_row[half];
-        const uint4 v_misc = st_row[2];
-        const float m_prev = __uint_as_float(v_misc.z), m_new = __uint_as_float(v_misc.w);
-        const uint32_t ue = half ? v_misc.y : v_misc.x;
-
-        // own partial row sum follows the reference
-        if (m_new != m_ref) l_sum *= reference_factor(m_ref, m_new, p.sl2);
-        m_ref = m_new;
-
-        // The two rare steps come BEFORE the scores are loaded, so that no large register array is
-        // live across their out-of-line calls.
-        // correction: O holds blocks 0..i-1 relative to m_prev; this warpgroup rescales its
-        // 64 columns of O
-        if (i > 0 && __any_sync(0xffffffffu, m_new != m_prev)) {
-          ok = __all_sync(0xffffffffu, mbar_wait(bars.at(Bars::kPvDone + ((G - 1) % kStagesV)),
-                                                 ((G - 1) / kStagesV) & 1, wc, kSitePvDone));
-          if (!ok) break;
-          tc_fence_after_sync();
-          const float f = (m_new != m_prev) ? reference_factor(m_prev, m_new, p.sl2) : 1.f;
-          rescale_accumulator(lane_addr + kTmO + 64 * half, f, 2);
-          tc_wait_st();
-        }
         const uint32_t s_addr = lane_addr + (b ? kTmS1 : kTmS0) + 64 * half;
-        // diagonal block: the statistics warps are done with S (st_ready), so this thread may
-        // overwrite the masked keys of its own half row in tensor memory before loading it
+        // diagonal block: this thread overwrites the masked keys of its own half row in tensor
+        // memory before loading it (out of line, nothing large is live yet).  The statistics
+        // warps may be reading the same row: they mask what they read themselves, and the visible
+        // keys are not changed.
         if (block_needs_mask(p, t, nb)) mask_scores_in_tmem(s_addr, causal_limit(p, t, row, nb) - 64 * half);
-
         float s[64];
         tmem_ld32(s_addr, reinterpret_cast<uint32_t*>(&s[0]));
         tmem_ld32(s_addr + 32, reinterpret_cast<uint32_t*>(&s[32]));
         tc_wait_ld();
         tc_fence_before_sync();
         mbar_arrive(bars.at(Bars::kSFree + b));
-        mbar_arrive(bars.at(Bars::kStFree + b));
 
-        // P buffer g is free once PV of block G-2 has completed
+        // 2. this row's exponents from the statistics warpgroup
+        ok = wait_probed(r_r, bar_r, par_r, wc, kSiteStReady);
+        if (!ok) break;
+        const uint4* st_row = reinterpret_cast<const uint4*>(&s_stats[b * 128 + row]);
+        const uint4 v_noff = st_row[half];
+        const uint4 v_misc = st_row[2];
+        mbar_arrive(bars.at(Bars::kStFree + b));
+        const float m_prev = __uint_as_float(v_misc.z), m_new = __uint_as_float(v_misc.w);
+        const uint32_t ue = half ? v_misc.y : v_misc.x;
+        // own partial row sum follows the reference
+        if (m_new != m_ref) l_sum *= reference_factor(m_ref, m_new, p.sl2);
+        m_ref = m_new;
+
+        // 3. exponentials and quantisation; P buffer b is free once PV of block G-2 has completed
         ok = wait_probed(r_p, bar_p, par_p, wc, kSitePvDone);
         if (!ok) break;
         FA4_TRACE_EV(6, G);
@@ -619,6 +613,19 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         // scales of this half: one 64-key MMA step = scale word `half`
         *reinterpret_cast<uint32_t*>(gbase + kOffSFP + b * kSfBytes + 512 * half + (row & 31) * 16 +
                                      (row >> 5) * 4) = block_scale_bytes(ue);
+
+        // 4. correction (rare, out of line, after the scores are consumed): O holds blocks
+        //    0..i-1 relative to m_prev and must move to m_new before PV of this block is issued,
+        //    i.e. before the arrival on p_full; this warpgroup rescales its 64 columns of O
+        if (i > 0 && __any_sync(0xffffffffu, m_new != m_prev)) {
+          ok = __all_sync(0xffffffffu, mbar_wait(bars.at(Bars::kPvDone + ((G - 1) % kStagesV)),
+                                                 ((G - 1) / kStagesV) & 1, wc, kSitePvDone));
+          if (!ok) break;
+          tc_fence_after_sync();
+          const float f = (m_new != m_prev) ? reference_factor(m_prev, m_new, p.sl2) : 1.f;
+          rescale_accumulator(lane_addr + kTmO + 64 * half, f, 2);
+          tc_wait_st();
+        }
         fence_proxy_async_smem();
         tc_fence_before_sync();  // orders the O rescale stores before the issuer's next MMA
         mbar_arrive(bars.at(Bars::kPFull + b));
@@ -637,6 +644,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         mbar_arrive(bars.at(Bars::kFin));
         ok = __all_sync(0xffffffffu, mbar_wait(bars.at(Bars::kFin), ti & 1, wc, kSiteFin));
         if (!ok) break;
+        FA4_TRACE_EV(40, gb);
         float lw[4], mw[4];
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
@@ -651,6 +659,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         ok = __all_sync(0xffffffffu,
                         mbar_wait(bars.at(Bars::kPvDone + (Gl % kStagesV)), (Gl / kStagesV) & 1, wc, kSiteFinalO));
         if (!ok) break;
+        FA4_TRACE_EV(41, gb);
         tc_fence_after_sync();
         scale = (l_tot > 0.f) ? p.out_scale / l_tot : 0.f;
       }
@@ -658,6 +667,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
       if (wg == 0 && p.lse != nullptr) {
         p.lse[((int64_t)t.b * p.Hq + t.h) * p.Sq + q_idx] = finish_lse(m_fin, l_tot, p.sl2);
       }
+      FA4_TRACE_EV(42, gb);
       gb += n;
       ti += (n > 0) ? 1u : 0u;
     }
