@@ -90,7 +90,8 @@ def lib() -> ctypes.CDLL:
             L.fa4_nvfp4_fwd.restype = ctypes.c_int
             L.fa4_nvfp4_sf_linear_to_tiled.argtypes = [
                 ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
-                ctypes.c_int32, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p]
+                ctypes.c_int32, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int32,
+                ctypes.c_void_p]
             L.fa4_nvfp4_sf_linear_to_tiled.restype = ctypes.c_int
             L.fa4_nvfp4_query.argtypes = [ctypes.c_int32]
             L.fa4_nvfp4_query.restype = ctypes.c_int

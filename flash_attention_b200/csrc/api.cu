@@ -74,8 +74,10 @@ extern "C" int fa4_nvfp4_fwd(const fa4_nvfp4_params* p, void* cuda_stream) {
   if (p->B <= 0 || p->Sq <= 0 || p->Sk <= 0 || p->Hq <= 0 || p->Hkv <= 0) return -FA4_E_SHAPE;
   if (p->Hq % p->Hkv != 0) return -FA4_E_SHAPE;
   if (p->D != 128 || p->Dv != 128) return -FA4_E_SHAPE;
-  if (p->Sq % kBlockM != 0 || p->Sk % kBlockN != 0) return -FA4_E_SHAPE;
-  if (p->Sq / kBlockM * (int64_t)p->Hq * p->B > 0x7fffffffLL) return -FA4_E_SHAPE;
+  // keys are blocked by 16 along Sk (V / P scales) and V rows are Sk/2 bytes with a 16-byte
+  // stride rule for TMA: Sk must be a multiple of 32; Sq is free
+  if (p->Sk % 32 != 0) return -FA4_E_SHAPE;
+  if ((int64_t)((p->Sq + kBlockM - 1) / kBlockM) * p->Hq * p->B > 0x7fffffffLL) return -FA4_E_SHAPE;
   if (!(p->softmax_scale > 0.f) || !(p->q_scale > 0.f) || !(p->k_scale > 0.f)) return -FA4_E_SHAPE;
   const void* ptrs[] = {p->q, p->k, p->v, p->q_sf, p->k_sf, p->v_sf, p->out};
   for (const void* q : ptrs)
@@ -117,15 +119,16 @@ extern "C" int fa4_nvfp4_fwd(const fa4_nvfp4_params* p, void* cuda_stream) {
   kp.o_stride_h = p->o_stride_h;
   kp.B = p->B; kp.Sq = p->Sq; kp.Sk = p->Sk; kp.Hq = p->Hq; kp.Hkv = p->Hkv;
   kp.group = p->Hq / p->Hkv;
-  kp.num_m_blocks = p->Sq / kBlockM;
-  kp.num_n_blocks = p->Sk / kBlockN;
+  kp.num_m_blocks = (p->Sq + kBlockM - 1) / kBlockM;
+  kp.num_n_blocks = (p->Sk + kBlockN - 1) / kBlockN;
   kp.causal = p->causal ? 1 : 0;
   // tiled scale factors: (B, H, row tiles, col tiles, 512)
   kp.qsf_stride_h = (int64_t)kp.num_m_blocks * (p->D / 64) * 512;
   kp.qsf_stride_b = kp.qsf_stride_h * p->Hq;
   kp.ksf_stride_h = (int64_t)kp.num_n_blocks * (p->D / 64) * 512;
   kp.ksf_stride_b = kp.ksf_stride_h * p->Hkv;
-  kp.vsf_stride_h = (int64_t)((p->Dv + 127) / 128) * (p->Sk / 64) * 512;
+  // V scales: two 64-key column tiles per 128-key block, the last block padded with zeros
+  kp.vsf_stride_h = (int64_t)((p->Dv + 127) / 128) * (2 * kp.num_n_blocks) * 512;
   kp.vsf_stride_b = kp.vsf_stride_h * p->Hkv;
   kp.sl2 = p->softmax_scale * p->q_scale * p->k_scale * 1.4426950408889634f;
   kp.out_scale = p->v_scale;
@@ -153,17 +156,20 @@ extern "C" int fa4_nvfp4_fwd(const fa4_nvfp4_params* p, void* cuda_stream) {
 extern "C" int fa4_nvfp4_sf_linear_to_tiled(const void* src, void* dst, int32_t n_outer,
                                             int32_t n_inner, int32_t rows, int32_t cols,
                                             int64_t stride_outer, int64_t stride_inner,
-                                            int64_t stride_row, void* cuda_stream) {
+                                            int64_t stride_row, int32_t col_tile_multiple,
+                                            void* cuda_stream) {
   if (!src || !dst) return -FA4_E_NULL;
-  if (n_outer <= 0 || n_inner <= 0 || rows <= 0 || cols <= 0) return -FA4_E_SHAPE;
+  if (n_outer <= 0 || n_inner <= 0 || rows <= 0 || cols <= 0 || col_tile_multiple <= 0)
+    return -FA4_E_SHAPE;
   if (!aligned16(dst)) return -FA4_E_ALIGN;
-  const int64_t total = (int64_t)n_outer * n_inner * ((rows + 127) / 128) * ((cols + 3) / 4) * 32;
+  const int64_t ct = ((cols + 3) / 4 + col_tile_multiple - 1) / col_tile_multiple * col_tile_multiple;
+  const int64_t total = (int64_t)n_outer * n_inner * ((rows + 127) / 128) * ct * 32;
   int64_t blocks = (total + 255) / 256;
   const int64_t cap = 148 * 16;  // grid-stride beyond a few waves
   if (blocks > cap) blocks = cap;
   sf_linear_to_tiled_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
       static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), n_outer, n_inner, rows, cols,
-      stride_outer, stride_inner, stride_row);
+      stride_outer, stride_inner, stride_row, col_tile_multiple);
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : (int)e;
 }
@@ -237,8 +243,9 @@ int scratch_address(uint8_t** out) {
   return 0;
 }
 
-inline int64_t tiled_sf_bytes(int64_t n_mats, int64_t rows, int64_t cols) {
-  return n_mats * ((rows + 127) / 128) * ((cols + 3) / 4) * 512;
+inline int64_t tiled_sf_bytes(int64_t n_mats, int64_t rows, int64_t cols, int64_t ct_multiple) {
+  const int64_t ct = ((cols + 3) / 4 + ct_multiple - 1) / ct_multiple * ct_multiple;
+  return n_mats * ((rows + 127) / 128) * ct * 512;
 }
 }  // namespace
 
@@ -249,9 +256,9 @@ extern "C" int fa4_nvfp4_fwd_linear_sf_noalloc(const fa4_nvfp4_params* p, void* 
   if (p->B <= 0 || p->Sq <= 0 || p->Sk <= 0 || p->Hq <= 0 || p->Hkv <= 0 || p->D <= 0 || p->Dv <= 0)
     return -FA4_E_SHAPE;
   if (p->D % 16 != 0 || p->Sk % 16 != 0) return -FA4_E_SHAPE;
-  const int64_t q_bytes = tiled_sf_bytes((int64_t)p->B * p->Hq, p->Sq, p->D / 16);
-  const int64_t k_bytes = tiled_sf_bytes((int64_t)p->B * p->Hkv, p->Sk, p->D / 16);
-  const int64_t v_bytes = tiled_sf_bytes((int64_t)p->B * p->Hkv, p->Dv, p->Sk / 16);
+  const int64_t q_bytes = tiled_sf_bytes((int64_t)p->B * p->Hq, p->Sq, p->D / 16, 1);
+  const int64_t k_bytes = tiled_sf_bytes((int64_t)p->B * p->Hkv, p->Sk, p->D / 16, 1);
+  const int64_t v_bytes = tiled_sf_bytes((int64_t)p->B * p->Hkv, p->Dv, p->Sk / 16, 2);
   if (q_bytes + k_bytes + v_bytes > (int64_t)FA4_STATIC_SCRATCH_BYTES) return -FA4_E_TOO_LARGE;
 
   uint8_t* scratch = nullptr;
@@ -263,16 +270,16 @@ extern "C" int fa4_nvfp4_fwd_linear_sf_noalloc(const fa4_nvfp4_params* p, void* 
   const int64_t cq = p->D / 16, cv = p->Sk / 16;
   // q_sf (B, Sq, Hq, D/16) and k_sf (B, Sk, Hkv, D/16): matrix (b, h) has row stride H * D/16
   if (int e = fa4_nvfp4_sf_linear_to_tiled(p->q_sf, q_t, p->B, p->Hq, p->Sq, (int)cq,
-                                           (int64_t)p->Sq * p->Hq * cq, cq, (int64_t)p->Hq * cq,
+                                           (int64_t)p->Sq * p->Hq * cq, cq, (int64_t)p->Hq * cq, 1,
                                            cuda_stream))
     return e;
   if (int e = fa4_nvfp4_sf_linear_to_tiled(p->k_sf, k_t, p->B, p->Hkv, p->Sk, (int)cq,
-                                           (int64_t)p->Sk * p->Hkv * cq, cq, (int64_t)p->Hkv * cq,
+                                           (int64_t)p->Sk * p->Hkv * cq, cq, (int64_t)p->Hkv * cq, 1,
                                            cuda_stream))
     return e;
   // v_sf (B, Hkv, Dv, Sk/16): matrix (b, h) is contiguous
   if (int e = fa4_nvfp4_sf_linear_to_tiled(p->v_sf, v_t, p->B, p->Hkv, p->Dv, (int)cv,
-                                           (int64_t)p->Hkv * p->Dv * cv, (int64_t)p->Dv * cv, cv,
+                                           (int64_t)p->Hkv * p->Dv * cv, (int64_t)p->Dv * cv, cv, 2,
                                            cuda_stream))
     return e;
   fa4_nvfp4_params tiled = *p;

@@ -60,13 +60,20 @@ __device__ __forceinline__ Tile decode_tile(const KernelParams& p, int tile_idx)
 }
 
 // In-block index of the last visible key for query row `row_in_tile` of tile t in K/V block
-// `nb`, or >= 127 when the block needs no mask for that row.
+// `nb` (>= 127 when the block needs no mask for that row).  Two limits combine: the causal one
+// (bottom-right aligned, flash_attn/cute/mask.py:369-527) and the key length (keys >= Sk of the
+// last, partial block are zero-filled by TMA and must not count; the reference masks them on the
+// first-processed block only, flash_fwd_sm100.py:1997-2004).
 __device__ __forceinline__ int causal_limit(const KernelParams& p, const Tile& t, int row_in_tile,
                                             int nb) {
-  return t.m_blk * kBlockM + row_in_tile + p.Sk - p.Sq - nb * kBlockN;
+  const int len_limit = p.Sk - 1 - nb * kBlockN;
+  if (!p.causal) return len_limit;
+  const int c = t.m_blk * kBlockM + row_in_tile + p.Sk - p.Sq - nb * kBlockN;
+  return c < len_limit ? c : len_limit;
 }
 __device__ __forceinline__ bool block_needs_mask(const KernelParams& p, const Tile& t, int nb) {
-  return p.causal && (nb * kBlockN + kBlockN - 1 > t.m_blk * kBlockM + p.Sk - p.Sq);
+  const bool partial = (nb + 1) * kBlockN > p.Sk;
+  return partial || (p.causal && (nb * kBlockN + kBlockN - 1 > t.m_blk * kBlockM + p.Sk - p.Sq));
 }
 
 // Final scaling and bf16 store of 32 consecutive output columns of one row.

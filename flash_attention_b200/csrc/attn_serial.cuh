@@ -204,6 +204,7 @@ attn_fwd_serial_kernel(const __grid_constant__ CUtensorMap tm_q,
   // ---- epilogue ---------------------------------------------------------------------------------
   if (ok) {
     const int q_idx = t.m_blk * kBlockM + row;
+    const bool row_valid = q_idx < p.Sq;  // rows of a partial last tile are not stored
     __nv_bfloat16* orow = p.out + t.b * p.o_stride_b + (int64_t)q_idx * p.o_stride_s + t.h * p.o_stride_h;
     const bool empty = (t.n_blocks == 0) || !(l_sum > 0.f);
     const float scale = empty ? 0.f : p.out_scale / l_sum;
@@ -218,9 +219,9 @@ attn_fwd_serial_kernel(const __grid_constant__ CUtensorMap tm_q,
 #pragma unroll
         for (int x = 0; x < 32; ++x) o[x] = 0u;
       }
-      store_out_32(orow + 32 * c, o, scale);
+      if (row_valid) store_out_32(orow + 32 * c, o, scale);
     }
-    if (p.lse != nullptr) {
+    if (p.lse != nullptr && row_valid) {
       p.lse[((int64_t)t.b * p.Hq + t.h) * p.Sq + q_idx] = finish_lse(m_ref, l_sum, p.sl2);
     }
   } else if (tid == 0 && !poisoned) {

@@ -97,10 +97,14 @@ constexpr int kStatsWarp0 = 16;
 constexpr int kProducerWarp = 20;
 constexpr int kIssuerWarp = 21;    // QK^T issuer, owns tensor memory
 constexpr int kPvIssuerWarp = 22;
-// registers per thread after setmaxnreg: 512 * 96 + 128 * 56 + 128 * 40 = 61440 = 768 * 80
-constexpr int kRegsSoftmax = 96;
-constexpr int kRegsStats = 56;
+// registers per thread after setmaxnreg: 512 * 88 + 128 * 88 + 128 * 40 = 61440 = 768 * 80
+constexpr int kRegsSoftmax = 88;
+constexpr int kRegsStats = 88;
 constexpr int kRegsOther = 40;
+constexpr int kRegsLaunch = 80;
+static_assert(512 * kRegsSoftmax + 128 * kRegsStats + 128 * kRegsOther <= kThreads * kRegsLaunch,
+              "setmaxnreg targets exceed the CTA's register allocation");
+static_assert(kRegsSoftmax > kRegsLaunch && kRegsOther < kRegsLaunch, "inc / dec directions");
 
 // per-row record the statistics warpgroup publishes for one block
 struct alignas(16) RowStats {
@@ -201,7 +205,7 @@ __device__ __noinline__ void store_accumulator_chunk(uint32_t taddr, __nv_bfloat
 #pragma unroll
     for (int x = 0; x < 32; ++x) o[x] = 0u;
   }
-  store_out_32(dst, o, scale);
+  if (dst != nullptr) store_out_32(dst, o, scale);  // null: a row beyond Sq of a partial tile
 }
 
 // Tile visited by CTA `cta` in round `it`: rounds alternate direction so that, with tiles sorted
@@ -459,7 +463,13 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
     }
   } else if (warp >= kStatsWarp0) {
     // =========================================== statistics warpgroup ===========================
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsStats));
+    // 768 threads launch with 80 registers each (65536 / 768 rounded down to a multiple of 8):
+    // a warpgroup that ends up above that must use .inc, below .dec
+    if constexpr (kRegsStats > kRegsLaunch) {
+      asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsStats));
+    } else if constexpr (kRegsStats < kRegsLaunch) {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsStats));
+    }
     const int row = tid & 127;
     const uint32_t lane_addr = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     FA4_FOR_EACH_TILE {
@@ -476,8 +486,8 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         const int nb = n - 1 - i;
         const uint32_t bar_s = bars.at(Bars::kSFull + (G % kStagesK)), par_s = (G / kStagesK) & 1;
         const uint32_t bar_f = bars.at(Bars::kStFree + b), par_f = ((G - 2) >> 1) & 1;
-        const bool r_s = mbar_try_wait(bar_s, par_s);
-        const bool r_f = (G >= 2) ? mbar_try_wait(bar_f, par_f) : true;
+        const bool r_s = mbar_test(bar_s, par_s);
+        const bool r_f = (G >= 2) ? mbar_test(bar_f, par_f) : true;
         ok = wait_probed(r_s, bar_s, par_s, wc, kSiteSFull);
         if (!ok) break;
         FA4_TRACE_EV(30, G);
@@ -486,16 +496,17 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         const int limit = causal_limit(p, t, row, nb);
         float bm[8];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          float s[32];
-          tmem_ld32(lane_addr + (b ? kTmS1 : kTmS0) + 32 * c, reinterpret_cast<uint32_t*>(&s[0]));
+        for (int h = 0; h < 2; ++h) {
+          float s[64];
+          tmem_ld32(lane_addr + (b ? kTmS1 : kTmS0) + 64 * h, reinterpret_cast<uint32_t*>(&s[0]));
+          tmem_ld32(lane_addr + (b ? kTmS1 : kTmS0) + 64 * h + 32, reinterpret_cast<uint32_t*>(&s[32]));
           tc_wait_ld();
           if (masked) {
 #pragma unroll
-            for (int x = 0; x < 32; ++x) s[x] = (32 * c + x <= limit) ? s[x] : kNegInf;
+            for (int x = 0; x < 64; ++x) s[x] = (64 * h + x <= limit) ? s[x] : kNegInf;
           }
 #pragma unroll
-          for (int q = 0; q < 2; ++q) {
+          for (int q = 0; q < 4; ++q) {
             float m0 = fmax3(s[16 * q], s[16 * q + 1], s[16 * q + 2]);
             float m1 = fmax3(s[16 * q + 3], s[16 * q + 4], s[16 * q + 5]);
             m0 = fmax3(m0, s[16 * q + 6], s[16 * q + 7]);
@@ -503,7 +514,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
             m0 = fmax3(m0, s[16 * q + 10], s[16 * q + 11]);
             m1 = fmax3(m1, s[16 * q + 12], s[16 * q + 13]);
             m0 = fmax3(m0, s[16 * q + 14], s[16 * q + 15]);
-            bm[2 * c + q] = fmaxf(m0, m1);
+            bm[4 * h + q] = fmaxf(m0, m1);
           }
         }
         tc_fence_before_sync();
@@ -537,7 +548,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
     const int wg = warp >> 2;          // 0..3
     const int half = wg & 1;           // key columns [64 half, 64 half + 64) of a block
-    const int g = wg >> 1;             // takes the blocks of a tile with (index in tile) % 2 == g
+    const uint32_t g = wg >> 1;        // takes the blocks with running index G % 2 == g
     const int row = (warp & 3) * 32 + lane;  // tile row == tensor-memory lane
     const uint32_t lane_addr = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
 
@@ -552,8 +563,8 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
       }
       float m_ref = kNegInf, l_sum = 0.f;
 
-      for (int i = g; i < n; i += 2) {
-        const uint32_t G = gb + i, b = G & 1;  // b: S / P / stats buffer of this block
+      for (int i = (g - gb) & 1; i < n; i += 2) {
+        const uint32_t G = gb + i, b = G & 1;  // b == g: S / P / stats buffer of this block
         const int nb = n - 1 - i;
         FA4_TRACE_EV(1, G);
         // Probe the three barriers this block depends on back to back so that their latencies
@@ -561,9 +572,8 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         const uint32_t bar_s = bars.at(Bars::kSFull + (G % kStagesK)), par_s = (G / kStagesK) & 1;
         const uint32_t bar_r = bars.at(Bars::kStReady + b), par_r = (G >> 1) & 1;
         const uint32_t bar_p = bars.at(Bars::kPvDone + ((G - 2) % kStagesV)), par_p = ((G - 2) / kStagesV) & 1;
-        const bool r_s = mbar_try_wait(bar_s, par_s);
-        const bool r_r = mbar_try_wait(bar_r, par_r);
-        const bool r_p = (G >= 2) ? mbar_try_wait(bar_p, par_p) : true;
+        const bool r_s = mbar_test(bar_s, par_s);
+        const bool r_p = (G >= 2) ? mbar_test(bar_p, par_p) : true;
 
         // 1. scores: copied to registers as soon as the MMA has written them, so that the S buffer
         //    goes back to the QK^T issuer without waiting for the statistics (the buffer's cycle
@@ -585,7 +595,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         mbar_arrive(bars.at(Bars::kSFree + b));
 
         // 2. this row's exponents from the statistics warpgroup
-        ok = wait_probed(r_r, bar_r, par_r, wc, kSiteStReady);
+        ok = wait_probed(mbar_test(bar_r, par_r), bar_r, par_r, wc, kSiteStReady);
         if (!ok) break;
         const uint4* st_row = reinterpret_cast<const uint4*>(&s_stats[b * 128 + row]);
         const uint4 v_noff = st_row[half];
@@ -639,8 +649,11 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
       float scale = 0.f, m_fin = kNegInf, l_tot = 0.f;
       if (n > 0) {
         volatile float* fin_slot = s_fin + (ti & 1) * (4 * 128 * 2);
-        fin_slot[(wg * 128 + row) * 2] = l_sum;
-        fin_slot[(wg * 128 + row) * 2 + 1] = m_ref;
+        // slot order = (parity of the block index inside the tile, half): the summation order of
+        // a row then depends on its tile only, not on what the CTA processed before
+        const uint32_t slot = (((g ^ gb) & 1u) << 1) | (uint32_t)half;
+        fin_slot[(slot * 128 + row) * 2] = l_sum;
+        fin_slot[(slot * 128 + row) * 2 + 1] = m_ref;
         mbar_arrive(bars.at(Bars::kFin));
         ok = __all_sync(0xffffffffu, mbar_wait(bars.at(Bars::kFin), ti & 1, wc, kSiteFin));
         if (!ok) break;
@@ -663,8 +676,9 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         tc_fence_after_sync();
         scale = (l_tot > 0.f) ? p.out_scale / l_tot : 0.f;
       }
-      store_accumulator_chunk(lane_addr + kTmO + 32 * wg, orow, scale, n > 0 ? bars.at(Bars::kOFree) : 0u);
-      if (wg == 0 && p.lse != nullptr) {
+      store_accumulator_chunk(lane_addr + kTmO + 32 * wg, q_idx < p.Sq ? orow : nullptr, scale,
+                              n > 0 ? bars.at(Bars::kOFree) : 0u);
+      if (wg == 0 && p.lse != nullptr && q_idx < p.Sq) {
         p.lse[((int64_t)t.b * p.Hq + t.h) * p.Sq + q_idx] = finish_lse(m_fin, l_tot, p.sl2);
       }
       FA4_TRACE_EV(42, gb);

@@ -15,9 +15,9 @@ namespace fa4 {
 __global__ void sf_linear_to_tiled_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
                                           int n_outer, int n_inner, int rows, int cols,
                                           int64_t stride_outer, int64_t stride_inner,
-                                          int64_t stride_row) {
+                                          int64_t stride_row, int col_tile_multiple) {
   const int row_tiles = (rows + 127) / 128;
-  const int col_tiles = (cols + 3) / 4;
+  const int col_tiles = ((cols + 3) / 4 + col_tile_multiple - 1) / col_tile_multiple * col_tile_multiple;
   const int64_t total = (int64_t)n_outer * n_inner * row_tiles * col_tiles * 32;
   for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (int64_t)gridDim.x * blockDim.x) {

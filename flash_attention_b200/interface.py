@@ -98,10 +98,11 @@ def flash_attn_fp4_func(
 
     q (B,Sq,Hq,D/2), k (B,Sk,Hkv,D/2), v (B,Hkv,Dv,Sk/2): packed e2m1 bytes (V key-contiguous).
     *_sf: e4m3 block scales, ``sf_layout="linear"``: (B,S,H,D/16) / (B,Hkv,Dv,Sk/16), converted
-    to the tiled layout by a small kernel; ``"tiled"``: already (B,H,ceil(rows/128),cols/4,512).
+    to the tiled layout by a small kernel; ``"tiled"``: already (B,H,ceil(rows/128),column tiles,512), see ``sf_to_tiled``.
     *_scale: fp32 per-tensor scales.  Returns ``(out bf16 (B,Sq,Hq,Dv), lse fp32 (B,Hq,Sq) | None)``.
 
-    Built so far: D = Dv = 128; Sq and Sk multiples of 128.  Anything else raises
+    Built so far: D = Dv = 128; any Sq; Sk a multiple of 32 (partial last tiles are handled by
+    zero-filled loads, a key-length mask and unstored rows).  Anything else raises
     ``NotImplementedError`` before a launch.
     """
     q, k, v = _as_u8(q, "q"), _as_u8(k, "k"), _as_u8(v, "v")
@@ -119,8 +120,8 @@ def flash_attn_fp4_func(
     assert Hq % Hkv == 0, "num_head must be divisible by num_head_kv"
     if D != 128 or Dv != 128:
         raise NotImplementedError(f"head dims (D={D}, Dv={Dv}) not built; supported: (128, 128)")
-    if Sq % 128 != 0 or Sk % 128 != 0:
-        raise NotImplementedError("seqlen_q and seqlen_k must be multiples of 128")
+    if Sk % 32 != 0:
+        raise NotImplementedError("seqlen_k must be a multiple of 32 (16-key scale blocks, 16-byte rows of V)")
     device = q.device
     if softmax_scale is None:
         softmax_scale = 1.0 / math.sqrt(D)
@@ -129,11 +130,11 @@ def flash_attn_fp4_func(
         _validate_tensor(k_sf, "k_sf", (B, Sk, Hkv, D // 16), torch.uint8, device)
         _validate_tensor(v_sf, "v_sf", (B, Hkv, Dv, Sk // 16), torch.uint8, device)
         q_sf, k_sf, v_sf = (t if t.stride(-1) == 1 else t.contiguous() for t in (q_sf, k_sf, v_sf))
-        q_sf, k_sf, v_sf = sf_to_tiled(q_sf, 1, 2), sf_to_tiled(k_sf, 1, 2), sf_to_tiled(v_sf, 2, 1)
+        q_sf, k_sf, v_sf = sf_to_tiled(q_sf, 1, 2), sf_to_tiled(k_sf, 1, 2), sf_to_tiled(v_sf, 2, 1, 2)
     elif sf_layout == "tiled":
-        _validate_tensor(q_sf, "q_sf", (B, Hq, Sq // 128, D // 64, 512), torch.uint8, device)
-        _validate_tensor(k_sf, "k_sf", (B, Hkv, Sk // 128, D // 64, 512), torch.uint8, device)
-        _validate_tensor(v_sf, "v_sf", (B, Hkv, Dv // 128, Sk // 64, 512), torch.uint8, device)
+        _validate_tensor(q_sf, "q_sf", (B, Hq, (Sq + 127) // 128, D // 64, 512), torch.uint8, device)
+        _validate_tensor(k_sf, "k_sf", (B, Hkv, (Sk + 127) // 128, D // 64, 512), torch.uint8, device)
+        _validate_tensor(v_sf, "v_sf", (B, Hkv, Dv // 128, 2 * ((Sk + 127) // 128), 512), torch.uint8, device)
         assert q_sf.is_contiguous() and k_sf.is_contiguous() and v_sf.is_contiguous()
     else:
         raise ValueError(f"sf_layout must be 'linear' or 'tiled', got {sf_layout!r}")

@@ -65,24 +65,28 @@ def dequantize_lastdim(packed: torch.Tensor, sf: torch.Tensor, scale: float) -> 
     return vb.reshape(vals.shape)
 
 
-def sf_to_tiled(sf: torch.Tensor, rows_dim: int, head_dim: Optional[int]) -> torch.Tensor:
+def sf_to_tiled(sf: torch.Tensor, rows_dim: int, head_dim: Optional[int],
+                col_tile_multiple: int = 1) -> torch.Tensor:
     """Linear block scales -> the tiled layout the kernel reads (see include/fa4_nvfp4.h).
 
     ``sf`` is (B, S, H, C) with ``rows_dim=1, head_dim=2`` (Q, K) or (B, H, R, C) with
-    ``rows_dim=2, head_dim=1`` (V).  Returns uint8 (B, H, ceil(rows/128), ceil(C/4), 512).
+    ``rows_dim=2, head_dim=1`` (V, which also needs ``col_tile_multiple=2``: a 128-key block is two
+    64-key column tiles).  Returns uint8 (B, H, ceil(rows/128), CT, 512) with CT = ceil(C/4)
+    rounded up to a multiple of ``col_tile_multiple``.
     Runs the library's conversion kernel on CUDA tensors; the result is scratch the attention
     call reads.
     """
     assert sf.dim() == 4 and sf.dtype == torch.uint8 and sf.stride(-1) == 1
     B = sf.shape[0]
     H, R, C = sf.shape[head_dim], sf.shape[rows_dim], sf.shape[3]
-    out = torch.empty(B, H, (R + 127) // 128, (C + 3) // 4, 512, dtype=torch.uint8, device=sf.device)
+    ct = ((C + 3) // 4 + col_tile_multiple - 1) // col_tile_multiple * col_tile_multiple
+    out = torch.empty(B, H, (R + 127) // 128, ct, 512, dtype=torch.uint8, device=sf.device)
     if not sf.is_cuda:
         raise RuntimeError("sf_to_tiled needs CUDA tensors (the conversion is a CUDA kernel)")
     stream = torch.cuda.current_stream(sf.device).cuda_stream
     rc = _lib.lib().fa4_nvfp4_sf_linear_to_tiled(
         sf.data_ptr(), out.data_ptr(), B, H, R, C, sf.stride(0), sf.stride(head_dim),
-        sf.stride(rows_dim), stream)
+        sf.stride(rows_dim), col_tile_multiple, stream)
     _lib.check(rc, "fa4_nvfp4_sf_linear_to_tiled")
     return out
 
@@ -105,7 +109,7 @@ class NVFP4Tensor:
     def tiled_sf(self) -> torch.Tensor:
         if self.tiled:
             return self.sf
-        return sf_to_tiled(self.sf, 2, 1) if self.is_v else sf_to_tiled(self.sf, 1, 2)
+        return sf_to_tiled(self.sf, 2, 1, 2) if self.is_v else sf_to_tiled(self.sf, 1, 2)
 
     def dequantize(self) -> torch.Tensor:
         """fp32 values in the reference layout (B, S, H, D) (linear scale factors only)."""

@@ -83,7 +83,7 @@ typedef struct fa4_nvfp4_params {
   const void* v;
   const void* q_sf;       /* e4m3, tiled: (B, Hq,  ceil(Sq/128), D/64,  512) bytes */
   const void* k_sf;       /* e4m3, tiled: (B, Hkv, ceil(Sk/128), D/64,  512) bytes */
-  const void* v_sf;       /* e4m3, tiled: (B, Hkv, ceil(Dv/128), Sk/64, 512) bytes */
+  const void* v_sf;       /* e4m3, tiled: (B, Hkv, ceil(Dv/128), 2*ceil(Sk/128), 512) bytes */
   void* out;              /* bf16 (B, Sq, Hq, Dv) */
   float* lse;             /* fp32 (B, Hq, Sq) or NULL */
   uint32_t* status;       /* one device word, zeroed by the caller; NULL = not reported */
@@ -114,7 +114,9 @@ int fa4_nvfp4_fwd(const fa4_nvfp4_params* p, void* cuda_stream);
  *        src + m_outer*stride_outer + m_inner*stride_inner + r*stride_row + c
  *        (n_outer x n_inner matrices; for q_sf given as (B, S, H, D/16):
  *        outer = batch, inner = head, stride_row = H*D/16)
- *   dst: (n_outer, n_inner, ceil(rows/128), ceil(cols/4), 512) bytes; inside a
+ *   dst: (n_outer, n_inner, ceil(rows/128), CT, 512) bytes, CT = ceil(cols/4) rounded up to a
+ *        multiple of col_tile_multiple (1 for q_sf / k_sf; 2 for v_sf, whose 128-key blocks
+ *        are read as two 64-key column tiles even when the last block is partial); inside a
  *        512-byte tile the scale of row r, column c sits at
  *        (r % 32) * 16 + (r / 32) * 4 + c   -- the 32x4x4 chunk that one
  *        `tcgen05.cp 32x128b.warpx4` moves to tensor memory.  Padding rows and
@@ -127,7 +129,8 @@ int fa4_nvfp4_sf_linear_to_tiled(const void* src, void* dst,
                                  int32_t n_outer, int32_t n_inner,
                                  int32_t rows, int32_t cols,
                                  int64_t stride_outer, int64_t stride_inner,
-                                 int64_t stride_row, void* cuda_stream);
+                                 int64_t stride_row, int32_t col_tile_multiple,
+                                 void* cuda_stream);
 
 /*
  * Version / capability query (host only, never touches a GPU).
@@ -171,7 +174,7 @@ int fa4_nvfp4_debug_wait_expiry(uint32_t* status, uint64_t budget_ns, void* cuda
  *
  * Limits and rules:
  *  - the three tiled scale-factor tensors together must fit: sum over q, k, v of
- *    matrices * ceil(rows/128) * ceil(cols/4) * 512 bytes <= 16 MiB, else -FA4_E_TOO_LARGE
+ *    matrices * ceil(rows/128) * column tiles * 512 bytes <= 16 MiB, else -FA4_E_TOO_LARGE
  *    (B=4, Hq=32, Hkv=8, S=8192, D=128 needs 12 MiB);
  *  - the first call on a device looks the array's device address up (cudaGetSymbolAddress, with
  *    that device current); make that first call outside any stream capture;

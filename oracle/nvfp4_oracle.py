@@ -126,11 +126,13 @@ def dequantize_nvfp4(q: NVFP4) -> np.ndarray:
     return (vb * (sf * np.float32(q.scale))[..., None]).reshape(vals.shape).astype(np.float32)
 
 
-def sf_linear_to_tiled(sf: np.ndarray) -> np.ndarray:
-    """(..., rows, cols) bytes -> (..., ceil(rows/128), ceil(cols/4), 512) bytes; inside a tile the
-    scale of (r, c) sits at (r % 32) * 16 + (r // 32) * 4 + c.  Zero padding."""
+def sf_linear_to_tiled(sf: np.ndarray, col_tile_multiple: int = 1) -> np.ndarray:
+    """(..., rows, cols) bytes -> (..., ceil(rows/128), CT, 512) bytes, CT = ceil(cols/4) rounded up
+    to a multiple of col_tile_multiple; inside a tile the scale of (r, c) sits at
+    (r % 32) * 16 + (r // 32) * 4 + c.  Zero padding."""
     rows, cols = sf.shape[-2:]
-    rt, ct = (rows + 127) // 128, (cols + 3) // 4
+    rt = (rows + 127) // 128
+    ct = ((cols + 3) // 4 + col_tile_multiple - 1) // col_tile_multiple * col_tile_multiple
     pad = np.zeros(sf.shape[:-2] + (rt * 128, ct * 4), dtype=np.uint8)
     pad[..., :rows, :cols] = sf
     t = pad.reshape(sf.shape[:-2] + (rt, 4, 32, ct, 4))        # (rt, r//32, r%32, ct, c)
@@ -204,38 +206,42 @@ def attention_oracle_b(qd, kd, vd, sl2: float, v_scale_out: float = 1.0, causal=
         for h in range(Hq):
             hk = h // g
             for m0 in range(0, Sq, 128):
-                rows = slice(m0, m0 + 128)
-                s_all = (qd[b, rows, h] @ kd[b, :, hk].T)                 # raw scores (128, Sk)
-                n_blocks = Sk // 128
+                rows = slice(m0, min(m0 + 128, Sq))
+                nr = rows.stop - rows.start
+                n_blocks = (Sk + 127) // 128
+                s_all = torch.full((nr, n_blocks * 128), float("-inf"))   # keys >= Sk never count
+                s_all[:, :Sk] = (qd[b, rows, h] @ kd[b, :, hk].T)         # raw scores
+                v_pad = torch.zeros(n_blocks * 128, Dv)
+                v_pad[:Sk] = vd[b, :, hk]
                 if causal:
                     last = m0 + 128 + Sk - Sq
                     n_blocks = min(n_blocks, max(0, (last + 127) // 128))
-                    s_all = s_all.masked_fill(_causal_mask(Sq, Sk)[rows], float("-inf"))
-                m_ref = torch.full((128,), float("-inf"))
-                l_sum = torch.zeros(128)
-                acc = torch.zeros(128, Dv)
+                    s_all[:, :Sk] = s_all[:, :Sk].masked_fill(_causal_mask(Sq, Sk)[rows], float("-inf"))
+                m_ref = torch.full((nr,), float("-inf"))
+                l_sum = torch.zeros(nr)
+                acc = torch.zeros(nr, Dv)
                 for nb in range(n_blocks - 1, -1, -1):
                     s = s_all[:, nb * 128:(nb + 1) * 128]
                     m_loc = s.amax(dim=-1)
                     keep = torch.isfinite(m_ref) & ((m_loc - m_ref) * sl2 <= P_LAZY)
                     m_new = torch.where(keep, m_ref, torch.maximum(m_ref, m_loc))
                     f = torch.where(torch.isfinite(m_ref), torch.exp2((m_ref - m_new) * sl2),
-                                    torch.zeros(128))
+                                    torch.zeros(nr))
                     f = torch.nan_to_num(f, nan=0.0)
                     acc = acc * f[:, None]
                     l_sum = l_sum * f
                     m_ref = m_new
-                    msc = torch.where(torch.isfinite(m_ref), m_ref * sl2, torch.zeros(128))
+                    msc = torch.where(torch.isfinite(m_ref), m_ref * sl2, torch.zeros(nr))
                     p_hat, p_sum = quantize_p_block_model(s * sl2, msc[:, None])
-                    acc = acc + p_hat @ vd[b, nb * 128:(nb + 1) * 128, hk]
+                    acc = acc + p_hat @ v_pad[nb * 128:(nb + 1) * 128]
                     l_sum = l_sum + p_sum
                 ok = l_sum > 0
-                safe = torch.where(ok, l_sum, torch.ones(128))
+                safe = torch.where(ok, l_sum, torch.ones(nr))
                 out[b, rows, h] = torch.where(ok[:, None], acc * (v_scale_out / safe)[:, None],
-                                              torch.zeros(128, Dv))
+                                              torch.zeros(nr, Dv))
                 lse[b, h, rows] = torch.where(
                     ok, (m_ref * sl2 + torch.log2(safe) - P_SHIFT) * math.log(2.0),
-                    torch.full((128,), float("-inf")))
+                    torch.full((nr,), float("-inf")))
     return out, lse
 
 

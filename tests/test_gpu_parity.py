@@ -68,11 +68,12 @@ def test_bounded_wait_gives_up_and_reports(cuda_device):
 
 def test_sf_linear_to_tiled_bit_exact(cuda_device):
     rng = np.random.default_rng(3)
-    for shape, rows_dim, head_dim in [((2, 300, 3, 8), 1, 2), ((1, 2, 128, 40), 2, 1), ((1, 5, 1, 3), 1, 2)]:
+    for shape, rows_dim, head_dim, mult in [((2, 300, 3, 8), 1, 2, 1), ((1, 2, 128, 40), 2, 1, 1),
+                                            ((1, 5, 1, 3), 1, 2, 1), ((1, 2, 128, 10), 2, 1, 2)]:
         sf = rng.integers(0, 255, size=shape, dtype=np.uint8)
-        got = fa.sf_to_tiled(torch.from_numpy(sf).to(cuda_device), rows_dim, head_dim).cpu().numpy()
+        got = fa.sf_to_tiled(torch.from_numpy(sf).to(cuda_device), rows_dim, head_dim, mult).cpu().numpy()
         lin = sf if rows_dim == 2 else np.transpose(sf, (0, 2, 1, 3))
-        assert np.array_equal(got, orc.sf_linear_to_tiled(lin))
+        assert np.array_equal(got, orc.sf_linear_to_tiled(lin, mult))
     # strided (non-contiguous) source
     big = torch.from_numpy(rng.integers(0, 255, size=(2, 256, 6, 8), dtype=np.uint8)).to(cuda_device)
     view = big[:, :, 2:4]
@@ -87,6 +88,12 @@ CASES = [
     ("causal_sq_gt_sk_masked_rows", 1, 384, 128, 2, 2, True, 1.0, 0.0),
     ("noncausal_sq_ne_sk_batch", 2, 128, 512, 2, 2, False, 1.0, 0.0),
     ("mqa_outlier_channels", 1, 256, 256, 8, 1, True, 1.0, 0.01),
+    # partial last tiles: Sq free, Sk a multiple of 32 (the reference's ragged shapes,
+    # tests/cute/test_flash_attn.py:91-119, restricted to what 16-key scale blocks allow)
+    ("ragged_noncausal", 2, 113, 224, 3, 1, False, 1.0, 0.0),
+    ("ragged_causal_sq_lt_sk", 1, 200, 352, 4, 2, True, 1.0, 0.0),
+    ("ragged_causal_sq_gt_sk", 1, 300, 160, 2, 2, True, 1.0, 0.0),
+    ("single_query_row", 1, 1, 160, 2, 1, True, 1.0, 0.0),
 ]
 
 
@@ -131,8 +138,9 @@ def test_softmax_scale_and_preallocated_outputs(cuda_device):
     with pytest.raises(AssertionError):
         fa.flash_attn_fp4_func(Q.data, K.data, V.data, Q.sf, K.sf, V.sf, 1.0, 1.0, 1.0,
                                out=torch.empty(1, 128, 2, 64, dtype=torch.bfloat16, device=cuda_device))
-    with pytest.raises(NotImplementedError):
-        fa.flash_attn_fp4_func(Q.data[:, :100], K.data, V.data, Q.sf[:, :100], K.sf, V.sf, 1.0, 1.0, 1.0)
+    with pytest.raises(NotImplementedError):   # Sk = 144 is not a multiple of 32
+        fa.flash_attn_fp4_func(Q.data, K.data[:, :144], V.data[..., :72].contiguous(), Q.sf, K.sf[:, :144],
+                               V.sf[..., :9].contiguous(), 1.0, 1.0, 1.0)
 
 
 def test_strided_views_and_tiled_scales(cuda_device):

@@ -82,7 +82,7 @@ def _good_params():
     (lambda p: setattr(p, "out", None), 1),
     (lambda p: (setattr(p, "Hq", 3), setattr(p, "Hkv", 2)), 2),   # Hq not a multiple of Hkv
     (lambda p: setattr(p, "D", 96), 2),
-    (lambda p: setattr(p, "Sq", 100), 2),
+    (lambda p: setattr(p, "Sk", 144), 2),       # Sk must be a multiple of 32
     (lambda p: setattr(p, "Sk", 0), 2),
     (lambda p: setattr(p, "softmax_scale", 0.0), 2),
     (lambda p: setattr(p, "k", 0x1008), 4),
@@ -100,9 +100,10 @@ def test_fwd_rejects_bad_arguments_on_host(mutate, code):
 
 def test_aux_entry_points_reject_bad_arguments():
     L = fa.lib()
-    assert L.fa4_nvfp4_sf_linear_to_tiled(None, 0x1000, 1, 1, 1, 1, 1, 1, 1, None) == -1
-    assert L.fa4_nvfp4_sf_linear_to_tiled(0x1000, 0x1000, 1, 1, 0, 1, 1, 1, 1, None) == -2
-    assert L.fa4_nvfp4_sf_linear_to_tiled(0x1000, 0x1004, 1, 1, 1, 1, 1, 1, 1, None) == -4
+    assert L.fa4_nvfp4_sf_linear_to_tiled(None, 0x1000, 1, 1, 1, 1, 1, 1, 1, 1, None) == -1
+    assert L.fa4_nvfp4_sf_linear_to_tiled(0x1000, 0x1000, 1, 1, 0, 1, 1, 1, 1, 1, None) == -2
+    assert L.fa4_nvfp4_sf_linear_to_tiled(0x1000, 0x1000, 1, 1, 1, 1, 1, 1, 1, 0, None) == -2
+    assert L.fa4_nvfp4_sf_linear_to_tiled(0x1000, 0x1004, 1, 1, 1, 1, 1, 1, 1, 1, None) == -4
     assert L.fa4_nvfp4_debug_qk_tile(0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 64, 0, None, None) == -2
     assert L.fa4_nvfp4_debug_wait_expiry(None, 1000, None) == -1
     assert L.fa4_nvfp4_debug_wait_expiry(0x1000, 0, None) == -2
