@@ -54,7 +54,9 @@
 //   s_free[2]            stats + softmax -> QK issuer: S buffer read by all (384 arrivals)
 //   st_ready[2]          stats -> softmax        exponents of block G published (128 arrivals)
 //   st_free[2]           softmax -> stats        exponents slot consumed (256 arrivals)
-//   p_full[2]            softmax -> PV issuer    P block + its scales in shared memory (256)
+//   p_full[stage]        softmax -> PV issuer    P block + its scales in shared memory (256);
+//                                                one barrier per P tile so that the softmax can
+//                                                never be two phases ahead of the issuer
 //   pv_done[stage]       PV issuer -> softmax, producer: PV of block G complete: P buffer and V
 //                                                stage free, O stable (tcgen05.commit)
 //   fin                  softmax warpgroups      partial row sums published (512, once per tile)
@@ -92,14 +94,15 @@ namespace ws {
 
 constexpr int kStagesK = 4;
 constexpr int kStagesV = 4;
+constexpr int kStagesP = 4;   // P tiles in shared memory (a block's P is rewritten once PV of block G-4 is done)
 constexpr int kThreads = 768;
 constexpr int kStatsWarp0 = 16;
 constexpr int kProducerWarp = 20;
 constexpr int kIssuerWarp = 21;    // QK^T issuer, owns tensor memory
 constexpr int kPvIssuerWarp = 22;
-// registers per thread after setmaxnreg: 512 * 88 + 128 * 88 + 128 * 40 = 61440 = 768 * 80
-constexpr int kRegsSoftmax = 88;
-constexpr int kRegsStats = 88;
+// registers per thread after setmaxnreg: 512 * 96 + 128 * 56 + 128 * 40 = 61440 = 768 * 80
+constexpr int kRegsSoftmax = 96;
+constexpr int kRegsStats = 56;
 constexpr int kRegsOther = 40;
 constexpr int kRegsLaunch = 80;
 static_assert(512 * kRegsSoftmax + 128 * kRegsStats + 128 * kRegsOther <= kThreads * kRegsLaunch,
@@ -119,15 +122,15 @@ static_assert(sizeof(RowStats) == 48, "RowStats is read with 16-byte loads");
 constexpr uint32_t kOffQ = 0;                                  // 2 x 8 KB
 constexpr uint32_t kOffK = kOffQ + 2 * kTileBytes;             // kStagesK x 8 KB
 constexpr uint32_t kOffV = kOffK + kStagesK * kTileBytes;      // kStagesV x 8 KB
-constexpr uint32_t kOffP = kOffV + kStagesV * kTileBytes;      // 2 x 8 KB
-constexpr uint32_t kOffSFQ = kOffP + 2 * kTileBytes;           // 2 x 1 KB
+constexpr uint32_t kOffP = kOffV + kStagesV * kTileBytes;      // kStagesP x 8 KB
+constexpr uint32_t kOffSFQ = kOffP + kStagesP * kTileBytes;    // 2 x 1 KB
 constexpr uint32_t kOffSFK = kOffSFQ + 2 * kSfBytes;           // kStagesK x 1 KB
 constexpr uint32_t kOffSFV = kOffSFK + kStagesK * kSfBytes;    // kStagesV x 1 KB
-constexpr uint32_t kOffSFP = kOffSFV + kStagesV * kSfBytes;    // 2 x 1 KB
-constexpr uint32_t kOffStats = kOffSFP + 2 * kSfBytes;         // 2 x 128 x RowStats
+constexpr uint32_t kOffSFP = kOffSFV + kStagesV * kSfBytes;    // kStagesP x 1 KB
+constexpr uint32_t kOffStats = kOffSFP + kStagesP * kSfBytes;  // 2 x 128 x RowStats
 constexpr uint32_t kOffFin = kOffStats + 2 * 128 * 48;         // 2 tiles x 4 WGs x 128 x (sum, ref)
 constexpr uint32_t kOffBar = kOffFin + 2 * 4 * 128 * 8;
-constexpr int kNumBars = 4 + 2 * kStagesK + 2 * kStagesV + 2 * 4 + 4;
+constexpr int kNumBars = 4 + 2 * kStagesK + 2 * kStagesV + 2 * 3 + kStagesP + 4;
 constexpr uint32_t kOffMisc = kOffBar + 8 * kNumBars;          // tmem slot, abort flag
 constexpr uint32_t kSmemUsed = kOffMisc + 16;
 constexpr uint32_t kSmemRequest = kSmemUsed + 1024;
@@ -145,7 +148,7 @@ struct Bars {
   static constexpr uint32_t kQFull = 0, kQEmpty = 2, kKFull = 4, kVFull = kKFull + kStagesK,
                             kSFull = kVFull + kStagesV, kPvDone = kSFull + kStagesK,
                             kSFree = kPvDone + kStagesV, kStReady = kSFree + 2, kStFree = kStReady + 2,
-                            kPFull = kStFree + 2, kFin = kPFull + 2, kOFree = kFin + 1,
+                            kPFull = kStFree + 2, kFin = kPFull + kStagesP, kOFree = kFin + 1,
                             kDrain = kOFree + 1, kCount = kDrain + 2;
   __device__ explicit Bars(uint32_t b) : base(b) {}
   __device__ __forceinline__ uint32_t at(uint32_t idx) const { return base + 8u * idx; }
@@ -245,9 +248,9 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
       mbar_init(bars.at(Bars::kSFree + b), 384);
       mbar_init(bars.at(Bars::kStReady + b), 128);
       mbar_init(bars.at(Bars::kStFree + b), 256);
-      mbar_init(bars.at(Bars::kPFull + b), 256);
       mbar_init(bars.at(Bars::kDrain + b), 1);
     }
+    for (int s = 0; s < kStagesP; ++s) mbar_init(bars.at(Bars::kPFull + s), 256);
     for (int s = 0; s < kStagesK; ++s) mbar_init(bars.at(Bars::kKFull + s), 1);
     for (int s = 0; s < kStagesV; ++s) mbar_init(bars.at(Bars::kVFull + s), 1);
     for (int s = 0; s < kStagesK; ++s) mbar_init(bars.at(Bars::kSFull + s), 1);
@@ -428,7 +431,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
           const uint32_t G = gb + i, st = G % kStagesV, b = G & 1;
           ok = mbar_wait(bars.at(Bars::kVFull + st), (G / kStagesV) & 1, wc, kSiteVFull);
           if (!ok) break;
-          ok = mbar_wait(bars.at(Bars::kPFull + b), (G >> 1) & 1, wc, kSitePFull);
+          ok = mbar_wait(bars.at(Bars::kPFull + (G % kStagesP)), (G / kStagesP) & 1, wc, kSitePFull);
           if (!ok) break;
           if (i == 0 && ti >= 1) {
             // O of the previous tile must have been copied out of tensor memory
@@ -438,8 +441,9 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
           FA4_TRACE_EV(22, G);
           tc_fence_after_sync();
           const uint32_t sfp = tmem + kTmSFP + 8 * b, sfv = tmem + kTmSFV + 8 * b;
-          const uint32_t psf = base + kOffSFP + b * kSfBytes, vsf = base + kOffSFV + st * kSfBytes;
-          const uint32_t pt = base + kOffP + b * kTileBytes, vt = base + kOffV + st * kTileBytes;
+          const uint32_t ps = G % kStagesP;
+          const uint32_t psf = base + kOffSFP + ps * kSfBytes, vsf = base + kOffSFV + st * kSfBytes;
+          const uint32_t pt = base + kOffP + ps * kTileBytes, vt = base + kOffV + st * kTileBytes;
           tc_cp_sf(sfp, psf);
           tc_cp_sf(sfv, vsf);
           mma_nvf4(tmem + kTmO, make_desc_sw64(pt), make_desc_sw64(vt), idesc, sfp, sfv,
@@ -496,17 +500,16 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         const int limit = causal_limit(p, t, row, nb);
         float bm[8];
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          float s[64];
-          tmem_ld32(lane_addr + (b ? kTmS1 : kTmS0) + 64 * h, reinterpret_cast<uint32_t*>(&s[0]));
-          tmem_ld32(lane_addr + (b ? kTmS1 : kTmS0) + 64 * h + 32, reinterpret_cast<uint32_t*>(&s[32]));
+        for (int c = 0; c < 4; ++c) {
+          float s[32];
+          tmem_ld32(lane_addr + (b ? kTmS1 : kTmS0) + 32 * c, reinterpret_cast<uint32_t*>(&s[0]));
           tc_wait_ld();
           if (masked) {
 #pragma unroll
-            for (int x = 0; x < 64; ++x) s[x] = (64 * h + x <= limit) ? s[x] : kNegInf;
+            for (int x = 0; x < 32; ++x) s[x] = (32 * c + x <= limit) ? s[x] : kNegInf;
           }
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
+          for (int q = 0; q < 2; ++q) {
             float m0 = fmax3(s[16 * q], s[16 * q + 1], s[16 * q + 2]);
             float m1 = fmax3(s[16 * q + 3], s[16 * q + 4], s[16 * q + 5]);
             m0 = fmax3(m0, s[16 * q + 6], s[16 * q + 7]);
@@ -514,7 +517,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
             m0 = fmax3(m0, s[16 * q + 10], s[16 * q + 11]);
             m1 = fmax3(m1, s[16 * q + 12], s[16 * q + 13]);
             m0 = fmax3(m0, s[16 * q + 14], s[16 * q + 15]);
-            bm[4 * h + q] = fmaxf(m0, m1);
+            bm[2 * c + q] = fmaxf(m0, m1);
           }
         }
         tc_fence_before_sync();
@@ -571,9 +574,10 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         // overlap; the blocking (bounded) wait only runs for a probe that failed.
         const uint32_t bar_s = bars.at(Bars::kSFull + (G % kStagesK)), par_s = (G / kStagesK) & 1;
         const uint32_t bar_r = bars.at(Bars::kStReady + b), par_r = (G >> 1) & 1;
-        const uint32_t bar_p = bars.at(Bars::kPvDone + ((G - 2) % kStagesV)), par_p = ((G - 2) / kStagesV) & 1;
+        const uint32_t bar_p = bars.at(Bars::kPvDone + ((G - kStagesP) % kStagesV)),
+                       par_p = ((G - kStagesP) / kStagesV) & 1;
         const bool r_s = mbar_test(bar_s, par_s);
-        const bool r_p = (G >= 2) ? mbar_test(bar_p, par_p) : true;
+        const bool r_p = (G >= kStagesP) ? mbar_test(bar_p, par_p) : true;
 
         // 1. scores: copied to registers as soon as the MMA has written them, so that the S buffer
         //    goes back to the QK^T issuer without waiting for the statistics (the buffer's cycle
@@ -607,11 +611,12 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         if (m_new != m_ref) l_sum *= reference_factor(m_ref, m_new, p.sl2);
         m_ref = m_new;
 
-        // 3. exponentials and quantisation; P buffer b is free once PV of block G-2 has completed
+        // 3. exponentials and quantisation; P tile G % kStagesP is free once PV of block
+        //    G - kStagesP has completed
         ok = wait_probed(r_p, bar_p, par_p, wc, kSitePvDone);
         if (!ok) break;
         FA4_TRACE_EV(6, G);
-        uint8_t* p_tile = gbase + kOffP + b * kTileBytes;
+        uint8_t* p_tile = gbase + kOffP + (G % kStagesP) * kTileBytes;
         uint4 chunk;
         l_sum += quantize_pair(&s[0], __uint_as_float(v_noff.x), __uint_as_float(v_noff.y),
                                __byte_perm(ue, 0u, 0x4440u), __byte_perm(ue, 0u, 0x4441u), p.sl2, chunk);
@@ -621,7 +626,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         *reinterpret_cast<uint4*>(p_tile + sw64_offset(row, 2 * half + 1)) = chunk;
         FA4_TRACE_EV(7, G);
         // scales of this half: one 64-key MMA step = scale word `half`
-        *reinterpret_cast<uint32_t*>(gbase + kOffSFP + b * kSfBytes + 512 * half + (row & 31) * 16 +
+        *reinterpret_cast<uint32_t*>(gbase + kOffSFP + (G % kStagesP) * kSfBytes + 512 * half + (row & 31) * 16 +
                                      (row >> 5) * 4) = block_scale_bytes(ue);
 
         // 4. correction (rare, out of line, after the scores are consumed): O holds blocks
@@ -638,7 +643,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         }
         fence_proxy_async_smem();
         tc_fence_before_sync();  // orders the O rescale stores before the issuer's next MMA
-        mbar_arrive(bars.at(Bars::kPFull + b));
+        mbar_arrive(bars.at(Bars::kPFull + (G % kStagesP)));
       }
       if (!ok) break;
 
