@@ -18,6 +18,7 @@ region.  ``cpu_baseline`` / ``--impl reference`` time the CPU restatement of the
 ``attention_ref`` (oracle/nvfp4_oracle.py) on a bounded sample of the same workload.
 """
 import argparse
+import datetime
 import json
 import math
 import os
@@ -145,7 +146,8 @@ def workload_config(name, wl, world):
 # GPU arm
 # ------------------------------------------------------------------------------------------------
 class ClockSampler:
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    """nvidia-smi clock / throttle-reason samples; only those stamped inside the timed region count."""
+    QUERY = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -154,12 +156,13 @@ class ClockSampler:
         self.p = None
         try:
             self.p = subprocess.Popen(["nvidia-smi", f"--id={gpu_index}", f"--query-gpu={self.QUERY}",
-                                       "--format=csv,noheader,nounits", "-lms", "100"],
+                                       "--format=csv,noheader,nounits", "-lms", "20"],
                                       stdout=self.f, stderr=subprocess.DEVNULL)
         except OSError:
             pass
 
-    def stop(self):
+    def stop(self, t_begin, t_end):
+        """t_begin / t_end: datetime.now() taken around the timed region."""
         if self.p is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.p.terminate()
@@ -170,21 +173,27 @@ class ClockSampler:
         self.f.flush()
         rows = [r.strip().split(", ") for r in open(self.f.name) if r.strip()]
         os.unlink(self.f.name)
-        sm, mx, reasons, power = [], [], set(), []
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        parsed = []
         for r in rows:
             if len(r) < 9:
                 continue
             try:
-                sm.append(float(r[1])); mx.append(float(r[2])); power.append(float(r[3]))
+                ts = datetime.datetime.strptime(r[0].strip(), "%Y/%m/%d %H:%M:%S.%f")
+                parsed.append((ts, float(r[1]), float(r[2]), float(r[3]),
+                               [nm for nm, val in zip(names, r[5:9]) if val.strip().lower() == "active"]))
             except ValueError:
                 continue
-            for nm, val in zip(names, r[5:9]):
-                if val.strip().lower() == "active":
-                    reasons.add(nm)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "power_w_max": max(power) if power else None, "samples": len(sm),
-                "reasons": sorted(reasons)}
+        inside = [x for x in parsed if t_begin <= x[0] <= t_end]
+        window = "timed region"
+        if not inside:                      # region shorter than the sampling interval
+            inside, window = parsed[-3:], "last samples before the region ended"
+        sm = [x[1] for x in inside]
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max((x[2] for x in inside), default=None),
+                "power_w_max": max((x[3] for x in inside), default=None),
+                "samples": len(inside), "samples_total": len(parsed), "window": window,
+                "reasons": sorted({nm for x in inside for nm in x[4]})}
 
 
 def run_gpu_arm(args, wl, rank, local_rank, world):
@@ -195,6 +204,7 @@ def run_gpu_arm(args, wl, rank, local_rank, world):
     torch.cuda.set_device(dev)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    sampler = ClockSampler(local_rank) if rank == 0 else None   # started early: its first sample is slow
 
     # ---- synthetic inputs of this rank's shard (global batch = B * world; this rank's B batches)
     g = torch.Generator(device=dev).manual_seed(1000 + rank)
@@ -228,11 +238,11 @@ def run_gpu_arm(args, wl, rank, local_rank, world):
     torch.cuda.synchronize()
     fa.check_status(dev)
 
-    sampler = ClockSampler(local_rank) if rank == 0 else None
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
            for _ in range(args.steps)]
     barrier()
     torch.cuda.nvtx.range_push("timed")          # lets a profiler select the timed region
+    t_begin = datetime.datetime.now()
     t_wall0 = time.perf_counter()
     for e0, e1 in evs:
         flush.zero_()
@@ -243,6 +253,7 @@ def run_gpu_arm(args, wl, rank, local_rank, world):
     torch.cuda.nvtx.range_pop()
     t_wall = time.perf_counter() - t_wall0
     dev_ms = sum(e0.elapsed_time(e1) for e0, e1 in evs)
+    clocks = sampler.stop(t_begin, datetime.datetime.now()) if sampler else None
     fa.check_status(dev)
 
     # ---- end to end through the public API with host buffers
@@ -271,8 +282,8 @@ def run_gpu_arm(args, wl, rank, local_rank, world):
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1) / e2e_steps
-    clocks = sampler.stop() if sampler else None
     fa.check_status(dev)
+    mma_rate = fa.measure_fp4_mma_rate(device=dev) if rank == 0 else None
 
     times = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device=dev)
     if world > 1:
@@ -301,6 +312,8 @@ def run_gpu_arm(args, wl, rank, local_rank, world):
                 "peak_note": f"4 x the {peaks['source']} cuBLAS bf16 burst figure "
                              f"({peaks['bf16_tflops']} TFLOP/s): block-scaled e2m1 MMAs issue at 4x the "
                              f"bf16 rate; nominal dense FP4 is {FP4_NOMINAL_TFLOPS} TFLOP/s",
+                "fp4_mma_rate_measured": mma_rate,
+                "frac_of_measured_fp4_mma_rate": tflops_gpu / mma_rate["tflops"],
                 "traffic": TRAFFIC_BYTES.get(args.workload),
                 "algorithmic_bytes": algorithmic_bytes(B, Hq, Hkv, S, D),
                 "hbm_gbs_achieved": algorithmic_bytes(B, Hq, Hkv, S, D) / (ms_per_step * 1e-3) / 1e9,
@@ -321,14 +334,16 @@ def run_gpu_arm(args, wl, rank, local_rank, world):
 
 
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the attention kernel,
-# from the ncu captures summarised under profiles/; None until captured.
-TRAFFIC_BYTES = {}
+# from the ncu captures summarised under profiles/.  cfg2 was captured whole (128.2 MB read +
+# 237.0 MB written); cfg1 is the capture of half of it (B = 2: 81.9 MB + 58.3 MB) scaled by the
+# batch, which the traffic is proportional to.  None for workloads that were not captured.
+TRAFFIC_BYTES = {"cfg2": 365_250_560, "cfg1": 2 * 140_234_752}
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default="cfg2")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])

@@ -100,6 +100,9 @@ def lib() -> ctypes.CDLL:
             L.fa4_nvfp4_debug_qk_tile.restype = ctypes.c_int
             L.fa4_nvfp4_debug_wait_expiry.argtypes = [ctypes.c_void_p, ctypes.c_uint64, ctypes.c_void_p]
             L.fa4_nvfp4_debug_wait_expiry.restype = ctypes.c_int
+            L.fa4_nvfp4_debug_mma_rate.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p,
+                                                   ctypes.c_void_p, ctypes.c_void_p]
+            L.fa4_nvfp4_debug_mma_rate.restype = ctypes.c_int
             L.fa4_nvfp4_fwd_linear_sf_noalloc.argtypes = [ctypes.POINTER(Params), ctypes.c_void_p]
             L.fa4_nvfp4_fwd_linear_sf_noalloc.restype = ctypes.c_int
             _lib = L
@@ -107,7 +110,8 @@ def lib() -> ctypes.CDLL:
 
 
 EXPORTS = ["fa4_nvfp4_fwd", "fa4_nvfp4_sf_linear_to_tiled", "fa4_nvfp4_query",
-           "fa4_nvfp4_debug_qk_tile", "fa4_nvfp4_debug_wait_expiry", "fa4_nvfp4_fwd_linear_sf_noalloc"]
+           "fa4_nvfp4_debug_qk_tile", "fa4_nvfp4_debug_wait_expiry", "fa4_nvfp4_debug_mma_rate",
+           "fa4_nvfp4_fwd_linear_sf_noalloc"]
 
 
 def check(rc: int, what: str) -> None:

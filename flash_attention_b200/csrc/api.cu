@@ -196,6 +196,18 @@ extern "C" int fa4_nvfp4_debug_qk_tile(const void* q, const void* k, const void*
   return e == cudaSuccess ? 0 : (int)e;
 }
 
+extern "C" int fa4_nvfp4_debug_mma_rate(int32_t iters, int32_t num_ctas, uint64_t* clocks_out,
+                                        uint32_t* status, void* cuda_stream) {
+  if (!clocks_out) return -FA4_E_NULL;
+  if (iters < 4 || iters % 4 != 0 || iters > (1 << 22) || num_ctas < 1 || num_ctas > 1024)
+    return -FA4_E_SHAPE;
+  if (int e = ensure_smem(mma_rate_kernel, serial::kSmemRequest)) return e;
+  mma_rate_kernel<<<num_ctas, 128, serial::kSmemRequest, static_cast<cudaStream_t>(cuda_stream)>>>(
+      iters, reinterpret_cast<unsigned long long*>(clocks_out), status, kDefaultBudgetNs);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : (int)e;
+}
+
 extern "C" int fa4_nvfp4_debug_wait_expiry(uint32_t* status, uint64_t budget_ns, void* cuda_stream) {
   if (!status) return -FA4_E_NULL;
   if (budget_ns == 0 || budget_ns > kDefaultBudgetNs) return -FA4_E_SHAPE;

@@ -145,6 +145,78 @@ qk_tile_probe_kernel(const __grid_constant__ CUtensorMap tm_q,
 }
 
 // ---------------------------------------------------------------------------------------------
+// Tensor-pipe rate of the block-scaled e2m1 MMA (the denominator "measured FP4 peak"): every CTA
+// (one per SM) fills one A and one B tile and their scale chunks with pseudo-random bytes, then
+// one thread issues `iters` 128 x 128 x 64 instructions back to back, alternating between two
+// accumulators, and the CTA reports the clocks from the first issue to the completion of the
+// last.  Nothing is read from or written to HBM inside the timed part.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128, 1)
+mma_rate_kernel(int iters, unsigned long long* clocks_out, uint32_t* status, uint64_t budget_ns) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gbase = smem_raw + (base - smem_u32(smem_raw));
+  constexpr uint32_t kOffA = 0, kOffB = 8192, kOffSFA = 16384, kOffSFB = 17408, kOffBar = 18432;
+  const uint32_t bar_mma = base + kOffBar;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + kOffBar + 16);
+  volatile uint32_t* s_abort = reinterpret_cast<volatile uint32_t*>(gbase + kOffBar + 20);
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const WaitCtx wc{s_abort, status, budget_ns};
+
+  if (tid == 0) {
+    *s_abort = 0u;
+    mbar_init(bar_mma, 1);
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(base + kOffBar + 16, kTmemCols);
+    tmem_relinquish();
+  }
+  // operand bytes: any nibble is a valid e2m1; scale bytes 0x30..0x3f are ue4m3 values 2^-1..2
+  uint32_t x = 0x9e3779b9u * (blockIdx.x * 128u + tid + 1u);
+  for (int i = tid; i < 16384 / 4; i += 128) {
+    x = x * 1664525u + 1013904223u;
+    reinterpret_cast<uint32_t*>(gbase + kOffA)[i] = x ^ (x >> 13);
+  }
+  for (int i = tid; i < 2048 / 4; i += 128) {
+    x = x * 1664525u + 1013904223u;
+    reinterpret_cast<uint32_t*>(gbase + kOffSFA)[i] = 0x30303030u | ((x >> 8) & 0x0f0f0f0fu);
+  }
+  fence_proxy_async_smem();
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+  long long t0 = 0;
+  if (tid == 0) {
+    tc_cp_sf(tmem + kTmSFQ, base + kOffSFA);
+    tc_cp_sf(tmem + kTmSFQ + 4, base + kOffSFA + 512);
+    tc_cp_sf(tmem + kTmSFK, base + kOffSFB);
+    tc_cp_sf(tmem + kTmSFK + 4, base + kOffSFB + 512);
+    constexpr uint32_t idesc = make_idesc_nvf4(128, 128);
+    const uint64_t da0 = make_smem_desc(base + kOffA, 16, 512, kSwizzle64);
+    const uint64_t db0 = make_smem_desc(base + kOffB, 16, 512, kSwizzle64);
+    const uint64_t da1 = make_smem_desc(base + kOffA + 32, 16, 512, kSwizzle64);
+    const uint64_t db1 = make_smem_desc(base + kOffB + 32, 16, 512, kSwizzle64);
+    t0 = clock64();
+#pragma unroll 1
+    for (int i = 0; i < iters; i += 4) {
+      // a fresh accumulation every 4 instructions per accumulator keeps the sums finite
+      mma_nvf4(tmem + kTmS0, da0, db0, idesc, tmem + kTmSFQ, tmem + kTmSFK, 0);
+      mma_nvf4(tmem + kTmS1, da0, db0, idesc, tmem + kTmSFQ, tmem + kTmSFK, 0);
+      mma_nvf4(tmem + kTmS0, da1, db1, idesc, tmem + kTmSFQ + 4, tmem + kTmSFK + 4, 1);
+      mma_nvf4(tmem + kTmS1, da1, db1, idesc, tmem + kTmSFQ + 4, tmem + kTmSFK + 4, 1);
+    }
+    tc_commit(bar_mma);
+  }
+  const bool ok = __all_sync(0xffffffffu, mbar_wait(bar_mma, 0, wc, 3));
+  if (tid == 0 && ok) clocks_out[blockIdx.x] = static_cast<unsigned long long>(clock64() - t0);
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, kTmemCols);
+}
+
+// ---------------------------------------------------------------------------------------------
 // Bounded-wait self test: a barrier nothing arrives at.
 // ---------------------------------------------------------------------------------------------
 __global__ void wait_expiry_kernel(uint32_t* status, uint64_t budget_ns) {

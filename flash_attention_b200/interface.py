@@ -219,3 +219,33 @@ def flash_attn_func(
         q.data, k.data, v.data, q.sf, k.sf, v.sf, q.scale, k.scale, v.scale,
         softmax_scale=softmax_scale, causal=causal, return_lse=return_lse,
         sf_layout="tiled" if q.tiled else "linear")
+
+
+def measure_fp4_mma_rate(iters: int = 1 << 16, device=None, repeats: int = 3) -> dict:
+    """Dense block-scaled e2m1 tensor-pipe rate of this GPU, measured.
+
+    Launches one CTA per SM that issues ``iters`` 128x128x64 MMAs back to back from shared memory
+    (``fa4_nvfp4_debug_mma_rate``) and times the launch with CUDA events.  Returns the best of
+    ``repeats``: ``{"tflops", "clk_per_mma" (median over CTAs, in-kernel clocks), "ms", "sms"}``.
+    The benchmark reports it beside the nominal dense-FP4 figure.
+    """
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    clocks = torch.zeros(sms, dtype=torch.int64, device=device)
+    status = DeviceStatus.word(device)
+    stream = torch.cuda.current_stream(device)
+    best = None
+    for _ in range(repeats + 1):          # the first launch is the warm-up
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        _lib.check(_lib.lib().fa4_nvfp4_debug_mma_rate(iters, sms, clocks.data_ptr(), status.data_ptr(),
+                                                      stream.cuda_stream), "fa4_nvfp4_debug_mma_rate")
+        e1.record(stream)
+        e1.synchronize()
+        ms = e0.elapsed_time(e1)
+        if best is None or ms < best:
+            best = ms
+    check_status(device)
+    flops = sms * iters * 2.0 * 128 * 128 * 64
+    return {"tflops": flops / (best * 1e-3) / 1e12, "ms": best, "sms": sms,
+            "clk_per_mma": float(clocks.double().median().item()) / iters}

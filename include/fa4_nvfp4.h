@@ -153,6 +153,18 @@ int fa4_nvfp4_debug_qk_tile(const void* q, const void* k, const void* q_sf,
                             int32_t mode, uint32_t* status, void* cuda_stream);
 
 /*
+ * Tensor-pipe rate probe: `num_ctas` CTAs (one per SM when num_ctas = SM count) each issue
+ * `iters` (a multiple of 4) block-scaled 128x128x64 e2m1 MMAs back to back on operands that
+ * stay in shared memory, and write the clocks from first issue to last completion to
+ * clocks_out[cta] (device memory, num_ctas entries).  The caller times the launch; FLOPs =
+ * num_ctas * iters * 2 * 128 * 128 * 64.  This is the measured dense-FP4 ceiling the benchmark
+ * reports beside the nominal one; no counterpart in the reference (its benchmark hard-codes a
+ * nominal peak, benchmarks/benchmark_attn.py:200).
+ */
+int fa4_nvfp4_debug_mma_rate(int32_t iters, int32_t num_ctas, uint64_t* clocks_out,
+                             uint32_t* status, void* cuda_stream);
+
+/*
  * Bounded-wait self test: launches one CTA that waits on a barrier nothing
  * arrives at, with a limit of `budget_ns`; the kernel must give up, record
  * FA4_S_WAIT_EXPIRED in *status and return normally.  No counterpart in the

@@ -66,6 +66,19 @@ def test_bounded_wait_gives_up_and_reports(cuda_device):
     assert float(torch.ones(4, device=cuda_device).sum()) == 4.0
 
 
+def test_mma_rate_probe_runs_and_is_plausible(cuda_device):
+    # 148 SMs x 32768 FLOP/clk at ~1.9 GHz is ~9 PFLOP/s; anything from a quarter of that up to a
+    # little above it is a sane reading, and 128x128x64 cannot retire faster than 64 clk.
+    r = fa.measure_fp4_mma_rate(iters=1 << 14, device=cuda_device)
+    assert r["sms"] >= 1 and r["clk_per_mma"] >= 60.0
+    assert 2000.0 < r["tflops"] * 148 / r["sms"] < 11000.0
+    assert lib_rc_rejects_bad_iters()
+
+
+def lib_rc_rejects_bad_iters():
+    return fa.lib().fa4_nvfp4_debug_mma_rate(3, 1, 1, None, None) < 0
+
+
 def test_sf_linear_to_tiled_bit_exact(cuda_device):
     rng = np.random.default_rng(3)
     for shape, rows_dim, head_dim, mult in [((2, 300, 3, 8), 1, 2, 1), ((1, 2, 128, 40), 2, 1, 1),
