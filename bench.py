@@ -217,6 +217,18 @@ def run_gpu_arm(args, wl, rank, local_rank, world):
             idx = torch.randperm(D, generator=g, device=dev)[:n]
             t[..., idx] *= 20.0
     Q, K, V = fa.quantize_qkv(q, k, v)
+    # the fused quantiser (the step in front of the path), timed on the same tensors: HBM-bound
+    for _ in range(2):
+        fa.quantize_qkv_fused(q, k, v, linear_sf=False)
+    qe0, qe1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    qe0.record()
+    for _ in range(5):
+        fa.quantize_qkv_fused(q, k, v, linear_sf=False)
+    qe1.record()
+    torch.cuda.synchronize()
+    quant_ms = qe0.elapsed_time(qe1) / 5
+    n_el = q.numel() + k.numel() + v.numel()
+    quant_bytes = n_el * (2 + 2) + n_el // 2 + n_el // 16     # two bf16 reads, packed + tiled scales
     del q, k, v
     Qt, Kt, Vt = (fa.NVFP4Tensor(t.data, t.tiled_sf(), t.scale, True, t.is_v) for t in (Q, K, V))
     out = torch.empty(B, S, Hq, D, dtype=torch.bfloat16, device=dev)
@@ -321,6 +333,11 @@ def run_gpu_arm(args, wl, rank, local_rank, world):
             "e2e": {"value": fl_rank * world / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
                     "launches_per_step": 4},
+            "quantizer": {"ms": quant_ms, "algorithmic_bytes": quant_bytes,
+                          "gbs": quant_bytes / (quant_ms * 1e-3) / 1e9,
+                          "frac_of_hbm_peak": quant_bytes / (quant_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                          "note": "fused bf16 -> NVFP4 quantiser of q, k, v (6 launches + one scale "
+                                  "read-back), outside the timed region"},
             "gpu_launches": args.steps,
             "wall_ms_timed_region": t_wall * 1e3,
             "clocks": clocks,

@@ -103,6 +103,15 @@ def lib() -> ctypes.CDLL:
             L.fa4_nvfp4_debug_mma_rate.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p,
                                                    ctypes.c_void_p, ctypes.c_void_p]
             L.fa4_nvfp4_debug_mma_rate.restype = ctypes.c_int
+            L.fa4_nvfp4_amax_bf16.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32,
+                                              ctypes.c_int32, ctypes.c_int32, ctypes.c_int64,
+                                              ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p,
+                                              ctypes.c_void_p]
+            L.fa4_nvfp4_amax_bf16.restype = ctypes.c_int
+            for fn in (L.fa4_nvfp4_quantize_qk_bf16, L.fa4_nvfp4_quantize_v_bf16):
+                fn.argtypes = [ctypes.c_void_p] + [ctypes.c_int32] * 4 + [ctypes.c_int64] * 3 + \
+                              [ctypes.c_void_p] * 6
+                fn.restype = ctypes.c_int
             L.fa4_nvfp4_fwd_linear_sf_noalloc.argtypes = [ctypes.POINTER(Params), ctypes.c_void_p]
             L.fa4_nvfp4_fwd_linear_sf_noalloc.restype = ctypes.c_int
             _lib = L
@@ -111,7 +120,8 @@ def lib() -> ctypes.CDLL:
 
 EXPORTS = ["fa4_nvfp4_fwd", "fa4_nvfp4_sf_linear_to_tiled", "fa4_nvfp4_query",
            "fa4_nvfp4_debug_qk_tile", "fa4_nvfp4_debug_wait_expiry", "fa4_nvfp4_debug_mma_rate",
-           "fa4_nvfp4_fwd_linear_sf_noalloc"]
+           "fa4_nvfp4_fwd_linear_sf_noalloc", "fa4_nvfp4_amax_bf16", "fa4_nvfp4_quantize_qk_bf16",
+           "fa4_nvfp4_quantize_v_bf16"]
 
 
 def check(rc: int, what: str) -> None:

@@ -6,6 +6,7 @@
 #include "attn_serial.cuh"
 #include "attn_ws.cuh"
 #include "aux_kernels.cuh"
+#include "quantize.cuh"
 
 #include <cudaTypedefs.h>
 #include <mutex>
@@ -170,6 +171,77 @@ extern "C" int fa4_nvfp4_sf_linear_to_tiled(const void* src, void* dst, int32_t 
   sf_linear_to_tiled_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
       static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), n_outer, n_inner, rows, cols,
       stride_outer, stride_inner, stride_row, col_tile_multiple);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : (int)e;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Fused NVFP4 quantiser (bf16 operands in the reference layout -> what fa4_nvfp4_fwd reads)
+// ---------------------------------------------------------------------------------------------
+extern "C" int fa4_nvfp4_amax_bf16(const void* x, int64_t n0, int32_t n1, int32_t n2, int32_t inner,
+                                   int64_t s0, int64_t s1, int64_t s2, float* amax,
+                                   void* cuda_stream) {
+  if (!x || !amax) return -FA4_E_NULL;
+  if (n0 <= 0 || n1 <= 0 || n2 <= 0 || inner <= 0 || inner % 8 != 0) return -FA4_E_SHAPE;
+  if (s0 % 8 != 0 || s1 % 8 != 0 || s2 % 8 != 0) return -FA4_E_STRIDE;
+  if (!aligned16(x)) return -FA4_E_ALIGN;
+  if (n0 * n1 > 0x7fffffffll || (int64_t)n2 * (inner / 8) > (1 << 24)) return -FA4_E_TOO_LARGE;
+  const int rows = (int)(n0 * n1);
+  const int per_row = n2 * (inner / 8);
+  // a group of rows gives every thread about 8 independent 16-byte loads
+  int rows_per_group = (256 * 8 + per_row - 1) / per_row;
+  if (rows_per_group > rows) rows_per_group = rows;
+  const int groups = (rows + rows_per_group - 1) / rows_per_group;
+  const int grid = groups < 148 * 8 ? groups : 148 * 8;
+  amax_bf16_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), n1, n2, inner / 8, s0, s1, s2, rows, rows_per_group,
+      make_fastdiv(per_row), make_fastdiv(inner / 8), make_fastdiv(n1), amax);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : (int)e;
+}
+
+extern "C" int fa4_nvfp4_quantize_qk_bf16(const void* x, int32_t B, int32_t S, int32_t H, int32_t D,
+                                          int64_t stride_b, int64_t stride_s, int64_t stride_h,
+                                          const float* amax, void* packed, void* sf_linear,
+                                          void* sf_tiled, float* scale_out, void* cuda_stream) {
+  if (!x || !amax || !packed) return -FA4_E_NULL;
+  if (B <= 0 || S <= 0 || H <= 0 || D <= 0 || D % 64 != 0) return -FA4_E_SHAPE;
+  if (stride_b % 8 != 0 || stride_s % 8 != 0 || stride_h % 8 != 0) return -FA4_E_STRIDE;
+  if (!aligned16(x) || !aligned16(packed) || (sf_linear && !aligned16(sf_linear)) ||
+      (sf_tiled && !aligned16(sf_tiled)))
+    return -FA4_E_ALIGN;
+  const int64_t rows64 = (int64_t)B * ((S + 127) / 128) * 128;
+  const int64_t per_row64 = (int64_t)H * (D / 16);
+  if (rows64 > 0x7fffffffll || per_row64 > (1 << 24)) return -FA4_E_TOO_LARGE;
+  const int per_row = (int)per_row64;
+  int rows_per_group = per_row >= 256 ? 1 : 256 / per_row;   // about one block of 16 per thread
+  const int64_t groups = (rows64 + rows_per_group - 1) / rows_per_group;
+  if (groups > 0x7fffffffll) return -FA4_E_TOO_LARGE;
+  quantize_rows_kernel<<<(unsigned)groups, 256, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), B, S, H, D, stride_b, stride_s, stride_h, amax,
+      static_cast<uint8_t*>(packed), static_cast<uint8_t*>(sf_linear),
+      static_cast<uint8_t*>(sf_tiled), scale_out, rows_per_group, make_fastdiv(per_row),
+      make_fastdiv(D / 16), make_fastdiv(((S + 127) / 128) * 128));
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : (int)e;
+}
+
+extern "C" int fa4_nvfp4_quantize_v_bf16(const void* x, int32_t B, int32_t Sk, int32_t H, int32_t Dv,
+                                         int64_t stride_b, int64_t stride_s, int64_t stride_h,
+                                         const float* amax, void* packed, void* sf_linear,
+                                         void* sf_tiled, float* scale_out, void* cuda_stream) {
+  if (!x || !amax || !packed) return -FA4_E_NULL;
+  if (B <= 0 || Sk <= 0 || H <= 0 || Dv <= 0 || Sk % 16 != 0 || Dv % 8 != 0) return -FA4_E_SHAPE;
+  if ((int64_t)B * H > 65535) return -FA4_E_TOO_LARGE;
+  if (stride_b % 8 != 0 || stride_s % 8 != 0 || stride_h % 8 != 0) return -FA4_E_STRIDE;
+  if (!aligned16(x) || !aligned16(packed) || (sf_linear && !aligned16(sf_linear)) ||
+      (sf_tiled && !aligned16(sf_tiled)))
+    return -FA4_E_ALIGN;
+  const dim3 grid((Sk + 127) / 128, (Dv + 127) / 128, B * H);
+  quantize_v_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), B, Sk, H, Dv, stride_b, stride_s, stride_h, amax,
+      static_cast<uint8_t*>(packed), static_cast<uint8_t*>(sf_linear),
+      static_cast<uint8_t*>(sf_tiled), scale_out);
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : (int)e;
 }

@@ -213,7 +213,7 @@ def flash_attn_func(
                                                            mask_block_cnt, mask_block_idx)):
         raise NotImplementedError("mask_mod / block sparsity is not built")
     layouts = {t.tiled for t in (q, k, v)}
-    if len(layouts) != 1:
+    if len(layouts) != 1 or any(t.sf_tiled is not None for t in (q, k, v)):
         q, k, v = (NVFP4Tensor(t.data, t.tiled_sf(), t.scale, True, t.is_v) for t in (q, k, v))
     return flash_attn_fp4_func(
         q.data, k.data, v.data, q.sf, k.sf, v.sf, q.scale, k.scale, v.scale,

@@ -105,10 +105,13 @@ class NVFP4Tensor:
     scale: float
     tiled: bool = False
     is_v: bool = False
+    sf_tiled: Optional[torch.Tensor] = None   # tiled copy of a linear ``sf`` when one exists already
 
     def tiled_sf(self) -> torch.Tensor:
         if self.tiled:
             return self.sf
+        if self.sf_tiled is not None:
+            return self.sf_tiled
         return sf_to_tiled(self.sf, 2, 1, 2) if self.is_v else sf_to_tiled(self.sf, 1, 2)
 
     def dequantize(self) -> torch.Tensor:
@@ -125,3 +128,53 @@ def quantize_qkv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor):
     vt = v.permute(0, 2, 3, 1)  # (B, Hkv, Dv, Sk): blocks along the key axis
     vd, vs, vg = quantize_lastdim(vt)
     return (NVFP4Tensor(qd, qs, qg), NVFP4Tensor(kd, ks, kg), NVFP4Tensor(vd, vs, vg, is_v=True))
+
+
+def quantize_qkv_fused(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, linear_sf: bool = True):
+    """CUDA quantiser: bf16 (B,S,H,D) tensors in the reference layout -> three NVFP4Tensor.
+
+    Same results as :func:`quantize_qkv` computed with correctly rounded fp32 divisions (the CPU
+    oracle's arithmetic), in two passes per tensor over HBM (amax, then quantise) instead of a few
+    dozen torch kernels: ``fa4_nvfp4_amax_bf16`` + ``fa4_nvfp4_quantize_qk_bf16`` /
+    ``fa4_nvfp4_quantize_v_bf16``.  V is transposed to key-contiguous on the way.  The tiled scale
+    factors the attention kernel reads are always produced; ``linear_sf=False`` skips the linear
+    copies (then ``NVFP4Tensor.dequantize`` is unavailable).  One host synchronisation at the end
+    fetches the three per-tensor scales.
+    """
+    L = _lib.lib()
+    outs = []
+    dev = q.device
+    amax = torch.zeros(3, dtype=torch.float32, device=dev)
+    scales = torch.empty(3, dtype=torch.float32, device=dev)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    for i, (x, is_v) in enumerate(((q, False), (k, False), (v, True))):
+        if not (x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 4 and x.stride(-1) == 1):
+            raise AssertionError("quantize_qkv_fused takes CUDA bf16 (B, S, H, D) tensors, last dim contiguous")
+        B, S, H, D = x.shape
+        a_ptr = amax.data_ptr() + 4 * i
+        s_ptr = scales.data_ptr() + 4 * i
+        _lib.check(L.fa4_nvfp4_amax_bf16(x.data_ptr(), B, S, H, D, x.stride(0), x.stride(1), x.stride(2),
+                                         a_ptr, stream), "fa4_nvfp4_amax_bf16")
+        if is_v:
+            packed = torch.empty(B, H, D, S // 2, dtype=torch.uint8, device=dev)
+            lin = torch.empty(B, H, D, S // 16, dtype=torch.uint8, device=dev) if linear_sf else None
+            tiled = torch.empty(B, H, (D + 127) // 128, 2 * ((S + 127) // 128), 512, dtype=torch.uint8,
+                                device=dev)
+            fn, what = L.fa4_nvfp4_quantize_v_bf16, "fa4_nvfp4_quantize_v_bf16"
+        else:
+            packed = torch.empty(B, S, H, D // 2, dtype=torch.uint8, device=dev)
+            lin = torch.empty(B, S, H, D // 16, dtype=torch.uint8, device=dev) if linear_sf else None
+            tiled = torch.empty(B, H, (S + 127) // 128, D // 64, 512, dtype=torch.uint8, device=dev)
+            fn, what = L.fa4_nvfp4_quantize_qk_bf16, "fa4_nvfp4_quantize_qk_bf16"
+        _lib.check(fn(x.data_ptr(), B, S, H, D, x.stride(0), x.stride(1), x.stride(2), a_ptr,
+                      packed.data_ptr(), lin.data_ptr() if lin is not None else None,
+                      tiled.data_ptr(), s_ptr, stream), what)
+        outs.append((packed, lin, tiled, is_v))
+    host_scales = scales.tolist()
+    res = []
+    for (packed, lin, tiled, is_v), sc in zip(outs, host_scales):
+        if lin is not None:
+            res.append(NVFP4Tensor(packed, lin, float(sc), False, is_v, tiled))
+        else:
+            res.append(NVFP4Tensor(packed, tiled, float(sc), True, is_v))
+    return tuple(res)

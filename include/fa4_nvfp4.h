@@ -141,6 +141,40 @@ int fa4_nvfp4_sf_linear_to_tiled(const void* src, void* dst,
 int fa4_nvfp4_query(int32_t what);
 
 /*
+ * Fused NVFP4 quantiser: bf16 operands in the reference's layout ((batch, seqlen, heads,
+ * head_dim), flash_attn/cute/interface.py:227-228, last dimension contiguous, strides in
+ * ELEMENTS and multiples of 8) -> the operands of fa4_nvfp4_fwd.  No counterpart in the
+ * reference, which takes fp16/bf16 only (interface.py:370); this is the step a caller runs
+ * directly before the forward.  Arithmetic, every step a correctly rounded fp32 operation:
+ *     tensor scale = amax / (6 * 448)               (1 for an all-zero tensor)
+ *     block scale  = e4m3_rne(min(block_amax / 6 / tensor scale, 448))   per 16 elements
+ *     element      = e2m1_rne(x / (block scale * tensor scale)), never negative zero
+ *
+ * fa4_nvfp4_amax_bf16: *amax = max(*amax, max |x|) over an (n0, n1, n2, inner) tensor; the
+ *     caller zeroes *amax (device memory) first.  inner % 8 == 0.
+ * fa4_nvfp4_quantize_qk_bf16: x (B, S, H, D), blocks along D (D % 64 == 0).  Writes
+ *     packed (B, S, H, D/2); sf_linear (B, S, H, D/16) and / or sf_tiled
+ *     (B, H, ceil(S/128), D/64, 512), either may be NULL; *scale_out (device, may be NULL)
+ *     receives the tensor scale.  `amax` is device memory (the result of the call above, or any
+ *     caller-chosen value: the tensor scale is derived from it).
+ * fa4_nvfp4_quantize_v_bf16: x (B, Sk, H, Dv), blocks along the KEY axis (Sk % 16 == 0,
+ *     Dv % 8 == 0, B * H <= 65535).  Writes packed (B, H, Dv, Sk/2) -- V key-contiguous --,
+ *     sf_linear (B, H, Dv, Sk/16) and / or sf_tiled (B, H, ceil(Dv/128), 2*ceil(Sk/128), 512).
+ * All outputs are fully contiguous and 16-byte aligned; nothing is allocated; the kernels run on
+ * `cuda_stream` in call order.
+ */
+int fa4_nvfp4_amax_bf16(const void* x, int64_t n0, int32_t n1, int32_t n2, int32_t inner,
+                        int64_t s0, int64_t s1, int64_t s2, float* amax, void* cuda_stream);
+int fa4_nvfp4_quantize_qk_bf16(const void* x, int32_t B, int32_t S, int32_t H, int32_t D,
+                               int64_t stride_b, int64_t stride_s, int64_t stride_h,
+                               const float* amax, void* packed, void* sf_linear, void* sf_tiled,
+                               float* scale_out, void* cuda_stream);
+int fa4_nvfp4_quantize_v_bf16(const void* x, int32_t B, int32_t Sk, int32_t H, int32_t Dv,
+                              int64_t stride_b, int64_t stride_s, int64_t stride_h,
+                              const float* amax, void* packed, void* sf_linear, void* sf_tiled,
+                              float* scale_out, void* cuda_stream);
+
+/*
  * Hardware-contract probe: one 128x128xD block-scaled tile S = A * B^T with
  * A = q tile, B = k tile (same operand formats as above, one head, one batch,
  * Sq = Sk = 128), written as fp32 (128,128) to `s_out`.  `mode` bit 0: stage the
