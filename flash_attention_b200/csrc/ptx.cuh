@@ -82,16 +82,32 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// One poll of a blocking wait: try_wait with a short suspend-time hint.  Measured against the
+// alternatives on the attention kernel: the default (system-chosen) suspend time was 2-3 % slower,
+// pure test_wait polling 4 % slower.
+__device__ __forceinline__ bool mbar_poll(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+      "selp.b32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(64u)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait.  Returns false when the CTA is aborting (this wait ran out, or another
 // role's did); the caller must then leave its loop and go to the common tear-down.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& w,
                                           uint32_t site) {
-  if (mbar_try_wait(bar, parity)) return true;
+  if (mbar_poll(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 32; ++i) {
-      if (mbar_try_wait(bar, parity)) return true;
+      if (mbar_poll(bar, parity)) return true;
     }
     if (*w.s_abort) return false;
     if (globaltimer_ns() - t0 > w.budget_ns) {
