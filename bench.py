@@ -362,6 +362,59 @@ def run_gpu_arm(args, wl, rank, local_rank, world):
 TRAFFIC_BYTES = {"cfg2": 365_250_560, "cfg1": 2 * 140_234_752}
 
 
+def run_sweep(args):
+    """Head-dim and shape sweep (B * H = 128 as B = 8, H = 16): every point is timed like the main
+    arm (resident inputs, L2 flush between launches, CUDA events); ONE JSON line with the table."""
+    import flash_attention_b200 as fa
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks = measured_peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    rows = []
+    steps = max(3, min(args.steps, 20))
+    for D in (64, 128):
+        for S in (1024, 2048, 4096, 16384):
+            for causal in (False, True):
+                B, H = 8, 16
+                g = torch.Generator(device=dev).manual_seed(7)
+                q, k, v = (torch.randn(B, S, H, D, generator=g, device=dev, dtype=torch.bfloat16) for _ in range(3))
+                Q, K, V = fa.quantize_qkv_fused(q, k, v, linear_sf=False)
+                del q, k, v
+                out = torch.empty(B, S, H, D, dtype=torch.bfloat16, device=dev)
+                lse = torch.empty(B, H, S, dtype=torch.float32, device=dev)
+
+                def step():
+                    fa.flash_attn_fp4_func(Q.data, K.data, V.data, Q.sf, K.sf, V.sf, Q.scale, K.scale, V.scale,
+                                           causal=causal, return_lse=True, out=out, lse=lse, sf_layout="tiled")
+                for _ in range(3):
+                    step()
+                torch.cuda.synchronize()
+                ms = 0.0
+                for _ in range(steps):
+                    flush.zero_()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record(); step(); e1.record(); e1.synchronize()
+                    ms += e0.elapsed_time(e1)
+                ms /= steps
+                fa.check_status(dev)
+                fl, by = flops_of(B, H, S, D, causal), algorithmic_bytes(B, H, H, S, D)
+                rows.append({"D": D, "S": S, "causal": causal, "ms": ms, "tflops": fl / ms / 1e9,
+                             "pct_fp4_peak_nominal": 100 * fl / ms / 1e9 / FP4_NOMINAL_TFLOPS,
+                             "frac_of_4x_bf16_measured": fl / ms / 1e9 / (4 * peaks["bf16_tflops"]),
+                             "hbm_gbs": by / ms / 1e6, "frac_of_hbm_peak": by / ms / 1e6 / peaks["hbm_gbs"]})
+                del Q, K, V, out, lse
+    head = next(r for r in rows if r["D"] == 128 and r["S"] == 4096 and r["causal"])
+    print(json.dumps({"metric": "nvfp4_attn_fwd_tflops", "value": head["tflops"], "unit": "TFLOP/s",
+                      "n_gpus": 1, "steps": steps, "warmup": 3, "ms_per_step": head["ms"],
+                      "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4",
+                      "data": "synthetic",
+                      "config": {"workload": "sweep: D in {64, 128} x S in {1024, 2048, 4096, 16384} x causal / "
+                                             "non-causal, B = 8, H = 16 (B * H = 128); headline row D=128, "
+                                             "S=4096, causal; D = 192 is not built",
+                                 "l2": "L2 flushed between timed launches (256 MiB write)"},
+                      "gpu_launches": steps * len(rows), "sweep": rows}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -371,6 +424,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
+    if args.workload == "sweep":
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device (no CPU fallback)")
+        return run_sweep(args)
     wl = parse_workload(args.workload)
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

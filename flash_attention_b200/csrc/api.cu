@@ -57,7 +57,7 @@ int ensure_smem(Kernel kernel, uint32_t bytes) {
 }  // namespace
 
 extern "C" int fa4_nvfp4_query(int32_t what) {
-  static const int dims[] = {128};
+  static const int dims[] = {128, 64};
   switch (what) {
     case 0: return FA4_NVFP4_ABI_VERSION;
     case 1: return (int)(sizeof(dims) / sizeof(dims[0]));
@@ -74,7 +74,7 @@ extern "C" int fa4_nvfp4_fwd(const fa4_nvfp4_params* p, void* cuda_stream) {
   if (!p->q || !p->k || !p->v || !p->q_sf || !p->k_sf || !p->v_sf || !p->out) return -FA4_E_NULL;
   if (p->B <= 0 || p->Sq <= 0 || p->Sk <= 0 || p->Hq <= 0 || p->Hkv <= 0) return -FA4_E_SHAPE;
   if (p->Hq % p->Hkv != 0) return -FA4_E_SHAPE;
-  if (p->D != 128 || p->Dv != 128) return -FA4_E_SHAPE;
+  if (p->D != p->Dv || (p->D != 128 && p->D != 64)) return -FA4_E_SHAPE;
   // keys are blocked by 16 along Sk (V / P scales) and V rows are Sk/2 bytes with a 16-byte
   // stride rule for TMA: Sk must be a multiple of 32; Sq is free
   if (p->Sk % 32 != 0) return -FA4_E_SHAPE;
@@ -90,20 +90,23 @@ extern "C" int fa4_nvfp4_fwd(const fa4_nvfp4_params* p, void* cuda_stream) {
   if ((p->o_stride_b & 7) || (p->o_stride_s & 7) || (p->o_stride_h & 7)) return -FA4_E_STRIDE;
   int variant = p->variant == FA4_VARIANT_AUTO ? FA4_VARIANT_WS : p->variant;
   if (variant != FA4_VARIANT_SERIAL && variant != FA4_VARIANT_WS) return -FA4_E_VARIANT;
+  if (variant == FA4_VARIANT_SERIAL && p->D != 128) return -FA4_E_SHAPE;  // bring-up kernel: 128 only
 
   CUtensorMap tm_q, tm_k, tm_v;
   {
     const uint64_t dq[4] = {(uint64_t)p->D / 2, (uint64_t)p->Hq, (uint64_t)p->Sq, (uint64_t)p->B};
     const uint64_t sq[3] = {(uint64_t)p->q_stride_h, (uint64_t)p->q_stride_s, (uint64_t)p->q_stride_b};
-    const uint32_t bq[4] = {64, 1, (uint32_t)kBlockM, 1};
+    const uint32_t bq[4] = {(uint32_t)p->D / 2, 1, (uint32_t)kBlockM, 1};
     const uint64_t dk[4] = {(uint64_t)p->D / 2, (uint64_t)p->Hkv, (uint64_t)p->Sk, (uint64_t)p->B};
     const uint64_t sk[3] = {(uint64_t)p->k_stride_h, (uint64_t)p->k_stride_s, (uint64_t)p->k_stride_b};
-    const uint32_t bk[4] = {64, 1, (uint32_t)kBlockN, 1};
+    const uint32_t bk[4] = {(uint32_t)p->D / 2, 1, (uint32_t)kBlockN, 1};
     const uint64_t dv[4] = {(uint64_t)p->Sk / 2, (uint64_t)p->Dv, (uint64_t)p->Hkv, (uint64_t)p->B};
     const uint64_t sv[3] = {(uint64_t)p->v_stride_d, (uint64_t)p->v_stride_h, (uint64_t)p->v_stride_b};
-    const uint32_t bv[4] = {64, 128, 1, 1};
-    if (!encode_u8_4d(&tm_q, p->q, dq, sq, bq, CU_TENSOR_MAP_SWIZZLE_64B) ||
-        !encode_u8_4d(&tm_k, p->k, dk, sk, bk, CU_TENSOR_MAP_SWIZZLE_64B) ||
+    const uint32_t bv[4] = {64, (uint32_t)p->Dv, 1, 1};
+    // a Q / K tile row is D / 2 bytes: 64-byte swizzle for D = 128, 32-byte for D = 64
+    const CUtensorMapSwizzle sw_qk = p->D == 128 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
+    if (!encode_u8_4d(&tm_q, p->q, dq, sq, bq, sw_qk) ||
+        !encode_u8_4d(&tm_k, p->k, dk, sk, bk, sw_qk) ||
         !encode_u8_4d(&tm_v, p->v, dv, sv, bv, CU_TENSOR_MAP_SWIZZLE_64B))
       return -FA4_E_TENSORMAP;
   }
@@ -147,8 +150,13 @@ extern "C" int fa4_nvfp4_fwd(const fa4_nvfp4_params* p, void* cuda_stream) {
     if (ce == cudaSuccess) ce = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (ce != cudaSuccess) return (int)ce;
     const unsigned grid = tiles < (unsigned)sms ? tiles : (unsigned)sms;
-    if (int e = ensure_smem(attn_fwd_ws_kernel, ws::kSmemRequest)) return e;
-    attn_fwd_ws_kernel<<<grid, ws::kThreads, ws::kSmemRequest, stream>>>(tm_q, tm_k, tm_v, kp);
+    if (p->D == 128) {
+      if (int e = ensure_smem(attn_fwd_ws_kernel<128>, ws::kSmemRequest)) return e;
+      attn_fwd_ws_kernel<128><<<grid, ws::kThreads, ws::kSmemRequest, stream>>>(tm_q, tm_k, tm_v, kp);
+    } else {
+      if (int e = ensure_smem(attn_fwd_ws_kernel<64>, ws::kSmemRequest)) return e;
+      attn_fwd_ws_kernel<64><<<grid, ws::kThreads, ws::kSmemRequest, stream>>>(tm_q, tm_k, tm_v, kp);
+    }
   }
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : (int)e;

@@ -196,11 +196,13 @@ __device__ __noinline__ void mask_scores_in_tmem(uint32_t taddr, int limit) {
 // overwritten: arrive on o_free_bar), scaled, rounded to bf16 and stored.  o_free_bar == 0: the
 // tile had no visible key, nothing to read, zeros are stored.
 __device__ __noinline__ void store_accumulator_chunk(uint32_t taddr, __nv_bfloat16* dst, float scale,
-                                                     uint32_t o_free_bar) {
+                                                     uint32_t o_free_bar, bool has_columns) {
   uint32_t o[32];
   if (o_free_bar != 0u) {
-    tmem_ld32(taddr, o);
-    tc_wait_ld();
+    if (has_columns) {  // warp-uniform
+      tmem_ld32(taddr, o);
+      tc_wait_ld();
+    }
     tc_fence_before_sync();
     mbar_arrive(o_free_bar);
   }
@@ -217,8 +219,23 @@ __device__ __forceinline__ int tile_of_round(int it, int cta, int ncta) {
   return it * ncta + ((it & 1) ? (ncta - 1 - cta) : cta);
 }
 
+// Shared-memory descriptor of 64-element step j of a Q or K tile (128 rows of kD / 2 bytes).
+template <int kD>
+__device__ __forceinline__ uint64_t make_desc_qk(uint32_t tile_addr, int j) {
+  if constexpr (kD == 128) {
+    return make_desc_sw64(tile_addr + 32 * j);
+  } else {
+    return make_desc_sw32(tile_addr);
+  }
+}
+
 }  // namespace ws
 
+// kD: head dimension of Q, K and V (128 or 64).  It sets the number of 64-element steps of
+// Q K^T, the width of O (tensor-memory columns, N of the P V instruction), the rows of a V tile and
+// the bytes of a Q / K tile (128 rows of kD / 2 bytes: 64-byte-swizzled rows for 128, 32-byte for
+// 64); the shared-memory slots keep the size of the larger case.
+template <int kD>
 __global__ void __launch_bounds__(ws::kThreads, 1)
 attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
                    const __grid_constant__ CUtensorMap tm_k,
@@ -272,7 +289,13 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
-  constexpr uint32_t idesc = make_idesc_nvf4(128, 128);
+  static_assert(kD == 128 || kD == 64, "head dimensions built: 128 and 64");
+  constexpr uint32_t idesc_qk = make_idesc_nvf4(128, 128);
+  constexpr uint32_t idesc_pv = make_idesc_nvf4(128, kD);
+  constexpr int kSteps = kD / 64;                      // 64-element steps of Q K^T
+  constexpr uint32_t kQkBytes = 128u * kD / 2;         // bytes of a Q or K tile
+  constexpr uint32_t kQkSfBytes = kSteps * 512u;       // its scale chunks (128 rows x kD / 16)
+  constexpr uint32_t kVBytes = kD * 64u;               // V tile: kD rows of 128 keys
   FA4_TRACE_DECL
   FA4_TRACE_EV(0, 0);
 
@@ -304,12 +327,12 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
           ok = mbar_wait(bars.at(Bars::kQEmpty + qb), ((ti - 2) >> 1) & 1, wc, kSiteQEmpty);
           if (!ok) break;
         }
-        mbar_arrive_expect_tx(bars.at(Bars::kQFull + qb), kTileBytes + kSfBytes);
+        mbar_arrive_expect_tx(bars.at(Bars::kQFull + qb), kQkBytes + kQkSfBytes);
         tma_load_4d(base + kOffQ + qb * kTileBytes, &tm_q, bars.at(Bars::kQFull + qb), 0, t.h,
                     t.m_blk * kBlockM, t.b);
         bulk_load(base + kOffSFQ + qb * kSfBytes,
-                  p.q_sf + t.b * p.qsf_stride_b + t.h * p.qsf_stride_h + (int64_t)t.m_blk * kSfBytes,
-                  kSfBytes, bars.at(Bars::kQFull + qb));
+                  p.q_sf + t.b * p.qsf_stride_b + t.h * p.qsf_stride_h + (int64_t)t.m_blk * kQkSfBytes,
+                  kQkSfBytes, bars.at(Bars::kQFull + qb));
         issued_q = ti + 1;
         const uint8_t* ksf = p.k_sf + t.b * p.ksf_stride_b + t.hk * p.ksf_stride_h;
         const uint8_t* vsf = p.v_sf + t.b * p.vsf_stride_b + t.hk * p.vsf_stride_h;
@@ -325,10 +348,10 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
               ok = mbar_wait(bars.at(Bars::kSFull + (j % kStagesK)), (j / kStagesK) & 1, wc, kSiteKEmpty);
               if (!ok) break;
             }
-            mbar_arrive_expect_tx(bars.at(Bars::kKFull + st), kTileBytes + kSfBytes);
+            mbar_arrive_expect_tx(bars.at(Bars::kKFull + st), kQkBytes + kQkSfBytes);
             tma_load_4d(base + kOffK + st * kTileBytes, &tm_k, bars.at(Bars::kKFull + st), 0, t.hk,
                         nb * kBlockN, t.b);
-            bulk_load(base + kOffSFK + st * kSfBytes, ksf + (int64_t)nb * kSfBytes, kSfBytes,
+            bulk_load(base + kOffSFK + st * kSfBytes, ksf + (int64_t)nb * kQkSfBytes, kQkSfBytes,
                       bars.at(Bars::kKFull + st));
             issued_k = G + 1;
           }
@@ -340,7 +363,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
               ok = mbar_wait(bars.at(Bars::kPvDone + (j % kStagesV)), (j / kStagesV) & 1, wc, kSiteVEmpty);
               if (!ok) break;
             }
-            mbar_arrive_expect_tx(bars.at(Bars::kVFull + st), kTileBytes + kSfBytes);
+            mbar_arrive_expect_tx(bars.at(Bars::kVFull + st), kVBytes + kSfBytes);
             tma_load_4d(base + kOffV + st * kTileBytes, &tm_v, bars.at(Bars::kVFull + st),
                         nb * (kBlockN / 2), 0, t.hk, t.b);
             bulk_load(base + kOffSFV + st * kSfBytes, vsf + (int64_t)nb * kSfBytes, kSfBytes,
@@ -381,10 +404,12 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         ok = mbar_wait(bars.at(Bars::kQFull + qb), (ti >> 1) & 1, wc, kSiteQFull);
         if (!ok) break;
         tc_fence_after_sync();
-        tc_cp_sf(tmem + kTmSFQ, base + kOffSFQ + qb * kSfBytes);
-        tc_cp_sf(tmem + kTmSFQ + 4, base + kOffSFQ + qb * kSfBytes + 512);
-        const uint64_t dq0 = make_desc_sw64(base + kOffQ + qb * kTileBytes);
-        const uint64_t dq1 = make_desc_sw64(base + kOffQ + qb * kTileBytes + 32);
+        uint64_t dq[kSteps];
+#pragma unroll
+        for (int j = 0; j < kSteps; ++j) {
+          tc_cp_sf(tmem + kTmSFQ + 4 * j, base + kOffSFQ + qb * kSfBytes + 512 * j);
+          dq[j] = make_desc_qk<kD>(base + kOffQ + qb * kTileBytes, j);
+        }
         for (int i = 0; i < n; ++i) {
           const uint32_t G = gb + i, st = G % kStagesK, b = G & 1;
           if (G >= 2) {
@@ -398,11 +423,14 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
           tc_fence_after_sync();
           const uint32_t sfk = tmem + kTmSFK + 8 * b;
           const uint32_t ksf = base + kOffSFK + st * kSfBytes, kt = base + kOffK + st * kTileBytes;
-          tc_cp_sf(sfk, ksf);
-          tc_cp_sf(sfk + 4, ksf + 512);
           const uint32_t s_tm = tmem + (b ? kTmS1 : kTmS0);
-          mma_nvf4(s_tm, dq0, make_desc_sw64(kt), idesc, tmem + kTmSFQ, sfk, 0u);
-          mma_nvf4(s_tm, dq1, make_desc_sw64(kt + 32), idesc, tmem + kTmSFQ + 4, sfk + 4, 1u);
+#pragma unroll
+          for (int j = 0; j < kSteps; ++j) tc_cp_sf(sfk + 4 * j, ksf + 512 * j);
+#pragma unroll
+          for (int j = 0; j < kSteps; ++j) {
+            mma_nvf4(s_tm, dq[j], make_desc_qk<kD>(kt, j), idesc_qk, tmem + kTmSFQ + 4 * j, sfk + 4 * j,
+                     j > 0 ? 1u : 0u);
+          }
           tc_commit(bars.at(Bars::kSFull + st));
           FA4_TRACE_EV(27, G);
         }
@@ -446,11 +474,11 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
           const uint32_t pt = base + kOffP + ps * kTileBytes, vt = base + kOffV + st * kTileBytes;
           tc_cp_sf(sfp, psf);
           tc_cp_sf(sfv, vsf);
-          mma_nvf4(tmem + kTmO, make_desc_sw64(pt), make_desc_sw64(vt), idesc, sfp, sfv,
+          mma_nvf4(tmem + kTmO, make_desc_sw64(pt), make_desc_sw64(vt), idesc_pv, sfp, sfv,
                    i > 0 ? 1u : 0u);
           tc_cp_sf(sfp + 4, psf + 512);
           tc_cp_sf(sfv + 4, vsf + 512);
-          mma_nvf4(tmem + kTmO, make_desc_sw64(pt + 32), make_desc_sw64(vt + 32), idesc, sfp + 4,
+          mma_nvf4(tmem + kTmO, make_desc_sw64(pt + 32), make_desc_sw64(vt + 32), idesc_pv, sfp + 4,
                    sfv + 4, 1u);
           tc_commit(bars.at(Bars::kPvDone + st));
           FA4_TRACE_EV(23, G);
@@ -638,7 +666,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
           if (!ok) break;
           tc_fence_after_sync();
           const float f = (m_new != m_prev) ? reference_factor(m_prev, m_new, p.sl2) : 1.f;
-          rescale_accumulator(lane_addr + kTmO + 64 * half, f, 2);
+          rescale_accumulator(lane_addr + kTmO + (kD / 2) * half, f, kD / 64);
           tc_wait_st();
         }
         fence_proxy_async_smem();
@@ -681,8 +709,9 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         tc_fence_after_sync();
         scale = (l_tot > 0.f) ? p.out_scale / l_tot : 0.f;
       }
-      store_accumulator_chunk(lane_addr + kTmO + 32 * wg, q_idx < p.Sq ? orow : nullptr, scale,
-                              n > 0 ? bars.at(Bars::kOFree) : 0u);
+      // warpgroup k stores output columns [32 k, 32 k + 32); with kD = 64 two of them only arrive
+      store_accumulator_chunk(lane_addr + kTmO + 32 * wg, (q_idx < p.Sq && 32 * wg < kD) ? orow : nullptr,
+                              scale, n > 0 ? bars.at(Bars::kOFree) : 0u, 32 * wg < kD);
       if (wg == 0 && p.lse != nullptr && q_idx < p.Sq) {
         p.lse[((int64_t)t.b * p.Hq + t.h) * p.Sq + q_idx] = finish_lse(m_fin, l_tot, p.sl2);
       }

@@ -205,6 +205,15 @@ __device__ __forceinline__ uint64_t make_desc_sw64(uint32_t saddr) {
   return d;
 }
 
+// Rows of 32 bytes (one 64-element step), 32-byte swizzle, 8-row groups 256 bytes apart.
+__device__ __forceinline__ uint64_t make_desc_sw32(uint32_t saddr) {
+  constexpr uint32_t hi = (256u >> 4) | (1u << 14) | (kSwizzle32 << 29);
+  const uint32_t lo = ((saddr >> 4) & 0x3fffu) | (1u << 16);
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+  return d;
+}
+
 // Instruction descriptor of kind::mxf4nvf4 (e2m1 x e2m1, ue4m3 scales of 16-element blocks,
 // fp32 accumulate, both operands K-major, K = 64 per instruction):
 //   [7,10) A format (1 = e2m1), [10,13) B format, [15] A major, [16] B major (0 = K),

@@ -101,7 +101,7 @@ def flash_attn_fp4_func(
     to the tiled layout by a small kernel; ``"tiled"``: already (B,H,ceil(rows/128),column tiles,512), see ``sf_to_tiled``.
     *_scale: fp32 per-tensor scales.  Returns ``(out bf16 (B,Sq,Hq,Dv), lse fp32 (B,Hq,Sq) | None)``.
 
-    Built so far: D = Dv = 128; any Sq; Sk a multiple of 32 (partial last tiles are handled by
+    Built so far: D = Dv = 128 or 64; any Sq; Sk a multiple of 32 (partial last tiles are handled by
     zero-filled loads, a key-length mask and unstored rows).  Anything else raises
     ``NotImplementedError`` before a launch.
     """
@@ -118,8 +118,10 @@ def flash_attn_fp4_func(
     assert Dhk == Dh, "q and k head dims differ"
     assert Hv == Hkv and Skh * 2 == Sk, f"v must be (B, Hkv, Dv, Sk/2), got {tuple(v.shape)}"
     assert Hq % Hkv == 0, "num_head must be divisible by num_head_kv"
-    if D != 128 or Dv != 128:
-        raise NotImplementedError(f"head dims (D={D}, Dv={Dv}) not built; supported: (128, 128)")
+    if D != Dv or D not in (64, 128):
+        raise NotImplementedError(f"head dims (D={D}, Dv={Dv}) not built; supported: (128, 128) and (64, 64)")
+    if D != 128 and variant == VARIANT_SERIAL:
+        raise NotImplementedError("the serial bring-up variant is built for head dim 128 only")
     if Sk % 32 != 0:
         raise NotImplementedError("seqlen_k must be a multiple of 32 (16-key scale blocks, 16-byte rows of V)")
     device = q.device
@@ -134,7 +136,7 @@ def flash_attn_fp4_func(
     elif sf_layout == "tiled":
         _validate_tensor(q_sf, "q_sf", (B, Hq, (Sq + 127) // 128, D // 64, 512), torch.uint8, device)
         _validate_tensor(k_sf, "k_sf", (B, Hkv, (Sk + 127) // 128, D // 64, 512), torch.uint8, device)
-        _validate_tensor(v_sf, "v_sf", (B, Hkv, Dv // 128, 2 * ((Sk + 127) // 128), 512), torch.uint8, device)
+        _validate_tensor(v_sf, "v_sf", (B, Hkv, (Dv + 127) // 128, 2 * ((Sk + 127) // 128), 512), torch.uint8, device)
         assert q_sf.is_contiguous() and k_sf.is_contiguous() and v_sf.is_contiguous()
     else:
         raise ValueError(f"sf_layout must be 'linear' or 'tiled', got {sf_layout!r}")

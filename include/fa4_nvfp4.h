@@ -105,6 +105,10 @@ typedef struct fa4_nvfp4_params {
  * NVFP4 attention forward.  Replaces the compiled-kernel call of the reference
  * (flash_attn/cute/interface.py:785-803).  Asynchronous on `cuda_stream`
  * (a cudaStream_t; NULL = legacy default stream), no host synchronisation.
+ * Shapes built: D == Dv in {128, 64} (the reference's table is
+ * flash_attn/cute/interface.py:84-99; fa4_nvfp4_query lists them), any Sq,
+ * Sk a multiple of 32, Hq a multiple of Hkv; everything else returns -FA4_E_SHAPE.
+ * FA4_VARIANT_SERIAL (the bring-up kernel) exists for D = 128 only.
  */
 int fa4_nvfp4_fwd(const fa4_nvfp4_params* p, void* cuda_stream);
 

@@ -295,3 +295,30 @@ def test_long_context_outlier_config_sampled_rows_and_head_split(cuda_device):
     Vs = fa.NVFP4Tensor(Vl.data[:, 5:6], Vl.sf[:, 5:6], Vl.scale, is_v=True)
     o1, l1 = fa.flash_attn_func(Qs, Ks, Vs, causal=True, return_lse=True)
     assert torch.equal(o1, out[:, :, g0:g1]) and torch.equal(l1, lse[:, g0:g1])
+
+
+CASES_D64 = [
+    # name, B, Sq, Sk, Hq, Hkv, causal
+    ("d64_noncausal", 1, 256, 256, 4, 4, False),
+    ("d64_causal_gqa", 2, 384, 384, 4, 2, True),
+    ("d64_causal_sq_gt_sk_masked_rows", 1, 384, 128, 2, 2, True),
+    ("d64_ragged_causal_sq_lt_sk", 1, 200, 352, 4, 1, True),
+]
+
+
+@pytest.mark.parametrize("case", CASES_D64, ids=[c[0] for c in CASES_D64])
+def test_parity_with_oracle_head_dim_64(cuda_device, case):
+    """Head dim 64 (the sweep configuration): one 64-element step of Q K^T on 32-byte-swizzled
+    tiles, 64 output columns.  Both quantisers feed it."""
+    _, B, Sq, Sk, Hq, Hkv, causal = case
+    q, k, v = make_qkv(B, Sq, Sk, Hq, Hkv, 64, seed=5, device=cuda_device)
+    Q, K, V = fa.quantize_qkv(q, k, v)
+    out, lse = run(Q, K, V, causal, fa.VARIANT_WS)
+    assert out.dtype == torch.bfloat16 and out.shape == (B, Sq, Hq, 64)
+    assert_parity(out, lse, *oracles(Q, K, V, causal))
+    if Sk % 16 == 0:
+        Qf, Kf, Vf = fa.quantize_qkv_fused(q, k, v)
+        out_f, lse_f = fa.flash_attn_func(Qf, Kf, Vf, causal=causal, return_lse=True)
+        assert_parity(out_f, lse_f, *oracles(Qf, Kf, Vf, causal))
+    with pytest.raises(NotImplementedError):
+        run(Q, K, V, causal, fa.VARIANT_SERIAL)
