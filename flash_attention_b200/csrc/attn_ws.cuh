@@ -9,7 +9,8 @@
 //               exponentials, P -> e2m1, row sums, O correction, epilogue
 //   warps 16-19 statistics warpgroup: for EVERY block, in order, reads S from tensor memory in
 //               32-column chunks, keeps the running reference maximum of each row and publishes
-//               the per-block exponents (softmax.cuh block_exponents) in shared memory
+//               the block maxima and the reference in shared memory (the softmax threads derive
+//               the per-block exponents from them, softmax.cuh block_exponents4)
 //   warp 20     TMA producer: Q (double buffered across tiles), K and V rings, scale factors
 //   warp 21     QK^T issuer: tcgen05.cp of the Q/K scale factors and the block-scaled tcgen05.mma
 //               for S = Q K^T (two S buffers in tensor memory); owns tensor memory
@@ -111,10 +112,10 @@ static_assert(kRegsSoftmax > kRegsLaunch && kRegsOther < kRegsLaunch, "inc / dec
 
 // per-row record the statistics warpgroup publishes for one block
 struct alignas(16) RowStats {
-  float noff[8];   // exponent offsets of the 8 key blocks
-  uint32_t ue[2];  // packed (e + 127) bytes
-  float m_prev;    // reference maximum before this block (raw units)
-  float m_new;     // reference maximum from this block on
+  float bm[8];      // maxima of the 8 key blocks (raw units, masked keys excluded)
+  uint32_t pad[2];
+  float m_prev;     // reference maximum before this block (raw units)
+  float m_new;      // reference maximum from this block on
 };
 static_assert(sizeof(RowStats) == 48, "RowStats is read with 16-byte loads");
 
@@ -195,11 +196,12 @@ __device__ __noinline__ void mask_scores_in_tmem(uint32_t taddr, int limit) {
 // Tile end: 32 accumulator columns of this thread's row -> registers (then the accumulator may be
 // overwritten: arrive on o_free_bar), scaled, rounded to bf16 and stored.  o_free_bar == 0: the
 // tile had no visible key, nothing to read, zeros are stored.
+template <bool kHasColumns>
 __device__ __noinline__ void store_accumulator_chunk(uint32_t taddr, __nv_bfloat16* dst, float scale,
-                                                     uint32_t o_free_bar, bool has_columns) {
+                                                     uint32_t o_free_bar) {
   uint32_t o[32];
   if (o_free_bar != 0u) {
-    if (has_columns) {  // warp-uniform
+    if constexpr (kHasColumns) {
       tmem_ld32(taddr, o);
       tc_wait_ld();
     }
@@ -554,19 +556,20 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         const float m23 = fmax3(bm[3], bm[4], bm[5]);
         const float m_loc = fmax3(fmaxf(m01, m23), bm[6], bm[7]);
         const float m_new = next_reference(m_run, m_loc, p.sl2);
-        RowStats rs;
-        block_exponents(bm, m_new, p.sl2, rs.noff, rs.ue);
-        rs.m_prev = m_run;
-        rs.m_new = m_new;
+        // the exponents themselves are derived by the softmax threads, each for its own four
+        // blocks: this warpgroup is serial over all blocks of the CTA and publishes as early as
+        // it can
+        const float m_prev = m_run;
         m_run = m_new;
         // the slot is free once the softmax warpgroups of block G-2 have read it
         ok = wait_probed(r_f, bar_f, par_f, wc, kSiteStFree);
         if (!ok) break;
         uint4* dst = reinterpret_cast<uint4*>(&s_stats[b * 128 + row]);
-        const uint4* src = reinterpret_cast<const uint4*>(&rs);
-        dst[0] = src[0];
-        dst[1] = src[1];
-        dst[2] = src[2];
+        dst[0] = make_uint4(__float_as_uint(bm[0]), __float_as_uint(bm[1]), __float_as_uint(bm[2]),
+                            __float_as_uint(bm[3]));
+        dst[1] = make_uint4(__float_as_uint(bm[4]), __float_as_uint(bm[5]), __float_as_uint(bm[6]),
+                            __float_as_uint(bm[7]));
+        dst[2] = make_uint4(0u, 0u, __float_as_uint(m_prev), __float_as_uint(m_new));
         mbar_arrive(bars.at(Bars::kStReady + b));
         FA4_TRACE_EV(31, G);
       }
@@ -630,11 +633,15 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         ok = wait_probed(mbar_test(bar_r, par_r), bar_r, par_r, wc, kSiteStReady);
         if (!ok) break;
         const uint4* st_row = reinterpret_cast<const uint4*>(&s_stats[b * 128 + row]);
-        const uint4 v_noff = st_row[half];
+        const uint4 v_bm = st_row[half];
         const uint4 v_misc = st_row[2];
         mbar_arrive(bars.at(Bars::kStFree + b));
         const float m_prev = __uint_as_float(v_misc.z), m_new = __uint_as_float(v_misc.w);
-        const uint32_t ue = half ? v_misc.y : v_misc.x;
+        const float bm4[4] = {__uint_as_float(v_bm.x), __uint_as_float(v_bm.y), __uint_as_float(v_bm.z),
+                              __uint_as_float(v_bm.w)};
+        float noff4[4];
+        uint32_t ue;
+        block_exponents4(bm4, m_new, p.sl2, noff4, ue);
         // own partial row sum follows the reference
         if (m_new != m_ref) l_sum *= reference_factor(m_ref, m_new, p.sl2);
         m_ref = m_new;
@@ -646,10 +653,10 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         FA4_TRACE_EV(6, G);
         uint8_t* p_tile = gbase + kOffP + (G % kStagesP) * kTileBytes;
         uint4 chunk;
-        l_sum += quantize_pair(&s[0], __uint_as_float(v_noff.x), __uint_as_float(v_noff.y),
+        l_sum += quantize_pair(&s[0], noff4[0], noff4[1],
                                __byte_perm(ue, 0u, 0x4440u), __byte_perm(ue, 0u, 0x4441u), p.sl2, chunk);
         *reinterpret_cast<uint4*>(p_tile + sw64_offset(row, 2 * half)) = chunk;
-        l_sum += quantize_pair(&s[32], __uint_as_float(v_noff.z), __uint_as_float(v_noff.w),
+        l_sum += quantize_pair(&s[32], noff4[2], noff4[3],
                                __byte_perm(ue, 0u, 0x4442u), __byte_perm(ue, 0u, 0x4443u), p.sl2, chunk);
         *reinterpret_cast<uint4*>(p_tile + sw64_offset(row, 2 * half + 1)) = chunk;
         FA4_TRACE_EV(7, G);
@@ -710,8 +717,12 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         scale = (l_tot > 0.f) ? p.out_scale / l_tot : 0.f;
       }
       // warpgroup k stores output columns [32 k, 32 k + 32); with kD = 64 two of them only arrive
-      store_accumulator_chunk(lane_addr + kTmO + 32 * wg, (q_idx < p.Sq && 32 * wg < kD) ? orow : nullptr,
-                              scale, n > 0 ? bars.at(Bars::kOFree) : 0u, 32 * wg < kD);
+      if (kD == 128 || wg < kD / 32) {
+        store_accumulator_chunk<true>(lane_addr + kTmO + 32 * wg, q_idx < p.Sq ? orow : nullptr, scale,
+                                      n > 0 ? bars.at(Bars::kOFree) : 0u);
+      } else {
+        store_accumulator_chunk<false>(0u, nullptr, 0.f, n > 0 ? bars.at(Bars::kOFree) : 0u);
+      }
       if (wg == 0 && p.lse != nullptr && q_idx < p.Sq) {
         p.lse[((int64_t)t.b * p.Hq + t.h) * p.Sq + q_idx] = finish_lse(m_fin, l_tot, p.sl2);
       }

@@ -80,36 +80,40 @@ __device__ __forceinline__ float reference_factor(float m_from, float m_to, floa
   return (m_from == kNegInf) ? 0.f : ex2_approx((m_from - m_to) * sl2);
 }
 
-// Per-block exponents of one row (8 blocks of 16 keys) from the block maxima.
+// Per-block exponents of four neighbouring blocks of 16 keys (64 keys) from their maxima.
 //   noff[b]  the exponent offset of block b:  p'/2^e = 2^(s * sl2 + noff[b])
 //   ue[w]    4 bytes per word, byte k = e + 127 of block 4 w + k (e = block scale exponent)
 //
 // No cvt / ceil (both would sit on the XU pipe next to the exponentials): u = t + (1.5 * 2^23 +
 // 127) rounds t to the nearest integer (t already carries the +0.5 that turns rounding into
 // ceil) and leaves e + 127 in the low byte of u's bit pattern.
-__device__ __forceinline__ void block_exponents(const float (&bm)[8], float m_ref, float sl2,
-                                                float (&noff)[8], uint32_t (&ue)[2]) {
+__device__ __forceinline__ void block_exponents4(const float* bm, float m_ref, float sl2,
+                                                 float* noff, uint32_t& ue) {
   constexpr float kMagic = 12582912.f + 127.f;  // 1.5 * 2^23 + exponent bias
   const float msc = (m_ref == kNegInf) ? 0.f : m_ref * sl2;
   // t' = log2(block max of p') - log2 6 + (0.5 - tiny)
   const float c_t = static_cast<float>(kShift) - kLog2Of6 + 0.4999995f - msc;
   const float c_off = static_cast<float>(kShift) - msc;  // noff = c_off - e
-  uint32_t ubits[8];
+  uint32_t ubits[4];
 #pragma unroll
-  for (int b = 0; b < 8; ++b) {
+  for (int b = 0; b < 4; ++b) {
     float t = fmaf(bm[b], sl2, c_t);
     t = fmaxf(t, static_cast<float>(kEMin) - 0.4f);  // also catches -inf (fully masked block)
     const float u = t + kMagic;
     ubits[b] = __float_as_uint(u);
     noff[b] = c_off - (u - kMagic);
   }
-#pragma unroll
-  for (int w = 0; w < 2; ++w) {
-    uint32_t lo, hi;
-    asm("prmt.b32 %0, %1, %2, 0x0040;" : "=r"(lo) : "r"(ubits[4 * w]), "r"(ubits[4 * w + 1]));
-    asm("prmt.b32 %0, %1, %2, 0x0040;" : "=r"(hi) : "r"(ubits[4 * w + 2]), "r"(ubits[4 * w + 3]));
-    asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(ue[w]) : "r"(lo), "r"(hi));
-  }
+  uint32_t lo, hi;
+  asm("prmt.b32 %0, %1, %2, 0x0040;" : "=r"(lo) : "r"(ubits[0]), "r"(ubits[1]));
+  asm("prmt.b32 %0, %1, %2, 0x0040;" : "=r"(hi) : "r"(ubits[2]), "r"(ubits[3]));
+  asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(ue) : "r"(lo), "r"(hi));
+}
+
+// The same for a whole row of 128 keys (8 blocks, two words of exponent bytes).
+__device__ __forceinline__ void block_exponents(const float (&bm)[8], float m_ref, float sl2,
+                                                float (&noff)[8], uint32_t (&ue)[2]) {
+  block_exponents4(&bm[0], m_ref, sl2, &noff[0], ue[0]);
+  block_exponents4(&bm[4], m_ref, sl2, &noff[4], ue[1]);
 }
 
 // ue4m3 bytes of the block scales 2^e from the packed (e + 127) bytes: (e + 7) << 3.
