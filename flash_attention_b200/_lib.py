@@ -88,6 +88,11 @@ def lib() -> ctypes.CDLL:
             L = ctypes.CDLL(LIB_PATH)
             L.fa4_nvfp4_fwd.argtypes = [ctypes.POINTER(Params), ctypes.c_void_p]
             L.fa4_nvfp4_fwd.restype = ctypes.c_int
+            L.fa4_nvfp4_splitkv_workspace_bytes.argtypes = [ctypes.POINTER(Params), ctypes.c_int32]
+            L.fa4_nvfp4_splitkv_workspace_bytes.restype = ctypes.c_int64
+            L.fa4_nvfp4_fwd_splitkv.argtypes = [ctypes.POINTER(Params), ctypes.c_int32, ctypes.c_void_p,
+                                                ctypes.c_uint64, ctypes.c_void_p]
+            L.fa4_nvfp4_fwd_splitkv.restype = ctypes.c_int
             L.fa4_nvfp4_sf_linear_to_tiled.argtypes = [
                 ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
                 ctypes.c_int32, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int32,
@@ -121,7 +126,7 @@ def lib() -> ctypes.CDLL:
 EXPORTS = ["fa4_nvfp4_fwd", "fa4_nvfp4_sf_linear_to_tiled", "fa4_nvfp4_query",
            "fa4_nvfp4_debug_qk_tile", "fa4_nvfp4_debug_wait_expiry", "fa4_nvfp4_debug_mma_rate",
            "fa4_nvfp4_fwd_linear_sf_noalloc", "fa4_nvfp4_amax_bf16", "fa4_nvfp4_quantize_qk_bf16",
-           "fa4_nvfp4_quantize_v_bf16"]
+           "fa4_nvfp4_quantize_v_bf16", "fa4_nvfp4_splitkv_workspace_bytes", "fa4_nvfp4_fwd_splitkv"]
 
 
 def check(rc: int, what: str) -> None:

@@ -68,7 +68,35 @@ extern "C" int fa4_nvfp4_query(int32_t what) {
   }
 }
 
+namespace {
+int64_t splitkv_bytes(const fa4_nvfp4_params* p, int num_splits) {
+  // partial O (num_splits, B, Sq, Hq, Dv) fp32, then partial LSE (num_splits, B, Hq, Sq) fp32
+  return (int64_t)num_splits * p->B * p->Sq * p->Hq * ((int64_t)p->Dv + 1) * 4;
+}
+int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint64_t workspace_bytes,
+               void* cuda_stream);
+}  // namespace
+
 extern "C" int fa4_nvfp4_fwd(const fa4_nvfp4_params* p, void* cuda_stream) {
+  return launch_fwd(p, 1, nullptr, 0, cuda_stream);
+}
+
+extern "C" int64_t fa4_nvfp4_splitkv_workspace_bytes(const fa4_nvfp4_params* p, int32_t num_splits) {
+  if (p == nullptr || p->struct_size != sizeof(fa4_nvfp4_params)) return -FA4_E_STRUCT;
+  if (num_splits < 1 || num_splits > 128 || p->B <= 0 || p->Sq <= 0 || p->Hq <= 0 || p->Dv <= 0)
+    return -FA4_E_SHAPE;
+  return num_splits == 1 ? 0 : splitkv_bytes(p, num_splits);
+}
+
+extern "C" int fa4_nvfp4_fwd_splitkv(const fa4_nvfp4_params* p, int32_t num_splits, void* workspace,
+                                     uint64_t workspace_bytes, void* cuda_stream) {
+  if (num_splits < 1 || num_splits > 128) return -FA4_E_SHAPE;
+  return launch_fwd(p, num_splits, workspace, workspace_bytes, cuda_stream);
+}
+
+namespace {
+int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint64_t workspace_bytes,
+               void* cuda_stream) {
   if (p == nullptr) return -FA4_E_NULL;
   if (p->struct_size != sizeof(fa4_nvfp4_params)) return -FA4_E_STRUCT;
   if (!p->q || !p->k || !p->v || !p->q_sf || !p->k_sf || !p->v_sf || !p->out) return -FA4_E_NULL;
@@ -91,6 +119,14 @@ extern "C" int fa4_nvfp4_fwd(const fa4_nvfp4_params* p, void* cuda_stream) {
   int variant = p->variant == FA4_VARIANT_AUTO ? FA4_VARIANT_WS : p->variant;
   if (variant != FA4_VARIANT_SERIAL && variant != FA4_VARIANT_WS) return -FA4_E_VARIANT;
   if (variant == FA4_VARIANT_SERIAL && p->D != 128) return -FA4_E_SHAPE;  // bring-up kernel: 128 only
+  if (num_splits > 1) {
+    if (variant == FA4_VARIANT_SERIAL) return -FA4_E_VARIANT;
+    if (workspace == nullptr) return -FA4_E_NULL;
+    if (!aligned16(workspace)) return -FA4_E_ALIGN;
+    if (workspace_bytes < (uint64_t)splitkv_bytes(p, num_splits)) return -FA4_E_TOO_LARGE;
+    if ((int64_t)((p->Sq + kBlockM - 1) / kBlockM) * p->Hq * p->B * num_splits > 0x7fffffffLL)
+      return -FA4_E_SHAPE;
+  }
 
   CUtensorMap tm_q, tm_k, tm_v;
   {
@@ -137,9 +173,15 @@ extern "C" int fa4_nvfp4_fwd(const fa4_nvfp4_params* p, void* cuda_stream) {
   kp.sl2 = p->softmax_scale * p->q_scale * p->k_scale * 1.4426950408889634f;
   kp.out_scale = p->v_scale;
   kp.budget_ns = p->wait_budget_ns ? p->wait_budget_ns : kDefaultBudgetNs;
+  kp.num_splits = num_splits;
+  kp.Dv = p->Dv;
+  kp.o_partial = static_cast<float*>(workspace);
+  kp.lse_partial = num_splits > 1
+                       ? kp.o_partial + (int64_t)num_splits * p->B * p->Sq * p->Hq * p->Dv
+                       : nullptr;
 
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
-  const unsigned tiles = (unsigned)(kp.num_m_blocks * p->Hq * p->B);
+  const unsigned tiles = (unsigned)(kp.num_m_blocks * p->Hq * p->B * num_splits);
   if (variant == FA4_VARIANT_SERIAL) {
     if (int e = ensure_smem(attn_fwd_serial_kernel, serial::kSmemRequest)) return e;
     attn_fwd_serial_kernel<<<tiles, 128, serial::kSmemRequest, stream>>>(tm_q, tm_k, tm_v, kp);
@@ -150,17 +192,33 @@ extern "C" int fa4_nvfp4_fwd(const fa4_nvfp4_params* p, void* cuda_stream) {
     if (ce == cudaSuccess) ce = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (ce != cudaSuccess) return (int)ce;
     const unsigned grid = tiles < (unsigned)sms ? tiles : (unsigned)sms;
+    auto launch = [&](auto kernel) -> int {
+      if (int e = ensure_smem(kernel, ws::kSmemRequest)) return e;
+      kernel<<<grid, ws::kThreads, ws::kSmemRequest, stream>>>(tm_q, tm_k, tm_v, kp);
+      return 0;
+    };
+    int rc;
     if (p->D == 128) {
-      if (int e = ensure_smem(attn_fwd_ws_kernel<128>, ws::kSmemRequest)) return e;
-      attn_fwd_ws_kernel<128><<<grid, ws::kThreads, ws::kSmemRequest, stream>>>(tm_q, tm_k, tm_v, kp);
+      rc = num_splits > 1 ? launch(attn_fwd_ws_kernel<128, true>) : launch(attn_fwd_ws_kernel<128, false>);
     } else {
-      if (int e = ensure_smem(attn_fwd_ws_kernel<64>, ws::kSmemRequest)) return e;
-      attn_fwd_ws_kernel<64><<<grid, ws::kThreads, ws::kSmemRequest, stream>>>(tm_q, tm_k, tm_v, kp);
+      rc = num_splits > 1 ? launch(attn_fwd_ws_kernel<64, true>) : launch(attn_fwd_ws_kernel<64, false>);
     }
+    if (rc != 0) return rc;
   }
-  const cudaError_t e = cudaGetLastError();
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  if (num_splits > 1) {
+    const int64_t items = (int64_t)p->B * p->Sq * p->Hq * (p->Dv / 4);
+    int64_t blocks = (items + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    combine_splits_kernel<<<(unsigned)blocks, 256, 0, stream>>>(
+        kp.o_partial, kp.lse_partial, kp.out, kp.lse, num_splits, p->B, p->Sq, p->Hq, p->Dv,
+        kp.o_stride_b, kp.o_stride_s, kp.o_stride_h);
+    e = cudaGetLastError();
+  }
   return e == cudaSuccess ? 0 : (int)e;
 }
+}  // namespace
 
 extern "C" int fa4_nvfp4_sf_linear_to_tiled(const void* src, void* dst, int32_t n_outer,
                                             int32_t n_inner, int32_t rows, int32_t cols,

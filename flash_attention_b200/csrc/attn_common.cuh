@@ -26,6 +26,14 @@ struct KernelParams {
   float sl2;        // softmax_scale * q_scale * k_scale * log2(e)
   float out_scale;  // v_scale
   uint64_t budget_ns;
+  // split-KV (num_splits > 1): every (tile, split) pair is a work item that visits a contiguous
+  // share of the tile's K/V blocks and writes a normalised fp32 partial O and a partial LSE;
+  // combine_splits_kernel merges them (flash_attn/cute/interface.py:494-510,804-812 and
+  // flash_fwd_combine.py in the reference)
+  int num_splits;
+  float* o_partial;    // (num_splits, B, Sq, Hq, Dv) fp32
+  float* lse_partial;  // (num_splits, B, Hq, Sq) fp32
+  int Dv;
 };
 
 // Work tile of a CTA.  Tiles are ordered so that, for causal problems, the m-blocks with the
@@ -34,11 +42,21 @@ struct KernelParams {
 // kv head are neighbours, so that their K/V tiles are shared through L2.
 struct Tile {
   int m_blk, h, b, hk;
-  int n_blocks;  // number of K/V blocks this tile visits (0: every row is fully masked)
+  int n_blocks;  // number of K/V blocks this work item visits (0: nothing visible / empty split)
+  int nb_top;    // K/V block index of the first visited block; the i-th visited is nb_top - i
+  int split;
 };
 
+// kSplit = false: the work list is the tile list (num_splits == 1); kept as a compile-time
+// switch so that the common case carries none of the split arithmetic or registers.
+template <bool kSplit = false>
 __device__ __forceinline__ Tile decode_tile(const KernelParams& p, int tile_idx) {
   Tile t;
+  t.split = 0;
+  if constexpr (kSplit) {
+    t.split = tile_idx % p.num_splits;   // the splits of one tile are neighbours in the work list
+    tile_idx /= p.num_splits;
+  }
   const int per_m = p.Hq * p.B;
   const int m_rev = tile_idx / per_m;
   const int rem = tile_idx - m_rev * per_m;
@@ -55,7 +73,17 @@ __device__ __forceinline__ Tile decode_tile(const KernelParams& p, int tile_idx)
     if (last <= 0) nb = 0;
     n = nb < n ? nb : n;
   }
-  t.n_blocks = n;
+  if constexpr (kSplit) {
+    // visit order is last block first; split s takes visits [s * per, (s + 1) * per)
+    const int per = (n + p.num_splits - 1) / p.num_splits;
+    const int i0 = t.split * per < n ? t.split * per : n;
+    const int i1 = i0 + per < n ? i0 + per : n;
+    t.n_blocks = i1 - i0;
+    t.nb_top = n - 1 - i0;
+  } else {
+    t.n_blocks = n;
+    t.nb_top = n - 1;
+  }
   return t;
 }
 

@@ -215,6 +215,30 @@ __device__ __noinline__ void store_accumulator_chunk(uint32_t taddr, __nv_bfloat
   if (dst != nullptr) store_out_32(dst, o, scale);  // null: a row beyond Sq of a partial tile
 }
 
+// Split-KV flavour of the same step: the 32 columns go out as fp32 (normalised by this split's
+// row sum) into the partial-output workspace.
+__device__ __noinline__ void store_accumulator_partial(uint32_t taddr, float* dst, float scale,
+                                                       uint32_t o_free_bar) {
+  uint32_t o[32];
+  if (o_free_bar != 0u) {
+    tmem_ld32(taddr, o);
+    tc_wait_ld();
+    tc_fence_before_sync();
+    mbar_arrive(o_free_bar);
+  }
+  if (dst == nullptr) return;
+  float4* d4 = reinterpret_cast<float4*>(dst);
+#pragma unroll
+  for (int v = 0; v < 8; ++v) {
+    float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (scale != 0.f) {
+      w = make_float4(__uint_as_float(o[4 * v]) * scale, __uint_as_float(o[4 * v + 1]) * scale,
+                      __uint_as_float(o[4 * v + 2]) * scale, __uint_as_float(o[4 * v + 3]) * scale);
+    }
+    d4[v] = w;
+  }
+}
+
 // Tile visited by CTA `cta` in round `it`: rounds alternate direction so that, with tiles sorted
 // by decreasing work, every CTA gets about the same total.
 __device__ __forceinline__ int tile_of_round(int it, int cta, int ncta) {
@@ -237,7 +261,8 @@ __device__ __forceinline__ uint64_t make_desc_qk(uint32_t tile_addr, int j) {
 // Q K^T, the width of O (tensor-memory columns, N of the P V instruction), the rows of a V tile and
 // the bytes of a Q / K tile (128 rows of kD / 2 bytes: 64-byte-swizzled rows for 128, 32-byte for
 // 64); the shared-memory slots keep the size of the larger case.
-template <int kD>
+// kSplit: split-KV work list and fp32 partial outputs (num_splits > 1).
+template <int kD, bool kSplit>
 __global__ void __launch_bounds__(ws::kThreads, 1)
 attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
                    const __grid_constant__ CUtensorMap tm_k,
@@ -256,7 +281,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
   const int warp = tid >> 5;
   const int lane = tid & 31;
   const WaitCtx wc{s_abort, p.status, p.budget_ns};
-  const int num_tiles = p.num_m_blocks * p.Hq * p.B;
+  const int num_tiles = p.num_m_blocks * p.Hq * p.B * (kSplit ? p.num_splits : 1);
   const int ncta = gridDim.x, cta = blockIdx.x;
 
   if (tid == 0) {
@@ -317,7 +342,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
       // ========================================= TMA producer ===================================
       uint32_t issued_k = 0, issued_v = 0, issued_q = 0;
       FA4_FOR_EACH_TILE {
-        const Tile t = decode_tile(p, tile);
+        const Tile t = decode_tile<kSplit>(p, tile);
         const int n = t.n_blocks;
         if (n == 0) continue;
         if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
@@ -343,7 +368,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
           const int ik = step, iv = step - 2;
           if (ik < n) {
             const uint32_t G = gb + ik, st = G % kStagesK;
-            const int nb = n - 1 - ik;
+            const int nb = (kSplit ? t.nb_top : n - 1) - ik;
             // stage st is free once QK^T of block G - kStagesK has completed (its s_full phase)
             if (G >= kStagesK) {
               const uint32_t j = G - kStagesK;
@@ -359,7 +384,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
           }
           if (iv >= 0 && iv < n) {
             const uint32_t G = gb + iv, st = G % kStagesV;
-            const int nb = n - 1 - iv;
+            const int nb = (kSplit ? t.nb_top : n - 1) - iv;
             if (G >= kStagesV) {
               const uint32_t j = G - kStagesV;
               ok = mbar_wait(bars.at(Bars::kPvDone + (j % kStagesV)), (j / kStagesV) & 1, wc, kSiteVEmpty);
@@ -395,7 +420,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
     } else if (warp == kIssuerWarp && lane == 0) {
       // ========================================= QK^T issuer ====================================
       FA4_FOR_EACH_TILE {
-        const Tile t = decode_tile(p, tile);
+        const Tile t = decode_tile<kSplit>(p, tile);
         const int n = t.n_blocks;
         if (n == 0) continue;
         if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
@@ -450,7 +475,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
     } else if (warp == kPvIssuerWarp && lane == 0) {
       // ========================================= PV issuer ======================================
       FA4_FOR_EACH_TILE {
-        const Tile t = decode_tile(p, tile);
+        const Tile t = decode_tile<kSplit>(p, tile);
         const int n = t.n_blocks;
         if (n == 0) continue;
         if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
@@ -507,7 +532,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
     const int row = tid & 127;
     const uint32_t lane_addr = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     FA4_FOR_EACH_TILE {
-      const Tile t = decode_tile(p, tile);
+      const Tile t = decode_tile<kSplit>(p, tile);
       const int n = t.n_blocks;
       if (n == 0) continue;
       if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
@@ -517,7 +542,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
       float m_run = kNegInf;
       for (int i = 0; i < n; ++i) {
         const uint32_t G = gb + i, b = G & 1;
-        const int nb = n - 1 - i;
+        const int nb = (kSplit ? t.nb_top : n - 1) - i;
         const uint32_t bar_s = bars.at(Bars::kSFull + (G % kStagesK)), par_s = (G / kStagesK) & 1;
         const uint32_t bar_f = bars.at(Bars::kStFree + b), par_f = ((G - 2) >> 1) & 1;
         const bool r_s = mbar_test(bar_s, par_s);
@@ -587,7 +612,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
     const uint32_t lane_addr = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
 
     FA4_FOR_EACH_TILE {
-      const Tile t = decode_tile(p, tile);
+      const Tile t = decode_tile<kSplit>(p, tile);
       const int n = t.n_blocks;
       const bool poisoned =
           (p.status != nullptr) && (*reinterpret_cast<volatile uint32_t*>(p.status) != 0u);
@@ -599,7 +624,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
 
       for (int i = (g - gb) & 1; i < n; i += 2) {
         const uint32_t G = gb + i, b = G & 1;  // b == g: S / P / stats buffer of this block
-        const int nb = n - 1 - i;
+        const int nb = (kSplit ? t.nb_top : n - 1) - i;
         FA4_TRACE_EV(1, G);
         // Probe the three barriers this block depends on back to back so that their latencies
         // overlap; the blocking (bounded) wait only runs for a probe that failed.
@@ -717,14 +742,24 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         scale = (l_tot > 0.f) ? p.out_scale / l_tot : 0.f;
       }
       // warpgroup k stores output columns [32 k, 32 k + 32); with kD = 64 two of them only arrive
-      if (kD == 128 || wg < kD / 32) {
+      if (kSplit && (kD == 128 || wg < kD / 32)) {
+        float* prow = p.o_partial +
+                      ((((int64_t)t.split * p.B + t.b) * p.Sq + q_idx) * p.Hq + t.h) * kD + 32 * wg;
+        store_accumulator_partial(lane_addr + kTmO + 32 * wg, q_idx < p.Sq ? prow : nullptr, scale,
+                                  n > 0 ? bars.at(Bars::kOFree) : 0u);
+      } else if (kD == 128 || wg < kD / 32) {
         store_accumulator_chunk<true>(lane_addr + kTmO + 32 * wg, q_idx < p.Sq ? orow : nullptr, scale,
                                       n > 0 ? bars.at(Bars::kOFree) : 0u);
       } else {
         store_accumulator_chunk<false>(0u, nullptr, 0.f, n > 0 ? bars.at(Bars::kOFree) : 0u);
       }
-      if (wg == 0 && p.lse != nullptr && q_idx < p.Sq) {
-        p.lse[((int64_t)t.b * p.Hq + t.h) * p.Sq + q_idx] = finish_lse(m_fin, l_tot, p.sl2);
+      if (wg == 0 && q_idx < p.Sq) {
+        if (kSplit) {
+          p.lse_partial[(((int64_t)t.split * p.B + t.b) * p.Hq + t.h) * p.Sq + q_idx] =
+              finish_lse(m_fin, l_tot, p.sl2);
+        } else if (p.lse != nullptr) {
+          p.lse[((int64_t)t.b * p.Hq + t.h) * p.Sq + q_idx] = finish_lse(m_fin, l_tot, p.sl2);
+        }
       }
       FA4_TRACE_EV(42, gb);
       gb += n;

@@ -145,6 +145,55 @@ qk_tile_probe_kernel(const __grid_constant__ CUtensorMap tm_q,
 }
 
 // ---------------------------------------------------------------------------------------------
+// Split-KV combine (the reference's flash_fwd_combine.py; math of
+// tests/cute/test_flash_attn_fast.py:295-300): per output row
+//   lse = log sum_i exp(lse_i),   out = sum_i exp(lse_i - lse) * out_i
+// over the splits' normalised fp32 partial outputs.  One thread = four neighbouring columns of
+// one (batch, query, head) row; HBM-bound: reads num_splits * (Dv + 1) floats, writes Dv bf16.
+// ---------------------------------------------------------------------------------------------
+__global__ void combine_splits_kernel(const float* __restrict__ o_partial,
+                                      const float* __restrict__ lse_partial,
+                                      __nv_bfloat16* __restrict__ out, float* __restrict__ lse,
+                                      int num_splits, int B, int Sq, int Hq, int Dv,
+                                      int64_t o_stride_b, int64_t o_stride_s, int64_t o_stride_h) {
+  const int per_row = Dv / 4;
+  const int64_t rows = (int64_t)B * Sq * Hq;
+  const int64_t split_o = rows * Dv, split_l = rows;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < rows * per_row;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(idx % per_row);
+    const int64_t r = idx / per_row;  // (b, s, h) in the partial layout
+    const int h = (int)(r % Hq);
+    const int64_t bs = r / Hq;
+    const int s = (int)(bs % Sq), b = (int)(bs / Sq);
+    const int64_t l_idx = ((int64_t)b * Hq + h) * Sq + s;
+    float m = -INFINITY;
+    for (int i = 0; i < num_splits; ++i) m = fmaxf(m, lse_partial[i * split_l + l_idx]);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float sum = 0.f;
+    if (m != -INFINITY) {
+      for (int i = 0; i < num_splits; ++i) {
+        const float w = __expf(lse_partial[i * split_l + l_idx] - m);
+        const float4 v = *reinterpret_cast<const float4*>(o_partial + i * split_o + r * Dv + 4 * c);
+        sum += w;
+        acc.x = fmaf(w, v.x, acc.x);
+        acc.y = fmaf(w, v.y, acc.y);
+        acc.z = fmaf(w, v.z, acc.z);
+        acc.w = fmaf(w, v.w, acc.w);
+      }
+      const float inv = 1.f / sum;
+      acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
+    }
+    __nv_bfloat16* dst = out + b * o_stride_b + (int64_t)s * o_stride_s + h * o_stride_h + 4 * c;
+    uint2 pk;
+    pk.x = pack_bf16x2(acc.x, acc.y);
+    pk.y = pack_bf16x2(acc.z, acc.w);
+    *reinterpret_cast<uint2*>(dst) = pk;
+    if (c == 0 && lse != nullptr) lse[l_idx] = (m == -INFINITY) ? -INFINITY : m + __logf(sum);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // Tensor-pipe rate of the block-scaled e2m1 MMA (the denominator "measured FP4 peak"): every CTA
 // (one per SM) fills one A and one B tile and their scale chunks with pseudo-random bytes, then
 // one thread issues `iters` 128 x 128 x 64 instructions back to back, alternating between two

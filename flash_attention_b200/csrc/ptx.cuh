@@ -85,6 +85,9 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
 // One poll of a blocking wait: try_wait with a short suspend-time hint.  Measured against the
 // alternatives on the attention kernel: the default (system-chosen) suspend time was 2-3 % slower,
 // pure test_wait polling 4 % slower.
+#ifndef FA4_WAIT_HINT_NS
+#define FA4_WAIT_HINT_NS 64
+#endif
 __device__ __forceinline__ bool mbar_poll(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -94,7 +97,7 @@ __device__ __forceinline__ bool mbar_poll(uint32_t bar, uint32_t parity) {
       "selp.b32 %0, 1, 0, p;\n"
       "}\n"
       : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(64u)
+      : "r"(bar), "r"(parity), "r"((uint32_t)FA4_WAIT_HINT_NS)
       : "memory");
   return ok != 0;
 }

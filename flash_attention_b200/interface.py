@@ -93,6 +93,7 @@ def flash_attn_fp4_func(
     lse: Optional[torch.Tensor] = None,
     sf_layout: str = "linear",
     variant: int = VARIANT_AUTO,
+    num_splits: int = 1,
 ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
     """NVFP4 attention forward.
 
@@ -100,6 +101,10 @@ def flash_attn_fp4_func(
     *_sf: e4m3 block scales, ``sf_layout="linear"``: (B,S,H,D/16) / (B,Hkv,Dv,Sk/16), converted
     to the tiled layout by a small kernel; ``"tiled"``: already (B,H,ceil(rows/128),column tiles,512), see ``sf_to_tiled``.
     *_scale: fp32 per-tensor scales.  Returns ``(out bf16 (B,Sq,Hq,Dv), lse fp32 (B,Hq,Sq) | None)``.
+
+    ``num_splits``: 1 = one pass over K/V per query tile; k > 1 = split-KV with a combine kernel
+    (the reference's ``num_splits``, interface.py:494-510), for short Sq against long Sk;
+    0 = choose (split only when the query tiles alone leave most SMs idle).
 
     Built so far: D = Dv = 128 or 64; any Sq; Sk a multiple of 32 (partial last tiles are handled by
     zero-filled loads, a key-length mask and unstored rows).  Anything else raises
@@ -170,11 +175,49 @@ def flash_attn_fp4_func(
                                        _scalar(v_scale, "v_scale"))
     p.softmax_scale = float(softmax_scale)
     p.wait_budget_ns = 0
+    if num_splits < 0 or num_splits > 128:
+        raise ValueError("num_splits must be in 0..128")
+    if num_splits == 0:
+        num_splits = choose_num_splits(B, Sq, Sk, Hq, causal, device)
     with torch.cuda.device(device):
         stream = torch.cuda.current_stream(device).cuda_stream
-        rc = _lib.lib().fa4_nvfp4_fwd(ctypes.byref(p), stream)
-    _lib.check(rc, "fa4_nvfp4_fwd")
+        if num_splits == 1:
+            rc = _lib.lib().fa4_nvfp4_fwd(ctypes.byref(p), stream)
+            what = "fa4_nvfp4_fwd"
+        else:
+            nbytes = _lib.lib().fa4_nvfp4_splitkv_workspace_bytes(ctypes.byref(p), num_splits)
+            if nbytes < 0:
+                _lib.check(int(nbytes), "fa4_nvfp4_splitkv_workspace_bytes")
+            workspace = torch.empty(nbytes, dtype=torch.uint8, device=device)   # stream-ordered scratch
+            rc = _lib.lib().fa4_nvfp4_fwd_splitkv(ctypes.byref(p), num_splits, workspace.data_ptr(), nbytes,
+                                                  stream)
+            what = "fa4_nvfp4_fwd_splitkv"
+    _lib.check(rc, what)
     return out, lse
+
+
+def choose_num_splits(B: int, Sq: int, Sk: int, Hq: int, causal: bool, device) -> int:
+    """Split count for ``num_splits=0``.
+
+    1 unless the query tiles alone would leave more than half of the SMs idle.  Otherwise the
+    count that minimises (waves of work items over the SMs) x (K/V blocks per item + 2 blocks of
+    fixed cost per item), at least four blocks per split -- the efficiency search of the
+    reference's heuristic (flash_attn/cute/interface.py:494-510) on this kernel's cost model.
+    """
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    tiles = B * Hq * ((Sq + 127) // 128)
+    blocks = (Sk + 127) // 128          # the last query rows see every key, causal or not
+    if tiles * 2 > sms or blocks < 8:
+        return 1
+    best, best_cost = 1, None
+    for n in range(1, min(blocks // 4, 128) + 1):
+        per = (blocks + n - 1) // n
+        if n > 1 and per * (n - 1) >= blocks:
+            continue                      # the last split would be empty
+        cost = ((tiles * n + sms - 1) // sms) * (per + 2)
+        if best_cost is None or cost < best_cost:
+            best, best_cost = n, cost
+    return best
 
 
 def flash_attn_func(
@@ -209,8 +252,6 @@ def flash_attn_func(
         raise NotImplementedError("learnable_sink is not built")
     if softcap not in (0.0, None):
         raise NotImplementedError("softcap is not built")
-    if num_splits != 1:
-        raise NotImplementedError("split-KV is not built (num_splits must be 1)")
     if mask_mod is not None or any(t is not None for t in (full_block_cnt, full_block_idx,
                                                            mask_block_cnt, mask_block_idx)):
         raise NotImplementedError("mask_mod / block sparsity is not built")
@@ -220,7 +261,7 @@ def flash_attn_func(
     return flash_attn_fp4_func(
         q.data, k.data, v.data, q.sf, k.sf, v.sf, q.scale, k.scale, v.scale,
         softmax_scale=softmax_scale, causal=causal, return_lse=return_lse,
-        sf_layout="tiled" if q.tiled else "linear")
+        sf_layout="tiled" if q.tiled else "linear", num_splits=num_splits)
 
 
 def measure_fp4_mma_rate(iters: int = 1 << 16, device=None, repeats: int = 3) -> dict:

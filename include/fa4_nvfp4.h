@@ -113,6 +113,22 @@ typedef struct fa4_nvfp4_params {
 int fa4_nvfp4_fwd(const fa4_nvfp4_params* p, void* cuda_stream);
 
 /*
+ * The same forward with the K/V sequence split `num_splits` ways (1..128): the reference's
+ * num_splits path (flash_attn/cute/interface.py:494-510 heuristics, :804-812 combine call,
+ * flash_attn/cute/flash_fwd_combine.py).  Every (query tile, split) pair becomes a work item that
+ * visits a contiguous share of the tile's K/V blocks and writes a normalised fp32 partial output
+ * and a partial LSE into `workspace`; a second kernel on the same stream merges them
+ * (lse = log sum exp(lse_i), out = sum exp(lse_i - lse) out_i) into p->out / p->lse.  For short
+ * Sq (decode) this is what fills the GPU: without it there are only B * Hq * ceil(Sq/128) work
+ * items.  `workspace`: caller-owned device memory, 16-byte aligned, at least
+ * fa4_nvfp4_splitkv_workspace_bytes(p, num_splits) bytes (= num_splits * B * Sq * Hq * (Dv + 1)
+ * floats; 0 for num_splits = 1, in which case this is fa4_nvfp4_fwd).  WS variant only.
+ */
+int64_t fa4_nvfp4_splitkv_workspace_bytes(const fa4_nvfp4_params* p, int32_t num_splits);
+int fa4_nvfp4_fwd_splitkv(const fa4_nvfp4_params* p, int32_t num_splits, void* workspace,
+                          uint64_t workspace_bytes, void* cuda_stream);
+
+/*
  * Scale-factor layout conversion, linear -> tiled.
  *   src: rows x cols e4m3 bytes; element (r, c) of matrix m at
  *        src + m_outer*stride_outer + m_inner*stride_inner + r*stride_row + c

@@ -190,11 +190,16 @@ def quantize_p_block_model(x: torch.Tensor, m_ref: torch.Tensor):
     return p_hat.reshape(x.shape), p_sum
 
 
-def attention_oracle_b(qd, kd, vd, sl2: float, v_scale_out: float = 1.0, causal=False):
+def attention_oracle_b(qd, kd, vd, sl2: float, v_scale_out: float = 1.0, causal=False,
+                       num_splits: int = 1):
     """Kernel model.  qd (B,Sq,Hq,D), kd (B,Sk,Hkv,D), vd (B,Sk,Hkv,Dv): fp32 values the tensor
     core sees (e2m1 * block scale, WITHOUT the per-tensor scales); sl2 = softmax_scale * q_scale
     * k_scale * log2(e); v_scale_out = v_scale.  Walks the K/V blocks of 128 keys from the last
     visible one to the first with the lazy reference maximum, like the kernel.
+    num_splits > 1 models the split-KV path: the visited blocks of a tile are cut into
+    num_splits contiguous shares (ceil division, in visit order), each share starts from a fresh
+    reference maximum, and the shares are merged with exp(lse_i - lse) weights (the combine
+    step of the reference, tests/cute/test_flash_attn_fast.py:295-300).
     Returns (out fp32 (B,Sq,Hq,Dv) before bf16 rounding, lse (B,Hq,Sq))."""
     qd, kd, vd = (torch.as_tensor(t, dtype=torch.float32) for t in (qd, kd, vd))
     B, Sq, Hq, D = qd.shape
@@ -217,31 +222,49 @@ def attention_oracle_b(qd, kd, vd, sl2: float, v_scale_out: float = 1.0, causal=
                     last = m0 + 128 + Sk - Sq
                     n_blocks = min(n_blocks, max(0, (last + 127) // 128))
                     s_all[:, :Sk] = s_all[:, :Sk].masked_fill(_causal_mask(Sq, Sk)[rows], float("-inf"))
-                m_ref = torch.full((nr,), float("-inf"))
-                l_sum = torch.zeros(nr)
-                acc = torch.zeros(nr, Dv)
-                for nb in range(n_blocks - 1, -1, -1):
-                    s = s_all[:, nb * 128:(nb + 1) * 128]
-                    m_loc = s.amax(dim=-1)
-                    keep = torch.isfinite(m_ref) & ((m_loc - m_ref) * sl2 <= P_LAZY)
-                    m_new = torch.where(keep, m_ref, torch.maximum(m_ref, m_loc))
-                    f = torch.where(torch.isfinite(m_ref), torch.exp2((m_ref - m_new) * sl2),
-                                    torch.zeros(nr))
-                    f = torch.nan_to_num(f, nan=0.0)
-                    acc = acc * f[:, None]
-                    l_sum = l_sum * f
-                    m_ref = m_new
-                    msc = torch.where(torch.isfinite(m_ref), m_ref * sl2, torch.zeros(nr))
-                    p_hat, p_sum = quantize_p_block_model(s * sl2, msc[:, None])
-                    acc = acc + p_hat @ v_pad[nb * 128:(nb + 1) * 128]
-                    l_sum = l_sum + p_sum
-                ok = l_sum > 0
-                safe = torch.where(ok, l_sum, torch.ones(nr))
-                out[b, rows, h] = torch.where(ok[:, None], acc * (v_scale_out / safe)[:, None],
-                                              torch.zeros(nr, Dv))
-                lse[b, h, rows] = torch.where(
-                    ok, (m_ref * sl2 + torch.log2(safe) - P_SHIFT) * math.log(2.0),
-                    torch.full((nr,), float("-inf")))
+                visit = list(range(n_blocks - 1, -1, -1))
+                per = (len(visit) + num_splits - 1) // num_splits if visit else 0
+                parts = []
+                for sp in range(num_splits):
+                    share = visit[sp * per:(sp + 1) * per] if per else []
+                    m_ref = torch.full((nr,), float("-inf"))
+                    l_sum = torch.zeros(nr)
+                    acc = torch.zeros(nr, Dv)
+                    for nb in share:
+                        s = s_all[:, nb * 128:(nb + 1) * 128]
+                        m_loc = s.amax(dim=-1)
+                        keep = torch.isfinite(m_ref) & ((m_loc - m_ref) * sl2 <= P_LAZY)
+                        m_new = torch.where(keep, m_ref, torch.maximum(m_ref, m_loc))
+                        f = torch.where(torch.isfinite(m_ref), torch.exp2((m_ref - m_new) * sl2),
+                                        torch.zeros(nr))
+                        f = torch.nan_to_num(f, nan=0.0)
+                        acc = acc * f[:, None]
+                        l_sum = l_sum * f
+                        m_ref = m_new
+                        msc = torch.where(torch.isfinite(m_ref), m_ref * sl2, torch.zeros(nr))
+                        p_hat, p_sum = quantize_p_block_model(s * sl2, msc[:, None])
+                        acc = acc + p_hat @ v_pad[nb * 128:(nb + 1) * 128]
+                        l_sum = l_sum + p_sum
+                    ok = l_sum > 0
+                    safe = torch.where(ok, l_sum, torch.ones(nr))
+                    o_part = torch.where(ok[:, None], acc * (v_scale_out / safe)[:, None],
+                                         torch.zeros(nr, Dv))
+                    l_part = torch.where(
+                        ok, (m_ref * sl2 + torch.log2(safe) - P_SHIFT) * math.log(2.0),
+                        torch.full((nr,), float("-inf")))
+                    parts.append((o_part, l_part))
+                if num_splits == 1:
+                    out[b, rows, h], lse[b, h, rows] = parts[0]
+                else:
+                    l_all = torch.stack([lp for _, lp in parts])                # (splits, nr)
+                    m = l_all.amax(dim=0)
+                    fin = torch.isfinite(m)
+                    w = torch.where(fin[None], torch.exp(l_all - torch.where(fin, m, torch.zeros(nr))[None]),
+                                    torch.zeros_like(l_all))
+                    tot = torch.where(fin, w.sum(dim=0), torch.ones(nr))
+                    o = sum(w[i][:, None] * parts[i][0] for i in range(num_splits))
+                    out[b, rows, h] = torch.where(fin[:, None], o / tot[:, None], torch.zeros(nr, Dv))
+                    lse[b, h, rows] = torch.where(fin, m + torch.log(tot), torch.full((nr,), float("-inf")))
     return out, lse
 
 

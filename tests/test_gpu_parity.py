@@ -322,3 +322,43 @@ def test_parity_with_oracle_head_dim_64(cuda_device, case):
         assert_parity(out_f, lse_f, *oracles(Qf, Kf, Vf, causal))
     with pytest.raises(NotImplementedError):
         run(Q, K, V, causal, fa.VARIANT_SERIAL)
+
+
+CASES_SPLIT = [
+    # name, B, Sq, Sk, Hq, Hkv, D, causal, splits
+    ("decode_one_row", 2, 1, 2048, 8, 2, 128, True, 4),
+    ("decode_17_rows_noncausal", 1, 17, 1536, 4, 4, 128, False, 3),
+    ("short_prefill_causal", 1, 128, 2048, 4, 1, 128, True, 8),
+    ("more_splits_than_blocks", 1, 64, 384, 2, 2, 128, False, 5),
+    ("two_tiles_sq_gt_sk_masked_rows", 1, 384, 256, 2, 2, 128, True, 2),
+    ("d64_decode", 2, 8, 1024, 4, 2, 64, True, 4),
+]
+
+
+@pytest.mark.parametrize("case", CASES_SPLIT, ids=[c[0] for c in CASES_SPLIT])
+def test_split_kv_parity(cuda_device, case):
+    _, B, Sq, Sk, Hq, Hkv, D, causal, splits = case
+    q, k, v = make_qkv(B, Sq, Sk, Hq, Hkv, D, seed=9, device=cuda_device)
+    Q, K, V = fa.quantize_qkv(q, k, v)
+    out, lse = run(Q, K, V, causal, fa.VARIANT_WS, num_splits=splits)
+    assert out.shape == (B, Sq, Hq, D) and lse.shape == (B, Hq, Sq)
+    assert_parity(out, lse, *oracles(Q, K, V, causal, num_splits=splits))
+    # the un-split result agrees to within the 4-bit P noise of two different groupings
+    out1, lse1 = run(Q, K, V, causal, fa.VARIANT_WS)
+    fin = torch.isfinite(lse1)
+    assert torch.equal(fin, torch.isfinite(lse))
+    assert (lse[fin] - lse1[fin]).abs().max().item() < 1e-3
+    e = orc.error_metrics(out.float(), out1.float())
+    assert e["rel_rms"] < 0.2, e
+    with pytest.raises((ValueError, NotImplementedError)):      # the bring-up variant does not split
+        run(Q, K, V, causal, fa.VARIANT_SERIAL, num_splits=splits)
+
+
+def test_split_kv_heuristic_and_surface(cuda_device):
+    assert fa.interface.choose_num_splits(4, 8192, 8192, 32, True, cuda_device) == 1
+    n = fa.interface.choose_num_splits(1, 1, 32768, 8, True, cuda_device)
+    assert 8 <= n <= 64
+    q, k, v = make_qkv(1, 4, 4096, 8, 2, 128, seed=1, device=cuda_device)
+    Q, K, V = fa.quantize_qkv(q, k, v)
+    o0, l0 = fa.flash_attn_func(Q, K, V, causal=True, return_lse=True, num_splits=0)
+    assert_parity(o0, l0, *oracles(Q, K, V, True, num_splits=fa.interface.choose_num_splits(1, 4, 4096, 8, True, cuda_device)))

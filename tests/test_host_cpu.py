@@ -23,7 +23,7 @@ HEADER = os.path.join(ROOT, "include", "fa4_nvfp4.h")
 def test_library_exports_every_declared_symbol():
     L = fa.lib()
     text = open(HEADER).read()
-    declared = set(re.findall(r"^int\s+(fa4_nvfp4_\w+)\s*\(", text, flags=re.M))
+    declared = set(re.findall(r"^(?:int|int64_t)\s+(fa4_nvfp4_\w+)\s*\(", text, flags=re.M))
     assert declared, "no declarations found in the header"
     assert declared == set(_lib.EXPORTS) or declared >= set(_lib.EXPORTS)
     for name in declared:
@@ -122,7 +122,7 @@ def test_python_surface_errors_before_launch():
         fa.flash_attn_func(q, q, v)
     Q = fa.NVFP4Tensor(q, sf, 1.0)
     V = fa.NVFP4Tensor(v, vsf, 1.0, is_v=True)
-    for kw in ({"window_size": (128, 0)}, {"softcap": 30.0}, {"num_splits": 2},
+    for kw in ({"window_size": (128, 0)}, {"softcap": 30.0},
                {"learnable_sink": torch.zeros(2)}, {"mask_mod": lambda *a: True}):
         with pytest.raises(NotImplementedError):
             fa.flash_attn_func(Q, Q, V, **kw)
@@ -186,3 +186,30 @@ def test_sharded_run_equals_unsharded_gloo_world2():
         port = 29500 + (os.getpid() % 2000)
         mp.spawn(_gloo_worker, args=(2, port, tmp), nprocs=2, join=True)
         assert [open(os.path.join(tmp, f"ok{r}")).read() for r in range(2)] == ["True", "True"]
+
+
+def test_split_heuristic_cost_model():
+    """choose_num_splits: no split when the query tiles fill the GPU, a wave-aware count otherwise."""
+    from unittest import mock
+    import flash_attention_b200.interface as I
+
+    class Props:
+        multi_processor_count = 148
+    with mock.patch.object(torch.cuda, "get_device_properties", lambda d: Props):
+        assert I.choose_num_splits(4, 8192, 8192, 32, True, None) == 1      # prefill: 8192 tiles
+        assert I.choose_num_splits(4, 1, 32768, 32, True, None) == 1        # 128 tiles: nearly a wave
+        n = I.choose_num_splits(1, 1, 131072, 32, True, None)               # 32 tiles, 1024 blocks
+        assert 4 <= n <= 9 and (32 * n + 147) // 148 == 2
+        assert I.choose_num_splits(1, 128, 512, 8, False, None) == 1        # too few blocks to split
+
+
+def test_oracle_split_model_matches_unsplit_statistics():
+    from oracle import nvfp4_oracle as orc
+    from tests.helpers import make_qkv, oracles
+    q, k, v = make_qkv(1, 17, 1536, 2, 1, 128, seed=9)
+    Q, K, V = fa.quantize_qkv(q, k, v)
+    oa, la, ob1, lb1 = oracles(Q, K, V, False)
+    _, _, ob3, lb3 = oracles(Q, K, V, False, num_splits=3)
+    assert (lb1 - lb3).abs().max().item() < 1e-5
+    e1, e3 = orc.error_metrics(ob1, oa), orc.error_metrics(ob3, oa)
+    assert abs(e1["rel_rms"] - e3["rel_rms"]) < 0.03
