@@ -46,6 +46,15 @@ class Params(ctypes.Structure):
     ]
 
 
+class Ext(ctypes.Structure):
+    """Mirror of ``fa4_nvfp4_ext``."""
+    _fields_ = [
+        ("struct_size", ctypes.c_uint32), ("num_splits", ctypes.c_int32),
+        ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_uint64),
+        ("window_left", ctypes.c_int32), ("window_right", ctypes.c_int32),
+    ]
+
+
 def _needs_build() -> bool:
     if not os.path.exists(LIB_PATH):
         return True
@@ -93,6 +102,8 @@ def lib() -> ctypes.CDLL:
             L.fa4_nvfp4_fwd_splitkv.argtypes = [ctypes.POINTER(Params), ctypes.c_int32, ctypes.c_void_p,
                                                 ctypes.c_uint64, ctypes.c_void_p]
             L.fa4_nvfp4_fwd_splitkv.restype = ctypes.c_int
+            L.fa4_nvfp4_fwd_ex.argtypes = [ctypes.POINTER(Params), ctypes.POINTER(Ext), ctypes.c_void_p]
+            L.fa4_nvfp4_fwd_ex.restype = ctypes.c_int
             L.fa4_nvfp4_sf_linear_to_tiled.argtypes = [
                 ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
                 ctypes.c_int32, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int32,
@@ -126,7 +137,8 @@ def lib() -> ctypes.CDLL:
 EXPORTS = ["fa4_nvfp4_fwd", "fa4_nvfp4_sf_linear_to_tiled", "fa4_nvfp4_query",
            "fa4_nvfp4_debug_qk_tile", "fa4_nvfp4_debug_wait_expiry", "fa4_nvfp4_debug_mma_rate",
            "fa4_nvfp4_fwd_linear_sf_noalloc", "fa4_nvfp4_amax_bf16", "fa4_nvfp4_quantize_qk_bf16",
-           "fa4_nvfp4_quantize_v_bf16", "fa4_nvfp4_splitkv_workspace_bytes", "fa4_nvfp4_fwd_splitkv"]
+           "fa4_nvfp4_quantize_v_bf16", "fa4_nvfp4_splitkv_workspace_bytes", "fa4_nvfp4_fwd_splitkv",
+           "fa4_nvfp4_fwd_ex"]
 
 
 def check(rc: int, what: str) -> None:

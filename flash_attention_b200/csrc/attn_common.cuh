@@ -34,6 +34,11 @@ struct KernelParams {
   float* o_partial;    // (num_splits, B, Sq, Hq, Dv) fp32
   float* lse_partial;  // (num_splits, B, Hq, Sq) fp32
   int Dv;
+  // local (sliding-window) attention, general instantiation only: query row i sees keys j with
+  //   i + Sk - Sq - win_left <= j <= i + Sk - Sq + win_right        (-1 = no limit on that side)
+  // (flash_attn/cute/testing.py:249-288 construct_local_mask; mask.py:487-527).  `causal` is set
+  // whenever the right limit exists; plain causal is win_right == 0, win_left == -1.
+  int win_left, win_right;
 };
 
 // Work tile of a CTA.  Tiles are ordered so that, for causal problems, the m-blocks with the
@@ -47,13 +52,14 @@ struct Tile {
   int split;
 };
 
-// kSplit = false: the work list is the tile list (num_splits == 1); kept as a compile-time
-// switch so that the common case carries none of the split arithmetic or registers.
-template <bool kSplit = false>
+// kGeneral = false: the work list is the tile list (num_splits == 1) and the only masks are
+// causal / key length; kept as a compile-time switch so that the common case carries none of the
+// split or window arithmetic or registers.
+template <bool kGeneral = false>
 __device__ __forceinline__ Tile decode_tile(const KernelParams& p, int tile_idx) {
   Tile t;
   t.split = 0;
-  if constexpr (kSplit) {
+  if constexpr (kGeneral) {
     t.split = tile_idx % p.num_splits;   // the splits of one tile are neighbours in the work list
     tile_idx /= p.num_splits;
   }
@@ -68,16 +74,24 @@ __device__ __forceinline__ Tile decode_tile(const KernelParams& p, int tile_idx)
   if (p.causal) {
     // last visible key of the tile's last row: (m_blk + 1) * 128 - 1 + Sk - Sq
     // (block range of flash_attn/cute/block_info.py:23-55, bottom-right aligned)
-    const int last = (t.m_blk + 1) * kBlockM + p.Sk - p.Sq;  // exclusive
+    const int last = (t.m_blk + 1) * kBlockM + p.Sk - p.Sq + (kGeneral ? p.win_right : 0);  // exclusive
     int nb = (last + kBlockN - 1) / kBlockN;
     if (last <= 0) nb = 0;
     n = nb < n ? nb : n;
   }
-  if constexpr (kSplit) {
+  if constexpr (kGeneral) {
+    // first block that holds a visible key of the tile's first row (left window limit)
+    int n_min = 0;
+    if (p.win_left >= 0) {
+      const int first = t.m_blk * kBlockM + p.Sk - p.Sq - p.win_left;
+      n_min = first > 0 ? first / kBlockN : 0;
+      if (n_min > n) n_min = n;
+    }
+    const int cnt = n - n_min;
     // visit order is last block first; split s takes visits [s * per, (s + 1) * per)
-    const int per = (n + p.num_splits - 1) / p.num_splits;
-    const int i0 = t.split * per < n ? t.split * per : n;
-    const int i1 = i0 + per < n ? i0 + per : n;
+    const int per = (cnt + p.num_splits - 1) / p.num_splits;
+    const int i0 = t.split * per < cnt ? t.split * per : cnt;
+    const int i1 = i0 + per < cnt ? i0 + per : cnt;
     t.n_blocks = i1 - i0;
     t.nb_top = n - 1 - i0;
   } else {
@@ -92,16 +106,30 @@ __device__ __forceinline__ Tile decode_tile(const KernelParams& p, int tile_idx)
 // (bottom-right aligned, flash_attn/cute/mask.py:369-527) and the key length (keys >= Sk of the
 // last, partial block are zero-filled by TMA and must not count; the reference masks them on the
 // first-processed block only, flash_fwd_sm100.py:1997-2004).
+template <bool kGeneral = false>
 __device__ __forceinline__ int causal_limit(const KernelParams& p, const Tile& t, int row_in_tile,
                                             int nb) {
   const int len_limit = p.Sk - 1 - nb * kBlockN;
   if (!p.causal) return len_limit;
-  const int c = t.m_blk * kBlockM + row_in_tile + p.Sk - p.Sq - nb * kBlockN;
+  const int c = t.m_blk * kBlockM + row_in_tile + p.Sk - p.Sq + (kGeneral ? p.win_right : 0) - nb * kBlockN;
   return c < len_limit ? c : len_limit;
 }
+// In-block index of the FIRST visible key (left window limit); <= 0 when nothing is cut.
+__device__ __forceinline__ int lower_limit(const KernelParams& p, const Tile& t, int row_in_tile,
+                                           int nb) {
+  if (p.win_left < 0) return -(1 << 30);
+  return t.m_blk * kBlockM + row_in_tile + p.Sk - p.Sq - p.win_left - nb * kBlockN;
+}
+template <bool kGeneral = false>
 __device__ __forceinline__ bool block_needs_mask(const KernelParams& p, const Tile& t, int nb) {
   const bool partial = (nb + 1) * kBlockN > p.Sk;
-  return partial || (p.causal && (nb * kBlockN + kBlockN - 1 > t.m_blk * kBlockM + p.Sk - p.Sq));
+  const int off = t.m_blk * kBlockM + p.Sk - p.Sq;
+  bool need = partial || (p.causal && (nb * kBlockN + kBlockN - 1 > off + (kGeneral ? p.win_right : 0)));
+  if constexpr (kGeneral) {
+    // the last row of the tile has the highest left limit
+    need = need || (p.win_left >= 0 && nb * kBlockN < off + kBlockM - 1 - p.win_left);
+  }
+  return need;
 }
 
 // Final scaling and bf16 store of 32 consecutive output columns of one row.

@@ -193,6 +193,20 @@ __device__ __noinline__ void mask_scores_in_tmem(uint32_t taddr, int limit) {
   tc_wait_st();
 }
 
+// The same with a lower limit as well (local attention): keys outside [lower, limit] become -inf.
+__device__ __noinline__ void mask_scores_in_tmem_range(uint32_t taddr, int lower, int limit) {
+  for (int c = 0; c < 2; ++c) {
+    if (__all_sync(0xffffffffu, limit >= 32 * c + 31 && lower <= 32 * c)) continue;  // fully visible
+    uint32_t v[32];
+    tmem_ld32(taddr + 32 * c, v);
+    tc_wait_ld();
+#pragma unroll
+    for (int x = 0; x < 32; ++x) v[x] = (32 * c + x <= limit && 32 * c + x >= lower) ? v[x] : 0xff800000u;
+    tmem_st32(taddr + 32 * c, v);
+  }
+  tc_wait_st();
+}
+
 // Tile end: 32 accumulator columns of this thread's row -> registers (then the accumulator may be
 // overwritten: arrive on o_free_bar), scaled, rounded to bf16 and stored.  o_free_bar == 0: the
 // tile had no visible key, nothing to read, zeros are stored.
@@ -261,8 +275,9 @@ __device__ __forceinline__ uint64_t make_desc_qk(uint32_t tile_addr, int j) {
 // Q K^T, the width of O (tensor-memory columns, N of the P V instruction), the rows of a V tile and
 // the bytes of a Q / K tile (128 rows of kD / 2 bytes: 64-byte-swizzled rows for 128, 32-byte for
 // 64); the shared-memory slots keep the size of the larger case.
-// kSplit: split-KV work list and fp32 partial outputs (num_splits > 1).
-template <int kD, bool kSplit>
+// kGeneral: split-KV work list with fp32 partial outputs (num_splits > 1) and / or the left and
+// right window limits of local attention.
+template <int kD, bool kGeneral>
 __global__ void __launch_bounds__(ws::kThreads, 1)
 attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
                    const __grid_constant__ CUtensorMap tm_k,
@@ -281,7 +296,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
   const int warp = tid >> 5;
   const int lane = tid & 31;
   const WaitCtx wc{s_abort, p.status, p.budget_ns};
-  const int num_tiles = p.num_m_blocks * p.Hq * p.B * (kSplit ? p.num_splits : 1);
+  const int num_tiles = p.num_m_blocks * p.Hq * p.B * (kGeneral ? p.num_splits : 1);
   const int ncta = gridDim.x, cta = blockIdx.x;
 
   if (tid == 0) {
@@ -342,7 +357,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
       // ========================================= TMA producer ===================================
       uint32_t issued_k = 0, issued_v = 0, issued_q = 0;
       FA4_FOR_EACH_TILE {
-        const Tile t = decode_tile<kSplit>(p, tile);
+        const Tile t = decode_tile<kGeneral>(p, tile);
         const int n = t.n_blocks;
         if (n == 0) continue;
         if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
@@ -368,7 +383,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
           const int ik = step, iv = step - 2;
           if (ik < n) {
             const uint32_t G = gb + ik, st = G % kStagesK;
-            const int nb = (kSplit ? t.nb_top : n - 1) - ik;
+            const int nb = (kGeneral ? t.nb_top : n - 1) - ik;
             // stage st is free once QK^T of block G - kStagesK has completed (its s_full phase)
             if (G >= kStagesK) {
               const uint32_t j = G - kStagesK;
@@ -384,7 +399,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
           }
           if (iv >= 0 && iv < n) {
             const uint32_t G = gb + iv, st = G % kStagesV;
-            const int nb = (kSplit ? t.nb_top : n - 1) - iv;
+            const int nb = (kGeneral ? t.nb_top : n - 1) - iv;
             if (G >= kStagesV) {
               const uint32_t j = G - kStagesV;
               ok = mbar_wait(bars.at(Bars::kPvDone + (j % kStagesV)), (j / kStagesV) & 1, wc, kSiteVEmpty);
@@ -420,7 +435,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
     } else if (warp == kIssuerWarp && lane == 0) {
       // ========================================= QK^T issuer ====================================
       FA4_FOR_EACH_TILE {
-        const Tile t = decode_tile<kSplit>(p, tile);
+        const Tile t = decode_tile<kGeneral>(p, tile);
         const int n = t.n_blocks;
         if (n == 0) continue;
         if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
@@ -475,7 +490,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
     } else if (warp == kPvIssuerWarp && lane == 0) {
       // ========================================= PV issuer ======================================
       FA4_FOR_EACH_TILE {
-        const Tile t = decode_tile<kSplit>(p, tile);
+        const Tile t = decode_tile<kGeneral>(p, tile);
         const int n = t.n_blocks;
         if (n == 0) continue;
         if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
@@ -532,7 +547,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
     const int row = tid & 127;
     const uint32_t lane_addr = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     FA4_FOR_EACH_TILE {
-      const Tile t = decode_tile<kSplit>(p, tile);
+      const Tile t = decode_tile<kGeneral>(p, tile);
       const int n = t.n_blocks;
       if (n == 0) continue;
       if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
@@ -542,7 +557,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
       float m_run = kNegInf;
       for (int i = 0; i < n; ++i) {
         const uint32_t G = gb + i, b = G & 1;
-        const int nb = (kSplit ? t.nb_top : n - 1) - i;
+        const int nb = (kGeneral ? t.nb_top : n - 1) - i;
         const uint32_t bar_s = bars.at(Bars::kSFull + (G % kStagesK)), par_s = (G / kStagesK) & 1;
         const uint32_t bar_f = bars.at(Bars::kStFree + b), par_f = ((G - 2) >> 1) & 1;
         const bool r_s = mbar_test(bar_s, par_s);
@@ -551,8 +566,9 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         if (!ok) break;
         FA4_TRACE_EV(30, G);
         tc_fence_after_sync();
-        const bool masked = block_needs_mask(p, t, nb);
-        const int limit = causal_limit(p, t, row, nb);
+        const bool masked = block_needs_mask<kGeneral>(p, t, nb);
+        const int limit = causal_limit<kGeneral>(p, t, row, nb);
+        [[maybe_unused]] const int lower = kGeneral ? lower_limit(p, t, row, nb) : 0;
         float bm[8];
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -561,7 +577,11 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
           tc_wait_ld();
           if (masked) {
 #pragma unroll
-            for (int x = 0; x < 32; ++x) s[x] = (32 * c + x <= limit) ? s[x] : kNegInf;
+            for (int x = 0; x < 32; ++x) {
+              bool vis = 32 * c + x <= limit;
+              if constexpr (kGeneral) vis = vis && (32 * c + x >= lower);
+              s[x] = vis ? s[x] : kNegInf;
+            }
           }
 #pragma unroll
           for (int q = 0; q < 2; ++q) {
@@ -612,7 +632,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
     const uint32_t lane_addr = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
 
     FA4_FOR_EACH_TILE {
-      const Tile t = decode_tile<kSplit>(p, tile);
+      const Tile t = decode_tile<kGeneral>(p, tile);
       const int n = t.n_blocks;
       const bool poisoned =
           (p.status != nullptr) && (*reinterpret_cast<volatile uint32_t*>(p.status) != 0u);
@@ -624,7 +644,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
 
       for (int i = (g - gb) & 1; i < n; i += 2) {
         const uint32_t G = gb + i, b = G & 1;  // b == g: S / P / stats buffer of this block
-        const int nb = (kSplit ? t.nb_top : n - 1) - i;
+        const int nb = (kGeneral ? t.nb_top : n - 1) - i;
         FA4_TRACE_EV(1, G);
         // Probe the three barriers this block depends on back to back so that their latencies
         // overlap; the blocking (bounded) wait only runs for a probe that failed.
@@ -646,7 +666,14 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         // memory before loading it (out of line, nothing large is live yet).  The statistics
         // warps may be reading the same row: they mask what they read themselves, and the visible
         // keys are not changed.
-        if (block_needs_mask(p, t, nb)) mask_scores_in_tmem(s_addr, causal_limit(p, t, row, nb) - 64 * half);
+        if (block_needs_mask<kGeneral>(p, t, nb)) {
+          if constexpr (kGeneral) {
+            mask_scores_in_tmem_range(s_addr, lower_limit(p, t, row, nb) - 64 * half,
+                                      causal_limit<true>(p, t, row, nb) - 64 * half);
+          } else {
+            mask_scores_in_tmem(s_addr, causal_limit(p, t, row, nb) - 64 * half);
+          }
+        }
         float s[64];
         tmem_ld32(s_addr, reinterpret_cast<uint32_t*>(&s[0]));
         tmem_ld32(s_addr + 32, reinterpret_cast<uint32_t*>(&s[32]));
@@ -742,7 +769,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         scale = (l_tot > 0.f) ? p.out_scale / l_tot : 0.f;
       }
       // warpgroup k stores output columns [32 k, 32 k + 32); with kD = 64 two of them only arrive
-      if (kSplit && (kD == 128 || wg < kD / 32)) {
+      if (kGeneral && p.num_splits > 1 && (kD == 128 || wg < kD / 32)) {
         float* prow = p.o_partial +
                       ((((int64_t)t.split * p.B + t.b) * p.Sq + q_idx) * p.Hq + t.h) * kD + 32 * wg;
         store_accumulator_partial(lane_addr + kTmO + 32 * wg, q_idx < p.Sq ? prow : nullptr, scale,
@@ -754,7 +781,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         store_accumulator_chunk<false>(0u, nullptr, 0.f, n > 0 ? bars.at(Bars::kOFree) : 0u);
       }
       if (wg == 0 && q_idx < p.Sq) {
-        if (kSplit) {
+        if (kGeneral && p.num_splits > 1) {
           p.lse_partial[(((int64_t)t.split * p.B + t.b) * p.Hq + t.h) * p.Sq + q_idx] =
               finish_lse(m_fin, l_tot, p.sl2);
         } else if (p.lse != nullptr) {

@@ -20,10 +20,11 @@
 // by the exponential (the exponent offset absorbs e), i.e. the quantisation costs no multiply.
 //
 // Pipe budget per 128x128 block on one SM (measured instruction rates on B200): 16 384
-// ex2.approx at 16/clk = 1024 clk and 8192 cvt.e2m1x2 at 16/clk = 512 clk share the XU pipe;
-// everything else is arranged to stay well below that on the FMA / ALU pipes and in issue
-// slots (packed f32x2 arithmetic, 3-input max, block scales derived with a magic-number
-// rounding instead of cvt / ceil, which would also land on the XU pipe).
+// ex2.approx at 16/clk = 1024 clk on the XU pipe and 8192 cvt.e2m1x2 at 16/clk = 512 clk (the
+// two overlap: interleaved they take ~1100 clk, and the profiler's XU counter follows the
+// exponentials alone); everything else is arranged to stay well below that on the FMA / ALU
+// pipes and in issue slots (packed f32x2 arithmetic, 3-input max, block scales derived with a
+// magic-number rounding instead of cvt / ceil, which run at the same low rate).
 #pragma once
 #include "ptx.cuh"
 #include <math.h>

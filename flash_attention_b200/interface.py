@@ -94,6 +94,7 @@ def flash_attn_fp4_func(
     sf_layout: str = "linear",
     variant: int = VARIANT_AUTO,
     num_splits: int = 1,
+    window_size: Tuple[Optional[int], Optional[int]] = (None, None),
 ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
     """NVFP4 attention forward.
 
@@ -105,6 +106,10 @@ def flash_attn_fp4_func(
     ``num_splits``: 1 = one pass over K/V per query tile; k > 1 = split-KV with a combine kernel
     (the reference's ``num_splits``, interface.py:494-510), for short Sq against long Sk;
     0 = choose (split only when the query tiles alone leave most SMs idle).
+
+    ``window_size=(left, right)``: local attention, query row i sees keys
+    ``i + Sk - Sq - left <= j <= i + Sk - Sq + right`` (``None`` = unlimited; ``causal`` is
+    ``right = 0``), the reference's semantics (flash_attn/cute/interface.py:256-276).
 
     Built so far: D = Dv = 128 or 64; any Sq; Sk a multiple of 32 (partial last tiles are handled by
     zero-filled loads, a key-length mask and unstored rows).  Anything else raises
@@ -179,21 +184,46 @@ def flash_attn_fp4_func(
         raise ValueError("num_splits must be in 0..128")
     if num_splits == 0:
         num_splits = choose_num_splits(B, Sq, Sk, Hq, causal, device)
+    causal, win_left, win_right = resolve_window(causal, window_size)
+    p.causal = 1 if causal else 0
     with torch.cuda.device(device):
         stream = torch.cuda.current_stream(device).cuda_stream
-        if num_splits == 1:
+        if num_splits == 1 and win_left is None and (win_right is None or win_right == 0):
             rc = _lib.lib().fa4_nvfp4_fwd(ctypes.byref(p), stream)
             what = "fa4_nvfp4_fwd"
         else:
-            nbytes = _lib.lib().fa4_nvfp4_splitkv_workspace_bytes(ctypes.byref(p), num_splits)
-            if nbytes < 0:
-                _lib.check(int(nbytes), "fa4_nvfp4_splitkv_workspace_bytes")
-            workspace = torch.empty(nbytes, dtype=torch.uint8, device=device)   # stream-ordered scratch
-            rc = _lib.lib().fa4_nvfp4_fwd_splitkv(ctypes.byref(p), num_splits, workspace.data_ptr(), nbytes,
-                                                  stream)
-            what = "fa4_nvfp4_fwd_splitkv"
+            x = _lib.Ext()
+            x.struct_size = ctypes.sizeof(_lib.Ext)
+            x.num_splits = num_splits
+            x.window_left = -1 if win_left is None else int(win_left)
+            x.window_right = -1 if win_right is None else int(win_right)
+            workspace = None
+            if num_splits > 1:
+                nbytes = _lib.lib().fa4_nvfp4_splitkv_workspace_bytes(ctypes.byref(p), num_splits)
+                if nbytes < 0:
+                    _lib.check(int(nbytes), "fa4_nvfp4_splitkv_workspace_bytes")
+                workspace = torch.empty(nbytes, dtype=torch.uint8, device=device)   # stream-ordered scratch
+                x.workspace, x.workspace_bytes = workspace.data_ptr(), nbytes
+            rc = _lib.lib().fa4_nvfp4_fwd_ex(ctypes.byref(p), ctypes.byref(x), stream)
+            what = "fa4_nvfp4_fwd_ex"
     _lib.check(rc, what)
     return out, lse
+
+
+def resolve_window(causal: bool, window_size) -> Tuple[bool, Optional[int], Optional[int]]:
+    """(causal, left, right) after the reference's rules (flash_attn/cute/interface.py:256-276):
+    causal sets right = 0; a window whose two limits sum to less than zero means no window;
+    (None, 0) is plain causal."""
+    left, right = window_size
+    if causal:
+        right = 0
+    if left is not None and right is not None and left + right < 0:
+        left, right = None, None
+    if left is not None and left < 0:
+        left = None
+    if right is not None and right < 0:
+        raise NotImplementedError("negative window_size_right with an unlimited left side is not built")
+    return right == 0 and left is None, left, right
 
 
 def choose_num_splits(B: int, Sq: int, Sk: int, Hq: int, causal: bool, device) -> int:
@@ -246,8 +276,6 @@ def flash_attn_func(
     if not all(isinstance(t, NVFP4Tensor) for t in (q, k, v)):
         raise TypeError("flash_attn_func of this package takes NVFP4Tensor operands; "
                         "see quantize_qkv()")
-    if window_size != (None, None) and tuple(window_size) != (None, 0 if causal else None):
-        raise NotImplementedError("sliding-window attention is not built")
     if learnable_sink is not None:
         raise NotImplementedError("learnable_sink is not built")
     if softcap not in (0.0, None):
@@ -261,7 +289,7 @@ def flash_attn_func(
     return flash_attn_fp4_func(
         q.data, k.data, v.data, q.sf, k.sf, v.sf, q.scale, k.scale, v.scale,
         softmax_scale=softmax_scale, causal=causal, return_lse=return_lse,
-        sf_layout="tiled" if q.tiled else "linear", num_splits=num_splits)
+        sf_layout="tiled" if q.tiled else "linear", num_splits=num_splits, window_size=tuple(window_size))
 
 
 def measure_fp4_mma_rate(iters: int = 1 << 16, device=None, repeats: int = 3) -> dict:

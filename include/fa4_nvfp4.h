@@ -129,6 +129,24 @@ int fa4_nvfp4_fwd_splitkv(const fa4_nvfp4_params* p, int32_t num_splits, void* w
                           uint64_t workspace_bytes, void* cuda_stream);
 
 /*
+ * Extended forward: split-KV and / or local (sliding-window) attention, the reference's
+ * window_size_left / window_size_right (flash_attn/cute/interface.py:256-276,293-294; mask
+ * semantics flash_attn/cute/testing.py:249-288, mask.py:487-527): query row i sees keys j with
+ *     i + Sk - Sq - window_left <= j <= i + Sk - Sq + window_right,     -1 = no limit.
+ * p->causal is the right limit 0 (an explicit window_right >= 0 takes its place).  Tiles skip
+ * the K/V blocks that lie wholly outside the window of all their rows.  WS variant only.
+ */
+typedef struct fa4_nvfp4_ext {
+  uint32_t struct_size;     /* = sizeof(fa4_nvfp4_ext) */
+  int32_t num_splits;       /* 0 or 1: no split; k > 1 needs the workspace of fa4_nvfp4_fwd_splitkv */
+  void* workspace;
+  uint64_t workspace_bytes;
+  int32_t window_left;      /* -1: unlimited */
+  int32_t window_right;     /* -1: unlimited (or 0 when p->causal) */
+} fa4_nvfp4_ext;
+int fa4_nvfp4_fwd_ex(const fa4_nvfp4_params* p, const fa4_nvfp4_ext* x, void* cuda_stream);
+
+/*
  * Scale-factor layout conversion, linear -> tiled.
  *   src: rows x cols e4m3 bytes; element (r, c) of matrix m at
  *        src + m_outer*stride_outer + m_inner*stride_inner + r*stride_row + c

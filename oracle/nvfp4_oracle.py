@@ -149,7 +149,26 @@ def _causal_mask(sq: int, sk: int) -> torch.Tensor:
     return j > i + (sk - sq)
 
 
-def attention_oracle_a(q, k, v, causal=False, softmax_scale=None):
+def _visibility_mask(sq: int, sk: int, causal: bool, window=(None, None)):
+    """True where key j is MASKED for query i: the reference's construct_local_mask
+    (flash_attn/cute/testing.py:249-288) with causal = right limit 0, bottom-right aligned.
+    Returns None when nothing is masked."""
+    left, right = window
+    if causal:
+        right = 0
+    if left is None and right is None:
+        return None
+    i = torch.arange(sq)[:, None]
+    j = torch.arange(sk)[None, :]
+    m = torch.zeros(sq, sk, dtype=torch.bool)
+    if right is not None:
+        m |= j > i + (sk - sq) + right
+    if left is not None:
+        m |= j < i + (sk - sq) - left
+    return m
+
+
+def attention_oracle_a(q, k, v, causal=False, softmax_scale=None, window=(None, None)):
     """q (B,Sq,Hq,D), k (B,Sk,Hkv,D), v (B,Sk,Hkv,Dv) fp32 torch CPU tensors.
     Returns (out (B,Sq,Hq,Dv) fp32, lse (B,Hq,Sq) fp32)."""
     q, k, v = (torch.as_tensor(t, dtype=torch.float32) for t in (q, k, v))
@@ -160,12 +179,13 @@ def attention_oracle_a(q, k, v, causal=False, softmax_scale=None):
     k = k.repeat_interleave(g, dim=2)
     v = v.repeat_interleave(g, dim=2)
     scores = torch.einsum("bthd,bshd->bhts", q * scale, k)
-    if causal:
-        scores = scores.masked_fill(_causal_mask(Sq, Sk), float("-inf"))
+    mask = _visibility_mask(Sq, Sk, causal, window)
+    if mask is not None:
+        scores = scores.masked_fill(mask, float("-inf"))
     lse = torch.logsumexp(scores, dim=-1)
     attn = torch.softmax(scores, dim=-1)
-    if causal:
-        attn = attn.masked_fill(torch.all(_causal_mask(Sq, Sk), dim=-1, keepdim=True), 0.0)
+    if mask is not None:
+        attn = attn.masked_fill(torch.all(mask, dim=-1, keepdim=True), 0.0)
     attn = torch.nan_to_num(attn, nan=0.0)
     out = torch.einsum("bhts,bshd->bthd", attn, v)
     return out, lse
@@ -191,7 +211,7 @@ def quantize_p_block_model(x: torch.Tensor, m_ref: torch.Tensor):
 
 
 def attention_oracle_b(qd, kd, vd, sl2: float, v_scale_out: float = 1.0, causal=False,
-                       num_splits: int = 1):
+                       num_splits: int = 1, window=(None, None)):
     """Kernel model.  qd (B,Sq,Hq,D), kd (B,Sk,Hkv,D), vd (B,Sk,Hkv,Dv): fp32 values the tensor
     core sees (e2m1 * block scale, WITHOUT the per-tensor scales); sl2 = softmax_scale * q_scale
     * k_scale * log2(e); v_scale_out = v_scale.  Walks the K/V blocks of 128 keys from the last
@@ -218,11 +238,20 @@ def attention_oracle_b(qd, kd, vd, sl2: float, v_scale_out: float = 1.0, causal=
                 s_all[:, :Sk] = (qd[b, rows, h] @ kd[b, :, hk].T)         # raw scores
                 v_pad = torch.zeros(n_blocks * 128, Dv)
                 v_pad[:Sk] = vd[b, :, hk]
+                left, right = window
                 if causal:
-                    last = m0 + 128 + Sk - Sq
+                    right = 0
+                n_min = 0
+                if right is not None:
+                    last = m0 + 128 + Sk - Sq + right
                     n_blocks = min(n_blocks, max(0, (last + 127) // 128))
-                    s_all[:, :Sk] = s_all[:, :Sk].masked_fill(_causal_mask(Sq, Sk)[rows], float("-inf"))
-                visit = list(range(n_blocks - 1, -1, -1))
+                if left is not None:
+                    first = m0 + Sk - Sq - left
+                    n_min = min(n_blocks, max(0, first // 128))
+                mask = _visibility_mask(Sq, Sk, causal, window)
+                if mask is not None:
+                    s_all[:, :Sk] = s_all[:, :Sk].masked_fill(mask[rows], float("-inf"))
+                visit = list(range(n_blocks - 1, n_min - 1, -1))
                 per = (len(visit) + num_splits - 1) // num_splits if visit else 0
                 parts = []
                 for sp in range(num_splits):

@@ -28,11 +28,14 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 from oracle import nvfp4_oracle as orc  # noqa: E402
 
 CASES = [
-    # name, B, Sq, Sk, Hq, Hkv, D, causal, seed
-    ("mha_noncausal", 1, 128, 128, 2, 2, 128, False, 0),
-    ("gqa_causal_sq_lt_sk", 2, 64, 192, 4, 2, 128, True, 1),
-    ("mqa_causal_sq_gt_sk", 1, 160, 96, 2, 1, 128, True, 2),
-    ("mqa_noncausal_ragged", 1, 113, 208, 3, 1, 64, False, 3),
+    # name, B, Sq, Sk, Hq, Hkv, D, causal, seed, window (left, right)
+    ("mha_noncausal", 1, 128, 128, 2, 2, 128, False, 0, (None, None)),
+    ("gqa_causal_sq_lt_sk", 2, 64, 192, 4, 2, 128, True, 1, (None, None)),
+    ("mqa_causal_sq_gt_sk", 1, 160, 96, 2, 1, 128, True, 2, (None, None)),
+    ("mqa_noncausal_ragged", 1, 113, 208, 3, 1, 64, False, 3, (None, None)),
+    # local attention (the reference's construct_local_mask, testing.py:249-288)
+    ("gqa_sliding_window_causal", 1, 320, 320, 4, 2, 128, True, 4, (100, 0)),
+    ("mha_window_both_sides_sq_lt_sk", 1, 96, 352, 2, 2, 128, False, 5, (40, 70)),
 ]
 
 
@@ -45,10 +48,12 @@ def load_reference_testing(ref_root):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py /path/to/reference")
+    ref_root = sys.argv[1]
     ref = load_reference_testing(ref_root)
     torch.set_num_threads(4)
-    for name, B, Sq, Sk, Hq, Hkv, D, causal, seed in CASES:
+    for name, B, Sq, Sk, Hq, Hkv, D, causal, seed, window in CASES:
         g = torch.Generator().manual_seed(seed)
         q = torch.randn(B, Sq, Hq, D, generator=g).bfloat16().float().numpy()
         k = torch.randn(B, Sk, Hkv, D, generator=g).bfloat16().float().numpy()
@@ -58,10 +63,14 @@ def main():
         qd = torch.from_numpy(orc.dequantize_nvfp4(Q))
         kd = torch.from_numpy(orc.dequantize_nvfp4(K))
         vd = torch.from_numpy(np.ascontiguousarray(np.transpose(orc.dequantize_nvfp4(V), (0, 3, 1, 2))))
-        out_ref, _ = ref.attention_ref(qd, kd, vd, causal=causal, upcast=True)
+        out_ref, _ = ref.attention_ref(qd, kd, vd, causal=causal, window_size=window, upcast=True)
         kk = kd.repeat_interleave(Hq // Hkv, dim=2)
         qk = torch.einsum("bshd,bthd->bhst", qd, kk) / (D ** 0.5)
-        if causal:
+        if window != (None, None):
+            w = (window[0], 0) if causal else window
+            mask = ref.construct_local_mask(Sq, Sk, w)
+            qk = qk.masked_fill(mask, float("-inf"))
+        elif causal:
             mask = torch.triu(torch.ones(Sq, Sk, dtype=torch.bool), diagonal=Sk - Sq + 1)
             qk = qk.masked_fill(mask, float("-inf"))
         lse_ref = torch.logsumexp(qk, dim=-1)
@@ -71,7 +80,8 @@ def main():
             k_data=K.data, k_sf=K.sf, k_scale=np.float32(K.scale),
             v_data=V.data, v_sf=V.sf, v_scale=np.float32(V.scale),
             out_ref=out_ref.numpy().astype(np.float32), lse_ref=lse_ref.numpy().astype(np.float32),
-            causal=np.bool_(causal), seed=np.int64(seed))
+            causal=np.bool_(causal), seed=np.int64(seed),
+            window=np.array([-1 if x is None else x for x in window], dtype=np.int64))
         print(name, out_ref.shape, float(out_ref.abs().max()))
 
 

@@ -122,7 +122,7 @@ def test_python_surface_errors_before_launch():
         fa.flash_attn_func(q, q, v)
     Q = fa.NVFP4Tensor(q, sf, 1.0)
     V = fa.NVFP4Tensor(v, vsf, 1.0, is_v=True)
-    for kw in ({"window_size": (128, 0)}, {"softcap": 30.0},
+    for kw in ({"softcap": 30.0},
                {"learnable_sink": torch.zeros(2)}, {"mask_mod": lambda *a: True}):
         with pytest.raises(NotImplementedError):
             fa.flash_attn_func(Q, Q, V, **kw)
@@ -213,3 +213,31 @@ def test_oracle_split_model_matches_unsplit_statistics():
     assert (lb1 - lb3).abs().max().item() < 1e-5
     e1, e3 = orc.error_metrics(ob1, oa), orc.error_metrics(ob3, oa)
     assert abs(e1["rel_rms"] - e3["rel_rms"]) < 0.03
+
+
+def test_window_resolution_follows_the_reference_rules():
+    """flash_attn/cute/interface.py:256-276: causal sets right = 0; (None, 0) is plain causal;
+    limits that sum below zero mean no window."""
+    from flash_attention_b200.interface import resolve_window
+    assert resolve_window(False, (None, None)) == (False, None, None)
+    assert resolve_window(True, (None, None)) == (True, None, 0)
+    assert resolve_window(False, (None, 0)) == (True, None, 0)
+    assert resolve_window(True, (128, None)) == (False, 128, 0)
+    assert resolve_window(False, (64, 32)) == (False, 64, 32)
+    assert resolve_window(False, (-1, -1)) == (False, None, None)
+    assert resolve_window(True, (5, 99)) == (False, 5, 0)          # causal overrides the right limit
+
+
+def test_oracle_window_masks_match_reference_formula():
+    """_visibility_mask against the closed form of construct_local_mask (testing.py:249-288)."""
+    for (sq, sk, causal, win) in [(5, 9, True, (None, None)), (7, 7, False, (2, 1)), (4, 10, True, (3, None)),
+                                  (9, 4, False, (None, 2)), (6, 6, False, (0, 0))]:
+        m = orc._visibility_mask(sq, sk, causal, win)
+        left, right = win
+        if causal:
+            right = 0
+        for i in range(sq):
+            for j in range(sk):
+                masked = (right is not None and j > i + sk - sq + right) or \
+                         (left is not None and j < i + sk - sq - left)
+                assert bool(m[i, j]) == masked
