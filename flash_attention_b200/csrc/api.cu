@@ -74,11 +74,11 @@ int64_t splitkv_bytes(const fa4_nvfp4_params* p, int num_splits) {
   return (int64_t)num_splits * p->B * p->Sq * p->Hq * ((int64_t)p->Dv + 1) * 4;
 }
 int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint64_t workspace_bytes,
-               int win_left, int win_right, void* cuda_stream);
+               int win_left, int win_right, const float* sink, void* cuda_stream);
 }  // namespace
 
 extern "C" int fa4_nvfp4_fwd(const fa4_nvfp4_params* p, void* cuda_stream) {
-  return launch_fwd(p, 1, nullptr, 0, -1, -1, cuda_stream);
+  return launch_fwd(p, 1, nullptr, 0, -1, -1, nullptr, cuda_stream);
 }
 
 extern "C" int fa4_nvfp4_fwd_ex(const fa4_nvfp4_params* p, const fa4_nvfp4_ext* x, void* cuda_stream) {
@@ -87,7 +87,7 @@ extern "C" int fa4_nvfp4_fwd_ex(const fa4_nvfp4_params* p, const fa4_nvfp4_ext* 
   const int splits = x->num_splits == 0 ? 1 : x->num_splits;
   if (splits < 1 || splits > 128 || x->window_left < -1 || x->window_right < -1) return -FA4_E_SHAPE;
   return launch_fwd(p, splits, x->workspace, x->workspace_bytes, x->window_left, x->window_right,
-                    cuda_stream);
+                    x->sink, cuda_stream);
 }
 
 extern "C" int64_t fa4_nvfp4_splitkv_workspace_bytes(const fa4_nvfp4_params* p, int32_t num_splits) {
@@ -100,12 +100,12 @@ extern "C" int64_t fa4_nvfp4_splitkv_workspace_bytes(const fa4_nvfp4_params* p, 
 extern "C" int fa4_nvfp4_fwd_splitkv(const fa4_nvfp4_params* p, int32_t num_splits, void* workspace,
                                      uint64_t workspace_bytes, void* cuda_stream) {
   if (num_splits < 1 || num_splits > 128) return -FA4_E_SHAPE;
-  return launch_fwd(p, num_splits, workspace, workspace_bytes, -1, -1, cuda_stream);
+  return launch_fwd(p, num_splits, workspace, workspace_bytes, -1, -1, nullptr, cuda_stream);
 }
 
 namespace {
 int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint64_t workspace_bytes,
-               int win_left, int win_right, void* cuda_stream) {
+               int win_left, int win_right, const float* sink, void* cuda_stream) {
   if (p == nullptr) return -FA4_E_NULL;
   if (p->struct_size != sizeof(fa4_nvfp4_params)) return -FA4_E_STRUCT;
   if (!p->q || !p->k || !p->v || !p->q_sf || !p->k_sf || !p->v_sf || !p->out) return -FA4_E_NULL;
@@ -131,8 +131,8 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
   // window limits: `causal` is the right limit 0; an explicit right limit overrides it
   if (p->causal && win_right < 0) win_right = 0;
   const bool local = win_left >= 0 || win_right > 0;
-  const bool general = local || num_splits > 1;
-  if (local && variant == FA4_VARIANT_SERIAL) return -FA4_E_VARIANT;
+  const bool general = local || num_splits > 1 || sink != nullptr;
+  if ((local || sink != nullptr) && variant == FA4_VARIANT_SERIAL) return -FA4_E_VARIANT;
   if (num_splits > 1) {
     if (variant == FA4_VARIANT_SERIAL) return -FA4_E_VARIANT;
     if (workspace == nullptr) return -FA4_E_NULL;
@@ -178,6 +178,7 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
   kp.causal = win_right >= 0 ? 1 : 0;
   kp.win_left = win_left;
   kp.win_right = win_right;
+  kp.sink = sink;
   // tiled scale factors: (B, H, row tiles, col tiles, 512)
   kp.qsf_stride_h = (int64_t)kp.num_m_blocks * (p->D / 64) * 512;
   kp.qsf_stride_b = kp.qsf_stride_h * p->Hq;

@@ -39,6 +39,10 @@ struct KernelParams {
   // (flash_attn/cute/testing.py:249-288 construct_local_mask; mask.py:487-527).  `causal` is set
   // whenever the right limit exists; plain causal is win_right == 0, win_left == -1.
   int win_left, win_right;
+  // learnable sink (general instantiation only): one extra logit per query head, in natural-log
+  // units of the scaled scores, that takes part in the normalisation and in the LSE but has no
+  // value row (flash_attn/cute/flash_fwd_sm100.py:2383-2394, testing.py:406-416); null = none
+  const float* sink;
 };
 
 // Work tile of a CTA.  Tiles are ordered so that, for causal problems, the m-blocks with the

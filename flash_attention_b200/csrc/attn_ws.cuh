@@ -760,6 +760,13 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
 #pragma unroll
         for (int w = 0; w < 4; ++w) l_tot += lw[w] * reference_factor(mw[w], m_fin, p.sl2);
         if (m_fin == kNegInf) l_tot = 0.f;
+        if constexpr (kGeneral) {
+          // the sink joins the row sum once (split 0), relative to the row's reference maximum
+          if (p.sink != nullptr && t.split == 0 && m_fin != kNegInf) {
+            l_tot += ex2_approx(static_cast<float>(kShift) + p.sink[t.h] * 1.4426950408889634f -
+                                m_fin * p.sl2);
+          }
+        }
         const uint32_t Gl = gb + n - 1;
         ok = __all_sync(0xffffffffu,
                         mbar_wait(bars.at(Bars::kPvDone + (Gl % kStagesV)), (Gl / kStagesV) & 1, wc, kSiteFinalO));
@@ -781,11 +788,15 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         store_accumulator_chunk<false>(0u, nullptr, 0.f, n > 0 ? bars.at(Bars::kOFree) : 0u);
       }
       if (wg == 0 && q_idx < p.Sq) {
+        float lse_v = finish_lse(m_fin, l_tot, p.sl2);
+        if constexpr (kGeneral) {
+          // a row without visible keys still has its sink: LSE = sink, output zero
+          if (p.sink != nullptr && t.split == 0 && m_fin == kNegInf) lse_v = p.sink[t.h];
+        }
         if (kGeneral && p.num_splits > 1) {
-          p.lse_partial[(((int64_t)t.split * p.B + t.b) * p.Hq + t.h) * p.Sq + q_idx] =
-              finish_lse(m_fin, l_tot, p.sl2);
+          p.lse_partial[(((int64_t)t.split * p.B + t.b) * p.Hq + t.h) * p.Sq + q_idx] = lse_v;
         } else if (p.lse != nullptr) {
-          p.lse[((int64_t)t.b * p.Hq + t.h) * p.Sq + q_idx] = finish_lse(m_fin, l_tot, p.sl2);
+          p.lse[((int64_t)t.b * p.Hq + t.h) * p.Sq + q_idx] = lse_v;
         }
       }
       FA4_TRACE_EV(42, gb);

@@ -95,6 +95,7 @@ def flash_attn_fp4_func(
     variant: int = VARIANT_AUTO,
     num_splits: int = 1,
     window_size: Tuple[Optional[int], Optional[int]] = (None, None),
+    learnable_sink: Optional[torch.Tensor] = None,
 ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
     """NVFP4 attention forward.
 
@@ -110,6 +111,9 @@ def flash_attn_fp4_func(
     ``window_size=(left, right)``: local attention, query row i sees keys
     ``i + Sk - Sq - left <= j <= i + Sk - Sq + right`` (``None`` = unlimited; ``causal`` is
     ``right = 0``), the reference's semantics (flash_attn/cute/interface.py:256-276).
+
+    ``learnable_sink``: (Hq,) logits that join every row's softmax normalisation (and the LSE)
+    without contributing a value, the reference's argument of the same name (testing.py:406-416).
 
     Built so far: D = Dv = 128 or 64; any Sq; Sk a multiple of 32 (partial last tiles are handled by
     zero-filled loads, a key-length mask and unstored rows).  Anything else raises
@@ -188,7 +192,11 @@ def flash_attn_fp4_func(
     p.causal = 1 if causal else 0
     with torch.cuda.device(device):
         stream = torch.cuda.current_stream(device).cuda_stream
-        if num_splits == 1 and win_left is None and (win_right is None or win_right == 0):
+        sink = None
+        if learnable_sink is not None:
+            assert learnable_sink.shape == (Hq,), "learnable_sink must have one entry per query head"
+            sink = learnable_sink.to(device=device, dtype=torch.float32).contiguous()
+        if num_splits == 1 and sink is None and win_left is None and (win_right is None or win_right == 0):
             rc = _lib.lib().fa4_nvfp4_fwd(ctypes.byref(p), stream)
             what = "fa4_nvfp4_fwd"
         else:
@@ -197,6 +205,7 @@ def flash_attn_fp4_func(
             x.num_splits = num_splits
             x.window_left = -1 if win_left is None else int(win_left)
             x.window_right = -1 if win_right is None else int(win_right)
+            x.sink = sink.data_ptr() if sink is not None else None
             workspace = None
             if num_splits > 1:
                 nbytes = _lib.lib().fa4_nvfp4_splitkv_workspace_bytes(ctypes.byref(p), num_splits)
@@ -276,8 +285,6 @@ def flash_attn_func(
     if not all(isinstance(t, NVFP4Tensor) for t in (q, k, v)):
         raise TypeError("flash_attn_func of this package takes NVFP4Tensor operands; "
                         "see quantize_qkv()")
-    if learnable_sink is not None:
-        raise NotImplementedError("learnable_sink is not built")
     if softcap not in (0.0, None):
         raise NotImplementedError("softcap is not built")
     if mask_mod is not None or any(t is not None for t in (full_block_cnt, full_block_idx,
@@ -289,7 +296,8 @@ def flash_attn_func(
     return flash_attn_fp4_func(
         q.data, k.data, v.data, q.sf, k.sf, v.sf, q.scale, k.scale, v.scale,
         softmax_scale=softmax_scale, causal=causal, return_lse=return_lse,
-        sf_layout="tiled" if q.tiled else "linear", num_splits=num_splits, window_size=tuple(window_size))
+        sf_layout="tiled" if q.tiled else "linear", num_splits=num_splits, window_size=tuple(window_size),
+        learnable_sink=learnable_sink)
 
 
 def measure_fp4_mma_rate(iters: int = 1 << 16, device=None, repeats: int = 3) -> dict:

@@ -143,6 +143,9 @@ typedef struct fa4_nvfp4_ext {
   uint64_t workspace_bytes;
   int32_t window_left;      /* -1: unlimited */
   int32_t window_right;     /* -1: unlimited (or 0 when p->causal) */
+  const float* sink;        /* learnable sink: Hq fp32 logits on the device (natural-log units of the
+                               scaled scores) that join every row's normalisation and LSE without a
+                               value row (flash_attn/cute/flash_fwd_sm100.py:2383-2394); NULL = none */
 } fa4_nvfp4_ext;
 int fa4_nvfp4_fwd_ex(const fa4_nvfp4_params* p, const fa4_nvfp4_ext* x, void* cuda_stream);
 

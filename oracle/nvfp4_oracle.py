@@ -168,7 +168,7 @@ def _visibility_mask(sq: int, sk: int, causal: bool, window=(None, None)):
     return m
 
 
-def attention_oracle_a(q, k, v, causal=False, softmax_scale=None, window=(None, None)):
+def attention_oracle_a(q, k, v, causal=False, softmax_scale=None, window=(None, None), sink=None):
     """q (B,Sq,Hq,D), k (B,Sk,Hkv,D), v (B,Sk,Hkv,Dv) fp32 torch CPU tensors.
     Returns (out (B,Sq,Hq,Dv) fp32, lse (B,Hq,Sq) fp32)."""
     q, k, v = (torch.as_tensor(t, dtype=torch.float32) for t in (q, k, v))
@@ -182,8 +182,15 @@ def attention_oracle_a(q, k, v, causal=False, softmax_scale=None, window=(None, 
     mask = _visibility_mask(Sq, Sk, causal, window)
     if mask is not None:
         scores = scores.masked_fill(mask, float("-inf"))
-    lse = torch.logsumexp(scores, dim=-1)
-    attn = torch.softmax(scores, dim=-1)
+    if sink is not None:
+        # one more logit per query head in the normaliser, no value row (testing.py:406-416)
+        sk_ = torch.as_tensor(sink, dtype=torch.float32).reshape(1, Hq, 1, 1).expand(B, Hq, Sq, 1)
+        ext = torch.cat([scores, sk_], dim=-1)
+        lse = torch.logsumexp(ext, dim=-1)
+        attn = torch.softmax(ext, dim=-1)[..., :-1]
+    else:
+        lse = torch.logsumexp(scores, dim=-1)
+        attn = torch.softmax(scores, dim=-1)
     if mask is not None:
         attn = attn.masked_fill(torch.all(mask, dim=-1, keepdim=True), 0.0)
     attn = torch.nan_to_num(attn, nan=0.0)
@@ -211,7 +218,7 @@ def quantize_p_block_model(x: torch.Tensor, m_ref: torch.Tensor):
 
 
 def attention_oracle_b(qd, kd, vd, sl2: float, v_scale_out: float = 1.0, causal=False,
-                       num_splits: int = 1, window=(None, None)):
+                       num_splits: int = 1, window=(None, None), sink=None):
     """Kernel model.  qd (B,Sq,Hq,D), kd (B,Sk,Hkv,D), vd (B,Sk,Hkv,Dv): fp32 values the tensor
     core sees (e2m1 * block scale, WITHOUT the per-tensor scales); sl2 = softmax_scale * q_scale
     * k_scale * log2(e); v_scale_out = v_scale.  Walks the K/V blocks of 128 keys from the last
@@ -274,6 +281,12 @@ def attention_oracle_b(qd, kd, vd, sl2: float, v_scale_out: float = 1.0, causal=
                         p_hat, p_sum = quantize_p_block_model(s * sl2, msc[:, None])
                         acc = acc + p_hat @ v_pad[nb * 128:(nb + 1) * 128]
                         l_sum = l_sum + p_sum
+                    if sink is not None and sp == 0:
+                        # the sink joins the row sum of split 0; a row without keys keeps LSE = sink
+                        sv = float(sink[h])
+                        has = torch.isfinite(m_ref)
+                        l_sum = torch.where(has, l_sum + torch.exp2(P_SHIFT + sv * math.log2(math.e) - m_ref * sl2),
+                                            l_sum)
                     ok = l_sum > 0
                     safe = torch.where(ok, l_sum, torch.ones(nr))
                     o_part = torch.where(ok[:, None], acc * (v_scale_out / safe)[:, None],
@@ -281,6 +294,8 @@ def attention_oracle_b(qd, kd, vd, sl2: float, v_scale_out: float = 1.0, causal=
                     l_part = torch.where(
                         ok, (m_ref * sl2 + torch.log2(safe) - P_SHIFT) * math.log(2.0),
                         torch.full((nr,), float("-inf")))
+                    if sink is not None and sp == 0:
+                        l_part = torch.where(torch.isfinite(m_ref), l_part, torch.full((nr,), float(sink[h])))
                     parts.append((o_part, l_part))
                 if num_splits == 1:
                     out[b, rows, h], lse[b, h, rows] = parts[0]

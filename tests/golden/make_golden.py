@@ -36,6 +36,8 @@ CASES = [
     # local attention (the reference's construct_local_mask, testing.py:249-288)
     ("gqa_sliding_window_causal", 1, 320, 320, 4, 2, 128, True, 4, (100, 0)),
     ("mha_window_both_sides_sq_lt_sk", 1, 96, 352, 2, 2, 128, False, 5, (40, 70)),
+    # learnable sink (testing.py:406-416): seeded N(0, 1) logits, one per query head
+    ("gqa_causal_learnable_sink", 1, 192, 192, 4, 2, 128, True, 6, (None, None)),
 ]
 
 
@@ -63,7 +65,9 @@ def main():
         qd = torch.from_numpy(orc.dequantize_nvfp4(Q))
         kd = torch.from_numpy(orc.dequantize_nvfp4(K))
         vd = torch.from_numpy(np.ascontiguousarray(np.transpose(orc.dequantize_nvfp4(V), (0, 3, 1, 2))))
-        out_ref, _ = ref.attention_ref(qd, kd, vd, causal=causal, window_size=window, upcast=True)
+        sink = torch.randn(Hq, generator=g) * 2.0 if "sink" in name else None
+        out_ref, _ = ref.attention_ref(qd, kd, vd, causal=causal, window_size=window, upcast=True,
+                                       learnable_sink=sink)
         kk = kd.repeat_interleave(Hq // Hkv, dim=2)
         qk = torch.einsum("bshd,bthd->bhst", qd, kk) / (D ** 0.5)
         if window != (None, None):
@@ -73,6 +77,8 @@ def main():
         elif causal:
             mask = torch.triu(torch.ones(Sq, Sk, dtype=torch.bool), diagonal=Sk - Sq + 1)
             qk = qk.masked_fill(mask, float("-inf"))
+        if sink is not None:
+            qk = torch.cat([qk, sink.reshape(1, Hq, 1, 1).expand(B, Hq, Sq, 1)], dim=-1)
         lse_ref = torch.logsumexp(qk, dim=-1)
         np.savez_compressed(
             os.path.join(HERE, f"{name}.npz"),
@@ -81,7 +87,8 @@ def main():
             v_data=V.data, v_sf=V.sf, v_scale=np.float32(V.scale),
             out_ref=out_ref.numpy().astype(np.float32), lse_ref=lse_ref.numpy().astype(np.float32),
             causal=np.bool_(causal), seed=np.int64(seed),
-            window=np.array([-1 if x is None else x for x in window], dtype=np.int64))
+            window=np.array([-1 if x is None else x for x in window], dtype=np.int64),
+            sink=(sink.numpy().astype(np.float32) if sink is not None else np.zeros(0, dtype=np.float32)))
         print(name, out_ref.shape, float(out_ref.abs().max()))
 
 

@@ -38,16 +38,16 @@ def make_qkv(B, Sq, Sk, Hq, Hkv, D, seed, v_std=1.0, outlier_frac=0.0, device="c
     return tuple(t.bfloat16().to(device) for t in (q, k, v))
 
 
-def oracles(Q, K, V, causal, softmax_scale=None, num_splits=1, window=(None, None)):
+def oracles(Q, K, V, causal, softmax_scale=None, num_splits=1, window=(None, None), sink=None):
     """Q, K, V: NVFP4Tensor with linear scales.  Returns (out_a, lse_a, out_b, lse_b) on CPU."""
     qd, kd, vd = Q.dequantize().cpu(), K.dequantize().cpu(), V.dequantize().cpu()
     D = qd.shape[-1]
     scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(D)
-    oa, la = orc.attention_oracle_a(qd, kd, vd, causal=causal, softmax_scale=scale, window=window)
+    oa, la = orc.attention_oracle_a(qd, kd, vd, causal=causal, softmax_scale=scale, window=window, sink=sink)
     sl2 = float(torch.tensor(scale, dtype=torch.float32) * torch.tensor(Q.scale, dtype=torch.float32)
                 * torch.tensor(K.scale, dtype=torch.float32) * torch.tensor(LOG2E, dtype=torch.float32))
     ob, lb = orc.attention_oracle_b(qd / Q.scale, kd / K.scale, vd / V.scale, sl2, V.scale, causal=causal,
-                                    num_splits=num_splits, window=window)
+                                    num_splits=num_splits, window=window, sink=sink)
     return oa, la, ob, lb
 
 

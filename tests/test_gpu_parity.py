@@ -124,7 +124,7 @@ def test_parity_with_oracle(cuda_device, case, variant):
 
 @pytest.mark.parametrize("name", ["mha_noncausal", "gqa_causal_sq_lt_sk", "mqa_causal_sq_gt_sk",
                                   "mqa_noncausal_ragged", "gqa_sliding_window_causal",
-                                  "mha_window_both_sides_sq_lt_sk"])
+                                  "mha_window_both_sides_sq_lt_sk", "gqa_causal_learnable_sink"])
 def test_golden_fixture_through_the_kernel(cuda_device, name):
     """The fixtures generated by the reference's attention_ref, through the kernel."""
     import os
@@ -135,7 +135,8 @@ def test_golden_fixture_through_the_kernel(cuda_device, name):
     out, lse = fa.flash_attn_fp4_func(t(z["q_data"]), t(z["k_data"]), t(z["v_data"]), t(z["q_sf"]),
                                       t(z["k_sf"]), t(z["v_sf"]), float(z["q_scale"]), float(z["k_scale"]),
                                       float(z["v_scale"]), causal=bool(z["causal"]), return_lse=True,
-                                      window_size=window)
+                                      window_size=window,
+                                      learnable_sink=torch.from_numpy(z["sink"]) if z["sink"].size else None)
     torch.cuda.synchronize()
     fa.check_status(dev)
     ref_out, ref_lse = torch.from_numpy(z["out_ref"]), torch.from_numpy(z["lse_ref"])
@@ -397,3 +398,19 @@ def test_local_attention_parity(cuda_device, case):
     fa.check_status(cuda_device)
     w = (window[0], 0) if causal else window
     assert_parity(out, lse, *oracles(Q, K, V, causal, num_splits=splits, window=w))
+
+
+@pytest.mark.parametrize("splits", [1, 3])
+def test_learnable_sink_parity(cuda_device, splits):
+    """Sink logits join the normalisation and the LSE; rows without keys get LSE = sink, O = 0."""
+    B, Sq, Sk, Hq, Hkv = 1, 384, 256, 4, 2            # causal with Sq > Sk: 128 rows see no key
+    q, k, v = make_qkv(B, Sq, Sk, Hq, Hkv, 128, seed=17, device=cuda_device)
+    Q, K, V = fa.quantize_qkv(q, k, v)
+    sink = torch.tensor([0.5, -3.0, 4.0, 0.0])
+    out, lse = fa.flash_attn_func(Q, K, V, causal=True, return_lse=True, learnable_sink=sink.to(cuda_device),
+                                  num_splits=splits)
+    torch.cuda.synchronize()
+    fa.check_status(cuda_device)
+    assert_parity(out, lse, *oracles(Q, K, V, True, num_splits=splits, sink=sink.numpy()))
+    assert torch.equal(lse[0, :, :128].cpu(), sink[:, None].expand(4, 128))
+    assert out[0, :128].abs().max().item() == 0.0

@@ -122,8 +122,7 @@ def test_python_surface_errors_before_launch():
         fa.flash_attn_func(q, q, v)
     Q = fa.NVFP4Tensor(q, sf, 1.0)
     V = fa.NVFP4Tensor(v, vsf, 1.0, is_v=True)
-    for kw in ({"softcap": 30.0},
-               {"learnable_sink": torch.zeros(2)}, {"mask_mod": lambda *a: True}):
+    for kw in ({"softcap": 30.0}, {"mask_mod": lambda *a: True}):
         with pytest.raises(NotImplementedError):
             fa.flash_attn_func(Q, Q, V, **kw)
 
