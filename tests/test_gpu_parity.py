@@ -414,3 +414,33 @@ def test_learnable_sink_parity(cuda_device, splits):
     assert_parity(out, lse, *oracles(Q, K, V, True, num_splits=splits, sink=sink.numpy()))
     assert torch.equal(lse[0, :, :128].cpu(), sink[:, None].expand(4, 128))
     assert out[0, :128].abs().max().item() == 0.0
+
+
+def test_varlen_packed_batch_matches_dense_calls(cuda_device):
+    """flash_attn_varlen_func surface: three sequences packed along the token axis give the bits
+    of three dense calls, and the oracle's tolerance per sequence; one slot is padded
+    (seqused_k)."""
+    Hq, Hkv, D = 4, 2, 128
+    sq, slot_k, used_k = [70, 128, 1], [96, 256, 160], [96, 224, 160]
+    cq = [0] + list(np.cumsum(sq))
+    ck = [0] + list(np.cumsum(slot_k))
+    g = torch.Generator().manual_seed(31)
+    q = torch.randn(1, cq[-1], Hq, D, generator=g).bfloat16().to(cuda_device)
+    k = torch.randn(1, ck[-1], Hkv, D, generator=g).bfloat16().to(cuda_device)
+    v = torch.randn(1, ck[-1], Hkv, D, generator=g).bfloat16().to(cuda_device)
+    Q, K, V = fa.quantize_qkv(q, k, v)                      # one tensor scale for the whole pack
+    out, lse = fa.flash_attn_varlen_fp4_func(
+        Q.data[0], K.data[0], V.data[0], Q.sf[0], K.sf[0], V.sf[0], Q.scale, K.scale, V.scale,
+        torch.tensor(cq, dtype=torch.int32), ck, seqused_k=used_k, causal=True, return_lse=True)
+    torch.cuda.synchronize()
+    fa.check_status(cuda_device)
+    assert out.shape == (cq[-1], Hq, D) and lse.shape == (Hq, cq[-1])
+    for i in range(3):
+        q0, q1, k0, k1 = cq[i], cq[i + 1], ck[i], ck[i] + used_k[i]
+        Qi = fa.NVFP4Tensor(Q.data[:, q0:q1].contiguous(), Q.sf[:, q0:q1].contiguous(), Q.scale)
+        Ki = fa.NVFP4Tensor(K.data[:, k0:k1].contiguous(), K.sf[:, k0:k1].contiguous(), K.scale)
+        Vi = fa.NVFP4Tensor(V.data[..., k0 // 2:k1 // 2].contiguous(), V.sf[..., k0 // 16:k1 // 16].contiguous(),
+                            V.scale, is_v=True)
+        o_d, l_d = fa.flash_attn_func(Qi, Ki, Vi, causal=True, return_lse=True)
+        assert torch.equal(out[q0:q1], o_d[0]) and torch.equal(lse[:, q0:q1], l_d[0])
+        assert_parity(o_d, l_d, *oracles(Qi, Ki, Vi, True))

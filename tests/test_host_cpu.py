@@ -240,3 +240,14 @@ def test_oracle_window_masks_match_reference_formula():
                 masked = (right is not None and j > i + sk - sq + right) or \
                          (left is not None and j < i + sk - sq - left)
                 assert bool(m[i, j]) == masked
+
+
+def test_varlen_surface_rejects_bad_offsets_before_any_launch():
+    z = lambda *s: torch.zeros(*s, dtype=torch.uint8)
+    args = (z(48, 2, 64), z(80, 1, 64), z(1, 128, 40), z(48, 2, 8), z(80, 1, 8), z(1, 128, 5), 1.0, 1.0, 1.0)
+    with pytest.raises(NotImplementedError):          # key boundary 48 is not a multiple of 32
+        fa.flash_attn_varlen_fp4_func(*args, [0, 16, 48], [0, 48, 80])
+    with pytest.raises(AssertionError):               # offsets do not cover the packed tensor
+        fa.flash_attn_varlen_fp4_func(*args, [0, 16, 40], [0, 32, 80])
+    with pytest.raises(AssertionError):               # different batch sizes
+        fa.flash_attn_varlen_fp4_func(*args, [0, 48], [0, 32, 80])
