@@ -213,43 +213,49 @@ __device__ __noinline__ void mask_scores_in_tmem_range(uint32_t taddr, int lower
 template <bool kHasColumns>
 __device__ __noinline__ void store_accumulator_chunk(uint32_t taddr, __nv_bfloat16* dst, float scale,
                                                      uint32_t o_free_bar) {
-  uint32_t o[32];
-  if (o_free_bar != 0u) {
-    if constexpr (kHasColumns) {
-      tmem_ld32(taddr, o);
-      tc_wait_ld();
-    }
-    tc_fence_before_sync();
-    mbar_arrive(o_free_bar);
-  }
-  if (!(scale != 0.f)) {
+  if (o_free_bar == 0u) {
+    // the tile saw no K/V block: nothing in tensor memory to read, the rows are zero
+    if (dst != nullptr) {
+      uint4* d4 = reinterpret_cast<uint4*>(dst);
 #pragma unroll
-    for (int x = 0; x < 32; ++x) o[x] = 0u;
+      for (int v = 0; v < 4; ++v) d4[v] = make_uint4(0u, 0u, 0u, 0u);
+    }
+    return;
   }
-  if (dst != nullptr) store_out_32(dst, o, scale);  // null: a row beyond Sq of a partial tile
+  uint32_t o[32];
+  if constexpr (kHasColumns) {
+    tmem_ld32(taddr, o);
+    tc_wait_ld();
+  }
+  tc_fence_before_sync();
+  mbar_arrive(o_free_bar);
+  // scale == 0 (a row whose keys were all masked): the accumulator holds finite sums of zeros,
+  // so the product is the zero row that is wanted
+  if (kHasColumns && dst != nullptr) store_out_32(dst, o, scale);  // null: a row beyond Sq
 }
 
 // Split-KV flavour of the same step: the 32 columns go out as fp32 (normalised by this split's
 // row sum) into the partial-output workspace.
 __device__ __noinline__ void store_accumulator_partial(uint32_t taddr, float* dst, float scale,
                                                        uint32_t o_free_bar) {
-  uint32_t o[32];
-  if (o_free_bar != 0u) {
-    tmem_ld32(taddr, o);
-    tc_wait_ld();
-    tc_fence_before_sync();
-    mbar_arrive(o_free_bar);
-  }
-  if (dst == nullptr) return;
   float4* d4 = reinterpret_cast<float4*>(dst);
+  if (o_free_bar == 0u) {
+    if (dst != nullptr) {
+#pragma unroll
+      for (int v = 0; v < 8; ++v) d4[v] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    return;
+  }
+  uint32_t o[32];
+  tmem_ld32(taddr, o);
+  tc_wait_ld();
+  tc_fence_before_sync();
+  mbar_arrive(o_free_bar);
+  if (dst == nullptr) return;
 #pragma unroll
   for (int v = 0; v < 8; ++v) {
-    float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (scale != 0.f) {
-      w = make_float4(__uint_as_float(o[4 * v]) * scale, __uint_as_float(o[4 * v + 1]) * scale,
-                      __uint_as_float(o[4 * v + 2]) * scale, __uint_as_float(o[4 * v + 3]) * scale);
-    }
-    d4[v] = w;
+    d4[v] = make_float4(__uint_as_float(o[4 * v]) * scale, __uint_as_float(o[4 * v + 1]) * scale,
+                        __uint_as_float(o[4 * v + 2]) * scale, __uint_as_float(o[4 * v + 3]) * scale);
   }
 }
 
