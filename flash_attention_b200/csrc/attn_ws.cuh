@@ -96,6 +96,9 @@ namespace ws {
 constexpr int kStagesK = 4;
 constexpr int kStagesV = 4;
 constexpr int kStagesP = 4;   // P tiles in shared memory (a block's P is rewritten once PV of block G-4 is done)
+// The softmax warps learn that P tile G % kStagesP is free from the pv_done barrier of block
+// G - kStagesP, whose phase must not have been reused by a later block yet.
+static_assert(kStagesP <= kStagesV, "P tiles are recycled through the pv_done barriers of the V stages");
 constexpr int kThreads = 768;
 constexpr int kStatsWarp0 = 16;
 constexpr int kProducerWarp = 20;
