@@ -50,7 +50,8 @@
 // Barriers (all mbarriers, every wait bounded):
 //   q_full[2]/q_empty[2] producer <-> QK issuer  Q tile + scales of a tile (q_empty by commit)
 //   k_full[], v_full[]   producer -> issuers     K / V tile + scales landed in ring stage
-//   s_full[stage]        QK issuer -> stats      S buffer holds block G (tcgen05.commit); also
+//   s_full[stage]        QK issuer -> stats      S buffer holds block G (tcgen05.commit; the softmax
+//                                                warps learn it through st_ready); also
 //                                                tells the producer that the K stage is free
 //   s_free[2]            stats + softmax -> QK issuer: S buffer read by all (384 arrivals)
 //   st_ready[2]          stats -> softmax        exponents of block G published (128 arrivals)
@@ -655,26 +656,20 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         const uint32_t G = gb + i, b = G & 1;  // b == g: S / P / stats buffer of this block
         const int nb = (kGeneral ? t.nb_top : n - 1) - i;
         FA4_TRACE_EV(1, G);
-        // Probe the three barriers this block depends on back to back so that their latencies
-        // overlap; the blocking (bounded) wait only runs for a probe that failed.
-        const uint32_t bar_s = bars.at(Bars::kSFull + (G % kStagesK)), par_s = (G / kStagesK) & 1;
+        // Probe the barriers this block depends on early so that their latencies overlap; the
+        // blocking (bounded) wait only runs for a probe that failed.
         const uint32_t bar_r = bars.at(Bars::kStReady + b), par_r = (G >> 1) & 1;
         const uint32_t bar_p = bars.at(Bars::kPvDone + ((G - kStagesP) % kStagesV)),
                        par_p = ((G - kStagesP) / kStagesV) & 1;
-        const bool r_s = mbar_test(bar_s, par_s);
         const bool r_p = (G >= kStagesP) ? mbar_test(bar_p, par_p) : true;
 
-        // 1. scores: copied to registers as soon as the MMA has written them, so that the S buffer
-        //    goes back to the QK^T issuer without waiting for the statistics (the buffer's cycle
-        //    MMA -> readers -> MMA bounds the block rate)
-        ok = wait_probed(r_s, bar_s, par_s, wc, kSiteSFull);
+        // 1. the statistics of this block are published only after its Q K^T has completed and
+        //    been read by the statistics warps (which waited on s_full and fenced), so this one
+        //    wait covers the scores as well; it saves a barrier round trip per block
+        ok = wait_probed(mbar_test(bar_r, par_r), bar_r, par_r, wc, kSiteStReady);
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t s_addr = lane_addr + (b ? kTmS1 : kTmS0) + 64 * half;
-        // diagonal block: this thread overwrites the masked keys of its own half row in tensor
-        // memory before loading it (out of line, nothing large is live yet).  The statistics
-        // warps may be reading the same row: they mask what they read themselves, and the visible
-        // keys are not changed.
         if (block_needs_mask<kGeneral>(p, t, nb)) {
           if constexpr (kGeneral) {
             mask_scores_in_tmem_range(s_addr, lower_limit(p, t, row, nb) - 64 * half,
@@ -686,13 +681,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         float s[64];
         tmem_ld32(s_addr, reinterpret_cast<uint32_t*>(&s[0]));
         tmem_ld32(s_addr + 32, reinterpret_cast<uint32_t*>(&s[32]));
-        tc_wait_ld();
-        tc_fence_before_sync();
-        mbar_arrive(bars.at(Bars::kSFree + b));
-
-        // 2. this row's exponents from the statistics warpgroup
-        ok = wait_probed(mbar_test(bar_r, par_r), bar_r, par_r, wc, kSiteStReady);
-        if (!ok) break;
+        // 2. read the statistics while the scores travel
         const uint4* st_row = reinterpret_cast<const uint4*>(&s_stats[b * 128 + row]);
         const uint4 v_bm = st_row[half];
         const uint4 v_misc = st_row[2];
@@ -703,9 +692,11 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         float noff4[4];
         uint32_t ue;
         block_exponents4(bm4, m_new, p.sl2, noff4, ue);
-        // own partial row sum follows the reference
         if (m_new != m_ref) l_sum *= reference_factor(m_ref, m_new, p.sl2);
         m_ref = m_new;
+        tc_wait_ld();
+        tc_fence_before_sync();
+        mbar_arrive(bars.at(Bars::kSFree + b));
 
         // 3. exponentials and quantisation; P tile G % kStagesP is free once PV of block
         //    G - kStagesP has completed
