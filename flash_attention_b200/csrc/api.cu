@@ -34,6 +34,19 @@ PFN_cuTensorMapEncodeTiled_v12000 get_encode() {
 
 // Byte tensor of rank 4, innermost dimension contiguous; box = {box0, box1, box2, box3} bytes /
 // rows; 64-byte swizzle when the innermost box is 64 bytes.
+// bf16 output tensor (B, Sq, Hq, Dv) as {Dv, Hq, Sq, B}; box = 64 columns x 128 rows, 128-byte
+// swizzle (the staging layout of the warp-specialised kernel's epilogue).
+bool encode_out_4d(CUtensorMap* m, void* base, const uint64_t (&dims)[4], const uint64_t (&strides)[3]) {
+  auto fn = get_encode();
+  if (fn == nullptr) return false;
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const cuuint32_t box[4] = {64, 1, 128, 1};
+  const CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, base, dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 bool encode_u8_4d(CUtensorMap* m, const void* base, const uint64_t (&dims)[4],
                   const uint64_t (&strides)[3], const uint32_t (&box)[4], CUtensorMapSwizzle sw) {
   auto fn = get_encode();
@@ -209,9 +222,16 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
     if (ce == cudaSuccess) ce = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (ce != cudaSuccess) return (int)ce;
     const unsigned grid = tiles < (unsigned)sms ? tiles : (unsigned)sms;
+    CUtensorMap tm_o;
+    {
+      const uint64_t d_o[4] = {(uint64_t)p->Dv, (uint64_t)p->Hq, (uint64_t)p->Sq, (uint64_t)p->B};
+      const uint64_t s_o[3] = {(uint64_t)p->o_stride_h * 2, (uint64_t)p->o_stride_s * 2,
+                               (uint64_t)p->o_stride_b * 2};
+      if (!encode_out_4d(&tm_o, p->out, d_o, s_o)) return -FA4_E_TENSORMAP;
+    }
     auto launch = [&](auto kernel) -> int {
       if (int e = ensure_smem(kernel, ws::kSmemRequest)) return e;
-      kernel<<<grid, ws::kThreads, ws::kSmemRequest, stream>>>(tm_q, tm_k, tm_v, kp);
+      kernel<<<grid, ws::kThreads, ws::kSmemRequest, stream>>>(tm_q, tm_k, tm_v, tm_o, kp);
       return 0;
     };
     int rc;

@@ -6,7 +6,7 @@
 //               (64 keys).  warpgroup k = warp / 4:  column half = k & 1 (keys 0-63 / 64-127),
 //               block parity = k >> 1 (blocks 0,2,4,.. / 1,3,5,.. of a tile in visit order,
 //               so that the summation order of a row depends on its tile only).
-//               exponentials, P -> e2m1, row sums, O correction, epilogue
+//               exponentials, P -> e2m1, row sums, O correction, O -> bf16 staging tile
 //   warps 16-19 statistics warpgroup: for EVERY block, in order, reads S from tensor memory in
 //               32-column chunks, keeps the running reference maximum of each row and publishes
 //               the block maxima and the reference in shared memory (the softmax threads derive
@@ -15,7 +15,7 @@
 //   warp 21     QK^T issuer: tcgen05.cp of the Q/K scale factors and the block-scaled tcgen05.mma
 //               for S = Q K^T (two S buffers in tensor memory); owns tensor memory
 //   warp 22     PV issuer: tcgen05.cp of the P/V scale factors and tcgen05.mma for O += P V
-//   warp 23     idle (completes the warpgroup for setmaxnreg)
+//   warp 23     output store: sends the staged bf16 O tile of every query tile with TMA
 //
 // Why this shape (measured on B200, see the timeline facility below):
 //  * The exponentials of a block cost 1024 clocks of the XU pipe per SM (16 ex2/clk), far more
@@ -63,6 +63,8 @@
 //                                                stage free, O stable (tcgen05.commit)
 //   fin                  softmax warpgroups      partial row sums published (512, once per tile)
 //   o_free               softmax -> PV issuer    O copied to registers (512, once per tile)
+//   o_staged             softmax -> store warp   bf16 O tile complete in the staging buffer (512)
+//   stage_free           store warp -> softmax   TMA has read the staging buffer (1)
 //   drain[2]             issuers                 tensor-core work drained on the abort path
 #pragma once
 #include "attn_common.cuh"
@@ -105,6 +107,7 @@ constexpr int kStatsWarp0 = 16;
 constexpr int kProducerWarp = 20;
 constexpr int kIssuerWarp = 21;    // QK^T issuer, owns tensor memory
 constexpr int kPvIssuerWarp = 22;
+constexpr int kStoreWarp = 23;     // sends the staged output tile with TMA
 // registers per thread after setmaxnreg: 512 * 96 + 128 * 56 + 128 * 40 = 61440 = 768 * 80
 constexpr int kRegsSoftmax = 96;
 constexpr int kRegsStats = 56;
@@ -132,10 +135,11 @@ constexpr uint32_t kOffSFQ = kOffP + kStagesP * kTileBytes;    // 2 x 1 KB
 constexpr uint32_t kOffSFK = kOffSFQ + 2 * kSfBytes;           // kStagesK x 1 KB
 constexpr uint32_t kOffSFV = kOffSFK + kStagesK * kSfBytes;    // kStagesV x 1 KB
 constexpr uint32_t kOffSFP = kOffSFV + kStagesV * kSfBytes;    // kStagesP x 1 KB
-constexpr uint32_t kOffStats = kOffSFP + kStagesP * kSfBytes;  // 2 x 128 x RowStats
+constexpr uint32_t kOffOut = kOffSFP + kStagesP * kSfBytes;    // 32 KB: bf16 O tile staged for the TMA store
+constexpr uint32_t kOffStats = kOffOut + 32 * 1024;            // 2 x 128 x RowStats
 constexpr uint32_t kOffFin = kOffStats + 2 * 128 * 48;         // 2 tiles x 4 WGs x 128 x (sum, ref)
 constexpr uint32_t kOffBar = kOffFin + 2 * 4 * 128 * 8;
-constexpr int kNumBars = 4 + 2 * kStagesK + 2 * kStagesV + 2 * 3 + kStagesP + 4;
+constexpr int kNumBars = 4 + 2 * kStagesK + 2 * kStagesV + 2 * 3 + kStagesP + 4 + 2;
 constexpr uint32_t kOffMisc = kOffBar + 8 * kNumBars;          // tmem slot, abort flag
 constexpr uint32_t kSmemUsed = kOffMisc + 16;
 constexpr uint32_t kSmemRequest = kSmemUsed + 1024;
@@ -143,7 +147,8 @@ static_assert(kSmemRequest > 114 * 1024, "one CTA per SM: every CTA allocates al
 
 enum Site {
   kSiteQFull = 10, kSiteQEmpty, kSiteKEmpty, kSiteVEmpty, kSiteKFull, kSiteVFull, kSiteSFull,
-  kSiteSFree, kSitePFull, kSitePvDone, kSiteStReady, kSiteStFree, kSiteFin, kSiteFinalO, kSiteOFree
+  kSiteSFree, kSitePFull, kSitePvDone, kSiteStReady, kSiteStFree, kSiteFin, kSiteFinalO, kSiteOFree,
+  kSiteOStaged, kSiteStageFree
 };
 
 // barrier indices (8 bytes each from the barrier base); kept as constants so that only the base
@@ -154,7 +159,8 @@ struct Bars {
                             kSFull = kVFull + kStagesV, kPvDone = kSFull + kStagesK,
                             kSFree = kPvDone + kStagesV, kStReady = kSFree + 2, kStFree = kStReady + 2,
                             kPFull = kStFree + 2, kFin = kPFull + kStagesP, kOFree = kFin + 1,
-                            kDrain = kOFree + 1, kCount = kDrain + 2;
+                            kDrain = kOFree + 1, kOStaged = kDrain + 2, kStageFree = kOStaged + 1,
+                            kCount = kStageFree + 1;
   __device__ explicit Bars(uint32_t b) : base(b) {}
   __device__ __forceinline__ uint32_t at(uint32_t idx) const { return base + 8u * idx; }
 };
@@ -212,17 +218,24 @@ __device__ __noinline__ void mask_scores_in_tmem_range(uint32_t taddr, int lower
 }
 
 // Tile end: 32 accumulator columns of this thread's row -> registers (then the accumulator may be
-// overwritten: arrive on o_free_bar), scaled, rounded to bf16 and stored.  o_free_bar == 0: the
-// tile had no visible key, nothing to read, zeros are stored.
+// overwritten: arrive on o_free_bar), scaled, rounded to bf16 and written into the staging tile in
+// shared memory, from where the store warp sends whole 128-byte rows with TMA (rows past Sq of a
+// partial tile are clipped by the tensor map).  Staging layout: boxes of 64 output columns, 128
+// rows x 128 bytes each, with the 128-byte swizzle of the tensor map: 16-byte chunk j of row r sits
+// at chunk j ^ (r % 8).  o_free_bar == 0: the tile had no visible key, nothing to read, zeros are
+// staged.  Direct 16-byte row stores from the softmax threads cost ~2000 clocks per tile in the
+// load/store unit (32 different rows per instruction).
 template <bool kHasColumns>
-__device__ __noinline__ void store_accumulator_chunk(uint32_t taddr, __nv_bfloat16* dst, float scale,
-                                                     uint32_t o_free_bar) {
+__device__ __noinline__ void stage_accumulator_chunk(uint32_t taddr, uint8_t* staging, int row, int wg,
+                                                     float scale, uint32_t o_free_bar) {
+  uint8_t* box_row = staging + (wg >> 1) * (16 * 1024) + row * 128;
   if (o_free_bar == 0u) {
-    // the tile saw no K/V block: nothing in tensor memory to read, the rows are zero
-    if (dst != nullptr) {
-      uint4* d4 = reinterpret_cast<uint4*>(dst);
+    if constexpr (kHasColumns) {
 #pragma unroll
-      for (int v = 0; v < 4; ++v) d4[v] = make_uint4(0u, 0u, 0u, 0u);
+      for (int v = 0; v < 4; ++v) {
+        const int chunk = ((wg & 1) * 4 + v) ^ (row & 7);
+        *reinterpret_cast<uint4*>(box_row + chunk * 16) = make_uint4(0u, 0u, 0u, 0u);
+      }
     }
     return;
   }
@@ -233,9 +246,18 @@ __device__ __noinline__ void store_accumulator_chunk(uint32_t taddr, __nv_bfloat
   }
   tc_fence_before_sync();
   mbar_arrive(o_free_bar);
-  // scale == 0 (a row whose keys were all masked): the accumulator holds finite sums of zeros,
-  // so the product is the zero row that is wanted
-  if (kHasColumns && dst != nullptr) store_out_32(dst, o, scale);  // null: a row beyond Sq
+  if constexpr (kHasColumns) {
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      uint4 w;
+      w.x = pack_bf16x2(__uint_as_float(o[8 * v + 0]) * scale, __uint_as_float(o[8 * v + 1]) * scale);
+      w.y = pack_bf16x2(__uint_as_float(o[8 * v + 2]) * scale, __uint_as_float(o[8 * v + 3]) * scale);
+      w.z = pack_bf16x2(__uint_as_float(o[8 * v + 4]) * scale, __uint_as_float(o[8 * v + 5]) * scale);
+      w.w = pack_bf16x2(__uint_as_float(o[8 * v + 6]) * scale, __uint_as_float(o[8 * v + 7]) * scale);
+      const int chunk = ((wg & 1) * 4 + v) ^ (row & 7);
+      *reinterpret_cast<uint4*>(box_row + chunk * 16) = w;
+    }
+  }
 }
 
 // Split-KV flavour of the same step: the 32 columns go out as fp32 (normalised by this split's
@@ -291,7 +313,8 @@ template <int kD, bool kGeneral>
 __global__ void __launch_bounds__(ws::kThreads, 1)
 attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
                    const __grid_constant__ CUtensorMap tm_k,
-                   const __grid_constant__ CUtensorMap tm_v, const KernelParams p) {
+                   const __grid_constant__ CUtensorMap tm_v,
+                   const __grid_constant__ CUtensorMap tm_o, const KernelParams p) {
   using namespace ws;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -326,6 +349,8 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
     for (int s = 0; s < kStagesV; ++s) mbar_init(bars.at(Bars::kPvDone + s), 1);
     mbar_init(bars.at(Bars::kFin), 512);
     mbar_init(bars.at(Bars::kOFree), 512);
+    mbar_init(bars.at(Bars::kOStaged), 512);
+    mbar_init(bars.at(Bars::kStageFree), 1);
     fence_barrier_init();
   }
   if (warp == kProducerWarp && lane == 0) {
@@ -544,6 +569,27 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         tc_commit(bars.at(Bars::kDrain + 1));
         while (!mbar_try_wait(bars.at(Bars::kDrain + 1), 0) && globaltimer_ns() - t0 < 50ull * 1000 * 1000) {}
       }
+    } else if (warp == kStoreWarp && lane == 0) {
+      // ========================================= output store ===================================
+      // (the split-KV path writes fp32 partial outputs directly and does not use this role)
+      if (!(kGeneral && p.num_splits > 1)) {
+        tma_prefetch_desc(&tm_o);
+        FA4_FOR_EACH_TILE {
+          const Tile t = decode_tile<kGeneral>(p, tile);
+          ok = mbar_wait(bars.at(Bars::kOStaged), it & 1, wc, kSiteOStaged);
+          if (!ok) break;
+#pragma unroll
+          for (int bx = 0; bx < kD / 64; ++bx) {
+            tma_store_4d(&tm_o, base + kOffOut + bx * 16 * 1024, 64 * bx, t.h, t.m_blk * kBlockM, t.b);
+          }
+          bulk_commit_group();
+          bulk_wait_group_read0();
+          mbar_arrive(bars.at(Bars::kStageFree));
+          (void)gb;
+          (void)ti;
+        }
+        bulk_wait_group0();  // the last stores complete before the CTA's shared memory goes away
+      }
     }
   } else if (warp >= kStatsWarp0) {
     // =========================================== statistics warpgroup ===========================
@@ -736,8 +782,6 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
 
       // ---- tile end: combine the four partial row sums, read O, store ---------------------------
       const int q_idx = t.m_blk * kBlockM + row;
-      __nv_bfloat16* orow =
-          p.out + t.b * p.o_stride_b + (int64_t)q_idx * p.o_stride_s + t.h * p.o_stride_h + 32 * wg;
       float scale = 0.f, m_fin = kNegInf, l_tot = 0.f;
       if (n > 0) {
         volatile float* fin_slot = s_fin + (ti & 1) * (4 * 128 * 2);
@@ -781,11 +825,20 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
                       ((((int64_t)t.split * p.B + t.b) * p.Sq + q_idx) * p.Hq + t.h) * kD + 32 * wg;
         store_accumulator_partial(lane_addr + kTmO + 32 * wg, q_idx < p.Sq ? prow : nullptr, scale,
                                   n > 0 ? bars.at(Bars::kOFree) : 0u);
-      } else if (kD == 128 || wg < kD / 32) {
-        store_accumulator_chunk<true>(lane_addr + kTmO + 32 * wg, q_idx < p.Sq ? orow : nullptr, scale,
-                                      n > 0 ? bars.at(Bars::kOFree) : 0u);
       } else {
-        store_accumulator_chunk<false>(0u, nullptr, 0.f, n > 0 ? bars.at(Bars::kOFree) : 0u);
+        if (it >= 1) {
+          // the staging tile is free once the store warp's TMA has read the previous tile out of it
+          ok = __all_sync(0xffffffffu, mbar_wait(bars.at(Bars::kStageFree), (it - 1) & 1, wc, kSiteStageFree));
+          if (!ok) break;
+        }
+        if (kD == 128 || wg < kD / 32) {
+          stage_accumulator_chunk<true>(lane_addr + kTmO + 32 * wg, gbase + kOffOut, row, wg, scale,
+                                        n > 0 ? bars.at(Bars::kOFree) : 0u);
+        } else {
+          stage_accumulator_chunk<false>(0u, gbase + kOffOut, row, wg, 0.f, n > 0 ? bars.at(Bars::kOFree) : 0u);
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(bars.at(Bars::kOStaged));
       }
       if (wg == 0 && q_idx < p.Sq) {
         float lse_v = finish_lse(m_fin, l_tot, p.sl2);
