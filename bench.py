@@ -356,10 +356,10 @@ def run_gpu_arm(args, wl, rank, local_rank, world):
 
 
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the attention kernel,
-# from the ncu captures summarised under profiles/.  cfg2 was captured whole (116.9 MB read +
-# 219.7 MB written); cfg1 is the capture of half of it (B = 2: 81.9 MB + 58.3 MB) scaled by the
+# from the ncu captures summarised under profiles/.  cfg2 was captured whole (118.8 MB read +
+# 220.1 MB written); cfg1 is the capture of half of it (B = 2: 81.9 MB + 58.3 MB) scaled by the
 # batch, which the traffic is proportional to.  None for workloads that were not captured.
-TRAFFIC_BYTES = {"cfg2": 336_628_992, "cfg1": 2 * 140_234_752}
+TRAFFIC_BYTES = {"cfg2": 338_914_304, "cfg1": 2 * 140_234_752}
 
 
 def run_sweep(args):
