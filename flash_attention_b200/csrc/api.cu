@@ -5,6 +5,7 @@
 #include "attn_common.cuh"
 #include "attn_serial.cuh"
 #include "attn_ws.cuh"
+#include "attn_ws64.cuh"
 #include "aux_kernels.cuh"
 #include "quantize.cuh"
 
@@ -139,7 +140,10 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
     if (s <= 0 || (s & 15) != 0) return -FA4_E_STRIDE;
   if ((p->o_stride_b & 7) || (p->o_stride_s & 7) || (p->o_stride_h & 7)) return -FA4_E_STRIDE;
   int variant = p->variant == FA4_VARIANT_AUTO ? FA4_VARIANT_WS : p->variant;
-  if (variant != FA4_VARIANT_SERIAL && variant != FA4_VARIANT_WS) return -FA4_E_VARIANT;
+  if (variant != FA4_VARIANT_SERIAL && variant != FA4_VARIANT_WS && variant != FA4_VARIANT_WS64)
+    return -FA4_E_VARIANT;
+  if (variant == FA4_VARIANT_WS64 && (p->D != 128 || num_splits > 1 || win_left >= 0 || win_right > 0 || sink))
+    return -FA4_E_SHAPE;
   if (variant == FA4_VARIANT_SERIAL && p->D != 128) return -FA4_E_SHAPE;  // bring-up kernel: 128 only
   // window limits: `causal` is the right limit 0; an explicit right limit overrides it
   if (p->causal && win_right < 0) win_right = 0;
@@ -235,7 +239,11 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
       return 0;
     };
     int rc;
-    if (p->D == 128) {
+    if (variant == FA4_VARIANT_WS64) {
+      if (int e = ensure_smem(attn_fwd_ws64_kernel, ws64::kSmemRequest)) return e;
+      attn_fwd_ws64_kernel<<<grid, ws64::kThreads, ws64::kSmemRequest, stream>>>(tm_q, tm_k, tm_v, tm_o, kp);
+      rc = 0;
+    } else if (p->D == 128) {
       rc = general ? launch(attn_fwd_ws_kernel<128, true>) : launch(attn_fwd_ws_kernel<128, false>);
     } else {
       rc = general ? launch(attn_fwd_ws_kernel<64, true>) : launch(attn_fwd_ws_kernel<64, false>);

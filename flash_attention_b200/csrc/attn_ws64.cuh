@@ -1,0 +1,588 @@
+// Warp-specialised kernel with 64-key sub-blocks and FOUR score buffers (head dim 128).
+//
+// The kernel of attn_ws.cuh keeps two 128-column S buffers in tensor memory and lets two pairs of
+// softmax warpgroups alternate over the 128-key blocks, a thread owning half a row.  The two
+// warpgroups of a pair move in lockstep, so a scheduler sees only two independent softmax
+// "strands", each with ~1000 clocks of exponentials and ~2000 clocks of latency-bound prologue /
+// epilogue per block: the exponential unit idles ~40 % of the time.
+//
+// Here a K/V block of 128 keys is processed as two sub-blocks of 64 keys, S has four buffers of 64
+// columns (the same 256 tensor-memory columns), and each of the four softmax warpgroups owns one
+// buffer: a thread holds the 64 scores of one row of one sub-block -- the same register footprint
+// -- but the four warpgroups are independent strands at different phases, and the statistics
+// warpgroup can run up to three sub-blocks ahead of the slowest of them.
+//
+//   warps 0-15  softmax: warpgroup w takes the sub-blocks with running index J % 4 == w
+//   warps 16-19 statistics: every sub-block in order (maxima of its four 16-key blocks, the
+//               running reference maximum)
+//   warp 20     TMA producer (Q double buffered, K / V rings of 128-key tiles)
+//   warp 21     QK^T issuer: per K tile two N = 64 products into two S buffers
+//   warp 22     P V issuer: per sub-block one K = 64 step into O
+//   warp 23     output store (TMA)
+//
+// Sub-block j of a tile (visit order): block i = j / 2 (last visible block first), upper half of
+// the block (keys 64-127) first.  J = 2 * (blocks before this tile) + j selects buffers, P slots
+// and barrier phases.  Everything else (operand formats, P quantisation, lazy reference, bounded
+// waits, epilogue) is as in attn_ws.cuh.
+#pragma once
+#include "attn_ws.cuh"
+
+// Optional phase profile (compile with -DFA4_TRACE -DFA4_PHASES): every warp of one CTA accumulates
+// the clocks it spends between marks in registers and lane 0 dumps them when the kernel ends.
+#ifdef FA4_PHASES
+#undef FA4_TRACE_EV
+#define FA4_TRACE_EV(ev, idx) do {} while (0)
+#define FA4_PH_DECL uint32_t ph_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; uint32_t ph_t = clock();
+#define FA4_PH_RESET() do { ph_t = clock(); } while (0)
+#define FA4_PH(k) do { const uint32_t c_ = clock(); ph_acc[k] += c_ - ph_t; ph_t = c_; } while (0)
+#define FA4_PH_DUMP()                                                                         \
+  do {                                                                                        \
+    if (g_trace_buf != nullptr && (int)blockIdx.x == g_trace_cta && (threadIdx.x & 31) == 0) { \
+      for (int k_ = 0; k_ < 8; ++k_) g_trace_buf[(threadIdx.x >> 5) * 8 + k_] = ph_acc[k_];    \
+    }                                                                                         \
+  } while (0)
+#else
+#define FA4_PH_DECL
+#define FA4_PH_RESET() do {} while (0)
+#define FA4_PH(k) do {} while (0)
+#define FA4_PH_DUMP() do {} while (0)
+#endif
+
+namespace fa4 {
+namespace ws64 {
+
+constexpr int kStagesK = 4, kStagesV = 4;  // 128-key tiles
+constexpr int kSBufs = 4;                  // S buffers of 64 columns
+constexpr int kPSlots = 8;                 // P tiles of 64 keys (4 KB each)
+constexpr int kThreads = 640;
+constexpr int kProducerWarp = 16, kIssuerWarp = 17, kPvIssuerWarp = 18, kStoreWarp = 19;
+// 640 threads launch with 96 registers each.  setmaxnreg.inc draws from the pool the CTA was
+// launched with (threads x launch registers), NOT from the whole register file, and blocks until
+// the pool can serve it: a total above the launch total never returns.
+constexpr int kRegsSoftmax = 104, kRegsOther = 40, kRegsLaunch = 96;
+static_assert(kThreads * kRegsLaunch <= 65536, "register file");
+static_assert(512 * kRegsSoftmax + 128 * kRegsOther <= kThreads * kRegsLaunch, "register pool of the CTA");
+
+// tensor memory: S[4] x 64 columns, O 128, scale factors
+// (O at column 256, Q scales at 384, K scales at 392 (2 x 8) as in the 128-key kernel)
+constexpr uint32_t kTmS64 = 0, kTmSFV64 = 408 /* 4 x 4 */, kTmSFP64 = 424 /* 4 x 4 */;
+constexpr uint32_t kPTileBytes = 128 * 32;  // 128 rows x 64 e2m1 keys
+
+constexpr uint32_t kOffQ = 0;
+constexpr uint32_t kOffK = kOffQ + 2 * kTileBytes;
+constexpr uint32_t kOffV = kOffK + kStagesK * kTileBytes;
+constexpr uint32_t kOffP = kOffV + kStagesV * kTileBytes;
+constexpr uint32_t kOffSFQ = kOffP + kPSlots * kPTileBytes;
+constexpr uint32_t kOffSFK = kOffSFQ + 2 * kSfBytes;
+constexpr uint32_t kOffSFV = kOffSFK + kStagesK * kSfBytes;
+constexpr uint32_t kOffSFP = kOffSFV + kStagesV * kSfBytes;      // kPSlots x 512
+constexpr uint32_t kOffOut = kOffSFP + kPSlots * 512;            // 32 KB staging tile
+constexpr uint32_t kOffHand = kOffOut + 32 * 1024;               // kSBufs x 128 reference maxima
+constexpr uint32_t kOffFin = kOffHand + kSBufs * 128 * 4;        // 2 tiles x 4 WGs x 128 x (sum, ref)
+constexpr uint32_t kOffBar = kOffFin + 2 * 4 * 128 * 8;
+
+struct Bars {
+  uint32_t base;
+  static constexpr uint32_t kQFull = 0, kQEmpty = 2, kKFull = 4, kVFull = kKFull + kStagesK,
+                            kKFree = kVFull + kStagesV, kVFree = kKFree + kStagesK,
+                            kSFull = kVFree + kStagesV, kSFree = kSFull + kSBufs,
+                            kHand = kSFree + kSBufs, kPFull = kHand + kSBufs, kPvDone = kPFull + kPSlots,
+                            kFin = kPvDone + kPSlots, kOFree = kFin + 1, kOStaged = kOFree + 1,
+                            kStageFree = kOStaged + 1, kDrain = kStageFree + 1, kCount = kDrain + 2;
+  __device__ explicit Bars(uint32_t b) : base(b) {}
+  __device__ __forceinline__ uint32_t at(uint32_t idx) const { return base + 8u * idx; }
+};
+constexpr uint32_t kOffMisc = kOffBar + 8 * Bars::kCount;
+constexpr uint32_t kSmemUsed = kOffMisc + 16;
+constexpr uint32_t kSmemRequest = kSmemUsed + 1024;
+static_assert(kSmemRequest <= 227 * 1024, "shared memory");
+
+enum Site64 {
+  kS64QFull = 40, kS64QEmpty, kS64KFree, kS64VFree, kS64KFull, kS64VFull, kS64SFull, kS64SFree,
+  kS64PFull, kS64PvDone, kS64Hand, kS64Fin, kS64FinalO, kS64OFree, kS64OStaged,
+  kS64StageFree
+};
+
+// byte offset of 16-byte chunk c (0, 1) of row r in a P tile (rows of 32 bytes, 32-byte swizzle)
+__device__ __forceinline__ uint32_t sw32_offset(uint32_t row, uint32_t chunk) {
+  return row * 32u + ((chunk ^ ((row >> 2) & 1u)) << 4);
+}
+
+}  // namespace ws64
+
+__global__ void __launch_bounds__(ws64::kThreads, 1)
+attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
+                     const __grid_constant__ CUtensorMap tm_k,
+                     const __grid_constant__ CUtensorMap tm_v,
+                     const __grid_constant__ CUtensorMap tm_o, const KernelParams p) {
+  using namespace ws64;
+  using ws::rescale_accumulator;
+  using ws::mask_scores_in_tmem;
+  using ws::stage_accumulator_chunk;
+  using ws::tile_of_round;
+  using ws::wait_probed;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gbase = smem_raw + (base - smem_u32(smem_raw));
+  const Bars bars(base + kOffBar);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + kOffMisc);
+  volatile uint32_t* s_abort = reinterpret_cast<volatile uint32_t*>(gbase + kOffMisc + 4);
+  volatile float* s_hand = reinterpret_cast<volatile float*>(gbase + kOffHand);  // [4][128]
+  volatile float* s_fin = reinterpret_cast<volatile float*>(gbase + kOffFin);    // [2][4][128][2]
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const WaitCtx wc{s_abort, p.status, p.budget_ns};
+  const int num_tiles = p.num_m_blocks * p.Hq * p.B;
+  const int ncta = gridDim.x, cta = blockIdx.x;
+  FA4_TRACE_DECL
+  FA4_PH_DECL
+
+  if (tid == 0) {
+    *s_abort = 0u;
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bars.at(Bars::kQFull + b), 1);
+      mbar_init(bars.at(Bars::kQEmpty + b), 1);
+      mbar_init(bars.at(Bars::kDrain + b), 1);
+    }
+    for (int s = 0; s < kStagesK; ++s) {
+      mbar_init(bars.at(Bars::kKFull + s), 1);
+      mbar_init(bars.at(Bars::kKFree + s), 1);
+    }
+    for (int s = 0; s < kStagesV; ++s) {
+      mbar_init(bars.at(Bars::kVFull + s), 1);
+      mbar_init(bars.at(Bars::kVFree + s), 1);
+    }
+    for (int s = 0; s < kSBufs; ++s) {
+      mbar_init(bars.at(Bars::kSFull + s), 1);
+      mbar_init(bars.at(Bars::kSFree + s), 128);    // the softmax warpgroup that owns the buffer
+      mbar_init(bars.at(Bars::kHand + s), 128);
+    }
+    for (int s = 0; s < kPSlots; ++s) {
+      mbar_init(bars.at(Bars::kPFull + s), 128);
+      mbar_init(bars.at(Bars::kPvDone + s), 1);
+    }
+    mbar_init(bars.at(Bars::kFin), 512);
+    mbar_init(bars.at(Bars::kOFree), 512);
+    mbar_init(bars.at(Bars::kOStaged), 512);
+    mbar_init(bars.at(Bars::kStageFree), 1);
+    fence_barrier_init();
+  }
+  if (warp == kProducerWarp && lane == 0) {
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+  }
+  if (warp == kIssuerWarp) {
+    tmem_alloc(base + kOffMisc, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+  constexpr uint32_t idesc_qk = make_idesc_nvf4(128, 64);
+  constexpr uint32_t idesc_pv = make_idesc_nvf4(128, 128);
+
+#define FA4_FOR_EACH_TILE                                                                        \
+  uint32_t gb = 0, ti = 0;                                                                       \
+  bool ok = true;                                                                                \
+  for (int it = 0, tile = tile_of_round(0, cta, ncta); ok && tile < num_tiles;                   \
+       ++it, tile = tile_of_round(it, cta, ncta))
+
+  if (warp >= kProducerWarp) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
+    if (warp == kProducerWarp && lane == 0) {
+      // ========================================= TMA producer ===================================
+      uint32_t issued_k = 0, issued_v = 0, issued_q = 0;
+      FA4_FOR_EACH_TILE {
+        const Tile t = decode_tile(p, tile);
+        const int n = t.n_blocks;
+        if (n == 0) continue;
+        if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
+          *s_abort = 1u;  // another CTA failed: stop this one quickly
+          break;
+        }
+        const uint32_t qb = ti & 1;
+        if (ti >= 2) {
+          ok = mbar_wait(bars.at(Bars::kQEmpty + qb), ((ti - 2) >> 1) & 1, wc, kS64QEmpty);
+          if (!ok) break;
+        }
+        mbar_arrive_expect_tx(bars.at(Bars::kQFull + qb), kTileBytes + kSfBytes);
+        tma_load_4d(base + kOffQ + qb * kTileBytes, &tm_q, bars.at(Bars::kQFull + qb), 0, t.h,
+                    t.m_blk * kBlockM, t.b);
+        bulk_load(base + kOffSFQ + qb * kSfBytes,
+                  p.q_sf + t.b * p.qsf_stride_b + t.h * p.qsf_stride_h + (int64_t)t.m_blk * kSfBytes,
+                  kSfBytes, bars.at(Bars::kQFull + qb));
+        issued_q = ti + 1;
+        const uint8_t* ksf = p.k_sf + t.b * p.ksf_stride_b + t.hk * p.ksf_stride_h;
+        const uint8_t* vsf = p.v_sf + t.b * p.vsf_stride_b + t.hk * p.vsf_stride_h;
+        // K runs two blocks ahead of V
+        for (int step = 0; ok && step < n + 2; ++step) {
+          const int ik = step, iv = step - 2;
+          if (ik < n) {
+            const uint32_t G = gb + ik, st = G % kStagesK;
+            const int nb = n - 1 - ik;
+            if (G >= kStagesK) {
+              ok = mbar_wait(bars.at(Bars::kKFree + st), ((G - kStagesK) / kStagesK) & 1, wc, kS64KFree);
+              if (!ok) break;
+            }
+            mbar_arrive_expect_tx(bars.at(Bars::kKFull + st), kTileBytes + kSfBytes);
+            tma_load_4d(base + kOffK + st * kTileBytes, &tm_k, bars.at(Bars::kKFull + st), 0, t.hk,
+                        nb * kBlockN, t.b);
+            bulk_load(base + kOffSFK + st * kSfBytes, ksf + (int64_t)nb * kSfBytes, kSfBytes,
+                      bars.at(Bars::kKFull + st));
+            issued_k = G + 1;
+          }
+          if (iv >= 0 && iv < n) {
+            const uint32_t G = gb + iv, st = G % kStagesV;
+            const int nb = n - 1 - iv;
+            if (G >= kStagesV) {
+              ok = mbar_wait(bars.at(Bars::kVFree + st), ((G - kStagesV) / kStagesV) & 1, wc, kS64VFree);
+              if (!ok) break;
+            }
+            mbar_arrive_expect_tx(bars.at(Bars::kVFull + st), kTileBytes + kSfBytes);
+            tma_load_4d(base + kOffV + st * kTileBytes, &tm_v, bars.at(Bars::kVFull + st),
+                        nb * (kBlockN / 2), 0, t.hk, t.b);
+            bulk_load(base + kOffSFV + st * kSfBytes, vsf + (int64_t)nb * kSfBytes, kSfBytes,
+                      bars.at(Bars::kVFull + st));
+            issued_v = G + 1;
+          }
+        }
+        gb += n;
+        ti += 1;
+      }
+      if (!ok) {
+        // bounded drain: let the copies already issued land before the CTA's memory is released
+        const uint64_t t0 = globaltimer_ns();
+        const uint64_t lim = 50ull * 1000 * 1000;
+        for (uint32_t i = issued_k > kStagesK ? issued_k - kStagesK : 0; i < issued_k; ++i) {
+          while (!mbar_try_wait(bars.at(Bars::kKFull + (i % kStagesK)), (i / kStagesK) & 1) &&
+                 globaltimer_ns() - t0 < lim) {}
+        }
+        for (uint32_t i = issued_v > kStagesV ? issued_v - kStagesV : 0; i < issued_v; ++i) {
+          while (!mbar_try_wait(bars.at(Bars::kVFull + (i % kStagesV)), (i / kStagesV) & 1) &&
+                 globaltimer_ns() - t0 < lim) {}
+        }
+        for (uint32_t i = issued_q > 2 ? issued_q - 2 : 0; i < issued_q; ++i) {
+          while (!mbar_try_wait(bars.at(Bars::kQFull + (i & 1)), (i >> 1) & 1) && globaltimer_ns() - t0 < lim) {}
+        }
+      }
+    } else if (warp == kIssuerWarp && lane == 0) {
+      // ========================================= QK^T issuer ====================================
+      FA4_FOR_EACH_TILE {
+        const Tile t = decode_tile(p, tile);
+        const int n = t.n_blocks;
+        if (n == 0) continue;
+        if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
+          *s_abort = 1u;
+          break;
+        }
+        const uint32_t qb = ti & 1;
+        ok = mbar_wait(bars.at(Bars::kQFull + qb), (ti >> 1) & 1, wc, kS64QFull);
+        if (!ok) break;
+        tc_fence_after_sync();
+        uint64_t dq[2];
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks) {
+          tc_cp_sf(tmem + kTmSFQ + 4 * ks, base + kOffSFQ + qb * kSfBytes + 512 * ks);
+          dq[ks] = make_desc_sw64(base + kOffQ + qb * kTileBytes + 32 * ks);
+        }
+        for (int i = 0; ok && i < n; ++i) {
+          const uint32_t G = gb + i, st = G % kStagesK, b = G & 1;
+          FA4_PH(0);
+          ok = mbar_wait(bars.at(Bars::kKFull + st), (G / kStagesK) & 1, wc, kS64KFull);
+          if (!ok) break;
+          FA4_PH(1);
+          FA4_TRACE_EV(20, G);
+          tc_fence_after_sync();
+          const uint32_t sfk = tmem + kTmSFK + 8 * b;
+          const uint32_t ksf = base + kOffSFK + st * kSfBytes, kt = base + kOffK + st * kTileBytes;
+          tc_cp_sf(sfk, ksf);
+          tc_cp_sf(sfk + 4, ksf + 512);
+          FA4_PH(3);
+#pragma unroll
+          for (int s = 0; s < 2; ++s) {
+            const uint32_t J = 2 * G + s, buf = J % kSBufs;
+            const uint32_t h64 = 1u - s;  // upper half of the block first
+            FA4_PH(0);
+            if (J >= kSBufs) {
+              // the buffer is free once sub-block J - 4 has been read by statistics and softmax
+              ok = mbar_wait(bars.at(Bars::kSFree + buf), ((J - kSBufs) / kSBufs) & 1, wc, kS64SFree);
+              if (!ok) break;
+              tc_fence_after_sync();
+            }
+            FA4_TRACE_EV(21, J);
+            FA4_PH(2);
+            const uint32_t s_tm = tmem + kTmS64 + 64 * buf;
+            // B operand: rows 64 h64 .. 64 h64 + 63 of the K tile; their scales sit two columns
+            // further in each 4-column group of the copied chunk
+#pragma unroll
+            for (int ks = 0; ks < 2; ++ks) {
+              mma_nvf4(s_tm, dq[ks], make_desc_sw64(kt + h64 * 4096 + 32 * ks), idesc_qk,
+                       tmem + kTmSFQ + 4 * ks, sfk + 4 * ks + 2 * h64, ks > 0 ? 1u : 0u);
+            }
+            FA4_PH(4);
+            tc_commit(bars.at(Bars::kSFull + buf));
+            FA4_PH(5);
+            FA4_TRACE_EV(27, J);
+          }
+          if (!ok) break;
+          tc_commit(bars.at(Bars::kKFree + st));  // the K stage is free once both products have run
+        }
+        if (!ok) break;
+        tc_commit(bars.at(Bars::kQEmpty + qb));
+        gb += n;
+        ti += 1;
+      }
+      if (!ok) {
+        const uint64_t t0 = globaltimer_ns();
+        tc_commit(bars.at(Bars::kDrain));
+        while (!mbar_try_wait(bars.at(Bars::kDrain), 0) && globaltimer_ns() - t0 < 50ull * 1000 * 1000) {}
+      }
+    } else if (warp == kPvIssuerWarp && lane == 0) {
+      // ========================================= P V issuer =====================================
+      FA4_FOR_EACH_TILE {
+        const Tile t = decode_tile(p, tile);
+        const int n = t.n_blocks;
+        if (n == 0) continue;
+        if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
+          *s_abort = 1u;
+          break;
+        }
+        for (int i = 0; ok && i < n; ++i) {
+          const uint32_t G = gb + i, st = G % kStagesV;
+          FA4_PH(0);
+          ok = mbar_wait(bars.at(Bars::kVFull + st), (G / kStagesV) & 1, wc, kS64VFull);
+          if (!ok) break;
+          FA4_PH(1);
+          const uint32_t vsf = base + kOffSFV + st * kSfBytes, vt = base + kOffV + st * kTileBytes;
+#pragma unroll
+          for (int s = 0; s < 2; ++s) {
+            const uint32_t J = 2 * G + s, slot = J % kPSlots, tb = J % kSBufs;
+            const uint32_t h64 = 1u - s;
+            FA4_PH(0);
+            ok = mbar_wait(bars.at(Bars::kPFull + slot), (J / kPSlots) & 1, wc, kS64PFull);
+            if (!ok) break;
+            FA4_PH(2);
+            if (i == 0 && s == 0 && ti >= 1) {
+              // O of the previous tile must have been copied out of tensor memory
+              ok = mbar_wait(bars.at(Bars::kOFree), (ti - 1) & 1, wc, kS64OFree);
+              if (!ok) break;
+            }
+            FA4_TRACE_EV(22, J);
+            tc_fence_after_sync();
+            const uint32_t sfp = tmem + kTmSFP64 + 4 * tb, sfv = tmem + kTmSFV64 + 4 * tb;
+            tc_cp_sf(sfp, base + kOffSFP + slot * 512);
+            FA4_PH(3);
+            tc_cp_sf(sfv, vsf + 512 * h64);
+            FA4_PH(4);
+            mma_nvf4(tmem + kTmO, make_desc_sw32(base + kOffP + slot * kPTileBytes),
+                     make_desc_sw64(vt + 32 * h64), idesc_pv, sfp, sfv, (i > 0 || s > 0) ? 1u : 0u);
+            FA4_PH(5);
+            tc_commit(bars.at(Bars::kPvDone + slot));
+            FA4_PH(6);
+            FA4_TRACE_EV(23, J);
+          }
+          if (!ok) break;
+          tc_commit(bars.at(Bars::kVFree + st));
+        }
+        if (!ok) break;
+        gb += n;
+        ti += 1;
+      }
+      if (!ok) {
+        const uint64_t t0 = globaltimer_ns();
+        tc_commit(bars.at(Bars::kDrain + 1));
+        while (!mbar_try_wait(bars.at(Bars::kDrain + 1), 0) && globaltimer_ns() - t0 < 50ull * 1000 * 1000) {}
+      }
+    } else if (warp == kStoreWarp && lane == 0) {
+      // ========================================= output store ===================================
+      tma_prefetch_desc(&tm_o);
+      FA4_FOR_EACH_TILE {
+        const Tile t = decode_tile(p, tile);
+        ok = mbar_wait(bars.at(Bars::kOStaged), it & 1, wc, kS64OStaged);
+        if (!ok) break;
+        tma_store_4d(&tm_o, base + kOffOut, 0, t.h, t.m_blk * kBlockM, t.b);
+        tma_store_4d(&tm_o, base + kOffOut + 16 * 1024, 64, t.h, t.m_blk * kBlockM, t.b);
+        bulk_commit_group();
+        bulk_wait_group_read0();
+        mbar_arrive(bars.at(Bars::kStageFree));
+        (void)gb;
+        (void)ti;
+      }
+      bulk_wait_group0();
+    }
+  } else {
+    // =========================================== softmax warpgroups =============================
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
+    const int wg = warp >> 2;                 // 0..3: owns S buffer wg, i.e. the sub-blocks J % 4 == wg
+    const int row = (warp & 3) * 32 + lane;   // tile row == tensor-memory lane
+    const uint32_t lane_addr = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+    const uint32_t s_addr = lane_addr + kTmS64 + 64 * wg;
+
+    FA4_FOR_EACH_TILE {
+      const Tile t = decode_tile(p, tile);
+      const int n = t.n_blocks;
+      const bool poisoned =
+          (p.status != nullptr) && (*reinterpret_cast<volatile uint32_t*>(p.status) != 0u);
+      if (poisoned) {
+        *s_abort = 1u;
+        break;
+      }
+      float m_ref = kNegInf, l_sum = 0.f;
+
+      for (int j = (wg - 2 * (int)gb) & 3; j < 2 * n; j += 4) {
+        const uint32_t J = 2 * gb + j, slot = J % kPSlots;  // J % 4 == wg
+        const int nb = n - 1 - (j >> 1);
+        const int h64 = 1 - (j & 1);
+        const uint32_t bar_s = bars.at(Bars::kSFull + wg), par_s = (J / kSBufs) & 1;
+        const uint32_t bar_p = bars.at(Bars::kPvDone + slot), par_p = ((J - kPSlots) / kPSlots) & 1;
+        const bool r_p = (J >= kPSlots) ? mbar_test(bar_p, par_p) : true;
+
+        // 1. the scores of this sub-block: the whole 64-key row of this thread
+        FA4_PH(7);
+        ok = wait_probed(mbar_test(bar_s, par_s), bar_s, par_s, wc, kS64SFull);
+        if (!ok) break;
+        FA4_PH(0);
+        FA4_TRACE_EV(5, J);
+        tc_fence_after_sync();
+        if (block_needs_mask(p, t, nb)) mask_scores_in_tmem(s_addr, causal_limit(p, t, row, nb) - 64 * h64);
+        float s[64];
+        tmem_ld32(s_addr, reinterpret_cast<uint32_t*>(&s[0]));
+        tmem_ld32(s_addr + 32, reinterpret_cast<uint32_t*>(&s[32]));
+        tc_wait_ld();
+        tc_fence_before_sync();
+        mbar_arrive(bars.at(Bars::kSFree + wg));
+        FA4_TRACE_EV(3, J);
+        FA4_PH(1);
+
+        // 2. maxima of the four 16-key blocks, then the running reference: it is handed from the
+        //    warpgroup of sub-block J - 1 to this one through shared memory (one float per row)
+        float bm4[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          float m0 = fmax3(s[16 * q], s[16 * q + 1], s[16 * q + 2]);
+          float m1 = fmax3(s[16 * q + 3], s[16 * q + 4], s[16 * q + 5]);
+          m0 = fmax3(m0, s[16 * q + 6], s[16 * q + 7]);
+          m1 = fmax3(m1, s[16 * q + 8], s[16 * q + 9]);
+          m0 = fmax3(m0, s[16 * q + 10], s[16 * q + 11]);
+          m1 = fmax3(m1, s[16 * q + 12], s[16 * q + 13]);
+          m0 = fmax3(m0, s[16 * q + 14], s[16 * q + 15]);
+          bm4[q] = fmaxf(m0, m1);
+        }
+        const float m_loc = fmaxf(fmaxf(bm4[0], bm4[1]), fmaxf(bm4[2], bm4[3]));
+        float m_prev = kNegInf;
+        FA4_PH(2);
+        if (j > 0) {
+          const uint32_t pw = (uint32_t)(wg + 3) & 3u;
+          ok = __all_sync(0xffffffffu, mbar_wait(bars.at(Bars::kHand + pw), ((J - 1) / kSBufs) & 1, wc, kS64Hand));
+          if (!ok) break;
+          m_prev = s_hand[pw * 128 + row];
+        }
+        const float m_new = next_reference(m_prev, m_loc, p.sl2);
+        s_hand[wg * 128 + row] = m_new;
+        mbar_arrive(bars.at(Bars::kHand + wg));
+        float noff4[4];
+        uint32_t ue;
+        block_exponents4(bm4, m_new, p.sl2, noff4, ue);
+        // own partial row sum follows the reference
+        if (m_new != m_ref) l_sum *= reference_factor(m_ref, m_new, p.sl2);
+        m_ref = m_new;
+        FA4_PH(3);
+
+        // 3. exponentials and quantisation; P slot J % 8 is free once P V of sub-block J - 8 has run
+        ok = wait_probed(r_p, bar_p, par_p, wc, kS64PvDone);
+        if (!ok) break;
+        FA4_TRACE_EV(6, J);
+        FA4_PH(4);
+        uint8_t* p_tile = gbase + kOffP + slot * kPTileBytes;
+        uint4 chunk;
+        l_sum += quantize_pair(&s[0], noff4[0], noff4[1],
+                               __byte_perm(ue, 0u, 0x4440u), __byte_perm(ue, 0u, 0x4441u), p.sl2, chunk);
+        *reinterpret_cast<uint4*>(p_tile + sw32_offset(row, 0)) = chunk;
+        l_sum += quantize_pair(&s[32], noff4[2], noff4[3],
+                               __byte_perm(ue, 0u, 0x4442u), __byte_perm(ue, 0u, 0x4443u), p.sl2, chunk);
+        *reinterpret_cast<uint4*>(p_tile + sw32_offset(row, 1)) = chunk;
+        // the four scale bytes of this row: one word of the 512-byte chunk
+        *reinterpret_cast<uint32_t*>(gbase + kOffSFP + slot * 512 + (row & 31) * 16 + (row >> 5) * 4) =
+            block_scale_bytes(ue);
+
+        // 4. correction (rare, out of line): O holds the sub-blocks before this one relative to
+        //    m_prev and must move to m_new before P V of this sub-block is issued; this thread
+        //    owns its whole row of O
+        if (j > 0 && __any_sync(0xffffffffu, m_new != m_prev)) {
+          const uint32_t Jp = J - 1;
+          ok = __all_sync(0xffffffffu, mbar_wait(bars.at(Bars::kPvDone + (Jp % kPSlots)),
+                                                 (Jp / kPSlots) & 1, wc, kS64PvDone));
+          if (!ok) break;
+          tc_fence_after_sync();
+          const float f = (m_new != m_prev) ? reference_factor(m_prev, m_new, p.sl2) : 1.f;
+          rescale_accumulator(lane_addr + kTmO, f, 4);
+          tc_wait_st();
+        }
+        fence_proxy_async_smem();
+        tc_fence_before_sync();
+        mbar_arrive(bars.at(Bars::kPFull + slot));
+        FA4_TRACE_EV(7, J);
+        FA4_PH(5);
+      }
+      if (!ok) break;
+
+      FA4_PH(7);
+      // ---- tile end: combine the four partial row sums, read O, stage the output --------------
+      const int q_idx = t.m_blk * kBlockM + row;
+      float scale = 0.f, m_fin = kNegInf, l_tot = 0.f;
+      if (n > 0) {
+        volatile float* fin_slot = s_fin + (ti & 1) * (4 * 128 * 2);
+        // slot order = position of the warpgroup's first sub-block inside the tile: the summation
+        // order of a row then depends on its tile only, not on what the CTA processed before
+        const uint32_t fslot = (uint32_t)(wg - 2 * (int)gb) & 3u;
+        fin_slot[(fslot * 128 + row) * 2] = l_sum;
+        fin_slot[(fslot * 128 + row) * 2 + 1] = m_ref;
+        mbar_arrive(bars.at(Bars::kFin));
+        ok = __all_sync(0xffffffffu, mbar_wait(bars.at(Bars::kFin), ti & 1, wc, kS64Fin));
+        if (!ok) break;
+        float lw[4], mw[4];
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          lw[w] = fin_slot[(w * 128 + row) * 2];
+          mw[w] = fin_slot[(w * 128 + row) * 2 + 1];
+          m_fin = fmaxf(m_fin, mw[w]);
+        }
+#pragma unroll
+        for (int w = 0; w < 4; ++w) l_tot += lw[w] * reference_factor(mw[w], m_fin, p.sl2);
+        if (m_fin == kNegInf) l_tot = 0.f;
+        const uint32_t Jl = 2 * gb + 2 * n - 1;
+        ok = __all_sync(0xffffffffu,
+                        mbar_wait(bars.at(Bars::kPvDone + (Jl % kPSlots)), (Jl / kPSlots) & 1, wc, kS64FinalO));
+        if (!ok) break;
+        tc_fence_after_sync();
+        scale = (l_tot > 0.f) ? p.out_scale / l_tot : 0.f;
+      }
+      if (it >= 1) {
+        ok = __all_sync(0xffffffffu, mbar_wait(bars.at(Bars::kStageFree), (it - 1) & 1, wc, kS64StageFree));
+        if (!ok) break;
+      }
+      stage_accumulator_chunk<true>(lane_addr + kTmO + 32 * wg, gbase + kOffOut, row, wg, scale,
+                                    n > 0 ? bars.at(Bars::kOFree) : 0u);
+      fence_proxy_async_smem();
+      mbar_arrive(bars.at(Bars::kOStaged));
+      if (wg == 0 && q_idx < p.Sq && p.lse != nullptr) {
+        p.lse[((int64_t)t.b * p.Hq + t.h) * p.Sq + q_idx] = finish_lse(m_fin, l_tot, p.sl2);
+      }
+      gb += n;
+      ti += (n > 0) ? 1u : 0u;
+      FA4_PH(6);
+    }
+  }
+  FA4_PH_DUMP();
+#undef FA4_FOR_EACH_TILE
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == kIssuerWarp) tmem_dealloc(tmem, kTmemCols);
+}
+
+}  // namespace fa4

@@ -26,7 +26,7 @@ import torch
 from . import _lib
 from .quant import NVFP4Tensor, sf_to_tiled
 
-VARIANT_AUTO, VARIANT_SERIAL, VARIANT_WS = 0, 1, 2
+VARIANT_AUTO, VARIANT_SERIAL, VARIANT_WS, VARIANT_WS64 = 0, 1, 2, 3
 
 
 def _validate_tensor(t, name, expected_shape, expected_dtype, expected_device):

@@ -71,7 +71,9 @@ enum {
 enum {
   FA4_VARIANT_AUTO = 0,
   FA4_VARIANT_SERIAL = 1, /* one warpgroup does every step in turn (bring-up / cross-check) */
-  FA4_VARIANT_WS = 2      /* warp-specialised load / MMA / softmax pipeline */
+  FA4_VARIANT_WS = 2,     /* warp-specialised load / MMA / softmax pipeline */
+  FA4_VARIANT_WS64 = 3    /* the same with 64-key sub-blocks and four score buffers (D = 128, no
+                             split / window / sink) */
 };
 
 typedef struct fa4_nvfp4_params {
