@@ -68,6 +68,17 @@ int ensure_smem(Kernel kernel, uint32_t bytes) {
   return e == cudaSuccess ? 0 : (int)e;
 }
 
+// The warp-specialised kernels re-partition registers with setmaxnreg, and an increase blocks for
+// ever when the CTA was launched with fewer registers per thread than the budget in the source
+// assumes.  Refuse to launch a build whose compiled register count is below that assumption.
+template <class Kernel>
+int ensure_launch_regs(Kernel kernel, int expected) {
+  cudaFuncAttributes attr;
+  const cudaError_t e = cudaFuncGetAttributes(&attr, kernel);
+  if (e != cudaSuccess) return (int)e;
+  return attr.numRegs >= expected ? 0 : -FA4_E_BUILD;
+}
+
 }  // namespace
 
 extern "C" int fa4_nvfp4_query(int32_t what) {
@@ -139,11 +150,14 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
   for (int64_t s : bstr)
     if (s <= 0 || (s & 15) != 0) return -FA4_E_STRIDE;
   if ((p->o_stride_b & 7) || (p->o_stride_s & 7) || (p->o_stride_h & 7)) return -FA4_E_STRIDE;
-  int variant = p->variant == FA4_VARIANT_AUTO ? FA4_VARIANT_WS : p->variant;
+  // automatic choice: the 64-key kernel where it applies (head dim 128, no split / window / sink),
+  // the 128-key kernel for everything else
+  const bool plain = p->D == 128 && num_splits == 1 && win_left < 0 && win_right <= 0 && sink == nullptr;
+  int variant = p->variant;
+  if (variant == FA4_VARIANT_AUTO) variant = plain ? FA4_VARIANT_WS64 : FA4_VARIANT_WS;
   if (variant != FA4_VARIANT_SERIAL && variant != FA4_VARIANT_WS && variant != FA4_VARIANT_WS64)
     return -FA4_E_VARIANT;
-  if (variant == FA4_VARIANT_WS64 && (p->D != 128 || num_splits > 1 || win_left >= 0 || win_right > 0 || sink))
-    return -FA4_E_SHAPE;
+  if (variant == FA4_VARIANT_WS64 && !plain) return -FA4_E_SHAPE;
   if (variant == FA4_VARIANT_SERIAL && p->D != 128) return -FA4_E_SHAPE;  // bring-up kernel: 128 only
   // window limits: `causal` is the right limit 0; an explicit right limit overrides it
   if (p->causal && win_right < 0) win_right = 0;
@@ -235,12 +249,14 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
     }
     auto launch = [&](auto kernel) -> int {
       if (int e = ensure_smem(kernel, ws::kSmemRequest)) return e;
+      if (int e = ensure_launch_regs(kernel, ws::kRegsLaunch)) return e;
       kernel<<<grid, ws::kThreads, ws::kSmemRequest, stream>>>(tm_q, tm_k, tm_v, tm_o, kp);
       return 0;
     };
     int rc;
     if (variant == FA4_VARIANT_WS64) {
       if (int e = ensure_smem(attn_fwd_ws64_kernel, ws64::kSmemRequest)) return e;
+      if (int e = ensure_launch_regs(attn_fwd_ws64_kernel, ws64::kRegsLaunch)) return e;
       attn_fwd_ws64_kernel<<<grid, ws64::kThreads, ws64::kSmemRequest, stream>>>(tm_q, tm_k, tm_v, tm_o, kp);
       rc = 0;
     } else if (p->D == 128) {

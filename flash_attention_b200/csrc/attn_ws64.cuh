@@ -20,8 +20,11 @@
 //   warp 22     P V issuer: per sub-block one K = 64 step into O
 //   warp 23     output store (TMA)
 //
-// Sub-block j of a tile (visit order): block i = j / 2 (last visible block first), upper half of
-// the block (keys 64-127) first.  J = 2 * (blocks before this tile) + j selects buffers, P slots
+// Sub-block j of a tile (visit order): keys 64 j .. 64 j + 63, ascending.  (The 128-key kernel
+// visits the last visible block first; with 64-key steps that order makes the first references
+// of a causal tile rest on one or two keys, and with the small lazy threshold that NVFP4 block
+// scales allow nearly every tile then pays several accumulator corrections, each of which
+// drains the P V pipeline.  Ascending, the first sub-block is fully visible.)  J = 2 * (blocks before this tile) + j selects buffers, P slots
 // and barrier phases.  Everything else (operand formats, P quantisation, lazy reference, bounded
 // waits, epilogue) is as in attn_ws.cuh.
 #pragma once
@@ -32,17 +35,21 @@
 #ifdef FA4_PHASES
 #undef FA4_TRACE_EV
 #define FA4_TRACE_EV(ev, idx) do {} while (0)
-#define FA4_PH_DECL uint32_t ph_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; uint32_t ph_t = clock();
+#define FA4_PH_DECL uint32_t ph_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; uint32_t ph_t = clock(); uint32_t ph_cnt = 0; const uint32_t ph_t0 = ph_t;
+#define FA4_PH_COUNT() do { ph_cnt += 1; } while (0)
 #define FA4_PH_RESET() do { ph_t = clock(); } while (0)
 #define FA4_PH(k) do { const uint32_t c_ = clock(); ph_acc[k] += c_ - ph_t; ph_t = c_; } while (0)
 #define FA4_PH_DUMP()                                                                         \
   do {                                                                                        \
-    if (g_trace_buf != nullptr && (int)blockIdx.x == g_trace_cta && (threadIdx.x & 31) == 0) { \
-      for (int k_ = 0; k_ < 8; ++k_) g_trace_buf[(threadIdx.x >> 5) * 8 + k_] = ph_acc[k_];    \
+    if (g_trace_buf != nullptr && (threadIdx.x & 31) == 0) {                                  \
+      unsigned long long* d_ = g_trace_buf + ((size_t)blockIdx.x * 24 + (threadIdx.x >> 5)) * 16; \
+      for (int k_ = 0; k_ < 8; ++k_) d_[k_] = ph_acc[k_];                                     \
+      d_[8] = ph_cnt; d_[9] = clock() - ph_t0;                                                \
     }                                                                                         \
   } while (0)
 #else
 #define FA4_PH_DECL
+#define FA4_PH_COUNT() do {} while (0)
 #define FA4_PH_RESET() do {} while (0)
 #define FA4_PH(k) do {} while (0)
 #define FA4_PH_DUMP() do {} while (0)
@@ -54,18 +61,25 @@ namespace ws64 {
 constexpr int kStagesK = 4, kStagesV = 4;  // 128-key tiles
 constexpr int kSBufs = 4;                  // S buffers of 64 columns
 constexpr int kPSlots = 8;                 // P tiles of 64 keys (4 KB each)
-constexpr int kThreads = 640;
-constexpr int kProducerWarp = 16, kIssuerWarp = 17, kPvIssuerWarp = 18, kStoreWarp = 19;
-// 640 threads launch with 96 registers each.  setmaxnreg.inc draws from the pool the CTA was
-// launched with (threads x launch registers), NOT from the whole register file, and blocks until
-// the pool can serve it: a total above the launch total never returns.
-constexpr int kRegsSoftmax = 104, kRegsOther = 40, kRegsLaunch = 96;
-static_assert(kThreads * kRegsLaunch <= 65536, "register file");
-static_assert(512 * kRegsSoftmax + 128 * kRegsOther <= kThreads * kRegsLaunch, "register pool of the CTA");
+constexpr int kThreads = 768;
+constexpr int kProducerWarp = 16, kIssuerWarp = 17, kPvIssuerWarp = 18, kCopyWarp = 19, kEpilogueWarp0 = 20;
+// Registers are a per-scheduler resource: 16384 per SM sub-partition, warp w living on sub-partition
+// w % 4.  With 21-24 warps a sub-partition holds 6, so the launch gets 80 registers per thread and
+// the CTA's pool per sub-partition is 6 x 32 x 80 = 15360.  setmaxnreg.inc draws from that pool
+// (NOT from the whole register file) and blocks until it can be served: a budget above the pool
+// never returns.  Per sub-partition: four softmax warps at 96, one service warp at 40 and one
+// epilogue warp at 56 use exactly the pool.
+constexpr int kRegsSoftmax = 96, kRegsOther = 40, kRegsEpilogue = 56, kRegsLaunch = 80;
+static_assert(kThreads == 768, "six warps per sub-partition");
+static_assert(4 * kRegsSoftmax + kRegsOther + kRegsEpilogue <= 6 * kRegsLaunch,
+              "register pool of a sub-partition");
+static_assert((kThreads / 128) * 32 * kRegsLaunch <= 16384, "register file of a sub-partition");
 
 // tensor memory: S[4] x 64 columns, O 128, scale factors
-// (O at column 256, Q scales at 384, K scales at 392 (2 x 8) as in the 128-key kernel)
-constexpr uint32_t kTmS64 = 0, kTmSFV64 = 408 /* 4 x 4 */, kTmSFP64 = 424 /* 4 x 4 */;
+// (O at column 256 and Q scales at 384 as in the 128-key kernel); K and V scales have one slot of
+// 8 columns per shared-memory stage, written by the copy warp as soon as the tile has landed
+constexpr uint32_t kTmS64 = 0, kTmSFK64 = 392 /* 4 x 8 */, kTmSFV64 = 424 /* 4 x 8 */, kTmSFP64 = 456 /* 4 x 4 */;
+static_assert(kTmSFP64 + 16 <= 512, "tensor memory columns");
 constexpr uint32_t kPTileBytes = 128 * 32;  // 128 rows x 64 e2m1 keys
 
 constexpr uint32_t kOffQ = 0;
@@ -87,8 +101,9 @@ struct Bars {
                             kKFree = kVFull + kStagesV, kVFree = kKFree + kStagesK,
                             kSFull = kVFree + kStagesV, kSFree = kSFull + kSBufs,
                             kHand = kSFree + kSBufs, kPFull = kHand + kSBufs, kPvDone = kPFull + kPSlots,
-                            kFin = kPvDone + kPSlots, kOFree = kFin + 1, kOStaged = kOFree + 1,
-                            kStageFree = kOStaged + 1, kDrain = kStageFree + 1, kCount = kDrain + 2;
+                            kFin = kPvDone + kPSlots, kFinFree = kFin + 2, kOFree = kFinFree + 2,
+                            kEpi = kOFree + 1, kKsf = kEpi + 1, kVsf = kKsf + kStagesK,
+                            kDrain = kVsf + kStagesV, kCount = kDrain + 3;
   __device__ explicit Bars(uint32_t b) : base(b) {}
   __device__ __forceinline__ uint32_t at(uint32_t idx) const { return base + 8u * idx; }
 };
@@ -99,8 +114,7 @@ static_assert(kSmemRequest <= 227 * 1024, "shared memory");
 
 enum Site64 {
   kS64QFull = 40, kS64QEmpty, kS64KFree, kS64VFree, kS64KFull, kS64VFull, kS64SFull, kS64SFree,
-  kS64PFull, kS64PvDone, kS64Hand, kS64Fin, kS64FinalO, kS64OFree, kS64OStaged,
-  kS64StageFree
+  kS64PFull, kS64PvDone, kS64Hand, kS64Fin, kS64FinFree, kS64FinalO, kS64OFree, kS64Ksf, kS64Vsf, kS64Epi
 };
 
 // byte offset of 16-byte chunk c (0, 1) of row r in a P tile (rows of 32 bytes, 32-byte swizzle)
@@ -144,15 +158,17 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
     for (int b = 0; b < 2; ++b) {
       mbar_init(bars.at(Bars::kQFull + b), 1);
       mbar_init(bars.at(Bars::kQEmpty + b), 1);
-      mbar_init(bars.at(Bars::kDrain + b), 1);
     }
+    for (int b = 0; b < 3; ++b) mbar_init(bars.at(Bars::kDrain + b), 1);
     for (int s = 0; s < kStagesK; ++s) {
       mbar_init(bars.at(Bars::kKFull + s), 1);
       mbar_init(bars.at(Bars::kKFree + s), 1);
+      mbar_init(bars.at(Bars::kKsf + s), 1);
     }
     for (int s = 0; s < kStagesV; ++s) {
       mbar_init(bars.at(Bars::kVFull + s), 1);
       mbar_init(bars.at(Bars::kVFree + s), 1);
+      mbar_init(bars.at(Bars::kVsf + s), 1);
     }
     for (int s = 0; s < kSBufs; ++s) {
       mbar_init(bars.at(Bars::kSFull + s), 1);
@@ -163,10 +179,12 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
       mbar_init(bars.at(Bars::kPFull + s), 128);
       mbar_init(bars.at(Bars::kPvDone + s), 1);
     }
-    mbar_init(bars.at(Bars::kFin), 512);
-    mbar_init(bars.at(Bars::kOFree), 512);
-    mbar_init(bars.at(Bars::kOStaged), 512);
-    mbar_init(bars.at(Bars::kStageFree), 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bars.at(Bars::kFin + b), 512);      // the four softmax warpgroups
+      mbar_init(bars.at(Bars::kFinFree + b), 128);  // the epilogue warpgroup
+    }
+    mbar_init(bars.at(Bars::kOFree), 128);
+    mbar_init(bars.at(Bars::kEpi), 128);            // the epilogue warpgroup's own rendezvous
     fence_barrier_init();
   }
   if (warp == kProducerWarp && lane == 0) {
@@ -191,7 +209,104 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
   for (int it = 0, tile = tile_of_round(0, cta, ncta); ok && tile < num_tiles;                   \
        ++it, tile = tile_of_round(it, cta, ncta))
 
-  if (warp >= kProducerWarp) {
+  if (warp >= kEpilogueWarp0) {
+    // =========================================== epilogue warpgroup =============================
+    // Thread = row.  Per tile: combine the four partial row sums, wait for the last P V, move O
+    // from tensor memory to the staging tile (bf16, normalised), send it with TMA, write the LSE.
+    // The softmax warpgroups meanwhile work on the next tile; only the P V issuer waits for the
+    // accumulator to be read out.
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsEpilogue));
+    const int row = tid & 127;
+    const uint32_t lane_addr = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+    const bool leader = (tid == kEpilogueWarp0 * 32);
+    if (leader) tma_prefetch_desc(&tm_o);
+    // rendezvous of the 128 epilogue threads on an mbarrier: unlike bar.sync the wait is bounded, so
+    // a warp that gave up elsewhere cannot leave the others blocked
+    uint32_t epi_phase = 0;
+#define FA4_EPI_SYNC()                                                                              \
+  mbar_arrive(bars.at(Bars::kEpi));                                                                 \
+  ok = __all_sync(0xffffffffu, mbar_wait(bars.at(Bars::kEpi), epi_phase & 1, wc, kS64Epi));          \
+  epi_phase += 1;                                                                                   \
+  if (!ok) break;
+    FA4_FOR_EACH_TILE {
+      const Tile t = decode_tile(p, tile);
+      const int n = t.n_blocks;
+      if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
+        *s_abort = 1u;
+        break;
+      }
+      const int q_idx = t.m_blk * kBlockM + row;
+      float scale = 0.f, m_fin = kNegInf, l_tot = 0.f;
+      if (n > 0) {
+        const uint32_t fb = ti & 1;
+        ok = __all_sync(0xffffffffu, mbar_wait(bars.at(Bars::kFin + fb), (ti >> 1) & 1, wc, kS64Fin));
+        if (!ok) break;
+        volatile float* fin_slot = s_fin + fb * (4 * 128 * 2);
+        float lw[4], mw[4];
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          lw[w] = fin_slot[(w * 128 + row) * 2];
+          mw[w] = fin_slot[(w * 128 + row) * 2 + 1];
+          m_fin = fmaxf(m_fin, mw[w]);
+        }
+        mbar_arrive(bars.at(Bars::kFinFree + fb));
+#pragma unroll
+        for (int w = 0; w < 4; ++w) l_tot += lw[w] * reference_factor(mw[w], m_fin, p.sl2);
+        if (m_fin == kNegInf) l_tot = 0.f;
+        const uint32_t Jl = 2 * gb + 2 * n - 1;
+        ok = __all_sync(0xffffffffu,
+                        mbar_wait(bars.at(Bars::kPvDone + (Jl % kPSlots)), (Jl / kPSlots) & 1, wc, kS64FinalO));
+        if (!ok) break;
+        tc_fence_after_sync();
+        scale = (l_tot > 0.f) ? p.out_scale / l_tot : 0.f;
+      }
+      // the staging tile is free once the previous store has read it
+      if (it >= 1) {
+        if (leader) bulk_wait_group_read0();
+        FA4_EPI_SYNC()
+      }
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint8_t* box_row = gbase + kOffOut + (c >> 1) * (16 * 1024) + row * 128;
+        uint32_t o[32];
+        if (n > 0) {
+          tmem_ld32(lane_addr + kTmO + 32 * c, o);
+          tc_wait_ld();
+          if (c == 3) {
+            tc_fence_before_sync();
+            mbar_arrive(bars.at(Bars::kOFree));  // the P V issuer may start the next tile
+          }
+        } else {
+#pragma unroll
+          for (int x = 0; x < 32; ++x) o[x] = 0u;
+        }
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          uint4 w;
+          w.x = pack_bf16x2(__uint_as_float(o[8 * v + 0]) * scale, __uint_as_float(o[8 * v + 1]) * scale);
+          w.y = pack_bf16x2(__uint_as_float(o[8 * v + 2]) * scale, __uint_as_float(o[8 * v + 3]) * scale);
+          w.z = pack_bf16x2(__uint_as_float(o[8 * v + 4]) * scale, __uint_as_float(o[8 * v + 5]) * scale);
+          w.w = pack_bf16x2(__uint_as_float(o[8 * v + 6]) * scale, __uint_as_float(o[8 * v + 7]) * scale);
+          const int chunk = ((c & 1) * 4 + v) ^ (row & 7);
+          *reinterpret_cast<uint4*>(box_row + chunk * 16) = w;
+        }
+      }
+      fence_proxy_async_smem();
+      FA4_EPI_SYNC()
+      if (leader) {
+        tma_store_4d(&tm_o, base + kOffOut, 0, t.h, t.m_blk * kBlockM, t.b);
+        tma_store_4d(&tm_o, base + kOffOut + 16 * 1024, 64, t.h, t.m_blk * kBlockM, t.b);
+        bulk_commit_group();
+      }
+      if (q_idx < p.Sq && p.lse != nullptr) {
+        p.lse[((int64_t)t.b * p.Hq + t.h) * p.Sq + q_idx] = finish_lse(m_fin, l_tot, p.sl2);
+      }
+      gb += n;
+      ti += (n > 0) ? 1u : 0u;
+    }
+#undef FA4_EPI_SYNC
+    if (leader) bulk_wait_group0();
+  } else if (warp >= kProducerWarp) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
     if (warp == kProducerWarp && lane == 0) {
       // ========================================= TMA producer ===================================
@@ -223,7 +338,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
           const int ik = step, iv = step - 2;
           if (ik < n) {
             const uint32_t G = gb + ik, st = G % kStagesK;
-            const int nb = n - 1 - ik;
+            const int nb = ik;  // ascending: the diagonal block of a causal tile comes last
             if (G >= kStagesK) {
               ok = mbar_wait(bars.at(Bars::kKFree + st), ((G - kStagesK) / kStagesK) & 1, wc, kS64KFree);
               if (!ok) break;
@@ -237,7 +352,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
           }
           if (iv >= 0 && iv < n) {
             const uint32_t G = gb + iv, st = G % kStagesV;
-            const int nb = n - 1 - iv;
+            const int nb = iv;
             if (G >= kStagesV) {
               ok = mbar_wait(bars.at(Bars::kVFree + st), ((G - kStagesV) / kStagesV) & 1, wc, kS64VFree);
               if (!ok) break;
@@ -290,22 +405,20 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
           dq[ks] = make_desc_sw64(base + kOffQ + qb * kTileBytes + 32 * ks);
         }
         for (int i = 0; ok && i < n; ++i) {
-          const uint32_t G = gb + i, st = G % kStagesK, b = G & 1;
+          const uint32_t G = gb + i, st = G % kStagesK;
           FA4_PH(0);
-          ok = mbar_wait(bars.at(Bars::kKFull + st), (G / kStagesK) & 1, wc, kS64KFull);
+          // the K tile has landed (the copy warp saw k_full) and its scales are in tensor memory
+          ok = mbar_wait(bars.at(Bars::kKsf + st), (G / kStagesK) & 1, wc, kS64Ksf);
           if (!ok) break;
           FA4_PH(1);
           FA4_TRACE_EV(20, G);
           tc_fence_after_sync();
-          const uint32_t sfk = tmem + kTmSFK + 8 * b;
-          const uint32_t ksf = base + kOffSFK + st * kSfBytes, kt = base + kOffK + st * kTileBytes;
-          tc_cp_sf(sfk, ksf);
-          tc_cp_sf(sfk + 4, ksf + 512);
-          FA4_PH(3);
+          const uint32_t sfk = tmem + kTmSFK64 + 8 * st;
+          const uint32_t kt = base + kOffK + st * kTileBytes;
 #pragma unroll
           for (int s = 0; s < 2; ++s) {
             const uint32_t J = 2 * G + s, buf = J % kSBufs;
-            const uint32_t h64 = 1u - s;  // upper half of the block first
+            const uint32_t h64 = s;  // lower half of the block first
             FA4_PH(0);
             if (J >= kSBufs) {
               // the buffer is free once sub-block J - 4 has been read by statistics and softmax
@@ -354,14 +467,14 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
         for (int i = 0; ok && i < n; ++i) {
           const uint32_t G = gb + i, st = G % kStagesV;
           FA4_PH(0);
-          ok = mbar_wait(bars.at(Bars::kVFull + st), (G / kStagesV) & 1, wc, kS64VFull);
+          ok = mbar_wait(bars.at(Bars::kVsf + st), (G / kStagesV) & 1, wc, kS64Vsf);
           if (!ok) break;
           FA4_PH(1);
-          const uint32_t vsf = base + kOffSFV + st * kSfBytes, vt = base + kOffV + st * kTileBytes;
+          const uint32_t vt = base + kOffV + st * kTileBytes;
 #pragma unroll
           for (int s = 0; s < 2; ++s) {
             const uint32_t J = 2 * G + s, slot = J % kPSlots, tb = J % kSBufs;
-            const uint32_t h64 = 1u - s;
+            const uint32_t h64 = s;
             FA4_PH(0);
             ok = mbar_wait(bars.at(Bars::kPFull + slot), (J / kPSlots) & 1, wc, kS64PFull);
             if (!ok) break;
@@ -373,11 +486,9 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
             }
             FA4_TRACE_EV(22, J);
             tc_fence_after_sync();
-            const uint32_t sfp = tmem + kTmSFP64 + 4 * tb, sfv = tmem + kTmSFV64 + 4 * tb;
+            const uint32_t sfp = tmem + kTmSFP64 + 4 * tb, sfv = tmem + kTmSFV64 + 8 * st + 4 * h64;
             tc_cp_sf(sfp, base + kOffSFP + slot * 512);
             FA4_PH(3);
-            tc_cp_sf(sfv, vsf + 512 * h64);
-            FA4_PH(4);
             mma_nvf4(tmem + kTmO, make_desc_sw32(base + kOffP + slot * kPTileBytes),
                      make_desc_sw64(vt + 32 * h64), idesc_pv, sfp, sfv, (i > 0 || s > 0) ? 1u : 0u);
             FA4_PH(5);
@@ -397,22 +508,51 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
         tc_commit(bars.at(Bars::kDrain + 1));
         while (!mbar_try_wait(bars.at(Bars::kDrain + 1), 0) && globaltimer_ns() - t0 < 50ull * 1000 * 1000) {}
       }
-    } else if (warp == kStoreWarp && lane == 0) {
-      // ========================================= output store ===================================
-      tma_prefetch_desc(&tm_o);
+    } else if (warp == kCopyWarp && lane == 0) {
+      // ========================================= scale copier ===================================
+      // moves the K and V scale tiles of every stage into tensor memory as soon as they land, so
+      // that the two issuers spend their (slow, in-order) tcgen05 issue slots on products only.
+      // A stage's tensor-memory slot is free when its shared-memory stage is: the producer
+      // reloads the stage only after the products that used it have completed.
       FA4_FOR_EACH_TILE {
         const Tile t = decode_tile(p, tile);
-        ok = mbar_wait(bars.at(Bars::kOStaged), it & 1, wc, kS64OStaged);
-        if (!ok) break;
-        tma_store_4d(&tm_o, base + kOffOut, 0, t.h, t.m_blk * kBlockM, t.b);
-        tma_store_4d(&tm_o, base + kOffOut + 16 * 1024, 64, t.h, t.m_blk * kBlockM, t.b);
-        bulk_commit_group();
-        bulk_wait_group_read0();
-        mbar_arrive(bars.at(Bars::kStageFree));
-        (void)gb;
-        (void)ti;
+        const int n = t.n_blocks;
+        if (n == 0) continue;
+        if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
+          *s_abort = 1u;
+          break;
+        }
+        for (int step = 0; ok && step < n + 2; ++step) {
+          const int ik = step, iv = step - 2;  // the producer's order
+          if (ik < n) {
+            const uint32_t G = gb + ik, st = G % kStagesK;
+            ok = mbar_wait(bars.at(Bars::kKFull + st), (G / kStagesK) & 1, wc, kS64KFull);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const uint32_t ksf = base + kOffSFK + st * kSfBytes;
+            tc_cp_sf(tmem + kTmSFK64 + 8 * st, ksf);
+            tc_cp_sf(tmem + kTmSFK64 + 8 * st + 4, ksf + 512);
+            tc_commit(bars.at(Bars::kKsf + st));
+          }
+          if (iv >= 0 && iv < n) {
+            const uint32_t G = gb + iv, st = G % kStagesV;
+            ok = mbar_wait(bars.at(Bars::kVFull + st), (G / kStagesV) & 1, wc, kS64VFull);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const uint32_t vsf = base + kOffSFV + st * kSfBytes;
+            tc_cp_sf(tmem + kTmSFV64 + 8 * st, vsf);
+            tc_cp_sf(tmem + kTmSFV64 + 8 * st + 4, vsf + 512);
+            tc_commit(bars.at(Bars::kVsf + st));
+          }
+        }
+        gb += n;
+        ti += 1;
       }
-      bulk_wait_group0();
+      if (!ok) {
+        const uint64_t t0 = globaltimer_ns();
+        tc_commit(bars.at(Bars::kDrain + 2));
+        while (!mbar_try_wait(bars.at(Bars::kDrain + 2), 0) && globaltimer_ns() - t0 < 50ull * 1000 * 1000) {}
+      }
     }
   } else {
     // =========================================== softmax warpgroups =============================
@@ -435,8 +575,8 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
 
       for (int j = (wg - 2 * (int)gb) & 3; j < 2 * n; j += 4) {
         const uint32_t J = 2 * gb + j, slot = J % kPSlots;  // J % 4 == wg
-        const int nb = n - 1 - (j >> 1);
-        const int h64 = 1 - (j & 1);
+        const int nb = j >> 1;
+        const int h64 = j & 1;
         const uint32_t bar_s = bars.at(Bars::kSFull + wg), par_s = (J / kSBufs) & 1;
         const uint32_t bar_p = bars.at(Bars::kPvDone + slot), par_p = ((J - kPSlots) / kPSlots) & 1;
         const bool r_p = (J >= kPSlots) ? mbar_test(bar_p, par_p) : true;
@@ -475,11 +615,16 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
         const float m_loc = fmaxf(fmaxf(bm4[0], bm4[1]), fmaxf(bm4[2], bm4[3]));
         float m_prev = kNegInf;
         FA4_PH(2);
-        if (j > 0) {
+        // Every sub-block but the CTA's very first waits for its predecessor's hand-over, also the
+        // first one of a tile (which ignores the value): the unbroken chain is what orders the
+        // reuse of a slot -- the value of sub-block J is overwritten by J + 4, which follows
+        // J + 3, J + 2 and J + 1, and J + 1 has read it -- and keeps a barrier from running two
+        // phases ahead of its waiter.
+        if (J > 0) {
           const uint32_t pw = (uint32_t)(wg + 3) & 3u;
           ok = __all_sync(0xffffffffu, mbar_wait(bars.at(Bars::kHand + pw), ((J - 1) / kSBufs) & 1, wc, kS64Hand));
           if (!ok) break;
-          m_prev = s_hand[pw * 128 + row];
+          if (j > 0) m_prev = s_hand[pw * 128 + row];
         }
         const float m_new = next_reference(m_prev, m_loc, p.sl2);
         s_hand[wg * 128 + row] = m_new;
@@ -512,13 +657,15 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
         // 4. correction (rare, out of line): O holds the sub-blocks before this one relative to
         //    m_prev and must move to m_new before P V of this sub-block is issued; this thread
         //    owns its whole row of O
-        if (j > 0 && __any_sync(0xffffffffu, m_new != m_prev)) {
+        //    (rows whose reference was -inf so far have an all-zero O: nothing to rescale)
+        const bool fix = (m_new != m_prev) && (m_prev != kNegInf);
+        if (j > 0 && __any_sync(0xffffffffu, fix)) {
           const uint32_t Jp = J - 1;
           ok = __all_sync(0xffffffffu, mbar_wait(bars.at(Bars::kPvDone + (Jp % kPSlots)),
                                                  (Jp / kPSlots) & 1, wc, kS64PvDone));
           if (!ok) break;
           tc_fence_after_sync();
-          const float f = (m_new != m_prev) ? reference_factor(m_prev, m_new, p.sl2) : 1.f;
+          const float f = fix ? reference_factor(m_prev, m_new, p.sl2) : 1.f;
           rescale_accumulator(lane_addr + kTmO, f, 4);
           tc_wait_st();
         }
@@ -527,50 +674,27 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
         mbar_arrive(bars.at(Bars::kPFull + slot));
         FA4_TRACE_EV(7, J);
         FA4_PH(5);
+        FA4_PH_COUNT();
       }
       if (!ok) break;
 
       FA4_PH(7);
-      // ---- tile end: combine the four partial row sums, read O, stage the output --------------
-      const int q_idx = t.m_blk * kBlockM + row;
-      float scale = 0.f, m_fin = kNegInf, l_tot = 0.f;
+      // ---- tile end: hand the partial row sum and its reference to the epilogue warpgroup and
+      //      go on with the next tile
       if (n > 0) {
-        volatile float* fin_slot = s_fin + (ti & 1) * (4 * 128 * 2);
+        const uint32_t fb = ti & 1;
+        if (ti >= 2) {
+          ok = __all_sync(0xffffffffu,
+                          mbar_wait(bars.at(Bars::kFinFree + fb), ((ti - 2) >> 1) & 1, wc, kS64FinFree));
+          if (!ok) break;
+        }
+        volatile float* fin_slot = s_fin + fb * (4 * 128 * 2);
         // slot order = position of the warpgroup's first sub-block inside the tile: the summation
         // order of a row then depends on its tile only, not on what the CTA processed before
         const uint32_t fslot = (uint32_t)(wg - 2 * (int)gb) & 3u;
         fin_slot[(fslot * 128 + row) * 2] = l_sum;
         fin_slot[(fslot * 128 + row) * 2 + 1] = m_ref;
-        mbar_arrive(bars.at(Bars::kFin));
-        ok = __all_sync(0xffffffffu, mbar_wait(bars.at(Bars::kFin), ti & 1, wc, kS64Fin));
-        if (!ok) break;
-        float lw[4], mw[4];
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-          lw[w] = fin_slot[(w * 128 + row) * 2];
-          mw[w] = fin_slot[(w * 128 + row) * 2 + 1];
-          m_fin = fmaxf(m_fin, mw[w]);
-        }
-#pragma unroll
-        for (int w = 0; w < 4; ++w) l_tot += lw[w] * reference_factor(mw[w], m_fin, p.sl2);
-        if (m_fin == kNegInf) l_tot = 0.f;
-        const uint32_t Jl = 2 * gb + 2 * n - 1;
-        ok = __all_sync(0xffffffffu,
-                        mbar_wait(bars.at(Bars::kPvDone + (Jl % kPSlots)), (Jl / kPSlots) & 1, wc, kS64FinalO));
-        if (!ok) break;
-        tc_fence_after_sync();
-        scale = (l_tot > 0.f) ? p.out_scale / l_tot : 0.f;
-      }
-      if (it >= 1) {
-        ok = __all_sync(0xffffffffu, mbar_wait(bars.at(Bars::kStageFree), (it - 1) & 1, wc, kS64StageFree));
-        if (!ok) break;
-      }
-      stage_accumulator_chunk<true>(lane_addr + kTmO + 32 * wg, gbase + kOffOut, row, wg, scale,
-                                    n > 0 ? bars.at(Bars::kOFree) : 0u);
-      fence_proxy_async_smem();
-      mbar_arrive(bars.at(Bars::kOStaged));
-      if (wg == 0 && q_idx < p.Sq && p.lse != nullptr) {
-        p.lse[((int64_t)t.b * p.Hq + t.h) * p.Sq + q_idx] = finish_lse(m_fin, l_tot, p.sl2);
+        mbar_arrive(bars.at(Bars::kFin + fb));
       }
       gb += n;
       ti += (n > 0) ? 1u : 0u;

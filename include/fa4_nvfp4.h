@@ -58,7 +58,8 @@ enum {
   FA4_E_VARIANT = 5,     /* unknown kernel variant */
   FA4_E_TENSORMAP = 6,   /* the driver rejected a TMA tensor map */
   FA4_E_STRUCT = 7,      /* struct_size does not match this ABI */
-  FA4_E_TOO_LARGE = 8    /* problem exceeds a fixed capacity of the entry point */
+  FA4_E_TOO_LARGE = 8,   /* problem exceeds a fixed capacity of the entry point */
+  FA4_E_BUILD = 9        /* the library was compiled with a register count its kernels cannot run with */
 };
 
 /* device status word: 0 = ok; otherwise (code << 24) | (site << 16) | (blockIdx.x & 0xffff) */
@@ -69,11 +70,13 @@ enum {
 
 /* kernel variants */
 enum {
-  FA4_VARIANT_AUTO = 0,
+  FA4_VARIANT_AUTO = 0,   /* WS64 where it applies, else WS */
   FA4_VARIANT_SERIAL = 1, /* one warpgroup does every step in turn (bring-up / cross-check) */
-  FA4_VARIANT_WS = 2,     /* warp-specialised load / MMA / softmax pipeline */
-  FA4_VARIANT_WS64 = 3    /* the same with 64-key sub-blocks and four score buffers (D = 128, no
-                             split / window / sink) */
+  FA4_VARIANT_WS = 2,     /* warp-specialised pipeline, steps of 128 keys from the last visible
+                             block down; every feature, D = 128 and 64 */
+  FA4_VARIANT_WS64 = 3    /* warp-specialised pipeline, steps of 64 keys upwards, four score
+                             buffers, separate epilogue warpgroup; D = 128 without split /
+                             window / sink (-FA4_E_SHAPE otherwise) */
 };
 
 typedef struct fa4_nvfp4_params {

@@ -202,10 +202,10 @@ def attention_oracle_a(q, k, v, causal=False, softmax_scale=None, window=(None, 
 # attention, oracle B: the kernel's arithmetic model (P re-quantised to NVFP4)
 # --------------------------------------------------------------------------------------------
 def quantize_p_block_model(x: torch.Tensor, m_ref: torch.Tensor):
-    """x: (..., 128) scaled scores in log2 units of ONE K/V block, m_ref: (..., 1) reference
+    """x: (..., 16 k) scaled scores in log2 units of ONE step of keys, m_ref: (..., 1) reference
     maximum in the same units (finite).  Returns (p_hat, p_sum): the de-quantised P' the tensor
     core multiplies with V, and the un-rounded row sums of P' (P' = 2^P_SHIFT * 2^(x - m_ref))."""
-    xb = x.reshape(x.shape[:-1] + (8, BLOCK))
+    xb = x.reshape(x.shape[:-1] + (x.shape[-1] // BLOCK, BLOCK))
     bmax = xb.amax(dim=-1, keepdim=True)
     t = bmax - m_ref[..., None] + P_SHIFT
     e = torch.clamp(torch.ceil(t - LOG2_6), float(P_EMIN), 8.0)
@@ -218,7 +218,8 @@ def quantize_p_block_model(x: torch.Tensor, m_ref: torch.Tensor):
 
 
 def attention_oracle_b(qd, kd, vd, sl2: float, v_scale_out: float = 1.0, causal=False,
-                       num_splits: int = 1, window=(None, None), sink=None):
+                       num_splits: int = 1, window=(None, None), sink=None,
+                       step_keys: int = 128, ascending: bool = False):
     """Kernel model.  qd (B,Sq,Hq,D), kd (B,Sk,Hkv,D), vd (B,Sk,Hkv,Dv): fp32 values the tensor
     core sees (e2m1 * block scale, WITHOUT the per-tensor scales); sl2 = softmax_scale * q_scale
     * k_scale * log2(e); v_scale_out = v_scale.  Walks the K/V blocks of 128 keys from the last
@@ -227,7 +228,14 @@ def attention_oracle_b(qd, kd, vd, sl2: float, v_scale_out: float = 1.0, causal=
     num_splits contiguous shares (ceil division, in visit order), each share starts from a fresh
     reference maximum, and the shares are merged with exp(lse_i - lse) weights (the combine
     step of the reference, tests/cute/test_flash_attn_fast.py:295-300).
+    step_keys / ascending select the kernel that is modelled: the 128-key kernel takes steps of
+    128 keys from the last visible block down (the defaults); the 64-key kernel
+    (csrc/attn_ws64.cuh) takes steps of 64 keys upwards from key 0.  The set of visited keys is
+    the same (whole 128-key blocks); the step decides where the lazy reference maximum may move,
+    hence the scaling under which P is rounded to e2m1.
     Returns (out fp32 (B,Sq,Hq,Dv) before bf16 rounding, lse (B,Hq,Sq))."""
+    assert step_keys in (64, 128) and (step_keys == 128 or num_splits == 1)
+    sub = 128 // step_keys
     qd, kd, vd = (torch.as_tensor(t, dtype=torch.float32) for t in (qd, kd, vd))
     B, Sq, Hq, D = qd.shape
     Sk, Hkv, Dv = kd.shape[1], kd.shape[2], vd.shape[3]
@@ -258,7 +266,11 @@ def attention_oracle_b(qd, kd, vd, sl2: float, v_scale_out: float = 1.0, causal=
                 mask = _visibility_mask(Sq, Sk, causal, window)
                 if mask is not None:
                     s_all[:, :Sk] = s_all[:, :Sk].masked_fill(mask[rows], float("-inf"))
-                visit = list(range(n_blocks - 1, n_min - 1, -1))
+                if ascending:
+                    visit = list(range(n_min * sub, n_blocks * sub))
+                else:
+                    visit = [nb * sub + h for nb in range(n_blocks - 1, n_min - 1, -1)
+                             for h in range(sub - 1, -1, -1)]
                 per = (len(visit) + num_splits - 1) // num_splits if visit else 0
                 parts = []
                 for sp in range(num_splits):
@@ -267,7 +279,7 @@ def attention_oracle_b(qd, kd, vd, sl2: float, v_scale_out: float = 1.0, causal=
                     l_sum = torch.zeros(nr)
                     acc = torch.zeros(nr, Dv)
                     for nb in share:
-                        s = s_all[:, nb * 128:(nb + 1) * 128]
+                        s = s_all[:, nb * step_keys:(nb + 1) * step_keys]
                         m_loc = s.amax(dim=-1)
                         keep = torch.isfinite(m_ref) & ((m_loc - m_ref) * sl2 <= P_LAZY)
                         m_new = torch.where(keep, m_ref, torch.maximum(m_ref, m_loc))
@@ -279,7 +291,7 @@ def attention_oracle_b(qd, kd, vd, sl2: float, v_scale_out: float = 1.0, causal=
                         m_ref = m_new
                         msc = torch.where(torch.isfinite(m_ref), m_ref * sl2, torch.zeros(nr))
                         p_hat, p_sum = quantize_p_block_model(s * sl2, msc[:, None])
-                        acc = acc + p_hat @ v_pad[nb * 128:(nb + 1) * 128]
+                        acc = acc + p_hat @ v_pad[nb * step_keys:(nb + 1) * step_keys]
                         l_sum = l_sum + p_sum
                     if sink is not None and sp == 0:
                         # the sink joins the row sum of split 0; a row without keys keeps LSE = sink

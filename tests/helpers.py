@@ -38,8 +38,19 @@ def make_qkv(B, Sq, Sk, Hq, Hkv, D, seed, v_std=1.0, outlier_frac=0.0, device="c
     return tuple(t.bfloat16().to(device) for t in (q, k, v))
 
 
-def oracles(Q, K, V, causal, softmax_scale=None, num_splits=1, window=(None, None), sink=None):
-    """Q, K, V: NVFP4Tensor with linear scales.  Returns (out_a, lse_a, out_b, lse_b) on CPU."""
+def kernel_model(D, num_splits=1, window=(None, None), sink=None, variant=0):
+    """Which kernel the library's automatic choice runs, as oracle B keywords: the 64-key kernel
+    for head dim 128 without split / window / sink, the 128-key kernel otherwise (mirrors
+    launch_fwd in csrc/api.cu).  ``variant`` 1 / 2 force the 128-key model, 3 the 64-key one."""
+    plain = num_splits == 1 and window == (None, None) and sink is None
+    if variant == 3 or (variant == 0 and D == 128 and plain):
+        return {"step_keys": 64, "ascending": True}
+    return {"step_keys": 128, "ascending": False}
+
+
+def oracles(Q, K, V, causal, softmax_scale=None, num_splits=1, window=(None, None), sink=None, variant=0):
+    """Q, K, V: NVFP4Tensor with linear scales.  Returns (out_a, lse_a, out_b, lse_b) on CPU;
+    oracle B models the kernel that ``variant`` (0 = automatic) selects for this problem."""
     qd, kd, vd = Q.dequantize().cpu(), K.dequantize().cpu(), V.dequantize().cpu()
     D = qd.shape[-1]
     scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(D)
@@ -47,7 +58,8 @@ def oracles(Q, K, V, causal, softmax_scale=None, num_splits=1, window=(None, Non
     sl2 = float(torch.tensor(scale, dtype=torch.float32) * torch.tensor(Q.scale, dtype=torch.float32)
                 * torch.tensor(K.scale, dtype=torch.float32) * torch.tensor(LOG2E, dtype=torch.float32))
     ob, lb = orc.attention_oracle_b(qd / Q.scale, kd / K.scale, vd / V.scale, sl2, V.scale, causal=causal,
-                                    num_splits=num_splits, window=window, sink=sink)
+                                    num_splits=num_splits, window=window, sink=sink,
+                                    **kernel_model(D, num_splits, window, sink, variant))
     return oa, la, ob, lb
 
 

@@ -14,7 +14,7 @@ from tests.helpers import assert_parity, make_qkv, oracles
 
 pytestmark = pytest.mark.gpu
 
-VARIANTS = [fa.VARIANT_SERIAL, fa.VARIANT_WS]
+VARIANTS = [fa.VARIANT_SERIAL, fa.VARIANT_WS, fa.VARIANT_WS64]
 
 
 def run(Q, K, V, causal, variant=fa.VARIANT_AUTO, **kw):
@@ -119,7 +119,7 @@ def test_parity_with_oracle(cuda_device, case, variant):
     out, lse = run(Q, K, V, causal, variant)
     assert out.dtype == torch.bfloat16 and out.shape == (B, Sq, Hq, 128)
     assert lse.dtype == torch.float32 and lse.shape == (B, Hq, Sq)
-    assert_parity(out, lse, *oracles(Q, K, V, causal))
+    assert_parity(out, lse, *oracles(Q, K, V, causal, variant=variant))
 
 
 # (the ragged fixture has Sk = 208, not a multiple of the kernel's 32-key granule: oracle only)
@@ -195,23 +195,29 @@ def _cfg(name, device):
     return Q, K, V, causal
 
 
+@pytest.mark.parametrize("kernel", [fa.VARIANT_WS, fa.VARIANT_WS64], ids=["ws128", "ws64"])
 @pytest.mark.parametrize("name", ["cfg1", "cfg2"])
-def test_full_size_properties(cuda_device, name):
+def test_full_size_properties(cuda_device, name, kernel):
     Q, K, V, causal = _cfg(name, cuda_device)
-    out, lse = run(Q, K, V, causal, fa.VARIANT_WS)
+    out, lse = run(Q, K, V, causal, kernel)
     assert torch.isfinite(out.float()).all() and torch.isfinite(lse).all()
     # determinism: a second run gives the same bits
-    out2, lse2 = run(Q, K, V, causal, fa.VARIANT_WS)
+    out2, lse2 = run(Q, K, V, causal, kernel)
     assert torch.equal(out, out2) and torch.equal(lse, lse2)
-    # the two kernel variants agree to one bf16 rounding
     outs, lses = run(Q, K, V, causal, fa.VARIANT_SERIAL)
     e = orc.error_metrics(out.float(), outs.float())
-    assert e["rel_rms"] < 1e-3 and e["max_abs"] <= 2.0 ** -7 * outs.float().abs().max().item(), e
+    if kernel == fa.VARIANT_WS:
+        # same steps, same order as the bring-up kernel: they agree to one bf16 rounding
+        assert e["rel_rms"] < 1e-3 and e["max_abs"] <= 2.0 ** -7 * outs.float().abs().max().item(), e
+    else:
+        # 64-key steps in ascending order round P under other references: two independent 4-bit
+        # roundings of the same attention (each about 0.13 from the exact result)
+        assert e["rel_rms"] < 0.25, e
     assert (lse - lses).abs().max().item() < 1e-4
     del outs, lses, out2, lse2
     # linearity in V: doubling V's tensor scale doubles O exactly (power of two), LSE unchanged
     V2 = fa.NVFP4Tensor(V.data, V.sf, 2.0 * V.scale, True, True)
-    out_v2, lse_v2 = run(Q, K, V2, causal, fa.VARIANT_WS)
+    out_v2, lse_v2 = run(Q, K, V2, causal, kernel)
     assert torch.equal(out_v2.float(), 2.0 * out.float()) and torch.equal(lse_v2, lse)
     # every output row is a convex combination of V rows: bounded by max |V|
     vmax = 6.0 * 448.0 * V.scale
@@ -220,7 +226,7 @@ def test_full_size_properties(cuda_device, name):
     Qs = fa.NVFP4Tensor(Q.data[1:2], Q.sf[1:2], Q.scale, True)
     Ks = fa.NVFP4Tensor(K.data[1:2], K.sf[1:2], K.scale, True)
     Vs = fa.NVFP4Tensor(V.data[1:2], V.sf[1:2], V.scale, True, True)
-    o1, l1 = run(Qs, Ks, Vs, causal, fa.VARIANT_WS)
+    o1, l1 = run(Qs, Ks, Vs, causal, kernel)
     assert torch.equal(o1, out[1:2]) and torch.equal(l1, lse[1:2])
 
 
@@ -228,7 +234,7 @@ def test_sampled_heads_of_cfg2_against_oracle(cuda_device):
     """cfg2-shaped problem (S = 8192 causal GQA), two (batch, head) pairs checked against exact
     attention on a window of query rows (the full oracle would need 34 GB of scores)."""
     Q, K, V, causal = _cfg("cfg2", cuda_device)
-    out, lse = run(Q, K, V, causal, fa.VARIANT_WS)
+    out, lse = run(Q, K, V, causal)          # the automatic choice, what the benchmark times
     g = torch.Generator(device=cuda_device).manual_seed(0)
     S = 8192
     q = torch.randn(4, S, 32, 128, generator=g, device=cuda_device, dtype=torch.bfloat16)

@@ -106,6 +106,14 @@ def test_oracle_b_close_to_a():
         e = orc.error_metrics(ob, oa)
         assert e["rel_rms"] < 0.2, e
         assert orc.error_metrics(lb, la)["max_abs"] < 1e-4
+        # the model of the 64-key kernel (steps of 64 keys, ascending): another rounding of P under
+        # other reference maxima, the same distance from exact attention and the same LSE
+        o64, l64 = orc.attention_oracle_b(qd / Q.scale, kd / K.scale, vd / V.scale, sl2, V.scale, causal=causal,
+                                          step_keys=64, ascending=True)
+        e64 = orc.error_metrics(o64, oa)
+        assert abs(e64["rel_rms"] - e["rel_rms"]) < 0.03, (e64, e)
+        assert orc.error_metrics(l64, la)["max_abs"] < 1e-4
+        assert not torch.equal(o64, ob)
 
 
 def test_flops_formula():
