@@ -235,10 +235,12 @@ def run_gpu_arm(args, wl, rank, local_rank, world):
     lse = torch.empty(B, Hq, S, dtype=torch.float32, device=dev)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
 
+    variant = fa.VARIANT_WS if args.kernel == "ws128" else fa.VARIANT_AUTO
+
     def step():
         fa.flash_attn_fp4_func(Qt.data, Kt.data, Vt.data, Qt.sf, Kt.sf, Vt.sf, Qt.scale, Kt.scale,
                                Vt.scale, causal=causal, return_lse=True, out=out, lse=lse,
-                               sf_layout="tiled")
+                               sf_layout="tiled", variant=variant)
 
     def barrier():
         if world > 1:
@@ -316,7 +318,9 @@ def run_gpu_arm(args, wl, rank, local_rank, world):
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "nvfp4", "data": "synthetic",
-            "config": workload_config(args.workload, wl, world),
+            "config": dict(workload_config(args.workload, wl, world),
+                           kernel="attn_fwd_ws64_kernel (automatic choice)" if args.kernel == "auto"
+                           else "attn_fwd_ws_kernel<128> (forced)"),
             "tflops_per_gpu": tflops_gpu,
             "tokens_per_s": B * S * world / (ms_per_step * 1e-3),
             "pct_fp4_peak_nominal": 100.0 * tflops_gpu / FP4_NOMINAL_TFLOPS,
@@ -355,11 +359,12 @@ def run_gpu_arm(args, wl, rank, local_rank, world):
         dist.destroy_process_group()
 
 
-# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the attention kernel,
-# from the ncu captures summarised under profiles/.  cfg2 was captured whole (118.8 MB read +
-# 220.1 MB written); cfg1 is the capture of half of it (B = 2: 81.9 MB + 58.3 MB) scaled by the
-# batch, which the traffic is proportional to.  None for workloads that were not captured.
-TRAFFIC_BYTES = {"cfg2": 338_914_304, "cfg1": 2 * 140_234_752}
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the attention kernel the
+# automatic choice runs (attn_fwd_ws64_kernel), from the ncu captures summarised under profiles/.
+# cfg2 was captured whole (121.1 MB read + 218.3 MB written); cfg1 is the capture of half of it
+# (B = 2: 68.0 MB + 42.3 MB) scaled by the batch, which the traffic is proportional to.  None for
+# workloads that were not captured.
+TRAFFIC_BYTES = {"cfg2": 339_312_128, "cfg1": 2 * 110_339_584}
 
 
 def run_sweep(args):
@@ -423,6 +428,9 @@ def main():
     ap.add_argument("--workload", default="cfg2")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--kernel", default="auto", choices=["auto", "ws128"],
+                    help="auto: the library's choice (the 64-key kernel for these workloads); ws128: force "
+                         "the 128-key kernel that serves head dim 64 / split-KV / windows / sinks")
     args = ap.parse_args()
     if args.workload == "sweep":
         if not torch.cuda.is_available():

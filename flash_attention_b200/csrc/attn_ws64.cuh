@@ -100,7 +100,7 @@ struct Bars {
   static constexpr uint32_t kQFull = 0, kQEmpty = 2, kKFull = 4, kVFull = kKFull + kStagesK,
                             kKFree = kVFull + kStagesV, kVFree = kKFree + kStagesK,
                             kSFull = kVFree + kStagesV, kSFree = kSFull + kSBufs,
-                            kHand = kSFree + kSBufs, kPFull = kHand + kSBufs, kPvDone = kPFull + kPSlots,
+                            kHand = kSFree + kSBufs, kPFull = kHand + 4 * kSBufs, kPvDone = kPFull + kPSlots,
                             kFin = kPvDone + kPSlots, kFinFree = kFin + 2, kOFree = kFinFree + 2,
                             kEpi = kOFree + 1, kKsf = kEpi + 1, kVsf = kKsf + kStagesK,
                             kDrain = kVsf + kStagesV, kCount = kDrain + 3;
@@ -173,7 +173,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
     for (int s = 0; s < kSBufs; ++s) {
       mbar_init(bars.at(Bars::kSFull + s), 1);
       mbar_init(bars.at(Bars::kSFree + s), 128);    // the softmax warpgroup that owns the buffer
-      mbar_init(bars.at(Bars::kHand + s), 128);
+      for (int q = 0; q < 4; ++q) mbar_init(bars.at(Bars::kHand + 4 * s + q), 32);  // per warp quarter
     }
     for (int s = 0; s < kPSlots; ++s) {
       mbar_init(bars.at(Bars::kPFull + s), 128);
@@ -200,7 +200,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
-  constexpr uint32_t idesc_qk = make_idesc_nvf4(128, 64);
+  constexpr uint32_t idesc_qk = make_idesc_nvf4(128, 128);
   constexpr uint32_t idesc_pv = make_idesc_nvf4(128, 128);
 
 #define FA4_FOR_EACH_TILE                                                                        \
@@ -415,33 +415,28 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
           tc_fence_after_sync();
           const uint32_t sfk = tmem + kTmSFK64 + 8 * st;
           const uint32_t kt = base + kOffK + st * kTileBytes;
-#pragma unroll
-          for (int s = 0; s < 2; ++s) {
-            const uint32_t J = 2 * G + s, buf = J % kSBufs;
-            const uint32_t h64 = s;  // lower half of the block first
-            FA4_PH(0);
-            if (J >= kSBufs) {
-              // the buffer is free once sub-block J - 4 has been read by statistics and softmax
-              ok = mbar_wait(bars.at(Bars::kSFree + buf), ((J - kSBufs) / kSBufs) & 1, wc, kS64SFree);
-              if (!ok) break;
-              tc_fence_after_sync();
-            }
-            FA4_TRACE_EV(21, J);
-            FA4_PH(2);
-            const uint32_t s_tm = tmem + kTmS64 + 64 * buf;
-            // B operand: rows 64 h64 .. 64 h64 + 63 of the K tile; their scales sit two columns
-            // further in each 4-column group of the copied chunk
-#pragma unroll
-            for (int ks = 0; ks < 2; ++ks) {
-              mma_nvf4(s_tm, dq[ks], make_desc_sw64(kt + h64 * 4096 + 32 * ks), idesc_qk,
-                       tmem + kTmSFQ + 4 * ks, sfk + 4 * ks + 2 * h64, ks > 0 ? 1u : 0u);
-            }
-            FA4_PH(4);
-            tc_commit(bars.at(Bars::kSFull + buf));
-            FA4_PH(5);
-            FA4_TRACE_EV(27, J);
+          // one product of N = 128 fills the two neighbouring S buffers of sub-blocks 2G and 2G + 1
+          // (keys 0-63 and 64-127 of the tile): half the tcgen05 instructions of two N = 64
+          // products, and the in-order issue slots of this thread are scarce
+          const uint32_t J0 = 2 * G, b0 = J0 % kSBufs;  // 0 or 2
+          FA4_PH(0);
+          if (J0 >= kSBufs) {
+            ok = mbar_wait(bars.at(Bars::kSFree + b0), ((J0 - kSBufs) / kSBufs) & 1, wc, kS64SFree) &&
+                 mbar_wait(bars.at(Bars::kSFree + b0 + 1), ((J0 - kSBufs) / kSBufs) & 1, wc, kS64SFree);
+            if (!ok) break;
+            tc_fence_after_sync();
           }
-          if (!ok) break;
+          FA4_TRACE_EV(21, J0);
+          FA4_PH(2);
+#pragma unroll
+          for (int ks = 0; ks < 2; ++ks) {
+            mma_nvf4(tmem + kTmS64 + 64 * b0, dq[ks], make_desc_sw64(kt + 32 * ks), idesc_qk,
+                     tmem + kTmSFQ + 4 * ks, sfk + 4 * ks, ks > 0 ? 1u : 0u);
+          }
+          FA4_PH(4);
+          tc_commit(bars.at(Bars::kSFull + b0));  // both softmax warpgroups of the pair wait on it
+          FA4_PH(5);
+          FA4_TRACE_EV(27, J0);
           tc_commit(bars.at(Bars::kKFree + st));  // the K stage is free once both products have run
         }
         if (!ok) break;
@@ -577,7 +572,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
         const uint32_t J = 2 * gb + j, slot = J % kPSlots;  // J % 4 == wg
         const int nb = j >> 1;
         const int h64 = j & 1;
-        const uint32_t bar_s = bars.at(Bars::kSFull + wg), par_s = (J / kSBufs) & 1;
+        const uint32_t bar_s = bars.at(Bars::kSFull + (wg & 2)), par_s = (J / kSBufs) & 1;
         const uint32_t bar_p = bars.at(Bars::kPvDone + slot), par_p = ((J - kPSlots) / kPSlots) & 1;
         const bool r_p = (J >= kPSlots) ? mbar_test(bar_p, par_p) : true;
 
@@ -622,13 +617,13 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
         // phases ahead of its waiter.
         if (J > 0) {
           const uint32_t pw = (uint32_t)(wg + 3) & 3u;
-          ok = __all_sync(0xffffffffu, mbar_wait(bars.at(Bars::kHand + pw), ((J - 1) / kSBufs) & 1, wc, kS64Hand));
+          ok = __all_sync(0xffffffffu, mbar_wait(bars.at(Bars::kHand + 4 * pw + (warp & 3)), ((J - 1) / kSBufs) & 1, wc, kS64Hand));
           if (!ok) break;
           if (j > 0) m_prev = s_hand[pw * 128 + row];
         }
         const float m_new = next_reference(m_prev, m_loc, p.sl2);
         s_hand[wg * 128 + row] = m_new;
-        mbar_arrive(bars.at(Bars::kHand + wg));
+        mbar_arrive(bars.at(Bars::kHand + 4 * wg + (warp & 3)));
         float noff4[4];
         uint32_t ue;
         block_exponents4(bm4, m_new, p.sl2, noff4, ue);
