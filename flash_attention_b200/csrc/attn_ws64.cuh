@@ -1,32 +1,36 @@
-// Warp-specialised kernel with 64-key sub-blocks and FOUR score buffers (head dim 128).
+// Warp-specialised kernel with 64-key sub-blocks and FOUR score buffers (head dim 128, no
+// split-KV / window / sink: those stay with attn_ws.cuh).
 //
 // The kernel of attn_ws.cuh keeps two 128-column S buffers in tensor memory and lets two pairs of
 // softmax warpgroups alternate over the 128-key blocks, a thread owning half a row.  The two
 // warpgroups of a pair move in lockstep, so a scheduler sees only two independent softmax
 // "strands", each with ~1000 clocks of exponentials and ~2000 clocks of latency-bound prologue /
-// epilogue per block: the exponential unit idles ~40 % of the time.
+// epilogue per block: the exponential unit idles ~40 % of the time, and every tile end drains
+// the pipeline while the softmax warps read the accumulator out.
 //
 // Here a K/V block of 128 keys is processed as two sub-blocks of 64 keys, S has four buffers of 64
 // columns (the same 256 tensor-memory columns), and each of the four softmax warpgroups owns one
-// buffer: a thread holds the 64 scores of one row of one sub-block -- the same register footprint
-// -- but the four warpgroups are independent strands at different phases, and the statistics
-// warpgroup can run up to three sub-blocks ahead of the slowest of them.
+// buffer: a thread holds the 64 scores of one WHOLE row of one sub-block -- the same register
+// footprint -- so it takes the maxima itself (no statistics warpgroup), and the four warpgroups
+// are independent strands at different phases.
 //
-//   warps 0-15  softmax: warpgroup w takes the sub-blocks with running index J % 4 == w
-//   warps 16-19 statistics: every sub-block in order (maxima of its four 16-key blocks, the
-//               running reference maximum)
-//   warp 20     TMA producer (Q double buffered, K / V rings of 128-key tiles)
-//   warp 21     QK^T issuer: per K tile two N = 64 products into two S buffers
-//   warp 22     P V issuer: per sub-block one K = 64 step into O
-//   warp 23     output store (TMA)
+//   warps 0-15  softmax: warpgroup w takes the sub-blocks with running index J % 4 == w; the
+//               running reference maximum of a row is handed from the warpgroup of sub-block
+//               J - 1 to that of J through shared memory
+//   warp 16     TMA producer (Q double buffered, K / V rings of 128-key tiles)
+//   warp 17     QK^T issuer: per K tile one N = 128 product into two neighbouring S buffers
+//   warp 18     P V issuer: per sub-block one K = 64 step into O
+//   warp 19     copies the K / V scale tiles into tensor memory as they land
+//   warps 20-23 epilogue: combine the partial row sums, read O out, TMA store, LSE -- while the
+//               softmax warpgroups already work on the next tile
 //
 // Sub-block j of a tile (visit order): keys 64 j .. 64 j + 63, ascending.  (The 128-key kernel
 // visits the last visible block first; with 64-key steps that order makes the first references
 // of a causal tile rest on one or two keys, and with the small lazy threshold that NVFP4 block
 // scales allow nearly every tile then pays several accumulator corrections, each of which
-// drains the P V pipeline.  Ascending, the first sub-block is fully visible.)  J = 2 * (blocks before this tile) + j selects buffers, P slots
-// and barrier phases.  Everything else (operand formats, P quantisation, lazy reference, bounded
-// waits, epilogue) is as in attn_ws.cuh.
+// drains the P V pipeline.  Ascending, the first sub-block is fully visible.)
+// J = 2 * (blocks before this tile) + j selects buffers, P slots and barrier phases.  Operand
+// formats, P quantisation, lazy reference and bounded waits are those of attn_ws.cuh.
 #pragma once
 #include "attn_ws.cuh"
 
