@@ -84,6 +84,7 @@ static_assert((kThreads / 128) * 32 * kRegsLaunch <= 16384, "register file of a 
 // 8 columns per shared-memory stage, written by the copy warp as soon as the tile has landed
 constexpr uint32_t kTmS64 = 0, kTmSFK64 = 392 /* 4 x 8 */, kTmSFV64 = 424 /* 4 x 8 */, kTmSFP64 = 456 /* 4 x 4 */;
 static_assert(kTmSFP64 + 16 <= 512, "tensor memory columns");
+constexpr uint32_t kSlackNs = 500;         // suspend hint of the waits of roles with slack
 constexpr uint32_t kPTileBytes = 128 * 32;  // 128 rows x 64 e2m1 keys
 
 constexpr uint32_t kOffQ = 0;
@@ -243,7 +244,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
       float scale = 0.f, m_fin = kNegInf, l_tot = 0.f;
       if (n > 0) {
         const uint32_t fb = ti & 1;
-        ok = __all_sync(0xffffffffu, mbar_wait(bars.at(Bars::kFin + fb), (ti >> 1) & 1, wc, kS64Fin));
+        ok = __all_sync(0xffffffffu, mbar_wait_relaxed<kSlackNs>(bars.at(Bars::kFin + fb), (ti >> 1) & 1, wc, kS64Fin));
         if (!ok) break;
         volatile float* fin_slot = s_fin + fb * (4 * 128 * 2);
         float lw[4], mw[4];
@@ -325,7 +326,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
         }
         const uint32_t qb = ti & 1;
         if (ti >= 2) {
-          ok = mbar_wait(bars.at(Bars::kQEmpty + qb), ((ti - 2) >> 1) & 1, wc, kS64QEmpty);
+          ok = mbar_wait_relaxed<kSlackNs>(bars.at(Bars::kQEmpty + qb), ((ti - 2) >> 1) & 1, wc, kS64QEmpty);
           if (!ok) break;
         }
         mbar_arrive_expect_tx(bars.at(Bars::kQFull + qb), kTileBytes + kSfBytes);
@@ -344,7 +345,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
             const uint32_t G = gb + ik, st = G % kStagesK;
             const int nb = ik;  // ascending: the diagonal block of a causal tile comes last
             if (G >= kStagesK) {
-              ok = mbar_wait(bars.at(Bars::kKFree + st), ((G - kStagesK) / kStagesK) & 1, wc, kS64KFree);
+              ok = mbar_wait_relaxed<kSlackNs>(bars.at(Bars::kKFree + st), ((G - kStagesK) / kStagesK) & 1, wc, kS64KFree);
               if (!ok) break;
             }
             mbar_arrive_expect_tx(bars.at(Bars::kKFull + st), kTileBytes + kSfBytes);
@@ -358,7 +359,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
             const uint32_t G = gb + iv, st = G % kStagesV;
             const int nb = iv;
             if (G >= kStagesV) {
-              ok = mbar_wait(bars.at(Bars::kVFree + st), ((G - kStagesV) / kStagesV) & 1, wc, kS64VFree);
+              ok = mbar_wait_relaxed<kSlackNs>(bars.at(Bars::kVFree + st), ((G - kStagesV) / kStagesV) & 1, wc, kS64VFree);
               if (!ok) break;
             }
             mbar_arrive_expect_tx(bars.at(Bars::kVFull + st), kTileBytes + kSfBytes);
@@ -525,7 +526,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
           const int ik = step, iv = step - 2;  // the producer's order
           if (ik < n) {
             const uint32_t G = gb + ik, st = G % kStagesK;
-            ok = mbar_wait(bars.at(Bars::kKFull + st), (G / kStagesK) & 1, wc, kS64KFull);
+            ok = mbar_wait_relaxed<kSlackNs>(bars.at(Bars::kKFull + st), (G / kStagesK) & 1, wc, kS64KFull);
             if (!ok) break;
             tc_fence_after_sync();
             const uint32_t ksf = base + kOffSFK + st * kSfBytes;
@@ -535,7 +536,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
           }
           if (iv >= 0 && iv < n) {
             const uint32_t G = gb + iv, st = G % kStagesV;
-            ok = mbar_wait(bars.at(Bars::kVFull + st), (G / kStagesV) & 1, wc, kS64VFull);
+            ok = mbar_wait_relaxed<kSlackNs>(bars.at(Bars::kVFull + st), (G / kStagesV) & 1, wc, kS64VFull);
             if (!ok) break;
             tc_fence_after_sync();
             const uint32_t vsf = base + kOffSFV + st * kSfBytes;

@@ -120,6 +120,36 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
   }
 }
 
+// The same bounded wait for roles with slack (producer, scale copier, epilogue): a longer suspend
+// hint per poll, so that a warp that waits most of the time takes fewer issue slots from the
+// softmax warps of its scheduler.
+template <uint32_t kHintNs>
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, const WaitCtx& w,
+                                                  uint32_t site) {
+  const uint64_t t0 = globaltimer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i) {
+      uint32_t ok;
+      asm volatile(
+          "{\n"
+          ".reg .pred p;\n"
+          "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+          "selp.b32 %0, 1, 0, p;\n"
+          "}\n"
+          : "=r"(ok)
+          : "r"(bar), "r"(parity), "r"(kHintNs)
+          : "memory");
+      if (ok) return true;
+    }
+    if (*w.s_abort) return false;
+    if (globaltimer_ns() - t0 > w.budget_ns) {
+      report_status(w, kStatusWaitExpired, site);
+      return false;
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // proxy / tcgen05 fences
 // ---------------------------------------------------------------------------------------------
