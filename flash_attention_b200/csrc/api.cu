@@ -150,9 +150,9 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
   for (int64_t s : bstr)
     if (s <= 0 || (s & 15) != 0) return -FA4_E_STRIDE;
   if ((p->o_stride_b & 7) || (p->o_stride_s & 7) || (p->o_stride_h & 7)) return -FA4_E_STRIDE;
-  // automatic choice: the 64-key kernel where it applies (head dim 128, no split / window / sink),
-  // the 128-key kernel for everything else
-  const bool plain = p->D == 128 && num_splits == 1 && win_left < 0 && win_right <= 0 && sink == nullptr;
+  // automatic choice: the 64-key kernel where it applies (no split / window / sink), the 128-key
+  // kernel for everything else
+  const bool plain = num_splits == 1 && win_left < 0 && win_right <= 0 && sink == nullptr;
   int variant = p->variant;
   if (variant == FA4_VARIANT_AUTO) variant = plain ? FA4_VARIANT_WS64 : FA4_VARIANT_WS;
   if (variant != FA4_VARIANT_SERIAL && variant != FA4_VARIANT_WS && variant != FA4_VARIANT_WS64)
@@ -255,10 +255,13 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
     };
     int rc;
     if (variant == FA4_VARIANT_WS64) {
-      if (int e = ensure_smem(attn_fwd_ws64_kernel, ws64::kSmemRequest)) return e;
-      if (int e = ensure_launch_regs(attn_fwd_ws64_kernel, ws64::kRegsLaunch)) return e;
-      attn_fwd_ws64_kernel<<<grid, ws64::kThreads, ws64::kSmemRequest, stream>>>(tm_q, tm_k, tm_v, tm_o, kp);
-      rc = 0;
+      auto launch64 = [&](auto kernel) -> int {
+        if (int e = ensure_smem(kernel, ws64::kSmemRequest)) return e;
+        if (int e = ensure_launch_regs(kernel, ws64::kRegsLaunch)) return e;
+        kernel<<<grid, ws64::kThreads, ws64::kSmemRequest, stream>>>(tm_q, tm_k, tm_v, tm_o, kp);
+        return 0;
+      };
+      rc = p->D == 128 ? launch64(attn_fwd_ws64_kernel<128>) : launch64(attn_fwd_ws64_kernel<64>);
     } else if (p->D == 128) {
       rc = general ? launch(attn_fwd_ws_kernel<128, true>) : launch(attn_fwd_ws_kernel<128, false>);
     } else {

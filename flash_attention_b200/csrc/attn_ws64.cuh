@@ -1,5 +1,5 @@
-// Warp-specialised kernel with 64-key sub-blocks and FOUR score buffers (head dim 128, no
-// split-KV / window / sink: those stay with attn_ws.cuh).
+// Warp-specialised kernel with 64-key sub-blocks and FOUR score buffers (no split-KV / window /
+// sink: those stay with attn_ws.cuh).
 //
 // The kernel of attn_ws.cuh keeps two 128-column S buffers in tensor memory and lets two pairs of
 // softmax warpgroups alternate over the 128-key blocks, a thread owning half a row.  The two
@@ -129,6 +129,11 @@ __device__ __forceinline__ uint32_t sw32_offset(uint32_t row, uint32_t chunk) {
 
 }  // namespace ws64
 
+// kD: head dimension of Q, K and V (128 or 64).  It sets the number of 64-element steps of Q K^T,
+// the bytes of a Q / K tile (128 rows of kD / 2 bytes: 64-byte-swizzled rows for 128, 32-byte for
+// 64) and of a V tile (kD rows of 128 keys), and the width of O.  Shared and tensor memory are
+// laid out for 128 either way.
+template <int kD>
 __global__ void __launch_bounds__(ws64::kThreads, 1)
 attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
                      const __grid_constant__ CUtensorMap tm_k,
@@ -205,8 +210,13 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
+  static_assert(kD == 128 || kD == 64, "head dimensions built: 128 and 64");
   constexpr uint32_t idesc_qk = make_idesc_nvf4(128, 128);
-  constexpr uint32_t idesc_pv = make_idesc_nvf4(128, 128);
+  constexpr uint32_t idesc_pv = make_idesc_nvf4(128, kD);
+  constexpr int kSteps = kD / 64;                      // 64-element steps of Q K^T
+  constexpr uint32_t kQkBytes = 128u * kD / 2;         // bytes of a Q or K tile
+  constexpr uint32_t kQkSfBytes = kSteps * 512u;       // its scale chunks (128 rows x kD / 16)
+  constexpr uint32_t kVBytes = kD * 64u;               // V tile: kD rows of 128 keys
 
 #define FA4_FOR_EACH_TILE                                                                        \
   uint32_t gb = 0, ti = 0;                                                                       \
@@ -271,13 +281,13 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
         FA4_EPI_SYNC()
       }
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < kD / 32; ++c) {
         uint8_t* box_row = gbase + kOffOut + (c >> 1) * (16 * 1024) + row * 128;
         uint32_t o[32];
         if (n > 0) {
           tmem_ld32(lane_addr + kTmO + 32 * c, o);
           tc_wait_ld();
-          if (c == 3) {
+          if (c == kD / 32 - 1) {
             tc_fence_before_sync();
             mbar_arrive(bars.at(Bars::kOFree));  // the P V issuer may start the next tile
           }
@@ -299,8 +309,10 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
       fence_proxy_async_smem();
       FA4_EPI_SYNC()
       if (leader) {
-        tma_store_4d(&tm_o, base + kOffOut, 0, t.h, t.m_blk * kBlockM, t.b);
-        tma_store_4d(&tm_o, base + kOffOut + 16 * 1024, 64, t.h, t.m_blk * kBlockM, t.b);
+#pragma unroll
+        for (int bx = 0; bx < kD / 64; ++bx) {
+          tma_store_4d(&tm_o, base + kOffOut + bx * 16 * 1024, 64 * bx, t.h, t.m_blk * kBlockM, t.b);
+        }
         bulk_commit_group();
       }
       if (q_idx < p.Sq && p.lse != nullptr) {
@@ -329,12 +341,12 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
           ok = mbar_wait_relaxed<kSlackNs>(bars.at(Bars::kQEmpty + qb), ((ti - 2) >> 1) & 1, wc, kS64QEmpty);
           if (!ok) break;
         }
-        mbar_arrive_expect_tx(bars.at(Bars::kQFull + qb), kTileBytes + kSfBytes);
+        mbar_arrive_expect_tx(bars.at(Bars::kQFull + qb), kQkBytes + kQkSfBytes);
         tma_load_4d(base + kOffQ + qb * kTileBytes, &tm_q, bars.at(Bars::kQFull + qb), 0, t.h,
                     t.m_blk * kBlockM, t.b);
         bulk_load(base + kOffSFQ + qb * kSfBytes,
-                  p.q_sf + t.b * p.qsf_stride_b + t.h * p.qsf_stride_h + (int64_t)t.m_blk * kSfBytes,
-                  kSfBytes, bars.at(Bars::kQFull + qb));
+                  p.q_sf + t.b * p.qsf_stride_b + t.h * p.qsf_stride_h + (int64_t)t.m_blk * kQkSfBytes,
+                  kQkSfBytes, bars.at(Bars::kQFull + qb));
         issued_q = ti + 1;
         const uint8_t* ksf = p.k_sf + t.b * p.ksf_stride_b + t.hk * p.ksf_stride_h;
         const uint8_t* vsf = p.v_sf + t.b * p.vsf_stride_b + t.hk * p.vsf_stride_h;
@@ -348,10 +360,10 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
               ok = mbar_wait_relaxed<kSlackNs>(bars.at(Bars::kKFree + st), ((G - kStagesK) / kStagesK) & 1, wc, kS64KFree);
               if (!ok) break;
             }
-            mbar_arrive_expect_tx(bars.at(Bars::kKFull + st), kTileBytes + kSfBytes);
+            mbar_arrive_expect_tx(bars.at(Bars::kKFull + st), kQkBytes + kQkSfBytes);
             tma_load_4d(base + kOffK + st * kTileBytes, &tm_k, bars.at(Bars::kKFull + st), 0, t.hk,
                         nb * kBlockN, t.b);
-            bulk_load(base + kOffSFK + st * kSfBytes, ksf + (int64_t)nb * kSfBytes, kSfBytes,
+            bulk_load(base + kOffSFK + st * kSfBytes, ksf + (int64_t)nb * kQkSfBytes, kQkSfBytes,
                       bars.at(Bars::kKFull + st));
             issued_k = G + 1;
           }
@@ -362,7 +374,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
               ok = mbar_wait_relaxed<kSlackNs>(bars.at(Bars::kVFree + st), ((G - kStagesV) / kStagesV) & 1, wc, kS64VFree);
               if (!ok) break;
             }
-            mbar_arrive_expect_tx(bars.at(Bars::kVFull + st), kTileBytes + kSfBytes);
+            mbar_arrive_expect_tx(bars.at(Bars::kVFull + st), kVBytes + kSfBytes);
             tma_load_4d(base + kOffV + st * kTileBytes, &tm_v, bars.at(Bars::kVFull + st),
                         nb * (kBlockN / 2), 0, t.hk, t.b);
             bulk_load(base + kOffSFV + st * kSfBytes, vsf + (int64_t)nb * kSfBytes, kSfBytes,
@@ -403,11 +415,11 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
         ok = mbar_wait(bars.at(Bars::kQFull + qb), (ti >> 1) & 1, wc, kS64QFull);
         if (!ok) break;
         tc_fence_after_sync();
-        uint64_t dq[2];
+        uint64_t dq[kSteps];
 #pragma unroll
-        for (int ks = 0; ks < 2; ++ks) {
+        for (int ks = 0; ks < kSteps; ++ks) {
           tc_cp_sf(tmem + kTmSFQ + 4 * ks, base + kOffSFQ + qb * kSfBytes + 512 * ks);
-          dq[ks] = make_desc_sw64(base + kOffQ + qb * kTileBytes + 32 * ks);
+          dq[ks] = ws::make_desc_qk<kD>(base + kOffQ + qb * kTileBytes, ks);
         }
         for (int i = 0; ok && i < n; ++i) {
           const uint32_t G = gb + i, st = G % kStagesK;
@@ -434,8 +446,8 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
           FA4_TRACE_EV(21, J0);
           FA4_PH(2);
 #pragma unroll
-          for (int ks = 0; ks < 2; ++ks) {
-            mma_nvf4(tmem + kTmS64 + 64 * b0, dq[ks], make_desc_sw64(kt + 32 * ks), idesc_qk,
+          for (int ks = 0; ks < kSteps; ++ks) {
+            mma_nvf4(tmem + kTmS64 + 64 * b0, dq[ks], ws::make_desc_qk<kD>(kt, ks), idesc_qk,
                      tmem + kTmSFQ + 4 * ks, sfk + 4 * ks, ks > 0 ? 1u : 0u);
           }
           FA4_PH(4);
@@ -530,8 +542,8 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
             if (!ok) break;
             tc_fence_after_sync();
             const uint32_t ksf = base + kOffSFK + st * kSfBytes;
-            tc_cp_sf(tmem + kTmSFK64 + 8 * st, ksf);
-            tc_cp_sf(tmem + kTmSFK64 + 8 * st + 4, ksf + 512);
+#pragma unroll
+            for (int ks = 0; ks < kSteps; ++ks) tc_cp_sf(tmem + kTmSFK64 + 8 * st + 4 * ks, ksf + 512 * ks);
             tc_commit(bars.at(Bars::kKsf + st));
           }
           if (iv >= 0 && iv < n) {
@@ -666,7 +678,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
           if (!ok) break;
           tc_fence_after_sync();
           const float f = fix ? reference_factor(m_prev, m_new, p.sl2) : 1.f;
-          rescale_accumulator(lane_addr + kTmO, f, 4);
+          rescale_accumulator(lane_addr + kTmO, f, kD / 32);
           tc_wait_st();
         }
         fence_proxy_async_smem();

@@ -75,8 +75,8 @@ enum {
   FA4_VARIANT_WS = 2,     /* warp-specialised pipeline, steps of 128 keys from the last visible
                              block down; every feature, D = 128 and 64 */
   FA4_VARIANT_WS64 = 3    /* warp-specialised pipeline, steps of 64 keys upwards, four score
-                             buffers, separate epilogue warpgroup; D = 128 without split /
-                             window / sink (-FA4_E_SHAPE otherwise) */
+                             buffers, separate epilogue warpgroup; no split / window / sink
+                             (-FA4_E_SHAPE otherwise) */
 };
 
 typedef struct fa4_nvfp4_params {

@@ -40,10 +40,10 @@ def make_qkv(B, Sq, Sk, Hq, Hkv, D, seed, v_std=1.0, outlier_frac=0.0, device="c
 
 def kernel_model(D, num_splits=1, window=(None, None), sink=None, variant=0):
     """Which kernel the library's automatic choice runs, as oracle B keywords: the 64-key kernel
-    for head dim 128 without split / window / sink, the 128-key kernel otherwise (mirrors
+    without split / window / sink, the 128-key kernel otherwise (mirrors
     launch_fwd in csrc/api.cu).  ``variant`` 1 / 2 force the 128-key model, 3 the 64-key one."""
     plain = num_splits == 1 and window == (None, None) and sink is None
-    if variant == 3 or (variant == 0 and D == 128 and plain):
+    if variant == 3 or (variant == 0 and plain):
         return {"step_keys": 64, "ascending": True}
     return {"step_keys": 128, "ascending": False}
 

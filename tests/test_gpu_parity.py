@@ -328,9 +328,10 @@ def test_parity_with_oracle_head_dim_64(cuda_device, case):
     _, B, Sq, Sk, Hq, Hkv, causal = case
     q, k, v = make_qkv(B, Sq, Sk, Hq, Hkv, 64, seed=5, device=cuda_device)
     Q, K, V = fa.quantize_qkv(q, k, v)
-    out, lse = run(Q, K, V, causal, fa.VARIANT_WS)
-    assert out.dtype == torch.bfloat16 and out.shape == (B, Sq, Hq, 64)
-    assert_parity(out, lse, *oracles(Q, K, V, causal))
+    for variant in (fa.VARIANT_AUTO, fa.VARIANT_WS, fa.VARIANT_WS64):   # both kernels build head dim 64
+        out, lse = run(Q, K, V, causal, variant)
+        assert out.dtype == torch.bfloat16 and out.shape == (B, Sq, Hq, 64)
+        assert_parity(out, lse, *oracles(Q, K, V, causal, variant=variant))
     if Sk % 16 == 0:
         Qf, Kf, Vf = fa.quantize_qkv_fused(q, k, v)
         out_f, lse_f = fa.flash_attn_func(Qf, Kf, Vf, causal=causal, return_lse=True)
