@@ -638,6 +638,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
           if (!ok) break;
           if (j > 0) m_prev = s_hand[pw * 128 + row];
         }
+        FA4_PH(6);
         const float m_new = next_reference(m_prev, m_loc, p.sl2);
         s_hand[wg * 128 + row] = m_new;
         mbar_arrive(bars.at(Bars::kHand + 4 * wg + (warp & 3)));
@@ -710,7 +711,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
       }
       gb += n;
       ti += (n > 0) ? 1u : 0u;
-      FA4_PH(6);
+      FA4_PH(7);
     }
   }
   FA4_PH_DUMP();
