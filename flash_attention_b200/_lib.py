@@ -52,7 +52,7 @@ class Ext(ctypes.Structure):
         ("struct_size", ctypes.c_uint32), ("num_splits", ctypes.c_int32),
         ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_uint64),
         ("window_left", ctypes.c_int32), ("window_right", ctypes.c_int32),
-        ("sink", ctypes.c_void_p),
+        ("sink", ctypes.c_void_p), ("softcap", ctypes.c_float), ("reserved", ctypes.c_uint32),
     ]
 
 

@@ -99,11 +99,11 @@ int64_t splitkv_bytes(const fa4_nvfp4_params* p, int num_splits) {
   return (int64_t)num_splits * p->B * p->Sq * p->Hq * ((int64_t)p->Dv + 1) * 4;
 }
 int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint64_t workspace_bytes,
-               int win_left, int win_right, const float* sink, void* cuda_stream);
+               int win_left, int win_right, const float* sink, float softcap, void* cuda_stream);
 }  // namespace
 
 extern "C" int fa4_nvfp4_fwd(const fa4_nvfp4_params* p, void* cuda_stream) {
-  return launch_fwd(p, 1, nullptr, 0, -1, -1, nullptr, cuda_stream);
+  return launch_fwd(p, 1, nullptr, 0, -1, -1, nullptr, 0.f, cuda_stream);
 }
 
 extern "C" int fa4_nvfp4_fwd_ex(const fa4_nvfp4_params* p, const fa4_nvfp4_ext* x, void* cuda_stream) {
@@ -111,8 +111,9 @@ extern "C" int fa4_nvfp4_fwd_ex(const fa4_nvfp4_params* p, const fa4_nvfp4_ext* 
   if (x->struct_size != sizeof(fa4_nvfp4_ext)) return -FA4_E_STRUCT;
   const int splits = x->num_splits == 0 ? 1 : x->num_splits;
   if (splits < 1 || splits > 128 || x->window_left < -1 || x->window_right < -1) return -FA4_E_SHAPE;
+  if (!(x->softcap >= 0.f) || x->softcap > 3.0e38f || x->reserved != 0u) return -FA4_E_SHAPE;
   return launch_fwd(p, splits, x->workspace, x->workspace_bytes, x->window_left, x->window_right,
-                    x->sink, cuda_stream);
+                    x->sink, x->softcap, cuda_stream);
 }
 
 extern "C" int64_t fa4_nvfp4_splitkv_workspace_bytes(const fa4_nvfp4_params* p, int32_t num_splits) {
@@ -125,12 +126,12 @@ extern "C" int64_t fa4_nvfp4_splitkv_workspace_bytes(const fa4_nvfp4_params* p, 
 extern "C" int fa4_nvfp4_fwd_splitkv(const fa4_nvfp4_params* p, int32_t num_splits, void* workspace,
                                      uint64_t workspace_bytes, void* cuda_stream) {
   if (num_splits < 1 || num_splits > 128) return -FA4_E_SHAPE;
-  return launch_fwd(p, num_splits, workspace, workspace_bytes, -1, -1, nullptr, cuda_stream);
+  return launch_fwd(p, num_splits, workspace, workspace_bytes, -1, -1, nullptr, 0.f, cuda_stream);
 }
 
 namespace {
 int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint64_t workspace_bytes,
-               int win_left, int win_right, const float* sink, void* cuda_stream) {
+               int win_left, int win_right, const float* sink, float softcap, void* cuda_stream) {
   if (p == nullptr) return -FA4_E_NULL;
   if (p->struct_size != sizeof(fa4_nvfp4_params)) return -FA4_E_STRUCT;
   if (!p->q || !p->k || !p->v || !p->q_sf || !p->k_sf || !p->v_sf || !p->out) return -FA4_E_NULL;
@@ -152,7 +153,7 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
   if ((p->o_stride_b & 7) || (p->o_stride_s & 7) || (p->o_stride_h & 7)) return -FA4_E_STRIDE;
   // automatic choice: the 64-key kernel where it applies (no split / window / sink), the 128-key
   // kernel for everything else
-  const bool plain = num_splits == 1 && win_left < 0 && win_right <= 0 && sink == nullptr;
+  const bool plain = num_splits == 1 && win_left < 0 && win_right <= 0 && sink == nullptr && softcap == 0.f;
   int variant = p->variant;
   if (variant == FA4_VARIANT_AUTO) variant = plain ? FA4_VARIANT_WS64 : FA4_VARIANT_WS;
   if (variant != FA4_VARIANT_SERIAL && variant != FA4_VARIANT_WS && variant != FA4_VARIANT_WS64)
@@ -162,8 +163,8 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
   // window limits: `causal` is the right limit 0; an explicit right limit overrides it
   if (p->causal && win_right < 0) win_right = 0;
   const bool local = win_left >= 0 || win_right > 0;
-  const bool general = local || num_splits > 1 || sink != nullptr;
-  if ((local || sink != nullptr) && variant == FA4_VARIANT_SERIAL) return -FA4_E_VARIANT;
+  const bool general = local || num_splits > 1 || sink != nullptr || softcap > 0.f;
+  if ((local || sink != nullptr || softcap > 0.f) && variant == FA4_VARIANT_SERIAL) return -FA4_E_VARIANT;
   if (num_splits > 1) {
     if (variant == FA4_VARIANT_SERIAL) return -FA4_E_VARIANT;
     if (workspace == nullptr) return -FA4_E_NULL;
@@ -219,6 +220,12 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
   kp.vsf_stride_h = (int64_t)((p->Dv + 127) / 128) * (2 * kp.num_n_blocks) * 512;
   kp.vsf_stride_b = kp.vsf_stride_h * p->Hkv;
   kp.sl2 = p->softmax_scale * p->q_scale * p->k_scale * 1.4426950408889634f;
+  kp.softcap_c1 = 0.f;
+  if (softcap > 0.f) {
+    // the kernel caps the raw products and then works in units of softcap * log2(e)
+    kp.softcap_c1 = p->softmax_scale * p->q_scale * p->k_scale / softcap;
+    kp.sl2 = softcap * 1.4426950408889634f;
+  }
   kp.out_scale = p->v_scale;
   kp.budget_ns = p->wait_budget_ns ? p->wait_budget_ns : kDefaultBudgetNs;
   kp.num_splits = num_splits;

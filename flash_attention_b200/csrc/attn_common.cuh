@@ -43,6 +43,10 @@ struct KernelParams {
   // units of the scaled scores, that takes part in the normalisation and in the LSE but has no
   // value row (flash_attn/cute/flash_fwd_sm100.py:2383-2394, testing.py:406-416); null = none
   const float* sink;
+  // soft cap (general instantiation only): 0 = off; otherwise the raw products s become
+  // tanh(s * softcap_c1) with softcap_c1 = softmax_scale * q_scale * k_scale / softcap, and sl2 is
+  // softcap * log2(e) instead of the product of the scales
+  float softcap_c1;
 };
 
 // Work tile of a CTA.  Tiles are ordered so that, for causal problems, the m-blocks with the

@@ -653,6 +653,13 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         }
         tc_fence_before_sync();
         mbar_arrive(bars.at(Bars::kSFree + b));
+        if constexpr (kGeneral) {
+          // tanh is monotone: capping the eight block maxima is capping every score under them
+          if (p.softcap_c1 != 0.f) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) bm[q] = soft_cap(bm[q], p.softcap_c1);
+          }
+        }
         const float m01 = fmax3(bm[0], bm[1], bm[2]);
         const float m23 = fmax3(bm[3], bm[4], bm[5]);
         const float m_loc = fmax3(fmaxf(m01, m23), bm[6], bm[7]);
@@ -743,6 +750,12 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         tc_wait_ld();
         tc_fence_before_sync();
         mbar_arrive(bars.at(Bars::kSFree + b));
+        if constexpr (kGeneral) {
+          if (p.softcap_c1 != 0.f) {
+#pragma unroll
+            for (int x = 0; x < 64; ++x) s[x] = soft_cap(s[x], p.softcap_c1);
+          }
+        }
 
         // 3. exponentials and quantisation; P tile G % kStagesP is free once PV of block
         //    G - kStagesP has completed

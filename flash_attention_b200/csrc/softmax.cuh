@@ -69,6 +69,15 @@ __device__ __forceinline__ float row_block_max(const float (&s)[128], float (&bm
   return fmax3(fmaxf(m01, m23), bm[6], bm[7]);
 }
 
+// Soft cap of a raw score (reference: scores = softcap * tanh(scores / softcap),
+// flash_attn/cute/testing.py:373-374; its kernel uses the same hardware approximation): the factor
+// softcap is folded into sl2 by the host.  Masked scores stay -inf.
+__device__ __forceinline__ float soft_cap(float s, float c1) {
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(s * c1));
+  return (s == kNegInf) ? kNegInf : t;
+}
+
 // Next reference maximum given the previous one and this block's row maximum (raw units).
 __device__ __forceinline__ float next_reference(float m_prev, float m_loc, float sl2) {
   const bool keep = (m_prev != kNegInf) && ((m_loc - m_prev) * sl2 <= static_cast<float>(kLazy));

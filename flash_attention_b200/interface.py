@@ -96,6 +96,7 @@ def flash_attn_fp4_func(
     num_splits: int = 1,
     window_size: Tuple[Optional[int], Optional[int]] = (None, None),
     learnable_sink: Optional[torch.Tensor] = None,
+    softcap: float = 0.0,
 ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
     """NVFP4 attention forward.
 
@@ -114,6 +115,10 @@ def flash_attn_fp4_func(
 
     ``learnable_sink``: (Hq,) logits that join every row's softmax normalisation (and the LSE)
     without contributing a value, the reference's argument of the same name (testing.py:406-416).
+
+    ``softcap`` > 0: the scaled scores become ``softcap * tanh(scores / softcap)`` before masking
+    (the reference's ``softcap``, interface.py:528-530 / testing.py:373-374), with the hardware
+    ``tanh.approx`` as in the reference's kernel; one more transcendental per score.
 
     Built so far: D = Dv = 128 or 64; any Sq; Sk a multiple of 32 (partial last tiles are handled by
     zero-filled loads, a key-length mask and unstored rows).  Anything else raises
@@ -196,7 +201,11 @@ def flash_attn_fp4_func(
         if learnable_sink is not None:
             assert learnable_sink.shape == (Hq,), "learnable_sink must have one entry per query head"
             sink = learnable_sink.to(device=device, dtype=torch.float32).contiguous()
-        if num_splits == 1 and sink is None and win_left is None and (win_right is None or win_right == 0):
+        softcap = 0.0 if softcap is None else float(softcap)
+        if softcap < 0.0 or not math.isfinite(softcap):
+            raise ValueError("softcap must be a finite number >= 0")
+        if (num_splits == 1 and sink is None and win_left is None and (win_right is None or win_right == 0)
+                and softcap == 0.0):
             rc = _lib.lib().fa4_nvfp4_fwd(ctypes.byref(p), stream)
             what = "fa4_nvfp4_fwd"
         else:
@@ -206,6 +215,7 @@ def flash_attn_fp4_func(
             x.window_left = -1 if win_left is None else int(win_left)
             x.window_right = -1 if win_right is None else int(win_right)
             x.sink = sink.data_ptr() if sink is not None else None
+            x.softcap, x.reserved = softcap, 0
             workspace = None
             if num_splits > 1:
                 nbytes = _lib.lib().fa4_nvfp4_splitkv_workspace_bytes(ctypes.byref(p), num_splits)
@@ -285,8 +295,6 @@ def flash_attn_func(
     if not all(isinstance(t, NVFP4Tensor) for t in (q, k, v)):
         raise TypeError("flash_attn_func of this package takes NVFP4Tensor operands; "
                         "see quantize_qkv()")
-    if softcap not in (0.0, None):
-        raise NotImplementedError("softcap is not built")
     if mask_mod is not None or any(t is not None for t in (full_block_cnt, full_block_idx,
                                                            mask_block_cnt, mask_block_idx)):
         raise NotImplementedError("mask_mod / block sparsity is not built")
@@ -297,7 +305,7 @@ def flash_attn_func(
         q.data, k.data, v.data, q.sf, k.sf, v.sf, q.scale, k.scale, v.scale,
         softmax_scale=softmax_scale, causal=causal, return_lse=return_lse,
         sf_layout="tiled" if q.tiled else "linear", num_splits=num_splits, window_size=tuple(window_size),
-        learnable_sink=learnable_sink)
+        learnable_sink=learnable_sink, softcap=0.0 if softcap is None else softcap)
 
 
 def measure_fp4_mma_rate(iters: int = 1 << 16, device=None, repeats: int = 3) -> dict:

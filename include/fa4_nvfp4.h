@@ -151,6 +151,10 @@ typedef struct fa4_nvfp4_ext {
   const float* sink;        /* learnable sink: Hq fp32 logits on the device (natural-log units of the
                                scaled scores) that join every row's normalisation and LSE without a
                                value row (flash_attn/cute/flash_fwd_sm100.py:2383-2394); NULL = none */
+  float softcap;            /* > 0: scores = softcap * tanh(scores / softcap) on the scaled scores
+                               before masking (flash_attn/cute/interface.py:528-530,
+                               testing.py:373-374), with the hardware tanh approximation; 0 = off */
+  uint32_t reserved;        /* 0 */
 } fa4_nvfp4_ext;
 int fa4_nvfp4_fwd_ex(const fa4_nvfp4_params* p, const fa4_nvfp4_ext* x, void* cuda_stream);
 

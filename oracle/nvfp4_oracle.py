@@ -168,8 +168,10 @@ def _visibility_mask(sq: int, sk: int, causal: bool, window=(None, None)):
     return m
 
 
-def attention_oracle_a(q, k, v, causal=False, softmax_scale=None, window=(None, None), sink=None):
+def attention_oracle_a(q, k, v, causal=False, softmax_scale=None, window=(None, None), sink=None,
+                       softcap: float = 0.0):
     """q (B,Sq,Hq,D), k (B,Sk,Hkv,D), v (B,Sk,Hkv,Dv) fp32 torch CPU tensors.
+    softcap > 0: scores = softcap * tanh(scores / softcap) before masking (testing.py:373-374).
     Returns (out (B,Sq,Hq,Dv) fp32, lse (B,Hq,Sq) fp32)."""
     q, k, v = (torch.as_tensor(t, dtype=torch.float32) for t in (q, k, v))
     B, Sq, Hq, D = q.shape
@@ -179,6 +181,8 @@ def attention_oracle_a(q, k, v, causal=False, softmax_scale=None, window=(None, 
     k = k.repeat_interleave(g, dim=2)
     v = v.repeat_interleave(g, dim=2)
     scores = torch.einsum("bthd,bshd->bhts", q * scale, k)
+    if softcap and softcap > 0:
+        scores = torch.tanh(scores / softcap) * softcap
     mask = _visibility_mask(Sq, Sk, causal, window)
     if mask is not None:
         scores = scores.masked_fill(mask, float("-inf"))
@@ -219,7 +223,7 @@ def quantize_p_block_model(x: torch.Tensor, m_ref: torch.Tensor):
 
 def attention_oracle_b(qd, kd, vd, sl2: float, v_scale_out: float = 1.0, causal=False,
                        num_splits: int = 1, window=(None, None), sink=None,
-                       step_keys: int = 128, ascending: bool = False):
+                       step_keys: int = 128, ascending: bool = False, softcap_c1: float = 0.0):
     """Kernel model.  qd (B,Sq,Hq,D), kd (B,Sk,Hkv,D), vd (B,Sk,Hkv,Dv): fp32 values the tensor
     core sees (e2m1 * block scale, WITHOUT the per-tensor scales); sl2 = softmax_scale * q_scale
     * k_scale * log2(e); v_scale_out = v_scale.  Walks the K/V blocks of 128 keys from the last
@@ -233,6 +237,9 @@ def attention_oracle_b(qd, kd, vd, sl2: float, v_scale_out: float = 1.0, causal=
     (csrc/attn_ws64.cuh) takes steps of 64 keys upwards from key 0.  The set of visited keys is
     the same (whole 128-key blocks); the step decides where the lazy reference maximum may move,
     hence the scaling under which P is rounded to e2m1.
+    softcap_c1 > 0 models the soft cap: the raw scores become tanh(raw * softcap_c1) with
+    softcap_c1 = softmax_scale * q_scale * k_scale / softcap, and the caller passes
+    sl2 = softcap * log2(e): everything after that is unchanged.
     Returns (out fp32 (B,Sq,Hq,Dv) before bf16 rounding, lse (B,Hq,Sq))."""
     assert step_keys in (64, 128) and (step_keys == 128 or num_splits == 1)
     sub = 128 // step_keys
@@ -251,6 +258,8 @@ def attention_oracle_b(qd, kd, vd, sl2: float, v_scale_out: float = 1.0, causal=
                 n_blocks = (Sk + 127) // 128
                 s_all = torch.full((nr, n_blocks * 128), float("-inf"))   # keys >= Sk never count
                 s_all[:, :Sk] = (qd[b, rows, h] @ kd[b, :, hk].T)         # raw scores
+                if softcap_c1 > 0:
+                    s_all[:, :Sk] = torch.tanh(s_all[:, :Sk] * softcap_c1)
                 v_pad = torch.zeros(n_blocks * 128, Dv)
                 v_pad[:Sk] = vd[b, :, hk]
                 left, right = window

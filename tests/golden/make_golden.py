@@ -38,7 +38,10 @@ CASES = [
     ("mha_window_both_sides_sq_lt_sk", 1, 96, 352, 2, 2, 128, False, 5, (40, 70)),
     # learnable sink (testing.py:406-416): seeded N(0, 1) logits, one per query head
     ("gqa_causal_learnable_sink", 1, 192, 192, 4, 2, 128, True, 6, (None, None)),
+    # soft cap (testing.py:373-374): scores = softcap * tanh(scores / softcap), value in SOFTCAP
+    ("gqa_causal_softcap", 1, 256, 256, 4, 2, 128, True, 7, (None, None)),
 ]
+SOFTCAP = {"gqa_causal_softcap": 2.0}
 
 
 def load_reference_testing(ref_root):
@@ -51,11 +54,15 @@ def load_reference_testing(ref_root):
 
 def main():
     if len(sys.argv) < 2:
-        raise SystemExit("usage: python tests/golden/make_golden.py /path/to/reference")
+        raise SystemExit("usage: python tests/golden/make_golden.py /path/to/reference [fixture name ...]")
     ref_root = sys.argv[1]
+    only = set(sys.argv[2:])        # regenerate these only (an .npz is a zip: rewriting changes its bytes)
     ref = load_reference_testing(ref_root)
     torch.set_num_threads(4)
     for name, B, Sq, Sk, Hq, Hkv, D, causal, seed, window in CASES:
+        if only and name not in only:
+            continue
+        softcap = SOFTCAP.get(name, 0.0)
         g = torch.Generator().manual_seed(seed)
         q = torch.randn(B, Sq, Hq, D, generator=g).bfloat16().float().numpy()
         k = torch.randn(B, Sk, Hkv, D, generator=g).bfloat16().float().numpy()
@@ -67,9 +74,11 @@ def main():
         vd = torch.from_numpy(np.ascontiguousarray(np.transpose(orc.dequantize_nvfp4(V), (0, 3, 1, 2))))
         sink = torch.randn(Hq, generator=g) * 2.0 if "sink" in name else None
         out_ref, _ = ref.attention_ref(qd, kd, vd, causal=causal, window_size=window, upcast=True,
-                                       learnable_sink=sink)
+                                       learnable_sink=sink, softcap=softcap)
         kk = kd.repeat_interleave(Hq // Hkv, dim=2)
         qk = torch.einsum("bshd,bthd->bhst", qd, kk) / (D ** 0.5)
+        if softcap > 0:
+            qk = torch.tanh(qk / softcap) * softcap
         if window != (None, None):
             w = (window[0], 0) if causal else window
             mask = ref.construct_local_mask(Sq, Sk, w)
@@ -88,7 +97,8 @@ def main():
             out_ref=out_ref.numpy().astype(np.float32), lse_ref=lse_ref.numpy().astype(np.float32),
             causal=np.bool_(causal), seed=np.int64(seed),
             window=np.array([-1 if x is None else x for x in window], dtype=np.int64),
-            sink=(sink.numpy().astype(np.float32) if sink is not None else np.zeros(0, dtype=np.float32)))
+            sink=(sink.numpy().astype(np.float32) if sink is not None else np.zeros(0, dtype=np.float32)),
+            softcap=np.float32(softcap))
         print(name, out_ref.shape, float(out_ref.abs().max()))
 
 

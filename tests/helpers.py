@@ -38,28 +38,36 @@ def make_qkv(B, Sq, Sk, Hq, Hkv, D, seed, v_std=1.0, outlier_frac=0.0, device="c
     return tuple(t.bfloat16().to(device) for t in (q, k, v))
 
 
-def kernel_model(D, num_splits=1, window=(None, None), sink=None, variant=0):
+def kernel_model(D, num_splits=1, window=(None, None), sink=None, variant=0, softcap=0.0):
     """Which kernel the library's automatic choice runs, as oracle B keywords: the 64-key kernel
     without split / window / sink, the 128-key kernel otherwise (mirrors
     launch_fwd in csrc/api.cu).  ``variant`` 1 / 2 force the 128-key model, 3 the 64-key one."""
-    plain = num_splits == 1 and window == (None, None) and sink is None
+    plain = num_splits == 1 and window == (None, None) and sink is None and not softcap
     if variant == 3 or (variant == 0 and plain):
         return {"step_keys": 64, "ascending": True}
     return {"step_keys": 128, "ascending": False}
 
 
-def oracles(Q, K, V, causal, softmax_scale=None, num_splits=1, window=(None, None), sink=None, variant=0):
+def oracles(Q, K, V, causal, softmax_scale=None, num_splits=1, window=(None, None), sink=None, variant=0,
+            softcap=0.0):
     """Q, K, V: NVFP4Tensor with linear scales.  Returns (out_a, lse_a, out_b, lse_b) on CPU;
     oracle B models the kernel that ``variant`` (0 = automatic) selects for this problem."""
     qd, kd, vd = Q.dequantize().cpu(), K.dequantize().cpu(), V.dequantize().cpu()
     D = qd.shape[-1]
     scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(D)
-    oa, la = orc.attention_oracle_a(qd, kd, vd, causal=causal, softmax_scale=scale, window=window, sink=sink)
+    oa, la = orc.attention_oracle_a(qd, kd, vd, causal=causal, softmax_scale=scale, window=window, sink=sink,
+                                    softcap=softcap)
     sl2 = float(torch.tensor(scale, dtype=torch.float32) * torch.tensor(Q.scale, dtype=torch.float32)
                 * torch.tensor(K.scale, dtype=torch.float32) * torch.tensor(LOG2E, dtype=torch.float32))
+    c1 = 0.0
+    if softcap:
+        # the kernel caps the raw products: tanh(raw * c1), then works in units of softcap * log2(e)
+        c1 = float(torch.tensor(scale, dtype=torch.float32) * torch.tensor(Q.scale, dtype=torch.float32)
+                   * torch.tensor(K.scale, dtype=torch.float32) / torch.tensor(softcap, dtype=torch.float32))
+        sl2 = float(torch.tensor(softcap, dtype=torch.float32) * torch.tensor(LOG2E, dtype=torch.float32))
     ob, lb = orc.attention_oracle_b(qd / Q.scale, kd / K.scale, vd / V.scale, sl2, V.scale, causal=causal,
                                     num_splits=num_splits, window=window, sink=sink,
-                                    **kernel_model(D, num_splits, window, sink, variant))
+                                    softcap_c1=c1, **kernel_model(D, num_splits, window, sink, variant, softcap))
     return oa, la, ob, lb
 
 

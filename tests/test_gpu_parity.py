@@ -125,7 +125,8 @@ def test_parity_with_oracle(cuda_device, case, variant):
 # (the ragged fixture has Sk = 208, not a multiple of the kernel's 32-key granule: oracle only)
 @pytest.mark.parametrize("name", ["mha_noncausal", "gqa_causal_sq_lt_sk", "mqa_causal_sq_gt_sk",
                                   "gqa_sliding_window_causal",
-                                  "mha_window_both_sides_sq_lt_sk", "gqa_causal_learnable_sink"])
+                                  "mha_window_both_sides_sq_lt_sk", "gqa_causal_learnable_sink",
+                                  "gqa_causal_softcap"])
 def test_golden_fixture_through_the_kernel(cuda_device, name):
     """The fixtures generated by the reference's attention_ref, through the kernel."""
     import os
@@ -137,7 +138,8 @@ def test_golden_fixture_through_the_kernel(cuda_device, name):
                                       t(z["k_sf"]), t(z["v_sf"]), float(z["q_scale"]), float(z["k_scale"]),
                                       float(z["v_scale"]), causal=bool(z["causal"]), return_lse=True,
                                       window_size=window,
-                                      learnable_sink=torch.from_numpy(z["sink"]) if z["sink"].size else None)
+                                      learnable_sink=torch.from_numpy(z["sink"]) if z["sink"].size else None,
+                                      softcap=float(z["softcap"]) if "softcap" in z.files else 0.0)
     torch.cuda.synchronize()
     fa.check_status(dev)
     ref_out, ref_lse = torch.from_numpy(z["out_ref"]), torch.from_numpy(z["lse_ref"])
@@ -422,6 +424,40 @@ def test_learnable_sink_parity(cuda_device, splits):
     assert_parity(out, lse, *oracles(Q, K, V, True, num_splits=splits, sink=sink.numpy()))
     assert torch.equal(lse[0, :, :128].cpu(), sink[:, None].expand(4, 128))
     assert out[0, :128].abs().max().item() == 0.0
+
+
+@pytest.mark.parametrize("case", [
+    # name, B, Sq, Sk, Hq, Hkv, D, causal, softcap, splits, window
+    ("softcap_causal_gqa", 1, 384, 384, 4, 2, 128, True, 3.0, 1, (None, None)),
+    ("softcap_noncausal_ragged_strong_cap", 2, 113, 224, 3, 1, 128, False, 0.75, 1, (None, None)),
+    ("softcap_masked_rows_d64", 1, 300, 160, 2, 2, 64, True, 2.0, 1, (None, None)),
+    ("softcap_with_splits_and_window", 1, 96, 1024, 4, 2, 128, True, 5.0, 3, (300, None)),
+], ids=lambda c: c[0])
+def test_softcap_parity(cuda_device, case):
+    """scores = softcap * tanh(scores / softcap) (the reference's softcap, testing.py:373-374).  The
+    kernel uses the hardware tanh approximation (relative error about 2^-11, as the reference's
+    kernel does), which moves a score by up to softcap * log2(e) * 2^-11 in the exponent: more P
+    values than usual land on the other side of an e2m1 rounding boundary than in the model, so
+    the bound against model B is looser here (rel-RMS 0.05); the bounds against exact attention
+    and on the LSE are the usual ones."""
+    _, B, Sq, Sk, Hq, Hkv, D, causal, cap, splits, window = case
+    q, k, v = make_qkv(B, Sq, Sk, Hq, Hkv, D, seed=31, device=cuda_device)
+    Q, K, V = fa.quantize_qkv(q * 2.0, k * 2.0, v)       # scores of std 4: the cap bites
+    out, lse = run(Q, K, V, causal, softcap=cap, num_splits=splits, window_size=window)
+    oa, la, ob, lb = oracles(Q, K, V, causal, softcap=cap, num_splits=splits, window=window)
+    o = out.float().cpu()
+    assert torch.isfinite(o).all()
+    eb, ea, eba = orc.error_metrics(o, ob), orc.error_metrics(o, oa), orc.error_metrics(ob, oa)
+    assert eb["rel_rms"] <= 0.05, eb
+    assert ea["rel_rms"] <= 1.25 * eba["rel_rms"] + 0.01, (ea, eba)
+    assert torch.equal(torch.isinf(lse.cpu()), torch.isinf(la))
+    fin = torch.isfinite(la)
+    assert (lse.cpu()[fin] - la[fin]).abs().max().item() <= 2e-3 * max(1.0, la[fin].abs().max().item())
+    # the cap changes the result (the test would not notice a kernel that ignored it otherwise)
+    out0, _ = run(Q, K, V, causal, num_splits=splits, window_size=window)
+    assert orc.error_metrics(out0.float().cpu(), oa)["rel_rms"] > 0.3
+    with pytest.raises((ValueError, NotImplementedError)):
+        run(Q, K, V, causal, fa.VARIANT_WS64, softcap=cap)
 
 
 def test_varlen_packed_batch_matches_dense_calls(cuda_device):

@@ -77,7 +77,9 @@ def test_oracle_a_matches_reference_golden(path):
     vd = torch.from_numpy(np.ascontiguousarray(np.transpose(orc.dequantize_nvfp4(V), (0, 3, 1, 2))))
     window = tuple(None if int(x) < 0 else int(x) for x in z["window"]) if "window" in z else (None, None)
     sink = z["sink"] if "sink" in z and z["sink"].size else None
-    out, lse = orc.attention_oracle_a(qd, kd, vd, causal=bool(z["causal"]), window=window, sink=sink)
+    softcap = float(z["softcap"]) if "softcap" in z.files else 0.0
+    out, lse = orc.attention_oracle_a(qd, kd, vd, causal=bool(z["causal"]), window=window, sink=sink,
+                                      softcap=softcap)
     ref_out, ref_lse = torch.from_numpy(z["out_ref"]), torch.from_numpy(z["lse_ref"])
     assert out.shape == ref_out.shape and lse.shape == ref_lse.shape
     assert torch.allclose(out, ref_out, rtol=1e-5, atol=1e-6)
@@ -87,7 +89,7 @@ def test_oracle_a_matches_reference_golden(path):
 
 
 def test_golden_fixtures_present():
-    assert len(glob.glob(os.path.join(GOLDEN, "*.npz"))) >= 7
+    assert len(glob.glob(os.path.join(GOLDEN, "*.npz"))) >= 8
 
 
 def test_oracle_b_close_to_a():
