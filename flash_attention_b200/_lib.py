@@ -53,6 +53,9 @@ class Ext(ctypes.Structure):
         ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_uint64),
         ("window_left", ctypes.c_int32), ("window_right", ctypes.c_int32),
         ("sink", ctypes.c_void_p), ("softcap", ctypes.c_float), ("reserved", ctypes.c_uint32),
+        ("seqused_k", ctypes.c_void_p), ("page_table", ctypes.c_void_p),
+        ("page_size", ctypes.c_int32), ("pages_per_seq", ctypes.c_int32),
+        ("num_pages", ctypes.c_int32), ("reserved2", ctypes.c_int32),
     ]
 
 

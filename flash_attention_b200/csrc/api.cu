@@ -98,12 +98,19 @@ int64_t splitkv_bytes(const fa4_nvfp4_params* p, int num_splits) {
   // partial O (num_splits, B, Sq, Hq, Dv) fp32, then partial LSE (num_splits, B, Hq, Sq) fp32
   return (int64_t)num_splits * p->B * p->Sq * p->Hq * ((int64_t)p->Dv + 1) * 4;
 }
+// KV-cache view of K / V: per-entry key counts and / or a page pool (see fa4_nvfp4_ext).
+struct CacheView {
+  const int32_t* seqused_k = nullptr;
+  const int32_t* page_table = nullptr;
+  int page_size = 0, pages_per_seq = 0, num_pages = 0;
+};
 int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint64_t workspace_bytes,
-               int win_left, int win_right, const float* sink, float softcap, void* cuda_stream);
+               int win_left, int win_right, const float* sink, float softcap, const CacheView& cache,
+               void* cuda_stream);
 }  // namespace
 
 extern "C" int fa4_nvfp4_fwd(const fa4_nvfp4_params* p, void* cuda_stream) {
-  return launch_fwd(p, 1, nullptr, 0, -1, -1, nullptr, 0.f, cuda_stream);
+  return launch_fwd(p, 1, nullptr, 0, -1, -1, nullptr, 0.f, CacheView{}, cuda_stream);
 }
 
 extern "C" int fa4_nvfp4_fwd_ex(const fa4_nvfp4_params* p, const fa4_nvfp4_ext* x, void* cuda_stream) {
@@ -112,8 +119,20 @@ extern "C" int fa4_nvfp4_fwd_ex(const fa4_nvfp4_params* p, const fa4_nvfp4_ext* 
   const int splits = x->num_splits == 0 ? 1 : x->num_splits;
   if (splits < 1 || splits > 128 || x->window_left < -1 || x->window_right < -1) return -FA4_E_SHAPE;
   if (!(x->softcap >= 0.f) || x->softcap > 3.0e38f || x->reserved != 0u) return -FA4_E_SHAPE;
+  CacheView cache;
+  cache.seqused_k = x->seqused_k;
+  if (x->page_table != nullptr) {
+    // pages hold whole 128-key blocks; the table must cover the logical key length
+    if (x->page_size <= 0 || x->page_size % 128 != 0 || x->num_pages <= 0 || x->pages_per_seq <= 0)
+      return -FA4_E_SHAPE;
+    if (p != nullptr && (int64_t)x->pages_per_seq * x->page_size < p->Sk) return -FA4_E_SHAPE;
+    cache.page_table = x->page_table;
+    cache.page_size = x->page_size;
+    cache.pages_per_seq = x->pages_per_seq;
+    cache.num_pages = x->num_pages;
+  }
   return launch_fwd(p, splits, x->workspace, x->workspace_bytes, x->window_left, x->window_right,
-                    x->sink, x->softcap, cuda_stream);
+                    x->sink, x->softcap, cache, cuda_stream);
 }
 
 extern "C" int64_t fa4_nvfp4_splitkv_workspace_bytes(const fa4_nvfp4_params* p, int32_t num_splits) {
@@ -126,12 +145,13 @@ extern "C" int64_t fa4_nvfp4_splitkv_workspace_bytes(const fa4_nvfp4_params* p, 
 extern "C" int fa4_nvfp4_fwd_splitkv(const fa4_nvfp4_params* p, int32_t num_splits, void* workspace,
                                      uint64_t workspace_bytes, void* cuda_stream) {
   if (num_splits < 1 || num_splits > 128) return -FA4_E_SHAPE;
-  return launch_fwd(p, num_splits, workspace, workspace_bytes, -1, -1, nullptr, 0.f, cuda_stream);
+  return launch_fwd(p, num_splits, workspace, workspace_bytes, -1, -1, nullptr, 0.f, CacheView{}, cuda_stream);
 }
 
 namespace {
 int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint64_t workspace_bytes,
-               int win_left, int win_right, const float* sink, float softcap, void* cuda_stream) {
+               int win_left, int win_right, const float* sink, float softcap, const CacheView& cache,
+               void* cuda_stream) {
   if (p == nullptr) return -FA4_E_NULL;
   if (p->struct_size != sizeof(fa4_nvfp4_params)) return -FA4_E_STRUCT;
   if (!p->q || !p->k || !p->v || !p->q_sf || !p->k_sf || !p->v_sf || !p->out) return -FA4_E_NULL;
@@ -153,7 +173,8 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
   if ((p->o_stride_b & 7) || (p->o_stride_s & 7) || (p->o_stride_h & 7)) return -FA4_E_STRIDE;
   // automatic choice: the 64-key kernel where it applies (no split / window / sink), the 128-key
   // kernel for everything else
-  const bool plain = num_splits == 1 && win_left < 0 && win_right <= 0 && sink == nullptr && softcap == 0.f;
+  const bool cached = cache.seqused_k != nullptr || cache.page_table != nullptr;
+  const bool plain = num_splits == 1 && win_left < 0 && win_right <= 0 && sink == nullptr && softcap == 0.f && !cached;
   int variant = p->variant;
   if (variant == FA4_VARIANT_AUTO) variant = plain ? FA4_VARIANT_WS64 : FA4_VARIANT_WS;
   if (variant != FA4_VARIANT_SERIAL && variant != FA4_VARIANT_WS && variant != FA4_VARIANT_WS64)
@@ -163,8 +184,8 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
   // window limits: `causal` is the right limit 0; an explicit right limit overrides it
   if (p->causal && win_right < 0) win_right = 0;
   const bool local = win_left >= 0 || win_right > 0;
-  const bool general = local || num_splits > 1 || sink != nullptr || softcap > 0.f;
-  if ((local || sink != nullptr || softcap > 0.f) && variant == FA4_VARIANT_SERIAL) return -FA4_E_VARIANT;
+  const bool general = local || num_splits > 1 || sink != nullptr || softcap > 0.f || cached;
+  if ((local || sink != nullptr || softcap > 0.f || cached) && variant == FA4_VARIANT_SERIAL) return -FA4_E_VARIANT;
   if (num_splits > 1) {
     if (variant == FA4_VARIANT_SERIAL) return -FA4_E_VARIANT;
     if (workspace == nullptr) return -FA4_E_NULL;
@@ -179,10 +200,13 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
     const uint64_t dq[4] = {(uint64_t)p->D / 2, (uint64_t)p->Hq, (uint64_t)p->Sq, (uint64_t)p->B};
     const uint64_t sq[3] = {(uint64_t)p->q_stride_h, (uint64_t)p->q_stride_s, (uint64_t)p->q_stride_b};
     const uint32_t bq[4] = {(uint32_t)p->D / 2, 1, (uint32_t)kBlockM, 1};
-    const uint64_t dk[4] = {(uint64_t)p->D / 2, (uint64_t)p->Hkv, (uint64_t)p->Sk, (uint64_t)p->B};
+    // with a page table K / V describe the pool: "batch" = page, "Sk" = keys per page
+    const uint64_t k_rows = cache.page_table ? (uint64_t)cache.page_size : (uint64_t)p->Sk;
+    const uint64_t k_batch = cache.page_table ? (uint64_t)cache.num_pages : (uint64_t)p->B;
+    const uint64_t dk[4] = {(uint64_t)p->D / 2, (uint64_t)p->Hkv, k_rows, k_batch};
     const uint64_t sk[3] = {(uint64_t)p->k_stride_h, (uint64_t)p->k_stride_s, (uint64_t)p->k_stride_b};
     const uint32_t bk[4] = {(uint32_t)p->D / 2, 1, (uint32_t)kBlockN, 1};
-    const uint64_t dv[4] = {(uint64_t)p->Sk / 2, (uint64_t)p->Dv, (uint64_t)p->Hkv, (uint64_t)p->B};
+    const uint64_t dv[4] = {k_rows / 2, (uint64_t)p->Dv, (uint64_t)p->Hkv, k_batch};
     const uint64_t sv[3] = {(uint64_t)p->v_stride_d, (uint64_t)p->v_stride_h, (uint64_t)p->v_stride_b};
     const uint32_t bv[4] = {64, (uint32_t)p->Dv, 1, 1};
     // a Q / K tile row is D / 2 bytes: 64-byte swizzle for D = 128, 32-byte for D = 64
@@ -214,11 +238,18 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
   // tiled scale factors: (B, H, row tiles, col tiles, 512)
   kp.qsf_stride_h = (int64_t)kp.num_m_blocks * (p->D / 64) * 512;
   kp.qsf_stride_b = kp.qsf_stride_h * p->Hq;
-  kp.ksf_stride_h = (int64_t)kp.num_n_blocks * (p->D / 64) * 512;
+  // (per page when K / V are a page pool: the tiled scales of a page are laid out like those of
+  // a batch entry of page_size keys)
+  const int64_t kv_blocks = cache.page_table ? cache.page_size / kBlockN : kp.num_n_blocks;
+  kp.ksf_stride_h = kv_blocks * (p->D / 64) * 512;
   kp.ksf_stride_b = kp.ksf_stride_h * p->Hkv;
   // V scales: two 64-key column tiles per 128-key block, the last block padded with zeros
-  kp.vsf_stride_h = (int64_t)((p->Dv + 127) / 128) * (2 * kp.num_n_blocks) * 512;
+  kp.vsf_stride_h = (int64_t)((p->Dv + 127) / 128) * (2 * kv_blocks) * 512;
   kp.vsf_stride_b = kp.vsf_stride_h * p->Hkv;
+  kp.seqused_k = cache.seqused_k;
+  kp.page_table = cache.page_table;
+  kp.page_size = cache.page_size;
+  kp.pages_per_seq = cache.pages_per_seq;
   kp.sl2 = p->softmax_scale * p->q_scale * p->k_scale * 1.4426950408889634f;
   kp.softcap_c1 = 0.f;
   if (softcap > 0.f) {

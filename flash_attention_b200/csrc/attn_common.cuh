@@ -47,6 +47,15 @@ struct KernelParams {
   // tanh(s * softcap_c1) with softcap_c1 = softmax_scale * q_scale * k_scale / softcap, and sl2 is
   // softcap * log2(e) instead of the product of the scales
   float softcap_c1;
+  // KV cache (general instantiation only).  seqused_k: per batch entry the number of valid keys
+  // (<= Sk; causal alignment and masks then use it in place of Sk); NULL = Sk for all.
+  // page_table: K / V / their scales live in a pool of pages of page_size keys (a multiple of
+  // 128) and logical key block nb of batch entry b sits in page page_table[b * pages_per_seq +
+  // nb * 128 / page_size]; the K / V tensor maps and scale strides then describe the POOL
+  // (their batch dimension is the page).  NULL = contiguous operands.
+  const int32_t* seqused_k;
+  const int32_t* page_table;
+  int page_size, pages_per_seq;
 };
 
 // Work tile of a CTA.  Tiles are ordered so that, for causal problems, the m-blocks with the
@@ -58,7 +67,15 @@ struct Tile {
   int n_blocks;  // number of K/V blocks this work item visits (0: nothing visible / empty split)
   int nb_top;    // K/V block index of the first visited block; the i-th visited is nb_top - i
   int split;
+  int sk;        // valid keys of this batch entry (general instantiation; p.Sk otherwise)
 };
+
+// Key length that masks and block ranges see.
+template <bool kGeneral>
+__device__ __forceinline__ int key_len(const KernelParams& p, const Tile& t) {
+  if constexpr (kGeneral) return t.sk;
+  return p.Sk;
+}
 
 // kGeneral = false: the work list is the tile list (num_splits == 1) and the only masks are
 // causal / key length; kept as a compile-time switch so that the common case carries none of the
@@ -78,11 +95,20 @@ __device__ __forceinline__ Tile decode_tile(const KernelParams& p, int tile_idx)
   t.h = rem - t.b * p.Hq;
   t.hk = t.h / p.group;
   t.m_blk = p.causal ? (p.num_m_blocks - 1 - m_rev) : m_rev;
+  t.sk = p.Sk;
   int n = p.num_n_blocks;
+  if constexpr (kGeneral) {
+    if (p.seqused_k != nullptr) {
+      const int used = p.seqused_k[t.b];
+      t.sk = used < 0 ? 0 : (used < p.Sk ? used : p.Sk);
+      n = (t.sk + kBlockN - 1) / kBlockN;
+    }
+  }
+  const int sk = key_len<kGeneral>(p, t);
   if (p.causal) {
     // last visible key of the tile's last row: (m_blk + 1) * 128 - 1 + Sk - Sq
     // (block range of flash_attn/cute/block_info.py:23-55, bottom-right aligned)
-    const int last = (t.m_blk + 1) * kBlockM + p.Sk - p.Sq + (kGeneral ? p.win_right : 0);  // exclusive
+    const int last = (t.m_blk + 1) * kBlockM + sk - p.Sq + (kGeneral ? p.win_right : 0);  // exclusive
     int nb = (last + kBlockN - 1) / kBlockN;
     if (last <= 0) nb = 0;
     n = nb < n ? nb : n;
@@ -91,7 +117,7 @@ __device__ __forceinline__ Tile decode_tile(const KernelParams& p, int tile_idx)
     // first block that holds a visible key of the tile's first row (left window limit)
     int n_min = 0;
     if (p.win_left >= 0) {
-      const int first = t.m_blk * kBlockM + p.Sk - p.Sq - p.win_left;
+      const int first = t.m_blk * kBlockM + sk - p.Sq - p.win_left;
       n_min = first > 0 ? first / kBlockN : 0;
       if (n_min > n) n_min = n;
     }
@@ -117,21 +143,23 @@ __device__ __forceinline__ Tile decode_tile(const KernelParams& p, int tile_idx)
 template <bool kGeneral = false>
 __device__ __forceinline__ int causal_limit(const KernelParams& p, const Tile& t, int row_in_tile,
                                             int nb) {
-  const int len_limit = p.Sk - 1 - nb * kBlockN;
+  const int sk = key_len<kGeneral>(p, t);
+  const int len_limit = sk - 1 - nb * kBlockN;
   if (!p.causal) return len_limit;
-  const int c = t.m_blk * kBlockM + row_in_tile + p.Sk - p.Sq + (kGeneral ? p.win_right : 0) - nb * kBlockN;
+  const int c = t.m_blk * kBlockM + row_in_tile + sk - p.Sq + (kGeneral ? p.win_right : 0) - nb * kBlockN;
   return c < len_limit ? c : len_limit;
 }
 // In-block index of the FIRST visible key (left window limit); <= 0 when nothing is cut.
 __device__ __forceinline__ int lower_limit(const KernelParams& p, const Tile& t, int row_in_tile,
                                            int nb) {
   if (p.win_left < 0) return -(1 << 30);
-  return t.m_blk * kBlockM + row_in_tile + p.Sk - p.Sq - p.win_left - nb * kBlockN;
+  return t.m_blk * kBlockM + row_in_tile + t.sk - p.Sq - p.win_left - nb * kBlockN;
 }
 template <bool kGeneral = false>
 __device__ __forceinline__ bool block_needs_mask(const KernelParams& p, const Tile& t, int nb) {
-  const bool partial = (nb + 1) * kBlockN > p.Sk;
-  const int off = t.m_blk * kBlockM + p.Sk - p.Sq;
+  const int sk = key_len<kGeneral>(p, t);
+  const bool partial = (nb + 1) * kBlockN > sk;
+  const int off = t.m_blk * kBlockM + sk - p.Sq;
   bool need = partial || (p.causal && (nb * kBlockN + kBlockN - 1 > off + (kGeneral ? p.win_right : 0)));
   if constexpr (kGeneral) {
     // the last row of the tile has the highest left limit

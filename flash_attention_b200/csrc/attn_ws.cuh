@@ -411,8 +411,19 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
                   p.q_sf + t.b * p.qsf_stride_b + t.h * p.qsf_stride_h + (int64_t)t.m_blk * kQkSfBytes,
                   kQkSfBytes, bars.at(Bars::kQFull + qb));
         issued_q = ti + 1;
-        const uint8_t* ksf = p.k_sf + t.b * p.ksf_stride_b + t.hk * p.ksf_stride_h;
-        const uint8_t* vsf = p.v_sf + t.b * p.vsf_stride_b + t.hk * p.vsf_stride_h;
+        // where logical K/V block nb of this batch entry lives: (batch coordinate, block inside
+        // it) -- the entry itself, or a page of the pool and the block inside the page
+        auto locate = [&](int nb, int& kb, int& nbl) {
+          kb = t.b;
+          nbl = nb;
+          if constexpr (kGeneral) {
+            if (p.page_table != nullptr) {
+              const int key0 = nb * kBlockN, pg = key0 / p.page_size;
+              kb = p.page_table[(int64_t)t.b * p.pages_per_seq + pg];
+              nbl = (key0 - pg * p.page_size) / kBlockN;
+            }
+          }
+        };
         // K runs two blocks ahead of V: QK^T of block i+2 is issued before PV of block i.
         for (int step = 0; ok && step < n + 2; ++step) {
           const int ik = step, iv = step - 2;
@@ -426,10 +437,13 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
               if (!ok) break;
             }
             mbar_arrive_expect_tx(bars.at(Bars::kKFull + st), kQkBytes + kQkSfBytes);
+            int kb, nbl;
+            locate(nb, kb, nbl);
             tma_load_4d(base + kOffK + st * kTileBytes, &tm_k, bars.at(Bars::kKFull + st), 0, t.hk,
-                        nb * kBlockN, t.b);
-            bulk_load(base + kOffSFK + st * kSfBytes, ksf + (int64_t)nb * kQkSfBytes, kQkSfBytes,
-                      bars.at(Bars::kKFull + st));
+                        nbl * kBlockN, kb);
+            bulk_load(base + kOffSFK + st * kSfBytes,
+                      p.k_sf + kb * p.ksf_stride_b + t.hk * p.ksf_stride_h + (int64_t)nbl * kQkSfBytes,
+                      kQkSfBytes, bars.at(Bars::kKFull + st));
             issued_k = G + 1;
           }
           if (iv >= 0 && iv < n) {
@@ -441,10 +455,13 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
               if (!ok) break;
             }
             mbar_arrive_expect_tx(bars.at(Bars::kVFull + st), kVBytes + kSfBytes);
+            int kb, nbl;
+            locate(nb, kb, nbl);
             tma_load_4d(base + kOffV + st * kTileBytes, &tm_v, bars.at(Bars::kVFull + st),
-                        nb * (kBlockN / 2), 0, t.hk, t.b);
-            bulk_load(base + kOffSFV + st * kSfBytes, vsf + (int64_t)nb * kSfBytes, kSfBytes,
-                      bars.at(Bars::kVFull + st));
+                        nbl * (kBlockN / 2), 0, t.hk, kb);
+            bulk_load(base + kOffSFV + st * kSfBytes,
+                      p.v_sf + kb * p.vsf_stride_b + t.hk * p.vsf_stride_h + (int64_t)nbl * kSfBytes,
+                      kSfBytes, bars.at(Bars::kVFull + st));
             issued_v = G + 1;
           }
         }

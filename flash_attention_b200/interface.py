@@ -97,6 +97,8 @@ def flash_attn_fp4_func(
     window_size: Tuple[Optional[int], Optional[int]] = (None, None),
     learnable_sink: Optional[torch.Tensor] = None,
     softcap: float = 0.0,
+    seqused_k: Optional[torch.Tensor] = None,
+    page_table: Optional[torch.Tensor] = None,
 ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
     """NVFP4 attention forward.
 
@@ -120,6 +122,14 @@ def flash_attn_fp4_func(
     (the reference's ``softcap``, interface.py:528-530 / testing.py:373-374), with the hardware
     ``tanh.approx`` as in the reference's kernel; one more transcendental per score.
 
+    KV cache, the reference's ``seqused_k`` / ``page_table`` (interface.py:296-300, paged_kv.py):
+    ``seqused_k`` (B,) int32: batch entry b attends to its first ``seqused_k[b]`` keys only (any
+    value in 0..Sk; causal and window limits align to it).  ``page_table`` (B, pages_per_seq)
+    int32: k, v and their scales are then a POOL of pages, k (num_pages, page_size, Hkv, D/2),
+    v (num_pages, Hkv, Dv, page_size/2), scales per page in either layout, page_size a multiple
+    of 128; the logical key length is ``pages_per_seq * page_size``.  Scale bytes of unused
+    cache slots must not be NaN encodings (a zero-filled cache is fine).
+
     Built so far: D = Dv = 128 or 64; any Sq; Sk a multiple of 32 (partial last tiles are handled by
     zero-filled loads, a key-length mask and unstored rows).  Anything else raises
     ``NotImplementedError`` before a launch.
@@ -133,29 +143,48 @@ def flash_attn_fp4_func(
     Bk, Sk, Hkv, Dhk = k.shape
     Bv, Hv, Dv, Skh = v.shape
     D = 2 * Dh
-    assert Bk == B and Bv == B, "batch size mismatch"
+    paged = page_table is not None
+    if paged:
+        # k / v are a pool of Bk pages of Sk (= page_size) keys
+        assert page_table.dim() == 2 and page_table.shape[0] == B and page_table.dtype == torch.int32 \
+            and page_table.is_cuda, "page_table must be a (B, pages_per_seq) int32 CUDA tensor"
+        assert Bv == Bk, "k and v pools differ in their number of pages"
+        if Sk % 128 != 0:
+            raise NotImplementedError("page_size must be a multiple of 128 (whole K/V blocks per page)")
+        page_table = page_table.contiguous()
+        num_pages, page_size, pages_per_seq = Bk, Sk, page_table.shape[1]
+        B_kv, Sk_kv = num_pages, page_size           # shapes of the K / V operands
+        Sk = pages_per_seq * page_size               # logical key length
+    else:
+        assert Bk == B and Bv == B, "batch size mismatch"
+        B_kv, Sk_kv = B, Sk
+    if seqused_k is not None:
+        assert seqused_k.shape == (B,) and seqused_k.dtype == torch.int32 and seqused_k.is_cuda, \
+            "seqused_k must be a (B,) int32 CUDA tensor"
+        seqused_k = seqused_k.contiguous()
     assert Dhk == Dh, "q and k head dims differ"
-    assert Hv == Hkv and Skh * 2 == Sk, f"v must be (B, Hkv, Dv, Sk/2), got {tuple(v.shape)}"
+    assert Hv == Hkv and Skh * 2 == Sk_kv, f"v must be (B, Hkv, Dv, Sk/2), got {tuple(v.shape)}"
     assert Hq % Hkv == 0, "num_head must be divisible by num_head_kv"
     if D != Dv or D not in (64, 128):
         raise NotImplementedError(f"head dims (D={D}, Dv={Dv}) not built; supported: (128, 128) and (64, 64)")
     if D != 128 and variant == VARIANT_SERIAL:
         raise NotImplementedError("the serial bring-up variant is built for head dim 128 only")
-    if Sk % 32 != 0:
+    if Sk_kv % 32 != 0:
         raise NotImplementedError("seqlen_k must be a multiple of 32 (16-key scale blocks, 16-byte rows of V)")
     device = q.device
     if softmax_scale is None:
         softmax_scale = 1.0 / math.sqrt(D)
     if sf_layout == "linear":
         _validate_tensor(q_sf, "q_sf", (B, Sq, Hq, D // 16), torch.uint8, device)
-        _validate_tensor(k_sf, "k_sf", (B, Sk, Hkv, D // 16), torch.uint8, device)
-        _validate_tensor(v_sf, "v_sf", (B, Hkv, Dv, Sk // 16), torch.uint8, device)
+        _validate_tensor(k_sf, "k_sf", (B_kv, Sk_kv, Hkv, D // 16), torch.uint8, device)
+        _validate_tensor(v_sf, "v_sf", (B_kv, Hkv, Dv, Sk_kv // 16), torch.uint8, device)
         q_sf, k_sf, v_sf = (t if t.stride(-1) == 1 else t.contiguous() for t in (q_sf, k_sf, v_sf))
         q_sf, k_sf, v_sf = sf_to_tiled(q_sf, 1, 2), sf_to_tiled(k_sf, 1, 2), sf_to_tiled(v_sf, 2, 1, 2)
     elif sf_layout == "tiled":
         _validate_tensor(q_sf, "q_sf", (B, Hq, (Sq + 127) // 128, D // 64, 512), torch.uint8, device)
-        _validate_tensor(k_sf, "k_sf", (B, Hkv, (Sk + 127) // 128, D // 64, 512), torch.uint8, device)
-        _validate_tensor(v_sf, "v_sf", (B, Hkv, (Dv + 127) // 128, 2 * ((Sk + 127) // 128), 512), torch.uint8, device)
+        _validate_tensor(k_sf, "k_sf", (B_kv, Hkv, (Sk_kv + 127) // 128, D // 64, 512), torch.uint8, device)
+        _validate_tensor(v_sf, "v_sf", (B_kv, Hkv, (Dv + 127) // 128, 2 * ((Sk_kv + 127) // 128), 512), torch.uint8,
+                         device)
         assert q_sf.is_contiguous() and k_sf.is_contiguous() and v_sf.is_contiguous()
     else:
         raise ValueError(f"sf_layout must be 'linear' or 'tiled', got {sf_layout!r}")
@@ -205,7 +234,7 @@ def flash_attn_fp4_func(
         if softcap < 0.0 or not math.isfinite(softcap):
             raise ValueError("softcap must be a finite number >= 0")
         if (num_splits == 1 and sink is None and win_left is None and (win_right is None or win_right == 0)
-                and softcap == 0.0):
+                and softcap == 0.0 and seqused_k is None and not paged):
             rc = _lib.lib().fa4_nvfp4_fwd(ctypes.byref(p), stream)
             what = "fa4_nvfp4_fwd"
         else:
@@ -216,6 +245,10 @@ def flash_attn_fp4_func(
             x.window_right = -1 if win_right is None else int(win_right)
             x.sink = sink.data_ptr() if sink is not None else None
             x.softcap, x.reserved = softcap, 0
+            x.seqused_k = seqused_k.data_ptr() if seqused_k is not None else None
+            x.page_table = page_table.data_ptr() if paged else None
+            if paged:
+                x.page_size, x.pages_per_seq, x.num_pages = page_size, pages_per_seq, num_pages
             workspace = None
             if num_splits > 1:
                 nbytes = _lib.lib().fa4_nvfp4_splitkv_workspace_bytes(ctypes.byref(p), num_splits)

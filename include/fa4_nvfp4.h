@@ -155,6 +155,22 @@ typedef struct fa4_nvfp4_ext {
                                before masking (flash_attn/cute/interface.py:528-530,
                                testing.py:373-374), with the hardware tanh approximation; 0 = off */
   uint32_t reserved;        /* 0 */
+  /* KV cache, the reference's seqused_k / page_table (flash_attn/cute/interface.py:296-300,
+   * paged_kv.py): */
+  const int32_t* seqused_k; /* B counts on the device: batch entry b attends to its first
+                               seqused_k[b] keys (clamped to 0..Sk); causal and window limits align
+                               to that length.  NULL = Sk for every entry.  Scale bytes of the
+                               unused slots must not be NaN encodings (a zero-filled cache is fine) */
+  const int32_t* page_table;/* (B, pages_per_seq) page numbers on the device, or NULL.  With a table
+                               p->k / p->v / p->k_sf / p->v_sf describe a POOL of num_pages pages of
+                               page_size keys: k (num_pages, page_size, Hkv, D/2), v (num_pages, Hkv,
+                               Dv, page_size/2), tiled scales per page; k_stride_b / v_stride_b are
+                               page strides; p->Sk is the logical key length, at most
+                               pages_per_seq * page_size */
+  int32_t page_size;        /* keys per page, a multiple of 128 */
+  int32_t pages_per_seq;
+  int32_t num_pages;
+  int32_t reserved2;        /* 0 */
 } fa4_nvfp4_ext;
 int fa4_nvfp4_fwd_ex(const fa4_nvfp4_params* p, const fa4_nvfp4_ext* x, void* cuda_stream);
 

@@ -460,6 +460,65 @@ def test_softcap_parity(cuda_device, case):
         run(Q, K, V, causal, fa.VARIANT_WS64, softcap=cap)
 
 
+@pytest.mark.parametrize("case", [
+    # name, Sq, page_size, pages_per_seq, seqused, D, causal, splits
+    ("decode_one_row", 1, 128, 5, [208, 640, 48], 128, True, 1),
+    ("append_17_rows_split", 17, 256, 3, [768, 304, 17 + 15], 128, True, 2),
+    ("prefill_tile_and_a_half_empty_entry", 192, 128, 4, [512, 0, 336], 128, True, 1),
+    ("noncausal_d64", 40, 128, 3, [384, 16, 272], 64, False, 1),
+], ids=lambda c: c[0])
+def test_kv_cache_seqused_and_page_table(cuda_device, case):
+    """The reference's seqused_k / page_table (interface.py:296-300, paged_kv.py): every batch entry
+    attends to its first seqused_k[b] keys, with and without K / V living in a shuffled page pool.
+    Each entry is checked against the oracle on its own truncated operands; the paged call must give
+    the bits of the contiguous one (same arithmetic, other addresses)."""
+    _, Sq, page_size, pps, used, D, causal, splits = case
+    B, Hq, Hkv, Sk = len(used), 4, 2, page_size * pps
+    q, k, v = make_qkv(B, Sq, Sk, Hq, Hkv, D, seed=41, device=cuda_device)
+    Q, K, V = fa.quantize_qkv(q, k, v)
+    su = torch.tensor(used, dtype=torch.int32, device=cuda_device)
+    out, lse = run(Q, K, V, causal, seqused_k=su, num_splits=splits)
+    for b, sk in enumerate(used):
+        if sk == 0:
+            assert torch.all(out[b] == 0) and torch.all(torch.isinf(lse[b]) & (lse[b] < 0))
+            continue
+        Qb = fa.NVFP4Tensor(Q.data[b:b + 1], Q.sf[b:b + 1], Q.scale)
+        Kb = fa.NVFP4Tensor(K.data[b:b + 1, :sk], K.sf[b:b + 1, :sk], K.scale)
+        Vb = fa.NVFP4Tensor(V.data[b:b + 1, :, :, :sk // 2], V.sf[b:b + 1, :, :, :sk // 16], V.scale, is_v=True)
+        assert_parity(out[b:b + 1], lse[b:b + 1], *oracles(Qb, Kb, Vb, causal, num_splits=splits, variant=fa.VARIANT_WS))
+    # the same through a page pool: pages of all entries shuffled among three spare pages whose
+    # packed bytes are noise (their scale bytes stay zero: no NaN encodings)
+    g = torch.Generator(device="cpu").manual_seed(7)
+    n_pages = B * pps + 3
+    perm = torch.randperm(n_pages, generator=g)[:B * pps].reshape(B, pps)
+    kp = torch.randint(0, 256, (n_pages, page_size, Hkv, D // 2), dtype=torch.uint8, generator=g).to(cuda_device)
+    vp = torch.randint(0, 256, (n_pages, Hkv, D, page_size // 2), dtype=torch.uint8, generator=g).to(cuda_device)
+    ksp = torch.zeros(n_pages, page_size, Hkv, D // 16, dtype=torch.uint8, device=cuda_device)
+    vsp = torch.zeros(n_pages, Hkv, D, page_size // 16, dtype=torch.uint8, device=cuda_device)
+    for b in range(B):
+        for j in range(pps):
+            pg, k0 = int(perm[b, j]), j * page_size
+            kp[pg] = K.data[b, k0:k0 + page_size]
+            ksp[pg] = K.sf[b, k0:k0 + page_size]
+            vp[pg] = V.data[b, :, :, k0 // 2:(k0 + page_size) // 2]
+            vsp[pg] = V.sf[b, :, :, k0 // 16:(k0 + page_size) // 16]
+    table = perm.to(torch.int32).to(cuda_device)
+    out_p, lse_p = fa.flash_attn_fp4_func(Q.data, kp, vp, Q.sf, ksp, vsp, Q.scale, K.scale, V.scale, causal=causal,
+                                          return_lse=True, seqused_k=su, page_table=table, num_splits=splits)
+    torch.cuda.synchronize()
+    fa.check_status(cuda_device)
+    assert torch.equal(out_p, out) and torch.equal(lse_p, lse)
+    # a table without seqused_k: every entry sees the whole logical length
+    out_f, lse_f = fa.flash_attn_fp4_func(Q.data, kp, vp, Q.sf, ksp, vsp, Q.scale, K.scale, V.scale, causal=causal,
+                                          return_lse=True, page_table=table)
+    want_f, want_l = run(Q, K, V, causal, fa.VARIANT_WS)
+    torch.cuda.synchronize()
+    assert torch.equal(out_f, want_f) and torch.equal(lse_f, want_l)
+    with pytest.raises(NotImplementedError):
+        fa.flash_attn_fp4_func(Q.data, kp[:, :96], vp[..., :48], Q.sf, ksp[:, :96], vsp[..., :6], Q.scale, K.scale,
+                               V.scale, page_table=table)
+
+
 def test_varlen_packed_batch_matches_dense_calls(cuda_device):
     """flash_attn_varlen_func surface: three sequences packed along the token axis give the bits
     of three dense calls, and the oracle's tolerance per sequence; one slot is padded
