@@ -55,14 +55,15 @@ def parse_workload(name):
     raise SystemExit(f"unknown workload {name}")
 
 
-def flops_of(B, Hq, S, D, causal):
+def flops_of(B, Hq, S, D, causal, Dv=None):
     avg = S / 2 if causal else S                  # flash_attn/cute/bench_utils.py:15-38, Sq == Sk
-    return B * Hq * 2 * S * avg * (D + D)
+    return B * Hq * 2 * S * avg * (D + (D if Dv is None else Dv))
 
 
-def algorithmic_bytes(B, Hq, Hkv, S, D):
-    per = lambda h: B * S * h * (D // 2 + D // 16)          # packed values + block scales
-    return per(Hq) + 2 * per(Hkv) + B * S * Hq * D * 2 + B * Hq * S * 4
+def algorithmic_bytes(B, Hq, Hkv, S, D, Dv=None):
+    Dv = D if Dv is None else Dv
+    per = lambda h, d: B * S * h * (d // 2 + d // 16)       # packed values + block scales
+    return per(Hq, D) + per(Hkv, D) + per(Hkv, Dv) + B * S * Hq * Dv * 2 + B * Hq * S * 4
 
 
 def measured_peaks():
@@ -377,15 +378,17 @@ def run_sweep(args):
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     rows = []
     steps = max(3, min(args.steps, 20))
-    for D in (64, 128):
+    for D in (64, 128, 192):
+        Dv = 128 if D == 192 else D               # 192 pairs with a V / O head dim of 128
         for S in (1024, 2048, 4096, 16384):
             for causal in (False, True):
                 B, H = 8, 16
                 g = torch.Generator(device=dev).manual_seed(7)
-                q, k, v = (torch.randn(B, S, H, D, generator=g, device=dev, dtype=torch.bfloat16) for _ in range(3))
+                q, k = (torch.randn(B, S, H, D, generator=g, device=dev, dtype=torch.bfloat16) for _ in range(2))
+                v = torch.randn(B, S, H, Dv, generator=g, device=dev, dtype=torch.bfloat16)
                 Q, K, V = fa.quantize_qkv_fused(q, k, v, linear_sf=False)
                 del q, k, v
-                out = torch.empty(B, S, H, D, dtype=torch.bfloat16, device=dev)
+                out = torch.empty(B, S, H, Dv, dtype=torch.bfloat16, device=dev)
                 lse = torch.empty(B, H, S, dtype=torch.float32, device=dev)
 
                 def step():
@@ -402,8 +405,8 @@ def run_sweep(args):
                     ms += e0.elapsed_time(e1)
                 ms /= steps
                 fa.check_status(dev)
-                fl, by = flops_of(B, H, S, D, causal), algorithmic_bytes(B, H, H, S, D)
-                rows.append({"D": D, "S": S, "causal": causal, "ms": ms, "tflops": fl / ms / 1e9,
+                fl, by = flops_of(B, H, S, D, causal, Dv), algorithmic_bytes(B, H, H, S, D, Dv)
+                rows.append({"D": D, "Dv": Dv, "S": S, "causal": causal, "ms": ms, "tflops": fl / ms / 1e9,
                              "pct_fp4_peak_nominal": 100 * fl / ms / 1e9 / FP4_NOMINAL_TFLOPS,
                              "frac_of_4x_bf16_measured": fl / ms / 1e9 / (4 * peaks["bf16_tflops"]),
                              "hbm_gbs": by / ms / 1e6, "frac_of_hbm_peak": by / ms / 1e6 / peaks["hbm_gbs"]})
@@ -413,9 +416,9 @@ def run_sweep(args):
                       "n_gpus": 1, "steps": steps, "warmup": 3, "ms_per_step": head["ms"],
                       "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4",
                       "data": "synthetic",
-                      "config": {"workload": "sweep: D in {64, 128} x S in {1024, 2048, 4096, 16384} x causal / "
-                                             "non-causal, B = 8, H = 16 (B * H = 128); headline row D=128, "
-                                             "S=4096, causal; D = 192 is not built",
+                      "config": {"workload": "sweep: D in {64, 128, 192 (with Dv = 128)} x S in {1024, 2048, 4096, "
+                                             "16384} x causal / non-causal, B = 8, H = 16 (B * H = 128); "
+                                             "headline row D=128, S=4096, causal",
                                  "l2": "L2 flushed between timed launches (256 MiB write)"},
                       "gpu_launches": steps * len(rows), "sweep": rows}), flush=True)
 

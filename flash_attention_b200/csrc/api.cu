@@ -82,7 +82,7 @@ int ensure_launch_regs(Kernel kernel, int expected) {
 }  // namespace
 
 extern "C" int fa4_nvfp4_query(int32_t what) {
-  static const int dims[] = {128, 64};
+  static const int dims[] = {128, 64, 192};   // 192 pairs with a V / O head dim of 128
   switch (what) {
     case 0: return FA4_NVFP4_ABI_VERSION;
     case 1: return (int)(sizeof(dims) / sizeof(dims[0]));
@@ -157,7 +157,9 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
   if (!p->q || !p->k || !p->v || !p->q_sf || !p->k_sf || !p->v_sf || !p->out) return -FA4_E_NULL;
   if (p->B <= 0 || p->Sq <= 0 || p->Sk <= 0 || p->Hq <= 0 || p->Hkv <= 0) return -FA4_E_SHAPE;
   if (p->Hq % p->Hkv != 0) return -FA4_E_SHAPE;
-  if (p->D != p->Dv || (p->D != 128 && p->D != 64)) return -FA4_E_SHAPE;
+  // head dims built: (128, 128), (64, 64) and (192, 128), the last on the plain path only
+  const bool d192 = p->D == 192 && p->Dv == 128;
+  if (!d192 && (p->D != p->Dv || (p->D != 128 && p->D != 64))) return -FA4_E_SHAPE;
   // keys are blocked by 16 along Sk (V / P scales) and V rows are Sk/2 bytes with a 16-byte
   // stride rule for TMA: Sk must be a multiple of 32; Sq is free
   if (p->Sk % 32 != 0) return -FA4_E_SHAPE;
@@ -180,6 +182,7 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
   if (variant != FA4_VARIANT_SERIAL && variant != FA4_VARIANT_WS && variant != FA4_VARIANT_WS64)
     return -FA4_E_VARIANT;
   if (variant == FA4_VARIANT_WS64 && !plain) return -FA4_E_SHAPE;
+  if (d192 && variant != FA4_VARIANT_WS64) return -FA4_E_SHAPE;
   if (variant == FA4_VARIANT_SERIAL && p->D != 128) return -FA4_E_SHAPE;  // bring-up kernel: 128 only
   // window limits: `causal` is the right limit 0; an explicit right limit overrides it
   if (p->causal && win_right < 0) win_right = 0;
@@ -199,13 +202,16 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
   {
     const uint64_t dq[4] = {(uint64_t)p->D / 2, (uint64_t)p->Hq, (uint64_t)p->Sq, (uint64_t)p->B};
     const uint64_t sq[3] = {(uint64_t)p->q_stride_h, (uint64_t)p->q_stride_s, (uint64_t)p->q_stride_b};
-    const uint32_t bq[4] = {(uint32_t)p->D / 2, 1, (uint32_t)kBlockM, 1};
+    // a Q / K tile row is D / 2 bytes: one 64-byte-swizzled box for D = 128; 32-byte-wide boxes
+    // (32-byte swizzle), one per 64-element step, for D = 64 and 192
+    const uint32_t qk_box = p->D == 128 ? 64u : 32u;
+    const uint32_t bq[4] = {qk_box, 1, (uint32_t)kBlockM, 1};
     // with a page table K / V describe the pool: "batch" = page, "Sk" = keys per page
     const uint64_t k_rows = cache.page_table ? (uint64_t)cache.page_size : (uint64_t)p->Sk;
     const uint64_t k_batch = cache.page_table ? (uint64_t)cache.num_pages : (uint64_t)p->B;
     const uint64_t dk[4] = {(uint64_t)p->D / 2, (uint64_t)p->Hkv, k_rows, k_batch};
     const uint64_t sk[3] = {(uint64_t)p->k_stride_h, (uint64_t)p->k_stride_s, (uint64_t)p->k_stride_b};
-    const uint32_t bk[4] = {(uint32_t)p->D / 2, 1, (uint32_t)kBlockN, 1};
+    const uint32_t bk[4] = {qk_box, 1, (uint32_t)kBlockN, 1};
     const uint64_t dv[4] = {k_rows / 2, (uint64_t)p->Dv, (uint64_t)p->Hkv, k_batch};
     const uint64_t sv[3] = {(uint64_t)p->v_stride_d, (uint64_t)p->v_stride_h, (uint64_t)p->v_stride_b};
     const uint32_t bv[4] = {64, (uint32_t)p->Dv, 1, 1};
@@ -299,7 +305,8 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
         kernel<<<grid, ws64::kThreads, ws64::kSmemRequest, stream>>>(tm_q, tm_k, tm_v, tm_o, kp);
         return 0;
       };
-      rc = p->D == 128 ? launch64(attn_fwd_ws64_kernel<128>) : launch64(attn_fwd_ws64_kernel<64>);
+      rc = p->D == 128 ? launch64(attn_fwd_ws64_kernel<128>)
+                       : (p->D == 64 ? launch64(attn_fwd_ws64_kernel<64>) : launch64(attn_fwd_ws64_kernel<192>));
     } else if (p->D == 128) {
       rc = general ? launch(attn_fwd_ws_kernel<128, true>) : launch(attn_fwd_ws_kernel<128, false>);
     } else {

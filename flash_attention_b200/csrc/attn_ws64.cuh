@@ -82,18 +82,23 @@ static_assert((kThreads / 128) * 32 * kRegsLaunch <= 16384, "register file of a 
 // tensor memory: S[4] x 64 columns, O 128, scale factors
 // (O at column 256 and Q scales at 384 as in the 128-key kernel); K and V scales have one slot of
 // 8 columns per shared-memory stage, written by the copy warp as soon as the tile has landed
-constexpr uint32_t kTmS64 = 0, kTmSFK64 = 392 /* 4 x 8 */, kTmSFV64 = 424 /* 4 x 8 */, kTmSFP64 = 456 /* 4 x 4 */;
+// (sized for head dim 192: three 64-element steps, 12 scale columns per Q / K tile)
+constexpr uint32_t kTmS64 = 0, kTmSFQ64 = 384 /* 12 */, kTmSFK64 = 396 /* 4 x 12 */, kTmSFV64 = 444 /* 4 x 8 */,
+                   kTmSFP64 = 476 /* 4 x 4 */;
 static_assert(kTmSFP64 + 16 <= 512, "tensor memory columns");
+// shared-memory slots of a Q / K tile and of its scales, sized for head dim 192 (128 rows of 96
+// bytes as three 32-byte-wide sub-tiles; three scale chunks)
+constexpr uint32_t kQkSlot = 128 * 96, kQkSfSlot = 3 * 512;
 constexpr uint32_t kSlackNs = 500;         // suspend hint of the waits of roles with slack
 constexpr uint32_t kPTileBytes = 128 * 32;  // 128 rows x 64 e2m1 keys
 
 constexpr uint32_t kOffQ = 0;
-constexpr uint32_t kOffK = kOffQ + 2 * kTileBytes;
-constexpr uint32_t kOffV = kOffK + kStagesK * kTileBytes;
+constexpr uint32_t kOffK = kOffQ + 2 * kQkSlot;
+constexpr uint32_t kOffV = kOffK + kStagesK * kQkSlot;
 constexpr uint32_t kOffP = kOffV + kStagesV * kTileBytes;
 constexpr uint32_t kOffSFQ = kOffP + kPSlots * kPTileBytes;
-constexpr uint32_t kOffSFK = kOffSFQ + 2 * kSfBytes;
-constexpr uint32_t kOffSFV = kOffSFK + kStagesK * kSfBytes;
+constexpr uint32_t kOffSFK = kOffSFQ + 2 * kQkSfSlot;
+constexpr uint32_t kOffSFV = kOffSFK + kStagesK * kQkSfSlot;
 constexpr uint32_t kOffSFP = kOffSFV + kStagesV * kSfBytes;      // kPSlots x 512
 constexpr uint32_t kOffOut = kOffSFP + kPSlots * 512;            // 32 KB staging tile
 constexpr uint32_t kOffHand = kOffOut + 32 * 1024;               // kSBufs x 128 reference maxima
@@ -210,13 +215,28 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
-  static_assert(kD == 128 || kD == 64, "head dimensions built: 128 and 64");
+  static_assert(kD == 128 || kD == 64 || kD == 192, "head dimensions built: 128, 64 and (192, 128)");
+  constexpr int kDv = kD == 192 ? 128 : kD;            // head dim of V and O
   constexpr uint32_t idesc_qk = make_idesc_nvf4(128, 128);
-  constexpr uint32_t idesc_pv = make_idesc_nvf4(128, kD);
+  constexpr uint32_t idesc_pv = make_idesc_nvf4(128, kDv);
   constexpr int kSteps = kD / 64;                      // 64-element steps of Q K^T
   constexpr uint32_t kQkBytes = 128u * kD / 2;         // bytes of a Q or K tile
   constexpr uint32_t kQkSfBytes = kSteps * 512u;       // its scale chunks (128 rows x kD / 16)
-  constexpr uint32_t kVBytes = kD * 64u;               // V tile: kD rows of 128 keys
+  constexpr uint32_t kVBytes = kDv * 64u;              // V tile: kDv rows of 128 keys
+  // A Q / K tile in shared memory: one 64-byte-swizzled box for head dim 128; for 64 and 192 one or
+  // three 32-byte-wide boxes (32-byte swizzle, 4 KB each), one per 64-element step.
+  auto load_qk_tile = [&](uint32_t dst, const CUtensorMap* tm, uint32_t bar, int h, int row, int b) {
+    if constexpr (kD == 128) {
+      tma_load_4d(dst, tm, bar, 0, h, row, b);
+    } else {
+#pragma unroll
+      for (int j = 0; j < kSteps; ++j) tma_load_4d(dst + 4096 * j, tm, bar, 32 * j, h, row, b);
+    }
+  };
+  auto desc_qk = [&](uint32_t tile, int j) -> uint64_t {
+    if constexpr (kD == 128) return make_desc_sw64(tile + 32 * j);
+    return make_desc_sw32(tile + 4096 * j);
+  };
 
 #define FA4_FOR_EACH_TILE                                                                        \
   uint32_t gb = 0, ti = 0;                                                                       \
@@ -281,13 +301,13 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
         FA4_EPI_SYNC()
       }
 #pragma unroll 1
-      for (int c = 0; c < kD / 32; ++c) {
+      for (int c = 0; c < kDv / 32; ++c) {
         uint8_t* box_row = gbase + kOffOut + (c >> 1) * (16 * 1024) + row * 128;
         uint32_t o[32];
         if (n > 0) {
           tmem_ld32(lane_addr + kTmO + 32 * c, o);
           tc_wait_ld();
-          if (c == kD / 32 - 1) {
+          if (c == kDv / 32 - 1) {
             tc_fence_before_sync();
             mbar_arrive(bars.at(Bars::kOFree));  // the P V issuer may start the next tile
           }
@@ -310,7 +330,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
       FA4_EPI_SYNC()
       if (leader) {
 #pragma unroll
-        for (int bx = 0; bx < kD / 64; ++bx) {
+        for (int bx = 0; bx < kDv / 64; ++bx) {
           tma_store_4d(&tm_o, base + kOffOut + bx * 16 * 1024, 64 * bx, t.h, t.m_blk * kBlockM, t.b);
         }
         bulk_commit_group();
@@ -342,9 +362,9 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
           if (!ok) break;
         }
         mbar_arrive_expect_tx(bars.at(Bars::kQFull + qb), kQkBytes + kQkSfBytes);
-        tma_load_4d(base + kOffQ + qb * kTileBytes, &tm_q, bars.at(Bars::kQFull + qb), 0, t.h,
-                    t.m_blk * kBlockM, t.b);
-        bulk_load(base + kOffSFQ + qb * kSfBytes,
+        load_qk_tile(base + kOffQ + qb * kQkSlot, &tm_q, bars.at(Bars::kQFull + qb), t.h,
+                     t.m_blk * kBlockM, t.b);
+        bulk_load(base + kOffSFQ + qb * kQkSfSlot,
                   p.q_sf + t.b * p.qsf_stride_b + t.h * p.qsf_stride_h + (int64_t)t.m_blk * kQkSfBytes,
                   kQkSfBytes, bars.at(Bars::kQFull + qb));
         issued_q = ti + 1;
@@ -361,9 +381,9 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
               if (!ok) break;
             }
             mbar_arrive_expect_tx(bars.at(Bars::kKFull + st), kQkBytes + kQkSfBytes);
-            tma_load_4d(base + kOffK + st * kTileBytes, &tm_k, bars.at(Bars::kKFull + st), 0, t.hk,
-                        nb * kBlockN, t.b);
-            bulk_load(base + kOffSFK + st * kSfBytes, ksf + (int64_t)nb * kQkSfBytes, kQkSfBytes,
+            load_qk_tile(base + kOffK + st * kQkSlot, &tm_k, bars.at(Bars::kKFull + st), t.hk,
+                         nb * kBlockN, t.b);
+            bulk_load(base + kOffSFK + st * kQkSfSlot, ksf + (int64_t)nb * kQkSfBytes, kQkSfBytes,
                       bars.at(Bars::kKFull + st));
             issued_k = G + 1;
           }
@@ -418,8 +438,8 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
         uint64_t dq[kSteps];
 #pragma unroll
         for (int ks = 0; ks < kSteps; ++ks) {
-          tc_cp_sf(tmem + kTmSFQ + 4 * ks, base + kOffSFQ + qb * kSfBytes + 512 * ks);
-          dq[ks] = ws::make_desc_qk<kD>(base + kOffQ + qb * kTileBytes, ks);
+          tc_cp_sf(tmem + kTmSFQ64 + 4 * ks, base + kOffSFQ + qb * kQkSfSlot + 512 * ks);
+          dq[ks] = desc_qk(base + kOffQ + qb * kQkSlot, ks);
         }
         for (int i = 0; ok && i < n; ++i) {
           const uint32_t G = gb + i, st = G % kStagesK;
@@ -430,8 +450,8 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
           FA4_PH(1);
           FA4_TRACE_EV(20, G);
           tc_fence_after_sync();
-          const uint32_t sfk = tmem + kTmSFK64 + 8 * st;
-          const uint32_t kt = base + kOffK + st * kTileBytes;
+          const uint32_t sfk = tmem + kTmSFK64 + 12 * st;
+          const uint32_t kt = base + kOffK + st * kQkSlot;
           // one product of N = 128 fills the two neighbouring S buffers of sub-blocks 2G and 2G + 1
           // (keys 0-63 and 64-127 of the tile): half the tcgen05 instructions of two N = 64
           // products, and the in-order issue slots of this thread are scarce
@@ -447,8 +467,8 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
           FA4_PH(2);
 #pragma unroll
           for (int ks = 0; ks < kSteps; ++ks) {
-            mma_nvf4(tmem + kTmS64 + 64 * b0, dq[ks], ws::make_desc_qk<kD>(kt, ks), idesc_qk,
-                     tmem + kTmSFQ + 4 * ks, sfk + 4 * ks, ks > 0 ? 1u : 0u);
+            mma_nvf4(tmem + kTmS64 + 64 * b0, dq[ks], desc_qk(kt, ks), idesc_qk,
+                     tmem + kTmSFQ64 + 4 * ks, sfk + 4 * ks, ks > 0 ? 1u : 0u);
           }
           FA4_PH(4);
           tc_commit(bars.at(Bars::kSFull + b0));  // both softmax warpgroups of the pair wait on it
@@ -541,9 +561,9 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
             ok = mbar_wait_relaxed<kSlackNs>(bars.at(Bars::kKFull + st), (G / kStagesK) & 1, wc, kS64KFull);
             if (!ok) break;
             tc_fence_after_sync();
-            const uint32_t ksf = base + kOffSFK + st * kSfBytes;
+            const uint32_t ksf = base + kOffSFK + st * kQkSfSlot;
 #pragma unroll
-            for (int ks = 0; ks < kSteps; ++ks) tc_cp_sf(tmem + kTmSFK64 + 8 * st + 4 * ks, ksf + 512 * ks);
+            for (int ks = 0; ks < kSteps; ++ks) tc_cp_sf(tmem + kTmSFK64 + 12 * st + 4 * ks, ksf + 512 * ks);
             tc_commit(bars.at(Bars::kKsf + st));
           }
           if (iv >= 0 && iv < n) {
@@ -679,7 +699,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
           if (!ok) break;
           tc_fence_after_sync();
           const float f = fix ? reference_factor(m_prev, m_new, p.sl2) : 1.f;
-          rescale_accumulator(lane_addr + kTmO, f, kD / 32);
+          rescale_accumulator(lane_addr + kTmO, f, kDv / 32);
           tc_wait_st();
         }
         fence_proxy_async_smem();

@@ -130,7 +130,7 @@ def flash_attn_fp4_func(
     of 128; the logical key length is ``pages_per_seq * page_size``.  Scale bytes of unused
     cache slots must not be NaN encodings (a zero-filled cache is fine).
 
-    Built so far: D = Dv = 128 or 64; any Sq; Sk a multiple of 32 (partial last tiles are handled by
+    Built so far: D = Dv = 128 or 64, or (D, Dv) = (192, 128) without split / window / sink / cache; any Sq; Sk a multiple of 32 (partial last tiles are handled by
     zero-filled loads, a key-length mask and unstored rows).  Anything else raises
     ``NotImplementedError`` before a launch.
     """
@@ -165,8 +165,9 @@ def flash_attn_fp4_func(
     assert Dhk == Dh, "q and k head dims differ"
     assert Hv == Hkv and Skh * 2 == Sk_kv, f"v must be (B, Hkv, Dv, Sk/2), got {tuple(v.shape)}"
     assert Hq % Hkv == 0, "num_head must be divisible by num_head_kv"
-    if D != Dv or D not in (64, 128):
-        raise NotImplementedError(f"head dims (D={D}, Dv={Dv}) not built; supported: (128, 128) and (64, 64)")
+    if not ((D == Dv and D in (64, 128)) or (D == 192 and Dv == 128)):
+        raise NotImplementedError(f"head dims (D={D}, Dv={Dv}) not built; supported: (128, 128), (64, 64) "
+                                  "and (192, 128)")
     if D != 128 and variant == VARIANT_SERIAL:
         raise NotImplementedError("the serial bring-up variant is built for head dim 128 only")
     if Sk_kv % 32 != 0:

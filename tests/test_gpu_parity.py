@@ -342,6 +342,35 @@ def test_parity_with_oracle_head_dim_64(cuda_device, case):
         run(Q, K, V, causal, fa.VARIANT_SERIAL)
 
 
+@pytest.mark.parametrize("case", [
+    # name, B, Sq, Sk, Hq, Hkv, causal
+    ("d192_noncausal", 1, 256, 384, 2, 2, False),
+    ("d192_causal_gqa", 2, 384, 384, 4, 2, True),
+    ("d192_ragged_causal_sq_lt_sk", 1, 200, 352, 4, 1, True),
+    ("d192_masked_rows", 1, 300, 160, 2, 2, True),
+], ids=lambda c: c[0])
+def test_parity_with_oracle_head_dim_192_128(cuda_device, case):
+    """Q / K head dim 192 with V / O head dim 128 (the reference's only pair above 128,
+    interface.py:84-99): three 64-element steps of Q K^T on 32-byte-wide sub-tiles, 64-key kernel
+    only.  Both quantisers feed it; features of the 128-key kernel are refused for this shape."""
+    _, B, Sq, Sk, Hq, Hkv, causal = case
+    g = torch.Generator().manual_seed(17)
+    q = torch.randn(B, Sq, Hq, 192, generator=g).bfloat16().to(cuda_device)
+    k = torch.randn(B, Sk, Hkv, 192, generator=g).bfloat16().to(cuda_device)
+    v = torch.randn(B, Sk, Hkv, 128, generator=g).bfloat16().to(cuda_device)
+    Q, K, V = fa.quantize_qkv(q, k, v)
+    out, lse = run(Q, K, V, causal)
+    assert out.dtype == torch.bfloat16 and out.shape == (B, Sq, Hq, 128)
+    assert_parity(out, lse, *oracles(Q, K, V, causal))
+    if Sk % 16 == 0:
+        Qf, Kf, Vf = fa.quantize_qkv_fused(q, k, v)
+        out_f, lse_f = fa.flash_attn_func(Qf, Kf, Vf, causal=causal, return_lse=True)
+        assert_parity(out_f, lse_f, *oracles(Qf, Kf, Vf, causal))
+    for kw in ({"variant": fa.VARIANT_WS}, {"num_splits": 2}, {"window_size": (64, 0)}):
+        with pytest.raises((ValueError, NotImplementedError)):
+            run(Q, K, V, causal, **kw)
+
+
 CASES_SPLIT = [
     # name, B, Sq, Sk, Hq, Hkv, D, causal, splits
     ("decode_one_row", 2, 1, 2048, 8, 2, 128, True, 4),
