@@ -16,7 +16,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libfa4_nvfp4.so")
 CSRC = os.path.join(_HERE, "csrc")
 SOURCES = ["api.cu"]
-HEADERS = ["ptx.cuh", "softmax.cuh", "attn_common.cuh", "attn_serial.cuh", "attn_ws.cuh", "attn_ws64.cuh",
+HEADERS = ["ptx.cuh", "softmax.cuh", "attn_common.cuh", "attn_serial.cuh", "attn_ws.cuh", "attn_ws64.cuh", "attn_decode.cuh",
            "aux_kernels.cuh"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--shared", "-Xcompiler", "-fPIC"]

@@ -6,6 +6,7 @@
 #include "attn_serial.cuh"
 #include "attn_ws.cuh"
 #include "attn_ws64.cuh"
+#include "attn_decode.cuh"
 #include "aux_kernels.cuh"
 #include "quantize.cuh"
 
@@ -179,8 +180,19 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
   const bool plain = num_splits == 1 && win_left < 0 && win_right <= 0 && sink == nullptr && softcap == 0.f && !cached;
   int variant = p->variant;
   if (variant == FA4_VARIANT_AUTO) variant = plain ? FA4_VARIANT_WS64 : FA4_VARIANT_WS;
-  if (variant != FA4_VARIANT_SERIAL && variant != FA4_VARIANT_WS && variant != FA4_VARIANT_WS64)
+  if (variant != FA4_VARIANT_SERIAL && variant != FA4_VARIANT_WS && variant != FA4_VARIANT_WS64 &&
+      variant != FA4_VARIANT_DECODE)
     return -FA4_E_VARIANT;
+  const bool decode = variant == FA4_VARIANT_DECODE;
+  const int dec_rows = p->Sq * (p->Hq / p->Hkv);
+  if (decode) {
+    // a handful of query rows per kv head, head dim 128, causal or unmasked; always through the
+    // partial-output workspace and the combine kernel
+    if (p->D != 128 || p->Dv != 128 || (int64_t)p->Sq * (p->Hq / p->Hkv) > dec::kMaxRows) return -FA4_E_SHAPE;
+    if (win_left >= 0 || win_right > 0 || sink != nullptr || softcap > 0.f) return -FA4_E_SHAPE;
+    if (workspace == nullptr || !aligned16(workspace)) return -FA4_E_NULL;
+    if (workspace_bytes < (uint64_t)splitkv_bytes(p, num_splits)) return -FA4_E_TOO_LARGE;
+  }
   if (variant == FA4_VARIANT_WS64 && !plain) return -FA4_E_SHAPE;
   if (d192 && variant != FA4_VARIANT_WS64) return -FA4_E_SHAPE;
   if (variant == FA4_VARIANT_SERIAL && p->D != 128) return -FA4_E_SHAPE;  // bring-up kernel: 128 only
@@ -268,13 +280,33 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
   kp.num_splits = num_splits;
   kp.Dv = p->Dv;
   kp.o_partial = static_cast<float*>(workspace);
-  kp.lse_partial = num_splits > 1
+  kp.lse_partial = (num_splits > 1 || decode)
                        ? kp.o_partial + (int64_t)num_splits * p->B * p->Sq * p->Hq * p->Dv
                        : nullptr;
 
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
   const unsigned tiles = (unsigned)(kp.num_m_blocks * p->Hq * p->B * num_splits);
-  if (variant == FA4_VARIANT_SERIAL) {
+  if (decode) {
+    DecodeParams dp;
+    dp.q = static_cast<const uint8_t*>(p->q);
+    dp.q_sf = kp.q_sf;
+    dp.q_stride_b = p->q_stride_b;
+    dp.q_stride_s = p->q_stride_s;
+    dp.q_stride_h = p->q_stride_h;
+    dp.num_splits = num_splits;
+    dp.o_partial = kp.o_partial;
+    dp.lse_partial = kp.lse_partial;
+    auto launch_dec = [&](auto kernel) -> int {
+      if (int e = ensure_smem(kernel, dec::kSmemRequest)) return e;
+      kernel<<<dim3((unsigned)num_splits, (unsigned)p->Hkv, (unsigned)p->B), dec::kThreads, dec::kSmemRequest,
+               stream>>>(tm_k, tm_v, kp, dp);
+      return 0;
+    };
+    const int rc = dec_rows <= 4 ? launch_dec(attn_decode_kernel<4>)
+                                 : (dec_rows <= 8 ? launch_dec(attn_decode_kernel<8>)
+                                                  : launch_dec(attn_decode_kernel<16>));
+    if (rc != 0) return rc;
+  } else if (variant == FA4_VARIANT_SERIAL) {
     if (int e = ensure_smem(attn_fwd_serial_kernel, serial::kSmemRequest)) return e;
     attn_fwd_serial_kernel<<<tiles, 128, serial::kSmemRequest, stream>>>(tm_q, tm_k, tm_v, kp);
   } else {
@@ -316,7 +348,7 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
-  if (num_splits > 1) {
+  if (num_splits > 1 || decode) {
     const int64_t items = (int64_t)p->B * p->Sq * p->Hq * (p->Dv / 4);
     int64_t blocks = (items + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;

@@ -1,0 +1,525 @@
+// Decode / append kernel: a handful of query rows against a long key range (head dim 128).
+//
+// The prefill kernels put QUERY rows on the 128 lanes of the tensor-core tile; with one query
+// token per sequence 127 of them are padding and the per-block latency chain (about 3000 clocks,
+// two blocks in flight) sets the pace: 0.7 TB/s of K/V.  Here the products are transposed, as
+// decode kernels usually do: the 128 KEYS of a block sit on the lanes and the query rows -- the
+// Sq x (query heads per kv head) rows that share this kv head, at most 16 -- on the N side:
+//
+//   S^T (128 keys x 16 rows)  = K (A operand, the tile as it is loaded) . Q^T (B operand)
+//   O^T (128 dv   x 16 rows) += V^T (A operand: V is stored key-contiguous, i.e. already as the
+//                                    K-major (dv, keys) matrix) . P^T (B operand)
+//
+// so no lane is wasted, an S^T buffer is 16 tensor-memory columns (four blocks in flight cost 64),
+// and a softmax thread owns ONE key with its <= 16 scores.  The softmax statistics run across
+// lanes: row maxima and sums by warp shuffles plus one exchange through shared memory per block,
+// the 16-key block maxima of the P scales by four shuffle steps.  P is quantised exactly as in
+// the prefill kernels (e2m1, power-of-two ue4m3 scale per row and 16 keys, lazy reference).
+//
+// One CTA = one (split, kv head, batch entry): a contiguous share of the entry's 128-key blocks,
+// visited in ascending order; it writes a normalised fp32 partial O and a partial LSE for
+// combine_splits_kernel, like the split-KV path of attn_ws.cuh.  Grid = (splits, Hkv, B).
+//   warps 0-3  softmax / correction / epilogue (thread = key lane, later = dv lane)
+//   warp 4     TMA producer (K / V rings of four tiles, through the page table if there is one)
+//   warp 5     MMA issuer (owns tensor memory)
+// Every wait is bounded, like everywhere else.
+#pragma once
+#include "attn_common.cuh"
+#include "attn_serial.cuh"  // tile byte sizes
+#include "softmax.cuh"
+
+namespace fa4 {
+namespace dec {
+
+constexpr int kThreads = 192;
+constexpr int kStages = 4;   // K and V tiles in flight
+constexpr int kSBufs = 4;    // S^T buffers (16 columns each)
+constexpr int kPSlots = 4;   // P^T tiles (16 rows x 64 bytes) and their scale chunks
+constexpr int kMaxRows = 16; // query rows per kv head: Sq * group
+
+// shared memory
+constexpr uint32_t kOffK = 0;
+constexpr uint32_t kOffV = kOffK + kStages * kTileBytes;
+constexpr uint32_t kOffSFK = kOffV + kStages * kTileBytes;
+constexpr uint32_t kOffSFV = kOffSFK + kStages * kSfBytes;
+constexpr uint32_t kOffQ = kOffSFV + kStages * kSfBytes;   // 16 rows x 64 bytes, 64-byte swizzle
+constexpr uint32_t kOffSFQ = kOffQ + 1024;                 // two 512-byte chunks
+constexpr uint32_t kOffP = kOffSFQ + 1024;                 // kPSlots x 1024
+constexpr uint32_t kOffSFP = kOffP + kPSlots * 1024;       // kPSlots x 2 chunks x 512
+constexpr uint32_t kOffRed = kOffSFP + kPSlots * 1024;     // 2 x 4 warps x 16 floats
+constexpr uint32_t kOffBar = kOffRed + 2 * 4 * 16 * 4;
+struct Bars {
+  uint32_t base;
+  static constexpr uint32_t kKFull = 0, kVFull = kKFull + kStages, kKFree = kVFull + kStages,
+                            kVFree = kKFree + kStages, kSFull = kVFree + kStages,
+                            kSFree = kSFull + kSBufs, kPFull = kSFree + kSBufs,
+                            kPvDone = kPFull + kPSlots, kQReady = kPvDone + kPSlots,
+                            kSync = kQReady + 1, kDrain = kSync + 1, kCount = kDrain + 1;
+  __device__ explicit Bars(uint32_t b) : base(b) {}
+  __device__ __forceinline__ uint32_t at(uint32_t idx) const { return base + 8u * idx; }
+};
+constexpr uint32_t kOffMisc = kOffBar + 8 * Bars::kCount;
+constexpr uint32_t kSmemRequest = kOffMisc + 16 + 1024;
+
+// tensor memory (256 columns allocated): S^T buffers, O^T, scale factors
+constexpr uint32_t kDTmemCols = 256;
+constexpr uint32_t kDTmS = 0, kDTmO = 64, kDTmSFQ = 80, kDTmSFK = 88 /* 4 x 8 */, kDTmSFV = 120 /* 4 x 8 */,
+                   kDTmSFP = 152 /* 4 x 8 */;
+
+enum Site { kDKFull = 80, kDVFull, kDKFree, kDVFree, kDSFull, kDSFree, kDPFull, kDPvDone, kDQReady, kDSync };
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15};"
+      ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+      "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),
+      "r"(r[15]), "r"(taddr)
+      : "memory");
+}
+
+// One e2m1 byte from two values: `lo` goes to the low nibble (the even key).
+__device__ __forceinline__ uint32_t pack2_e2m1(float lo, float hi) {
+  uint16_t b;
+  asm("{\n"
+      ".reg .b8 t;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 t, %2, %1;\n"
+      "cvt.u16.u8 %0, t;\n"
+      "}\n"
+      : "=h"(b)
+      : "f"(lo), "f"(hi));
+  return b;
+}
+
+// Exponent of one 16-key block of P from its maximum (the scalar form of block_exponents4):
+// noff with p'/2^e = 2^(s * sl2 + noff), and the byte e + 127.
+__device__ __forceinline__ void block_exponent1(float bm, float m_ref, float sl2, float& noff,
+                                                uint32_t& ue) {
+  constexpr float kMagic = 12582912.f + 127.f;
+  const float msc = (m_ref == kNegInf) ? 0.f : m_ref * sl2;
+  const float c_t = static_cast<float>(kShift) - kLog2Of6 + 0.4999995f - msc;
+  const float c_off = static_cast<float>(kShift) - msc;
+  float t = fmaf(bm, sl2, c_t);
+  t = fmaxf(t, static_cast<float>(kEMin) - 0.4f);
+  const float u = t + kMagic;
+  ue = __float_as_uint(u) & 0xffu;
+  noff = c_off - (u - kMagic);
+}
+
+}  // namespace dec
+
+struct DecodeParams {
+  const uint8_t* q;      // (B, Sq, Hq, 64) packed e2m1
+  const uint8_t* q_sf;   // tiled (B, Hq, ceil(Sq/128), 2, 512)
+  int64_t q_stride_b, q_stride_s, q_stride_h;
+  int num_splits;
+  float* o_partial;      // (splits, B, Sq, Hq, 128) fp32
+  float* lse_partial;    // (splits, B, Hq, Sq) fp32
+};
+
+// kR: query rows the softmax code is unrolled for (4, 8 or 16 >= Sq * group).  The row loops are
+// fully unrolled, and sixteen rows of them no longer fit the instruction cache (measured: 10 000
+// clocks per block, instruction-fetch bound), so the common decode shapes get the short forms.
+template <int kR>
+__global__ void __launch_bounds__(dec::kThreads, 1)
+attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                   const KernelParams p, const DecodeParams d) {
+  using namespace dec;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gbase = smem_raw + (base - smem_u32(smem_raw));
+  const Bars bars(base + kOffBar);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + kOffMisc);
+  volatile uint32_t* s_abort = reinterpret_cast<volatile uint32_t*>(gbase + kOffMisc + 4);
+  volatile float* s_red = reinterpret_cast<volatile float*>(gbase + kOffRed);  // [2][4][16]
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const WaitCtx wc{s_abort, p.status, p.budget_ns};
+  const int R = p.Sq * p.group;  // live query rows (<= 16)
+
+  // this CTA's share of the entry's K/V blocks (ascending, contiguous, ceil division like the
+  // split-KV path of the prefill kernel)
+  int sk = p.Sk;
+  if (p.seqused_k != nullptr) {
+    const int used = p.seqused_k[b];
+    sk = used < 0 ? 0 : (used < p.Sk ? used : p.Sk);
+  }
+  const int n_total = (sk + kBlockN - 1) / kBlockN;
+  const int per = (n_total + d.num_splits - 1) / d.num_splits;
+  const int i0 = split * per < n_total ? split * per : n_total;
+  const int i1 = i0 + per < n_total ? i0 + per : n_total;
+  const int n = i1 - i0;
+
+  if (tid == 0) {
+    *s_abort = 0u;
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bars.at(Bars::kKFull + s), 1);
+      mbar_init(bars.at(Bars::kVFull + s), 1);
+      mbar_init(bars.at(Bars::kKFree + s), 1);
+      mbar_init(bars.at(Bars::kVFree + s), 1);
+      mbar_init(bars.at(Bars::kSFull + s), 1);
+      mbar_init(bars.at(Bars::kSFree + s), 128);
+      mbar_init(bars.at(Bars::kPFull + s), 128);
+      mbar_init(bars.at(Bars::kPvDone + s), 1);
+    }
+    mbar_init(bars.at(Bars::kQReady), 128);
+    mbar_init(bars.at(Bars::kSync), 128);
+    mbar_init(bars.at(Bars::kDrain), 1);
+    fence_barrier_init();
+  }
+  if (warp == 4 && lane == 0) {
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+  }
+  if (warp == 5) {
+    tmem_alloc(base + kOffMisc, kDTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+  constexpr uint32_t idesc = make_idesc_nvf4(128, 16);
+  bool ok = true;
+
+  if (warp == 4) {
+    // ============================================ TMA producer ==================================
+    if (lane == 0) {
+      uint32_t issued = 0;
+      for (int li = 0; ok && li < n; ++li) {
+        const int nb = i0 + li;
+        const uint32_t st = li % kStages;
+        int kb = b, nbl = nb;   // batch coordinate and block inside it (a page of the pool)
+        if (p.page_table != nullptr) {
+          const int key0 = nb * kBlockN, pg = key0 / p.page_size;
+          kb = p.page_table[(int64_t)b * p.pages_per_seq + pg];
+          nbl = (key0 - pg * p.page_size) / kBlockN;
+        }
+        if (li >= kStages) {
+          ok = mbar_wait(bars.at(Bars::kKFree + st), ((li - kStages) / kStages) & 1, wc, kDKFree);
+          if (!ok) break;
+        }
+        mbar_arrive_expect_tx(bars.at(Bars::kKFull + st), kTileBytes + kSfBytes);
+        tma_load_4d(base + kOffK + st * kTileBytes, &tm_k, bars.at(Bars::kKFull + st), 0, hk,
+                    nbl * kBlockN, kb);
+        bulk_load(base + kOffSFK + st * kSfBytes,
+                  p.k_sf + kb * p.ksf_stride_b + hk * p.ksf_stride_h + (int64_t)nbl * kSfBytes, kSfBytes,
+                  bars.at(Bars::kKFull + st));
+        if (li >= kStages) {
+          ok = mbar_wait(bars.at(Bars::kVFree + st), ((li - kStages) / kStages) & 1, wc, kDVFree);
+          if (!ok) break;
+        }
+        mbar_arrive_expect_tx(bars.at(Bars::kVFull + st), kTileBytes + kSfBytes);
+        tma_load_4d(base + kOffV + st * kTileBytes, &tm_v, bars.at(Bars::kVFull + st),
+                    nbl * (kBlockN / 2), 0, hk, kb);
+        bulk_load(base + kOffSFV + st * kSfBytes,
+                  p.v_sf + kb * p.vsf_stride_b + hk * p.vsf_stride_h + (int64_t)nbl * kSfBytes, kSfBytes,
+                  bars.at(Bars::kVFull + st));
+        issued = li + 1;
+      }
+      if (!ok) {
+        // bounded drain: let the copies already issued land before the CTA's memory is released
+        const uint64_t t0 = globaltimer_ns();
+        for (uint32_t i = issued > kStages ? issued - kStages : 0; i < issued; ++i) {
+          while (!(mbar_try_wait(bars.at(Bars::kKFull + (i % kStages)), (i / kStages) & 1) &&
+                   mbar_try_wait(bars.at(Bars::kVFull + (i % kStages)), (i / kStages) & 1)) &&
+                 globaltimer_ns() - t0 < 50ull * 1000 * 1000) {}
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // ============================================ MMA issuer ====================================
+    if (lane == 0 && n > 0) {
+      ok = mbar_wait(bars.at(Bars::kQReady), 0, wc, kDQReady);
+      uint64_t dq[2];
+      if (ok) {
+        tc_fence_after_sync();
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks) {
+          tc_cp_sf(tmem + kDTmSFQ + 4 * ks, base + kOffSFQ + 512 * ks);
+          dq[ks] = make_desc_sw64(base + kOffQ + 32 * ks);
+        }
+      }
+      for (int step = 0; ok && step < n + 2; ++step) {
+        if (step < n) {
+          // S^T = K . Q^T of block step
+          const uint32_t li = step, st = li % kStages, buf = li % kSBufs;
+          ok = mbar_wait(bars.at(Bars::kKFull + st), (li / kStages) & 1, wc, kDKFull);
+          if (!ok) break;
+          if (li >= kSBufs) {
+            ok = mbar_wait(bars.at(Bars::kSFree + buf), ((li - kSBufs) / kSBufs) & 1, wc, kDSFree);
+            if (!ok) break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sfk = tmem + kDTmSFK + 8 * st;
+          const uint32_t kt = base + kOffK + st * kTileBytes, ksf = base + kOffSFK + st * kSfBytes;
+#pragma unroll
+          for (int ks = 0; ks < 2; ++ks) tc_cp_sf(sfk + 4 * ks, ksf + 512 * ks);
+#pragma unroll
+          for (int ks = 0; ks < 2; ++ks) {
+            mma_nvf4(tmem + kDTmS + 16 * buf, make_desc_sw64(kt + 32 * ks), dq[ks], idesc, sfk + 4 * ks,
+                     tmem + kDTmSFQ + 4 * ks, ks > 0 ? 1u : 0u);
+          }
+          tc_commit(bars.at(Bars::kSFull + buf));
+          tc_commit(bars.at(Bars::kKFree + st));
+        }
+        if (step >= 2) {
+          // O^T += V^T . P^T of block step - 2
+          const uint32_t li = step - 2, st = li % kStages, slot = li % kPSlots;
+          ok = mbar_wait(bars.at(Bars::kVFull + st), (li / kStages) & 1, wc, kDVFull);
+          if (!ok) break;
+          ok = mbar_wait(bars.at(Bars::kPFull + slot), (li / kPSlots) & 1, wc, kDPFull);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t sfv = tmem + kDTmSFV + 8 * st, sfp = tmem + kDTmSFP + 8 * slot;
+          const uint32_t vt = base + kOffV + st * kTileBytes, vsf = base + kOffSFV + st * kSfBytes;
+          const uint32_t pt = base + kOffP + slot * 1024, psf = base + kOffSFP + slot * 1024;
+#pragma unroll
+          for (int ks = 0; ks < 2; ++ks) {
+            tc_cp_sf(sfv + 4 * ks, vsf + 512 * ks);
+            tc_cp_sf(sfp + 4 * ks, psf + 512 * ks);
+          }
+#pragma unroll
+          for (int ks = 0; ks < 2; ++ks) {
+            mma_nvf4(tmem + kDTmO, make_desc_sw64(vt + 32 * ks), make_desc_sw64(pt + 32 * ks), idesc,
+                     sfv + 4 * ks, sfp + 4 * ks, (li > 0 || ks > 0) ? 1u : 0u);
+          }
+          tc_commit(bars.at(Bars::kPvDone + slot));
+          tc_commit(bars.at(Bars::kVFree + st));
+        }
+      }
+      if (!ok) {
+        const uint64_t t0 = globaltimer_ns();
+        tc_commit(bars.at(Bars::kDrain));
+        while (!mbar_try_wait(bars.at(Bars::kDrain), 0) && globaltimer_ns() - t0 < 50ull * 1000 * 1000) {}
+      }
+    }
+  } else {
+    // ============================================ softmax / epilogue warpgroup ==================
+    const uint32_t lane_addr = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+    uint32_t sync_phase = 0;
+    // rendezvous of the 128 threads on an mbarrier (bounded, unlike bar.sync)
+#define FA4_DEC_SYNC()                                                                          \
+  mbar_arrive(bars.at(Bars::kSync));                                                            \
+  ok = __all_sync(0xffffffffu, mbar_wait(bars.at(Bars::kSync), sync_phase & 1, wc, kDSync));     \
+  sync_phase += 1;
+
+    // ---- set-up: Q^T operand (16 rows x 64 bytes, rows past R zero), its scale chunks, zeroed
+    //      P^T tiles and scale chunks (rows past R are never written again)
+    for (uint32_t i = tid; i < (kPSlots * 2048u + 2048u) / 16; i += 128) {
+      *reinterpret_cast<uint4*>(gbase + kOffQ + i * 16) = make_uint4(0u, 0u, 0u, 0u);  // Q, SFQ, P, SFP are contiguous
+    }
+    ok = true;
+    FA4_DEC_SYNC()
+    if (ok && tid < 64) {
+      const int r = tid >> 2, ch = tid & 3;
+      if (r < R) {
+        const int s = r / p.group, h = hk * p.group + r % p.group;
+        const uint4 v = *reinterpret_cast<const uint4*>(d.q + b * d.q_stride_b + s * d.q_stride_s +
+                                                        h * d.q_stride_h + ch * 16);
+        *reinterpret_cast<uint4*>(gbase + kOffQ + sw64_offset(r, ch)) = v;
+      }
+    } else if (ok && tid < 64 + 32) {
+      // scale bytes of row r: two words (one per 64-element step) of the tiled layout
+      const int r = (tid - 64) >> 1, ks = tid & 1;
+      if (r < R) {
+        const int s = r / p.group, h = hk * p.group + r % p.group;
+        const uint8_t* chunk = d.q_sf + b * p.qsf_stride_b + h * p.qsf_stride_h +
+                               ((int64_t)(s / 128) * 2 + ks) * 512;
+        const int rr = s % 128;
+        const uint32_t w = *reinterpret_cast<const uint32_t*>(chunk + (rr % 32) * 16 + (rr / 32) * 4);
+        *reinterpret_cast<uint32_t*>(gbase + kOffSFQ + 512 * ks + r * 16) = w;
+      }
+    }
+    fence_proxy_async_smem();
+    mbar_arrive(bars.at(Bars::kQReady));
+
+    float m_ref[kR], l_sum[kR];
+#pragma unroll
+    for (int r = 0; r < kR; ++r) {
+      m_ref[r] = kNegInf;
+      l_sum[r] = 0.f;
+    }
+    // last visible key of row r (causal: bottom-right aligned on the entry's key count); rows past
+    // R see nothing.  Also the output coordinates of the rows, fixed for the whole CTA.
+    int lim[kR], row_s[kR], row_h[kR];
+#pragma unroll
+    for (int r = 0; r < kR; ++r) {
+      row_s[r] = r / p.group;
+      row_h[r] = hk * p.group + r % p.group;
+      const int c = sk - p.Sq + row_s[r];
+      lim[r] = (r < R) ? ((p.causal && c < sk - 1) ? c : sk - 1) : -1;
+    }
+
+    for (int li = 0; ok && li < n; ++li) {
+      const int nb = i0 + li;
+      const uint32_t buf = li % kSBufs, slot = li % kPSlots;
+      ok = __all_sync(0xffffffffu, mbar_wait(bars.at(Bars::kSFull + buf), (li / kSBufs) & 1, wc, kDSFull));
+      if (!ok) break;
+      tc_fence_after_sync();
+      float s16[16];
+      tmem_ld16(lane_addr + kDTmS + 16 * buf, reinterpret_cast<uint32_t*>(s16));
+      tc_wait_ld();
+      float s[kR];
+#pragma unroll
+      for (int r = 0; r < kR; ++r) s[r] = s16[r];
+      tc_fence_before_sync();
+      mbar_arrive(bars.at(Bars::kSFree + buf));
+
+      // mask: this thread's key against every row's limit; rows past R count as fully masked
+      const int key = nb * kBlockN + tid;
+      float wmax[kR];
+#pragma unroll
+      for (int r = 0; r < kR; ++r) {
+        s[r] = (key <= lim[r]) ? s[r] : kNegInf;
+        float m = s[r];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        wmax[r] = m;
+      }
+      volatile float* red = s_red + (li & 1) * 64;
+      if (lane < kR) {
+        float mine = wmax[0];
+#pragma unroll
+        for (int r = 1; r < kR; ++r) mine = (lane == r) ? wmax[r] : mine;
+        red[warp * 16 + lane] = mine;
+      }
+      FA4_DEC_SYNC()
+      if (!ok) break;
+
+      // reference maxima (every thread keeps all rows: the values are CTA-uniform)
+      bool moved = false;
+      float fac[kR];
+#pragma unroll
+      for (int r = 0; r < kR; ++r) {
+        const float m_loc = fmaxf(fmaxf(red[r], red[16 + r]), fmaxf(red[32 + r], red[48 + r]));
+        const float m_new = next_reference(m_ref[r], m_loc, p.sl2);
+        fac[r] = 1.f;
+        if (m_new != m_ref[r]) {
+          fac[r] = reference_factor(m_ref[r], m_new, p.sl2);
+          moved = moved || (m_ref[r] != kNegInf);
+          l_sum[r] *= fac[r];
+          m_ref[r] = m_new;
+        }
+      }
+
+      // P slot free once P V of block li - kPSlots has run
+      if (li >= kPSlots) {
+        ok = __all_sync(0xffffffffu, mbar_wait(bars.at(Bars::kPvDone + slot), ((li - kPSlots) / kPSlots) & 1, wc,
+                                               kDPvDone));
+        if (!ok) break;
+      }
+      uint8_t* p_tile = gbase + kOffP + slot * 1024;
+      uint8_t* p_sf = gbase + kOffSFP + slot * 1024;
+      const int blk = tid >> 4;  // 16-key block of this thread inside the 128 keys
+#pragma unroll
+      for (int r = 0; r < kR; ++r) {
+        if (r < R) {  // R is CTA-uniform
+          float bm = s[r];
+#pragma unroll
+          for (int o = 8; o > 0; o >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, o));
+          float noff;
+          uint32_t ue;
+          block_exponent1(bm, m_ref[r], p.sl2, noff, ue);
+          const float pv = ex2_approx(fmaf(s[r], p.sl2, noff));
+          l_sum[r] = fmaf(pv, __uint_as_float(ue << 23), l_sum[r]);
+          const float other = __shfl_xor_sync(0xffffffffu, pv, 1);
+          if ((tid & 1) == 0) {
+            const uint32_t col = tid >> 1;  // byte of the 64-byte row: keys 2 col, 2 col + 1
+            p_tile[sw64_offset(r, col >> 4) + (col & 15)] = static_cast<uint8_t>(pack2_e2m1(pv, other));
+          }
+          if ((tid & 15) == 0) {
+            p_sf[512 * (blk >> 2) + r * 16 + (blk & 3)] = static_cast<uint8_t>((ue - 0x78u) << 3);
+          }
+        }
+      }
+
+      // correction (rare): O^T holds the earlier blocks relative to the old references
+      if (li > 0 && moved) {
+        ok = __all_sync(0xffffffffu, mbar_wait(bars.at(Bars::kPvDone + ((li - 1) % kPSlots)),
+                                               ((li - 1) / kPSlots) & 1, wc, kDPvDone));
+        if (!ok) break;
+        tc_fence_after_sync();
+        float o[16];
+        tmem_ld16(lane_addr + kDTmO, reinterpret_cast<uint32_t*>(o));
+        tc_wait_ld();
+#pragma unroll
+        for (int r = 0; r < kR; ++r) o[r] *= fac[r];
+        tmem_st16(lane_addr + kDTmO, reinterpret_cast<const uint32_t*>(o));
+        tc_wait_st();
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(bars.at(Bars::kPFull + slot));
+    }
+
+    // ---- epilogue: row sums over the 128 key lanes, then thread = dv lane of O^T --------------
+    if (ok) {
+      volatile float* red = s_red + (n & 1) * 64;
+      float wsum[kR];
+#pragma unroll
+      for (int r = 0; r < kR; ++r) {
+        float v = l_sum[r];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        wsum[r] = v;
+      }
+      if (lane < kR) {
+        float mine = wsum[0];
+#pragma unroll
+        for (int r = 1; r < kR; ++r) mine = (lane == r) ? wsum[r] : mine;
+        red[warp * 16 + lane] = mine;
+      }
+      FA4_DEC_SYNC()
+    }
+    if (ok) {
+      volatile float* red = s_red + (n & 1) * 64;
+      float o[16];
+#pragma unroll
+      for (int r = 0; r < 16; ++r) o[r] = 0.f;
+      if (n > 0) {
+        ok = __all_sync(0xffffffffu, mbar_wait(bars.at(Bars::kPvDone + ((n - 1) % kPSlots)),
+                                               ((n - 1) / kPSlots) & 1, wc, kDPvDone));
+        if (ok) {
+          tc_fence_after_sync();
+          tmem_ld16(lane_addr + kDTmO, reinterpret_cast<uint32_t*>(o));
+          tc_wait_ld();
+        }
+      }
+      if (ok) {
+#pragma unroll
+        for (int r = 0; r < kR; ++r) {
+          if (r < R) {
+            // fixed order over the four warps: the sum of a row does not depend on timing
+            const float l_tot = ((red[r] + red[16 + r]) + red[32 + r]) + red[48 + r];
+            const int s = row_s[r], h = row_h[r];
+            const float scale = (l_tot > 0.f && n > 0) ? p.out_scale / l_tot : 0.f;
+            d.o_partial[((((int64_t)split * p.B + b) * p.Sq + s) * p.Hq + h) * 128 + tid] = o[r] * scale;
+            if (tid == r) {
+              d.lse_partial[(((int64_t)split * p.B + b) * p.Hq + h) * p.Sq + s] =
+                  finish_lse(m_ref[r], l_tot, p.sl2);
+            }
+          }
+        }
+      }
+    }
+#undef FA4_DEC_SYNC
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 5) tmem_dealloc(tmem, dec::kDTmemCols);
+}
+
+}  // namespace fa4

@@ -26,7 +26,7 @@ import torch
 from . import _lib
 from .quant import NVFP4Tensor, sf_to_tiled
 
-VARIANT_AUTO, VARIANT_SERIAL, VARIANT_WS, VARIANT_WS64 = 0, 1, 2, 3
+VARIANT_AUTO, VARIANT_SERIAL, VARIANT_WS, VARIANT_WS64, VARIANT_DECODE = 0, 1, 2, 3, 4
 
 
 def _validate_tensor(t, name, expected_shape, expected_dtype, expected_device):
@@ -109,7 +109,10 @@ def flash_attn_fp4_func(
 
     ``num_splits``: 1 = one pass over K/V per query tile; k > 1 = split-KV with a combine kernel
     (the reference's ``num_splits``, interface.py:494-510), for short Sq against long Sk;
-    0 = choose (split only when the query tiles alone leave most SMs idle).
+    0 = choose (split only when the query tiles alone leave most SMs idle).  Decode and append
+    shapes (D = Dv = 128, Sq * Hq / Hkv <= 16, no window / sink / softcap) run the transposed
+    decode kernel (``VARIANT_DECODE``: keys on the tile's lanes, grid = splits x Hkv x B); there
+    ``num_splits=0`` is what a serving loop wants (about two CTAs per SM).
 
     ``window_size=(left, right)``: local attention, query row i sees keys
     ``i + Sk - Sq - left <= j <= i + Sk - Sq + right`` (``None`` = unlimited; ``causal`` is
@@ -221,10 +224,24 @@ def flash_attn_fp4_func(
     p.wait_budget_ns = 0
     if num_splits < 0 or num_splits > 128:
         raise ValueError("num_splits must be in 0..128")
-    if num_splits == 0:
+    auto_splits = num_splits == 0
+    if auto_splits:
         num_splits = choose_num_splits(B, Sq, Sk, Hq, causal, device)
     causal, win_left, win_right = resolve_window(causal, window_size)
     p.causal = 1 if causal else 0
+    # A handful of query rows per kv head (decode, append): the transposed kernel, which always
+    # splits the keys over CTAs and merges with the combine kernel.
+    decode_ok = (D == 128 and Dv == 128 and Sq * (Hq // Hkv) <= 16 and win_left is None
+                 and (win_right is None or win_right == 0) and learnable_sink is None and not softcap)
+    if variant == VARIANT_DECODE and not decode_ok:
+        raise NotImplementedError("the decode kernel takes D = Dv = 128, Sq * (Hq / Hkv) <= 16, no window / "
+                                  "sink / softcap")
+    if variant == VARIANT_AUTO and decode_ok:
+        variant = VARIANT_DECODE
+    if variant == VARIANT_DECODE:
+        p.variant = VARIANT_DECODE
+        if auto_splits:
+            num_splits = choose_decode_splits(B, Hkv, Sk, device)
     with torch.cuda.device(device):
         stream = torch.cuda.current_stream(device).cuda_stream
         sink = None
@@ -235,7 +252,7 @@ def flash_attn_fp4_func(
         if softcap < 0.0 or not math.isfinite(softcap):
             raise ValueError("softcap must be a finite number >= 0")
         if (num_splits == 1 and sink is None and win_left is None and (win_right is None or win_right == 0)
-                and softcap == 0.0 and seqused_k is None and not paged):
+                and softcap == 0.0 and seqused_k is None and not paged and variant != VARIANT_DECODE):
             rc = _lib.lib().fa4_nvfp4_fwd(ctypes.byref(p), stream)
             what = "fa4_nvfp4_fwd"
         else:
@@ -251,8 +268,8 @@ def flash_attn_fp4_func(
             if paged:
                 x.page_size, x.pages_per_seq, x.num_pages = page_size, pages_per_seq, num_pages
             workspace = None
-            if num_splits > 1:
-                nbytes = _lib.lib().fa4_nvfp4_splitkv_workspace_bytes(ctypes.byref(p), num_splits)
+            if num_splits > 1 or variant == VARIANT_DECODE:
+                nbytes = _lib.lib().fa4_nvfp4_splitkv_workspace_bytes(ctypes.byref(p), max(2, num_splits))
                 if nbytes < 0:
                     _lib.check(int(nbytes), "fa4_nvfp4_splitkv_workspace_bytes")
                 workspace = torch.empty(nbytes, dtype=torch.uint8, device=device)   # stream-ordered scratch
@@ -261,6 +278,15 @@ def flash_attn_fp4_func(
             what = "fa4_nvfp4_fwd_ex"
     _lib.check(rc, what)
     return out, lse
+
+
+def choose_decode_splits(B: int, Hkv: int, Sk: int, device=None) -> int:
+    """Key splits of the decode kernel (grid = splits x Hkv x B, two CTAs fit an SM): enough CTAs for
+    about two per SM, at least two 128-key blocks per split."""
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    blocks = (Sk + 127) // 128
+    want = (2 * sms) // max(1, B * Hkv)          # rounded down: a second, nearly empty wave doubles the time
+    return max(1, min(128, want, max(1, blocks // 2)))
 
 
 def resolve_window(causal: bool, window_size) -> Tuple[bool, Optional[int], Optional[int]]:

@@ -74,9 +74,14 @@ enum {
   FA4_VARIANT_SERIAL = 1, /* one warpgroup does every step in turn (bring-up / cross-check) */
   FA4_VARIANT_WS = 2,     /* warp-specialised pipeline, steps of 128 keys from the last visible
                              block down; every feature, D = 128 and 64 */
-  FA4_VARIANT_WS64 = 3    /* warp-specialised pipeline, steps of 64 keys upwards, four score
+  FA4_VARIANT_WS64 = 3,   /* warp-specialised pipeline, steps of 64 keys upwards, four score
                              buffers, separate epilogue warpgroup; no split / window / sink
                              (-FA4_E_SHAPE otherwise) */
+  FA4_VARIANT_DECODE = 4  /* transposed products for a handful of query rows: keys on the tile's
+                             lanes, the Sq * (Hq / Hkv) <= 16 query rows of a kv head on the N
+                             side; D = Dv = 128, causal or unmasked, seqused_k / page_table allowed;
+                             through fa4_nvfp4_fwd_ex with num_splits >= 1 and the split-KV
+                             workspace (grid = splits x Hkv x B) */
 };
 
 typedef struct fa4_nvfp4_params {

@@ -38,11 +38,16 @@ def make_qkv(B, Sq, Sk, Hq, Hkv, D, seed, v_std=1.0, outlier_frac=0.0, device="c
     return tuple(t.bfloat16().to(device) for t in (q, k, v))
 
 
-def kernel_model(D, num_splits=1, window=(None, None), sink=None, variant=0, softcap=0.0):
+def kernel_model(D, num_splits=1, window=(None, None), sink=None, variant=0, softcap=0.0, rows=None):
     """Which kernel the library's automatic choice runs, as oracle B keywords: the 64-key kernel
     without split / window / sink, the 128-key kernel otherwise (mirrors
     launch_fwd in csrc/api.cu).  ``variant`` 1 / 2 force the 128-key model, 3 the 64-key one."""
     plain = num_splits == 1 and window == (None, None) and sink is None and not softcap
+    # decode / append shapes: the transposed kernel, 128-key steps upwards, any number of splits
+    decode_ok = (D == 128 and rows is not None and rows <= 16 and window in ((None, None), (None, 0))
+                 and sink is None and not softcap)
+    if variant == 4 or (variant == 0 and decode_ok):
+        return {"step_keys": 128, "ascending": True}
     if variant == 3 or (variant == 0 and plain):
         return {"step_keys": 64, "ascending": True}
     return {"step_keys": 128, "ascending": False}
@@ -67,7 +72,10 @@ def oracles(Q, K, V, causal, softmax_scale=None, num_splits=1, window=(None, Non
         sl2 = float(torch.tensor(softcap, dtype=torch.float32) * torch.tensor(LOG2E, dtype=torch.float32))
     ob, lb = orc.attention_oracle_b(qd / Q.scale, kd / K.scale, vd / V.scale, sl2, V.scale, causal=causal,
                                     num_splits=num_splits, window=window, sink=sink,
-                                    softcap_c1=c1, **kernel_model(D, num_splits, window, sink, variant, softcap))
+                                    softcap_c1=c1,
+                                    **kernel_model(D, num_splits, window, sink, variant, softcap,
+                                                   rows=qd.shape[1] * (qd.shape[2] // kd.shape[2])
+                                                   if vd.shape[-1] == D else None))
     return oa, la, ob, lb
 
 

@@ -389,7 +389,7 @@ def test_split_kv_parity(cuda_device, case):
     Q, K, V = fa.quantize_qkv(q, k, v)
     out, lse = run(Q, K, V, causal, fa.VARIANT_WS, num_splits=splits)
     assert out.shape == (B, Sq, Hq, D) and lse.shape == (B, Hq, Sq)
-    assert_parity(out, lse, *oracles(Q, K, V, causal, num_splits=splits))
+    assert_parity(out, lse, *oracles(Q, K, V, causal, num_splits=splits, variant=fa.VARIANT_WS))
     # the un-split result agrees to within the 4-bit P noise of two different groupings
     out1, lse1 = run(Q, K, V, causal, fa.VARIANT_WS)
     fin = torch.isfinite(lse1)
@@ -407,8 +407,15 @@ def test_split_kv_heuristic_and_surface(cuda_device):
     assert 8 <= n <= 64
     q, k, v = make_qkv(1, 4, 4096, 8, 2, 128, seed=1, device=cuda_device)
     Q, K, V = fa.quantize_qkv(q, k, v)
+    # 4 rows x 4 query heads per kv head = 16 rows: the automatic choice is the decode kernel
     o0, l0 = fa.flash_attn_func(Q, K, V, causal=True, return_lse=True, num_splits=0)
-    assert_parity(o0, l0, *oracles(Q, K, V, True, num_splits=fa.interface.choose_num_splits(1, 4, 4096, 8, True, cuda_device)))
+    n_dec = fa.interface.choose_decode_splits(1, 2, 4096, cuda_device)
+    assert 2 <= n_dec <= 16
+    assert_parity(o0, l0, *oracles(Q, K, V, True, num_splits=n_dec))
+    # the prefill kernel's split heuristic, on the same problem
+    o1, l1 = run(Q, K, V, True, fa.VARIANT_WS, num_splits=0)
+    assert_parity(o1, l1, *oracles(Q, K, V, True, variant=fa.VARIANT_WS,
+                                   num_splits=fa.interface.choose_num_splits(1, 4, 4096, 8, True, cuda_device)))
 
 
 CASES_WINDOW = [
@@ -490,6 +497,47 @@ def test_softcap_parity(cuda_device, case):
 
 
 @pytest.mark.parametrize("case", [
+    # name, B, Sq, Sk, Hq, Hkv, causal, splits (0 = chosen)
+    ("one_row_gqa4", 2, 1, 1024, 8, 2, True, 2),
+    ("one_row_mqa_ragged_keys", 1, 1, 160, 2, 1, True, 1),
+    ("four_rows_three_splits", 1, 4, 640, 4, 2, True, 3),
+    ("two_rows_noncausal", 2, 2, 384, 8, 2, False, 1),
+    ("sixteen_rows_mha", 1, 16, 512, 2, 2, True, 2),
+    ("eight_rows_more_splits_than_blocks", 1, 2, 256, 8, 2, True, 5),
+    ("one_row_chosen_splits", 3, 1, 4096, 8, 2, True, 0),
+], ids=lambda c: c[0])
+def test_decode_kernel_parity(cuda_device, case):
+    """The transposed decode kernel (keys on the lanes, the Sq * Hq / Hkv <= 16 query rows of a kv
+    head on the N side), which the automatic choice runs for these shapes: against the oracle's
+    model of it (128-key steps upwards, contiguous shares of the blocks per split) at the usual
+    tolerances, and deterministic."""
+    _, B, Sq, Sk, Hq, Hkv, causal, splits = case
+    q, k, v = make_qkv(B, Sq, Sk, Hq, Hkv, 128, seed=13, device=cuda_device)
+    Q, K, V = fa.quantize_qkv(q, k, v)
+    out, lse = run(Q, K, V, causal, num_splits=splits)
+    n = splits if splits else fa.interface.choose_decode_splits(B, Hkv, Sk, cuda_device)
+    assert_parity(out, lse, *oracles(Q, K, V, causal, num_splits=n))
+    out2, lse2 = run(Q, K, V, causal, fa.VARIANT_DECODE, num_splits=splits)
+    assert torch.equal(out, out2) and torch.equal(lse, lse2)
+    # the prefill kernel on the same problem: another grouping of the same 4-bit P
+    out_w, lse_w = run(Q, K, V, causal, fa.VARIANT_WS)
+    assert (lse - lse_w).abs().max().item() < 1e-3
+    assert orc.error_metrics(out.float(), out_w.float())["rel_rms"] < 0.25
+
+
+def test_decode_kernel_refuses_other_shapes(cuda_device):
+    q, k, v = make_qkv(1, 17, 256, 2, 2, 128, seed=1, device=cuda_device)
+    Q, K, V = fa.quantize_qkv(q, k, v)
+    with pytest.raises(NotImplementedError):
+        run(Q, K, V, True, fa.VARIANT_DECODE)                      # 17 rows
+    q, k, v = make_qkv(1, 2, 256, 2, 2, 128, seed=1, device=cuda_device)
+    Q, K, V = fa.quantize_qkv(q, k, v)
+    for kw in ({"window_size": (64, 0)}, {"softcap": 2.0}, {"learnable_sink": torch.zeros(2)}):
+        with pytest.raises(NotImplementedError):
+            run(Q, K, V, True, fa.VARIANT_DECODE, **kw)
+
+
+@pytest.mark.parametrize("case", [
     # name, Sq, page_size, pages_per_seq, seqused, D, causal, splits
     ("decode_one_row", 1, 128, 5, [208, 640, 48], 128, True, 1),
     ("append_17_rows_split", 17, 256, 3, [768, 304, 17 + 15], 128, True, 2),
@@ -506,6 +554,8 @@ def test_kv_cache_seqused_and_page_table(cuda_device, case):
     q, k, v = make_qkv(B, Sq, Sk, Hq, Hkv, D, seed=41, device=cuda_device)
     Q, K, V = fa.quantize_qkv(q, k, v)
     su = torch.tensor(used, dtype=torch.int32, device=cuda_device)
+    # what the automatic choice runs for this shape: the decode kernel for a handful of rows
+    model = fa.VARIANT_DECODE if (D == 128 and Sq * (Hq // Hkv) <= 16) else fa.VARIANT_WS
     out, lse = run(Q, K, V, causal, seqused_k=su, num_splits=splits)
     for b, sk in enumerate(used):
         if sk == 0:
@@ -514,7 +564,7 @@ def test_kv_cache_seqused_and_page_table(cuda_device, case):
         Qb = fa.NVFP4Tensor(Q.data[b:b + 1], Q.sf[b:b + 1], Q.scale)
         Kb = fa.NVFP4Tensor(K.data[b:b + 1, :sk], K.sf[b:b + 1, :sk], K.scale)
         Vb = fa.NVFP4Tensor(V.data[b:b + 1, :, :, :sk // 2], V.sf[b:b + 1, :, :, :sk // 16], V.scale, is_v=True)
-        assert_parity(out[b:b + 1], lse[b:b + 1], *oracles(Qb, Kb, Vb, causal, num_splits=splits, variant=fa.VARIANT_WS))
+        assert_parity(out[b:b + 1], lse[b:b + 1], *oracles(Qb, Kb, Vb, causal, num_splits=splits, variant=model))
     # the same through a page pool: pages of all entries shuffled among three spare pages whose
     # packed bytes are noise (their scale bytes stay zero: no NaN encodings)
     g = torch.Generator(device="cpu").manual_seed(7)
@@ -540,7 +590,7 @@ def test_kv_cache_seqused_and_page_table(cuda_device, case):
     # a table without seqused_k: every entry sees the whole logical length
     out_f, lse_f = fa.flash_attn_fp4_func(Q.data, kp, vp, Q.sf, ksp, vsp, Q.scale, K.scale, V.scale, causal=causal,
                                           return_lse=True, page_table=table)
-    want_f, want_l = run(Q, K, V, causal, fa.VARIANT_WS)
+    want_f, want_l = run(Q, K, V, causal, model)
     torch.cuda.synchronize()
     assert torch.equal(out_f, want_f) and torch.equal(lse_f, want_l)
     with pytest.raises(NotImplementedError):
