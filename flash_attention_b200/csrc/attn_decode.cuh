@@ -32,9 +32,11 @@ namespace fa4 {
 namespace dec {
 
 constexpr int kThreads = 192;
-constexpr int kStages = 4;   // K and V tiles in flight
-constexpr int kSBufs = 4;    // S^T buffers (16 columns each)
-constexpr int kPSlots = 4;   // P^T tiles (16 rows x 64 bytes) and their scale chunks
+// Three of everything: 65 KB of shared memory and 128 tensor-memory columns per CTA, so that THREE
+// CTAs share an SM -- the softmax chain of a block is latency-bound and one CTA has one in flight.
+constexpr int kStages = 3;   // K and V tiles in flight
+constexpr int kSBufs = 3;    // S^T buffers (16 columns each)
+constexpr int kPSlots = 3;   // P^T tiles (16 rows x 64 bytes) and their scale chunks
 constexpr int kMaxRows = 16; // query rows per kv head: Sq * group
 
 // shared memory
@@ -61,10 +63,12 @@ struct Bars {
 constexpr uint32_t kOffMisc = kOffBar + 8 * Bars::kCount;
 constexpr uint32_t kSmemRequest = kOffMisc + 16 + 1024;
 
-// tensor memory (256 columns allocated): S^T buffers, O^T, scale factors
-constexpr uint32_t kDTmemCols = 256;
-constexpr uint32_t kDTmS = 0, kDTmO = 64, kDTmSFQ = 80, kDTmSFK = 88 /* 4 x 8 */, kDTmSFV = 120 /* 4 x 8 */,
-                   kDTmSFP = 152 /* 4 x 8 */;
+// tensor memory (128 columns allocated): S^T buffers, O^T, scale factors.  The K / V / P scale
+// slots alternate between two copies: the copy and the product that reads it are issued by one
+// thread to the in-order tensor pipe, the second copy keeps a copy from racing the product before.
+constexpr uint32_t kDTmemCols = 128;
+constexpr uint32_t kDTmS = 0 /* 3 x 16 */, kDTmO = 48, kDTmSFQ = 64, kDTmSFK = 72 /* 2 x 8 */,
+                   kDTmSFV = 88 /* 2 x 8 */, kDTmSFP = 104 /* 2 x 8 */;
 
 enum Site { kDKFull = 80, kDVFull, kDKFree, kDVFree, kDSFull, kDSFree, kDPFull, kDPvDone, kDQReady, kDSync };
 
@@ -131,7 +135,7 @@ struct DecodeParams {
 // fully unrolled, and sixteen rows of them no longer fit the instruction cache (measured: 10 000
 // clocks per block, instruction-fetch bound), so the common decode shapes get the short forms.
 template <int kR>
-__global__ void __launch_bounds__(dec::kThreads, 1)
+__global__ void __launch_bounds__(dec::kThreads, 3)
 attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                    const KernelParams p, const DecodeParams d) {
   using namespace dec;
@@ -262,7 +266,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
             if (!ok) break;
           }
           tc_fence_after_sync();
-          const uint32_t sfk = tmem + kDTmSFK + 8 * st;
+          const uint32_t sfk = tmem + kDTmSFK + 8 * (li & 1);
           const uint32_t kt = base + kOffK + st * kTileBytes, ksf = base + kOffSFK + st * kSfBytes;
 #pragma unroll
           for (int ks = 0; ks < 2; ++ks) tc_cp_sf(sfk + 4 * ks, ksf + 512 * ks);
@@ -282,7 +286,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
           ok = mbar_wait(bars.at(Bars::kPFull + slot), (li / kPSlots) & 1, wc, kDPFull);
           if (!ok) break;
           tc_fence_after_sync();
-          const uint32_t sfv = tmem + kDTmSFV + 8 * st, sfp = tmem + kDTmSFP + 8 * slot;
+          const uint32_t sfv = tmem + kDTmSFV + 8 * (li & 1), sfp = tmem + kDTmSFP + 8 * (li & 1);
           const uint32_t vt = base + kOffV + st * kTileBytes, vsf = base + kOffSFV + st * kSfBytes;
           const uint32_t pt = base + kOffP + slot * 1024, psf = base + kOffSFP + slot * 1024;
 #pragma unroll

@@ -281,11 +281,11 @@ def flash_attn_fp4_func(
 
 
 def choose_decode_splits(B: int, Hkv: int, Sk: int, device=None) -> int:
-    """Key splits of the decode kernel (grid = splits x Hkv x B, two CTAs fit an SM): enough CTAs for
-    about two per SM, at least two 128-key blocks per split."""
+    """Key splits of the decode kernel (grid = splits x Hkv x B, three CTAs fit an SM): enough CTAs for
+    about three per SM, at least two 128-key blocks per split."""
     sms = torch.cuda.get_device_properties(device).multi_processor_count
     blocks = (Sk + 127) // 128
-    want = (2 * sms) // max(1, B * Hkv)          # rounded down: a second, nearly empty wave doubles the time
+    want = (3 * sms) // max(1, B * Hkv)          # rounded down: a second, nearly empty wave doubles the time
     return max(1, min(128, want, max(1, blocks // 2)))
 
 
