@@ -423,6 +423,62 @@ def run_sweep(args):
                       "gpu_launches": steps * len(rows), "sweep": rows}), flush=True)
 
 
+def run_decode(args):
+    """Decode shapes (one query token per sequence against a long NVFP4 KV cache, GQA 4): the
+    transposed decode kernel with chosen key splits beside the prefill kernel's split-KV path.
+    HBM-bound work: the figure of merit is bytes of K, V and their scales per second."""
+    import flash_attention_b200 as fa
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks = measured_peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    steps = max(3, min(args.steps, 20))
+    rows = []
+    for (B, Sk) in ((4, 32768), (1, 131072), (8, 8192), (64, 4096)):
+        Hq, Hkv, D = 32, 8, 128
+        g = torch.Generator(device=dev).manual_seed(11)
+        q = torch.randn(B, 1, Hq, D, generator=g, device=dev, dtype=torch.bfloat16)
+        k = torch.randn(B, Sk, Hkv, D, generator=g, device=dev, dtype=torch.bfloat16)
+        v = torch.randn(B, Sk, Hkv, D, generator=g, device=dev, dtype=torch.bfloat16)
+        Q, K, V = fa.quantize_qkv_fused(q, k, v, linear_sf=False)
+        del q, k, v
+        kv_bytes = 2 * B * Hkv * Sk * (D // 2 + D // 16)
+        row = {"B": B, "Sk": Sk, "Hq": Hq, "Hkv": Hkv, "kv_bytes": kv_bytes,
+               "splits": fa.interface.choose_decode_splits(B, Hkv, Sk, dev)}
+        for name, variant in (("decode", fa.VARIANT_DECODE), ("prefill_splitkv", fa.VARIANT_WS)):
+            def step():
+                fa.flash_attn_fp4_func(Q.data, K.data, V.data, Q.sf, K.sf, V.sf, Q.scale, K.scale, V.scale,
+                                       causal=True, return_lse=True, sf_layout="tiled", variant=variant,
+                                       num_splits=0)
+            for _ in range(3):
+                step()
+            torch.cuda.synchronize()
+            ms = 0.0
+            for _ in range(steps):
+                flush.zero_()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(); step(); e1.record(); e1.synchronize()
+                ms += e0.elapsed_time(e1)
+            ms /= steps
+            fa.check_status(dev)
+            row[name] = {"us": ms * 1e3, "kv_gbs": kv_bytes / ms / 1e6,
+                         "frac_of_hbm_peak": kv_bytes / ms / 1e6 / peaks["hbm_gbs"]}
+        rows.append(row)
+        del Q, K, V
+    head = rows[0]
+    print(json.dumps({"metric": "nvfp4_decode_kv_gbs", "value": head["decode"]["kv_gbs"], "unit": "GB/s",
+                      "n_gpus": 1, "steps": steps, "warmup": 3, "ms_per_step": head["decode"]["us"] / 1e3,
+                      "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4",
+                      "data": "synthetic",
+                      "config": {"workload": "decode: Sq = 1, Hq = 32, Hkv = 8, D = 128, causal, (B, Sk) in "
+                                             "{(4, 32768), (1, 131072), (8, 8192), (64, 4096)}; headline row "
+                                             "B = 4, Sk = 32768; one call = decode kernel + combine kernel",
+                                 "l2": "L2 flushed between timed calls (256 MiB write)"},
+                      "roofline": {"bound": "hbm", "achieved": head["decode"]["kv_gbs"], "peak": peaks["hbm_gbs"],
+                                   "unit": "GB/s", "frac": head["decode"]["frac_of_hbm_peak"], "traffic": None},
+                      "gpu_launches": 2 * steps * 2 * len(rows), "decode": rows}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -435,10 +491,10 @@ def main():
                     help="auto: the library's choice (the 64-key kernel for these workloads); ws128: force "
                          "the 128-key kernel that serves split-KV / windows / sinks")
     args = ap.parse_args()
-    if args.workload == "sweep":
+    if args.workload in ("sweep", "decode"):
         if not torch.cuda.is_available():
             raise SystemExit("bench.py needs a CUDA device (no CPU fallback)")
-        return run_sweep(args)
+        return run_sweep(args) if args.workload == "sweep" else run_decode(args)
     wl = parse_workload(args.workload)
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
