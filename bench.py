@@ -16,6 +16,11 @@ host -> device copies of the packed operands and linear scale factors, the scale
 kernels, the attention kernel, and the device -> host copy of O and LSE, all inside the timed
 region.  ``cpu_baseline`` / ``--impl reference`` time the CPU restatement of the reference's
 ``attention_ref`` (oracle/nvfp4_oracle.py) on a bounded sample of the same workload.
+
+``--workload sweep`` (head dims 64 / 128 / 192 x sequence lengths x causal) and ``--workload
+decode`` (one query token against a long KV cache: decode kernel beside the prefill kernel's
+split-KV path, GB/s of K/V) print one JSON line each with a table; ``--kernel ws128`` forces the
+128-key prefill kernel on the main workloads.
 """
 import argparse
 import datetime
