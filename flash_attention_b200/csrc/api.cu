@@ -352,9 +352,28 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
     const int64_t items = (int64_t)p->B * p->Sq * p->Hq * (p->Dv / 4);
     int64_t blocks = (items + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
-    combine_splits_kernel<<<(unsigned)blocks, 256, 0, stream>>>(
-        kp.o_partial, kp.lse_partial, kp.out, kp.lse, num_splits, p->B, p->Sq, p->Hq, p->Dv,
-        kp.o_stride_b, kp.o_stride_s, kp.o_stride_h);
+    if (decode) {
+      // programmatic dependent launch: the launch latency of the combine kernel overlaps the
+      // decode kernel (the combine CTAs wait on griddepcontrol.wait)
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3((unsigned)blocks);
+      cfg.blockDim = dim3(256);
+      cfg.dynamicSmemBytes = 0;
+      cfg.stream = stream;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[0].val.programmaticStreamSerializationAllowed = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      const cudaError_t le = cudaLaunchKernelEx(
+          &cfg, combine_splits_kernel, (const float*)kp.o_partial, (const float*)kp.lse_partial, kp.out, kp.lse,
+          num_splits, p->B, p->Sq, p->Hq, p->Dv, kp.o_stride_b, kp.o_stride_s, kp.o_stride_h);
+      if (le != cudaSuccess) return (int)le;
+    } else {
+      combine_splits_kernel<<<(unsigned)blocks, 256, 0, stream>>>(
+          kp.o_partial, kp.lse_partial, kp.out, kp.lse, num_splits, p->B, p->Sq, p->Hq, p->Dv,
+          kp.o_stride_b, kp.o_stride_s, kp.o_stride_h);
+    }
     e = cudaGetLastError();
   }
   return e == cudaSuccess ? 0 : (int)e;

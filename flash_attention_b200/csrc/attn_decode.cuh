@@ -193,6 +193,9 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
+  // the combine kernel is launched as a programmatic dependent: let its CTAs be scheduled while
+  // this grid still runs (they wait for its completion before they read the partials)
+  asm volatile("griddepcontrol.launch_dependents;");
   const uint32_t tmem = *tmem_slot;
   constexpr uint32_t idesc = make_idesc_nvf4(128, 16);
   bool ok = true;

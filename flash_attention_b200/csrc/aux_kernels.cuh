@@ -159,6 +159,10 @@ __global__ void combine_splits_kernel(const float* __restrict__ o_partial,
   const int per_row = Dv / 4;
   const int64_t rows = (int64_t)B * Sq * Hq;
   const int64_t split_o = rows * Dv, split_l = rows;
+  // When launched as a programmatic dependent of the kernel that writes the partials (decode
+  // path) the CTAs may start before that kernel has finished: wait for it here.  A plain launch
+  // returns from this at once.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < rows * per_row;
        idx += (int64_t)gridDim.x * blockDim.x) {
     const int c = (int)(idx % per_row);
