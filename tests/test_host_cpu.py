@@ -201,6 +201,30 @@ def test_split_heuristic_cost_model():
         assert I.choose_num_splits(1, 128, 512, 8, False, None) == 1        # too few blocks to split
 
 
+def test_decode_split_choice_and_oracle_model_selection():
+    """Host logic around the decode kernel: key splits fill the GPU in one wave (three CTAs per SM)
+    with at least two blocks per split, and the test helper picks the oracle model of the kernel
+    the library would run."""
+    from unittest import mock
+    import flash_attention_b200.interface as I
+    from tests.helpers import kernel_model
+
+    class Props:
+        multi_processor_count = 148
+    with mock.patch.object(torch.cuda, "get_device_properties", lambda d: Props):
+        assert I.choose_decode_splits(4, 8, 32768, None) == 13          # 416 CTAs <= 444 slots
+        assert I.choose_decode_splits(64, 8, 4096, None) == 1           # already 512 CTAs
+        assert I.choose_decode_splits(1, 1, 512, None) == 2             # at least two blocks per split
+        assert I.choose_decode_splits(1, 8, 1 << 20, None) == 55
+    assert kernel_model(128, rows=4) == {"step_keys": 128, "ascending": True}          # decode kernel
+    assert kernel_model(128, rows=4, num_splits=5) == {"step_keys": 128, "ascending": True}
+    assert kernel_model(128, rows=256) == {"step_keys": 64, "ascending": True}         # 64-key prefill kernel
+    assert kernel_model(64, rows=4) == {"step_keys": 64, "ascending": True}            # head dim 64: no decode kernel
+    assert kernel_model(128, rows=4, softcap=2.0) == {"step_keys": 128, "ascending": False}
+    assert kernel_model(128, rows=256, num_splits=2) == {"step_keys": 128, "ascending": False}
+    assert kernel_model(128, rows=4, variant=2) == {"step_keys": 128, "ascending": False}
+
+
 def test_oracle_split_model_matches_unsplit_statistics():
     from oracle import nvfp4_oracle as orc
     from tests.helpers import make_qkv, oracles
