@@ -368,9 +368,9 @@ def run_gpu_arm(args, wl, rank, local_rank, world):
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the attention kernel the
 # automatic choice runs (attn_fwd_ws64_kernel), from the ncu captures summarised under profiles/.
 # cfg2 was captured whole (121.2 MB read + 218.9 MB written); cfg1 is the capture of half of it
-# (B = 2: 68.0 MB + 42.3 MB) scaled by the batch, which the traffic is proportional to.  None for
+# (B = 2: 67.9 MB + 45.0 MB) scaled by the batch, which the traffic is proportional to.  None for
 # workloads that were not captured.
-TRAFFIC_BYTES = {"cfg2": 340_117_248, "cfg1": 2 * 110_339_584}
+TRAFFIC_BYTES = {"cfg2": 340_117_248, "cfg1": 2 * 112_986_112}
 
 
 def run_sweep(args):
