@@ -386,14 +386,17 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
 
       // mask: this thread's key against every row's limit; rows past R count as fully masked
       const int key = nb * kBlockN + tid;
-      float wmax[kR];
+      // maxima of this thread's 16-key block per row (four shuffle steps, kept for the P scales),
+      // then of the warp's 32 keys (one more)
+      float wmax[kR], bmax[kR];
 #pragma unroll
       for (int r = 0; r < kR; ++r) {
         s[r] = (key <= lim[r]) ? s[r] : kNegInf;
         float m = s[r];
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-        wmax[r] = m;
+        for (int o = 8; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        bmax[r] = m;
+        wmax[r] = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
       }
       volatile float* red = s_red + (li & 1) * 64;
       if (lane < kR) {
@@ -433,12 +436,9 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
 #pragma unroll
       for (int r = 0; r < kR; ++r) {
         if (r < R) {  // R is CTA-uniform
-          float bm = s[r];
-#pragma unroll
-          for (int o = 8; o > 0; o >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, o));
           float noff;
           uint32_t ue;
-          block_exponent1(bm, m_ref[r], p.sl2, noff, ue);
+          block_exponent1(bmax[r], m_ref[r], p.sl2, noff, ue);
           const float pv = ex2_approx(fmaf(s[r], p.sl2, noff));
           l_sum[r] = fmaf(pv, __uint_as_float(ue << 23), l_sum[r]);
           const float other = __shfl_xor_sync(0xffffffffu, pv, 1);
