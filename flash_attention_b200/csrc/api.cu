@@ -174,10 +174,10 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
   for (int64_t s : bstr)
     if (s <= 0 || (s & 15) != 0) return -FA4_E_STRIDE;
   if ((p->o_stride_b & 7) || (p->o_stride_s & 7) || (p->o_stride_h & 7)) return -FA4_E_STRIDE;
-  // automatic choice: the 64-key kernel where it applies (no split / window / sink), the 128-key
-  // kernel for everything else
+  // automatic choice: the 64-key kernel where it applies (no split-KV, no KV-cache view), the
+  // 128-key kernel for everything else
   const bool cached = cache.seqused_k != nullptr || cache.page_table != nullptr;
-  const bool plain = num_splits == 1 && win_left < 0 && win_right <= 0 && sink == nullptr && softcap == 0.f && !cached;
+  const bool plain = num_splits == 1 && !cached;   // what the 64-key kernel takes
   int variant = p->variant;
   if (variant == FA4_VARIANT_AUTO) variant = plain ? FA4_VARIANT_WS64 : FA4_VARIANT_WS;
   if (variant != FA4_VARIANT_SERIAL && variant != FA4_VARIANT_WS && variant != FA4_VARIANT_WS64 &&
@@ -337,8 +337,14 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
         kernel<<<grid, ws64::kThreads, ws64::kSmemRequest, stream>>>(tm_q, tm_k, tm_v, tm_o, kp);
         return 0;
       };
-      rc = p->D == 128 ? launch64(attn_fwd_ws64_kernel<128>)
-                       : (p->D == 64 ? launch64(attn_fwd_ws64_kernel<64>) : launch64(attn_fwd_ws64_kernel<192>));
+      if (general) {   // window / sink / softcap
+        rc = p->D == 128 ? launch64(attn_fwd_ws64_kernel<128, true>)
+                         : (p->D == 64 ? launch64(attn_fwd_ws64_kernel<64, true>)
+                                       : launch64(attn_fwd_ws64_kernel<192, true>));
+      } else {
+        rc = p->D == 128 ? launch64(attn_fwd_ws64_kernel<128>)
+                         : (p->D == 64 ? launch64(attn_fwd_ws64_kernel<64>) : launch64(attn_fwd_ws64_kernel<192>));
+      }
     } else if (p->D == 128) {
       rc = general ? launch(attn_fwd_ws_kernel<128, true>) : launch(attn_fwd_ws_kernel<128, false>);
     } else {

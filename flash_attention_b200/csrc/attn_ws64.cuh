@@ -1,5 +1,5 @@
-// Warp-specialised kernel with 64-key sub-blocks and FOUR score buffers (no split-KV / window /
-// sink: those stay with attn_ws.cuh).
+// Warp-specialised kernel with 64-key sub-blocks and FOUR score buffers (split-KV and KV-cache views
+// stay with attn_ws.cuh).
 //
 // The kernel of attn_ws.cuh keeps two 128-column S buffers in tensor memory and lets two pairs of
 // softmax warpgroups alternate over the 128-key blocks, a thread owning half a row.  The two
@@ -138,7 +138,11 @@ __device__ __forceinline__ uint32_t sw32_offset(uint32_t row, uint32_t chunk) {
 // the bytes of a Q / K tile (128 rows of kD / 2 bytes: 64-byte-swizzled rows for 128, 32-byte for
 // 64) and of a V tile (kD rows of 128 keys), and the width of O.  Shared and tensor memory are
 // laid out for 128 either way.
-template <int kD>
+// kGeneral adds sliding windows (the block range starts at the first block the window reaches, both
+// limits are masked), the learnable sink (one more term of the row sum, in the epilogue) and the
+// soft cap (tanh on the raw scores); a compile-time switch so that the plain instantiation carries
+// none of it.  Split-KV and the KV-cache view stay with attn_ws.cuh.
+template <int kD, bool kGeneral = false>
 __global__ void __launch_bounds__(ws64::kThreads, 1)
 attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
                      const __grid_constant__ CUtensorMap tm_k,
@@ -264,7 +268,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
   epi_phase += 1;                                                                                   \
   if (!ok) break;
     FA4_FOR_EACH_TILE {
-      const Tile t = decode_tile(p, tile);
+      const Tile t = decode_tile<kGeneral>(p, tile);
       const int n = t.n_blocks;
       if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
         *s_abort = 1u;
@@ -288,6 +292,12 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
 #pragma unroll
         for (int w = 0; w < 4; ++w) l_tot += lw[w] * reference_factor(mw[w], m_fin, p.sl2);
         if (m_fin == kNegInf) l_tot = 0.f;
+        if constexpr (kGeneral) {
+          // the sink joins the row sum, relative to the row's reference maximum
+          if (p.sink != nullptr && m_fin != kNegInf) {
+            l_tot += ex2_approx(static_cast<float>(kShift) + p.sink[t.h] * 1.4426950408889634f - m_fin * p.sl2);
+          }
+        }
         const uint32_t Jl = 2 * gb + 2 * n - 1;
         ok = __all_sync(0xffffffffu,
                         mbar_wait(bars.at(Bars::kPvDone + (Jl % kPSlots)), (Jl / kPSlots) & 1, wc, kS64FinalO));
@@ -336,7 +346,12 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
         bulk_commit_group();
       }
       if (q_idx < p.Sq && p.lse != nullptr) {
-        p.lse[((int64_t)t.b * p.Hq + t.h) * p.Sq + q_idx] = finish_lse(m_fin, l_tot, p.sl2);
+        float lse_v = finish_lse(m_fin, l_tot, p.sl2);
+        if constexpr (kGeneral) {
+          // a row without visible keys still has its sink: LSE = sink, output zero
+          if (p.sink != nullptr && m_fin == kNegInf) lse_v = p.sink[t.h];
+        }
+        p.lse[((int64_t)t.b * p.Hq + t.h) * p.Sq + q_idx] = lse_v;
       }
       gb += n;
       ti += (n > 0) ? 1u : 0u;
@@ -349,7 +364,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
       // ========================================= TMA producer ===================================
       uint32_t issued_k = 0, issued_v = 0, issued_q = 0;
       FA4_FOR_EACH_TILE {
-        const Tile t = decode_tile(p, tile);
+        const Tile t = decode_tile<kGeneral>(p, tile);
         const int n = t.n_blocks;
         if (n == 0) continue;
         if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
@@ -375,7 +390,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
           const int ik = step, iv = step - 2;
           if (ik < n) {
             const uint32_t G = gb + ik, st = G % kStagesK;
-            const int nb = ik;  // ascending: the diagonal block of a causal tile comes last
+            const int nb = (kGeneral ? t.nb_top - n + 1 : 0) + ik;  // ascending: the diagonal block comes last
             if (G >= kStagesK) {
               ok = mbar_wait_relaxed<kSlackNs>(bars.at(Bars::kKFree + st), ((G - kStagesK) / kStagesK) & 1, wc, kS64KFree);
               if (!ok) break;
@@ -389,7 +404,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
           }
           if (iv >= 0 && iv < n) {
             const uint32_t G = gb + iv, st = G % kStagesV;
-            const int nb = iv;
+            const int nb = (kGeneral ? t.nb_top - n + 1 : 0) + iv;
             if (G >= kStagesV) {
               ok = mbar_wait_relaxed<kSlackNs>(bars.at(Bars::kVFree + st), ((G - kStagesV) / kStagesV) & 1, wc, kS64VFree);
               if (!ok) break;
@@ -424,7 +439,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
     } else if (warp == kIssuerWarp && lane == 0) {
       // ========================================= QK^T issuer ====================================
       FA4_FOR_EACH_TILE {
-        const Tile t = decode_tile(p, tile);
+        const Tile t = decode_tile<kGeneral>(p, tile);
         const int n = t.n_blocks;
         if (n == 0) continue;
         if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
@@ -489,7 +504,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
     } else if (warp == kPvIssuerWarp && lane == 0) {
       // ========================================= P V issuer =====================================
       FA4_FOR_EACH_TILE {
-        const Tile t = decode_tile(p, tile);
+        const Tile t = decode_tile<kGeneral>(p, tile);
         const int n = t.n_blocks;
         if (n == 0) continue;
         if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
@@ -547,7 +562,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
       // A stage's tensor-memory slot is free when its shared-memory stage is: the producer
       // reloads the stage only after the products that used it have completed.
       FA4_FOR_EACH_TILE {
-        const Tile t = decode_tile(p, tile);
+        const Tile t = decode_tile<kGeneral>(p, tile);
         const int n = t.n_blocks;
         if (n == 0) continue;
         if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
@@ -595,7 +610,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
     const uint32_t s_addr = lane_addr + kTmS64 + 64 * wg;
 
     FA4_FOR_EACH_TILE {
-      const Tile t = decode_tile(p, tile);
+      const Tile t = decode_tile<kGeneral>(p, tile);
       const int n = t.n_blocks;
       const bool poisoned =
           (p.status != nullptr) && (*reinterpret_cast<volatile uint32_t*>(p.status) != 0u);
@@ -607,7 +622,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
 
       for (int j = (wg - 2 * (int)gb) & 3; j < 2 * n; j += 4) {
         const uint32_t J = 2 * gb + j, slot = J % kPSlots;  // J % 4 == wg
-        const int nb = j >> 1;
+        const int nb = (kGeneral ? t.nb_top - n + 1 : 0) + (j >> 1);
         const int h64 = j & 1;
         const uint32_t bar_s = bars.at(Bars::kSFull + (wg & 2)), par_s = (J / kSBufs) & 1;
         const uint32_t bar_p = bars.at(Bars::kPvDone + slot), par_p = ((J - kPSlots) / kPSlots) & 1;
@@ -620,7 +635,14 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
         FA4_PH(0);
         FA4_TRACE_EV(5, J);
         tc_fence_after_sync();
-        if (block_needs_mask(p, t, nb)) mask_scores_in_tmem(s_addr, causal_limit(p, t, row, nb) - 64 * h64);
+        if (block_needs_mask<kGeneral>(p, t, nb)) {
+          if constexpr (kGeneral) {
+            ws::mask_scores_in_tmem_range(s_addr, lower_limit(p, t, row, nb) - 64 * h64,
+                                          causal_limit<true>(p, t, row, nb) - 64 * h64);
+          } else {
+            mask_scores_in_tmem(s_addr, causal_limit(p, t, row, nb) - 64 * h64);
+          }
+        }
         float s[64];
         tmem_ld32(s_addr, reinterpret_cast<uint32_t*>(&s[0]));
         tmem_ld32(s_addr + 32, reinterpret_cast<uint32_t*>(&s[32]));
@@ -629,6 +651,12 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
         mbar_arrive(bars.at(Bars::kSFree + wg));
         FA4_TRACE_EV(3, J);
         FA4_PH(1);
+        if constexpr (kGeneral) {
+          if (p.softcap_c1 != 0.f) {
+#pragma unroll
+            for (int x = 0; x < 64; ++x) s[x] = soft_cap(s[x], p.softcap_c1);
+          }
+        }
 
         // 2. maxima of the four 16-key blocks, then the running reference: it is handed from the
         //    warpgroup of sub-block J - 1 to this one through shared memory (one float per row)

@@ -366,9 +366,13 @@ def test_parity_with_oracle_head_dim_192_128(cuda_device, case):
         Qf, Kf, Vf = fa.quantize_qkv_fused(q, k, v)
         out_f, lse_f = fa.flash_attn_func(Qf, Kf, Vf, causal=causal, return_lse=True)
         assert_parity(out_f, lse_f, *oracles(Qf, Kf, Vf, causal))
-    for kw in ({"variant": fa.VARIANT_WS}, {"num_splits": 2}, {"window_size": (64, 0)}):
+    for kw in ({"variant": fa.VARIANT_WS}, {"num_splits": 2}):
         with pytest.raises((ValueError, NotImplementedError)):
             run(Q, K, V, causal, **kw)
+    # windows, sinks and the soft cap are features of the 64-key kernel too
+    sink = torch.linspace(-1.0, 1.0, Hq)
+    out_w, lse_w = run(Q, K, V, causal, window_size=(96, None if not causal else 0), learnable_sink=sink)
+    assert_parity(out_w, lse_w, *oracles(Q, K, V, causal, window=(96, None), sink=sink.numpy()))
 
 
 CASES_SPLIT = [
@@ -492,8 +496,9 @@ def test_softcap_parity(cuda_device, case):
     # the cap changes the result (the test would not notice a kernel that ignored it otherwise)
     out0, _ = run(Q, K, V, causal, num_splits=splits, window_size=window)
     assert orc.error_metrics(out0.float().cpu(), oa)["rel_rms"] > 0.3
-    with pytest.raises((ValueError, NotImplementedError)):
-        run(Q, K, V, causal, fa.VARIANT_WS64, softcap=cap)
+    if splits > 1:
+        with pytest.raises((ValueError, NotImplementedError)):      # the 64-key kernel does not split
+            run(Q, K, V, causal, fa.VARIANT_WS64, softcap=cap, num_splits=splits, window_size=window)
 
 
 @pytest.mark.parametrize("case", [
