@@ -174,10 +174,12 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
   for (int64_t s : bstr)
     if (s <= 0 || (s & 15) != 0) return -FA4_E_STRIDE;
   if ((p->o_stride_b & 7) || (p->o_stride_s & 7) || (p->o_stride_h & 7)) return -FA4_E_STRIDE;
-  // automatic choice: the 64-key kernel where it applies (no split-KV, no KV-cache view), the
-  // 128-key kernel for everything else
+  // automatic choice: the 64-key kernel where it applies and is the faster one (no split-KV, no
+  // KV-cache view; sliding windows are measured faster on the 128-key kernel, whose visit order
+  // starts at the diagonal instead of the window's ragged left edge), the 128-key kernel otherwise
   const bool cached = cache.seqused_k != nullptr || cache.page_table != nullptr;
-  const bool plain = num_splits == 1 && !cached;   // what the 64-key kernel takes
+  const bool takes64 = num_splits == 1 && !cached;   // what the 64-key kernel can run
+  const bool plain = takes64 && win_left < 0 && win_right <= 0;
   int variant = p->variant;
   if (variant == FA4_VARIANT_AUTO) variant = plain ? FA4_VARIANT_WS64 : FA4_VARIANT_WS;
   if (variant != FA4_VARIANT_SERIAL && variant != FA4_VARIANT_WS && variant != FA4_VARIANT_WS64 &&
@@ -193,7 +195,7 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
     if (workspace == nullptr || !aligned16(workspace)) return -FA4_E_NULL;
     if (workspace_bytes < (uint64_t)splitkv_bytes(p, num_splits)) return -FA4_E_TOO_LARGE;
   }
-  if (variant == FA4_VARIANT_WS64 && !plain) return -FA4_E_SHAPE;
+  if (variant == FA4_VARIANT_WS64 && !takes64) return -FA4_E_SHAPE;
   if (d192 && variant != FA4_VARIANT_WS64) return -FA4_E_SHAPE;
   if (variant == FA4_VARIANT_SERIAL && p->D != 128) return -FA4_E_SHAPE;  // bring-up kernel: 128 only
   // window limits: `causal` is the right limit 0; an explicit right limit overrides it

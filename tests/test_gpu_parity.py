@@ -369,10 +369,12 @@ def test_parity_with_oracle_head_dim_192_128(cuda_device, case):
     for kw in ({"variant": fa.VARIANT_WS}, {"num_splits": 2}):
         with pytest.raises((ValueError, NotImplementedError)):
             run(Q, K, V, causal, **kw)
-    # windows, sinks and the soft cap are features of the 64-key kernel too
+    # sinks, the soft cap and (when asked for explicitly) windows are features of the 64-key kernel
     sink = torch.linspace(-1.0, 1.0, Hq)
-    out_w, lse_w = run(Q, K, V, causal, window_size=(96, None if not causal else 0), learnable_sink=sink)
-    assert_parity(out_w, lse_w, *oracles(Q, K, V, causal, window=(96, None), sink=sink.numpy()))
+    out_s, lse_s = run(Q, K, V, causal, learnable_sink=sink)
+    assert_parity(out_s, lse_s, *oracles(Q, K, V, causal, sink=sink.numpy()))
+    out_w, lse_w = run(Q, K, V, causal, fa.VARIANT_WS64, window_size=(96, None if not causal else 0))
+    assert_parity(out_w, lse_w, *oracles(Q, K, V, causal, window=(96, None), variant=fa.VARIANT_WS64))
 
 
 CASES_SPLIT = [
