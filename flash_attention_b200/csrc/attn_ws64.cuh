@@ -142,7 +142,10 @@ __device__ __forceinline__ uint32_t sw32_offset(uint32_t row, uint32_t chunk) {
 // limits are masked), the learnable sink (one more term of the row sum, in the epilogue) and the
 // soft cap (tanh on the raw scores); a compile-time switch so that the plain instantiation carries
 // none of it.  Split-KV and the KV-cache view stay with attn_ws.cuh.
-template <int kD, bool kGeneral = false>
+// (kWindow separates the two halves of it: the window changes the tile geometry and the masks of
+// the hot loop, sink and soft cap do not -- a call with only those keeps the plain geometry code,
+// which measured 16 % faster than carrying the window arithmetic along.)
+template <int kD, bool kGeneral = false, bool kWindow = kGeneral>
 __global__ void __launch_bounds__(ws64::kThreads, 1)
 attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
                      const __grid_constant__ CUtensorMap tm_k,
@@ -268,7 +271,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
   epi_phase += 1;                                                                                   \
   if (!ok) break;
     FA4_FOR_EACH_TILE {
-      const Tile t = decode_tile<kGeneral>(p, tile);
+      const Tile t = decode_tile<kWindow>(p, tile);
       const int n = t.n_blocks;
       if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
         *s_abort = 1u;
@@ -364,7 +367,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
       // ========================================= TMA producer ===================================
       uint32_t issued_k = 0, issued_v = 0, issued_q = 0;
       FA4_FOR_EACH_TILE {
-        const Tile t = decode_tile<kGeneral>(p, tile);
+        const Tile t = decode_tile<kWindow>(p, tile);
         const int n = t.n_blocks;
         if (n == 0) continue;
         if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
@@ -390,7 +393,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
           const int ik = step, iv = step - 2;
           if (ik < n) {
             const uint32_t G = gb + ik, st = G % kStagesK;
-            const int nb = (kGeneral ? t.nb_top - n + 1 : 0) + ik;  // ascending: the diagonal block comes last
+            const int nb = (kWindow ? t.nb_top - n + 1 : 0) + ik;  // ascending: the diagonal block comes last
             if (G >= kStagesK) {
               ok = mbar_wait_relaxed<kSlackNs>(bars.at(Bars::kKFree + st), ((G - kStagesK) / kStagesK) & 1, wc, kS64KFree);
               if (!ok) break;
@@ -404,7 +407,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
           }
           if (iv >= 0 && iv < n) {
             const uint32_t G = gb + iv, st = G % kStagesV;
-            const int nb = (kGeneral ? t.nb_top - n + 1 : 0) + iv;
+            const int nb = (kWindow ? t.nb_top - n + 1 : 0) + iv;
             if (G >= kStagesV) {
               ok = mbar_wait_relaxed<kSlackNs>(bars.at(Bars::kVFree + st), ((G - kStagesV) / kStagesV) & 1, wc, kS64VFree);
               if (!ok) break;
@@ -439,7 +442,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
     } else if (warp == kIssuerWarp && lane == 0) {
       // ========================================= QK^T issuer ====================================
       FA4_FOR_EACH_TILE {
-        const Tile t = decode_tile<kGeneral>(p, tile);
+        const Tile t = decode_tile<kWindow>(p, tile);
         const int n = t.n_blocks;
         if (n == 0) continue;
         if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
@@ -504,7 +507,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
     } else if (warp == kPvIssuerWarp && lane == 0) {
       // ========================================= P V issuer =====================================
       FA4_FOR_EACH_TILE {
-        const Tile t = decode_tile<kGeneral>(p, tile);
+        const Tile t = decode_tile<kWindow>(p, tile);
         const int n = t.n_blocks;
         if (n == 0) continue;
         if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
@@ -562,7 +565,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
       // A stage's tensor-memory slot is free when its shared-memory stage is: the producer
       // reloads the stage only after the products that used it have completed.
       FA4_FOR_EACH_TILE {
-        const Tile t = decode_tile<kGeneral>(p, tile);
+        const Tile t = decode_tile<kWindow>(p, tile);
         const int n = t.n_blocks;
         if (n == 0) continue;
         if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
@@ -610,7 +613,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
     const uint32_t s_addr = lane_addr + kTmS64 + 64 * wg;
 
     FA4_FOR_EACH_TILE {
-      const Tile t = decode_tile<kGeneral>(p, tile);
+      const Tile t = decode_tile<kWindow>(p, tile);
       const int n = t.n_blocks;
       const bool poisoned =
           (p.status != nullptr) && (*reinterpret_cast<volatile uint32_t*>(p.status) != 0u);
@@ -622,7 +625,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
 
       for (int j = (wg - 2 * (int)gb) & 3; j < 2 * n; j += 4) {
         const uint32_t J = 2 * gb + j, slot = J % kPSlots;  // J % 4 == wg
-        const int nb = (kGeneral ? t.nb_top - n + 1 : 0) + (j >> 1);
+        const int nb = (kWindow ? t.nb_top - n + 1 : 0) + (j >> 1);
         const int h64 = j & 1;
         const uint32_t bar_s = bars.at(Bars::kSFull + (wg & 2)), par_s = (J / kSBufs) & 1;
         const uint32_t bar_p = bars.at(Bars::kPvDone + slot), par_p = ((J - kPSlots) / kPSlots) & 1;
@@ -635,8 +638,8 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
         FA4_PH(0);
         FA4_TRACE_EV(5, J);
         tc_fence_after_sync();
-        if (block_needs_mask<kGeneral>(p, t, nb)) {
-          if constexpr (kGeneral) {
+        if (block_needs_mask<kWindow>(p, t, nb)) {
+          if constexpr (kWindow) {
             ws::mask_scores_in_tmem_range(s_addr, lower_limit(p, t, row, nb) - 64 * h64,
                                           causal_limit<true>(p, t, row, nb) - 64 * h64);
           } else {
