@@ -352,9 +352,11 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
                          : (p->D == 64 ? launch64(attn_fwd_ws64_kernel<64>) : launch64(attn_fwd_ws64_kernel<192>));
       }
     } else if (p->D == 128) {
-      rc = general ? launch(attn_fwd_ws_kernel<128, true>) : launch(attn_fwd_ws_kernel<128, false>);
+      rc = !general ? launch(attn_fwd_ws_kernel<128, false>)
+                    : (local ? launch(attn_fwd_ws_kernel<128, true>) : launch(attn_fwd_ws_kernel<128, true, false>));
     } else {
-      rc = general ? launch(attn_fwd_ws_kernel<64, true>) : launch(attn_fwd_ws_kernel<64, false>);
+      rc = !general ? launch(attn_fwd_ws_kernel<64, false>)
+                    : (local ? launch(attn_fwd_ws_kernel<64, true>) : launch(attn_fwd_ws_kernel<64, true, false>));
     }
     if (rc != 0) return rc;
   }

@@ -140,13 +140,15 @@ __device__ __forceinline__ Tile decode_tile(const KernelParams& p, int tile_idx)
 // (bottom-right aligned, flash_attn/cute/mask.py:369-527) and the key length (keys >= Sk of the
 // last, partial block are zero-filled by TMA and must not count; the reference masks them on the
 // first-processed block only, flash_fwd_sm100.py:1997-2004).
-template <bool kGeneral = false>
+// (kWindow = false with kGeneral = true: the entry's own key count, no window arithmetic -- what
+// split-KV and KV-cache calls without a window use.)
+template <bool kGeneral = false, bool kWindow = kGeneral>
 __device__ __forceinline__ int causal_limit(const KernelParams& p, const Tile& t, int row_in_tile,
                                             int nb) {
   const int sk = key_len<kGeneral>(p, t);
   const int len_limit = sk - 1 - nb * kBlockN;
   if (!p.causal) return len_limit;
-  const int c = t.m_blk * kBlockM + row_in_tile + sk - p.Sq + (kGeneral ? p.win_right : 0) - nb * kBlockN;
+  const int c = t.m_blk * kBlockM + row_in_tile + sk - p.Sq + (kWindow ? p.win_right : 0) - nb * kBlockN;
   return c < len_limit ? c : len_limit;
 }
 // In-block index of the FIRST visible key (left window limit); <= 0 when nothing is cut.
@@ -155,13 +157,13 @@ __device__ __forceinline__ int lower_limit(const KernelParams& p, const Tile& t,
   if (p.win_left < 0) return -(1 << 30);
   return t.m_blk * kBlockM + row_in_tile + t.sk - p.Sq - p.win_left - nb * kBlockN;
 }
-template <bool kGeneral = false>
+template <bool kGeneral = false, bool kWindow = kGeneral>
 __device__ __forceinline__ bool block_needs_mask(const KernelParams& p, const Tile& t, int nb) {
   const int sk = key_len<kGeneral>(p, t);
   const bool partial = (nb + 1) * kBlockN > sk;
   const int off = t.m_blk * kBlockM + sk - p.Sq;
-  bool need = partial || (p.causal && (nb * kBlockN + kBlockN - 1 > off + (kGeneral ? p.win_right : 0)));
-  if constexpr (kGeneral) {
+  bool need = partial || (p.causal && (nb * kBlockN + kBlockN - 1 > off + (kWindow ? p.win_right : 0)));
+  if constexpr (kWindow) {
     // the last row of the tile has the highest left limit
     need = need || (p.win_left >= 0 && nb * kBlockN < off + kBlockM - 1 - p.win_left);
   }
