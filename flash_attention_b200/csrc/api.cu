@@ -174,11 +174,11 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
   for (int64_t s : bstr)
     if (s <= 0 || (s & 15) != 0) return -FA4_E_STRIDE;
   if ((p->o_stride_b & 7) || (p->o_stride_s & 7) || (p->o_stride_h & 7)) return -FA4_E_STRIDE;
-  // automatic choice: the 64-key kernel where it applies and is the faster one (no split-KV, no
-  // KV-cache view; sliding windows are measured faster on the 128-key kernel, whose visit order
-  // starts at the diagonal instead of the window's ragged left edge), the 128-key kernel otherwise
+  // automatic choice: the 64-key kernel where it applies and is the faster one (no split-KV;
+  // sliding windows are measured faster on the 128-key kernel, whose visit order starts at the
+  // diagonal instead of the window's ragged left edge), the 128-key kernel otherwise
   const bool cached = cache.seqused_k != nullptr || cache.page_table != nullptr;
-  const bool takes64 = num_splits == 1 && !cached;   // what the 64-key kernel can run
+  const bool takes64 = num_splits == 1;   // what the 64-key kernel can run
   const bool plain = takes64 && win_left < 0 && win_right <= 0;
   int variant = p->variant;
   if (variant == FA4_VARIANT_AUTO) variant = plain ? FA4_VARIANT_WS64 : FA4_VARIANT_WS;
@@ -339,7 +339,7 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
         kernel<<<grid, ws64::kThreads, ws64::kSmemRequest, stream>>>(tm_q, tm_k, tm_v, tm_o, kp);
         return 0;
       };
-      if (general && local) {   // window (with or without sink / softcap)
+      if (general && (local || cached)) {   // window and / or KV-cache view (with or without sink / softcap)
         rc = p->D == 128 ? launch64(attn_fwd_ws64_kernel<128, true>)
                          : (p->D == 64 ? launch64(attn_fwd_ws64_kernel<64, true>)
                                        : launch64(attn_fwd_ws64_kernel<192, true>));

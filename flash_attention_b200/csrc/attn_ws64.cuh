@@ -141,7 +141,8 @@ __device__ __forceinline__ uint32_t sw32_offset(uint32_t row, uint32_t chunk) {
 // kGeneral adds sliding windows (the block range starts at the first block the window reaches, both
 // limits are masked), the learnable sink (one more term of the row sum, in the epilogue) and the
 // soft cap (tanh on the raw scores); a compile-time switch so that the plain instantiation carries
-// none of it.  Split-KV and the KV-cache view stay with attn_ws.cuh.
+// none of it.  The window instantiation also serves KV-cache views (per-entry key counts, page
+// tables); split-KV stays with attn_ws.cuh.
 // (kWindow separates the two halves of it: the window changes the tile geometry and the masks of
 // the hot loop, sink and soft cap do not -- a call with only those keeps the plain geometry code,
 // which measured 16 % faster than carrying the window arithmetic along.)
@@ -386,8 +387,19 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
                   p.q_sf + t.b * p.qsf_stride_b + t.h * p.qsf_stride_h + (int64_t)t.m_blk * kQkSfBytes,
                   kQkSfBytes, bars.at(Bars::kQFull + qb));
         issued_q = ti + 1;
-        const uint8_t* ksf = p.k_sf + t.b * p.ksf_stride_b + t.hk * p.ksf_stride_h;
-        const uint8_t* vsf = p.v_sf + t.b * p.vsf_stride_b + t.hk * p.vsf_stride_h;
+        // where logical K/V block nb of this batch entry lives: the entry itself, or (window
+        // instantiation, which also serves KV-cache views) a page of the pool and the block in it
+        auto locate = [&](int nb, int& kb, int& nbl) {
+          kb = t.b;
+          nbl = nb;
+          if constexpr (kWindow) {
+            if (p.page_table != nullptr) {
+              const int key0 = nb * kBlockN, pg = key0 / p.page_size;
+              kb = p.page_table[(int64_t)t.b * p.pages_per_seq + pg];
+              nbl = (key0 - pg * p.page_size) / kBlockN;
+            }
+          }
+        };
         // K runs two blocks ahead of V
         for (int step = 0; ok && step < n + 2; ++step) {
           const int ik = step, iv = step - 2;
@@ -399,10 +411,13 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
               if (!ok) break;
             }
             mbar_arrive_expect_tx(bars.at(Bars::kKFull + st), kQkBytes + kQkSfBytes);
+            int kb, nbl;
+            locate(nb, kb, nbl);
             load_qk_tile(base + kOffK + st * kQkSlot, &tm_k, bars.at(Bars::kKFull + st), t.hk,
-                         nb * kBlockN, t.b);
-            bulk_load(base + kOffSFK + st * kQkSfSlot, ksf + (int64_t)nb * kQkSfBytes, kQkSfBytes,
-                      bars.at(Bars::kKFull + st));
+                         nbl * kBlockN, kb);
+            bulk_load(base + kOffSFK + st * kQkSfSlot,
+                      p.k_sf + kb * p.ksf_stride_b + t.hk * p.ksf_stride_h + (int64_t)nbl * kQkSfBytes,
+                      kQkSfBytes, bars.at(Bars::kKFull + st));
             issued_k = G + 1;
           }
           if (iv >= 0 && iv < n) {
@@ -413,10 +428,13 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
               if (!ok) break;
             }
             mbar_arrive_expect_tx(bars.at(Bars::kVFull + st), kVBytes + kSfBytes);
+            int kb, nbl;
+            locate(nb, kb, nbl);
             tma_load_4d(base + kOffV + st * kTileBytes, &tm_v, bars.at(Bars::kVFull + st),
-                        nb * (kBlockN / 2), 0, t.hk, t.b);
-            bulk_load(base + kOffSFV + st * kSfBytes, vsf + (int64_t)nb * kSfBytes, kSfBytes,
-                      bars.at(Bars::kVFull + st));
+                        nbl * (kBlockN / 2), 0, t.hk, kb);
+            bulk_load(base + kOffSFV + st * kSfBytes,
+                      p.v_sf + kb * p.vsf_stride_b + t.hk * p.vsf_stride_h + (int64_t)nbl * kSfBytes,
+                      kSfBytes, bars.at(Bars::kVFull + st));
             issued_v = G + 1;
           }
         }

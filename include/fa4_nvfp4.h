@@ -76,8 +76,8 @@ enum {
                              block down; every feature, D = 128 and 64 */
   FA4_VARIANT_WS64 = 3,   /* warp-specialised pipeline, steps of 64 keys upwards, four score
                              buffers, separate epilogue warpgroup; D = 128, 64 and (192, 128);
-                             windows, sinks and the soft cap, but no split-KV and no KV-cache
-                             view (-FA4_E_SHAPE) */
+                             windows, sinks, the soft cap and KV-cache views, but no split-KV
+                             (-FA4_E_SHAPE) */
   FA4_VARIANT_DECODE = 4  /* transposed products for a handful of query rows: keys on the tile's
                              lanes, the Sq * (Hq / Hkv) <= 16 query rows of a kv head on the N
                              side; D = Dv = 128, causal or unmasked, seqused_k / page_table allowed;

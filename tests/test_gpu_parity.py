@@ -562,7 +562,8 @@ def test_kv_cache_seqused_and_page_table(cuda_device, case):
     Q, K, V = fa.quantize_qkv(q, k, v)
     su = torch.tensor(used, dtype=torch.int32, device=cuda_device)
     # what the automatic choice runs for this shape: the decode kernel for a handful of rows
-    model = fa.VARIANT_DECODE if (D == 128 and Sq * (Hq // Hkv) <= 16) else fa.VARIANT_WS
+    model = (fa.VARIANT_DECODE if (D == 128 and Sq * (Hq // Hkv) <= 16)
+             else (fa.VARIANT_WS64 if splits == 1 else fa.VARIANT_WS))
     out, lse = run(Q, K, V, causal, seqused_k=su, num_splits=splits)
     for b, sk in enumerate(used):
         if sk == 0:
@@ -597,7 +598,8 @@ def test_kv_cache_seqused_and_page_table(cuda_device, case):
     # a table without seqused_k: every entry sees the whole logical length
     out_f, lse_f = fa.flash_attn_fp4_func(Q.data, kp, vp, Q.sf, ksp, vsp, Q.scale, K.scale, V.scale, causal=causal,
                                           return_lse=True, page_table=table)
-    want_f, want_l = run(Q, K, V, causal, model)
+    model1 = fa.VARIANT_DECODE if model == fa.VARIANT_DECODE else fa.VARIANT_WS64      # this call does not split
+    want_f, want_l = run(Q, K, V, causal, model1)
     torch.cuda.synchronize()
     assert torch.equal(out_f, want_f) and torch.equal(lse_f, want_l)
     with pytest.raises(NotImplementedError):
