@@ -339,10 +339,14 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
         kernel<<<grid, ws64::kThreads, ws64::kSmemRequest, stream>>>(tm_q, tm_k, tm_v, tm_o, kp);
         return 0;
       };
-      if (general && (local || cached)) {   // window and / or KV-cache view (with or without sink / softcap)
+      if (general && local) {   // window (with or without sink / softcap / cache view)
         rc = p->D == 128 ? launch64(attn_fwd_ws64_kernel<128, true>)
                          : (p->D == 64 ? launch64(attn_fwd_ws64_kernel<64, true>)
                                        : launch64(attn_fwd_ws64_kernel<192, true>));
+      } else if (general && cached) {   // KV-cache view without a window
+        rc = p->D == 128 ? launch64(attn_fwd_ws64_kernel<128, true, false, true>)
+                         : (p->D == 64 ? launch64(attn_fwd_ws64_kernel<64, true, false, true>)
+                                       : launch64(attn_fwd_ws64_kernel<192, true, false, true>));
       } else if (general) {     // sink / softcap only: plain tile geometry
         rc = p->D == 128 ? launch64(attn_fwd_ws64_kernel<128, true, false>)
                          : (p->D == 64 ? launch64(attn_fwd_ws64_kernel<64, true, false>)

@@ -146,7 +146,8 @@ __device__ __forceinline__ uint32_t sw32_offset(uint32_t row, uint32_t chunk) {
 // (kWindow separates the two halves of it: the window changes the tile geometry and the masks of
 // the hot loop, sink and soft cap do not -- a call with only those keeps the plain geometry code,
 // which measured 16 % faster than carrying the window arithmetic along.)
-template <int kD, bool kGeneral = false, bool kWindow = kGeneral>
+// kCache: per-entry key counts and page tables without the window arithmetic.
+template <int kD, bool kGeneral = false, bool kWindow = kGeneral, bool kCache = kWindow>
 __global__ void __launch_bounds__(ws64::kThreads, 1)
 attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
                      const __grid_constant__ CUtensorMap tm_k,
@@ -272,7 +273,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
   epi_phase += 1;                                                                                   \
   if (!ok) break;
     FA4_FOR_EACH_TILE {
-      const Tile t = decode_tile<kWindow>(p, tile);
+      const Tile t = decode_tile<kWindow || kCache>(p, tile);
       const int n = t.n_blocks;
       if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
         *s_abort = 1u;
@@ -368,7 +369,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
       // ========================================= TMA producer ===================================
       uint32_t issued_k = 0, issued_v = 0, issued_q = 0;
       FA4_FOR_EACH_TILE {
-        const Tile t = decode_tile<kWindow>(p, tile);
+        const Tile t = decode_tile<kWindow || kCache>(p, tile);
         const int n = t.n_blocks;
         if (n == 0) continue;
         if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
@@ -392,7 +393,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
         auto locate = [&](int nb, int& kb, int& nbl) {
           kb = t.b;
           nbl = nb;
-          if constexpr (kWindow) {
+          if constexpr (kWindow || kCache) {
             if (p.page_table != nullptr) {
               const int key0 = nb * kBlockN, pg = key0 / p.page_size;
               kb = p.page_table[(int64_t)t.b * p.pages_per_seq + pg];
@@ -460,7 +461,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
     } else if (warp == kIssuerWarp && lane == 0) {
       // ========================================= QK^T issuer ====================================
       FA4_FOR_EACH_TILE {
-        const Tile t = decode_tile<kWindow>(p, tile);
+        const Tile t = decode_tile<kWindow || kCache>(p, tile);
         const int n = t.n_blocks;
         if (n == 0) continue;
         if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
@@ -525,7 +526,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
     } else if (warp == kPvIssuerWarp && lane == 0) {
       // ========================================= P V issuer =====================================
       FA4_FOR_EACH_TILE {
-        const Tile t = decode_tile<kWindow>(p, tile);
+        const Tile t = decode_tile<kWindow || kCache>(p, tile);
         const int n = t.n_blocks;
         if (n == 0) continue;
         if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
@@ -583,7 +584,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
       // A stage's tensor-memory slot is free when its shared-memory stage is: the producer
       // reloads the stage only after the products that used it have completed.
       FA4_FOR_EACH_TILE {
-        const Tile t = decode_tile<kWindow>(p, tile);
+        const Tile t = decode_tile<kWindow || kCache>(p, tile);
         const int n = t.n_blocks;
         if (n == 0) continue;
         if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
@@ -631,7 +632,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
     const uint32_t s_addr = lane_addr + kTmS64 + 64 * wg;
 
     FA4_FOR_EACH_TILE {
-      const Tile t = decode_tile<kWindow>(p, tile);
+      const Tile t = decode_tile<kWindow || kCache>(p, tile);
       const int n = t.n_blocks;
       const bool poisoned =
           (p.status != nullptr) && (*reinterpret_cast<volatile uint32_t*>(p.status) != 0u);
@@ -656,12 +657,12 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
         FA4_PH(0);
         FA4_TRACE_EV(5, J);
         tc_fence_after_sync();
-        if (block_needs_mask<kWindow>(p, t, nb)) {
+        if (block_needs_mask<kWindow || kCache, kWindow>(p, t, nb)) {
           if constexpr (kWindow) {
             ws::mask_scores_in_tmem_range(s_addr, lower_limit(p, t, row, nb) - 64 * h64,
                                           causal_limit<true>(p, t, row, nb) - 64 * h64);
           } else {
-            mask_scores_in_tmem(s_addr, causal_limit(p, t, row, nb) - 64 * h64);
+            mask_scores_in_tmem(s_addr, causal_limit<kWindow || kCache, kWindow>(p, t, row, nb) - 64 * h64);
           }
         }
         float s[64];
