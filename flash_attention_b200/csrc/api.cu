@@ -174,12 +174,11 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
   for (int64_t s : bstr)
     if (s <= 0 || (s & 15) != 0) return -FA4_E_STRIDE;
   if ((p->o_stride_b & 7) || (p->o_stride_s & 7) || (p->o_stride_h & 7)) return -FA4_E_STRIDE;
-  // automatic choice: the 64-key kernel where it applies and is the faster one (no split-KV;
-  // sliding windows are measured faster on the 128-key kernel, whose visit order starts at the
-  // diagonal instead of the window's ragged left edge), the 128-key kernel otherwise
+  // automatic choice: the 64-key kernel where it applies (no split-KV), the 128-key kernel
+  // otherwise
   const bool cached = cache.seqused_k != nullptr || cache.page_table != nullptr;
   const bool takes64 = num_splits == 1;   // what the 64-key kernel can run
-  const bool plain = takes64 && win_left < 0 && win_right <= 0;
+  const bool plain = takes64;
   int variant = p->variant;
   if (variant == FA4_VARIANT_AUTO) variant = plain ? FA4_VARIANT_WS64 : FA4_VARIANT_WS;
   if (variant != FA4_VARIANT_SERIAL && variant != FA4_VARIANT_WS && variant != FA4_VARIANT_WS64 &&

@@ -127,6 +127,19 @@ enum Site64 {
   kS64PFull, kS64PvDone, kS64Hand, kS64Fin, kS64FinFree, kS64FinalO, kS64OFree, kS64Ksf, kS64Vsf, kS64Epi
 };
 
+// Visit order of a windowed tile: the i-th visited 128-key block.  Ascending from the first block
+// the window reaches, EXCEPT that the two blocks at the window's left edge -- where the lower rows
+// of the tile see a few keys or none, so that references taken there would be low -- are visited
+// last: a tile starts at a block every row sees whole.  (The right edge, the diagonal, is last in
+// ascending order anyway.)  rotate: the tile is cut on the left and has more than two blocks.
+__device__ __forceinline__ int window_visit_block(int i, int n, int nb_lo, bool rotate) {
+  if (!rotate) return nb_lo + i;
+  return i < n - 2 ? nb_lo + 2 + i : nb_lo + (i - (n - 2));
+}
+__device__ __forceinline__ bool window_rotates(const KernelParams& p, const Tile& t) {
+  return p.win_left >= 0 && t.n_blocks > 2 && (t.m_blk * kBlockM + t.sk - p.Sq - p.win_left) > 0;
+}
+
 // byte offset of 16-byte chunk c (0, 1) of row r in a P tile (rows of 32 bytes, 32-byte swizzle)
 __device__ __forceinline__ uint32_t sw32_offset(uint32_t row, uint32_t chunk) {
   return row * 32u + ((chunk ^ ((row >> 2) & 1u)) << 4);
@@ -406,7 +419,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
           const int ik = step, iv = step - 2;
           if (ik < n) {
             const uint32_t G = gb + ik, st = G % kStagesK;
-            const int nb = (kWindow ? t.nb_top - n + 1 : 0) + ik;  // ascending: the diagonal block comes last
+            const int nb = kWindow ? window_visit_block(ik, n, t.nb_top - n + 1, window_rotates(p, t)) : ik;  // ascending
             if (G >= kStagesK) {
               ok = mbar_wait_relaxed<kSlackNs>(bars.at(Bars::kKFree + st), ((G - kStagesK) / kStagesK) & 1, wc, kS64KFree);
               if (!ok) break;
@@ -423,7 +436,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
           }
           if (iv >= 0 && iv < n) {
             const uint32_t G = gb + iv, st = G % kStagesV;
-            const int nb = (kWindow ? t.nb_top - n + 1 : 0) + iv;
+            const int nb = kWindow ? window_visit_block(iv, n, t.nb_top - n + 1, window_rotates(p, t)) : iv;
             if (G >= kStagesV) {
               ok = mbar_wait_relaxed<kSlackNs>(bars.at(Bars::kVFree + st), ((G - kStagesV) / kStagesV) & 1, wc, kS64VFree);
               if (!ok) break;
@@ -644,7 +657,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
 
       for (int j = (wg - 2 * (int)gb) & 3; j < 2 * n; j += 4) {
         const uint32_t J = 2 * gb + j, slot = J % kPSlots;  // J % 4 == wg
-        const int nb = (kWindow ? t.nb_top - n + 1 : 0) + (j >> 1);
+        const int nb = kWindow ? window_visit_block(j >> 1, n, t.nb_top - n + 1, window_rotates(p, t)) : (j >> 1);
         const int h64 = j & 1;
         const uint32_t bar_s = bars.at(Bars::kSFull + (wg & 2)), par_s = (J / kSBufs) & 1;
         const uint32_t bar_p = bars.at(Bars::kPvDone + slot), par_p = ((J - kPSlots) / kPSlots) & 1;

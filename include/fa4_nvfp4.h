@@ -70,7 +70,7 @@ enum {
 
 /* kernel variants */
 enum {
-  FA4_VARIANT_AUTO = 0,   /* WS64 where it applies, else WS */
+  FA4_VARIANT_AUTO = 0,   /* WS64 unless the call splits the keys (then WS) */
   FA4_VARIANT_SERIAL = 1, /* one warpgroup does every step in turn (bring-up / cross-check) */
   FA4_VARIANT_WS = 2,     /* warp-specialised pipeline, steps of 128 keys from the last visible
                              block down; every feature, D = 128 and 64 */

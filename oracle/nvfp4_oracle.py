@@ -276,7 +276,12 @@ def attention_oracle_b(qd, kd, vd, sl2: float, v_scale_out: float = 1.0, causal=
                 if mask is not None:
                     s_all[:, :Sk] = s_all[:, :Sk].masked_fill(mask[rows], float("-inf"))
                 if ascending:
-                    visit = list(range(n_min * sub, n_blocks * sub))
+                    # a tile that is cut on the left visits the two blocks of the window's left
+                    # edge last (csrc/attn_ws64.cuh, window_visit_block)
+                    blocks = list(range(n_min, n_blocks))
+                    if left is not None and len(blocks) > 2 and (m0 + Sk - Sq - left) > 0:
+                        blocks = blocks[2:] + blocks[:2]
+                    visit = [nb * sub + h for nb in blocks for h in range(sub)]
                 else:
                     visit = [nb * sub + h for nb in range(n_blocks - 1, n_min - 1, -1)
                              for h in range(sub - 1, -1, -1)]

@@ -42,7 +42,7 @@ def kernel_model(D, num_splits=1, window=(None, None), sink=None, variant=0, sof
     """Which kernel the library's automatic choice runs, as oracle B keywords: the 64-key kernel
     without split-KV and windows (sinks and the soft cap included), the 128-key kernel otherwise (mirrors
     launch_fwd in csrc/api.cu).  ``variant`` 1 / 2 force the 128-key model, 3 the 64-key one."""
-    plain = num_splits == 1 and window in ((None, None), (None, 0))
+    plain = num_splits == 1
     # decode / append shapes: the transposed kernel, 128-key steps upwards, any number of splits
     decode_ok = (D == 128 and rows is not None and rows <= 16 and window in ((None, None), (None, 0))
                  and sink is None and not softcap)

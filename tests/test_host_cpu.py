@@ -221,7 +221,7 @@ def test_decode_split_choice_and_oracle_model_selection():
     assert kernel_model(128, rows=256) == {"step_keys": 64, "ascending": True}         # 64-key prefill kernel
     assert kernel_model(64, rows=4) == {"step_keys": 64, "ascending": True}            # head dim 64: no decode kernel
     assert kernel_model(128, rows=4, softcap=2.0) == {"step_keys": 64, "ascending": True}   # general 64-key kernel
-    assert kernel_model(128, rows=256, window=(64, None)) == {"step_keys": 128, "ascending": False}   # windows: 128-key
+    assert kernel_model(128, rows=256, window=(64, None)) == {"step_keys": 64, "ascending": True}
     assert kernel_model(128, rows=256, sink=[0.0]) == {"step_keys": 64, "ascending": True}
     assert kernel_model(128, rows=256, num_splits=2) == {"step_keys": 128, "ascending": False}
     assert kernel_model(128, rows=4, variant=2) == {"step_keys": 128, "ascending": False}
