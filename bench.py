@@ -494,7 +494,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--kernel", default="auto", choices=["auto", "ws128"],
                     help="auto: the library's choice (the 64-key kernel for these workloads); ws128: force "
-                         "the 128-key kernel that serves split-KV / windows / sinks")
+                         "the 128-key kernel that serves split-KV")
     args = ap.parse_args()
     if args.workload in ("sweep", "decode"):
         if not torch.cuda.is_available():
