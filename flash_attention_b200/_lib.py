@@ -7,6 +7,8 @@ or cannot be loaded, every operator of this package raises.
 from __future__ import annotations
 
 import ctypes
+import fcntl
+import glob
 import os
 import shutil
 import subprocess
@@ -15,15 +17,15 @@ import threading
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libfa4_nvfp4.so")
 CSRC = os.path.join(_HERE, "csrc")
+LOCK_PATH = os.path.join(_HERE, ".build.lock")
 SOURCES = ["api.cu"]
-HEADERS = ["ptx.cuh", "softmax.cuh", "attn_common.cuh", "attn_serial.cuh", "attn_ws.cuh", "attn_ws64.cuh", "attn_decode.cuh",
-           "aux_kernels.cuh"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--shared", "-Xcompiler", "-fPIC"]
 
 ERROR_NAMES = {1: "null pointer", 2: "unsupported shape", 3: "bad stride", 4: "misaligned pointer",
                5: "unknown variant", 6: "tensor map rejected", 7: "struct size mismatch",
-               8: "problem too large for this entry point"}
+               8: "problem too large for this entry point",
+               9: "library built with a register count its kernels cannot run with"}
 
 
 class Params(ctypes.Structure):
@@ -59,27 +61,54 @@ class Ext(ctypes.Structure):
     ]
 
 
+def _dependencies():
+    """Every file the library is compiled from: all of csrc/ and the public header."""
+    deps = sorted(glob.glob(os.path.join(CSRC, "*.cu")) + glob.glob(os.path.join(CSRC, "*.cuh")))
+    deps.append(os.path.join(_HERE, "..", "include", "fa4_nvfp4.h"))
+    return deps
+
+
 def _needs_build() -> bool:
     if not os.path.exists(LIB_PATH):
         return True
     t = os.path.getmtime(LIB_PATH)
-    deps = [os.path.join(CSRC, f) for f in SOURCES + HEADERS]
-    deps.append(os.path.join(_HERE, "..", "include", "fa4_nvfp4.h"))
-    return any(os.path.exists(d) and os.path.getmtime(d) > t for d in deps)
+    return any(os.path.exists(d) and os.path.getmtime(d) > t for d in _dependencies())
+
+
+class _BuildLock:
+    """Inter-process lock around build and load: the ranks of one node share the source tree, and
+    a rank must never load a library another rank is still writing."""
+
+    def __enter__(self):
+        self.f = open(LOCK_PATH, "w")
+        fcntl.flock(self.f, fcntl.LOCK_EX)
+        return self
+
+    def __exit__(self, *exc):
+        fcntl.flock(self.f, fcntl.LOCK_UN)
+        self.f.close()
+
+
+def _compile(verbose: bool) -> None:
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    tmp = f"{LIB_PATH}.{os.getpid()}.tmp"
+    cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + \
+          ["-o", tmp] + [os.path.join(CSRC, s) for s in SOURCES]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        if os.path.exists(tmp):
+            os.unlink(tmp)
+        raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
+    os.replace(tmp, LIB_PATH)       # readers see the old file or the complete new one
+    if verbose:
+        print(res.stderr)
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
     """Compile the CUDA library for sm_100a (cross-compiles without a GPU)."""
-    if not force and not _needs_build():
-        return LIB_PATH
-    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
-    cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + \
-          ["-o", LIB_PATH] + [os.path.join(CSRC, s) for s in SOURCES]
-    res = subprocess.run(cmd, capture_output=True, text=True)
-    if res.returncode != 0:
-        raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
-    if verbose:
-        print(res.stderr)
+    with _BuildLock():
+        if force or _needs_build():
+            _compile(verbose)
     return LIB_PATH
 
 
@@ -92,13 +121,14 @@ def lib() -> ctypes.CDLL:
     global _lib
     with _lock:
         if _lib is None:
-            if _needs_build():
-                if shutil.which("nvcc") or os.path.exists("/usr/local/cuda/bin/nvcc"):
-                    build()
-                elif not os.path.exists(LIB_PATH):
-                    raise RuntimeError(f"{LIB_PATH} is missing and nvcc is not available; "
-                                       "run flash_attention_b200.build() first")
-            L = ctypes.CDLL(LIB_PATH)
+            with _BuildLock():
+                if _needs_build():
+                    if shutil.which("nvcc") or os.path.exists("/usr/local/cuda/bin/nvcc"):
+                        _compile(False)
+                    elif not os.path.exists(LIB_PATH):
+                        raise RuntimeError(f"{LIB_PATH} is missing and nvcc is not available; "
+                                           "run flash_attention_b200.build() first")
+                L = ctypes.CDLL(LIB_PATH)
             L.fa4_nvfp4_fwd.argtypes = [ctypes.POINTER(Params), ctypes.c_void_p]
             L.fa4_nvfp4_fwd.restype = ctypes.c_int
             L.fa4_nvfp4_splitkv_workspace_bytes.argtypes = [ctypes.POINTER(Params), ctypes.c_int32]

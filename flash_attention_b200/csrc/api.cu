@@ -11,7 +11,10 @@
 #include "quantize.cuh"
 
 #include <cudaTypedefs.h>
+#include <atomic>
+#include <map>
 #include <mutex>
+#include <utility>
 
 namespace {
 
@@ -60,24 +63,49 @@ bool encode_u8_4d(CUtensorMap* m, const void* base, const uint64_t (&dims)[4],
   return r == CUDA_SUCCESS;
 }
 
-inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
-
-template <class Kernel>
-int ensure_smem(Kernel kernel, uint32_t bytes) {
-  const cudaError_t e =
-      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
-  return e == cudaSuccess ? 0 : (int)e;
+// Launch epoch recorded with a device-side failure (see ptx.cuh): launches modulo 256.
+uint32_t next_launch_epoch() {
+  static std::atomic<uint32_t> counter{0};
+  return counter.fetch_add(1, std::memory_order_relaxed) & 0xffu;
 }
 
-// The warp-specialised kernels re-partition registers with setmaxnreg, and an increase blocks for
-// ever when the CTA was launched with fewer registers per thread than the budget in the source
-// assumes.  Refuse to launch a build whose compiled register count is below that assumption.
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Per-kernel launch preparation, done once per (kernel, device) and remembered: the opt-in to
+// `smem_bytes` of dynamic shared memory and -- for the warp-specialised kernels, which re-partition
+// registers with setmaxnreg -- the check that the build kept the register count the budget in the
+// source assumes (an increase blocks for ever when the CTA was launched with fewer registers per
+// thread; such a build is refused with -FA4_E_BUILD instead of being launched).
+// expected_regs = 0: no register check.
+int prepare_kernel(const void* kernel, uint32_t smem_bytes, int expected_regs) {
+  static std::mutex mu;
+  static std::map<std::pair<const void*, int>, int> seen;   // -> result of the first preparation
+  int dev = 0;
+  const cudaError_t ge = cudaGetDevice(&dev);
+  if (ge != cudaSuccess) return (int)ge;
+  std::lock_guard<std::mutex> lock(mu);
+  const auto key = std::make_pair(kernel, dev);
+  const auto it = seen.find(key);
+  if (it != seen.end()) return it->second;
+  int rc = 0;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+  if (e != cudaSuccess) return (int)e;          // not remembered: the caller may retry
+  if (expected_regs > 0) {
+    cudaFuncAttributes attr;
+    e = cudaFuncGetAttributes(&attr, kernel);
+    if (e != cudaSuccess) return (int)e;
+    if (attr.numRegs < expected_regs) rc = -FA4_E_BUILD;
+  }
+  seen[key] = rc;
+  return rc;
+}
 template <class Kernel>
-int ensure_launch_regs(Kernel kernel, int expected) {
-  cudaFuncAttributes attr;
-  const cudaError_t e = cudaFuncGetAttributes(&attr, kernel);
-  if (e != cudaSuccess) return (int)e;
-  return attr.numRegs >= expected ? 0 : -FA4_E_BUILD;
+int ensure_smem(Kernel kernel, uint32_t bytes) {
+  return prepare_kernel(reinterpret_cast<const void*>(kernel), bytes, 0);
+}
+template <class Kernel>
+int ensure_kernel(Kernel kernel, uint32_t bytes, int expected_regs) {
+  return prepare_kernel(reinterpret_cast<const void*>(kernel), bytes, expected_regs);
 }
 
 }  // namespace
@@ -150,15 +178,26 @@ extern "C" int fa4_nvfp4_fwd_splitkv(const fa4_nvfp4_params* p, int32_t num_spli
 }
 
 namespace {
-int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint64_t workspace_bytes,
-               int win_left, int win_right, const float* sink, float softcap, const CacheView& cache,
-               void* cuda_stream) {
+// What a call resolves to once its arguments have been accepted.
+struct FwdPlan {
+  int variant = 0;
+  int win_left = -1, win_right = -1;
+  bool decode = false, d192 = false, local = false, general = false, cached = false;
+  int dec_rows = 0;
+};
+
+// Every host-side check of a forward call.  Touches no CUDA API: a call that fails here has
+// launched nothing and has not made a device current.  `linear_sf`: the three scale pointers are
+// the caller's LINEAR layouts (the allocation-free entry point), which need no 16-byte alignment.
+int validate_fwd(const fa4_nvfp4_params* p, int num_splits, const void* workspace, uint64_t workspace_bytes,
+                 int win_left, int win_right, const float* sink, float softcap, const CacheView& cache,
+                 bool linear_sf, FwdPlan* plan) {
   if (p == nullptr) return -FA4_E_NULL;
   if (p->struct_size != sizeof(fa4_nvfp4_params)) return -FA4_E_STRUCT;
   if (!p->q || !p->k || !p->v || !p->q_sf || !p->k_sf || !p->v_sf || !p->out) return -FA4_E_NULL;
   if (p->B <= 0 || p->Sq <= 0 || p->Sk <= 0 || p->Hq <= 0 || p->Hkv <= 0) return -FA4_E_SHAPE;
   if (p->Hq % p->Hkv != 0) return -FA4_E_SHAPE;
-  // head dims built: (128, 128), (64, 64) and (192, 128), the last on the plain path only
+  // head dims built: (128, 128), (64, 64) and (192, 128), the last on the 64-key kernel only
   const bool d192 = p->D == 192 && p->Dv == 128;
   if (!d192 && (p->D != p->Dv || (p->D != 128 && p->D != 64))) return -FA4_E_SHAPE;
   // keys are blocked by 16 along Sk (V / P scales) and V rows are Sk/2 bytes with a 16-byte
@@ -166,9 +205,10 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
   if (p->Sk % 32 != 0) return -FA4_E_SHAPE;
   if ((int64_t)((p->Sq + kBlockM - 1) / kBlockM) * p->Hq * p->B > 0x7fffffffLL) return -FA4_E_SHAPE;
   if (!(p->softmax_scale > 0.f) || !(p->q_scale > 0.f) || !(p->k_scale > 0.f)) return -FA4_E_SHAPE;
-  const void* ptrs[] = {p->q, p->k, p->v, p->q_sf, p->k_sf, p->v_sf, p->out};
+  const void* ptrs[] = {p->q, p->k, p->v, p->out};
   for (const void* q : ptrs)
     if (!aligned16(q)) return -FA4_E_ALIGN;
+  if (!linear_sf && (!aligned16(p->q_sf) || !aligned16(p->k_sf) || !aligned16(p->v_sf))) return -FA4_E_ALIGN;
   const int64_t bstr[] = {p->q_stride_b, p->q_stride_s, p->q_stride_h, p->k_stride_b, p->k_stride_s,
                           p->k_stride_h, p->v_stride_b, p->v_stride_h, p->v_stride_d};
   for (int64_t s : bstr)
@@ -178,14 +218,12 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
   // otherwise
   const bool cached = cache.seqused_k != nullptr || cache.page_table != nullptr;
   const bool takes64 = num_splits == 1;   // what the 64-key kernel can run
-  const bool plain = takes64;
   int variant = p->variant;
-  if (variant == FA4_VARIANT_AUTO) variant = plain ? FA4_VARIANT_WS64 : FA4_VARIANT_WS;
+  if (variant == FA4_VARIANT_AUTO) variant = takes64 ? FA4_VARIANT_WS64 : FA4_VARIANT_WS;
   if (variant != FA4_VARIANT_SERIAL && variant != FA4_VARIANT_WS && variant != FA4_VARIANT_WS64 &&
       variant != FA4_VARIANT_DECODE)
     return -FA4_E_VARIANT;
   const bool decode = variant == FA4_VARIANT_DECODE;
-  const int dec_rows = p->Sq * (p->Hq / p->Hkv);
   if (decode) {
     // a handful of query rows per kv head, head dim 128, causal or unmasked; always through the
     // partial-output workspace and the combine kernel
@@ -200,16 +238,39 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
   // window limits: `causal` is the right limit 0; an explicit right limit overrides it
   if (p->causal && win_right < 0) win_right = 0;
   const bool local = win_left >= 0 || win_right > 0;
-  const bool general = local || num_splits > 1 || sink != nullptr || softcap > 0.f || cached;
-  if ((local || sink != nullptr || softcap > 0.f || cached) && variant == FA4_VARIANT_SERIAL) return -FA4_E_VARIANT;
+  if ((local || sink != nullptr || softcap > 0.f || cached || num_splits > 1) && variant == FA4_VARIANT_SERIAL)
+    return -FA4_E_VARIANT;
   if (num_splits > 1) {
-    if (variant == FA4_VARIANT_SERIAL) return -FA4_E_VARIANT;
     if (workspace == nullptr) return -FA4_E_NULL;
     if (!aligned16(workspace)) return -FA4_E_ALIGN;
     if (workspace_bytes < (uint64_t)splitkv_bytes(p, num_splits)) return -FA4_E_TOO_LARGE;
     if ((int64_t)((p->Sq + kBlockM - 1) / kBlockM) * p->Hq * p->B * num_splits > 0x7fffffffLL)
       return -FA4_E_SHAPE;
   }
+  plan->variant = variant;
+  plan->win_left = win_left;
+  plan->win_right = win_right;
+  plan->decode = decode;
+  plan->d192 = d192;
+  plan->local = local;
+  plan->cached = cached;
+  plan->general = local || num_splits > 1 || sink != nullptr || softcap > 0.f || cached;
+  plan->dec_rows = p->Sq * (p->Hq / p->Hkv);
+  return 0;
+}
+
+int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint64_t workspace_bytes,
+               int win_left, int win_right, const float* sink, float softcap, const CacheView& cache,
+               void* cuda_stream) {
+  FwdPlan plan;
+  if (int e = validate_fwd(p, num_splits, workspace, workspace_bytes, win_left, win_right, sink, softcap, cache,
+                           false, &plan))
+    return e;
+  const int variant = plan.variant;
+  const bool decode = plan.decode, local = plan.local, general = plan.general, cached = plan.cached;
+  const int dec_rows = plan.dec_rows;
+  win_left = plan.win_left;
+  win_right = plan.win_right;
 
   CUtensorMap tm_q, tm_k, tm_v;
   {
@@ -243,6 +304,7 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
   kp.out = static_cast<__nv_bfloat16*>(p->out);
   kp.lse = p->lse;
   kp.status = p->status;
+  kp.epoch = next_launch_epoch();
   kp.o_stride_b = p->o_stride_b;
   kp.o_stride_s = p->o_stride_s;
   kp.o_stride_h = p->o_stride_h;
@@ -325,16 +387,14 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
       if (!encode_out_4d(&tm_o, p->out, d_o, s_o)) return -FA4_E_TENSORMAP;
     }
     auto launch = [&](auto kernel) -> int {
-      if (int e = ensure_smem(kernel, ws::kSmemRequest)) return e;
-      if (int e = ensure_launch_regs(kernel, ws::kRegsLaunch)) return e;
+      if (int e = ensure_kernel(kernel, ws::kSmemRequest, ws::kRegsLaunch)) return e;
       kernel<<<grid, ws::kThreads, ws::kSmemRequest, stream>>>(tm_q, tm_k, tm_v, tm_o, kp);
       return 0;
     };
     int rc;
     if (variant == FA4_VARIANT_WS64) {
       auto launch64 = [&](auto kernel) -> int {
-        if (int e = ensure_smem(kernel, ws64::kSmemRequest)) return e;
-        if (int e = ensure_launch_regs(kernel, ws64::kRegsLaunch)) return e;
+        if (int e = ensure_kernel(kernel, ws64::kSmemRequest, ws64::kRegsLaunch)) return e;
         kernel<<<grid, ws64::kThreads, ws64::kSmemRequest, stream>>>(tm_q, tm_k, tm_v, tm_o, kp);
         return 0;
       };
@@ -542,34 +602,14 @@ extern "C" int fa4_nvfp4_debug_wait_expiry(uint32_t* status, uint64_t budget_ns,
 // device.  For them the scratch lives in the library image instead: one fixed array per GPU,
 // resident from the moment the library is loaded on that GPU until the process exits.
 //
-// The array name below is only a host-side handle; the device address is looked up once per
-// device with cudaGetSymbolAddress and cached.
+// The array name below is only a host-side handle; every call asks the runtime for the device
+// address on the current device (cudaGetSymbolAddress), so a pointer from before a
+// cudaDeviceReset is never reused.
 // ---------------------------------------------------------------------------------------------
 #define FA4_STATIC_SCRATCH_BYTES (16u << 20)
 static __device__ __align__(256) uint8_t g_sf_scratch[FA4_STATIC_SCRATCH_BYTES];
 
 namespace {
-constexpr int kMaxDevices = 64;
-std::mutex g_scratch_mutex;
-uint8_t* g_scratch_addr[kMaxDevices] = {};
-
-// Device address of g_sf_scratch on the CURRENT device (looked up on first use per device).
-int scratch_address(uint8_t** out) {
-  int dev = -1;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) return (int)e;
-  if (dev < 0 || dev >= kMaxDevices) return -FA4_E_SHAPE;
-  std::lock_guard<std::mutex> lock(g_scratch_mutex);
-  if (g_scratch_addr[dev] == nullptr) {
-    void* ptr = nullptr;
-    e = cudaGetSymbolAddress(&ptr, g_sf_scratch);
-    if (e != cudaSuccess) return (int)e;
-    g_scratch_addr[dev] = static_cast<uint8_t*>(ptr);
-  }
-  *out = g_scratch_addr[dev];
-  return 0;
-}
-
 inline int64_t tiled_sf_bytes(int64_t n_mats, int64_t rows, int64_t cols, int64_t ct_multiple) {
   const int64_t ct = ((cols + 3) / 4 + ct_multiple - 1) / ct_multiple * ct_multiple;
   return n_mats * ((rows + 127) / 128) * ct * 512;
@@ -577,20 +617,23 @@ inline int64_t tiled_sf_bytes(int64_t n_mats, int64_t rows, int64_t cols, int64_
 }  // namespace
 
 extern "C" int fa4_nvfp4_fwd_linear_sf_noalloc(const fa4_nvfp4_params* p, void* cuda_stream) {
-  if (p == nullptr) return -FA4_E_NULL;
-  if (p->struct_size != sizeof(fa4_nvfp4_params)) return -FA4_E_STRUCT;
-  if (!p->q_sf || !p->k_sf || !p->v_sf) return -FA4_E_NULL;
-  if (p->B <= 0 || p->Sq <= 0 || p->Sk <= 0 || p->Hq <= 0 || p->Hkv <= 0 || p->D <= 0 || p->Dv <= 0)
-    return -FA4_E_SHAPE;
-  if (p->D % 16 != 0 || p->Sk % 16 != 0) return -FA4_E_SHAPE;
+  // 1. every host-side check of the forward itself, before anything touches the GPU or the
+  //    shared array: a negative return means nothing was launched and nothing was overwritten
+  FwdPlan plan;
+  if (int e = validate_fwd(p, 1, nullptr, 0, -1, -1, nullptr, 0.f, CacheView{}, /*linear_sf=*/true, &plan))
+    return e;
+  if (plan.variant == FA4_VARIANT_DECODE) return -FA4_E_VARIANT;   // needs a caller-owned workspace
+  // 2. capacity of the array
   const int64_t q_bytes = tiled_sf_bytes((int64_t)p->B * p->Hq, p->Sq, p->D / 16, 1);
   const int64_t k_bytes = tiled_sf_bytes((int64_t)p->B * p->Hkv, p->Sk, p->D / 16, 1);
   const int64_t v_bytes = tiled_sf_bytes((int64_t)p->B * p->Hkv, p->Dv, p->Sk / 16, 2);
   if (q_bytes + k_bytes + v_bytes > (int64_t)FA4_STATIC_SCRATCH_BYTES) return -FA4_E_TOO_LARGE;
 
-  uint8_t* scratch = nullptr;
-  if (int e = scratch_address(&scratch)) return e;
-  uint8_t* q_t = scratch;
+  // 3. device address of the array on the current device
+  void* sym = nullptr;
+  const cudaError_t se = cudaGetSymbolAddress(&sym, g_sf_scratch);
+  if (se != cudaSuccess) return (int)se;
+  uint8_t* q_t = static_cast<uint8_t*>(sym);
   uint8_t* k_t = q_t + q_bytes;   // multiples of 512: every region stays 256-byte aligned
   uint8_t* v_t = k_t + k_bytes;
 

@@ -26,6 +26,7 @@ struct KernelParams {
   float sl2;        // softmax_scale * q_scale * k_scale * log2(e)
   float out_scale;  // v_scale
   uint64_t budget_ns;
+  uint32_t epoch;   // launch epoch (0..255): a failure in the status word stops only the launch that recorded it
   // split-KV (num_splits > 1): every (tile, split) pair is a work item that visits a contiguous
   // share of the tile's K/V blocks and writes a normalised fp32 partial O and a partial LSE;
   // combine_splits_kernel merges them (flash_attn/cute/interface.py:494-510,804-812 and

@@ -149,7 +149,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
-  const WaitCtx wc{s_abort, p.status, p.budget_ns};
+  const WaitCtx wc{s_abort, p.status, p.budget_ns, p.epoch};
   const int R = p.Sq * p.group;  // live query rows (<= 16)
 
   // this CTA's share of the entry's K/V blocks (ascending, contiguous, ceil division like the

@@ -43,7 +43,7 @@ attn_fwd_serial_kernel(const __grid_constant__ CUtensorMap tm_q,
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
-  const WaitCtx wc{s_abort, p.status, p.budget_ns};
+  const WaitCtx wc{s_abort, p.status, p.budget_ns, p.epoch};
 
   if (tid == 0) {
     *s_abort = 0u;
@@ -64,7 +64,7 @@ attn_fwd_serial_kernel(const __grid_constant__ CUtensorMap tm_q,
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
   // a CTA that starts after an earlier one failed does nothing
-  const bool poisoned = (p.status != nullptr) && (*reinterpret_cast<volatile uint32_t*>(p.status) != 0u);
+  const bool poisoned = status_poisoned(p.status, p.epoch);
 
   const Tile t = decode_tile(p, blockIdx.x);
   const int row = tid;  // tile row == tensor-memory lane

@@ -330,7 +330,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  const WaitCtx wc{s_abort, p.status, p.budget_ns};
+  const WaitCtx wc{s_abort, p.status, p.budget_ns, p.epoch};
   const int num_tiles = p.num_m_blocks * p.Hq * p.B * (kGeneral ? p.num_splits : 1);
   const int ncta = gridDim.x, cta = blockIdx.x;
 
@@ -397,7 +397,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         const Tile t = decode_tile<kGeneral>(p, tile);
         const int n = t.n_blocks;
         if (n == 0) continue;
-        if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
+        if (status_poisoned(p.status, p.epoch)) {
           *s_abort = 1u;  // another CTA failed: stop this one quickly
           break;
         }
@@ -492,7 +492,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         const Tile t = decode_tile<kGeneral>(p, tile);
         const int n = t.n_blocks;
         if (n == 0) continue;
-        if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
+        if (status_poisoned(p.status, p.epoch)) {
           *s_abort = 1u;  // another CTA failed: stop this one quickly
           break;
         }
@@ -547,7 +547,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         const Tile t = decode_tile<kGeneral>(p, tile);
         const int n = t.n_blocks;
         if (n == 0) continue;
-        if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
+        if (status_poisoned(p.status, p.epoch)) {
           *s_abort = 1u;  // another CTA failed: stop this one quickly
           break;
         }
@@ -625,7 +625,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
       const Tile t = decode_tile<kGeneral>(p, tile);
       const int n = t.n_blocks;
       if (n == 0) continue;
-      if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
+      if (status_poisoned(p.status, p.epoch)) {
           *s_abort = 1u;  // another CTA failed: stop this one quickly
           break;
         }
@@ -717,7 +717,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
       const Tile t = decode_tile<kGeneral>(p, tile);
       const int n = t.n_blocks;
       const bool poisoned =
-          (p.status != nullptr) && (*reinterpret_cast<volatile uint32_t*>(p.status) != 0u);
+          status_poisoned(p.status, p.epoch);
       if (poisoned) {
         *s_abort = 1u;
         break;

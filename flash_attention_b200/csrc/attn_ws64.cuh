@@ -184,7 +184,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  const WaitCtx wc{s_abort, p.status, p.budget_ns};
+  const WaitCtx wc{s_abort, p.status, p.budget_ns, p.epoch};
   const int num_tiles = p.num_m_blocks * p.Hq * p.B;
   const int ncta = gridDim.x, cta = blockIdx.x;
   FA4_TRACE_DECL
@@ -288,7 +288,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
     FA4_FOR_EACH_TILE {
       const Tile t = decode_tile<kWindow || kCache>(p, tile);
       const int n = t.n_blocks;
-      if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
+      if (status_poisoned(p.status, p.epoch)) {
         *s_abort = 1u;
         break;
       }
@@ -385,7 +385,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
         const Tile t = decode_tile<kWindow || kCache>(p, tile);
         const int n = t.n_blocks;
         if (n == 0) continue;
-        if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
+        if (status_poisoned(p.status, p.epoch)) {
           *s_abort = 1u;  // another CTA failed: stop this one quickly
           break;
         }
@@ -477,7 +477,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
         const Tile t = decode_tile<kWindow || kCache>(p, tile);
         const int n = t.n_blocks;
         if (n == 0) continue;
-        if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
+        if (status_poisoned(p.status, p.epoch)) {
           *s_abort = 1u;
           break;
         }
@@ -542,7 +542,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
         const Tile t = decode_tile<kWindow || kCache>(p, tile);
         const int n = t.n_blocks;
         if (n == 0) continue;
-        if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
+        if (status_poisoned(p.status, p.epoch)) {
           *s_abort = 1u;
           break;
         }
@@ -600,7 +600,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
         const Tile t = decode_tile<kWindow || kCache>(p, tile);
         const int n = t.n_blocks;
         if (n == 0) continue;
-        if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
+        if (status_poisoned(p.status, p.epoch)) {
           *s_abort = 1u;
           break;
         }
@@ -648,7 +648,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
       const Tile t = decode_tile<kWindow || kCache>(p, tile);
       const int n = t.n_blocks;
       const bool poisoned =
-          (p.status != nullptr) && (*reinterpret_cast<volatile uint32_t*>(p.status) != 0u);
+          status_poisoned(p.status, p.epoch);
       if (poisoned) {
         *s_abort = 1u;
         break;

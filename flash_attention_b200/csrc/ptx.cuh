@@ -10,6 +10,11 @@ namespace fa4 {
 
 // ---------------------------------------------------------------------------------------------
 // status word (global) + abort flag (shared): the no-hang contract
+//
+// Status word: (code << 24) | (site << 16) | (launch epoch << 8) | (blockIdx.x & 0xff).  The first
+// failure stays in the word until the host reads and clears it (compare-and-swap from 0), but it
+// stops only the CTAs of the launch that recorded it: a later launch carries another epoch (the
+// host counts launches modulo 256) and runs normally beside a stale word.
 // ---------------------------------------------------------------------------------------------
 constexpr uint32_t kStatusWaitExpired = 1u;
 
@@ -17,7 +22,15 @@ struct WaitCtx {
   volatile uint32_t* s_abort;  // shared-memory flag, set by the first role that gives up
   uint32_t* g_status;          // device status word (may be null)
   uint64_t budget_ns;          // limit of one wait
+  uint32_t epoch = 0;          // launch epoch (0..255) recorded with a failure
 };
+
+// True when the status word holds a failure recorded by THIS launch (another CTA gave up).
+__device__ __forceinline__ bool status_poisoned(const uint32_t* g_status, uint32_t epoch) {
+  if (g_status == nullptr) return false;
+  const uint32_t v = *reinterpret_cast<const volatile uint32_t*>(g_status);
+  return v != 0u && ((v >> 8) & 0xffu) == epoch;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -32,7 +45,8 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 __device__ __forceinline__ void report_status(const WaitCtx& w, uint32_t code, uint32_t site) {
   *w.s_abort = 1u;
   if (w.g_status != nullptr) {
-    atomicCAS(w.g_status, 0u, (code << 24) | ((site & 0xffu) << 16) | (blockIdx.x & 0xffffu));
+    atomicCAS(w.g_status, 0u,
+              (code << 24) | ((site & 0xffu) << 16) | ((w.epoch & 0xffu) << 8) | (blockIdx.x & 0xffu));
   }
 }
 

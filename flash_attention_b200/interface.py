@@ -57,6 +57,10 @@ class DeviceStatus:
 
     The word is checked lazily: :func:`check_status` reads it back (one small copy, which
     synchronises) and raises if a kernel gave up; the attention call itself never synchronises.
+    A launch whose wait ran out leaves its outputs unwritten and returns normally, like any
+    asynchronous CUDA failure: call :func:`check_status` wherever results are consumed on the host.
+    The word keeps the first failure until it is read, but only the launch that recorded it stops
+    early (the kernels compare a per-launch epoch), so later calls are not affected by a stale word.
     """
     _words = {}
 
@@ -77,9 +81,9 @@ def check_status(device=None) -> None:
     v = int(w.item()) & 0xFFFFFFFF
     if v != 0:
         w.zero_()
-        code, site, blk = v >> 24, (v >> 16) & 0xFF, v & 0xFFFF
+        code, site, epoch, blk = v >> 24, (v >> 16) & 0xFF, (v >> 8) & 0xFF, v & 0xFF
         raise RuntimeError(f"fa4_nvfp4 kernel failure: code {code} (1 = bounded wait expired), "
-                           f"wait site {site}, block {blk}")
+                           f"wait site {site}, launch epoch {epoch}, block {blk} (mod 256)")
 
 
 def flash_attn_fp4_func(
@@ -133,9 +137,10 @@ def flash_attn_fp4_func(
     of 128; the logical key length is ``pages_per_seq * page_size``.  Scale bytes of unused
     cache slots must not be NaN encodings (a zero-filled cache is fine).
 
-    Built so far: D = Dv = 128 or 64, or (D, Dv) = (192, 128) without split / window / sink / cache; any Sq; Sk a multiple of 32 (partial last tiles are handled by
-    zero-filled loads, a key-length mask and unstored rows).  Anything else raises
-    ``NotImplementedError`` before a launch.
+    Built so far: D = Dv = 128 or 64, or (D, Dv) = (192, 128) (every feature but split-KV and the
+    decode kernel); any Sq; Sk a multiple of 32 (partial last tiles are handled by zero-filled
+    loads, a key-length mask and unstored rows).  Anything else raises ``NotImplementedError``
+    before a launch.
     """
     q, k, v = _as_u8(q, "q"), _as_u8(k, "k"), _as_u8(v, "v")
     q_sf, k_sf, v_sf = _as_u8(q_sf, "q_sf"), _as_u8(k_sf, "k_sf"), _as_u8(v_sf, "v_sf")
@@ -292,16 +297,16 @@ def choose_decode_splits(B: int, Hkv: int, Sk: int, device=None) -> int:
 def resolve_window(causal: bool, window_size) -> Tuple[bool, Optional[int], Optional[int]]:
     """(causal, left, right) after the reference's rules (flash_attn/cute/interface.py:256-276):
     causal sets right = 0; a window whose two limits sum to less than zero means no window;
-    (None, 0) is plain causal."""
+    (None, 0) is plain causal.  One difference: the reference keeps a negative limit whose partner
+    outweighs it (a band shifted off the diagonal, e.g. (-2, 5)); the C ABI encodes "no limit" as
+    -1, so such windows raise ``NotImplementedError`` here instead."""
     left, right = window_size
     if causal:
         right = 0
     if left is not None and right is not None and left + right < 0:
         left, right = None, None
-    if left is not None and left < 0:
-        left = None
-    if right is not None and right < 0:
-        raise NotImplementedError("negative window_size_right with an unlimited left side is not built")
+    if (left is not None and left < 0) or (right is not None and right < 0):
+        raise NotImplementedError("negative window limits (a band shifted off the diagonal) are not built")
     return right == 0 and left is None, left, right
 
 

@@ -62,7 +62,14 @@ enum {
   FA4_E_BUILD = 9        /* the library was compiled with a register count its kernels cannot run with */
 };
 
-/* device status word: 0 = ok; otherwise (code << 24) | (site << 16) | (blockIdx.x & 0xffff) */
+/* device status word: 0 = ok; otherwise
+ *     (code << 24) | (site << 16) | (launch epoch << 8) | (blockIdx.x & 0xff).
+ * The word is sticky for REPORTING: the first failure stays until the host reads and clears it.
+ * It is not sticky for EXECUTION: every launch carries an epoch (the library counts launches
+ * modulo 256) and only CTAs of the launch that recorded the failure stop early, so a stale word
+ * does not disturb later calls.  A launch that gave up leaves (part of) its outputs unwritten
+ * and the entry point has long returned 0 by then, as with any asynchronous CUDA failure: read
+ * the word wherever results are consumed on the host. */
 enum {
   FA4_S_OK = 0,
   FA4_S_WAIT_EXPIRED = 1 /* a bounded mbarrier wait ran out; `site` names the wait */
@@ -116,10 +123,11 @@ typedef struct fa4_nvfp4_params {
  * NVFP4 attention forward.  Replaces the compiled-kernel call of the reference
  * (flash_attn/cute/interface.py:785-803).  Asynchronous on `cuda_stream`
  * (a cudaStream_t; NULL = legacy default stream), no host synchronisation.
- * Shapes built: D == Dv in {128, 64} (the reference's table is
- * flash_attn/cute/interface.py:84-99; fa4_nvfp4_query lists them), any Sq,
- * Sk a multiple of 32, Hq a multiple of Hkv; everything else returns -FA4_E_SHAPE.
- * FA4_VARIANT_SERIAL (the bring-up kernel) exists for D = 128 only.
+ * Shapes built: (D, Dv) = (128, 128), (64, 64) or (192, 128) (the reference's table is
+ * flash_attn/cute/interface.py:84-99; fa4_nvfp4_query lists D), any Sq, Sk a multiple of 32,
+ * Hq a multiple of Hkv; everything else returns -FA4_E_SHAPE.  (192, 128) runs on the 64-key
+ * kernel only (no split-KV, no decode variant); FA4_VARIANT_SERIAL (the bring-up kernel)
+ * exists for D = 128 only.
  */
 int fa4_nvfp4_fwd(const fa4_nvfp4_params* p, void* cuda_stream);
 
@@ -133,7 +141,8 @@ int fa4_nvfp4_fwd(const fa4_nvfp4_params* p, void* cuda_stream);
  * Sq (decode) this is what fills the GPU: without it there are only B * Hq * ceil(Sq/128) work
  * items.  `workspace`: caller-owned device memory, 16-byte aligned, at least
  * fa4_nvfp4_splitkv_workspace_bytes(p, num_splits) bytes (= num_splits * B * Sq * Hq * (Dv + 1)
- * floats; 0 for num_splits = 1, in which case this is fa4_nvfp4_fwd).  WS variant only.
+ * floats; 0 for num_splits = 1, in which case this is fa4_nvfp4_fwd).  Split calls run the
+ * 128-key kernel (FA4_VARIANT_WS) or the decode kernel; D = 128 and 64.
  */
 int64_t fa4_nvfp4_splitkv_workspace_bytes(const fa4_nvfp4_params* p, int32_t num_splits);
 int fa4_nvfp4_fwd_splitkv(const fa4_nvfp4_params* p, int32_t num_splits, void* workspace,
@@ -145,7 +154,9 @@ int fa4_nvfp4_fwd_splitkv(const fa4_nvfp4_params* p, int32_t num_splits, void* w
  * semantics flash_attn/cute/testing.py:249-288, mask.py:487-527): query row i sees keys j with
  *     i + Sk - Sq - window_left <= j <= i + Sk - Sq + window_right,     -1 = no limit.
  * p->causal is the right limit 0 (an explicit window_right >= 0 takes its place).  Tiles skip
- * the K/V blocks that lie wholly outside the window of all their rows.  WS variant only.
+ * the K/V blocks that lie wholly outside the window of all their rows.  Windows, sinks, the soft
+ * cap and KV-cache views run on the 64-key kernel (every head dim) when the call does not split
+ * the keys, and on the 128-key kernel (D = 128, 64) when it does.
  */
 typedef struct fa4_nvfp4_ext {
   uint32_t struct_size;     /* = sizeof(fa4_nvfp4_ext) */
@@ -294,8 +305,13 @@ int fa4_nvfp4_debug_wait_expiry(uint32_t* status, uint64_t budget_ns, void* cuda
  *  - the three tiled scale-factor tensors together must fit: sum over q, k, v of
  *    matrices * ceil(rows/128) * column tiles * 512 bytes <= 16 MiB, else -FA4_E_TOO_LARGE
  *    (B=4, Hq=32, Hkv=8, S=8192, D=128 needs 12 MiB);
- *  - the first call on a device looks the array's device address up (cudaGetSymbolAddress, with
- *    that device current); make that first call outside any stream capture;
+ *  - the call is validated exactly like fa4_nvfp4_fwd BEFORE anything is launched: a negative
+ *    return means no kernel ran and the array was not touched.  FA4_VARIANT_DECODE is refused
+ *    (it needs a caller-owned workspace);
+ *  - every call asks the runtime for the array's device address on the current device
+ *    (cudaGetSymbolAddress; no pointer is kept across calls, so a cudaDeviceReset in between is
+ *    harmless).  The first call on a device also loads the library image there: make that first
+ *    call outside any stream capture;
  *  - all calls on a device share the one array, and it keeps whatever the previous call left
  *    there.  Each call rewrites every byte it later reads (padding included), so nothing has to
  *    be cleared, but two calls that overlap on the GPU (different streams without an ordering

@@ -39,9 +39,11 @@ def make_qkv(B, Sq, Sk, Hq, Hkv, D, seed, v_std=1.0, outlier_frac=0.0, device="c
 
 
 def kernel_model(D, num_splits=1, window=(None, None), sink=None, variant=0, softcap=0.0, rows=None):
-    """Which kernel the library's automatic choice runs, as oracle B keywords: the 64-key kernel
-    without split-KV and windows (sinks and the soft cap included), the 128-key kernel otherwise (mirrors
-    launch_fwd in csrc/api.cu).  ``variant`` 1 / 2 force the 128-key model, 3 the 64-key one."""
+    """Which kernel the library's automatic choice runs, as oracle B keywords: the decode kernel
+    for a handful of query rows, the 64-key kernel for every other call that does not split the
+    keys (windows, sinks, the soft cap and KV-cache views included), the 128-key kernel for split
+    calls (mirrors validate_fwd in csrc/api.cu).  ``variant`` 1 / 2 force the 128-key model, 3 the
+    64-key one, 4 the decode kernel's."""
     plain = num_splits == 1
     # decode / append shapes: the transposed kernel, 128-key steps upwards, any number of splits
     decode_ok = (D == 128 and rows is not None and rows <= 16 and window in ((None, None), (None, 0))

@@ -5,8 +5,9 @@ all of it, or their steady-state loop forbids the allocator because cudaMalloc s
 device).  For them the scratch that the linear-scale-factor route needs sits in a fixed array
 inside the library.  This file checks, through the C ABI, that the entry point gives exactly the
 bits of the regular route, twice in a row with different problems (the array keeps the previous
-call's contents, so the second call would show stale data if anything were left unwritten), and
-that it refuses a problem whose scale factors exceed the array.
+call's contents, so a later call would show stale data if anything were left unwritten), that a
+call the forward would reject is rejected before any kernel runs, and that it refuses a problem
+whose scale factors exceed the array.
 
 Named test_zz_* so that pytest collects it last."""
 import ctypes
@@ -19,10 +20,8 @@ from flash_attention_b200 import _lib
 from flash_attention_b200.interface import DeviceStatus
 from tests.helpers import make_qkv
 
-pytestmark = pytest.mark.gpu
 
-
-def _params(Q, K, V, out, lse, causal, status):
+def _params(Q, K, V, out, lse, causal, status, D=128, Dv=128):
     B, Sq, Hq, _ = Q.data.shape
     _, Sk, Hkv, _ = K.data.shape
     p = _lib.Params()
@@ -35,45 +34,98 @@ def _params(Q, K, V, out, lse, causal, status):
     p.k_stride_b, p.k_stride_s, p.k_stride_h = K.data.stride(0), K.data.stride(1), K.data.stride(2)
     p.v_stride_b, p.v_stride_h, p.v_stride_d = V.data.stride(0), V.data.stride(1), V.data.stride(2)
     p.o_stride_b, p.o_stride_s, p.o_stride_h = out.stride(0), out.stride(1), out.stride(2)
-    p.B, p.Sq, p.Sk, p.Hq, p.Hkv, p.D, p.Dv = B, Sq, Sk, Hq, Hkv, 128, 128
+    p.B, p.Sq, p.Sk, p.Hq, p.Hkv, p.D, p.Dv = B, Sq, Sk, Hq, Hkv, D, Dv
     p.causal = 1 if causal else 0
     p.q_scale, p.k_scale, p.v_scale = Q.scale, K.scale, V.scale
-    p.softmax_scale = 128 ** -0.5
+    p.softmax_scale = D ** -0.5
     return p
 
 
+def _free_bytes(dev):
+    # free device memory as the driver sees it: an allocation made inside the library (which
+    # torch's own counters cannot see) would show here
+    torch.cuda.synchronize()
+    return torch.cuda.mem_get_info(dev)[0]
+
+
+@pytest.mark.gpu
 def test_noalloc_entry_matches_regular_entry_twice_in_a_row(cuda_device):
     dev = cuda_device
     L = fa.lib()
     stream = torch.cuda.current_stream(dev).cuda_stream
-    # the larger problem first, so that the second call finds the array full of other data
-    for (B, Sq, Sk, Hq, Hkv, causal, seed) in [(2, 512, 384, 4, 2, True, 21), (1, 128, 256, 2, 1, False, 22)]:
-        q, k, v = make_qkv(B, Sq, Sk, Hq, Hkv, 128, seed=seed, device=dev)
+    # The larger problem first, so that later calls find the array full of other data.  The
+    # ragged cases (rows and keys that do not fill their last tile, head dims 64 and (192, 128))
+    # read zero padding that each call has to rewrite over whatever the previous call left.
+    cases = [(2, 512, 384, 4, 2, 128, 128, True, 21), (1, 128, 256, 2, 1, 128, 128, False, 22),
+             (1, 200, 160, 4, 2, 64, 64, True, 23), (2, 72, 96, 2, 2, 192, 128, False, 24),
+             (1, 130, 32, 2, 1, 128, 128, False, 25)]
+    for (B, Sq, Sk, Hq, Hkv, D, Dv, causal, seed) in cases:
+        q, k, _ = make_qkv(B, Sq, Sk, Hq, Hkv, D, seed=seed, device=dev)
+        _, _, v = make_qkv(B, Sq, Sk, Hq, Hkv, Dv, seed=seed + 100, device=dev)
         Q, K, V = fa.quantize_qkv(q, k, v)
         assert Q.sf.is_contiguous() and K.sf.is_contiguous() and V.sf.is_contiguous()
         want_o, want_l = fa.flash_attn_fp4_func(Q.data, K.data, V.data, Q.sf, K.sf, V.sf, Q.scale,
                                                 K.scale, V.scale, causal=causal, return_lse=True)
-        out = torch.full((B, Sq, Hq, 128), float("nan"), dtype=torch.bfloat16, device=dev)
+        out = torch.full((B, Sq, Hq, Dv), float("nan"), dtype=torch.bfloat16, device=dev)
         lse = torch.full((B, Hq, Sq), float("nan"), dtype=torch.float32, device=dev)
         status = DeviceStatus.word(dev)
-        p = _params(Q, K, V, out, lse, causal, status)
-        before = torch.cuda.memory_allocated(dev)
+        p = _params(Q, K, V, out, lse, causal, status, D, Dv)
+        # warm the entry point once so that loading the library image on this device (a one-off
+        # cost of the first call) is not mistaken for a per-call allocation
+        assert L.fa4_nvfp4_fwd_linear_sf_noalloc(ctypes.byref(p), stream) == 0
+        before_torch, before_free = torch.cuda.memory_allocated(dev), _free_bytes(dev)
         rc = L.fa4_nvfp4_fwd_linear_sf_noalloc(ctypes.byref(p), stream)
         assert rc == 0
-        assert torch.cuda.memory_allocated(dev) == before      # nothing came from torch's allocator
-        torch.cuda.synchronize()
+        assert torch.cuda.memory_allocated(dev) == before_torch   # nothing from torch's allocator
+        assert _free_bytes(dev) >= before_free                    # nothing from cudaMalloc either
         fa.check_status(dev)
         # same kernels on the same bytes: tolerance zero
-        assert torch.equal(out, want_o) and torch.equal(lse, want_l)
+        assert torch.equal(out, want_o) and torch.equal(lse, want_l), (B, Sq, Sk, D)
+
+
+def _dummy_params():
+    """A call that fits the array and is well formed, on pointers that are never dereferenced by
+    the host-side checks."""
+    p = _lib.Params()
+    p.struct_size = ctypes.sizeof(_lib.Params)
+    for f in ("q", "k", "v", "q_sf", "k_sf", "v_sf", "out"):
+        setattr(p, f, 0x1000)
+    p.B, p.Sq, p.Sk, p.Hq, p.Hkv, p.D, p.Dv = 1, 128, 128, 2, 1, 128, 128
+    p.q_stride_b, p.q_stride_s, p.q_stride_h = 128 * 2 * 64, 2 * 64, 64
+    p.k_stride_b, p.k_stride_s, p.k_stride_h = 128 * 64, 64, 64
+    p.v_stride_b, p.v_stride_h, p.v_stride_d = 128 * 64, 128 * 64, 64
+    p.o_stride_b, p.o_stride_s, p.o_stride_h = 128 * 2 * 128, 2 * 128, 128
+    p.q_scale = p.k_scale = p.v_scale = 1.0
+    p.softmax_scale = 0.088
+    return p
+
+
+@pytest.mark.parametrize("field,value,code", [
+    ("q", 0, -1),                 # NULL operand
+    ("out", 0x1008, -4),          # misaligned output
+    ("D", 96, -2),                # head dim that is not built
+    ("Sk", 48, -2),               # keys not a multiple of 32
+    ("Hkv", 3, -2),               # Hq not a multiple of Hkv
+    ("k_stride_s", 8, -3),        # 8-byte stride
+    ("softmax_scale", 0.0, -2),
+    ("variant", 9, -5),
+    ("variant", 4, -2),           # decode variant on a prefill shape (and it would need a workspace)
+])
+def test_noalloc_entry_validates_the_forward_before_anything_runs(field, value, code):
+    """Runs without a GPU: the calls fit the array but are bad for the forward.  Every one must come back with its negative argument code.
+    Had the entry point started its layout kernels first, the result on a machine without a GPU
+    would be a positive CUDA error instead, and on a GPU the shared array would already have
+    been overwritten under a concurrent caller."""
+    L = fa.lib()
+    p = _dummy_params()
+    setattr(p, field, value)
+    assert L.fa4_nvfp4_fwd_linear_sf_noalloc(ctypes.byref(p), None) == code
 
 
 def test_noalloc_entry_rejects_what_does_not_fit():
     """Host-side checks only: no GPU work is started for a rejected call."""
     L = fa.lib()
-    p = _lib.Params()
-    p.struct_size = ctypes.sizeof(_lib.Params)
-    for f in ("q", "k", "v", "q_sf", "k_sf", "v_sf", "out"):
-        setattr(p, f, 0x1000)
+    p = _dummy_params()
     p.B, p.Sq, p.Sk, p.Hq, p.Hkv, p.D, p.Dv = 8, 8192, 8192, 32, 8, 128, 128   # 24 MiB of scales
     assert L.fa4_nvfp4_fwd_linear_sf_noalloc(ctypes.byref(p), None) == -8
     p.struct_size = 4
