@@ -259,6 +259,112 @@ def test_sampled_heads_of_cfg2_against_oracle(cuda_device):
         assert rel < 0.2, rel
 
 
+def _check_windows(Ql, Kl, Vl, out, lse, samples, causal, softmax_scale, group):
+    """Sampled (batch, head, first row) windows of 128 query rows of a full-size run against
+    (A) exact attention on the dequantised operands, in fp64 on the GPU, and (B) the oracle's
+    model of the 64-key kernel on the CPU.  A window of a causal Sq = Sk problem that starts at a
+    multiple of 128 is itself a causal problem (128 queries, bottom-right aligned against keys
+    0 .. r0 + 127) whose tile walks the same steps in the same order, so model B applies to it
+    unchanged.  Tolerances: tests/helpers.py (B: two bf16 roundings + 2^-7 max, rel-RMS 0.01;
+    A: 1.25 x the B-vs-A gap + 0.01; LSE 1e-3)."""
+    dev = out.device
+    S = Kl.data.shape[1]
+    D = Ql.data.shape[-1] * 2
+    for (b, h, r0) in samples:
+        hk = h // group
+        sk = r0 + 128 if causal else S
+        qd = fa.dequantize_lastdim(Ql.data[b, r0:r0 + 128, h], Ql.sf[b, r0:r0 + 128, h], Ql.scale)
+        kd = fa.dequantize_lastdim(Kl.data[b, :sk, hk], Kl.sf[b, :sk, hk], Kl.scale)
+        vd = fa.dequantize_lastdim(Vl.data[b, hk, :, :sk // 2], Vl.sf[b, hk, :, :sk // 16], Vl.scale).T   # (sk, Dv)
+        s = (qd.double() @ kd.double().T) * softmax_scale
+        if causal:
+            rows = torch.arange(r0, r0 + 128, device=dev)[:, None]
+            s = s.masked_fill(torch.arange(sk, device=dev)[None, :] > rows, float("-inf"))
+        la = torch.logsumexp(s, dim=-1).float().cpu()[None, None]                      # (1, 1, 128)
+        oa = (torch.softmax(s, dim=-1) @ vd.double()).float().cpu()[None, :, None]     # (1, 128, 1, Dv)
+        sl2 = float(torch.tensor(softmax_scale, dtype=torch.float32) * torch.tensor(Ql.scale, dtype=torch.float32)
+                    * torch.tensor(Kl.scale, dtype=torch.float32) * torch.tensor(1.4426950408889634, dtype=torch.float32))
+        ob, lb = orc.attention_oracle_b((qd / Ql.scale).cpu()[None, :, None], (kd / Kl.scale).cpu()[None, :, None],
+                                        (vd / Vl.scale).cpu()[None, :, None], sl2, Vl.scale, causal=causal,
+                                        step_keys=64, ascending=True)
+        got_o = out[b, r0:r0 + 128, h][None, :, None]
+        got_l = lse[b, h, r0:r0 + 128][None, None]
+        assert_parity(got_o, got_l, oa, la, ob, lb)
+
+
+def test_sampled_windows_of_cfg1_against_both_oracles(cuda_device):
+    """The non-causal benchmark configuration (B=4, H=32/32, S=4096, D=128) at full size: three
+    (batch, head, window) samples against exact attention and against the kernel model."""
+    B, S, H = 4, 4096, 32
+    q, k, v = make_qkv(B, S, S, H, H, 128, seed=0, device=cuda_device)
+    Ql, Kl, Vl = fa.quantize_qkv_fused(q, k, v)
+    del q, k, v
+    out, lse = fa.flash_attn_func(Ql, Kl, Vl, causal=False, return_lse=True)
+    torch.cuda.synchronize()
+    fa.check_status(cuda_device)
+    _check_windows(Ql, Kl, Vl, out, lse, [(0, 0, 0), (2, 17, 2048), (3, 31, S - 128)], False, 128 ** -0.5, 1)
+
+
+def test_sampled_windows_of_cfg2_against_the_kernel_model(cuda_device):
+    """The causal GQA benchmark configuration (B=4, Hq=32, Hkv=8, S=8192) at full size, held to
+    the tight bound against the kernel model too (first, a middle and the last tile)."""
+    B, S, Hq, Hkv = 4, 8192, 32, 8
+    q, k, v = make_qkv(B, S, S, Hq, Hkv, 128, seed=0, v_std=0.5, device=cuda_device)
+    Ql, Kl, Vl = fa.quantize_qkv_fused(q, k, v)
+    del q, k, v
+    out, lse = fa.flash_attn_func(Ql, Kl, Vl, causal=True, return_lse=True)
+    torch.cuda.synchronize()
+    fa.check_status(cuda_device)
+    _check_windows(Ql, Kl, Vl, out, lse, [(0, 0, 0), (1, 13, 3968), (3, 29, S - 128)], True, 128 ** -0.5, Hq // Hkv)
+
+
+@pytest.mark.parametrize("causal", [False, True], ids=["noncausal", "causal"])
+@pytest.mark.parametrize("S", [4096, 16384])
+@pytest.mark.parametrize("D,Dv", [(64, 64), (128, 128), (192, 128)], ids=["d64", "d128", "d192"])
+def test_sweep_shapes_at_size_against_both_oracles(cuda_device, D, Dv, S, causal):
+    """The head-dim / shape sweep at its real size (B = 8, H = 16, i.e. B * H = 128): thousands of
+    tiles per launch, several per CTA, the snake order over CTAs and the 32-byte-swizzled
+    sub-tiles of head dims 64 and 192.  First, a middle and the last tile of sampled (batch,
+    head) pairs against exact attention and the kernel model."""
+    B, H = 8, 16
+    g = torch.Generator(device=cuda_device).manual_seed(5)
+    q, k = (torch.randn(B, S, H, D, generator=g, device=cuda_device, dtype=torch.bfloat16) for _ in range(2))
+    v = torch.randn(B, S, H, Dv, generator=g, device=cuda_device, dtype=torch.bfloat16)
+    Ql, Kl, Vl = fa.quantize_qkv_fused(q, k, v)
+    del q, k, v
+    out, lse = fa.flash_attn_func(Ql, Kl, Vl, causal=causal, return_lse=True)
+    torch.cuda.synchronize()
+    fa.check_status(cuda_device)
+    assert torch.isfinite(out.float()).all() and torch.isfinite(lse).all()
+    _check_windows(Ql, Kl, Vl, out, lse, [(0, 0, 0), (5, 9, S // 2), (7, 15, S - 128)], causal, D ** -0.5, 1)
+
+
+@pytest.mark.parametrize("shape", [(1, 256, 256, 4, 2, True), (2, 2048, 2048, 16, 4, True),
+                                   (4, 1024, 1024, 32, 32, False)],
+                         ids=["small", "causal_several_tiles_per_cta", "noncausal_several_tiles_per_cta"])
+def test_a_thousand_runs_give_the_same_bits(cuda_device, shape):
+    """The reference's race / determinism loop (tests/cute/test_flash_attn_race_condition.py:310-344:
+    re-run 1000 times, torch.equal against the first result), on one small problem and on problems
+    with several tiles per CTA, where a missed barrier phase or a slot reused too early would show
+    as a changed bit sooner or later.  Differences are accumulated on the device and read once."""
+    B, Sq, Sk, Hq, Hkv, causal = shape
+    q, k, v = make_qkv(B, Sq, Sk, Hq, Hkv, 128, seed=31, device=cuda_device)
+    Q, K, V = fa.quantize_qkv_fused(q, k, v, linear_sf=False)
+    out0, lse0 = run(Q, K, V, causal)
+    out = torch.empty_like(out0)
+    lse = torch.empty_like(lse0)
+    bad = torch.zeros((), dtype=torch.int64, device=cuda_device)
+    for _ in range(1000):
+        fa.flash_attn_fp4_func(Q.data, K.data, V.data, Q.sf, K.sf, V.sf, Q.scale, K.scale, V.scale,
+                               causal=causal, return_lse=True, sf_layout="tiled", out=out, lse=lse)
+        bad += (out.view(torch.int16) != out0.view(torch.int16)).sum() + \
+               (lse.view(torch.int32) != lse0.view(torch.int32)).sum()
+        out.zero_()
+    torch.cuda.synchronize()
+    fa.check_status(cuda_device)
+    assert int(bad.item()) == 0
+
+
 @pytest.mark.parametrize("causal", [False, True])
 def test_host_pipeline_matches_the_single_call_bit_for_bit(cuda_device, causal):
     B, S, Hq, Hkv = 2, 640, 4, 2
