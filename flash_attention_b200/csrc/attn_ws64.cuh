@@ -288,10 +288,6 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
     FA4_FOR_EACH_TILE {
       const Tile t = decode_tile<kWindow || kCache>(p, tile);
       const int n = t.n_blocks;
-      if (status_poisoned(p.status, p.epoch)) {
-        *s_abort = 1u;
-        break;
-      }
       const int q_idx = t.m_blk * kBlockM + row;
       float scale = 0.f, m_fin = kNegInf, l_tot = 0.f;
       if (n > 0) {
@@ -386,7 +382,10 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
         const int n = t.n_blocks;
         if (n == 0) continue;
         if (status_poisoned(p.status, p.epoch)) {
-          *s_abort = 1u;  // another CTA failed: stop this one quickly
+          // another CTA of this launch failed: stop this one quickly.  Only this role polls the
+          // status word (a global load at every tile start); the others see the abort flag in
+          // their next wait, when the tiles stop coming
+          *s_abort = 1u;
           break;
         }
         const uint32_t qb = ti & 1;
@@ -477,10 +476,6 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
         const Tile t = decode_tile<kWindow || kCache>(p, tile);
         const int n = t.n_blocks;
         if (n == 0) continue;
-        if (status_poisoned(p.status, p.epoch)) {
-          *s_abort = 1u;
-          break;
-        }
         const uint32_t qb = ti & 1;
         ok = mbar_wait(bars.at(Bars::kQFull + qb), (ti >> 1) & 1, wc, kS64QFull);
         if (!ok) break;
@@ -542,10 +537,6 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
         const Tile t = decode_tile<kWindow || kCache>(p, tile);
         const int n = t.n_blocks;
         if (n == 0) continue;
-        if (status_poisoned(p.status, p.epoch)) {
-          *s_abort = 1u;
-          break;
-        }
         for (int i = 0; ok && i < n; ++i) {
           const uint32_t G = gb + i, st = G % kStagesV;
           FA4_PH(0);
@@ -600,10 +591,6 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
         const Tile t = decode_tile<kWindow || kCache>(p, tile);
         const int n = t.n_blocks;
         if (n == 0) continue;
-        if (status_poisoned(p.status, p.epoch)) {
-          *s_abort = 1u;
-          break;
-        }
         for (int step = 0; ok && step < n + 2; ++step) {
           const int ik = step, iv = step - 2;  // the producer's order
           if (ik < n) {
@@ -647,12 +634,6 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
     FA4_FOR_EACH_TILE {
       const Tile t = decode_tile<kWindow || kCache>(p, tile);
       const int n = t.n_blocks;
-      const bool poisoned =
-          status_poisoned(p.status, p.epoch);
-      if (poisoned) {
-        *s_abort = 1u;
-        break;
-      }
       float m_ref = kNegInf, l_sum = 0.f;
 
       for (int j = (wg - 2 * (int)gb) & 3; j < 2 * n; j += 4) {
@@ -681,6 +662,20 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
         float s[64];
         tmem_ld32(s_addr, reinterpret_cast<uint32_t*>(&s[0]));
         tmem_ld32(s_addr + 32, reinterpret_cast<uint32_t*>(&s[32]));
+        // While the scores travel (measured: 2.5 % of the kernel's time): the running reference,
+        // handed from the warpgroup of sub-block J - 1 to this one through shared memory (one float
+        // per row).  Every sub-block but the CTA's very first waits for its predecessor's hand-over,
+        // also the first one of a tile (which ignores the value): the unbroken chain is what orders
+        // the reuse of a slot -- the value of sub-block J is overwritten by J + 4, which follows
+        // J + 3, J + 2 and J + 1, and J + 1 has read it -- and keeps a barrier from running two
+        // phases ahead of its waiter.
+        float m_prev = kNegInf;
+        if (J > 0) {
+          const uint32_t pw = (uint32_t)(wg + 3) & 3u;
+          ok = __all_sync(0xffffffffu, mbar_wait(bars.at(Bars::kHand + 4 * pw + (warp & 3)), ((J - 1) / kSBufs) & 1, wc, kS64Hand));
+          if (!ok) break;
+          if (j > 0) m_prev = s_hand[pw * 128 + row];
+        }
         tc_wait_ld();
         tc_fence_before_sync();
         mbar_arrive(bars.at(Bars::kSFree + wg));
@@ -693,8 +688,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
           }
         }
 
-        // 2. maxima of the four 16-key blocks, then the running reference: it is handed from the
-        //    warpgroup of sub-block J - 1 to this one through shared memory (one float per row)
+        // 2. maxima of the four 16-key blocks, then the new reference
         float bm4[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -708,19 +702,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
           bm4[q] = fmaxf(m0, m1);
         }
         const float m_loc = fmaxf(fmaxf(bm4[0], bm4[1]), fmaxf(bm4[2], bm4[3]));
-        float m_prev = kNegInf;
         FA4_PH(2);
-        // Every sub-block but the CTA's very first waits for its predecessor's hand-over, also the
-        // first one of a tile (which ignores the value): the unbroken chain is what orders the
-        // reuse of a slot -- the value of sub-block J is overwritten by J + 4, which follows
-        // J + 3, J + 2 and J + 1, and J + 1 has read it -- and keeps a barrier from running two
-        // phases ahead of its waiter.
-        if (J > 0) {
-          const uint32_t pw = (uint32_t)(wg + 3) & 3u;
-          ok = __all_sync(0xffffffffu, mbar_wait(bars.at(Bars::kHand + 4 * pw + (warp & 3)), ((J - 1) / kSBufs) & 1, wc, kS64Hand));
-          if (!ok) break;
-          if (j > 0) m_prev = s_hand[pw * 128 + row];
-        }
         FA4_PH(6);
         const float m_new = next_reference(m_prev, m_loc, p.sl2);
         s_hand[wg * 128 + row] = m_new;
@@ -739,13 +721,19 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
         FA4_TRACE_EV(6, J);
         FA4_PH(4);
         uint8_t* p_tile = gbase + kOffP + slot * kPTileBytes;
-        uint4 chunk;
-        l_sum += quantize_pair(&s[0], noff4[0], noff4[1],
-                               __byte_perm(ue, 0u, 0x4440u), __byte_perm(ue, 0u, 0x4441u), p.sl2, chunk);
-        *reinterpret_cast<uint4*>(p_tile + sw32_offset(row, 0)) = chunk;
-        l_sum += quantize_pair(&s[32], noff4[2], noff4[3],
-                               __byte_perm(ue, 0u, 0x4442u), __byte_perm(ue, 0u, 0x4443u), p.sl2, chunk);
-        *reinterpret_cast<uint4*>(p_tile + sw32_offset(row, 1)) = chunk;
+        {
+          uint32_t pk[8];
+          float acc = 0.f;
+#pragma unroll
+          for (int b4 = 0; b4 < 4; ++b4) {
+            const float bsum = quantize_block16(&s[16 * b4], noff4[b4], p.sl2, pk[2 * b4], pk[2 * b4 + 1]);
+            // 2^e as fp32: byte (e + 127) moved into the exponent field
+            acc = fmaf(bsum, __uint_as_float(__byte_perm(ue, 0u, 0x4440u + b4) << 23), acc);
+          }
+          l_sum += acc;
+          *reinterpret_cast<uint4*>(p_tile + sw32_offset(row, 0)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          *reinterpret_cast<uint4*>(p_tile + sw32_offset(row, 1)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+        }
         // the four scale bytes of this row: one word of the 512-byte chunk
         *reinterpret_cast<uint32_t*>(gbase + kOffSFP + slot * 512 + (row & 31) * 16 + (row >> 5) * 4) =
             block_scale_bytes(ue);

@@ -166,6 +166,81 @@ __device__ __forceinline__ float quantize_pair(const float* s, float noff0, floa
   return acc;
 }
 
+// 2^x for a pair on the FMA pipe instead of the exponential unit (the reference mixes the two the
+// same way when the exponential unit bounds its kernel: flash_attn/cute/softmax.py:237-279, the
+// arithmetic in flash_attn/cute/utils.py:703-737).  Input is NOT x but y = sat((x + 126) / 256),
+// which one scalar FMA with the saturate modifier produces from the raw score: the clamp that
+// keeps masked (-inf) and hopelessly small scores out of the exponent arithmetic costs no
+// instruction of its own.  Steps, all packed two-wide:
+//   t = rd(256 y + (M - 126))     M = 1.5 * 2^23: the low mantissa bits of t hold k = floor(x)
+//   u = t - (M - 126)             = k + 126, exact
+//   f = 256 y - u                 = x - k in [0, 1), one rounding
+//   q = 1 + f (c1 + f (c2 + f c3))   minimax fit of 2^f on [0, 1), relative error 8.6e-5
+//   result bits = q bits + (t bits << 23)   (k added to the exponent field; k is in [-126, 2])
+// A clamped input gives 2^-126, which rounds to an e2m1 zero and adds nothing visible to a sum.
+constexpr float kEx2C1 = 0.6951167583465576f, kEx2C2 = 0.22764499485492706f, kEx2C3 = 0.07706703990697861f;
+constexpr float kEx2Magic = 12582912.f - 126.f;
+__device__ __forceinline__ float ex2_arg_sat(float s, float sl2_256, float c) {
+  float y;
+  asm("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(s), "f"(sl2_256), "f"(c));
+  return y;
+}
+__device__ __forceinline__ float2 ex2_emulated2(float2 y) {
+  const float2 k256 = make_float2(256.f, 256.f);
+  const float2 t = __ffma2_rd(y, k256, make_float2(kEx2Magic, kEx2Magic));
+  const float2 u = __fadd2_rn(t, make_float2(-kEx2Magic, -kEx2Magic));
+  const float2 f = __ffma2_rn(y, k256, make_float2(-u.x, -u.y));
+  float2 q = __ffma2_rn(make_float2(kEx2C3, kEx2C3), f, make_float2(kEx2C2, kEx2C2));
+  q = __ffma2_rn(q, f, make_float2(kEx2C1, kEx2C1));
+  q = __ffma2_rn(q, f, make_float2(1.f, 1.f));
+  uint32_t rx, ry;
+  // multiply-add on the FMA pipe (a shift + add would go to the ALU pipe, which the e2m1
+  // conversions already load)
+  asm("mad.lo.u32 %0, %1, 8388608, %2;" : "=r"(rx) : "r"(__float_as_uint(t.x)), "r"(__float_as_uint(q.x)));
+  asm("mad.lo.u32 %0, %1, 8388608, %2;" : "=r"(ry) : "r"(__float_as_uint(t.y)), "r"(__float_as_uint(q.y)));
+  return make_float2(__uint_as_float(rx), __uint_as_float(ry));
+}
+
+// Which of the 8 pairs of a 16-key block take the FMA-pipe exponential (bit j = pair j, keys 2j and
+// 2j + 1 of the block).  The share is a compile-time knob like the reference's ex2_emu_freq
+// (flash_attn/cute/flash_fwd_sm100.py:71-90).
+#ifndef FA4_EX2_EMU_MASK
+#define FA4_EX2_EMU_MASK 0x00u
+#endif
+constexpr uint32_t kEx2EmuMask = FA4_EX2_EMU_MASK;
+
+// Quantise one block of 16 scores of a row: 8 packed e2m1 bytes (two words); returns the block's
+// sum of p' / 2^e (un-rounded; the caller multiplies by the block scale).
+template <uint32_t kEmuMask = kEx2EmuMask>
+__device__ __forceinline__ float quantize_block16(const float* s, float noff, float sl2,
+                                                  uint32_t& pk0, uint32_t& pk1) {
+  const float2 sl2_2 = make_float2(sl2, sl2);
+  const float2 noff2 = make_float2(noff, noff);
+  const float sl2_256 = sl2 * (1.f / 256.f);
+  const float c_sat = fmaf(noff, 1.f / 256.f, 126.f / 256.f);
+  float2 p[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    if ((kEmuMask >> j) & 1u) {
+      p[j] = ex2_emulated2(make_float2(ex2_arg_sat(s[2 * j], sl2_256, c_sat),
+                                       ex2_arg_sat(s[2 * j + 1], sl2_256, c_sat)));
+    } else {
+      const float2 x = __ffma2_rn(make_float2(s[2 * j], s[2 * j + 1]), sl2_2, noff2);
+      p[j] = make_float2(ex2_approx(x.x), ex2_approx(x.y));
+    }
+  }
+  float2 sum_a = __fadd2_rn(p[0], p[1]);
+  float2 sum_b = __fadd2_rn(p[2], p[3]);
+  sum_a = __fadd2_rn(sum_a, p[4]);
+  sum_b = __fadd2_rn(sum_b, p[5]);
+  sum_a = __fadd2_rn(sum_a, p[6]);
+  sum_b = __fadd2_rn(sum_b, p[7]);
+  sum_a = __fadd2_rn(sum_a, sum_b);
+  pk0 = pack8_e2m1(p[0].x, p[0].y, p[1].x, p[1].y, p[2].x, p[2].y, p[3].x, p[3].y);
+  pk1 = pack8_e2m1(p[4].x, p[4].y, p[5].x, p[5].y, p[6].x, p[6].y, p[7].x, p[7].y);
+  return sum_a.x + sum_a.y;
+}
+
 // Quantise one row of 128 scores with the exponents from block_exponents() and store it as one
 // row of the P tile (K-major, 64-byte rows, 64-byte swizzle), one 16-byte chunk at a time.
 // Returns the row's sum of p' (un-rounded), to be added to the running sum.
