@@ -3,11 +3,16 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg2] [--impl ours|reference]
 
-One "step" is one forward over the whole workload held by a rank.  At N = 1 the workload is the
-causal GQA prefill configuration (B=4, Hq=32, Hkv=8, S=8192, D=128, the one the 50 %-of-FP4-peak
-target is quoted on).  With N > 1 (launched by torch.distributed.run, one rank per GPU) every rank
-holds one such workload -- the (batch, kv-head) units of a global batch of 4 N -- and nothing is
-exchanged on the data path: weak scaling, value = total FLOPs of all ranks / max-over-ranks time.
+One "step" is one forward over the (batch, kv-head) units a rank holds.  At N = 1 the workload is
+the causal GQA prefill configuration (B=4, Hq=32, Hkv=8, S=8192, D=128, the one the 50 %-of-FP4-peak
+target is quoted on).  With N > 1 (launched by torch.distributed.run, one rank per GPU) the SAME
+problem is dealt over the ranks: it is quantised once (tensor scales from the whole tensors), its
+B * Hkv = 32 units go 32 / 16 / 8 / 4 per GPU (flash_attention_b200.shard), every rank times its
+shard with nothing exchanged on the data path, and value = FLOPs of the whole problem / max-over-
+ranks time: strong scaling.  Outside the timed region the shards of O and LSE are all-gathered
+over NCCL, rank 0 compares them bit for bit with the un-sharded call and checks sampled windows
+against exact attention (``verified``).  ``--scaling weak`` runs one whole problem per rank
+instead (replicas).
 
 Rank 0 prints ONE JSON line.  ``value`` is measured with inputs resident in HBM (scale factors
 already tiled, one kernel launch per step, CUDA events around each launch, L2 flushed between
@@ -75,7 +80,8 @@ def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         d = json.load(open(path))
-        return {"bf16_tflops": d["bf16_tflops"], "hbm_gbs": d["hbm_gbs"], "source": "measured"}
+        return {"bf16_tflops": d["bf16_tflops"], "hbm_gbs": d["hbm_gbs"], "source": "measured",
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"])}
     return {"bf16_tflops": 1590.0, "hbm_gbs": 6650.0, "source": "fallback"}
 
 
@@ -129,7 +135,7 @@ def run_reference_arm(args, wl, rank, world):
     line = {
         "impl": "reference", "metric": "nvfp4_attn_fwd_tflops", "value": cb["value"], "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup, "ms_per_step": cb["ms_per_pass"],
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "f32",
         "data": "synthetic", "config": workload_config(args.workload, wl, world),
         "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": cb["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -202,43 +208,140 @@ class ClockSampler:
                 "reasons": sorted({nm for x in inside for nm in x[4]})}
 
 
+def numa_pin(local_rank):
+    """Run this rank on the CPUs of its GPU's NUMA node, so that the pinned host buffers it
+    allocates afterwards (first touch) sit next to the GPU's PCIe root.  Returns a note."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(local_rank)
+        bus = pynvml.nvmlDeviceGetPciInfo(h).busId
+        bus = bus.decode() if isinstance(bus, bytes) else bus
+        bus = bus.lower()
+        if len(bus.split(":")[0]) == 8:           # 00000000:1B:00.0 -> 0000:1b:00.0
+            bus = bus[4:]
+        node = int(open(f"/sys/bus/pci/devices/{bus}/numa_node").read())
+        if node < 0:
+            return "single NUMA node"
+        cpus = open(f"/sys/devices/system/node/node{node}/cpulist").read().strip()
+        ids = []
+        for part in cpus.split(","):
+            a, _, b = part.partition("-")
+            ids += list(range(int(a), int(b or a) + 1))
+        allowed = sorted(set(ids) & os.sched_getaffinity(0))
+        if allowed:
+            os.sched_setaffinity(0, allowed)
+            return f"NUMA node {node}, cpus {cpus}"
+        return f"NUMA node {node} (its cpus are outside this process's affinity mask)"
+    except Exception as e:                        # nothing here may stop the benchmark
+        return f"not pinned ({type(e).__name__})"
+
+
+def blocks_of(B, Hq, S, causal):
+    """128 x 128 score blocks the kernel visits (whole diagonal blocks count)."""
+    m = (S + 127) // 128
+    per_head = m * (m + 1) // 2 if causal else m * m
+    return B * Hq * per_head
+
+
+def sampled_window_check(fa, Ql, Kl, Vl, out, lse, samples, causal, group):
+    """max relative O error and max LSE error of sampled 128-row windows against exact attention
+    (fp64, on the GPU) on the dequantised operands."""
+    dev = out.device
+    S = Kl.data.shape[1]
+    D = Ql.data.shape[-1] * 2
+    worst_o, worst_l = 0.0, 0.0
+    for (b, h, r0) in samples:
+        hk = h // group
+        sk = r0 + 128 if causal else S
+        qd = fa.dequantize_lastdim(Ql.data[b, r0:r0 + 128, h], Ql.sf[b, r0:r0 + 128, h], Ql.scale).double()
+        kd = fa.dequantize_lastdim(Kl.data[b, :sk, hk], Kl.sf[b, :sk, hk], Kl.scale).double()
+        vd = fa.dequantize_lastdim(Vl.data[b, hk, :, :sk // 2], Vl.sf[b, hk, :, :sk // 16], Vl.scale).double().T
+        s = (qd @ kd.T) / math.sqrt(D)
+        if causal:
+            rows = torch.arange(r0, r0 + 128, device=dev)[:, None]
+            s = s.masked_fill(torch.arange(sk, device=dev)[None, :] > rows, float("-inf"))
+        ref_l = torch.logsumexp(s, dim=-1)
+        ref_o = torch.softmax(s, dim=-1) @ vd
+        got_o, got_l = out[b, r0:r0 + 128, h].double(), lse[b, h, r0:r0 + 128].double()
+        worst_o = max(worst_o, ((got_o - ref_o).norm() / ref_o.norm()).item())
+        worst_l = max(worst_l, (got_l - ref_l).abs().max().item())
+    return worst_o, worst_l
+
+
 def run_gpu_arm(args, wl, rank, local_rank, world):
     import torch.distributed as dist
     import flash_attention_b200 as fa
+    from flash_attention_b200 import shard as sh
     B, Hq, Hkv, S, D, causal, v_std, outl = wl
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    strong = args.scaling == "strong"
+    numa_note = numa_pin(local_rank) if world > 1 else "one rank"
     sampler = ClockSampler(local_rank) if rank == 0 else None   # started early: its first sample is slow
 
-    # ---- synthetic inputs of this rank's shard (global batch = B * world; this rank's B batches)
-    g = torch.Generator(device=dev).manual_seed(1000 + rank)
-    q = torch.randn(B, S, Hq, D, generator=g, device=dev, dtype=torch.bfloat16)
-    k = torch.randn(B, S, Hkv, D, generator=g, device=dev, dtype=torch.bfloat16)
-    v = (torch.randn(B, S, Hkv, D, generator=g, device=dev) * v_std).bfloat16()
-    if outl > 0:
-        n = max(1, int(round(outl * D)))
-        for t in (q, k):
-            idx = torch.randperm(D, generator=g, device=dev)[:n]
-            t[..., idx] *= 20.0
-    Q, K, V = fa.quantize_qkv(q, k, v)
-    # the fused quantiser (the step in front of the path), timed on the same tensors: HBM-bound
-    for _ in range(2):
-        fa.quantize_qkv_fused(q, k, v, linear_sf=False)
-    qe0, qe1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    qe0.record()
-    for _ in range(5):
-        fa.quantize_qkv_fused(q, k, v, linear_sf=False)
-    qe1.record()
-    torch.cuda.synchronize()
-    quant_ms = qe0.elapsed_time(qe1) / 5
-    n_el = q.numel() + k.numel() + v.numel()
-    quant_bytes = n_el * (2 + 2) + n_el // 2 + n_el // 16     # two bf16 reads, packed + tiled scales
-    del q, k, v
-    Qt, Kt, Vt = (fa.NVFP4Tensor(t.data, t.tiled_sf(), t.scale, True, t.is_v) for t in (Q, K, V))
-    out = torch.empty(B, S, Hq, D, dtype=torch.bfloat16, device=dev)
-    lse = torch.empty(B, Hq, S, dtype=torch.float32, device=dev)
+    # ---- synthetic inputs.  strong: ONE problem of the workload's size, quantised on rank 0 (tensor
+    # scales computed on the whole tensors), broadcast, and every rank keeps its (batch, kv-head)
+    # units.  weak: every rank draws its own problem of that size (replicas).
+    def draw(seed):
+        g = torch.Generator(device=dev).manual_seed(seed)
+        q = torch.randn(B, S, Hq, D, generator=g, device=dev, dtype=torch.bfloat16)
+        k = torch.randn(B, S, Hkv, D, generator=g, device=dev, dtype=torch.bfloat16)
+        v = (torch.randn(B, S, Hkv, D, generator=g, device=dev) * v_std).bfloat16()
+        if outl > 0:
+            n = max(1, int(round(outl * D)))
+            for t in (q, k):
+                idx = torch.randperm(D, generator=g, device=dev)[:n]
+                t[..., idx] *= 20.0
+        return q, k, v
+
+    quant_ms = quant_bytes = None
+    if strong:
+        u8 = torch.uint8
+        shapes = [(B, S, Hq, D // 2), (B, S, Hkv, D // 2), (B, Hkv, D, S // 2),
+                  (B, S, Hq, D // 16), (B, S, Hkv, D // 16), (B, Hkv, D, S // 16)]
+        scales = torch.zeros(3, dtype=torch.float64, device=dev)
+        if rank == 0:
+            q, k, v = draw(1000)
+            Qf, Kf, Vf = fa.quantize_qkv_fused(q, k, v)          # linear + tiled scale factors
+            for _ in range(2):
+                fa.quantize_qkv_fused(q, k, v, linear_sf=False)
+            qe0, qe1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            qe0.record()
+            for _ in range(5):
+                fa.quantize_qkv_fused(q, k, v, linear_sf=False)
+            qe1.record()
+            torch.cuda.synchronize()
+            quant_ms = qe0.elapsed_time(qe1) / 5
+            n_el = q.numel() + k.numel() + v.numel()
+            quant_bytes = n_el * (2 + 2) + n_el // 2 + n_el // 16     # two bf16 reads, packed + tiled scales
+            del q, k, v
+            bufs = [Qf.data, Kf.data, Vf.data, Qf.sf, Kf.sf, Vf.sf]
+            scales.copy_(torch.tensor([Qf.scale, Kf.scale, Vf.scale], dtype=torch.float64))
+        else:
+            bufs = [torch.empty(s_, dtype=u8, device=dev) for s_ in shapes]
+        if world > 1:
+            for t in bufs:
+                dist.broadcast(t, 0)
+            dist.broadcast(scales, 0)
+        sc = [float(x) for x in scales.cpu()]
+        Qg = fa.NVFP4Tensor(bufs[0], bufs[3], sc[0])
+        Kg = fa.NVFP4Tensor(bufs[1], bufs[4], sc[1])
+        Vg = fa.NVFP4Tensor(bufs[2], bufs[5], sc[2], is_v=True)
+        plan = sh.plan_shard(B, Hkv, world, rank)
+        Qs, Ks, Vs = sh.shard_operands(Qg, Kg, Vg, plan)          # views: strided head / batch slices
+    else:
+        q, k, v = draw(1000 + rank)
+        Qs, Ks, Vs = fa.quantize_qkv(q, k, v)
+        del q, k, v
+        plan = sh.Shard(rank, world, 0, B, 0, Hkv)
+        Qg, Kg, Vg = Qs, Ks, Vs
+    Bs, Hq_s, Hkv_s = Qs.data.shape[0], Qs.data.shape[2], Ks.data.shape[2]
+    Qt, Kt, Vt = (fa.NVFP4Tensor(t.data, t.tiled_sf(), t.scale, True, t.is_v) for t in (Qs, Ks, Vs))
+    out = torch.empty(Bs, S, Hq_s, D, dtype=torch.bfloat16, device=dev)
+    lse = torch.empty(Bs, Hq_s, S, dtype=torch.float32, device=dev)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
 
     variant = fa.VARIANT_WS if args.kernel == "ws128" else fa.VARIANT_AUTO
@@ -275,20 +378,61 @@ def run_gpu_arm(args, wl, rank, local_rank, world):
     dev_ms = sum(e0.elapsed_time(e1) for e0, e1 in evs)
     clocks = sampler.stop(t_begin, datetime.datetime.now()) if sampler else None
     fa.check_status(dev)
+    # ---- sustained mode: launches back to back for a few seconds (no flush between them; the
+    # operands of one launch exceed L2), clocks sampled throughout: what a serving loop sees once
+    # the power cap has pulled the clock down
+    sustained = None
+    if args.sustained > 0:
+        samp2 = ClockSampler(local_rank) if rank == 0 else None
+        n_launch = max(10, int(args.sustained * 1e3 / (dev_ms / args.steps)))
+        barrier()
+        tb = datetime.datetime.now()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for _ in range(n_launch):
+            step()
+        s1.record()
+        barrier()
+        sus_ms = s0.elapsed_time(s1) / n_launch
+        sustained = {"launches": n_launch, "ms_per_step": sus_ms,
+                     "clocks": samp2.stop(tb, datetime.datetime.now()) if samp2 else None}
+        fa.check_status(dev)
 
-    # ---- end to end through the public API with host buffers
-    host_in = [t.cpu().pin_memory() for t in (Q.data, K.data, V.data, Q.sf, K.sf, V.sf)]
+    # ---- verification (outside every timed region): all-gather O / LSE of the shards over NCCL,
+    # rank 0 compares with the un-sharded call it computes itself (must be bit-identical) and checks
+    # sampled windows against exact attention on the dequantised operands
+    verified = None
+    if strong:
+        full_o, full_l = (sh.gather_output(out, lse, plan, B, Hq, Hkv) if world > 1 else (out, lse))
+        if rank == 0:
+            if world > 1:
+                ref_o, ref_l = fa.flash_attn_func(Qg, Kg, Vg, causal=causal, return_lse=True)
+                torch.cuda.synchronize()
+                same = bool(torch.equal(ref_o, full_o) and torch.equal(ref_l, full_l))
+                del ref_o, ref_l
+            else:
+                same = True
+            samples = [(0, 0, 0), (B - 1, Hq - 3, (S // 2 // 128) * 128), (B // 2, Hq // 2, S - 128)]
+            err_o, err_l = sampled_window_check(fa, Qg, Kg, Vg, full_o, full_l, samples, causal, Hq // Hkv)
+            verified = {"ok": bool(same and err_o < 0.2 and err_l < 1e-3),
+                        "sharded_equals_unsharded_bitwise": same, "gathered_with": "nccl all_gather" if world > 1 else "n/a",
+                        "max_rel_err_o_vs_exact": err_o, "max_abs_err_lse_vs_exact": err_l,
+                        "tolerance": "rel-RMS(O) < 0.2 per sampled 128-row window (4-bit P), |dLSE| < 1e-3"}
+        del full_o, full_l
+
+    # ---- end to end through the public API with host buffers (this rank's shard)
+    host_in = [t.contiguous().cpu().pin_memory() for t in (Qs.data, Ks.data, Vs.data, Qs.sf, Ks.sf, Vs.sf)]
     host_out = torch.empty(out.shape, dtype=out.dtype).pin_memory()
     host_lse = torch.empty(lse.shape, dtype=lse.dtype).pin_memory()
     h2d = sum(t.numel() * t.element_size() for t in host_in)
     d2h = host_out.numel() * 2 + host_lse.numel() * 4
 
-    pipe = fa.HostPipeline(B, S, S, Hq, Hkv, D, D, device=dev)
+    pipe = fa.HostPipeline(Bs, S, S, Hq_s, Hkv_s, D, D, device=dev)
 
     def e2e_step():
         # public host-buffer API: copy-in, scale tiling, attention and copy-out of row ranges on
         # three streams; every step moves all inputs in and the whole result out
-        pipe.run(*host_in, Q.scale, K.scale, V.scale, host_out, host_lse, causal=causal)
+        pipe.run(*host_in, Qs.scale, Ks.scale, Vs.scale, host_out, host_lse, causal=causal)
 
     e2e_steps = max(2, min(args.steps, 10))
     e2e_step()
@@ -306,30 +450,57 @@ def run_gpu_arm(args, wl, rank, local_rank, world):
     e2e_ms = e0.elapsed_time(e1) / e2e_steps
     fa.check_status(dev)
     mma_rate = fa.measure_fp4_mma_rate(device=dev) if rank == 0 else None
+    ex2_rate = fa.measure_ex2_rate(device=dev) if rank == 0 else None
 
-    times = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device=dev)
+    sus_ms = sustained["ms_per_step"] if sustained else 0.0
+    times = torch.tensor([dev_ms, e2e_ms, sus_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    dev_ms, e2e_ms = (float(x) for x in times.cpu())
-
+    dev_ms, e2e_ms, sus_ms = (float(x) for x in times.cpu())
     if rank == 0:
-        fl_rank = flops_of(B, Hq, S, D, causal)
+        fl_job = flops_of(B, Hq, S, D, causal) * (1 if strong else world)
+        fl_rank = fl_job / world
         ms_per_step = dev_ms / args.steps
-        tflops_total = fl_rank * world / (ms_per_step * 1e-3) / 1e12
+        tflops_total = fl_job / (ms_per_step * 1e-3) / 1e12
         tflops_gpu = tflops_total / world
         peaks = measured_peaks()
         fp4_peak = 4.0 * peaks["bf16_tflops"]
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        blocks_rank = blocks_of(Bs, Hq_s, S, causal)
+        tiles_rank = Bs * Hq_s * ((S + 127) // 128)
+        sm_mhz = (clocks or {}).get("sm_mhz") or 0.0
+        clk_per_block = ms_per_step * 1e-3 * sm_mhz * 1e6 / (blocks_rank / sms) if sm_mhz else None
+        # exponential roofline: one exp2 per score; the hardware unit's measured rate, the share
+        # of the exponentials this build moves to the FMA pipe, and the ceiling that leaves
+        emu_mask = fa.lib().fa4_nvfp4_query(101)
+        emu_share = bin(emu_mask).count("1") / 8.0
+        exp_ceiling = None
+        if ex2_rate and sm_mhz:
+            clk_floor = 128 * 128 * (1.0 - emu_share) / ex2_rate["per_clk_per_sm"]
+            exp_ceiling = sms * 4.0 * 128 * 128 * D * sm_mhz * 1e6 / clk_floor / 1e12
+        work = (f"one problem B={B}, Hq={Hq}, Hkv={Hkv}, Sq=Sk={S}, D={D}, causal={causal} dealt over {world} GPU(s): "
+                f"{Bs * Hkv_s} (batch, kv-head) units per GPU" if strong else
+                f"B={B} per GPU (global batch {B * world}), Hq={Hq}, Hkv={Hkv}, Sq=Sk={S}, D={D}, causal={causal}")
+        cfg = dict(workload_config(args.workload, wl, world),
+                   workload=f"{args.workload}: NVFP4 attention forward, {work}",
+                   kernel="attn_fwd_ws64_kernel (automatic choice)" if args.kernel == "auto"
+                   else "attn_fwd_ws_kernel<128> (forced)",
+                   units_per_gpu=Bs * Hkv_s, tiles_per_gpu=tiles_rank, tiles_per_cta=tiles_rank / min(sms, tiles_rank),
+                   blocks_128x128_per_sm=blocks_rank / sms, host_numa=numa_note)
+        if strong:
+            cfg.update(B_per_gpu=Bs, global_batch=B,
+                       sharding=f"(batch, kv-head) units of ONE problem, {Bs * Hkv_s} per GPU, no collective on the "
+                                "data path; NCCL all-gather of O / LSE for verification only")
         line = {
             "metric": "nvfp4_attn_fwd_tflops", "value": tflops_total, "unit": "TFLOP/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": args.scaling,
             "vs_baseline": None, "dtype": "nvfp4", "data": "synthetic",
-            "config": dict(workload_config(args.workload, wl, world),
-                           kernel="attn_fwd_ws64_kernel (automatic choice)" if args.kernel == "auto"
-                           else "attn_fwd_ws_kernel<128> (forced)"),
+            "config": cfg,
             "tflops_per_gpu": tflops_gpu,
-            "tokens_per_s": B * S * world / (ms_per_step * 1e-3),
+            "tokens_per_s": B * S * (1 if strong else world) / (ms_per_step * 1e-3),
             "pct_fp4_peak_nominal": 100.0 * tflops_gpu / FP4_NOMINAL_TFLOPS,
+            "clk_per_block": clk_per_block,
             "roofline": {
                 "bound": "tensor", "achieved": tflops_gpu, "peak": fp4_peak, "unit": "TFLOP/s",
                 "frac": tflops_gpu / fp4_peak,
@@ -338,39 +509,84 @@ def run_gpu_arm(args, wl, rank, local_rank, world):
                              f"bf16 rate; nominal dense FP4 is {FP4_NOMINAL_TFLOPS} TFLOP/s",
                 "fp4_mma_rate_measured": mma_rate,
                 "frac_of_measured_fp4_mma_rate": tflops_gpu / mma_rate["tflops"],
-                "traffic": TRAFFIC_BYTES.get(args.workload),
-                "algorithmic_bytes": algorithmic_bytes(B, Hq, Hkv, S, D),
-                "hbm_gbs_achieved": algorithmic_bytes(B, Hq, Hkv, S, D) / (ms_per_step * 1e-3) / 1e9,
+                "exp": {"ex2_per_clk_per_sm_measured": ex2_rate["per_clk_per_sm"] if ex2_rate else None,
+                        "emulated_share": emu_share, "ceiling_tflops": exp_ceiling,
+                        "frac": tflops_gpu / exp_ceiling if exp_ceiling else None,
+                        "note": "one exp2 per score; ceiling = FLOPs of a 128x128 block / (its hardware exp2 / "
+                                "measured rate) at the sampled SM clock"},
+                **traffic_record(args.workload),
+                "algorithmic_bytes": algorithmic_bytes(B, Hq, Hkv, S, D) // (world if strong else 1),
+                "hbm_gbs_achieved": algorithmic_bytes(B, Hq, Hkv, S, D) / (world if strong else 1)
+                                    / (ms_per_step * 1e-3) / 1e9,
             },
-            "e2e": {"value": fl_rank * world / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+            "e2e": {"value": fl_job / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
-                    "launches_per_step": B * len(pipe.ranges) * 5,
-                    "pieces_per_step": B * len(pipe.ranges),
-                    "note": "HostPipeline: pinned host buffers, copy-in / compute / copy-out of query-row "
-                            "ranges on three streams, successive steps overlap"},
-            "quantizer": {"ms": quant_ms, "algorithmic_bytes": quant_bytes,
-                          "gbs": quant_bytes / (quant_ms * 1e-3) / 1e9,
-                          "frac_of_hbm_peak": quant_bytes / (quant_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
-                          "note": "fused bf16 -> NVFP4 quantiser of q, k, v (6 launches + one scale "
-                                  "read-back), outside the timed region"},
+                    "h2d_gbs_per_rank": h2d / (e2e_ms * 1e-3) / 1e9, "d2h_gbs_per_rank": d2h / (e2e_ms * 1e-3) / 1e9,
+                    "launches_per_step": Bs * len(pipe.ranges) * 5,
+                    "pieces_per_step": Bs * len(pipe.ranges),
+                    "note": "HostPipeline on this rank's shard: pinned host buffers, copy-in / compute / copy-out of "
+                            "query-row ranges on three streams, successive steps overlap; bytes are per rank"},
             "gpu_launches": args.steps,
             "wall_ms_timed_region": t_wall * 1e3,
             "clocks": clocks,
         }
+        if verified is not None:
+            line["verified"] = verified["ok"]
+            line["verification"] = verified
+        if quant_ms is not None:
+            line["quantizer"] = {"ms": quant_ms, "algorithmic_bytes": quant_bytes,
+                                 "gbs": quant_bytes / (quant_ms * 1e-3) / 1e9,
+                                 "frac_of_hbm_peak": quant_bytes / (quant_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                                 "note": "fused bf16 -> NVFP4 quantiser of q, k, v of the whole problem on rank 0 "
+                                         "(6 launches + one scale read-back), outside the timed region"}
+        if sustained:
+            sus_tf = fl_job / (sus_ms * 1e-3) / 1e12 / world
+            sus_peak = 4.0 * peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
+            smhz = (sustained["clocks"] or {}).get("sm_mhz") or 0.0
+            line["sustained"] = {"seconds_requested": args.sustained, "launches": sustained["launches"],
+                                 "ms_per_step": sus_ms, "tflops_per_gpu": sus_tf, "peak": sus_peak,
+                                 "frac": sus_tf / sus_peak,
+                                 "clk_per_block": sus_ms * 1e-3 * smhz * 1e6 / (blocks_rank / sms) if smhz else None,
+                                 "clocks": sustained["clocks"],
+                                 "note": "back-to-back launches, no L2 flush (one launch's operands exceed L2); peak = "
+                                         "4 x the measured sustained cuBLAS bf16 figure"}
         if world == 1 and not args.no_cpu:
             cb = time_cpu(wl, 3, 1)
             line["cpu_baseline"] = {k2: cb[k2] for k2 in ("value", "unit", "cores", "kind", "sample")}
+            line["cpu_baseline"]["note"] = ("a rate on ONE (batch, head) pair; ms_per_step of the CPU arm and of this "
+                                            "arm are not comparable, the TFLOP/s are")
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
 
-# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the attention kernel the
-# automatic choice runs (attn_fwd_ws64_kernel), from the ncu captures summarised under profiles/.
-# cfg2 was captured whole (121.2 MB read + 218.9 MB written); cfg1 is the capture of half of it
-# (B = 2: 67.9 MB + 45.0 MB) scaled by the batch, which the traffic is proportional to.  None for
-# workloads that were not captured.
-TRAFFIC_BYTES = {"cfg2": 340_117_248, "cfg1": 2 * 112_986_112}
+def traffic_record(workload):
+    """DRAM bytes per launch of the attention kernel from the ncu capture recorded in
+    profiles/traffic.json, with the hash of the kernel sources it was captured on; a capture of
+    other sources is reported as stale."""
+    import hashlib
+    path = os.path.join(ROOT, "profiles", "traffic.json")
+    try:
+        rec = json.load(open(path)).get(workload)
+    except (OSError, ValueError):
+        rec = None
+    if not rec:
+        return {"traffic": None}
+    h = hashlib.sha256()
+    csrc = os.path.join(ROOT, "flash_attention_b200", "csrc")
+    for name in sorted(os.listdir(csrc)):
+        h.update(open(os.path.join(csrc, name), "rb").read())
+    return {"traffic": rec["bytes"], "traffic_note": rec.get("note"),
+            "traffic_stale": rec.get("source_sha256") != h.hexdigest()}
+
+
+def kernel_source_hash():
+    import hashlib
+    h = hashlib.sha256()
+    csrc = os.path.join(ROOT, "flash_attention_b200", "csrc")
+    for name in sorted(os.listdir(csrc)):
+        h.update(open(os.path.join(csrc, name), "rb").read())
+    return h.hexdigest()
 
 
 def run_sweep(args):
@@ -492,6 +708,11 @@ def main():
     ap.add_argument("--workload", default="cfg2")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
+                    help="strong (default): ONE problem of the workload's size, its (batch, kv-head) units dealt "
+                         "over the GPUs, verified after an NCCL all-gather; weak: one such problem per GPU")
+    ap.add_argument("--sustained", type=float, default=0.0,
+                    help="also time back-to-back launches for this many seconds (no L2 flush, clocks sampled)")
     ap.add_argument("--kernel", default="auto", choices=["auto", "ws128"],
                     help="auto: the library's choice (the 64-key kernel for these workloads); ws128: force "
                          "the 128-key kernel that serves split-KV")

@@ -153,6 +153,9 @@ def lib() -> ctypes.CDLL:
             L.fa4_nvfp4_debug_mma_rate.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p,
                                                    ctypes.c_void_p, ctypes.c_void_p]
             L.fa4_nvfp4_debug_mma_rate.restype = ctypes.c_int
+            L.fa4_nvfp4_debug_ex2_rate.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p,
+                                                   ctypes.c_void_p, ctypes.c_void_p]
+            L.fa4_nvfp4_debug_ex2_rate.restype = ctypes.c_int
             L.fa4_nvfp4_amax_bf16.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32,
                                               ctypes.c_int32, ctypes.c_int32, ctypes.c_int64,
                                               ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p,
@@ -170,6 +173,7 @@ def lib() -> ctypes.CDLL:
 
 EXPORTS = ["fa4_nvfp4_fwd", "fa4_nvfp4_sf_linear_to_tiled", "fa4_nvfp4_query",
            "fa4_nvfp4_debug_qk_tile", "fa4_nvfp4_debug_wait_expiry", "fa4_nvfp4_debug_mma_rate",
+           "fa4_nvfp4_debug_ex2_rate",
            "fa4_nvfp4_fwd_linear_sf_noalloc", "fa4_nvfp4_amax_bf16", "fa4_nvfp4_quantize_qk_bf16",
            "fa4_nvfp4_quantize_v_bf16", "fa4_nvfp4_splitkv_workspace_bytes", "fa4_nvfp4_fwd_splitkv",
            "fa4_nvfp4_fwd_ex"]

@@ -116,6 +116,7 @@ extern "C" int fa4_nvfp4_query(int32_t what) {
     case 0: return FA4_NVFP4_ABI_VERSION;
     case 1: return (int)(sizeof(dims) / sizeof(dims[0]));
     case 100: return (int)fa4::ws::kSmemRequest;
+    case 101: return (int)fa4::kEx2EmuMask;
     default:
       if (what >= 2 && what < 2 + (int)(sizeof(dims) / sizeof(dims[0]))) return dims[what - 2];
       return -FA4_E_SHAPE;
@@ -579,6 +580,16 @@ extern "C" int fa4_nvfp4_debug_mma_rate(int32_t iters, int32_t num_ctas, uint64_
   if (int e = ensure_smem(mma_rate_kernel, serial::kSmemRequest)) return e;
   mma_rate_kernel<<<num_ctas, 128, serial::kSmemRequest, static_cast<cudaStream_t>(cuda_stream)>>>(
       iters, reinterpret_cast<unsigned long long*>(clocks_out), status, kDefaultBudgetNs);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : (int)e;
+}
+
+extern "C" int fa4_nvfp4_debug_ex2_rate(int32_t iters, int32_t num_ctas, uint64_t* clocks_out, float* scratch,
+                                        void* cuda_stream) {
+  if (!clocks_out || !scratch) return -FA4_E_NULL;
+  if (iters < 1 || iters > (1 << 22) || num_ctas < 1 || num_ctas > 1024) return -FA4_E_SHAPE;
+  ex2_rate_kernel<<<num_ctas, 512, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+      iters, reinterpret_cast<unsigned long long*>(clocks_out), scratch);
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : (int)e;
 }

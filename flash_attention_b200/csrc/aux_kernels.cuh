@@ -270,6 +270,33 @@ mma_rate_kernel(int iters, unsigned long long* clocks_out, uint32_t* status, uin
 }
 
 // ---------------------------------------------------------------------------------------------
+// Rate of the exponential unit (the denominator of the kernel's exponential roofline): every
+// thread of 16 warps per CTA runs `iters` rounds of 16 independent ex2.approx, nothing else in
+// the loop competes for the unit; the CTA reports its clocks.  exp2 per clock per SM =
+// 512 threads * iters * 16 / clocks.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(512, 1)
+ex2_rate_kernel(int iters, unsigned long long* clocks_out, float* sink) {
+  float x[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) x[i] = -1.f - 0.01f * (float)(threadIdx.x + i);
+  __syncthreads();
+  const long long t0 = clock64();
+#pragma unroll 1
+  for (int it = 0; it < iters; ++it) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) x[i] = ex2_approx(x[i]) - 1.5f;   // stays in (-1.5, -0.5): no denormals
+  }
+  const long long t1 = clock64();
+  float acc = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) acc += x[i];
+  if (acc == 12345.678f) *sink = acc;   // keeps the loop alive
+  __syncthreads();
+  if (threadIdx.x == 0) clocks_out[blockIdx.x] = static_cast<unsigned long long>(t1 - t0);
+}
+
+// ---------------------------------------------------------------------------------------------
 // Bounded-wait self test: a barrier nothing arrives at.
 // ---------------------------------------------------------------------------------------------
 __global__ void wait_expiry_kernel(uint32_t* status, uint64_t budget_ns) {

@@ -401,3 +401,20 @@ def measure_fp4_mma_rate(iters: int = 1 << 16, device=None, repeats: int = 3) ->
     flops = sms * iters * 2.0 * 128 * 128 * 64
     return {"tflops": flops / (best * 1e-3) / 1e12, "ms": best, "sms": sms,
             "clk_per_mma": float(clocks.double().median().item()) / iters}
+
+
+def measure_ex2_rate(iters: int = 1 << 12, device=None) -> dict:
+    """Rate of the exponential unit of this GPU, measured (``fa4_nvfp4_debug_ex2_rate``): one CTA of
+    16 warps per SM, 16 independent ``ex2.approx`` per thread and round.  Returns
+    ``{"per_clk_per_sm" (median over CTAs), "sms"}``; the benchmark's exponential roofline uses it."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    clocks = torch.zeros(sms, dtype=torch.int64, device=device)
+    scratch = torch.zeros(1, dtype=torch.float32, device=device)
+    stream = torch.cuda.current_stream(device)
+    for _ in range(2):                    # the first launch is the warm-up
+        _lib.check(_lib.lib().fa4_nvfp4_debug_ex2_rate(iters, sms, clocks.data_ptr(), scratch.data_ptr(),
+                                                      stream.cuda_stream), "fa4_nvfp4_debug_ex2_rate")
+    torch.cuda.synchronize(device)
+    clk = float(clocks.double().median().item())
+    return {"per_clk_per_sm": 512.0 * iters * 16 / clk, "sms": sms}

@@ -218,7 +218,10 @@ int fa4_nvfp4_sf_linear_to_tiled(const void* src, void* dst,
 /*
  * Version / capability query (host only, never touches a GPU).
  *   what = 0: ABI version; 1: number of supported head dims; 2+i: i-th supported
- *   head dim; 100: default dynamic shared memory per CTA of the WS variant.
+ *   head dim; 100: default dynamic shared memory per CTA of the WS variant; 101: which of the 8
+ *   pairs of a 16-key block take the FMA-pipe exp2 in this build (bit mask, 0 = none; the
+ *   compile-time knob that corresponds to the reference's ex2_emu_freq,
+ *   flash_attn/cute/flash_fwd_sm100.py:71-90).
  * Mirrors the head-dim validation of flash_attn/cute/interface.py:84-99.
  */
 int fa4_nvfp4_query(int32_t what);
@@ -280,6 +283,17 @@ int fa4_nvfp4_debug_qk_tile(const void* q, const void* k, const void* q_sf,
  */
 int fa4_nvfp4_debug_mma_rate(int32_t iters, int32_t num_ctas, uint64_t* clocks_out,
                              uint32_t* status, void* cuda_stream);
+
+/*
+ * Exponential-unit rate probe: `num_ctas` CTAs of 512 threads each run `iters` rounds of 16
+ * independent ex2.approx per thread and write their clocks to clocks_out[cta]; exp2 per clock per
+ * SM = 512 * iters * 16 / clocks.  `scratch`: one float of device memory (never written in
+ * practice).  The denominator of the benchmark's exponential roofline (one exp2 per score); the
+ * reference's tuning script states the same limit in words (benchmarks/tune_ex2_emu.py:1-30) and
+ * has no probe.
+ */
+int fa4_nvfp4_debug_ex2_rate(int32_t iters, int32_t num_ctas, uint64_t* clocks_out, float* scratch,
+                             void* cuda_stream);
 
 /*
  * Bounded-wait self test: launches one CTA that waits on a barrier nothing
