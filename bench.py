@@ -136,7 +136,7 @@ def run_reference_arm(args, wl, rank, world):
         "impl": "reference", "metric": "nvfp4_attn_fwd_tflops", "value": cb["value"], "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup, "ms_per_step": cb["ms_per_pass"],
         "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic", "config": workload_config(args.workload, wl, world),
+        "data": "synthetic", "config": workload_config(args.workload, wl, world, args.scaling),
         "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": cb["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "tokens_per_s": S / (cb["ms_per_pass"] * 1e-3) / Hq,
@@ -144,13 +144,23 @@ def run_reference_arm(args, wl, rank, world):
     print(json.dumps(line), flush=True)
 
 
-def workload_config(name, wl, world):
+def workload_config(name, wl, world, scaling="strong"):
+    """The ``config`` both arms print: same ``workload`` string for the same run."""
     B, Hq, Hkv, S, D, causal, v_std, outl = wl
-    return {"workload": f"{name}: NVFP4 attention forward, B={B} per GPU (global batch {B * world}), "
-                        f"Hq={Hq}, Hkv={Hkv}, Sq=Sk={S}, D={D}, causal={causal}",
-            "B_per_gpu": B, "global_batch": B * world, "Hq": Hq, "Hkv": Hkv, "seq_len": S, "head_dim": D,
-            "causal": causal, "v_std": v_std, "outlier_frac": outl,
-            "sharding": f"(batch, kv-head) units, {B * Hkv} per GPU, no collective on the data path",
+    if scaling == "strong":
+        per = B * Hkv // world if (B * Hkv) % world == 0 else None
+        work = (f"one problem B={B}, Hq={Hq}, Hkv={Hkv}, Sq=Sk={S}, D={D}, causal={causal}, its {B * Hkv} "
+                f"(batch, kv-head) units dealt over {world} GPU(s), {per} per GPU")
+        sharding = (f"(batch, kv-head) units of ONE problem, {per} per GPU, no collective on the data path; NCCL "
+                    "all-gather of O / LSE for verification only")
+        gb = B
+    else:
+        work = f"B={B} per GPU (global batch {B * world}), Hq={Hq}, Hkv={Hkv}, Sq=Sk={S}, D={D}, causal={causal}"
+        sharding = f"(batch, kv-head) units, {B * Hkv} per GPU (one whole problem per GPU), no collective on the data path"
+        gb = B * world
+    return {"workload": f"{name}: NVFP4 attention forward, {work}",
+            "global_batch": gb, "Hq": Hq, "Hkv": Hkv, "seq_len": S, "head_dim": D,
+            "causal": causal, "v_std": v_std, "outlier_frac": outl, "sharding": sharding,
             "l2": "L2 flushed between timed launches (256 MiB write)"}
 
 
@@ -478,19 +488,12 @@ def run_gpu_arm(args, wl, rank, local_rank, world):
         if ex2_rate and sm_mhz:
             clk_floor = 128 * 128 * (1.0 - emu_share) / ex2_rate["per_clk_per_sm"]
             exp_ceiling = sms * 4.0 * 128 * 128 * D * sm_mhz * 1e6 / clk_floor / 1e12
-        work = (f"one problem B={B}, Hq={Hq}, Hkv={Hkv}, Sq=Sk={S}, D={D}, causal={causal} dealt over {world} GPU(s): "
-                f"{Bs * Hkv_s} (batch, kv-head) units per GPU" if strong else
-                f"B={B} per GPU (global batch {B * world}), Hq={Hq}, Hkv={Hkv}, Sq=Sk={S}, D={D}, causal={causal}")
-        cfg = dict(workload_config(args.workload, wl, world),
-                   workload=f"{args.workload}: NVFP4 attention forward, {work}",
+        cfg = dict(workload_config(args.workload, wl, world, args.scaling),
                    kernel="attn_fwd_ws64_kernel (automatic choice)" if args.kernel == "auto"
                    else "attn_fwd_ws_kernel<128> (forced)",
-                   units_per_gpu=Bs * Hkv_s, tiles_per_gpu=tiles_rank, tiles_per_cta=tiles_rank / min(sms, tiles_rank),
+                   B_per_gpu=Bs, units_per_gpu=Bs * Hkv_s, tiles_per_gpu=tiles_rank,
+                   tiles_per_cta=tiles_rank / min(sms, tiles_rank),
                    blocks_128x128_per_sm=blocks_rank / sms, host_numa=numa_note)
-        if strong:
-            cfg.update(B_per_gpu=Bs, global_batch=B,
-                       sharding=f"(batch, kv-head) units of ONE problem, {Bs * Hkv_s} per GPU, no collective on the "
-                                "data path; NCCL all-gather of O / LSE for verification only")
         line = {
             "metric": "nvfp4_attn_fwd_tflops", "value": tflops_total, "unit": "TFLOP/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
@@ -591,10 +594,21 @@ def kernel_source_hash():
 
 def run_sweep(args):
     """Head-dim and shape sweep (B * H = 128 as B = 8, H = 16): every point is timed like the main
-    arm (resident inputs, L2 flush between launches, CUDA events); ONE JSON line with the table."""
+    arm (resident inputs, L2 flush between launches, CUDA events); ONE JSON line with the table.
+    With N ranks every point is ONE problem whose 128 (batch, head) units are dealt 128 / N per GPU
+    (whole batch entries; the tensor scales come from the whole tensors, which every rank draws
+    from the same seed); a point's time is the maximum over the ranks."""
+    import torch.distributed as dist
     import flash_attention_b200 as fa
-    dev = torch.device("cuda", 0)
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    if 8 % world != 0:
+        raise SystemExit("the sweep deals 8 batch entries: 1, 2, 4 or 8 GPUs")
     peaks = measured_peaks()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     rows = []
@@ -609,8 +623,10 @@ def run_sweep(args):
                 v = torch.randn(B, S, H, Dv, generator=g, device=dev, dtype=torch.bfloat16)
                 Q, K, V = fa.quantize_qkv_fused(q, k, v, linear_sf=False)
                 del q, k, v
-                out = torch.empty(B, S, H, Dv, dtype=torch.bfloat16, device=dev)
-                lse = torch.empty(B, H, S, dtype=torch.float32, device=dev)
+                b0, b1 = rank * (B // world), (rank + 1) * (B // world)      # this rank's batch entries
+                Q, K, V = (fa.NVFP4Tensor(t.data[b0:b1], t.sf[b0:b1], t.scale, True, t.is_v) for t in (Q, K, V))
+                out = torch.empty(b1 - b0, S, H, Dv, dtype=torch.bfloat16, device=dev)
+                lse = torch.empty(b1 - b0, H, S, dtype=torch.float32, device=dev)
 
                 def step():
                     fa.flash_attn_fp4_func(Q.data, K.data, V.data, Q.sf, K.sf, V.sf, Q.scale, K.scale, V.scale,
@@ -626,16 +642,24 @@ def run_sweep(args):
                     ms += e0.elapsed_time(e1)
                 ms /= steps
                 fa.check_status(dev)
+                if world > 1:
+                    tmax = torch.tensor([ms], dtype=torch.float64, device=dev)
+                    dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+                    ms = float(tmax.item())
                 fl, by = flops_of(B, H, S, D, causal, Dv), algorithmic_bytes(B, H, H, S, D, Dv)
                 rows.append({"D": D, "Dv": Dv, "S": S, "causal": causal, "ms": ms, "tflops": fl / ms / 1e9,
-                             "pct_fp4_peak_nominal": 100 * fl / ms / 1e9 / FP4_NOMINAL_TFLOPS,
-                             "frac_of_4x_bf16_measured": fl / ms / 1e9 / (4 * peaks["bf16_tflops"]),
-                             "hbm_gbs": by / ms / 1e6, "frac_of_hbm_peak": by / ms / 1e6 / peaks["hbm_gbs"]})
+                             "pct_fp4_peak_nominal": 100 * fl / ms / 1e9 / world / FP4_NOMINAL_TFLOPS,
+                             "frac_of_4x_bf16_measured": fl / ms / 1e9 / world / (4 * peaks["bf16_tflops"]),
+                             "hbm_gbs": by / ms / 1e6, "frac_of_hbm_peak": by / ms / 1e6 / world / peaks["hbm_gbs"]})
                 del Q, K, V, out, lse
+    if world > 1:
+        dist.destroy_process_group()
+    if rank != 0:
+        return
     head = next(r for r in rows if r["D"] == 128 and r["S"] == 4096 and r["causal"])
     print(json.dumps({"metric": "nvfp4_attn_fwd_tflops", "value": head["tflops"], "unit": "TFLOP/s",
-                      "n_gpus": 1, "steps": steps, "warmup": 3, "ms_per_step": head["ms"],
-                      "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4",
+                      "n_gpus": world, "steps": steps, "warmup": 3, "ms_per_step": head["ms"],
+                      "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "nvfp4",
                       "data": "synthetic",
                       "config": {"workload": "sweep: D in {64, 128, 192 (with Dv = 128)} x S in {1024, 2048, 4096, "
                                              "16384} x causal / non-causal, B = 8, H = 16 (B * H = 128); "
@@ -717,6 +741,12 @@ def main():
                     help="auto: the library's choice (the 64-key kernel for these workloads); ws128: force "
                          "the 128-key kernel that serves split-KV")
     args = ap.parse_args()
+    if args.gpus > 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1 and args.workload != "decode":
+        # not under a launcher: start one rank per GPU ourselves
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
+               f"--nproc-per-node={args.gpus}", "--master-addr", "127.0.0.1", "--master-port", "29517",
+               os.path.abspath(__file__)] + sys.argv[1:]
+        raise SystemExit(subprocess.call(cmd))
     if args.workload in ("sweep", "decode"):
         if not torch.cuda.is_available():
             raise SystemExit("bench.py needs a CUDA device (no CPU fallback)")
@@ -725,12 +755,6 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    if args.gpus > 1 and world == 1:
-        # not under a launcher: start one rank per GPU ourselves
-        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
-               f"--nproc-per-node={args.gpus}", "--master-addr", "127.0.0.1", "--master-port", "29517",
-               os.path.abspath(__file__)] + sys.argv[1:]
-        raise SystemExit(subprocess.call(cmd))
     if args.impl == "reference":
         run_reference_arm(args, wl, rank, world)
         return
