@@ -668,6 +668,113 @@ def run_sweep(args):
                       "gpu_launches": steps * len(rows), "sweep": rows}), flush=True)
 
 
+def run_fa4_bf16(args):
+    """Same-box comparator: the reference's own Blackwell forward (flash_attn.cute.flash_attn_func,
+    flash_attn/cute/interface.py:1753, BF16, CuTe-DSL JIT) on the DEQUANTISED operands of the
+    benchmark configurations, rounded to bf16 -- the kernel the NVFP4 path sits beside.  Needs the
+    reference's `flash_attn/cute` package installed into baseline/_ref (see DESIGN.md) and a GPU;
+    prints {"impl": "fa4_bf16", "unavailable": ...} otherwise.  Timed like the main arm (resident
+    inputs, warm-up 5, L2 flush between launches, CUDA events), one JSON line with a table."""
+    import types
+    ref_root = os.path.join(ROOT, "baseline", "_ref", "flash_attn")
+    if not os.path.isdir(os.path.join(ref_root, "cute")):
+        print(json.dumps({"impl": "fa4_bf16", "unavailable": "baseline/_ref/flash_attn/cute is not installed"}))
+        return
+    try:
+        # the image also carries another `flash_attn` distribution: bind the name to the installed
+        # reference package explicitly
+        pkg = types.ModuleType("flash_attn")
+        pkg.__path__ = [ref_root]
+        sys.modules["flash_attn"] = pkg
+        from flash_attn.cute.interface import flash_attn_func as ref_func
+    except Exception as e:  # noqa: BLE001
+        print(json.dumps({"impl": "fa4_bf16", "unavailable": f"import failed: {type(e).__name__}: {e}"[:300]}))
+        return
+    import flash_attention_b200 as fa
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    steps = max(3, min(args.steps, 20))
+    points = [("cfg1", WORKLOADS["cfg1"]), ("cfg2", WORKLOADS["cfg2"])]
+    points += [(f"sweep D=128 S={S} causal={c}", (8, 16, 16, S, 128, c, 1.0, 0.0))
+               for S in (1024, 2048, 4096, 16384) for c in (False, True)]
+    rows = []
+
+    def sm_clock():
+        try:
+            r = subprocess.run(["nvidia-smi", "--id=0", "--query-gpu=clocks.sm", "--format=csv,noheader,nounits"],
+                               capture_output=True, text=True, timeout=10)
+            return float(r.stdout.strip().splitlines()[0])
+        except Exception:  # noqa: BLE001
+            return None
+
+    def timed(fn):
+        """mean ms per call and the SM clock sampled while a further batch of calls is in flight"""
+        ms = 0.0
+        for _ in range(steps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); fn(); e1.record(); e1.synchronize()
+            ms += e0.elapsed_time(e1)
+        for _ in range(20):
+            fn()
+        mhz = sm_clock()
+        torch.cuda.synchronize()
+        return ms / steps, mhz
+
+    for name, (B, Hq, Hkv, S, D, causal, v_std, _) in points:
+        g = torch.Generator(device=dev).manual_seed(1000)
+        q = torch.randn(B, S, Hq, D, generator=g, device=dev, dtype=torch.bfloat16)
+        k = torch.randn(B, S, Hkv, D, generator=g, device=dev, dtype=torch.bfloat16)
+        v = (torch.randn(B, S, Hkv, D, generator=g, device=dev) * v_std).bfloat16()
+        Q, K, V = fa.quantize_qkv_fused(q, k, v)
+        del q, k, v
+        qd, kd, vd = (t.dequantize().bfloat16() for t in (Q, K, V))      # (B, S, H, D) bf16
+        row = {"workload": name, "B": B, "Hq": Hq, "Hkv": Hkv, "S": S, "D": D, "causal": causal}
+        fl = flops_of(B, Hq, S, D, causal)
+        # this repository's kernel on the quantised operands
+        out = torch.empty(B, S, Hq, D, dtype=torch.bfloat16, device=dev)
+        Qt, Kt, Vt = (fa.NVFP4Tensor(t.data, t.tiled_sf(), t.scale, True, t.is_v) for t in (Q, K, V))
+
+        def our_step():
+            fa.flash_attn_fp4_func(Qt.data, Kt.data, Vt.data, Qt.sf, Kt.sf, Vt.sf, Qt.scale, Kt.scale, Vt.scale,
+                                   causal=causal, out=out, sf_layout="tiled")
+        for _ in range(5):
+            our_step()
+        torch.cuda.synchronize()
+        ms, mhz = timed(our_step)
+        fa.check_status(dev)
+        row.update(nvfp4_ms=ms, nvfp4_tflops=fl / ms / 1e9, nvfp4_sm_mhz=mhz)
+        # the reference's BF16 kernel on the dequantised operands
+        try:
+            holder = {}
+
+            def ref_step():
+                holder["r"] = ref_func(qd, kd, vd, causal=causal)
+            for _ in range(5):
+                ref_step()
+            torch.cuda.synchronize()
+            ms_ref, mhz_ref = timed(ref_step)
+            r = holder["r"]
+            ref_out = r[0] if isinstance(r, (tuple, list)) else r
+            row.update(fa4_bf16_ms=ms_ref, fa4_bf16_tflops=fl / ms_ref / 1e9, fa4_bf16_sm_mhz=mhz_ref,
+                       speedup_vs_fa4_bf16=ms_ref / ms)
+            a_, b_ = out[0, :, 0].float(), ref_out[0, :, 0].float()
+            row["rel_rms_nvfp4_vs_fa4_bf16_sample"] = float((a_ - b_).norm() / b_.norm())
+        except Exception as e:  # noqa: BLE001
+            row.update(fa4_bf16_error=f"{type(e).__name__}: {e}"[:300])
+        rows.append(row)
+        del Q, K, V, Qt, Kt, Vt, qd, kd, vd, out
+    head = rows[1]
+    print(json.dumps({"impl": "fa4_bf16", "metric": "nvfp4_attn_fwd_tflops", "value": head.get("fa4_bf16_tflops"),
+                      "unit": "TFLOP/s", "n_gpus": 1, "steps": steps, "warmup": 5, "ms_per_step": head.get("fa4_bf16_ms"),
+                      "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+                      "config": {"workload": "the reference's BF16 sm_100 forward on the dequantised operands of cfg1, "
+                                             "cfg2 and the D = 128 sweep points, beside this repository's NVFP4 kernel",
+                                 "l2": "L2 flushed between timed launches (256 MiB write)"},
+                      "table": rows}), flush=True)
+
+
 def run_decode(args):
     """Decode shapes (one query token per sequence against a long NVFP4 KV cache, GQA 4): the
     transposed decode kernel with chosen key splits beside the prefill kernel's split-KV path.
@@ -730,7 +837,10 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default="cfg2")
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "fa4-bf16"],
+                    help="ours: this repository's kernels; reference: the CPU restatement of attention_ref on the "
+                         "host cores; fa4-bf16: the reference's own BF16 Blackwell kernel from baseline/_ref on the "
+                         "dequantised operands (the same-box comparator)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
                     help="strong (default): ONE problem of the workload's size, its (batch, kv-head) units dealt "
@@ -747,6 +857,11 @@ def main():
                f"--nproc-per-node={args.gpus}", "--master-addr", "127.0.0.1", "--master-port", "29517",
                os.path.abspath(__file__)] + sys.argv[1:]
         raise SystemExit(subprocess.call(cmd))
+    if args.impl == "fa4-bf16":
+        if not torch.cuda.is_available():
+            print(json.dumps({"impl": "fa4_bf16", "unavailable": "no CUDA device"}))
+            return
+        return run_fa4_bf16(args)
     if args.workload in ("sweep", "decode"):
         if not torch.cuda.is_available():
             raise SystemExit("bench.py needs a CUDA device (no CPU fallback)")
