@@ -61,6 +61,18 @@ class Ext(ctypes.Structure):
     ]
 
 
+class Varlen(ctypes.Structure):
+    """Mirror of ``fa4_nvfp4_varlen``."""
+    _fields_ = [
+        ("struct_size", ctypes.c_uint32), ("num_seqs", ctypes.c_int32),
+        ("cu_seqlens_q", ctypes.c_void_p), ("cu_seqlens_k", ctypes.c_void_p), ("seqused_k", ctypes.c_void_p),
+        ("total_q", ctypes.c_int32), ("total_k", ctypes.c_int32),
+        ("max_seqlen_q", ctypes.c_int32), ("max_seqlen_k", ctypes.c_int32),
+        ("window_left", ctypes.c_int32), ("window_right", ctypes.c_int32),
+        ("sink", ctypes.c_void_p), ("softcap", ctypes.c_float), ("reserved", ctypes.c_uint32),
+    ]
+
+
 def _dependencies():
     """Every file the library is compiled from: all of csrc/ and the public header."""
     deps = sorted(glob.glob(os.path.join(CSRC, "*.cu")) + glob.glob(os.path.join(CSRC, "*.cuh")))
@@ -138,6 +150,12 @@ def lib() -> ctypes.CDLL:
             L.fa4_nvfp4_fwd_splitkv.restype = ctypes.c_int
             L.fa4_nvfp4_fwd_ex.argtypes = [ctypes.POINTER(Params), ctypes.POINTER(Ext), ctypes.c_void_p]
             L.fa4_nvfp4_fwd_ex.restype = ctypes.c_int
+            L.fa4_nvfp4_fwd_varlen.argtypes = [ctypes.POINTER(Params), ctypes.POINTER(Varlen), ctypes.c_void_p]
+            L.fa4_nvfp4_fwd_varlen.restype = ctypes.c_int
+            L.fa4_nvfp4_sf_linear_to_tiled_packed.argtypes = [
+                ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
+                ctypes.c_int32, ctypes.c_int64, ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p]
+            L.fa4_nvfp4_sf_linear_to_tiled_packed.restype = ctypes.c_int
             L.fa4_nvfp4_sf_linear_to_tiled.argtypes = [
                 ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
                 ctypes.c_int32, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int32,
@@ -173,7 +191,7 @@ def lib() -> ctypes.CDLL:
 
 EXPORTS = ["fa4_nvfp4_fwd", "fa4_nvfp4_sf_linear_to_tiled", "fa4_nvfp4_query",
            "fa4_nvfp4_debug_qk_tile", "fa4_nvfp4_debug_wait_expiry", "fa4_nvfp4_debug_mma_rate",
-           "fa4_nvfp4_debug_ex2_rate",
+           "fa4_nvfp4_debug_ex2_rate", "fa4_nvfp4_fwd_varlen", "fa4_nvfp4_sf_linear_to_tiled_packed",
            "fa4_nvfp4_fwd_linear_sf_noalloc", "fa4_nvfp4_amax_bf16", "fa4_nvfp4_quantize_qk_bf16",
            "fa4_nvfp4_quantize_v_bf16", "fa4_nvfp4_splitkv_workspace_bytes", "fa4_nvfp4_fwd_splitkv",
            "fa4_nvfp4_fwd_ex"]

@@ -117,6 +117,7 @@ extern "C" int fa4_nvfp4_query(int32_t what) {
     case 1: return (int)(sizeof(dims) / sizeof(dims[0]));
     case 100: return (int)fa4::ws::kSmemRequest;
     case 101: return (int)fa4::kEx2EmuMask;
+    case 102: return FA4_P_SCALE_E4M3;
     default:
       if (what >= 2 && what < 2 + (int)(sizeof(dims) / sizeof(dims[0]))) return dims[what - 2];
       return -FA4_E_SHAPE;
@@ -133,6 +134,10 @@ struct CacheView {
   const int32_t* seqused_k = nullptr;
   const int32_t* page_table = nullptr;
   int page_size = 0, pages_per_seq = 0, num_pages = 0;
+  // packed variable-length batch (see fa4_nvfp4_varlen)
+  const int32_t* cu_seqlens_q = nullptr;
+  const int32_t* cu_seqlens_k = nullptr;
+  int total_q = 0, total_k = 0;
 };
 int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint64_t workspace_bytes,
                int win_left, int win_right, const float* sink, float softcap, const CacheView& cache,
@@ -163,6 +168,53 @@ extern "C" int fa4_nvfp4_fwd_ex(const fa4_nvfp4_params* p, const fa4_nvfp4_ext* 
   }
   return launch_fwd(p, splits, x->workspace, x->workspace_bytes, x->window_left, x->window_right,
                     x->sink, x->softcap, cache, cuda_stream);
+}
+
+extern "C" int fa4_nvfp4_fwd_varlen(const fa4_nvfp4_params* p, const fa4_nvfp4_varlen* v, void* cuda_stream) {
+  if (p == nullptr || v == nullptr) return -FA4_E_NULL;
+  if (v->struct_size != sizeof(fa4_nvfp4_varlen) || p->struct_size != sizeof(fa4_nvfp4_params)) return -FA4_E_STRUCT;
+  if (v->cu_seqlens_q == nullptr || v->cu_seqlens_k == nullptr) return -FA4_E_NULL;
+  if (v->num_seqs <= 0 || v->total_q <= 0 || v->total_k <= 0 || v->max_seqlen_q <= 0 || v->max_seqlen_k <= 0 ||
+      v->max_seqlen_q > v->total_q || v->max_seqlen_k > v->total_k)
+    return -FA4_E_SHAPE;
+  if (v->window_left < -1 || v->window_right < -1 || !(v->softcap >= 0.f) || v->softcap > 3.0e38f || v->reserved != 0u)
+    return -FA4_E_SHAPE;
+  if (p->variant != FA4_VARIANT_AUTO && p->variant != FA4_VARIANT_WS64) return -FA4_E_VARIANT;
+  // one launch over (sequence, m-block of the longest sequence, head): the grid of the dense call
+  // with B = number of sequences and Sq / Sk = the longest ones
+  fa4_nvfp4_params q = *p;
+  q.B = v->num_seqs;
+  q.Sq = v->max_seqlen_q;
+  q.Sk = v->max_seqlen_k;
+  q.variant = FA4_VARIANT_WS64;
+  CacheView cache;
+  cache.seqused_k = v->seqused_k;
+  cache.cu_seqlens_q = v->cu_seqlens_q;
+  cache.cu_seqlens_k = v->cu_seqlens_k;
+  cache.total_q = v->total_q;
+  cache.total_k = v->total_k;
+  return launch_fwd(&q, 1, nullptr, 0, v->window_left, v->window_right, v->sink, v->softcap, cache, cuda_stream);
+}
+
+extern "C" int fa4_nvfp4_sf_linear_to_tiled_packed(const void* src, void* dst, const int32_t* cu_seqlens,
+                                                   int32_t num_seqs, int32_t n_inner, int32_t max_rows,
+                                                   int32_t max_cols, int64_t stride_inner, int64_t stride_row,
+                                                   int32_t col_tile_multiple, int32_t packed_rows,
+                                                   void* cuda_stream) {
+  if (!src || !dst || !cu_seqlens) return -FA4_E_NULL;
+  if (num_seqs <= 0 || n_inner <= 0 || max_rows <= 0 || max_cols <= 0 || col_tile_multiple <= 0)
+    return -FA4_E_SHAPE;
+  if (!aligned16(dst)) return -FA4_E_ALIGN;
+  const int64_t ct = ((max_cols + 3) / 4 + col_tile_multiple - 1) / col_tile_multiple * col_tile_multiple;
+  const int64_t total = (int64_t)num_seqs * n_inner * ((max_rows + 127) / 128) * ct * 32;
+  int64_t blocks = (total + 255) / 256;
+  const int64_t cap = 148 * 16;
+  if (blocks > cap) blocks = cap;
+  sf_linear_to_tiled_packed_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+      static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), cu_seqlens, num_seqs, n_inner, max_rows,
+      max_cols, stride_inner, stride_row, col_tile_multiple, packed_rows ? 1 : 0);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : (int)e;
 }
 
 extern "C" int64_t fa4_nvfp4_splitkv_workspace_bytes(const fa4_nvfp4_params* p, int32_t num_splits) {
@@ -201,9 +253,9 @@ int validate_fwd(const fa4_nvfp4_params* p, int num_splits, const void* workspac
   // head dims built: (128, 128), (64, 64) and (192, 128), the last on the 64-key kernel only
   const bool d192 = p->D == 192 && p->Dv == 128;
   if (!d192 && (p->D != p->Dv || (p->D != 128 && p->D != 64))) return -FA4_E_SHAPE;
-  // keys are blocked by 16 along Sk (V / P scales) and V rows are Sk/2 bytes with a 16-byte
-  // stride rule for TMA: Sk must be a multiple of 32; Sq is free
-  if (p->Sk % 32 != 0) return -FA4_E_SHAPE;
+  // Sq and Sk are free.  V is stored key-contiguous with its key axis padded to a multiple of 32
+  // (zero values, zero scales): keys are blocked by 16 along that axis and the 16-byte stride rule
+  // of TMA (checked below) needs whole 32-key groups per row; keys >= Sk are masked
   if ((int64_t)((p->Sq + kBlockM - 1) / kBlockM) * p->Hq * p->B > 0x7fffffffLL) return -FA4_E_SHAPE;
   if (!(p->softmax_scale > 0.f) || !(p->q_scale > 0.f) || !(p->k_scale > 0.f)) return -FA4_E_SHAPE;
   const void* ptrs[] = {p->q, p->k, p->v, p->out};
@@ -217,7 +269,7 @@ int validate_fwd(const fa4_nvfp4_params* p, int num_splits, const void* workspac
   if ((p->o_stride_b & 7) || (p->o_stride_s & 7) || (p->o_stride_h & 7)) return -FA4_E_STRIDE;
   // automatic choice: the 64-key kernel where it applies (no split-KV), the 128-key kernel
   // otherwise
-  const bool cached = cache.seqused_k != nullptr || cache.page_table != nullptr;
+  const bool cached = cache.seqused_k != nullptr || cache.page_table != nullptr || cache.cu_seqlens_q != nullptr;
   const bool takes64 = num_splits == 1;   // what the 64-key kernel can run
   int variant = p->variant;
   if (variant == FA4_VARIANT_AUTO) variant = takes64 ? FA4_VARIANT_WS64 : FA4_VARIANT_WS;
@@ -275,19 +327,24 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
 
   CUtensorMap tm_q, tm_k, tm_v;
   {
-    const uint64_t dq[4] = {(uint64_t)p->D / 2, (uint64_t)p->Hq, (uint64_t)p->Sq, (uint64_t)p->B};
+    // a packed batch is one long sequence for the tensor maps: the kernel adds each sequence's
+    // first row to the row coordinate
+    const bool packed = cache.cu_seqlens_q != nullptr;
+    const uint64_t dq[4] = {(uint64_t)p->D / 2, (uint64_t)p->Hq, packed ? (uint64_t)cache.total_q : (uint64_t)p->Sq,
+                            packed ? 1u : (uint64_t)p->B};
     const uint64_t sq[3] = {(uint64_t)p->q_stride_h, (uint64_t)p->q_stride_s, (uint64_t)p->q_stride_b};
     // a Q / K tile row is D / 2 bytes: one 64-byte-swizzled box for D = 128; 32-byte-wide boxes
     // (32-byte swizzle), one per 64-element step, for D = 64 and 192
     const uint32_t qk_box = p->D == 128 ? 64u : 32u;
     const uint32_t bq[4] = {qk_box, 1, (uint32_t)kBlockM, 1};
     // with a page table K / V describe the pool: "batch" = page, "Sk" = keys per page
-    const uint64_t k_rows = cache.page_table ? (uint64_t)cache.page_size : (uint64_t)p->Sk;
-    const uint64_t k_batch = cache.page_table ? (uint64_t)cache.num_pages : (uint64_t)p->B;
+    const uint64_t k_rows = cache.page_table ? (uint64_t)cache.page_size
+                                             : (packed ? (uint64_t)cache.total_k : (uint64_t)p->Sk);
+    const uint64_t k_batch = cache.page_table ? (uint64_t)cache.num_pages : (packed ? 1u : (uint64_t)p->B);
     const uint64_t dk[4] = {(uint64_t)p->D / 2, (uint64_t)p->Hkv, k_rows, k_batch};
     const uint64_t sk[3] = {(uint64_t)p->k_stride_h, (uint64_t)p->k_stride_s, (uint64_t)p->k_stride_b};
     const uint32_t bk[4] = {qk_box, 1, (uint32_t)kBlockN, 1};
-    const uint64_t dv[4] = {k_rows / 2, (uint64_t)p->Dv, (uint64_t)p->Hkv, k_batch};
+    const uint64_t dv[4] = {(k_rows + 31) / 32 * 16, (uint64_t)p->Dv, (uint64_t)p->Hkv, k_batch};   // padded key axis
     const uint64_t sv[3] = {(uint64_t)p->v_stride_d, (uint64_t)p->v_stride_h, (uint64_t)p->v_stride_b};
     const uint32_t bv[4] = {64, (uint32_t)p->Dv, 1, 1};
     // a Q / K tile row is D / 2 bytes: 64-byte swizzle for D = 128, 32-byte for D = 64
@@ -332,6 +389,9 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
   kp.page_table = cache.page_table;
   kp.page_size = cache.page_size;
   kp.pages_per_seq = cache.pages_per_seq;
+  kp.cu_seqlens_q = cache.cu_seqlens_q;
+  kp.cu_seqlens_k = cache.cu_seqlens_k;
+  kp.total_q = cache.total_q;
   kp.sl2 = p->softmax_scale * p->q_scale * p->k_scale * 1.4426950408889634f;
   kp.softcap_c1 = 0.f;
   if (softcap > 0.f) {
@@ -382,7 +442,9 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
     const unsigned grid = tiles < (unsigned)sms ? tiles : (unsigned)sms;
     CUtensorMap tm_o;
     {
-      const uint64_t d_o[4] = {(uint64_t)p->Dv, (uint64_t)p->Hq, (uint64_t)p->Sq, (uint64_t)p->B};
+      const bool packed = cache.cu_seqlens_q != nullptr;
+      const uint64_t d_o[4] = {(uint64_t)p->Dv, (uint64_t)p->Hq, packed ? (uint64_t)cache.total_q : (uint64_t)p->Sq,
+                               packed ? 1u : (uint64_t)p->B};
       const uint64_t s_o[3] = {(uint64_t)p->o_stride_h * 2, (uint64_t)p->o_stride_s * 2,
                                (uint64_t)p->o_stride_b * 2};
       if (!encode_out_4d(&tm_o, p->out, d_o, s_o)) return -FA4_E_TENSORMAP;
@@ -637,7 +699,8 @@ extern "C" int fa4_nvfp4_fwd_linear_sf_noalloc(const fa4_nvfp4_params* p, void* 
   // 2. capacity of the array
   const int64_t q_bytes = tiled_sf_bytes((int64_t)p->B * p->Hq, p->Sq, p->D / 16, 1);
   const int64_t k_bytes = tiled_sf_bytes((int64_t)p->B * p->Hkv, p->Sk, p->D / 16, 1);
-  const int64_t v_bytes = tiled_sf_bytes((int64_t)p->B * p->Hkv, p->Dv, p->Sk / 16, 2);
+  const int64_t skp = ((int64_t)p->Sk + 31) / 32 * 32;   // V's padded key axis
+  const int64_t v_bytes = tiled_sf_bytes((int64_t)p->B * p->Hkv, p->Dv, skp / 16, 2);
   if (q_bytes + k_bytes + v_bytes > (int64_t)FA4_STATIC_SCRATCH_BYTES) return -FA4_E_TOO_LARGE;
 
   // 3. device address of the array on the current device
@@ -648,7 +711,7 @@ extern "C" int fa4_nvfp4_fwd_linear_sf_noalloc(const fa4_nvfp4_params* p, void* 
   uint8_t* k_t = q_t + q_bytes;   // multiples of 512: every region stays 256-byte aligned
   uint8_t* v_t = k_t + k_bytes;
 
-  const int64_t cq = p->D / 16, cv = p->Sk / 16;
+  const int64_t cq = p->D / 16, cv = skp / 16;
   // q_sf (B, Sq, Hq, D/16) and k_sf (B, Sk, Hkv, D/16): matrix (b, h) has row stride H * D/16
   if (int e = fa4_nvfp4_sf_linear_to_tiled(p->q_sf, q_t, p->B, p->Hq, p->Sq, (int)cq,
                                            (int64_t)p->Sq * p->Hq * cq, cq, (int64_t)p->Hq * cq, 1,
@@ -669,13 +732,3 @@ extern "C" int fa4_nvfp4_fwd_linear_sf_noalloc(const fa4_nvfp4_params* p, void* 
   tiled.v_sf = v_t;
   return fa4_nvfp4_fwd(&tiled, cuda_stream);
 }
-
-#ifdef FA4_TRACE
-// Timeline capture for one CTA (build with -DFA4_TRACE; not part of the shipped library).
-extern "C" int fa4_nvfp4_debug_set_trace(void* buf, int cta) {
-  unsigned long long* b = static_cast<unsigned long long*>(buf);
-  cudaError_t e = cudaMemcpyToSymbol(fa4::g_trace_buf, &b, sizeof(b));
-  if (e == cudaSuccess) e = cudaMemcpyToSymbol(fa4::g_trace_cta, &cta, sizeof(cta));
-  return (int)e;
-}
-#endif

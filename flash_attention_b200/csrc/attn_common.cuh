@@ -57,6 +57,15 @@ struct KernelParams {
   const int32_t* seqused_k;
   const int32_t* page_table;
   int page_size, pages_per_seq;
+  // Packed variable-length batch (general instantiation only; the reference's cu_seqlens_q /
+  // cu_seqlens_k, flash_attn/cute/interface.py:1795-1840): q, k, v, out are packed along the token
+  // axis without a batch dimension, sequence b owns query rows cu_seqlens_q[b] .. cu_seqlens_q[b+1]
+  // and keys cu_seqlens_k[b] .. cu_seqlens_k[b+1] (B = number of sequences; Sq / Sk = the longest
+  // sequence, which sizes the tile grid -- tiles past a sequence's end visit nothing).  The tiled
+  // scales stay per sequence, padded to that longest length.  LSE is (Hq, total_q).  NULL = dense.
+  const int32_t* cu_seqlens_q;
+  const int32_t* cu_seqlens_k;
+  int total_q;
 };
 
 // Work tile of a CTA.  Tiles are ordered so that, for causal problems, the m-blocks with the
@@ -69,7 +78,16 @@ struct Tile {
   int nb_top;    // K/V block index of the first visited block; the i-th visited is nb_top - i
   int split;
   int sk;        // valid keys of this batch entry (general instantiation; p.Sk otherwise)
+  int sq;        // query rows of this batch entry (packed batches; p.Sq otherwise)
+  int q0, k0;    // first packed query row / key of this entry (packed batches; 0 otherwise)
 };
+
+// Query length that masks, block ranges and stores see.
+template <bool kGeneral>
+__device__ __forceinline__ int query_len(const KernelParams& p, const Tile& t) {
+  if constexpr (kGeneral) return t.sq;
+  return p.Sq;
+}
 
 // Key length that masks and block ranges see.
 template <bool kGeneral>
@@ -97,19 +115,31 @@ __device__ __forceinline__ Tile decode_tile(const KernelParams& p, int tile_idx)
   t.hk = t.h / p.group;
   t.m_blk = p.causal ? (p.num_m_blocks - 1 - m_rev) : m_rev;
   t.sk = p.Sk;
+  t.sq = p.Sq;
+  t.q0 = 0;
+  t.k0 = 0;
   int n = p.num_n_blocks;
   if constexpr (kGeneral) {
-    if (p.seqused_k != nullptr) {
-      const int used = p.seqused_k[t.b];
-      t.sk = used < 0 ? 0 : (used < p.Sk ? used : p.Sk);
+    if (p.cu_seqlens_q != nullptr) {
+      t.q0 = p.cu_seqlens_q[t.b];
+      t.sq = p.cu_seqlens_q[t.b + 1] - t.q0;
+      t.k0 = p.cu_seqlens_k[t.b];
+      t.sk = p.cu_seqlens_k[t.b + 1] - t.k0;
       n = (t.sk + kBlockN - 1) / kBlockN;
     }
+    if (p.seqused_k != nullptr) {
+      const int used = p.seqused_k[t.b];
+      t.sk = used < 0 ? 0 : (used < t.sk ? used : t.sk);
+      n = (t.sk + kBlockN - 1) / kBlockN;
+    }
+    if (t.m_blk * kBlockM >= t.sq) n = 0;   // a tile past the end of a short sequence
   }
   const int sk = key_len<kGeneral>(p, t);
+  const int sq = query_len<kGeneral>(p, t);
   if (p.causal) {
     // last visible key of the tile's last row: (m_blk + 1) * 128 - 1 + Sk - Sq
     // (block range of flash_attn/cute/block_info.py:23-55, bottom-right aligned)
-    const int last = (t.m_blk + 1) * kBlockM + sk - p.Sq + (kGeneral ? p.win_right : 0);  // exclusive
+    const int last = (t.m_blk + 1) * kBlockM + sk - sq + (kGeneral ? p.win_right : 0);  // exclusive
     int nb = (last + kBlockN - 1) / kBlockN;
     if (last <= 0) nb = 0;
     n = nb < n ? nb : n;
@@ -118,7 +148,7 @@ __device__ __forceinline__ Tile decode_tile(const KernelParams& p, int tile_idx)
     // first block that holds a visible key of the tile's first row (left window limit)
     int n_min = 0;
     if (p.win_left >= 0) {
-      const int first = t.m_blk * kBlockM + sk - p.Sq - p.win_left;
+      const int first = t.m_blk * kBlockM + sk - sq - p.win_left;
       n_min = first > 0 ? first / kBlockN : 0;
       if (n_min > n) n_min = n;
     }
@@ -149,20 +179,20 @@ __device__ __forceinline__ int causal_limit(const KernelParams& p, const Tile& t
   const int sk = key_len<kGeneral>(p, t);
   const int len_limit = sk - 1 - nb * kBlockN;
   if (!p.causal) return len_limit;
-  const int c = t.m_blk * kBlockM + row_in_tile + sk - p.Sq + (kWindow ? p.win_right : 0) - nb * kBlockN;
+  const int c = t.m_blk * kBlockM + row_in_tile + sk - query_len<kGeneral>(p, t) + (kWindow ? p.win_right : 0) - nb * kBlockN;
   return c < len_limit ? c : len_limit;
 }
 // In-block index of the FIRST visible key (left window limit); <= 0 when nothing is cut.
 __device__ __forceinline__ int lower_limit(const KernelParams& p, const Tile& t, int row_in_tile,
                                            int nb) {
   if (p.win_left < 0) return -(1 << 30);
-  return t.m_blk * kBlockM + row_in_tile + t.sk - p.Sq - p.win_left - nb * kBlockN;
+  return t.m_blk * kBlockM + row_in_tile + t.sk - t.sq - p.win_left - nb * kBlockN;
 }
 template <bool kGeneral = false, bool kWindow = kGeneral>
 __device__ __forceinline__ bool block_needs_mask(const KernelParams& p, const Tile& t, int nb) {
   const int sk = key_len<kGeneral>(p, t);
   const bool partial = (nb + 1) * kBlockN > sk;
-  const int off = t.m_blk * kBlockM + sk - p.Sq;
+  const int off = t.m_blk * kBlockM + sk - query_len<kGeneral>(p, t);
   bool need = partial || (p.causal && (nb * kBlockN + kBlockN - 1 > off + (kWindow ? p.win_right : 0)));
   if constexpr (kWindow) {
     // the last row of the tile has the highest left limit

@@ -72,28 +72,6 @@
 
 namespace fa4 {
 
-// Optional per-role timeline (compile with -DFA4_TRACE): lane 0 of every warp of ONE CTA appends
-// (event, block index, clock64) records to a global buffer set by fa4_nvfp4_debug_set_trace.
-#ifdef FA4_TRACE
-__device__ unsigned long long* g_trace_buf = nullptr;   // [24 warps][kTraceCap][2]
-__device__ int g_trace_cta = 0;
-constexpr int kTraceCap = 1024;
-#define FA4_TRACE_DECL int trace_n = 0;
-#define FA4_TRACE_EV(ev, idx)                                                                  \
-  do {                                                                                         \
-    if (g_trace_buf != nullptr && (int)blockIdx.x == g_trace_cta && (threadIdx.x & 31) == 0 && \
-        trace_n < kTraceCap) {                                                                 \
-      unsigned long long* r_ = g_trace_buf + ((threadIdx.x >> 5) * kTraceCap + trace_n) * 2;   \
-      r_[0] = ((unsigned long long)(ev) << 32) | (unsigned)(idx);                              \
-      r_[1] = clock64();                                                                       \
-      ++trace_n;                                                                               \
-    }                                                                                          \
-  } while (0)
-#else
-#define FA4_TRACE_DECL
-#define FA4_TRACE_EV(ev, idx) do {} while (0)
-#endif
-
 namespace ws {
 
 constexpr int kStagesK = 4;
@@ -375,8 +353,6 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
   constexpr uint32_t kQkBytes = 128u * kD / 2;         // bytes of a Q or K tile
   constexpr uint32_t kQkSfBytes = kSteps * 512u;       // its scale chunks (128 rows x kD / 16)
   constexpr uint32_t kVBytes = kD * 64u;               // V tile: kD rows of 128 keys
-  FA4_TRACE_DECL
-  FA4_TRACE_EV(0, 0);
 
   // Every role walks the same tile list with the same counters:
   //   gb = number of K/V blocks of the tiles before the current one, ti = number of non-empty
@@ -515,7 +491,6 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
           }
           ok = mbar_wait(bars.at(Bars::kKFull + st), (G / kStagesK) & 1, wc, kSiteKFull);
           if (!ok) break;
-          FA4_TRACE_EV(20, G);
           tc_fence_after_sync();
           const uint32_t sfk = tmem + kTmSFK + 8 * b;
           const uint32_t ksf = base + kOffSFK + st * kSfBytes, kt = base + kOffK + st * kTileBytes;
@@ -528,7 +503,6 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
                      j > 0 ? 1u : 0u);
           }
           tc_commit(bars.at(Bars::kSFull + st));
-          FA4_TRACE_EV(27, G);
         }
         if (!ok) break;
         tc_commit(bars.at(Bars::kQEmpty + qb));  // the Q buffer is free once the tile's QK^T have run
@@ -562,7 +536,6 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
             ok = mbar_wait(bars.at(Bars::kOFree), (ti - 1) & 1, wc, kSiteOFree);
             if (!ok) break;
           }
-          FA4_TRACE_EV(22, G);
           tc_fence_after_sync();
           const uint32_t sfp = tmem + kTmSFP + 8 * b, sfv = tmem + kTmSFV + 8 * b;
           const uint32_t ps = G % kStagesP;
@@ -577,7 +550,6 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
           mma_nvf4(tmem + kTmO, make_desc_sw64(pt + 32), make_desc_sw64(vt + 32), idesc_pv, sfp + 4,
                    sfv + 4, 1u);
           tc_commit(bars.at(Bars::kPvDone + st));
-          FA4_TRACE_EV(23, G);
         }
         if (!ok) break;
         gb += n;
@@ -639,7 +611,6 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         const bool r_f = (G >= 2) ? mbar_test(bar_f, par_f) : true;
         ok = wait_probed(r_s, bar_s, par_s, wc, kSiteSFull);
         if (!ok) break;
-        FA4_TRACE_EV(30, G);
         tc_fence_after_sync();
         const bool masked = block_needs_mask<kGeneral, kWindow>(p, t, nb);
         const int limit = causal_limit<kGeneral, kWindow>(p, t, row, nb);
@@ -698,7 +669,6 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
                             __float_as_uint(bm[7]));
         dst[2] = make_uint4(0u, 0u, __float_as_uint(m_prev), __float_as_uint(m_new));
         mbar_arrive(bars.at(Bars::kStReady + b));
-        FA4_TRACE_EV(31, G);
       }
       if (!ok) break;
       gb += n;
@@ -727,7 +697,6 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
       for (int i = (g - gb) & 1; i < n; i += 2) {
         const uint32_t G = gb + i, b = G & 1;  // b == g: S / P / stats buffer of this block
         const int nb = (kGeneral ? t.nb_top : n - 1) - i;
-        FA4_TRACE_EV(1, G);
         // Probe the barriers this block depends on early so that their latencies overlap; the
         // blocking (bounded) wait only runs for a probe that failed.
         const uint32_t bar_r = bars.at(Bars::kStReady + b), par_r = (G >> 1) & 1;
@@ -780,7 +749,6 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         //    G - kStagesP has completed
         ok = wait_probed(r_p, bar_p, par_p, wc, kSitePvDone);
         if (!ok) break;
-        FA4_TRACE_EV(6, G);
         uint8_t* p_tile = gbase + kOffP + (G % kStagesP) * kTileBytes;
         uint4 chunk;
         l_sum += quantize_pair(&s[0], noff4[0], noff4[1],
@@ -789,7 +757,6 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         l_sum += quantize_pair(&s[32], noff4[2], noff4[3],
                                __byte_perm(ue, 0u, 0x4442u), __byte_perm(ue, 0u, 0x4443u), p.sl2, chunk);
         *reinterpret_cast<uint4*>(p_tile + sw64_offset(row, 2 * half + 1)) = chunk;
-        FA4_TRACE_EV(7, G);
         // scales of this half: one 64-key MMA step = scale word `half`
         *reinterpret_cast<uint32_t*>(gbase + kOffSFP + (G % kStagesP) * kSfBytes + 512 * half + (row & 31) * 16 +
                                      (row >> 5) * 4) = block_scale_bytes(ue);
@@ -825,7 +792,6 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         mbar_arrive(bars.at(Bars::kFin));
         ok = __all_sync(0xffffffffu, mbar_wait(bars.at(Bars::kFin), ti & 1, wc, kSiteFin));
         if (!ok) break;
-        FA4_TRACE_EV(40, gb);
         float lw[4], mw[4];
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
@@ -847,7 +813,6 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
         ok = __all_sync(0xffffffffu,
                         mbar_wait(bars.at(Bars::kPvDone + (Gl % kStagesV)), (Gl / kStagesV) & 1, wc, kSiteFinalO));
         if (!ok) break;
-        FA4_TRACE_EV(41, gb);
         tc_fence_after_sync();
         scale = (l_tot > 0.f) ? p.out_scale / l_tot : 0.f;
       }
@@ -884,7 +849,6 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q,
           p.lse[((int64_t)t.b * p.Hq + t.h) * p.Sq + q_idx] = lse_v;
         }
       }
-      FA4_TRACE_EV(42, gb);
       gb += n;
       ti += (n > 0) ? 1u : 0u;
     }

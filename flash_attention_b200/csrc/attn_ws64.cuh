@@ -34,31 +34,6 @@
 #pragma once
 #include "attn_ws.cuh"
 
-// Optional phase profile (compile with -DFA4_TRACE -DFA4_PHASES): every warp of one CTA accumulates
-// the clocks it spends between marks in registers and lane 0 dumps them when the kernel ends.
-#ifdef FA4_PHASES
-#undef FA4_TRACE_EV
-#define FA4_TRACE_EV(ev, idx) do {} while (0)
-#define FA4_PH_DECL uint32_t ph_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; uint32_t ph_t = clock(); uint32_t ph_cnt = 0; const uint32_t ph_t0 = ph_t;
-#define FA4_PH_COUNT() do { ph_cnt += 1; } while (0)
-#define FA4_PH_RESET() do { ph_t = clock(); } while (0)
-#define FA4_PH(k) do { const uint32_t c_ = clock(); ph_acc[k] += c_ - ph_t; ph_t = c_; } while (0)
-#define FA4_PH_DUMP()                                                                         \
-  do {                                                                                        \
-    if (g_trace_buf != nullptr && (threadIdx.x & 31) == 0) {                                  \
-      unsigned long long* d_ = g_trace_buf + ((size_t)blockIdx.x * 24 + (threadIdx.x >> 5)) * 16; \
-      for (int k_ = 0; k_ < 8; ++k_) d_[k_] = ph_acc[k_];                                     \
-      d_[8] = ph_cnt; d_[9] = clock() - ph_t0;                                                \
-    }                                                                                         \
-  } while (0)
-#else
-#define FA4_PH_DECL
-#define FA4_PH_COUNT() do {} while (0)
-#define FA4_PH_RESET() do {} while (0)
-#define FA4_PH(k) do {} while (0)
-#define FA4_PH_DUMP() do {} while (0)
-#endif
-
 namespace fa4 {
 namespace ws64 {
 
@@ -137,7 +112,7 @@ __device__ __forceinline__ int window_visit_block(int i, int n, int nb_lo, bool 
   return i < n - 2 ? nb_lo + 2 + i : nb_lo + (i - (n - 2));
 }
 __device__ __forceinline__ bool window_rotates(const KernelParams& p, const Tile& t) {
-  return p.win_left >= 0 && t.n_blocks > 2 && (t.m_blk * kBlockM + t.sk - p.Sq - p.win_left) > 0;
+  return p.win_left >= 0 && t.n_blocks > 2 && (t.m_blk * kBlockM + t.sk - t.sq - p.win_left) > 0;
 }
 
 // byte offset of 16-byte chunk c (0, 1) of row r in a P tile (rows of 32 bytes, 32-byte swizzle)
@@ -187,8 +162,6 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
   const WaitCtx wc{s_abort, p.status, p.budget_ns, p.epoch};
   const int num_tiles = p.num_m_blocks * p.Hq * p.B;
   const int ncta = gridDim.x, cta = blockIdx.x;
-  FA4_TRACE_DECL
-  FA4_PH_DECL
 
   if (tid == 0) {
     *s_abort = 0u;
@@ -289,6 +262,10 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
       const Tile t = decode_tile<kWindow || kCache>(p, tile);
       const int n = t.n_blocks;
       const int q_idx = t.m_blk * kBlockM + row;
+      if constexpr (kWindow || kCache) {
+        // a tile past the end of a short sequence of a packed batch has no rows at all
+        if (t.m_blk * kBlockM >= t.sq) continue;
+      }
       float scale = 0.f, m_fin = kNegInf, l_tot = 0.f;
       if (n > 0) {
         const uint32_t fb = ti & 1;
@@ -352,20 +329,39 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
       }
       fence_proxy_async_smem();
       FA4_EPI_SYNC()
-      if (leader) {
+      const int sq = query_len<kWindow || kCache>(p, t);
+      const bool packed = (kWindow || kCache) && p.cu_seqlens_q != nullptr;
+      if (packed && (t.m_blk + 1) * kBlockM > sq) {
+        // last, partial tile of a packed sequence: a tiled store would run into the rows of the
+        // next sequence (the tensor map only clips at the end of the whole batch), so every
+        // thread copies its own row from the staging tile, if it has one
+        if (q_idx < sq) {
+          __nv_bfloat16* orow = p.out + (int64_t)(t.q0 + q_idx) * p.o_stride_s + (int64_t)t.h * p.o_stride_h;
+#pragma unroll
+          for (int c16 = 0; c16 < kDv / 8; ++c16) {
+            const uint8_t* src = gbase + kOffOut + (c16 >> 3) * (16 * 1024) + row * 128 + (((c16 & 7) ^ (row & 7)) << 4);
+            reinterpret_cast<uint4*>(orow)[c16] = *reinterpret_cast<const uint4*>(src);
+          }
+        }
+      } else if (leader) {
 #pragma unroll
         for (int bx = 0; bx < kDv / 64; ++bx) {
-          tma_store_4d(&tm_o, base + kOffOut + bx * 16 * 1024, 64 * bx, t.h, t.m_blk * kBlockM, t.b);
+          tma_store_4d(&tm_o, base + kOffOut + bx * 16 * 1024, 64 * bx, t.h, t.q0 + t.m_blk * kBlockM,
+                       packed ? 0 : t.b);
         }
         bulk_commit_group();
       }
-      if (q_idx < p.Sq && p.lse != nullptr) {
+      if (q_idx < sq && p.lse != nullptr) {
         float lse_v = finish_lse(m_fin, l_tot, p.sl2);
         if constexpr (kGeneral) {
           // a row without visible keys still has its sink: LSE = sink, output zero
           if (p.sink != nullptr && m_fin == kNegInf) lse_v = p.sink[t.h];
         }
-        p.lse[((int64_t)t.b * p.Hq + t.h) * p.Sq + q_idx] = lse_v;
+        if (packed) {
+          p.lse[(int64_t)t.h * p.total_q + t.q0 + q_idx] = lse_v;   // (Hq, total_q)
+        } else {
+          p.lse[((int64_t)t.b * p.Hq + t.h) * p.Sq + q_idx] = lse_v;
+        }
       }
       gb += n;
       ti += (n > 0) ? 1u : 0u;
@@ -394,8 +390,11 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
           if (!ok) break;
         }
         mbar_arrive_expect_tx(bars.at(Bars::kQFull + qb), kQkBytes + kQkSfBytes);
+        // a packed batch has no batch dimension: the sequence's first row is added to the row
+        // coordinate instead (the scale tiles stay per sequence)
+        const bool packed = (kWindow || kCache) && p.cu_seqlens_q != nullptr;
         load_qk_tile(base + kOffQ + qb * kQkSlot, &tm_q, bars.at(Bars::kQFull + qb), t.h,
-                     t.m_blk * kBlockM, t.b);
+                     t.q0 + t.m_blk * kBlockM, packed ? 0 : t.b);
         bulk_load(base + kOffSFQ + qb * kQkSfSlot,
                   p.q_sf + t.b * p.qsf_stride_b + t.h * p.qsf_stride_h + (int64_t)t.m_blk * kQkSfBytes,
                   kQkSfBytes, bars.at(Bars::kQFull + qb));
@@ -427,7 +426,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
             int kb, nbl;
             locate(nb, kb, nbl);
             load_qk_tile(base + kOffK + st * kQkSlot, &tm_k, bars.at(Bars::kKFull + st), t.hk,
-                         nbl * kBlockN, kb);
+                         t.k0 + nbl * kBlockN, packed ? 0 : kb);
             bulk_load(base + kOffSFK + st * kQkSfSlot,
                       p.k_sf + kb * p.ksf_stride_b + t.hk * p.ksf_stride_h + (int64_t)nbl * kQkSfBytes,
                       kQkSfBytes, bars.at(Bars::kKFull + st));
@@ -444,7 +443,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
             int kb, nbl;
             locate(nb, kb, nbl);
             tma_load_4d(base + kOffV + st * kTileBytes, &tm_v, bars.at(Bars::kVFull + st),
-                        nbl * (kBlockN / 2), 0, t.hk, kb);
+                        (t.k0 + nbl * kBlockN) / 2, 0, t.hk, packed ? 0 : kb);
             bulk_load(base + kOffSFV + st * kSfBytes,
                       p.v_sf + kb * p.vsf_stride_b + t.hk * p.vsf_stride_h + (int64_t)nbl * kSfBytes,
                       kSfBytes, bars.at(Bars::kVFull + st));
@@ -488,12 +487,9 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
         }
         for (int i = 0; ok && i < n; ++i) {
           const uint32_t G = gb + i, st = G % kStagesK;
-          FA4_PH(0);
           // the K tile has landed (the copy warp saw k_full) and its scales are in tensor memory
           ok = mbar_wait(bars.at(Bars::kKsf + st), (G / kStagesK) & 1, wc, kS64Ksf);
           if (!ok) break;
-          FA4_PH(1);
-          FA4_TRACE_EV(20, G);
           tc_fence_after_sync();
           const uint32_t sfk = tmem + kTmSFK64 + 12 * st;
           const uint32_t kt = base + kOffK + st * kQkSlot;
@@ -501,24 +497,18 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
           // (keys 0-63 and 64-127 of the tile): half the tcgen05 instructions of two N = 64
           // products, and the in-order issue slots of this thread are scarce
           const uint32_t J0 = 2 * G, b0 = J0 % kSBufs;  // 0 or 2
-          FA4_PH(0);
           if (J0 >= kSBufs) {
             ok = mbar_wait(bars.at(Bars::kSFree + b0), ((J0 - kSBufs) / kSBufs) & 1, wc, kS64SFree) &&
                  mbar_wait(bars.at(Bars::kSFree + b0 + 1), ((J0 - kSBufs) / kSBufs) & 1, wc, kS64SFree);
             if (!ok) break;
             tc_fence_after_sync();
           }
-          FA4_TRACE_EV(21, J0);
-          FA4_PH(2);
 #pragma unroll
           for (int ks = 0; ks < kSteps; ++ks) {
             mma_nvf4(tmem + kTmS64 + 64 * b0, dq[ks], desc_qk(kt, ks), idesc_qk,
                      tmem + kTmSFQ64 + 4 * ks, sfk + 4 * ks, ks > 0 ? 1u : 0u);
           }
-          FA4_PH(4);
           tc_commit(bars.at(Bars::kSFull + b0));  // both softmax warpgroups of the pair wait on it
-          FA4_PH(5);
-          FA4_TRACE_EV(27, J0);
           tc_commit(bars.at(Bars::kKFree + st));  // the K stage is free once both products have run
         }
         if (!ok) break;
@@ -539,35 +529,26 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
         if (n == 0) continue;
         for (int i = 0; ok && i < n; ++i) {
           const uint32_t G = gb + i, st = G % kStagesV;
-          FA4_PH(0);
           ok = mbar_wait(bars.at(Bars::kVsf + st), (G / kStagesV) & 1, wc, kS64Vsf);
           if (!ok) break;
-          FA4_PH(1);
           const uint32_t vt = base + kOffV + st * kTileBytes;
 #pragma unroll
           for (int s = 0; s < 2; ++s) {
             const uint32_t J = 2 * G + s, slot = J % kPSlots, tb = J % kSBufs;
             const uint32_t h64 = s;
-            FA4_PH(0);
             ok = mbar_wait(bars.at(Bars::kPFull + slot), (J / kPSlots) & 1, wc, kS64PFull);
             if (!ok) break;
-            FA4_PH(2);
             if (i == 0 && s == 0 && ti >= 1) {
               // O of the previous tile must have been copied out of tensor memory
               ok = mbar_wait(bars.at(Bars::kOFree), (ti - 1) & 1, wc, kS64OFree);
               if (!ok) break;
             }
-            FA4_TRACE_EV(22, J);
             tc_fence_after_sync();
             const uint32_t sfp = tmem + kTmSFP64 + 4 * tb, sfv = tmem + kTmSFV64 + 8 * st + 4 * h64;
             tc_cp_sf(sfp, base + kOffSFP + slot * 512);
-            FA4_PH(3);
             mma_nvf4(tmem + kTmO, make_desc_sw32(base + kOffP + slot * kPTileBytes),
                      make_desc_sw64(vt + 32 * h64), idesc_pv, sfp, sfv, (i > 0 || s > 0) ? 1u : 0u);
-            FA4_PH(5);
             tc_commit(bars.at(Bars::kPvDone + slot));
-            FA4_PH(6);
-            FA4_TRACE_EV(23, J);
           }
           if (!ok) break;
           tc_commit(bars.at(Bars::kVFree + st));
@@ -645,11 +626,8 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
         const bool r_p = (J >= kPSlots) ? mbar_test(bar_p, par_p) : true;
 
         // 1. the scores of this sub-block: the whole 64-key row of this thread
-        FA4_PH(7);
         ok = wait_probed(mbar_test(bar_s, par_s), bar_s, par_s, wc, kS64SFull);
         if (!ok) break;
-        FA4_PH(0);
-        FA4_TRACE_EV(5, J);
         tc_fence_after_sync();
         if (block_needs_mask<kWindow || kCache, kWindow>(p, t, nb)) {
           if constexpr (kWindow) {
@@ -679,8 +657,6 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
         tc_wait_ld();
         tc_fence_before_sync();
         mbar_arrive(bars.at(Bars::kSFree + wg));
-        FA4_TRACE_EV(3, J);
-        FA4_PH(1);
         if constexpr (kGeneral) {
           if (p.softcap_c1 != 0.f) {
 #pragma unroll
@@ -702,24 +678,29 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
           bm4[q] = fmaxf(m0, m1);
         }
         const float m_loc = fmaxf(fmaxf(bm4[0], bm4[1]), fmaxf(bm4[2], bm4[3]));
-        FA4_PH(2);
-        FA4_PH(6);
         const float m_new = next_reference(m_prev, m_loc, p.sl2);
         s_hand[wg * 128 + row] = m_new;
         mbar_arrive(bars.at(Bars::kHand + 4 * wg + (warp & 3)));
         float noff4[4];
-        uint32_t ue;
-        block_exponents4(bm4, m_new, p.sl2, noff4, ue);
+        uint32_t sbits4[4], sf_bytes;
+#if FA4_P_SCALE_E4M3
+        block_scales4_e4m3(bm4, m_new, p.sl2, noff4, sf_bytes, sbits4);
+#else
+        {
+          uint32_t ue;
+          block_exponents4(bm4, m_new, p.sl2, noff4, ue);
+          sf_bytes = block_scale_bytes(ue);
+#pragma unroll
+          for (int b4 = 0; b4 < 4; ++b4) sbits4[b4] = __byte_perm(ue, 0u, 0x4440u + b4) << 23;  // 2^e as fp32
+        }
+#endif
         // own partial row sum follows the reference
         if (m_new != m_ref) l_sum *= reference_factor(m_ref, m_new, p.sl2);
         m_ref = m_new;
-        FA4_PH(3);
 
         // 3. exponentials and quantisation; P slot J % 8 is free once P V of sub-block J - 8 has run
         ok = wait_probed(r_p, bar_p, par_p, wc, kS64PvDone);
         if (!ok) break;
-        FA4_TRACE_EV(6, J);
-        FA4_PH(4);
         uint8_t* p_tile = gbase + kOffP + slot * kPTileBytes;
         {
           uint32_t pk[8];
@@ -727,16 +708,14 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
 #pragma unroll
           for (int b4 = 0; b4 < 4; ++b4) {
             const float bsum = quantize_block16(&s[16 * b4], noff4[b4], p.sl2, pk[2 * b4], pk[2 * b4 + 1]);
-            // 2^e as fp32: byte (e + 127) moved into the exponent field
-            acc = fmaf(bsum, __uint_as_float(__byte_perm(ue, 0u, 0x4440u + b4) << 23), acc);
+            acc = fmaf(bsum, __uint_as_float(sbits4[b4]), acc);   // times the block scale
           }
           l_sum += acc;
           *reinterpret_cast<uint4*>(p_tile + sw32_offset(row, 0)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
           *reinterpret_cast<uint4*>(p_tile + sw32_offset(row, 1)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
         }
         // the four scale bytes of this row: one word of the 512-byte chunk
-        *reinterpret_cast<uint32_t*>(gbase + kOffSFP + slot * 512 + (row & 31) * 16 + (row >> 5) * 4) =
-            block_scale_bytes(ue);
+        *reinterpret_cast<uint32_t*>(gbase + kOffSFP + slot * 512 + (row & 31) * 16 + (row >> 5) * 4) = sf_bytes;
 
         // 4. correction (rare, out of line): O holds the sub-blocks before this one relative to
         //    m_prev and must move to m_new before P V of this sub-block is issued; this thread
@@ -756,13 +735,9 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
         fence_proxy_async_smem();
         tc_fence_before_sync();
         mbar_arrive(bars.at(Bars::kPFull + slot));
-        FA4_TRACE_EV(7, J);
-        FA4_PH(5);
-        FA4_PH_COUNT();
       }
       if (!ok) break;
 
-      FA4_PH(7);
       // ---- tile end: hand the partial row sum and its reference to the epilogue warpgroup and
       //      go on with the next tile
       if (n > 0) {
@@ -782,10 +757,8 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
       }
       gb += n;
       ti += (n > 0) ? 1u : 0u;
-      FA4_PH(7);
     }
   }
-  FA4_PH_DUMP();
 #undef FA4_FOR_EACH_TILE
 
   tc_fence_before_sync();

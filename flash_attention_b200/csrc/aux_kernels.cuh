@@ -49,6 +49,56 @@ __global__ void sf_linear_to_tiled_kernel(const uint8_t* __restrict__ src, uint8
 }
 
 // ---------------------------------------------------------------------------------------------
+// The same conversion for a PACKED batch (sequences concatenated along the token axis, bounds in
+// cu_seqlens on the device): every sequence gets its own tiles, padded with zeros to the longest
+// sequence, so that a tile never mixes two sequences.
+//   packed_rows = 1: the packed axis is the row axis (q / k scales, (total, H, cols)): matrix
+//       (b, h) has rows cu[b] .. cu[b+1] at src + row * stride_row + h * stride_inner
+//   packed_rows = 0: the packed axis is the column axis (v scales, (H, rows, total / 16)): matrix
+//       (b, h) has `rows` rows at src + h * stride_inner + r * stride_row and the columns
+//       cu[b] / 16 .. ceil(cu[b+1] / 16) (sequence starts are multiples of 16 keys)
+// dst: (num_seqs, n_inner, ceil(max_rows / 128), col tiles of max_cols, 512).
+// ---------------------------------------------------------------------------------------------
+__global__ void sf_linear_to_tiled_packed_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
+                                                 const int32_t* __restrict__ cu, int num_seqs, int n_inner,
+                                                 int max_rows, int max_cols, int64_t stride_inner,
+                                                 int64_t stride_row, int col_tile_multiple, int packed_rows) {
+  const int row_tiles = (max_rows + 127) / 128;
+  const int col_tiles = ((max_cols + 3) / 4 + col_tile_multiple - 1) / col_tile_multiple * col_tile_multiple;
+  const int64_t total = (int64_t)num_seqs * n_inner * row_tiles * col_tiles * 32;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int l = (int)(idx & 31);
+    int64_t tile = idx >> 5;
+    const int ct = (int)(tile % col_tiles);
+    tile /= col_tiles;
+    const int rt = (int)(tile % row_tiles);
+    tile /= row_tiles;
+    const int mi = (int)(tile % n_inner);
+    const int mo = (int)(tile / n_inner);
+    const int c0 = cu[mo], c1 = cu[mo + 1];
+    const int rows = packed_rows ? (c1 - c0) : max_rows;
+    const int cols = packed_rows ? max_cols : ((c1 - c0 + 15) >> 4);
+    const uint8_t* m = src + mi * stride_inner + (packed_rows ? (int64_t)c0 * stride_row : (int64_t)(c0 >> 4));
+    uint32_t w[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int r = rt * 128 + c * 32 + l;
+      uint32_t v = 0;
+      if (r < rows) {
+        const uint8_t* pr = m + (int64_t)r * stride_row + ct * 4;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          if (ct * 4 + k < cols) v |= (uint32_t)pr[k] << (8 * k);
+        }
+      }
+      w[c] = v;
+    }
+    reinterpret_cast<uint4*>(dst)[idx] = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // Probe: S (128 x 128 fp32) = Q tile x K tile^T, head dim 128, through exactly the descriptors
 // the attention kernels use.  mode bit 0 = stage operands with plain stores (the path P takes)
 // instead of TMA.

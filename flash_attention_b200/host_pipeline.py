@@ -37,10 +37,11 @@ class HostPipeline:
         u8 = torch.uint8
         self.q = torch.empty(B, Sq, Hq, D // 2, dtype=u8, device=dev)
         self.k = torch.empty(B, Sk, Hkv, D // 2, dtype=u8, device=dev)
-        self.v = torch.empty(B, Hkv, Dv, Sk // 2, dtype=u8, device=dev)
+        skp = (Sk + 31) // 32 * 32          # V's key axis is padded to whole 32-key groups
+        self.v = torch.empty(B, Hkv, Dv, skp // 2, dtype=u8, device=dev)
         self.q_sf = torch.empty(B, Sq, Hq, D // 16, dtype=u8, device=dev)
         self.k_sf = torch.empty(B, Sk, Hkv, D // 16, dtype=u8, device=dev)
-        self.v_sf = torch.empty(B, Hkv, Dv, Sk // 16, dtype=u8, device=dev)
+        self.v_sf = torch.empty(B, Hkv, Dv, skp // 16, dtype=u8, device=dev)
         self.out = torch.empty(B, Sq, Hq, Dv, dtype=torch.bfloat16, device=dev)
         self.lse = torch.empty(B, Hq, Sq, dtype=torch.float32, device=dev)
         self.s_in = torch.cuda.Stream(dev)
@@ -110,8 +111,8 @@ class HostPipeline:
         Sq = self.shape[1]
         whole = (s1 - s0 == Sq)
         _, lse_piece = flash_attn_fp4_func(
-            self.q[b:b + 1, s0:s1], self.k[b:b + 1, :sk], self.v[b:b + 1, :, :, :sk // 2],
-            self.q_sf[b:b + 1, s0:s1], self.k_sf[b:b + 1, :sk], self.v_sf[b:b + 1, :, :, :sk // 16],
+            self.q[b:b + 1, s0:s1], self.k[b:b + 1, :sk], self.v[b:b + 1, :, :, :(sk + 31) // 32 * 16],
+            self.q_sf[b:b + 1, s0:s1], self.k_sf[b:b + 1, :sk], self.v_sf[b:b + 1, :, :, :(sk + 31) // 32 * 2],
             q_scale, k_scale, v_scale, softmax_scale=softmax_scale, causal=causal, return_lse=True,
             out=self.out[b:b + 1, s0:s1], lse=self.lse[b:b + 1] if whole else None, sf_layout="linear")
         if not whole:

@@ -106,8 +106,9 @@ def flash_attn_fp4_func(
 ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
     """NVFP4 attention forward.
 
-    q (B,Sq,Hq,D/2), k (B,Sk,Hkv,D/2), v (B,Hkv,Dv,Sk/2): packed e2m1 bytes (V key-contiguous).
-    *_sf: e4m3 block scales, ``sf_layout="linear"``: (B,S,H,D/16) / (B,Hkv,Dv,Sk/16), converted
+    q (B,Sq,Hq,D/2), k (B,Sk,Hkv,D/2), v (B,Hkv,Dv,Skp/2): packed e2m1 bytes (V key-contiguous, its
+    key axis padded with zeros to Skp = Sk rounded up to a multiple of 32; the quantisers do that).
+    *_sf: e4m3 block scales, ``sf_layout="linear"``: (B,S,H,D/16) / (B,Hkv,Dv,Skp/16), converted
     to the tiled layout by a small kernel; ``"tiled"``: already (B,H,ceil(rows/128),column tiles,512), see ``sf_to_tiled``.
     *_scale: fp32 per-tensor scales.  Returns ``(out bf16 (B,Sq,Hq,Dv), lse fp32 (B,Hq,Sq) | None)``.
 
@@ -138,8 +139,8 @@ def flash_attn_fp4_func(
     cache slots must not be NaN encodings (a zero-filled cache is fine).
 
     Built so far: D = Dv = 128 or 64, or (D, Dv) = (192, 128) (every feature but split-KV and the
-    decode kernel); any Sq; Sk a multiple of 32 (partial last tiles are handled by zero-filled
-    loads, a key-length mask and unstored rows).  Anything else raises ``NotImplementedError``
+    decode kernel); any Sq and Sk, as in the reference (partial last tiles are handled by
+    zero-filled loads, a key-length mask and unstored rows).  Anything else raises ``NotImplementedError``
     before a launch.
     """
     q, k, v = _as_u8(q, "q"), _as_u8(k, "k"), _as_u8(v, "v")
@@ -171,22 +172,22 @@ def flash_attn_fp4_func(
             "seqused_k must be a (B,) int32 CUDA tensor"
         seqused_k = seqused_k.contiguous()
     assert Dhk == Dh, "q and k head dims differ"
-    assert Hv == Hkv and Skh * 2 == Sk_kv, f"v must be (B, Hkv, Dv, Sk/2), got {tuple(v.shape)}"
+    Sk_pad = (Sk_kv + 31) // 32 * 32           # V's key axis is padded to whole 32-key groups (zeros)
+    assert Hv == Hkv and Skh * 2 == Sk_pad, \
+        f"v must be (B, Hkv, Dv, Skp/2) with Skp = seqlen_k rounded up to a multiple of 32, got {tuple(v.shape)}"
     assert Hq % Hkv == 0, "num_head must be divisible by num_head_kv"
     if not ((D == Dv and D in (64, 128)) or (D == 192 and Dv == 128)):
         raise NotImplementedError(f"head dims (D={D}, Dv={Dv}) not built; supported: (128, 128), (64, 64) "
                                   "and (192, 128)")
     if D != 128 and variant == VARIANT_SERIAL:
         raise NotImplementedError("the serial bring-up variant is built for head dim 128 only")
-    if Sk_kv % 32 != 0:
-        raise NotImplementedError("seqlen_k must be a multiple of 32 (16-key scale blocks, 16-byte rows of V)")
     device = q.device
     if softmax_scale is None:
         softmax_scale = 1.0 / math.sqrt(D)
     if sf_layout == "linear":
         _validate_tensor(q_sf, "q_sf", (B, Sq, Hq, D // 16), torch.uint8, device)
         _validate_tensor(k_sf, "k_sf", (B_kv, Sk_kv, Hkv, D // 16), torch.uint8, device)
-        _validate_tensor(v_sf, "v_sf", (B_kv, Hkv, Dv, Sk_kv // 16), torch.uint8, device)
+        _validate_tensor(v_sf, "v_sf", (B_kv, Hkv, Dv, Sk_pad // 16), torch.uint8, device)
         q_sf, k_sf, v_sf = (t if t.stride(-1) == 1 else t.contiguous() for t in (q_sf, k_sf, v_sf))
         q_sf, k_sf, v_sf = sf_to_tiled(q_sf, 1, 2), sf_to_tiled(k_sf, 1, 2), sf_to_tiled(v_sf, 2, 1, 2)
     elif sf_layout == "tiled":

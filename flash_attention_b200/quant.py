@@ -115,17 +115,29 @@ class NVFP4Tensor:
         return sf_to_tiled(self.sf, 2, 1, 2) if self.is_v else sf_to_tiled(self.sf, 1, 2)
 
     def dequantize(self) -> torch.Tensor:
-        """fp32 values in the reference layout (B, S, H, D) (linear scale factors only)."""
+        """fp32 values in the reference layout (B, S, H, D) (linear scale factors only; for V the
+        key axis still carries its zero padding to a multiple of 32)."""
         assert not self.tiled
         x = dequantize_lastdim(self.data, self.sf, self.scale)
         return x.permute(0, 3, 1, 2).contiguous() if self.is_v else x
+
+
+def _pad_keys(v: torch.Tensor) -> torch.Tensor:
+    """V (B, Sk, H, D) with its key axis padded with zeros to a multiple of 32: V is quantised and
+    stored key-contiguous in blocks of 16 keys, and a row of the packed tensor must be a multiple
+    of 16 bytes for the tiled loads.  The kernels mask keys >= Sk (the length of K)."""
+    pad = (-v.shape[1]) % 32
+    if pad == 0:
+        return v
+    return torch.cat([v, v.new_zeros(v.shape[0], pad, v.shape[2], v.shape[3])], dim=1)
 
 
 def quantize_qkv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor):
     """bf16/fp32 (B,S,H,D) tensors in the reference layout -> three NVFP4Tensor (linear scales)."""
     qd, qs, qg = quantize_lastdim(q)
     kd, ks, kg = quantize_lastdim(k)
-    vt = v.permute(0, 2, 3, 1)  # (B, Hkv, Dv, Sk): blocks along the key axis
+    v = _pad_keys(v)
+    vt = v.permute(0, 2, 3, 1)  # (B, Hkv, Dv, Skp): blocks along the key axis
     vd, vs, vg = quantize_lastdim(vt)
     return (NVFP4Tensor(qd, qs, qg), NVFP4Tensor(kd, ks, kg), NVFP4Tensor(vd, vs, vg, is_v=True))
 
@@ -147,6 +159,7 @@ def quantize_qkv_fused(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, linear
     amax = torch.zeros(3, dtype=torch.float32, device=dev)
     scales = torch.empty(3, dtype=torch.float32, device=dev)
     stream = torch.cuda.current_stream(dev).cuda_stream
+    v = _pad_keys(v)
     for i, (x, is_v) in enumerate(((q, False), (k, False), (v, True))):
         if not (x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 4 and x.stride(-1) == 1):
             raise AssertionError("quantize_qkv_fused takes CUDA bf16 (B, S, H, D) tensors, last dim contiguous")

@@ -1,38 +1,53 @@
 """Variable-length (packed) batches: the call surface of the reference's ``flash_attn_varlen_func``
-(flash_attn/cute/interface.py:1795-1840) for NVFP4 operands.
+(flash_attn/cute/interface.py:1795-1840) for NVFP4 operands, in ONE kernel launch.
 
-Sequences are packed along the token axis, ``cu_seqlens_*`` are the usual exclusive prefix sums:
+Sequences are packed along the token axis, ``cu_seqlens_*`` are the usual exclusive prefix sums
+(int32, on the device):
 
     q     (total_q, Hq,  D/2)    packed e2m1        q_sf  (total_q, Hq,  D/16)
     k     (total_k, Hkv, D/2)                       k_sf  (total_k, Hkv, D/16)
-    v     (Hkv, Dv, total_k/2)   key-contiguous     v_sf  (Hkv, Dv, total_k/16)
+    v     (Hkv, Dv, total_kp/2)  key-contiguous     v_sf  (Hkv, Dv, total_kp/16)
     out   (total_q, Hq, Dv) bf16                    lse   (Hq, total_q) fp32
 
-This first version runs the dense kernel once per sequence on views of the packed tensors (pointer
-offsets and strides only, no copies): every sequence is an independent problem, so the results
-are those of the dense call.  The reference instead walks all sequences inside one persistent
-kernel (tile_scheduler.py:755-1087); with launches of a few microseconds each this wrapper is
-the same thing for prefill-sized sequences and launch-bound for many tiny ones.  Because V is
-blocked by 16 keys and its rows must start on 16-byte boundaries, every key-sequence boundary
-must be a multiple of 32 (pad the keys of a sequence up to it; padded keys are masked when
-``seqused_k`` gives the true lengths).  Query boundaries are free.
+(total_kp = total_k rounded up to a multiple of 32, the padding zero).  The reference walks all
+sequences inside one persistent kernel (flash_attn/cute/tile_scheduler.py:755-1087); so does this:
+the kernel's work list is (sequence, 128-row block of the LONGEST sequence, head), every CTA reads
+the bounds of its sequence from ``cu_seqlens`` on the device, a tile past the end of a short
+sequence is skipped, the last tile of a sequence stores only its own rows.  Nothing is read back
+to the host when ``max_seqlen_q`` / ``max_seqlen_k`` are given, as in the reference's call; without
+them they are taken from ``cu_seqlens`` (one synchronising read).  Because V is blocked by 16 keys
+and its rows must start on 16-byte boundaries, every key-sequence boundary must be a multiple of
+32 (pad the keys of a sequence up to it; ``seqused_k`` gives the true lengths, any value).  Query
+boundaries are free.  The results are bit-identical to dense calls on the single sequences.
 """
 from __future__ import annotations
 
-from typing import Optional, Sequence, Tuple
+import ctypes
+import math
+from typing import Optional, Tuple
 
 import torch
 
-from .interface import flash_attn_fp4_func
+from . import _lib
+from .interface import DeviceStatus, _as_u8, _scalar, resolve_window
 
 
-def _host_offsets(cu, name: str) -> Sequence[int]:
-    if isinstance(cu, torch.Tensor):
-        cu = cu.tolist()          # device tensors are read back once (a synchronisation)
-    cu = [int(x) for x in cu]
-    assert len(cu) >= 2 and cu[0] == 0 and all(b >= a for a, b in zip(cu, cu[1:])), \
-        f"{name} must be non-decreasing and start at 0"
-    return cu
+def _device_i32(x, name: str, device) -> torch.Tensor:
+    if not isinstance(x, torch.Tensor):
+        x = torch.tensor(list(x), dtype=torch.int32)
+    assert x.dim() == 1, f"{name} must be one-dimensional"
+    return x.to(device=device, dtype=torch.int32).contiguous()
+
+
+def _tiled_packed(sf, cu, num_seqs, n_inner, max_rows, max_cols, stride_inner, stride_row, mult, packed_rows):
+    ct = ((max_cols + 3) // 4 + mult - 1) // mult * mult
+    out = torch.empty(num_seqs, n_inner, (max_rows + 127) // 128, ct, 512, dtype=torch.uint8, device=sf.device)
+    stream = torch.cuda.current_stream(sf.device).cuda_stream
+    rc = _lib.lib().fa4_nvfp4_sf_linear_to_tiled_packed(sf.data_ptr(), out.data_ptr(), cu.data_ptr(), num_seqs,
+                                                       n_inner, max_rows, max_cols, stride_inner, stride_row,
+                                                       mult, 1 if packed_rows else 0, stream)
+    _lib.check(rc, "fa4_nvfp4_sf_linear_to_tiled_packed")
+    return out
 
 
 def flash_attn_varlen_fp4_func(
@@ -40,50 +55,118 @@ def flash_attn_varlen_fp4_func(
     q_sf: torch.Tensor, k_sf: torch.Tensor, v_sf: torch.Tensor,
     q_scale, k_scale, v_scale,
     cu_seqlens_q, cu_seqlens_k,
-    seqused_k: Optional[Sequence[int]] = None,
+    seqused_k=None,
+    max_seqlen_q: Optional[int] = None,
+    max_seqlen_k: Optional[int] = None,
     softmax_scale: Optional[float] = None,
     causal: bool = False,
     window_size: Tuple[Optional[int], Optional[int]] = (None, None),
     learnable_sink: Optional[torch.Tensor] = None,
+    softcap: float = 0.0,
     return_lse: bool = False,
 ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
-    """NVFP4 attention over a packed batch; see the module docstring for the layouts.
+    """NVFP4 attention over a packed batch in one launch; see the module docstring for the layouts.
 
-    ``seqused_k[i]`` (optional) is the number of valid keys of sequence i when its slot
-    ``cu_seqlens_k[i+1] - cu_seqlens_k[i]`` is padded; it must be a multiple of 32 too (the key
-    granule of the kernel), and causal alignment is then taken against the valid length.
+    ``seqused_k[i]`` (optional, any value up to the slot) is the number of valid keys of sequence i
+    when its slot ``cu_seqlens_k[i+1] - cu_seqlens_k[i]`` is padded; causal alignment is then taken
+    against the valid length.  A sequence without keys gives zero rows and LSE = -inf (LSE = sink
+    with a learnable sink), as the dense call does.
     """
+    q, k, v = _as_u8(q, "q"), _as_u8(k, "k"), _as_u8(v, "v")
+    q_sf, k_sf, v_sf = _as_u8(q_sf, "q_sf"), _as_u8(k_sf, "k_sf"), _as_u8(v_sf, "v_sf")
     assert q.dim() == 3 and k.dim() == 3 and v.dim() == 3, "packed operands are 3-D"
+    # offsets that arrive as host sequences are checked here, before any launch; device tensors are
+    # taken as they are (reading them back would synchronise)
+    for name, cu, total in (("cu_seqlens_q", cu_seqlens_q, q.shape[0]), ("cu_seqlens_k", cu_seqlens_k, k.shape[0])):
+        if not isinstance(cu, torch.Tensor):
+            c = [int(x_) for x_ in cu]
+            assert len(c) >= 2 and c[0] == 0 and all(b_ >= a_ for a_, b_ in zip(c, c[1:])), \
+                f"{name} must be non-decreasing and start at 0"
+            assert c[-1] == total, f"{name} does not cover the packed tensor"
+            if name == "cu_seqlens_k" and any(x_ % 32 for x_ in c[:-1]):
+                raise NotImplementedError("key-sequence starts must be multiples of 32 (16-key scale blocks, "
+                                          "16-byte rows of V); pad each sequence's keys")
+    if not isinstance(cu_seqlens_q, torch.Tensor) and not isinstance(cu_seqlens_k, torch.Tensor):
+        assert len(list(cu_seqlens_q)) == len(list(cu_seqlens_k)), \
+            "cu_seqlens_q and cu_seqlens_k describe different batch sizes"
+    assert q.is_cuda and k.is_cuda and v.is_cuda, "inputs must be on CUDA"
+    q, k, v = (t if t.stride(-1) == 1 else t.contiguous() for t in (q, k, v))
+    q_sf, k_sf, v_sf = (t.contiguous() for t in (q_sf, k_sf, v_sf))
+    device = q.device
     total_q, Hq, Dh = q.shape
-    total_k, Hkv, _ = k.shape
-    Dv = v.shape[1]
-    cq, ck = _host_offsets(cu_seqlens_q, "cu_seqlens_q"), _host_offsets(cu_seqlens_k, "cu_seqlens_k")
-    assert len(cq) == len(ck), "cu_seqlens_q and cu_seqlens_k describe different batch sizes"
-    assert cq[-1] == total_q and ck[-1] == total_k, "cu_seqlens do not cover the packed tensors"
-    if any(x % 32 for x in ck):
-        raise NotImplementedError("key-sequence boundaries must be multiples of 32 (16-key scale blocks, "
-                                  "16-byte rows of V); pad each sequence's keys")
-    out = torch.empty(total_q, Hq, Dv, dtype=torch.bfloat16, device=q.device)
-    lse = torch.empty(Hq, total_q, dtype=torch.float32, device=q.device) if return_lse else None
-    for i in range(len(cq) - 1):
-        q0, q1, k0, k1 = cq[i], cq[i + 1], ck[i], ck[i + 1]
-        if q1 == q0:
-            continue
-        sk = k1 - k0 if seqused_k is None else int(seqused_k[i])
-        assert 0 <= sk <= k1 - k0
-        if sk == 0:
-            out[q0:q1].zero_()
-            if lse is not None:
-                lse[:, q0:q1] = float("-inf")
-            continue
-        if sk % 32:
-            raise NotImplementedError("seqused_k must be a multiple of 32")
-        o_i, l_i = flash_attn_fp4_func(
-            q[q0:q1].unsqueeze(0), k[k0:k0 + sk].unsqueeze(0), v[:, :, k0 // 2:(k0 + sk) // 2].unsqueeze(0),
-            q_sf[q0:q1].unsqueeze(0), k_sf[k0:k0 + sk].unsqueeze(0),
-            v_sf[:, :, k0 // 16:(k0 + sk) // 16].unsqueeze(0),
-            q_scale, k_scale, v_scale, softmax_scale=softmax_scale, causal=causal, return_lse=return_lse,
-            out=out[q0:q1].unsqueeze(0), window_size=window_size, learnable_sink=learnable_sink)
-        if lse is not None:
-            lse[:, q0:q1] = l_i[0]
+    total_k, Hkv, Dhk = k.shape
+    Hv, Dv, Tkh = v.shape
+    D = 2 * Dh
+    total_kp = (total_k + 31) // 32 * 32
+    assert Dhk == Dh and Hv == Hkv and Hq % Hkv == 0, "head counts / head dims of q, k, v do not fit"
+    assert Tkh * 2 == total_kp, f"v must be (Hkv, Dv, total_kp/2) with total_kp = {total_kp}, got {tuple(v.shape)}"
+    assert q_sf.shape == (total_q, Hq, D // 16) and k_sf.shape == (total_k, Hkv, D // 16) and \
+        v_sf.shape == (Hkv, Dv, total_kp // 16), "scale factors must be the packed linear layouts"
+    if not ((D == Dv and D in (64, 128)) or (D == 192 and Dv == 128)):
+        raise NotImplementedError(f"head dims (D={D}, Dv={Dv}) not built")
+    cu_q = _device_i32(cu_seqlens_q, "cu_seqlens_q", device)
+    cu_k = _device_i32(cu_seqlens_k, "cu_seqlens_k", device)
+    assert cu_q.numel() == cu_k.numel() and cu_q.numel() >= 2, "cu_seqlens_q / cu_seqlens_k describe different batches"
+    num_seqs = cu_q.numel() - 1
+    used = None
+    if seqused_k is not None:
+        used = _device_i32(seqused_k, "seqused_k", device)
+        assert used.numel() == num_seqs
+    if max_seqlen_q is None or max_seqlen_k is None:
+        # one synchronising read; pass both to stay asynchronous, as the reference's callers do
+        max_seqlen_q = int((cu_q[1:] - cu_q[:-1]).max())
+        max_seqlen_k = int((cu_k[1:] - cu_k[:-1]).max())
+    max_seqlen_q = min(max(1, int(max_seqlen_q)), total_q)
+    max_seqlen_k = min(max(1, int(max_seqlen_k)), total_k)
+    if softmax_scale is None:
+        softmax_scale = 1.0 / math.sqrt(D)
+    causal, win_left, win_right = resolve_window(causal, window_size)
+
+    # per-sequence tiled scale factors, padded to the longest sequence (a conversion kernel each)
+    q_t = _tiled_packed(q_sf, cu_q, num_seqs, Hq, max_seqlen_q, D // 16, D // 16, Hq * (D // 16), 1, True)
+    k_t = _tiled_packed(k_sf, cu_k, num_seqs, Hkv, max_seqlen_k, D // 16, D // 16, Hkv * (D // 16), 1, True)
+    v_t = _tiled_packed(v_sf, cu_k, num_seqs, Hkv, Dv, (max_seqlen_k + 15) // 16, Dv * (total_kp // 16),
+                        total_kp // 16, 2, False)
+
+    out = torch.empty(total_q, Hq, Dv, dtype=torch.bfloat16, device=device)
+    lse = torch.empty(Hq, total_q, dtype=torch.float32, device=device) if return_lse else None
+
+    p = _lib.Params()
+    p.struct_size = ctypes.sizeof(_lib.Params)
+    p.variant = 0
+    p.q, p.k, p.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
+    p.q_sf, p.k_sf, p.v_sf = q_t.data_ptr(), k_t.data_ptr(), v_t.data_ptr()
+    p.out = out.data_ptr()
+    p.lse = lse.data_ptr() if lse is not None else None
+    p.status = DeviceStatus.word(device).data_ptr()
+    p.q_stride_s, p.q_stride_h, p.q_stride_b = q.stride(0), q.stride(1), q.stride(0) * max(1, total_q)
+    p.k_stride_s, p.k_stride_h, p.k_stride_b = k.stride(0), k.stride(1), k.stride(0) * max(1, total_k)
+    p.v_stride_h, p.v_stride_d, p.v_stride_b = v.stride(0), v.stride(1), v.stride(0) * Hkv
+    p.o_stride_s, p.o_stride_h, p.o_stride_b = out.stride(0), out.stride(1), out.stride(0) * max(1, total_q)
+    p.B, p.Sq, p.Sk, p.Hq, p.Hkv, p.D, p.Dv = num_seqs, max_seqlen_q, max_seqlen_k, Hq, Hkv, D, Dv
+    p.causal = 1 if causal else 0
+    p.q_scale, p.k_scale, p.v_scale = _scalar(q_scale, "q_scale"), _scalar(k_scale, "k_scale"), _scalar(v_scale, "v_scale")
+    p.softmax_scale = float(softmax_scale)
+    p.wait_budget_ns = 0
+
+    x = _lib.Varlen()
+    x.struct_size = ctypes.sizeof(_lib.Varlen)
+    x.num_seqs = num_seqs
+    x.cu_seqlens_q, x.cu_seqlens_k = cu_q.data_ptr(), cu_k.data_ptr()
+    x.seqused_k = used.data_ptr() if used is not None else None
+    x.total_q, x.total_k = total_q, total_k
+    x.max_seqlen_q, x.max_seqlen_k = max_seqlen_q, max_seqlen_k
+    x.window_left = -1 if win_left is None else int(win_left)
+    x.window_right = -1 if win_right is None else int(win_right)
+    sink = None
+    if learnable_sink is not None:
+        assert learnable_sink.shape == (Hq,), "learnable_sink must have one entry per query head"
+        sink = learnable_sink.to(device=device, dtype=torch.float32).contiguous()
+    x.sink = sink.data_ptr() if sink is not None else None
+    x.softcap = float(softcap or 0.0)
+    x.reserved = 0
+    with torch.cuda.device(device):
+        stream = torch.cuda.current_stream(device).cuda_stream
+        rc = _lib.lib().fa4_nvfp4_fwd_varlen(ctypes.byref(p), ctypes.byref(x), stream)
+    _lib.check(rc, "fa4_nvfp4_fwd_varlen")
     return out, lse

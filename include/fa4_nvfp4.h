@@ -23,8 +23,10 @@
  * Operand formats
  *   q   (B, Sq, Hq,  D/2)  bytes, two e2m1 values per byte, low nibble = even index
  *   k   (B, Sk, Hkv, D/2)  bytes
- *   v   (B, Hkv, Dv, Sk/2) bytes: V is stored key-contiguous ("V transposed")
- *                           because 4-bit tensor-core operands must be K-major
+ *   v   (B, Hkv, Dv, Skp/2) bytes: V is stored key-contiguous ("V transposed")
+ *                           because 4-bit tensor-core operands must be K-major; its key axis
+ *                           is padded to Skp = Sk rounded up to a multiple of 32, the padding
+ *                           holds zero values and zero scales (Sk itself is free)
  *   *_sf  e4m3 (unsigned use: scales are >= 0) scale of each block of 16
  *         consecutive elements (along D for q and k, along the key axis for v),
  *         in the 128x4 TILED layout described at fa4_nvfp4_sf_linear_to_tiled
@@ -101,7 +103,7 @@ typedef struct fa4_nvfp4_params {
   const void* v;
   const void* q_sf;       /* e4m3, tiled: (B, Hq,  ceil(Sq/128), D/64,  512) bytes */
   const void* k_sf;       /* e4m3, tiled: (B, Hkv, ceil(Sk/128), D/64,  512) bytes */
-  const void* v_sf;       /* e4m3, tiled: (B, Hkv, ceil(Dv/128), 2*ceil(Sk/128), 512) bytes */
+  const void* v_sf;       /* e4m3, tiled: (B, Hkv, ceil(Dv/128), 2*ceil(Sk/128), 512) bytes (zero past Sk) */
   void* out;              /* bf16 (B, Sq, Hq, Dv) */
   float* lse;             /* fp32 (B, Hq, Sq) or NULL */
   uint32_t* status;       /* one device word, zeroed by the caller; NULL = not reported */
@@ -124,7 +126,8 @@ typedef struct fa4_nvfp4_params {
  * (flash_attn/cute/interface.py:785-803).  Asynchronous on `cuda_stream`
  * (a cudaStream_t; NULL = legacy default stream), no host synchronisation.
  * Shapes built: (D, Dv) = (128, 128), (64, 64) or (192, 128) (the reference's table is
- * flash_attn/cute/interface.py:84-99; fa4_nvfp4_query lists D), any Sq, Sk a multiple of 32,
+ * flash_attn/cute/interface.py:84-99; fa4_nvfp4_query lists D), any Sq, any Sk (the reference's
+ * ragged shapes, tests/cute/test_flash_attn.py:91-119; V's key axis padded as above),
  * Hq a multiple of Hkv; everything else returns -FA4_E_SHAPE.  (192, 128) runs on the 64-key
  * kernel only (no split-KV, no decode variant); FA4_VARIANT_SERIAL (the bring-up kernel)
  * exists for D = 128 only.
@@ -190,6 +193,55 @@ typedef struct fa4_nvfp4_ext {
   int32_t reserved2;        /* 0 */
 } fa4_nvfp4_ext;
 int fa4_nvfp4_fwd_ex(const fa4_nvfp4_params* p, const fa4_nvfp4_ext* x, void* cuda_stream);
+
+/*
+ * Packed variable-length batches in ONE launch: the reference's flash_attn_varlen_func
+ * (flash_attn/cute/interface.py:1795-1840; its persistent varlen scheduler is
+ * flash_attn/cute/tile_scheduler.py:755-1087).  q, k, v, out of `p` have no batch dimension:
+ *   q (total_q, Hq, D/2), k (total_k, Hkv, D/2), v (Hkv, Dv, total_kp/2) with total_kp = total_k
+ *   rounded up to a multiple of 32, out (total_q, Hq, Dv), lse (Hq, total_q);
+ * p->q_stride_s / q_stride_h etc. are the token and head strides (the batch strides must still be
+ * positive multiples of 16 and are not used), p->B / Sq / Sk are ignored.  Sequence b owns query
+ * rows cu_seqlens_q[b] .. cu_seqlens_q[b+1] and keys cu_seqlens_k[b] .. cu_seqlens_k[b+1] (device
+ * arrays of num_seqs + 1 int32; no host read-back anywhere).  Every key-sequence start must be a
+ * multiple of 32 (V's 16-key scale blocks and 16-byte rows); `seqused_k` (optional) gives the
+ * valid keys of each slot.  The tile grid is (sequence, m-block of the LONGEST sequence, head):
+ * pass max_seqlen_q / max_seqlen_k as the reference's call does; tiles past a sequence's end
+ * cost a few instructions.  The tiled scale factors are per sequence, padded to the longest:
+ *   q_sf (num_seqs, Hq, ceil(max_seqlen_q/128), D/64, 512), k_sf (num_seqs, Hkv,
+ *   ceil(max_seqlen_k/128), D/64, 512), v_sf (num_seqs, Hkv, ceil(Dv/128),
+ *   2*ceil(max_seqlen_k/128), 512): fa4_nvfp4_sf_linear_to_tiled_packed builds them from the
+ * packed linear layouts.  Causal and window limits align bottom-right per sequence.  Runs the
+ * 64-key kernel (no split-KV).
+ */
+typedef struct fa4_nvfp4_varlen {
+  uint32_t struct_size;          /* = sizeof(fa4_nvfp4_varlen) */
+  int32_t num_seqs;
+  const int32_t* cu_seqlens_q;   /* device, num_seqs + 1 */
+  const int32_t* cu_seqlens_k;   /* device, num_seqs + 1 */
+  const int32_t* seqused_k;      /* device, num_seqs, or NULL */
+  int32_t total_q, total_k;
+  int32_t max_seqlen_q, max_seqlen_k;
+  int32_t window_left, window_right;   /* -1: unlimited (right: 0 when p->causal) */
+  const float* sink;             /* Hq logits or NULL */
+  float softcap;                 /* 0 = off */
+  uint32_t reserved;             /* 0 */
+} fa4_nvfp4_varlen;
+int fa4_nvfp4_fwd_varlen(const fa4_nvfp4_params* p, const fa4_nvfp4_varlen* v, void* cuda_stream);
+
+/*
+ * Linear -> tiled scale factors of a packed batch (see fa4_nvfp4_varlen): per-sequence tiles,
+ * padded with zeros to max_rows x max_cols.  packed_rows = 1: src is (total, n_inner, cols) with
+ * the packed axis on the rows (q / k scales; stride_row = n_inner * cols, stride_inner = cols);
+ * packed_rows = 0: src is (n_inner, rows, total / 16) with the packed axis on the columns
+ * (v scales; cu_seqlens in keys, stride_inner = rows * row length, stride_row = row length).
+ * No counterpart in the reference (it has no scale factors).
+ */
+int fa4_nvfp4_sf_linear_to_tiled_packed(const void* src, void* dst, const int32_t* cu_seqlens,
+                                        int32_t num_seqs, int32_t n_inner, int32_t max_rows,
+                                        int32_t max_cols, int64_t stride_inner, int64_t stride_row,
+                                        int32_t col_tile_multiple, int32_t packed_rows,
+                                        void* cuda_stream);
 
 /*
  * Scale-factor layout conversion, linear -> tiled.
@@ -309,7 +361,8 @@ int fa4_nvfp4_debug_wait_expiry(uint32_t* status, uint64_t budget_ns, void* cuda
  * factors at all).
  *
  * Same contract as fa4_nvfp4_fwd except that p->q_sf, p->k_sf, p->v_sf are the linear, fully
- * contiguous layouts (B, Sq, Hq, D/16), (B, Sk, Hkv, D/16), (B, Hkv, Dv, Sk/16).  The tiled copies
+ * contiguous layouts (B, Sq, Hq, D/16), (B, Sk, Hkv, D/16), (B, Hkv, Dv, Skp/16), Skp = Sk rounded up
+ * to a multiple of 32.  The tiled copies
  * the kernel reads are staged in a fixed 16 MiB array that is part of the library image on every
  * GPU the library is loaded on (FA4_NVFP4_STATIC_SCRATCH_BYTES), so the call performs no
  * cudaMalloc / cudaFree and needs no workspace argument.  Meant for callers whose device memory

@@ -205,13 +205,35 @@ def attention_oracle_a(q, k, v, causal=False, softmax_scale=None, window=(None, 
 # --------------------------------------------------------------------------------------------
 # attention, oracle B: the kernel's arithmetic model (P re-quantised to NVFP4)
 # --------------------------------------------------------------------------------------------
-def quantize_p_block_model(x: torch.Tensor, m_ref: torch.Tensor):
+# general ue4m3 block scales of the 64-key kernel (csrc/softmax.cuh, block_scales4_e4m3)
+_POW2M1_C1, _POW2M1_C2 = np.float32(5.2904577), np.float32(2.6854515)
+_LOG2_1P8 = torch.tensor([math.log2(1.0 + m / 8.0) for m in range(9)], dtype=torch.float32)
+
+
+def quantize_p_block_model(x: torch.Tensor, m_ref: torch.Tensor, p_scale: str = "pow2"):
     """x: (..., 16 k) scaled scores in log2 units of ONE step of keys, m_ref: (..., 1) reference
     maximum in the same units (finite).  Returns (p_hat, p_sum): the de-quantised P' the tensor
-    core multiplies with V, and the un-rounded row sums of P' (P' = 2^P_SHIFT * 2^(x - m_ref))."""
+    core multiplies with V, and the un-rounded row sums of P' (P' = 2^P_SHIFT * 2^(x - m_ref)).
+    p_scale: "pow2" -- block scale 2^e, e = ceil(log2(block max / 6)); "e4m3" -- the smallest
+    2^e (1 + m/8) >= block max / 6, found the way the kernel finds it (floor, a quadratic for
+    8 (2^fr - 1), round to nearest of that + 0.5)."""
     xb = x.reshape(x.shape[:-1] + (x.shape[-1] // BLOCK, BLOCK))
     bmax = xb.amax(dim=-1, keepdim=True)
     t = bmax - m_ref[..., None] + P_SHIFT
+    if p_scale == "e4m3":
+        t = (t - np.float32(LOG2_6)).to(torch.float32)
+        t = torch.where(torch.isfinite(t), torch.clamp(t, min=float(P_EMIN)), torch.full_like(t, float(P_EMIN)))
+        e = torch.floor(t)
+        fr = t - e
+        g = fr * (fr * _POW2M1_C2 + _POW2M1_C1)
+        m = torch.round(g + np.float32(0.4999995))            # round half to even, like the magic add
+        lm = _LOG2_1P8[m.long()]
+        scale = torch.exp2(e) * (1.0 + m / 8.0)
+        p_scaled = torch.exp2(xb - (m_ref[..., None] - P_SHIFT) - e - lm)
+        codes = e2m1_encode(p_scaled.numpy())
+        p_hat = torch.from_numpy(e2m1_decode(codes)) * scale
+        p_sum = (p_scaled.sum(dim=-1) * scale[..., 0]).sum(dim=-1)
+        return p_hat.reshape(x.shape), p_sum
     e = torch.clamp(torch.ceil(t - LOG2_6), float(P_EMIN), 8.0)
     e = torch.where(torch.isfinite(t), e, torch.full_like(e, float(P_EMIN)))
     p_scaled = torch.exp2(xb - (m_ref[..., None] - P_SHIFT + e))          # in [0, 6]
@@ -223,7 +245,8 @@ def quantize_p_block_model(x: torch.Tensor, m_ref: torch.Tensor):
 
 def attention_oracle_b(qd, kd, vd, sl2: float, v_scale_out: float = 1.0, causal=False,
                        num_splits: int = 1, window=(None, None), sink=None,
-                       step_keys: int = 128, ascending: bool = False, softcap_c1: float = 0.0):
+                       step_keys: int = 128, ascending: bool = False, softcap_c1: float = 0.0,
+                       p_scale: str = "pow2"):
     """Kernel model.  qd (B,Sq,Hq,D), kd (B,Sk,Hkv,D), vd (B,Sk,Hkv,Dv): fp32 values the tensor
     core sees (e2m1 * block scale, WITHOUT the per-tensor scales); sl2 = softmax_scale * q_scale
     * k_scale * log2(e); v_scale_out = v_scale.  Walks the K/V blocks of 128 keys from the last
@@ -240,6 +263,7 @@ def attention_oracle_b(qd, kd, vd, sl2: float, v_scale_out: float = 1.0, causal=
     softcap_c1 > 0 models the soft cap: the raw scores become tanh(raw * softcap_c1) with
     softcap_c1 = softmax_scale * q_scale * k_scale / softcap, and the caller passes
     sl2 = softcap * log2(e): everything after that is unchanged.
+    p_scale selects the rule of the P block scales (see quantize_p_block_model).
     Returns (out fp32 (B,Sq,Hq,Dv) before bf16 rounding, lse (B,Hq,Sq))."""
     assert step_keys in (64, 128) and (step_keys == 128 or num_splits == 1)
     sub = 128 // step_keys
@@ -304,7 +328,7 @@ def attention_oracle_b(qd, kd, vd, sl2: float, v_scale_out: float = 1.0, causal=
                         l_sum = l_sum * f
                         m_ref = m_new
                         msc = torch.where(torch.isfinite(m_ref), m_ref * sl2, torch.zeros(nr))
-                        p_hat, p_sum = quantize_p_block_model(s * sl2, msc[:, None])
+                        p_hat, p_sum = quantize_p_block_model(s * sl2, msc[:, None], p_scale)
                         acc = acc + p_hat @ v_pad[nb * step_keys:(nb + 1) * step_keys]
                         l_sum = l_sum + p_sum
                     if sink is not None and sp == 0:

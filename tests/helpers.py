@@ -38,6 +38,13 @@ def make_qkv(B, Sq, Sk, Hq, Hkv, D, seed, v_std=1.0, outlier_frac=0.0, device="c
     return tuple(t.bfloat16().to(device) for t in (q, k, v))
 
 
+def p_scale_rule_of_the_64_key_kernel() -> str:
+    """The P block-scale rule the loaded library's 64-key kernel was built with (a compile-time
+    choice the library reports: fa4_nvfp4_query(102))."""
+    import flash_attention_b200 as fa
+    return "e4m3" if fa.lib().fa4_nvfp4_query(102) == 1 else "pow2"
+
+
 def kernel_model(D, num_splits=1, window=(None, None), sink=None, variant=0, softcap=0.0, rows=None):
     """Which kernel the library's automatic choice runs, as oracle B keywords: the decode kernel
     for a handful of query rows, the 64-key kernel for every other call that does not split the
@@ -51,7 +58,7 @@ def kernel_model(D, num_splits=1, window=(None, None), sink=None, variant=0, sof
     if variant == 4 or (variant == 0 and decode_ok):
         return {"step_keys": 128, "ascending": True}
     if variant == 3 or (variant == 0 and plain):
-        return {"step_keys": 64, "ascending": True}
+        return {"step_keys": 64, "ascending": True, "p_scale": p_scale_rule_of_the_64_key_kernel()}
     return {"step_keys": 128, "ascending": False}
 
 
@@ -60,6 +67,7 @@ def oracles(Q, K, V, causal, softmax_scale=None, num_splits=1, window=(None, Non
     """Q, K, V: NVFP4Tensor with linear scales.  Returns (out_a, lse_a, out_b, lse_b) on CPU;
     oracle B models the kernel that ``variant`` (0 = automatic) selects for this problem."""
     qd, kd, vd = Q.dequantize().cpu(), K.dequantize().cpu(), V.dequantize().cpu()
+    vd = vd[:, :kd.shape[1]]            # V's key axis carries zero padding to a multiple of 32
     D = qd.shape[-1]
     scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(D)
     oa, la = orc.attention_oracle_a(qd, kd, vd, causal=causal, softmax_scale=scale, window=window, sink=sink,

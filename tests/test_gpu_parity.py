@@ -10,7 +10,7 @@ import torch
 
 import flash_attention_b200 as fa
 from oracle import nvfp4_oracle as orc
-from tests.helpers import assert_parity, make_qkv, oracles
+from tests.helpers import assert_parity, make_qkv, oracles, p_scale_rule_of_the_64_key_kernel
 
 pytestmark = pytest.mark.gpu
 
@@ -107,6 +107,11 @@ CASES = [
     ("ragged_causal_sq_lt_sk", 1, 200, 352, 4, 2, True, 1.0, 0.0),
     ("ragged_causal_sq_gt_sk", 1, 300, 160, 2, 2, True, 1.0, 0.0),
     ("single_query_row", 1, 1, 160, 2, 1, True, 1.0, 0.0),
+    # any Sk, as in the reference (tests/cute/test_flash_attn.py:91-119): keys that do not fill a
+    # 16-key scale block, Sq and Sk odd
+    ("ragged_sk_203_noncausal", 1, 113, 203, 3, 1, False, 1.0, 0.0),
+    ("ragged_sk_799_causal", 1, 800, 799, 2, 2, True, 1.0, 0.0),
+    ("ragged_sk_1_causal", 2, 1, 1, 2, 1, True, 1.0, 0.0),
 ]
 
 
@@ -122,8 +127,8 @@ def test_parity_with_oracle(cuda_device, case, variant):
     assert_parity(out, lse, *oracles(Q, K, V, causal, variant=variant))
 
 
-# (the ragged fixture has Sk = 208, not a multiple of the kernel's 32-key granule: oracle only)
 @pytest.mark.parametrize("name", ["mha_noncausal", "gqa_causal_sq_lt_sk", "mqa_causal_sq_gt_sk",
+                                  "mqa_noncausal_ragged",
                                   "gqa_sliding_window_causal",
                                   "mha_window_both_sides_sq_lt_sk", "gqa_causal_learnable_sink",
                                   "gqa_causal_softcap"])
@@ -134,8 +139,15 @@ def test_golden_fixture_through_the_kernel(cuda_device, name):
     dev = cuda_device
     t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
     window = tuple(None if int(x) < 0 else int(x) for x in z["window"])
-    out, lse = fa.flash_attn_fp4_func(t(z["q_data"]), t(z["k_data"]), t(z["v_data"]), t(z["q_sf"]),
-                                      t(z["k_sf"]), t(z["v_sf"]), float(z["q_scale"]), float(z["k_scale"]),
+    # the fixtures hold V with exactly Sk keys; the call takes its key axis padded with zeros to a
+    # multiple of 32 (the ragged fixture has Sk = 208 -> 224)
+    v_data, v_sf = z["v_data"], z["v_sf"]
+    pad = (-2 * v_data.shape[-1]) % 32
+    if pad:
+        v_data = np.concatenate([v_data, np.zeros(v_data.shape[:-1] + (pad // 2,), np.uint8)], axis=-1)
+        v_sf = np.concatenate([v_sf, np.zeros(v_sf.shape[:-1] + (pad // 16,), np.uint8)], axis=-1)
+    out, lse = fa.flash_attn_fp4_func(t(z["q_data"]), t(z["k_data"]), t(v_data), t(z["q_sf"]),
+                                      t(z["k_sf"]), t(v_sf), float(z["q_scale"]), float(z["k_scale"]),
                                       float(z["v_scale"]), causal=bool(z["causal"]), return_lse=True,
                                       window_size=window,
                                       learnable_sink=torch.from_numpy(z["sink"]) if z["sink"].size else None,
@@ -162,7 +174,7 @@ def test_softmax_scale_and_preallocated_outputs(cuda_device):
     with pytest.raises(AssertionError):
         fa.flash_attn_fp4_func(Q.data, K.data, V.data, Q.sf, K.sf, V.sf, 1.0, 1.0, 1.0,
                                out=torch.empty(1, 128, 2, 64, dtype=torch.bfloat16, device=cuda_device))
-    with pytest.raises(NotImplementedError):   # Sk = 144 is not a multiple of 32
+    with pytest.raises(AssertionError):        # Sk = 144: V must come with its key axis padded to 160
         fa.flash_attn_fp4_func(Q.data, K.data[:, :144], V.data[..., :72].contiguous(), Q.sf, K.sf[:, :144],
                                V.sf[..., :9].contiguous(), 1.0, 1.0, 1.0)
 
@@ -286,7 +298,8 @@ def _check_windows(Ql, Kl, Vl, out, lse, samples, causal, softmax_scale, group):
                     * torch.tensor(Kl.scale, dtype=torch.float32) * torch.tensor(1.4426950408889634, dtype=torch.float32))
         ob, lb = orc.attention_oracle_b((qd / Ql.scale).cpu()[None, :, None], (kd / Kl.scale).cpu()[None, :, None],
                                         (vd / Vl.scale).cpu()[None, :, None], sl2, Vl.scale, causal=causal,
-                                        step_keys=64, ascending=True)
+                                        step_keys=64, ascending=True,
+                                        p_scale=p_scale_rule_of_the_64_key_kernel())
         got_o = out[b, r0:r0 + 128, h][None, :, None]
         got_l = lse[b, h, r0:r0 + 128][None, None]
         assert_parity(got_o, got_l, oa, la, ob, lb)
@@ -738,6 +751,85 @@ def test_varlen_packed_batch_matches_dense_calls(cuda_device):
         Ki = fa.NVFP4Tensor(K.data[:, k0:k1].contiguous(), K.sf[:, k0:k1].contiguous(), K.scale)
         Vi = fa.NVFP4Tensor(V.data[..., k0 // 2:k1 // 2].contiguous(), V.sf[..., k0 // 16:k1 // 16].contiguous(),
                             V.scale, is_v=True)
-        o_d, l_d = fa.flash_attn_func(Qi, Ki, Vi, causal=True, return_lse=True)
+        # (the packed call runs the 64-key kernel for every sequence; the dense call would pick the
+        # decode kernel for the one-token sequence, so the kernel is named here)
+        o_d, l_d = run(Qi, Ki, Vi, True, fa.VARIANT_WS64)
         assert torch.equal(out[q0:q1], o_d[0]) and torch.equal(lse[:, q0:q1], l_d[0])
-        assert_parity(o_d, l_d, *oracles(Qi, Ki, Vi, True))
+        assert_parity(o_d, l_d, *oracles(Qi, Ki, Vi, True, variant=fa.VARIANT_WS64))
+
+
+def test_varlen_one_launch_device_offsets_noncausal_window_and_sink(cuda_device):
+    """Packed batch with odd query lengths, device cu_seqlens and max_seqlen given (nothing is read
+    back): non-causal, a sliding window, and a learnable sink, each bit-identical to the dense
+    call on the single sequences."""
+    Hq, Hkv, D = 4, 2, 128
+    sq, sk = [257, 3, 128, 60], [320, 64, 128, 96]
+    cq = [0] + list(np.cumsum(sq))
+    ck = [0] + list(np.cumsum(sk))
+    g = torch.Generator().manual_seed(32)
+    q = torch.randn(1, cq[-1], Hq, D, generator=g).bfloat16().to(cuda_device)
+    k = torch.randn(1, ck[-1], Hkv, D, generator=g).bfloat16().to(cuda_device)
+    v = torch.randn(1, ck[-1], Hkv, D, generator=g).bfloat16().to(cuda_device)
+    Q, K, V = fa.quantize_qkv(q, k, v)
+    cu_q = torch.tensor(cq, dtype=torch.int32, device=cuda_device)
+    cu_k = torch.tensor(ck, dtype=torch.int32, device=cuda_device)
+    sink = torch.tensor([0.3, -1.0, 2.0, 0.0])
+    for kw in (dict(causal=False), dict(causal=True, window_size=(100, None)), dict(causal=True, learnable_sink=sink)):
+        out, lse = fa.flash_attn_varlen_fp4_func(
+            Q.data[0], K.data[0], V.data[0], Q.sf[0], K.sf[0], V.sf[0], Q.scale, K.scale, V.scale,
+            cu_q, cu_k, max_seqlen_q=max(sq), max_seqlen_k=max(sk), return_lse=True, **kw)
+        torch.cuda.synchronize()
+        fa.check_status(cuda_device)
+        for i in range(len(sq)):
+            q0, q1, k0, k1 = cq[i], cq[i + 1], ck[i], ck[i + 1]
+            Qi = fa.NVFP4Tensor(Q.data[:, q0:q1].contiguous(), Q.sf[:, q0:q1].contiguous(), Q.scale)
+            Ki = fa.NVFP4Tensor(K.data[:, k0:k1].contiguous(), K.sf[:, k0:k1].contiguous(), K.scale)
+            Vi = fa.NVFP4Tensor(V.data[..., k0 // 2:k1 // 2].contiguous(), V.sf[..., k0 // 16:k1 // 16].contiguous(),
+                                V.scale, is_v=True)
+            kw_d = dict(kw)
+            causal_d = kw_d.pop("causal")
+            o_d, l_d = run(Qi, Ki, Vi, causal_d, fa.VARIANT_WS64, **kw_d)     # the kernel the packed call runs
+            assert torch.equal(out[q0:q1], o_d[0]) and torch.equal(lse[:, q0:q1], l_d[0]), (kw, i)
+
+
+def test_varlen_many_short_sequences_cost_about_a_dense_call(cuda_device):
+    """512 sequences of 128 tokens in one launch: bit-identical to, and within 1.5x of, the dense
+    call on the same tokens shaped (512, 128) (measured 1.36x: the packed call runs the kernel's
+    KV-cache flavour, which reads every sequence's bounds from the device; 512 per-sequence
+    launches took more than ten times as long)."""
+    Hq, Hkv, D, n, L = 8, 2, 128, 512, 128
+    g = torch.Generator(device=cuda_device).manual_seed(5)
+    q = torch.randn(n, L, Hq, D, generator=g, device=cuda_device, dtype=torch.bfloat16)
+    k = torch.randn(n, L, Hkv, D, generator=g, device=cuda_device, dtype=torch.bfloat16)
+    v = torch.randn(n, L, Hkv, D, generator=g, device=cuda_device, dtype=torch.bfloat16)
+    Qd, Kd, Vd = fa.quantize_qkv_fused(q, k, v)
+    # the same tokens packed: (n * L, H, D), V key-contiguous over the packed keys
+    Qp, Kp, Vp = fa.quantize_qkv_fused(q.reshape(1, n * L, Hq, D), k.reshape(1, n * L, Hkv, D),
+                                       v.reshape(1, n * L, Hkv, D))
+    cu = torch.arange(0, (n + 1) * L, L, dtype=torch.int32, device=cuda_device)
+
+    def dense():      # linear scale factors, converted per call like the packed call's
+        return fa.flash_attn_fp4_func(Qd.data, Kd.data, Vd.data, Qd.sf, Kd.sf, Vd.sf, Qd.scale, Kd.scale, Vd.scale,
+                                      causal=True, return_lse=True)
+
+    def packed():
+        return fa.flash_attn_varlen_fp4_func(Qp.data[0], Kp.data[0], Vp.data[0], Qp.sf[0], Kp.sf[0], Vp.sf[0],
+                                             Qp.scale, Kp.scale, Vp.scale, cu, cu, max_seqlen_q=L, max_seqlen_k=L,
+                                             causal=True, return_lse=True)
+    o_d, l_d = dense()
+    o_p, l_p = packed()
+    torch.cuda.synchronize()
+    fa.check_status(cuda_device)
+    assert torch.equal(o_p.reshape(n, L, Hq, D), o_d)
+    assert torch.equal(l_p.reshape(Hq, n, L).permute(1, 0, 2), l_d)
+
+    def best_ms(fn):
+        ts = []
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); fn(); e1.record(); e1.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return min(ts)
+    t_d, t_p = best_ms(dense), best_ms(packed)
+    assert t_p <= 1.5 * t_d, (t_p, t_d)
+

@@ -22,6 +22,10 @@ def _oracle_qk(x):
 
 
 def _oracle_v(v):
+    # V is quantised key-contiguous with its key axis padded with zeros to a multiple of 32
+    pad = (-v.shape[1]) % 32
+    if pad:
+        v = torch.cat([v, v.new_zeros(v.shape[0], pad, v.shape[2], v.shape[3])], dim=1)
     return orc.quantize_nvfp4(v.float().permute(0, 2, 3, 1).contiguous().cpu().numpy())
 
 

@@ -82,7 +82,7 @@ def _good_params():
     (lambda p: setattr(p, "out", None), 1),
     (lambda p: (setattr(p, "Hq", 3), setattr(p, "Hkv", 2)), 2),   # Hq not a multiple of Hkv
     (lambda p: setattr(p, "D", 96), 2),
-    (lambda p: setattr(p, "Sk", 144), 2),       # Sk must be a multiple of 32
+    (lambda p: setattr(p, "v_stride_d", 72), 3),   # V rows (the padded key axis) must be 16-byte multiples
     (lambda p: setattr(p, "Sk", 0), 2),
     (lambda p: setattr(p, "softmax_scale", 0.0), 2),
     (lambda p: setattr(p, "k", 0x1008), 4),
@@ -136,8 +136,9 @@ def test_product_quantiser_is_bit_identical_to_oracle():
     assert np.array_equal(orc.dequantize_nvfp4(a), fa.dequantize_lastdim(d, s, g).numpy())
     q, k, v = (torch.from_numpy(x), torch.from_numpy(x[:, :, :1]), torch.from_numpy(x[:, :, :1] * 0.5))
     Q, K, V = fa.quantize_qkv(q, k, v)
-    assert V.data.shape == (2, 1, 128, 24) and V.sf.shape == (2, 1, 128, 3) and V.is_v
-    assert V.dequantize().shape == (2, 48, 1, 128)
+    # V's key axis is padded with zeros to a multiple of 32 (48 -> 64 keys)
+    assert V.data.shape == (2, 1, 128, 32) and V.sf.shape == (2, 1, 128, 4) and V.is_v
+    assert V.dequantize().shape == (2, 64, 1, 128) and not V.dequantize()[:, 48:].any()
 
 
 def test_shard_plan_covers_every_unit_once():
@@ -218,11 +219,13 @@ def test_decode_split_choice_and_oracle_model_selection():
         assert I.choose_decode_splits(1, 8, 1 << 20, None) == 55
     assert kernel_model(128, rows=4) == {"step_keys": 128, "ascending": True}          # decode kernel
     assert kernel_model(128, rows=4, num_splits=5) == {"step_keys": 128, "ascending": True}
-    assert kernel_model(128, rows=256) == {"step_keys": 64, "ascending": True}         # 64-key prefill kernel
-    assert kernel_model(64, rows=4) == {"step_keys": 64, "ascending": True}            # head dim 64: no decode kernel
-    assert kernel_model(128, rows=4, softcap=2.0) == {"step_keys": 64, "ascending": True}   # general 64-key kernel
-    assert kernel_model(128, rows=256, window=(64, None)) == {"step_keys": 64, "ascending": True}
-    assert kernel_model(128, rows=256, sink=[0.0]) == {"step_keys": 64, "ascending": True}
+    def is64(m):       # the 64-key kernel's model (its P block-scale rule is whatever the library was built with)
+        return (m["step_keys"], m["ascending"]) == (64, True) and m["p_scale"] in ("pow2", "e4m3")
+    assert is64(kernel_model(128, rows=256))                           # 64-key prefill kernel
+    assert is64(kernel_model(64, rows=4))                              # head dim 64: no decode kernel
+    assert is64(kernel_model(128, rows=4, softcap=2.0))                # general 64-key kernel
+    assert is64(kernel_model(128, rows=256, window=(64, None)))
+    assert is64(kernel_model(128, rows=256, sink=[0.0]))
     assert kernel_model(128, rows=256, num_splits=2) == {"step_keys": 128, "ascending": False}
     assert kernel_model(128, rows=4, variant=2) == {"step_keys": 128, "ascending": False}
 
@@ -269,9 +272,9 @@ def test_oracle_window_masks_match_reference_formula():
 
 def test_varlen_surface_rejects_bad_offsets_before_any_launch():
     z = lambda *s: torch.zeros(*s, dtype=torch.uint8)
-    args = (z(48, 2, 64), z(80, 1, 64), z(1, 128, 40), z(48, 2, 8), z(80, 1, 8), z(1, 128, 5), 1.0, 1.0, 1.0)
-    with pytest.raises(NotImplementedError):          # key boundary 48 is not a multiple of 32
-        fa.flash_attn_varlen_fp4_func(*args, [0, 16, 48], [0, 48, 80])
+    args = (z(48, 2, 64), z(80, 1, 64), z(1, 128, 48), z(48, 2, 8), z(80, 1, 8), z(1, 128, 6), 1.0, 1.0, 1.0)
+    with pytest.raises(NotImplementedError):          # a key sequence that starts at 48: not a multiple of 32
+        fa.flash_attn_varlen_fp4_func(*args, [0, 16, 32, 48], [0, 32, 48, 80])
     with pytest.raises(AssertionError):               # offsets do not cover the packed tensor
         fa.flash_attn_varlen_fp4_func(*args, [0, 16, 40], [0, 32, 80])
     with pytest.raises(AssertionError):               # different batch sizes

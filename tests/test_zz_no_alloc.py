@@ -104,7 +104,7 @@ def _dummy_params():
     ("q", 0, -1),                 # NULL operand
     ("out", 0x1008, -4),          # misaligned output
     ("D", 96, -2),                # head dim that is not built
-    ("Sk", 48, -2),               # keys not a multiple of 32
+    ("v_stride_d", 24, -3),       # V rows not padded to whole 32-key groups
     ("Hkv", 3, -2),               # Hq not a multiple of Hkv
     ("k_stride_s", 8, -3),        # 8-byte stride
     ("softmax_scale", 0.0, -2),
