@@ -3,7 +3,6 @@
 #include "../../include/fa4_nvfp4.h"
 
 #include "attn_common.cuh"
-#include "attn_serial.cuh"
 #include "attn_ws.cuh"
 #include "attn_ws64.cuh"
 #include "attn_decode.cuh"
@@ -273,8 +272,7 @@ int validate_fwd(const fa4_nvfp4_params* p, int num_splits, const void* workspac
   const bool takes64 = num_splits == 1;   // what the 64-key kernel can run
   int variant = p->variant;
   if (variant == FA4_VARIANT_AUTO) variant = takes64 ? FA4_VARIANT_WS64 : FA4_VARIANT_WS;
-  if (variant != FA4_VARIANT_SERIAL && variant != FA4_VARIANT_WS && variant != FA4_VARIANT_WS64 &&
-      variant != FA4_VARIANT_DECODE)
+  if (variant != FA4_VARIANT_WS && variant != FA4_VARIANT_WS64 && variant != FA4_VARIANT_DECODE)
     return -FA4_E_VARIANT;
   const bool decode = variant == FA4_VARIANT_DECODE;
   if (decode) {
@@ -287,12 +285,9 @@ int validate_fwd(const fa4_nvfp4_params* p, int num_splits, const void* workspac
   }
   if (variant == FA4_VARIANT_WS64 && !takes64) return -FA4_E_SHAPE;
   if (d192 && variant != FA4_VARIANT_WS64) return -FA4_E_SHAPE;
-  if (variant == FA4_VARIANT_SERIAL && p->D != 128) return -FA4_E_SHAPE;  // bring-up kernel: 128 only
   // window limits: `causal` is the right limit 0; an explicit right limit overrides it
   if (p->causal && win_right < 0) win_right = 0;
   const bool local = win_left >= 0 || win_right > 0;
-  if ((local || sink != nullptr || softcap > 0.f || cached || num_splits > 1) && variant == FA4_VARIANT_SERIAL)
-    return -FA4_E_VARIANT;
   if (num_splits > 1) {
     if (workspace == nullptr) return -FA4_E_NULL;
     if (!aligned16(workspace)) return -FA4_E_ALIGN;
@@ -430,9 +425,6 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
                                  : (dec_rows <= 8 ? launch_dec(attn_decode_kernel<8>)
                                                   : launch_dec(attn_decode_kernel<16>));
     if (rc != 0) return rc;
-  } else if (variant == FA4_VARIANT_SERIAL) {
-    if (int e = ensure_smem(attn_fwd_serial_kernel, serial::kSmemRequest)) return e;
-    attn_fwd_serial_kernel<<<tiles, 128, serial::kSmemRequest, stream>>>(tm_q, tm_k, tm_v, kp);
   } else {
     // persistent: one CTA per SM walks the tile list
     int dev = 0, sms = 0;
@@ -625,8 +617,8 @@ extern "C" int fa4_nvfp4_debug_qk_tile(const void* q, const void* k, const void*
   if (!encode_u8_4d(&tm_q, q, d, s, b, CU_TENSOR_MAP_SWIZZLE_64B) ||
       !encode_u8_4d(&tm_k, k, d, s, b, CU_TENSOR_MAP_SWIZZLE_64B))
     return -FA4_E_TENSORMAP;
-  if (int e = ensure_smem(qk_tile_probe_kernel, serial::kSmemRequest)) return e;
-  qk_tile_probe_kernel<<<1, 128, serial::kSmemRequest, static_cast<cudaStream_t>(cuda_stream)>>>(
+  if (int e = ensure_smem(qk_tile_probe_kernel, kProbeSmemRequest)) return e;
+  qk_tile_probe_kernel<<<1, 128, kProbeSmemRequest, static_cast<cudaStream_t>(cuda_stream)>>>(
       tm_q, tm_k, static_cast<const uint8_t*>(q), static_cast<const uint8_t*>(k),
       static_cast<const uint8_t*>(q_sf), static_cast<const uint8_t*>(k_sf), s_out, mode, status,
       kDefaultBudgetNs);
@@ -639,8 +631,8 @@ extern "C" int fa4_nvfp4_debug_mma_rate(int32_t iters, int32_t num_ctas, uint64_
   if (!clocks_out) return -FA4_E_NULL;
   if (iters < 4 || iters % 4 != 0 || iters > (1 << 22) || num_ctas < 1 || num_ctas > 1024)
     return -FA4_E_SHAPE;
-  if (int e = ensure_smem(mma_rate_kernel, serial::kSmemRequest)) return e;
-  mma_rate_kernel<<<num_ctas, 128, serial::kSmemRequest, static_cast<cudaStream_t>(cuda_stream)>>>(
+  if (int e = ensure_smem(mma_rate_kernel, kProbeSmemRequest)) return e;
+  mma_rate_kernel<<<num_ctas, 128, kProbeSmemRequest, static_cast<cudaStream_t>(cuda_stream)>>>(
       iters, reinterpret_cast<unsigned long long*>(clocks_out), status, kDefaultBudgetNs);
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : (int)e;

@@ -9,6 +9,23 @@ namespace fa4 {
 constexpr int kBlockM = 128;  // query rows per CTA tile (= tensor-memory lanes)
 constexpr int kBlockN = 128;  // keys per K/V block
 
+// tensor-memory column map (512 columns allocated) shared by the 128-key kernel, the decode
+// kernel and the probes; the 64-key kernel has its own map
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kTmS0 = 0, kTmS1 = 128, kTmO = 256;
+constexpr uint32_t kTmSFQ = 384;  // 8 columns: 2 MMA K-steps x 4
+constexpr uint32_t kTmSFK = 392;  // 2 buffers x 8
+constexpr uint32_t kTmSFV = 408;  // 2 buffers x 8
+constexpr uint32_t kTmSFP = 424;  // 2 buffers x 8
+
+constexpr uint32_t kTileBytes = 128 * 64;  // one 128-row x 128-element e2m1 tile
+constexpr uint32_t kSfBytes = 1024;        // its scale factors: 2 chunks of 512
+
+// Shared memory the single-tile probes request: padded so that only one CTA fits per SM (every
+// CTA allocates all 512 tensor-memory columns, and a second resident CTA would block inside
+// tcgen05.alloc).
+constexpr uint32_t kProbeSmemRequest = 120 * 1024;
+
 struct KernelParams {
   const uint8_t* q_sf;  // tiled scale factors, see fa4_nvfp4.h
   const uint8_t* k_sf;

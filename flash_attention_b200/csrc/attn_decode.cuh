@@ -25,7 +25,6 @@
 // Every wait is bounded, like everywhere else.
 #pragma once
 #include "attn_common.cuh"
-#include "attn_serial.cuh"  // tile byte sizes
 #include "softmax.cuh"
 
 namespace fa4 {

@@ -68,7 +68,7 @@
 //   drain[2]             issuers                 tensor-core work drained on the abort path
 #pragma once
 #include "attn_common.cuh"
-#include "attn_serial.cuh"  // tensor-memory map, tile byte sizes
+#include "attn_common.cuh"
 
 namespace fa4 {
 

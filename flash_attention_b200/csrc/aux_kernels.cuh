@@ -1,7 +1,7 @@
 // Small kernels around the attention forward: scale-factor layout conversion, the
 // hardware-contract probe (one Q K^T tile) and the bounded-wait self test.
 #pragma once
-#include "attn_serial.cuh"
+#include "attn_common.cuh"
 
 namespace fa4 {
 

@@ -26,7 +26,7 @@ import torch
 from . import _lib
 from .quant import NVFP4Tensor, sf_to_tiled
 
-VARIANT_AUTO, VARIANT_SERIAL, VARIANT_WS, VARIANT_WS64, VARIANT_DECODE = 0, 1, 2, 3, 4
+VARIANT_AUTO, VARIANT_WS, VARIANT_WS64, VARIANT_DECODE = 0, 2, 3, 4
 
 
 def _validate_tensor(t, name, expected_shape, expected_dtype, expected_device):
@@ -179,8 +179,6 @@ def flash_attn_fp4_func(
     if not ((D == Dv and D in (64, 128)) or (D == 192 and Dv == 128)):
         raise NotImplementedError(f"head dims (D={D}, Dv={Dv}) not built; supported: (128, 128), (64, 64) "
                                   "and (192, 128)")
-    if D != 128 and variant == VARIANT_SERIAL:
-        raise NotImplementedError("the serial bring-up variant is built for head dim 128 only")
     device = q.device
     if softmax_scale is None:
         softmax_scale = 1.0 / math.sqrt(D)

@@ -80,7 +80,7 @@ enum {
 /* kernel variants */
 enum {
   FA4_VARIANT_AUTO = 0,   /* WS64 unless the call splits the keys (then WS) */
-  FA4_VARIANT_SERIAL = 1, /* one warpgroup does every step in turn (bring-up / cross-check) */
+  /* 1: retired (a one-warpgroup bring-up kernel); -FA4_E_VARIANT */
   FA4_VARIANT_WS = 2,     /* warp-specialised pipeline, steps of 128 keys from the last visible
                              block down; every feature, D = 128 and 64 */
   FA4_VARIANT_WS64 = 3,   /* warp-specialised pipeline, steps of 64 keys upwards, four score
@@ -129,8 +129,7 @@ typedef struct fa4_nvfp4_params {
  * flash_attn/cute/interface.py:84-99; fa4_nvfp4_query lists D), any Sq, any Sk (the reference's
  * ragged shapes, tests/cute/test_flash_attn.py:91-119; V's key axis padded as above),
  * Hq a multiple of Hkv; everything else returns -FA4_E_SHAPE.  (192, 128) runs on the 64-key
- * kernel only (no split-KV, no decode variant); FA4_VARIANT_SERIAL (the bring-up kernel)
- * exists for D = 128 only.
+ * kernel only (no split-KV, no decode variant).
  */
 int fa4_nvfp4_fwd(const fa4_nvfp4_params* p, void* cuda_stream);
 
