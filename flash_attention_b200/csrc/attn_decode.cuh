@@ -20,8 +20,9 @@
 // visited in ascending order; it writes a normalised fp32 partial O and a partial LSE for
 // combine_splits_kernel, like the split-KV path of attn_ws.cuh.  Grid = (splits, Hkv, B).
 //   warps 0-3  softmax / correction / epilogue (thread = key lane, later = dv lane)
-//   warp 4     TMA producer (K / V rings of four tiles, through the page table if there is one)
+//   warp 4     TMA producer of K (ring of three tiles, through the page table if there is one)
 //   warp 5     MMA issuer (owns tensor memory)
+//   warp 6     TMA producer of V (its own ring, independent of K's)
 // Every wait is bounded, like everywhere else.
 #pragma once
 #include "attn_common.cuh"
@@ -30,7 +31,7 @@
 namespace fa4 {
 namespace dec {
 
-constexpr int kThreads = 192;
+constexpr int kThreads = 224;
 // Three of everything: 65 KB of shared memory and 128 tensor-memory columns per CTA, so that THREE
 // CTAs share an SM -- the softmax chain of a block is latency-bound and one CTA has one in flight.
 constexpr int kStages = 3;   // K and V tiles in flight
@@ -104,6 +105,58 @@ __device__ __forceinline__ uint32_t pack2_e2m1(float lo, float hi) {
   return b;
 }
 
+// kN columns (4, 8 or 16) of this thread's tensor-memory lane.
+template <int kN>
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t* r) {
+  if constexpr (kN == 4) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(taddr)
+                 : "memory");
+  } else if constexpr (kN == 8) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
+  } else {
+    tmem_ld16(taddr, r);
+  }
+}
+template <int kN>
+__device__ __forceinline__ void tmem_st_cols(uint32_t taddr, const uint32_t* r) {
+  if constexpr (kN == 4) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%4], {%0, %1, %2, %3};"
+                 ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(taddr)
+                 : "memory");
+  } else if constexpr (kN == 8) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%8], {%0, %1, %2, %3, %4, %5, %6, %7};"
+                 ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                 "r"(taddr)
+                 : "memory");
+  } else {
+    tmem_st16(taddr, r);
+  }
+}
+
+// T x T transpose inside every group of T neighbouring lanes (T = 4, 8, 16): before, lane i of a
+// group holds x[0..T) = its own column; after, x[j] is what lane j of the group held in x[i].
+// log2(T) butterfly rounds of T / 2 shuffles.
+template <int T>
+__device__ __forceinline__ void lane_group_transpose(float (&x)[T], int lane) {
+#pragma unroll
+  for (int bit = 1; bit < T; bit <<= 1) {
+    const bool up = (lane & bit) != 0;
+#pragma unroll
+    for (int j = 0; j < T; ++j) {
+      if ((j & bit) == 0) {
+        const float send = up ? x[j] : x[j | bit];
+        const float recv = __shfl_xor_sync(0xffffffffu, send, bit);
+        if (up) x[j] = recv; else x[j | bit] = recv;
+      }
+    }
+  }
+}
+
 // Exponent of one 16-key block of P from its maximum (the scalar form of block_exponents4):
 // noff with p'/2^e = 2^(s * sl2 + noff), and the byte e + 127.
 __device__ __forceinline__ void block_exponent1(float bm, float m_ref, float sl2, float& noff,
@@ -151,6 +204,29 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   const WaitCtx wc{s_abort, p.status, p.budget_ns, p.epoch};
   const int R = p.Sq * p.group;  // live query rows (<= 16)
 
+  // The query rows and their scale words go to registers first thing: their latency (a trip to
+  // HBM while every CTA of the grid starts its K / V stream) then overlaps the set-up below
+  // instead of following it.  Threads 0-63: row tid / 4, 16-byte chunk tid % 4; threads 64-95: row
+  // (tid - 64) / 2, the scale word of 64-element step tid % 2.
+  uint4 q_pref = make_uint4(0u, 0u, 0u, 0u);
+  uint32_t qsf_pref = 0u;
+  if (tid < 64) {
+    const int r = tid >> 2, ch = tid & 3;
+    if (r < R) {
+      const int s = r / p.group, h = hk * p.group + r % p.group;
+      q_pref = *reinterpret_cast<const uint4*>(d.q + b * d.q_stride_b + s * d.q_stride_s + h * d.q_stride_h +
+                                               ch * 16);
+    }
+  } else if (tid < 64 + 32) {
+    const int r = (tid - 64) >> 1, ks = tid & 1;
+    if (r < R) {
+      const int s = r / p.group, h = hk * p.group + r % p.group;
+      const uint8_t* chunk = d.q_sf + b * p.qsf_stride_b + h * p.qsf_stride_h + ((int64_t)(s / 128) * 2 + ks) * 512;
+      const int rr = s % 128;
+      qsf_pref = *reinterpret_cast<const uint32_t*>(chunk + (rr % 32) * 16 + (rr / 32) * 4);
+    }
+  }
+
   // this CTA's share of the entry's K/V blocks (ascending, contiguous, ceil division like the
   // split-KV path of the prefill kernel)
   int sk = p.Sk;
@@ -181,10 +257,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     mbar_init(bars.at(Bars::kDrain), 1);
     fence_barrier_init();
   }
-  if (warp == 4 && lane == 0) {
-    tma_prefetch_desc(&tm_k);
-    tma_prefetch_desc(&tm_v);
-  }
+  if (warp == 4 && lane == 0) tma_prefetch_desc(&tm_k);
+  if (warp == 6 && lane == 0) tma_prefetch_desc(&tm_v);
   if (warp == 5) {
     tmem_alloc(base + kOffMisc, kDTmemCols);
     tmem_relinquish();
@@ -199,9 +273,18 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   constexpr uint32_t idesc = make_idesc_nvf4(128, 16);
   bool ok = true;
 
-  if (warp == 4) {
-    // ============================================ TMA producer ==================================
+  if (warp == 4 || warp == 6) {
+    // ============================================ TMA producers =================================
+    // Warp 4 streams K, warp 6 streams V, each as far ahead as its own ring allows.  (One thread
+    // issuing K and V in turn tied the K stream to the P V products: K of block i + 1 went out
+    // only when P V of block i - 3 had freed a V stage, one block time before Q K^T needs it, and
+    // the kernel ran at one block per memory latency.)
     if (lane == 0) {
+      const bool is_k = warp == 4;
+      const uint32_t full0 = is_k ? Bars::kKFull : Bars::kVFull, free0 = is_k ? Bars::kKFree : Bars::kVFree;
+      const uint32_t tile0 = base + (is_k ? kOffK : kOffV), sf0 = base + (is_k ? kOffSFK : kOffSFV);
+      const uint8_t* sf_src = is_k ? p.k_sf + hk * p.ksf_stride_h : p.v_sf + hk * p.vsf_stride_h;
+      const int64_t sf_stride_b = is_k ? p.ksf_stride_b : p.vsf_stride_b;
       uint32_t issued = 0;
       for (int li = 0; ok && li < n; ++li) {
         const int nb = i0 + li;
@@ -213,33 +296,24 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
           nbl = (key0 - pg * p.page_size) / kBlockN;
         }
         if (li >= kStages) {
-          ok = mbar_wait(bars.at(Bars::kKFree + st), ((li - kStages) / kStages) & 1, wc, kDKFree);
+          ok = mbar_wait(bars.at(free0 + st), ((li - kStages) / kStages) & 1, wc, is_k ? kDKFree : kDVFree);
           if (!ok) break;
         }
-        mbar_arrive_expect_tx(bars.at(Bars::kKFull + st), kTileBytes + kSfBytes);
-        tma_load_4d(base + kOffK + st * kTileBytes, &tm_k, bars.at(Bars::kKFull + st), 0, hk,
-                    nbl * kBlockN, kb);
-        bulk_load(base + kOffSFK + st * kSfBytes,
-                  p.k_sf + kb * p.ksf_stride_b + hk * p.ksf_stride_h + (int64_t)nbl * kSfBytes, kSfBytes,
-                  bars.at(Bars::kKFull + st));
-        if (li >= kStages) {
-          ok = mbar_wait(bars.at(Bars::kVFree + st), ((li - kStages) / kStages) & 1, wc, kDVFree);
-          if (!ok) break;
+        mbar_arrive_expect_tx(bars.at(full0 + st), kTileBytes + kSfBytes);
+        if (is_k) {
+          tma_load_4d(tile0 + st * kTileBytes, &tm_k, bars.at(full0 + st), 0, hk, nbl * kBlockN, kb);
+        } else {
+          tma_load_4d(tile0 + st * kTileBytes, &tm_v, bars.at(full0 + st), nbl * (kBlockN / 2), 0, hk, kb);
         }
-        mbar_arrive_expect_tx(bars.at(Bars::kVFull + st), kTileBytes + kSfBytes);
-        tma_load_4d(base + kOffV + st * kTileBytes, &tm_v, bars.at(Bars::kVFull + st),
-                    nbl * (kBlockN / 2), 0, hk, kb);
-        bulk_load(base + kOffSFV + st * kSfBytes,
-                  p.v_sf + kb * p.vsf_stride_b + hk * p.vsf_stride_h + (int64_t)nbl * kSfBytes, kSfBytes,
-                  bars.at(Bars::kVFull + st));
+        bulk_load(sf0 + st * kSfBytes, sf_src + kb * sf_stride_b + (int64_t)nbl * kSfBytes, kSfBytes,
+                  bars.at(full0 + st));
         issued = li + 1;
       }
       if (!ok) {
         // bounded drain: let the copies already issued land before the CTA's memory is released
         const uint64_t t0 = globaltimer_ns();
         for (uint32_t i = issued > kStages ? issued - kStages : 0; i < issued; ++i) {
-          while (!(mbar_try_wait(bars.at(Bars::kKFull + (i % kStages)), (i / kStages) & 1) &&
-                   mbar_try_wait(bars.at(Bars::kVFull + (i % kStages)), (i / kStages) & 1)) &&
+          while (!mbar_try_wait(bars.at(full0 + (i % kStages)), (i / kStages) & 1) &&
                  globaltimer_ns() - t0 < 50ull * 1000 * 1000) {}
         }
       }
@@ -330,42 +404,28 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     FA4_DEC_SYNC()
     if (ok && tid < 64) {
       const int r = tid >> 2, ch = tid & 3;
-      if (r < R) {
-        const int s = r / p.group, h = hk * p.group + r % p.group;
-        const uint4 v = *reinterpret_cast<const uint4*>(d.q + b * d.q_stride_b + s * d.q_stride_s +
-                                                        h * d.q_stride_h + ch * 16);
-        *reinterpret_cast<uint4*>(gbase + kOffQ + sw64_offset(r, ch)) = v;
-      }
+      if (r < R) *reinterpret_cast<uint4*>(gbase + kOffQ + sw64_offset(r, ch)) = q_pref;
     } else if (ok && tid < 64 + 32) {
       // scale bytes of row r: two words (one per 64-element step) of the tiled layout
       const int r = (tid - 64) >> 1, ks = tid & 1;
-      if (r < R) {
-        const int s = r / p.group, h = hk * p.group + r % p.group;
-        const uint8_t* chunk = d.q_sf + b * p.qsf_stride_b + h * p.qsf_stride_h +
-                               ((int64_t)(s / 128) * 2 + ks) * 512;
-        const int rr = s % 128;
-        const uint32_t w = *reinterpret_cast<const uint32_t*>(chunk + (rr % 32) * 16 + (rr / 32) * 4);
-        *reinterpret_cast<uint32_t*>(gbase + kOffSFQ + 512 * ks + r * 16) = w;
-      }
+      if (r < R) *reinterpret_cast<uint32_t*>(gbase + kOffSFQ + 512 * ks + r * 16) = qsf_pref;
     }
     fence_proxy_async_smem();
     mbar_arrive(bars.at(Bars::kQReady));
 
-    float m_ref[kR], l_sum[kR];
-#pragma unroll
-    for (int r = 0; r < kR; ++r) {
-      m_ref[r] = kNegInf;
-      l_sum[r] = 0.f;
-    }
-    // last visible key of row r (causal: bottom-right aligned on the entry's key count); rows past
-    // R see nothing.  Also the output coordinates of the rows, fixed for the whole CTA.
-    int lim[kR], row_s[kR], row_h[kR];
-#pragma unroll
-    for (int r = 0; r < kR; ++r) {
-      row_s[r] = r / p.group;
-      row_h[r] = hk * p.group + r % p.group;
-      const int c = sk - p.Sq + row_s[r];
-      lim[r] = (r < R) ? ((p.causal && c < sk - 1) ? c : sk - 1) : -1;
+    // After the transpose below a thread owns ONE query row (row = lane % kR) with kR neighbouring
+    // keys of its warp's 32 (group = lane / kR), so everything per row -- mask limit, reference
+    // maximum, block exponent, running sum -- is scalar per thread and runs once per block, where a
+    // thread that kept "its key, all rows" ran it kR times.
+    const int my_row = lane & (kR - 1), grp = lane / kR;
+    const int key_in_blk = warp * 32 + grp * kR;   // first of this thread's kR keys inside the block
+    float m_ref = kNegInf, l_sum = 0.f;
+    // last visible key of the row (causal: bottom-right aligned on the entry's key count); rows
+    // past R see nothing
+    int lim = -1;
+    if (my_row < R) {
+      const int c = sk - p.Sq + my_row / p.group;
+      lim = (p.causal && c < sk - 1) ? c : sk - 1;
     }
 
     for (int li = 0; ok && li < n; ++li) {
@@ -374,54 +434,42 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       ok = __all_sync(0xffffffffu, mbar_wait(bars.at(Bars::kSFull + buf), (li / kSBufs) & 1, wc, kDSFull));
       if (!ok) break;
       tc_fence_after_sync();
-      float s16[16];
-      tmem_ld16(lane_addr + kDTmS + 16 * buf, reinterpret_cast<uint32_t*>(s16));
+      float x[kR];
+      tmem_ld_cols<kR>(lane_addr + kDTmS + 16 * buf, reinterpret_cast<uint32_t*>(x));
       tc_wait_ld();
-      float s[kR];
-#pragma unroll
-      for (int r = 0; r < kR; ++r) s[r] = s16[r];
       tc_fence_before_sync();
       mbar_arrive(bars.at(Bars::kSFree + buf));
 
-      // mask: this thread's key against every row's limit; rows past R count as fully masked
-      const int key = nb * kBlockN + tid;
-      // maxima of this thread's 16-key block per row (four shuffle steps, kept for the P scales),
-      // then of the warp's 32 keys (one more)
-      float wmax[kR], bmax[kR];
+      // (key = lane, all rows) -> (row = lane % kR, kR keys): x[j] = score of key key_in_blk + j
+      lane_group_transpose<kR>(x, lane);
+      const int key0 = nb * kBlockN + key_in_blk;
+      float bm = kNegInf;
 #pragma unroll
-      for (int r = 0; r < kR; ++r) {
-        s[r] = (key <= lim[r]) ? s[r] : kNegInf;
-        float m = s[r];
-#pragma unroll
-        for (int o = 8; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-        bmax[r] = m;
-        wmax[r] = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
+      for (int j = 0; j < kR; ++j) {
+        x[j] = (key0 + j <= lim) ? x[j] : kNegInf;
+        bm = fmaxf(bm, x[j]);
       }
+      // maximum of the row's 16-key block (kept for the P scale), then of the warp's 32 keys
+#pragma unroll
+      for (int o = kR; o < 16; o <<= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, o));
+      const float wm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 16));
       volatile float* red = s_red + (li & 1) * 64;
-      if (lane < kR) {
-        float mine = wmax[0];
-#pragma unroll
-        for (int r = 1; r < kR; ++r) mine = (lane == r) ? wmax[r] : mine;
-        red[warp * 16 + lane] = mine;
-      }
+      if (lane < kR) red[warp * 16 + lane] = wm;
       FA4_DEC_SYNC()
       if (!ok) break;
 
-      // reference maxima (every thread keeps all rows: the values are CTA-uniform)
-      bool moved = false;
-      float fac[kR];
-#pragma unroll
-      for (int r = 0; r < kR; ++r) {
-        const float m_loc = fmaxf(fmaxf(red[r], red[16 + r]), fmaxf(red[32 + r], red[48 + r]));
-        const float m_new = next_reference(m_ref[r], m_loc, p.sl2);
-        fac[r] = 1.f;
-        if (m_new != m_ref[r]) {
-          fac[r] = reference_factor(m_ref[r], m_new, p.sl2);
-          moved = moved || (m_ref[r] != kNegInf);
-          l_sum[r] *= fac[r];
-          m_ref[r] = m_new;
-        }
+      // reference maximum of the row (CTA-uniform per row: every warp computes the same value)
+      const float m_loc = fmaxf(fmaxf(red[my_row], red[16 + my_row]), fmaxf(red[32 + my_row], red[48 + my_row]));
+      const float m_new = next_reference(m_ref, m_loc, p.sl2);
+      float fac = 1.f;
+      bool moved_row = false;
+      if (m_new != m_ref) {
+        fac = reference_factor(m_ref, m_new, p.sl2);
+        moved_row = m_ref != kNegInf;
+        l_sum *= fac;
+        m_ref = m_new;
       }
+      const bool moved = __any_sync(0xffffffffu, moved_row);   // every warp holds all rows
 
       // P slot free once P V of block li - kPSlots has run
       if (li >= kPSlots) {
@@ -429,40 +477,53 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
                                                kDPvDone));
         if (!ok) break;
       }
-      uint8_t* p_tile = gbase + kOffP + slot * 1024;
-      uint8_t* p_sf = gbase + kOffSFP + slot * 1024;
-      const int blk = tid >> 4;  // 16-key block of this thread inside the 128 keys
+      {
+        float noff;
+        uint32_t ue;
+        block_exponent1(bm, m_ref, p.sl2, noff, ue);
+        float pv[kR], psum = 0.f;
 #pragma unroll
-      for (int r = 0; r < kR; ++r) {
-        if (r < R) {  // R is CTA-uniform
-          float noff;
-          uint32_t ue;
-          block_exponent1(bmax[r], m_ref[r], p.sl2, noff, ue);
-          const float pv = ex2_approx(fmaf(s[r], p.sl2, noff));
-          l_sum[r] = fmaf(pv, __uint_as_float(ue << 23), l_sum[r]);
-          const float other = __shfl_xor_sync(0xffffffffu, pv, 1);
-          if ((tid & 1) == 0) {
-            const uint32_t col = tid >> 1;  // byte of the 64-byte row: keys 2 col, 2 col + 1
-            p_tile[sw64_offset(r, col >> 4) + (col & 15)] = static_cast<uint8_t>(pack2_e2m1(pv, other));
+        for (int j = 0; j < kR; ++j) {
+          pv[j] = ex2_approx(fmaf(x[j], p.sl2, noff));
+          psum += pv[j];
+        }
+        l_sum = fmaf(psum, __uint_as_float(ue << 23), l_sum);
+        if (my_row < R) {   // rows past R stay zero (written once at set-up)
+          // kR keys = kR / 2 bytes of the row's 64, inside one 16-byte chunk of the swizzled tile
+          const uint32_t col = static_cast<uint32_t>(key_in_blk) >> 1;
+          uint8_t* dst = gbase + kOffP + slot * 1024 + sw64_offset(my_row, col >> 4) + (col & 15);
+          if constexpr (kR == 4) {
+            *reinterpret_cast<uint16_t*>(dst) =
+                static_cast<uint16_t>(pack2_e2m1(pv[0], pv[1]) | (pack2_e2m1(pv[2], pv[3]) << 8));
+          } else if constexpr (kR == 8) {
+            *reinterpret_cast<uint32_t*>(dst) = pack8_e2m1(pv[0], pv[1], pv[2], pv[3], pv[4], pv[5], pv[6], pv[7]);
+          } else {
+            *reinterpret_cast<uint2*>(dst) =
+                make_uint2(pack8_e2m1(pv[0], pv[1], pv[2], pv[3], pv[4], pv[5], pv[6], pv[7]),
+                           pack8_e2m1(pv[8 % kR], pv[9 % kR], pv[10 % kR], pv[11 % kR], pv[12 % kR], pv[13 % kR],
+                                      pv[14 % kR], pv[15 % kR]));
           }
-          if ((tid & 15) == 0) {
-            p_sf[512 * (blk >> 2) + r * 16 + (blk & 3)] = static_cast<uint8_t>((ue - 0x78u) << 3);
+          if ((key_in_blk & 15) == 0) {
+            const int blk = key_in_blk >> 4;  // 16-key block inside the 128 keys
+            gbase[kOffSFP + slot * 1024 + 512 * (blk >> 2) + my_row * 16 + (blk & 3)] =
+                static_cast<uint8_t>((ue - 0x78u) << 3);
           }
         }
       }
 
-      // correction (rare): O^T holds the earlier blocks relative to the old references
+      // correction (rare): O^T holds the earlier blocks relative to the old references; here a
+      // thread is a dv lane with all rows in its columns, the factor of row r sits in lane r
       if (li > 0 && moved) {
         ok = __all_sync(0xffffffffu, mbar_wait(bars.at(Bars::kPvDone + ((li - 1) % kPSlots)),
                                                ((li - 1) / kPSlots) & 1, wc, kDPvDone));
         if (!ok) break;
         tc_fence_after_sync();
-        float o[16];
-        tmem_ld16(lane_addr + kDTmO, reinterpret_cast<uint32_t*>(o));
+        float o[kR];
+        tmem_ld_cols<kR>(lane_addr + kDTmO, reinterpret_cast<uint32_t*>(o));
         tc_wait_ld();
 #pragma unroll
-        for (int r = 0; r < kR; ++r) o[r] *= fac[r];
-        tmem_st16(lane_addr + kDTmO, reinterpret_cast<const uint32_t*>(o));
+        for (int r = 0; r < kR; ++r) o[r] *= __shfl_sync(0xffffffffu, fac, r);
+        tmem_st_cols<kR>(lane_addr + kDTmO, reinterpret_cast<const uint32_t*>(o));
         tc_wait_st();
       }
       fence_proxy_async_smem();
@@ -473,33 +534,23 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     // ---- epilogue: row sums over the 128 key lanes, then thread = dv lane of O^T --------------
     if (ok) {
       volatile float* red = s_red + (n & 1) * 64;
-      float wsum[kR];
+      float v = l_sum;   // this thread's share of its row; the lanes of one row are kR apart
 #pragma unroll
-      for (int r = 0; r < kR; ++r) {
-        float v = l_sum[r];
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        wsum[r] = v;
-      }
-      if (lane < kR) {
-        float mine = wsum[0];
-#pragma unroll
-        for (int r = 1; r < kR; ++r) mine = (lane == r) ? wsum[r] : mine;
-        red[warp * 16 + lane] = mine;
-      }
+      for (int o = kR; o < 32; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (lane < kR) red[warp * 16 + lane] = v;
       FA4_DEC_SYNC()
     }
     if (ok) {
       volatile float* red = s_red + (n & 1) * 64;
-      float o[16];
+      float o[kR];
 #pragma unroll
-      for (int r = 0; r < 16; ++r) o[r] = 0.f;
+      for (int r = 0; r < kR; ++r) o[r] = 0.f;
       if (n > 0) {
         ok = __all_sync(0xffffffffu, mbar_wait(bars.at(Bars::kPvDone + ((n - 1) % kPSlots)),
                                                ((n - 1) / kPSlots) & 1, wc, kDPvDone));
         if (ok) {
           tc_fence_after_sync();
-          tmem_ld16(lane_addr + kDTmO, reinterpret_cast<uint32_t*>(o));
+          tmem_ld_cols<kR>(lane_addr + kDTmO, reinterpret_cast<uint32_t*>(o));
           tc_wait_ld();
         }
       }
@@ -509,12 +560,12 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
           if (r < R) {
             // fixed order over the four warps: the sum of a row does not depend on timing
             const float l_tot = ((red[r] + red[16 + r]) + red[32 + r]) + red[48 + r];
-            const int s = row_s[r], h = row_h[r];
+            const int s = r / p.group, h = hk * p.group + r % p.group;
             const float scale = (l_tot > 0.f && n > 0) ? p.out_scale / l_tot : 0.f;
             d.o_partial[((((int64_t)split * p.B + b) * p.Sq + s) * p.Hq + h) * 128 + tid] = o[r] * scale;
-            if (tid == r) {
+            if (tid == r) {   // thread r (warp 0, lane r) owns row r: its m_ref is the row's
               d.lse_partial[(((int64_t)split * p.B + b) * p.Hq + h) * p.Sq + s] =
-                  finish_lse(m_ref[r], l_tot, p.sl2);
+                  finish_lse(m_ref, l_tot, p.sl2);
             }
           }
         }

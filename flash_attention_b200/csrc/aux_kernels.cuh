@@ -221,19 +221,39 @@ __global__ void combine_splits_kernel(const float* __restrict__ o_partial,
     const int64_t bs = r / Hq;
     const int s = (int)(bs % Sq), b = (int)(bs / Sq);
     const int64_t l_idx = ((int64_t)b * Hq + h) * Sq + s;
+    // loads in batches of eight, all in flight before the first is used: the partials come from L2
+    // (the kernel before wrote them) and a chain of dependent round trips would set the pace
+    constexpr int kBatch = 8;
     float m = -INFINITY;
-    for (int i = 0; i < num_splits; ++i) m = fmaxf(m, lse_partial[i * split_l + l_idx]);
+    for (int i0 = 0; i0 < num_splits; i0 += kBatch) {
+      float l[kBatch];
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j) l[j] = (i0 + j < num_splits) ? lse_partial[(i0 + j) * split_l + l_idx] : -INFINITY;
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j) m = fmaxf(m, l[j]);
+    }
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     float sum = 0.f;
     if (m != -INFINITY) {
-      for (int i = 0; i < num_splits; ++i) {
-        const float w = __expf(lse_partial[i * split_l + l_idx] - m);
-        const float4 v = *reinterpret_cast<const float4*>(o_partial + i * split_o + r * Dv + 4 * c);
-        sum += w;
-        acc.x = fmaf(w, v.x, acc.x);
-        acc.y = fmaf(w, v.y, acc.y);
-        acc.z = fmaf(w, v.z, acc.z);
-        acc.w = fmaf(w, v.w, acc.w);
+      for (int i0 = 0; i0 < num_splits; i0 += kBatch) {
+        float l[kBatch];
+        float4 v[kBatch];
+#pragma unroll
+        for (int j = 0; j < kBatch; ++j) {
+          const bool live = i0 + j < num_splits;
+          l[j] = live ? lse_partial[(i0 + j) * split_l + l_idx] : -INFINITY;
+          v[j] = live ? *reinterpret_cast<const float4*>(o_partial + (i0 + j) * split_o + r * Dv + 4 * c)
+                      : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < kBatch; ++j) {   // ascending split order, as before
+          const float w = __expf(l[j] - m);  // exp(-inf) = 0 for the padding of the last batch
+          sum += w;
+          acc.x = fmaf(w, v[j].x, acc.x);
+          acc.y = fmaf(w, v[j].y, acc.y);
+          acc.z = fmaf(w, v[j].z, acc.z);
+          acc.w = fmaf(w, v[j].w, acc.w);
+        }
       }
       const float inv = 1.f / sum;
       acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;

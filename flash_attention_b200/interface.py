@@ -285,11 +285,22 @@ def flash_attn_fp4_func(
 
 
 def choose_decode_splits(B: int, Hkv: int, Sk: int, device=None) -> int:
-    """Key splits of the decode kernel (grid = splits x Hkv x B, three CTAs fit an SM): enough CTAs for
-    about three per SM, at least two 128-key blocks per split."""
+    """Key splits of the decode kernel (grid = splits x Hkv x B; three CTAs fit an SM).
+
+    The kernel streams K and V at the pace of HBM once about two CTAs per SM pull on it, so the
+    count aims at 2 x SMs CTAs (more splits only add partials for the combine kernel), with at
+    least two 128-key blocks per split.  When B x Hkv alone exceeds the 3 x SMs resident CTAs the
+    grid runs in waves anyway: then the count (up to 4) that minimises waves x (blocks per split + 4
+    blocks of fixed cost per CTA) evens out the last wave.  Measured on B200 (Hq 32, Hkv 8, us per
+    call): B=4, Sk=32768: 9 or 13 splits 46, 18 splits 54; B=1, Sk=131072: 37 splits 50, 55 splits
+    54; B=64, Sk=4096: 1 split 89, 2 splits 79."""
     sms = torch.cuda.get_device_properties(device).multi_processor_count
     blocks = (Sk + 127) // 128
-    want = (3 * sms) // max(1, B * Hkv)          # rounded down: a second, nearly empty wave doubles the time
+    units = max(1, B * Hkv)
+    if units > 3 * sms:
+        cost = lambda ns: -(-ns * units // (3 * sms)) * (-(-blocks // ns) + 4)
+        return min((ns for ns in range(1, 5) if ns <= max(1, blocks // 2)), key=lambda ns: (cost(ns), ns))
+    want = max(1, (2 * sms + units // 2) // units)
     return max(1, min(128, want, max(1, blocks // 2)))
 
 

@@ -203,7 +203,7 @@ def test_split_heuristic_cost_model():
 
 
 def test_decode_split_choice_and_oracle_model_selection():
-    """Host logic around the decode kernel: key splits fill the GPU in one wave (three CTAs per SM)
+    """Host logic around the decode kernel: key splits aim at about two CTAs per SM (the kernel is HBM-bound from there)
     with at least two blocks per split, and the test helper picks the oracle model of the kernel
     the library would run."""
     from unittest import mock
@@ -213,10 +213,10 @@ def test_decode_split_choice_and_oracle_model_selection():
     class Props:
         multi_processor_count = 148
     with mock.patch.object(torch.cuda, "get_device_properties", lambda d: Props):
-        assert I.choose_decode_splits(4, 8, 32768, None) == 13          # 416 CTAs <= 444 slots
-        assert I.choose_decode_splits(64, 8, 4096, None) == 1           # already 512 CTAs
+        assert I.choose_decode_splits(4, 8, 32768, None) == 9           # 288 CTAs: about two per SM
+        assert I.choose_decode_splits(64, 8, 4096, None) == 2           # 512 units run in waves: 3 x 20 < 2 x 36
         assert I.choose_decode_splits(1, 1, 512, None) == 2             # at least two blocks per split
-        assert I.choose_decode_splits(1, 8, 1 << 20, None) == 55
+        assert I.choose_decode_splits(1, 8, 1 << 20, None) == 37
     assert kernel_model(128, rows=4) == {"step_keys": 128, "ascending": True}          # decode kernel
     assert kernel_model(128, rows=4, num_splits=5) == {"step_keys": 128, "ascending": True}
     def is64(m):       # the 64-key kernel's model (its P block-scale rule is whatever the library was built with)
