@@ -30,7 +30,7 @@ class HostPipeline:
     """
 
     def __init__(self, B: int, Sq: int, Sk: int, Hq: int, Hkv: int, D: int = 128, Dv: int = 128,
-                 device=None, row_chunks: int = 4):
+                 device=None, row_chunks: Optional[int] = None):
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.shape = (B, Sq, Sk, Hq, Hkv, D, Dv)
         dev = self.device
@@ -50,8 +50,16 @@ class HostPipeline:
         self.inputs_free = None      # event: the previous run's kernels have read the staging inputs
         self.outputs_free = None     # event: the previous run's copy-out has drained the staging outputs
         self.done = None
-        # query-row ranges: equal numbers of 128-row tiles, the last range takes the remainder
+        # query-row ranges: equal numbers of 128-row tiles, the last range takes the remainder.
+        # Every piece costs about ten stream operations on the host; the default keeps a piece's
+        # output at 8 MiB or more (up to four ranges per batch entry) so that small problems --
+        # one GPU's shard of a sharded call -- are not bound by the host's launch rate, and at
+        # least four pieces per call so that the three streams have something to overlap.
         tiles = (Sq + 127) // 128
+        if row_chunks is None:
+            row_chunks = max(1, min(4, (Sq * Hq * Dv * 2) // (8 << 20)))
+            if B * row_chunks < 4:
+                row_chunks = -(-4 // B)
         n = max(1, min(row_chunks, tiles))
         per = (tiles + n - 1) // n
         self.ranges = [(t * 128, min(Sq, (t + per) * 128)) for t in range(0, tiles, per)]
@@ -125,7 +133,7 @@ class HostPipeline:
 
 
 def flash_attn_fp4_host(q, k, v, q_sf, k_sf, v_sf, q_scale, k_scale, v_scale, causal: bool = False,
-                        softmax_scale: Optional[float] = None, device=None, row_chunks: int = 4,
+                        softmax_scale: Optional[float] = None, device=None, row_chunks: Optional[int] = None,
                         pipeline: Optional[HostPipeline] = None
                         ) -> Tuple[torch.Tensor, torch.Tensor]:
     """One-shot convenience wrapper: host operands in, pinned host ``(out, lse)`` back (synchronises)."""

@@ -628,6 +628,10 @@ def test_softcap_parity(cuda_device, case):
     ("sixteen_rows_mha", 1, 16, 512, 2, 2, True, 2),
     ("eight_rows_more_splits_than_blocks", 1, 2, 256, 8, 2, True, 5),
     ("one_row_chosen_splits", 3, 1, 4096, 8, 2, True, 0),
+    # row counts that do not fill the kernel's 4 / 8 / 16-row forms (padding rows see nothing)
+    ("three_rows_of_four", 1, 3, 416, 2, 2, True, 2),
+    ("six_rows_of_eight_noncausal", 2, 3, 300, 4, 2, False, 1),
+    ("twelve_rows_of_sixteen", 1, 3, 1000, 8, 2, True, 3),
 ], ids=lambda c: c[0])
 def test_decode_kernel_parity(cuda_device, case):
     """The transposed decode kernel (keys on the lanes, the Sq * Hq / Hkv <= 16 query rows of a kv
