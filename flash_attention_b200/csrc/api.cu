@@ -572,7 +572,9 @@ extern "C" int fa4_nvfp4_quantize_qk_bf16(const void* x, int32_t B, int32_t S, i
   const int64_t per_row64 = (int64_t)H * (D / 16);
   if (rows64 > 0x7fffffffll || per_row64 > (1 << 24)) return -FA4_E_TOO_LARGE;
   const int per_row = (int)per_row64;
-  int rows_per_group = per_row >= 256 ? 1 : 256 / per_row;   // about one block of 16 per thread
+  // about eight blocks of 16 per thread: the per-thread set-up (tensor scale and its reciprocal,
+  // index constants) is paid once per CTA, and a CTA streams 64 KB
+  int rows_per_group = per_row >= 2048 ? 1 : 2048 / per_row;
   const int64_t groups = (rows64 + rows_per_group - 1) / rows_per_group;
   if (groups > 0x7fffffffll) return -FA4_E_TOO_LARGE;
   quantize_rows_kernel<<<(unsigned)groups, 256, 0, static_cast<cudaStream_t>(cuda_stream)>>>(

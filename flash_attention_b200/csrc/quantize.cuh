@@ -68,23 +68,67 @@ __device__ __noinline__ uint2 quantize_block16_exact(Block16 x, float denom) {
                     pack8_e2m1(y[8], y[9], y[10], y[11], y[12], y[13], y[14], y[15]));
 }
 
+// Correctly rounded a / b from the correctly rounded reciprocal rb = RN(1 / b) and nb = -b: the
+// product a rb is within 2 ulp of the quotient, one residual step (the residual a - y b is exact
+// in an FMA) makes it faithful and a second one correctly rounded (Markstein's division theorem).
+// Five FMA-pipe instructions where a library division takes a dozen and a branch.  Needs finite
+// rb and residuals that do not underflow: callers keep operands near the bottom of the fp32
+// range on the library path.
+__device__ __forceinline__ float div_rn_by(float a, float nb, float rb) {
+  const float y0 = __fmul_rn(a, rb);
+  const float y1 = fmaf(fmaf(y0, nb, a), rb, y0);
+  return fmaf(fmaf(y1, nb, a), rb, y1);
+}
+// The same for a pair (packed fp32 instructions: both lanes round like the scalar ones).
+__device__ __forceinline__ float2 div_rn_by2(float2 a, float2 nb, float2 rb) {
+  const float2 y0 = __fmul2_rn(a, rb);
+  const float2 y1 = __ffma2_rn(__ffma2_rn(y0, nb, a), rb, y0);
+  return __ffma2_rn(__ffma2_rn(y1, nb, a), rb, y1);
+}
+
+// Per-tensor constants of the quantisers: the tensor scale g, -g, RN(1 / g), and whether g is so
+// small (below 1e-18) that the residual steps above could underflow where it matters: then the
+// block scales take the library division.
+struct TensorScale {
+  float g, neg_g, rcp_g;
+  bool tiny;
+};
+__device__ __forceinline__ TensorScale make_tensor_scale(float amax) {
+  TensorScale t;
+  t.g = tensor_scale_of(amax);
+  t.neg_g = -t.g;
+  t.tiny = !(t.g >= 1e-18f);
+  t.rcp_g = t.tiny ? 0.f : __frcp_rn(t.g);
+  return t;
+}
+
 // One block of 16 values -> 8 packed bytes (two words) and its scale byte.
-__device__ __forceinline__ void quantize_block16(const float (&x)[16], float g, uint32_t& lo,
+__device__ __forceinline__ void quantize_block16(const float (&x)[16], const TensorScale& ts, uint32_t& lo,
                                                  uint32_t& hi, uint32_t& sf_byte) {
-  float bmax = 0.f;
+  const float g = ts.g;
+  // |x| maxima of the block (two chains)
+  float bm0 = fmaxf(fabsf(x[0]), fabsf(x[1])), bm1 = fmaxf(fabsf(x[2]), fabsf(x[3]));
 #pragma unroll
-  for (int i = 0; i < 16; ++i) bmax = fmaxf(bmax, fabsf(x[i]));
-  const float t = fminf(__fdiv_rn(__fdiv_rn(bmax, 6.f), g), 448.f);
-  sf_byte = e4m3_byte(t);
+  for (int i = 4; i < 16; i += 2) {
+    bm0 = fmaxf(bm0, fabsf(x[i]));
+    bm1 = fmaxf(bm1, fabsf(x[i + 1]));
+  }
+  const float bmax = fmaxf(bm0, bm1);
+  // block scale = e4m3_rne(min((bmax / 6) / g, 448)).  With g >= 1e-18 every quotient that can
+  // reach the first rounding boundary of e4m3 (2^-10) has exact residuals; smaller quotients give
+  // the zero byte whatever their last bits are.
+  constexpr float kRcp6 = 0.16666667163372039794921875f;   // RN(1 / 6)
+  float t;
+  if (ts.tiny) {
+    t = __fdiv_rn(__fdiv_rn(bmax, 6.f), g);
+  } else {
+    t = div_rn_by(div_rn_by(bmax, -6.f, kRcp6), ts.neg_g, ts.rcp_g);
+  }
+  sf_byte = e4m3_byte(fminf(t, 448.f));
   const float denom = __fmul_rn(e4m3_value(sf_byte), g);
-  // The element codes are those of the correctly rounded quotients x / denom.  With r the
-  // correctly rounded reciprocal, y0 = x r is within 2 ulp of the quotient; one residual step
-  // (e = x - y d exactly, by FMA; y += e r) makes it faithful, and a second one then yields the
-  // correctly rounded quotient (Markstein's division theorem) -- five instructions per element
-  // and no branch, where sixteen library divisions made the kernel instruction-bound.  The
-  // theorem needs a finite reciprocal and no underflow of the residuals: denominators near the
-  // bottom of the fp32 range take the out-of-line exact path; quotients that small are far below
-  // the first rounding boundary (0.25) whatever the residuals do.
+  // The element codes are those of the correctly rounded quotients x / denom.  Denominators near
+  // the bottom of the fp32 range take the out-of-line exact path; quotients that small are far
+  // below the first rounding boundary (0.25) whatever the residuals do.
   if (denom < 1e-30f) {
     Block16 blk;
 #pragma unroll
@@ -94,15 +138,12 @@ __device__ __forceinline__ void quantize_block16(const float (&x)[16], float g, 
     hi = e.y;
   } else {
     const float r = __frcp_rn(denom);
-    float y[16];
+    const float2 rr = make_float2(r, r), nd = make_float2(-denom, -denom);
+    float2 y[8];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const float y0 = __fmul_rn(x[i], r);
-      const float y1 = fmaf(fmaf(-y0, denom, x[i]), r, y0);
-      y[i] = fmaf(fmaf(-y1, denom, x[i]), r, y1);
-    }
-    lo = pack8_e2m1(y[0], y[1], y[2], y[3], y[4], y[5], y[6], y[7]);
-    hi = pack8_e2m1(y[8], y[9], y[10], y[11], y[12], y[13], y[14], y[15]);
+    for (int i = 0; i < 8; ++i) y[i] = div_rn_by2(make_float2(x[2 * i], x[2 * i + 1]), nd, rr);
+    lo = pack8_e2m1(y[0].x, y[0].y, y[1].x, y[1].y, y[2].x, y[2].y, y[3].x, y[3].y);
+    hi = pack8_e2m1(y[4].x, y[4].y, y[5].x, y[5].y, y[6].x, y[6].y, y[7].x, y[7].y);
   }
   lo = drop_negative_zero(lo);
   hi = drop_negative_zero(hi);
@@ -164,8 +205,9 @@ amax_bf16_kernel(const __nv_bfloat16* __restrict__ x, int n1, int n2, int inner8
 }
 
 // ---------------------------------------------------------------------------------------------
-// Q / K: x (B, S, H, D) bf16, blocks along D.  One thread = one block of 16 elements (two
-// 16-byte loads, one 8-byte store); a CTA takes a group of (b, s) rows, H * D/16 blocks each.
+// Q / K: x (B, S, H, D) bf16, blocks along D.  One item = one block of 16 elements (two 16-byte
+// loads, one 8-byte store); a CTA takes a group of (b, s) rows, H * D/16 blocks each, about
+// eight items per thread.
 // The row index runs over S padded to a multiple of 128 so that the tiled scale layout gets its
 // zero padding from the same pass.
 //   packed    (B, S, H, D/2)  contiguous
@@ -180,8 +222,8 @@ quantize_rows_kernel(const __nv_bfloat16* __restrict__ x, int B, int S, int H, i
                      uint8_t* __restrict__ packed, uint8_t* __restrict__ sf_lin,
                      uint8_t* __restrict__ sf_tiled, float* __restrict__ scale_out,
                      int rows_per_group, FastDiv div_per_row, FastDiv div_nb, FastDiv div_spad) {
-  const float g = tensor_scale_of(*amax);
-  if (scale_out != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *scale_out = g;
+  const TensorScale g = make_tensor_scale(*amax);
+  if (scale_out != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *scale_out = g.g;
   const int nb = D / 16, ct = D / 64;
   const int rt = (S + 127) / 128, s_pad = rt * 128;
   const int rows = B * s_pad;
@@ -189,8 +231,9 @@ quantize_rows_kernel(const __nv_bfloat16* __restrict__ x, int B, int S, int H, i
   const int per_group = rows_per_group * per_row;
   const int row0 = blockIdx.x * rows_per_group;
   // Every lane of a warp runs the same number of iterations (shuffles below).  kBatch items per
-  // thread are loaded before any is processed (larger batches measured slower: the kernel is
-  // bound by instruction issue, not by loads in flight).
+  // thread are loaded before any is processed (2 measured the same, 4 slower: the ALU and FMA
+  // pipes are 55-66 % busy and two thirds of the issue slots are used; loads in flight are not
+  // what limits it).
   constexpr int kBatch = 1;
   const int iters = (per_group + 256 * kBatch - 1) / (256 * kBatch);
   for (int it = 0; it < iters; ++it) {
@@ -260,10 +303,10 @@ quantize_v_kernel(const __nv_bfloat16* __restrict__ x, int B, int Sk, int H, int
                   uint8_t* __restrict__ packed, uint8_t* __restrict__ sf_lin,
                   uint8_t* __restrict__ sf_tiled, float* __restrict__ scale_out) {
   __shared__ __align__(16) uint8_t tile[128 * 256];  // [key][16 chunks of 16 B], chunk ^ (key/16)
-  const float g = tensor_scale_of(*amax);
+  const TensorScale g = make_tensor_scale(*amax);
   if (scale_out != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 &&
       threadIdx.x == 0)
-    *scale_out = g;
+    *scale_out = g.g;
   const int k0 = blockIdx.x * 128, d0 = blockIdx.y * 128;
   const int b = blockIdx.z / H, h = blockIdx.z % H;
   const int tid = threadIdx.x;
