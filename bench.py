@@ -672,7 +672,8 @@ def run_fa4_bf16(args):
     """Same-box comparator: the reference's own Blackwell forward (flash_attn.cute.flash_attn_func,
     flash_attn/cute/interface.py:1753, BF16, CuTe-DSL JIT) on the DEQUANTISED operands of the
     benchmark configurations, rounded to bf16 -- the kernel the NVFP4 path sits beside.  Needs the
-    reference's `flash_attn/cute` package installed into baseline/_ref (see DESIGN.md) and a GPU;
+    reference's `flash_attn/cute` package installed into baseline/_ref (pip install --no-index
+    --no-build-isolation --no-deps --target baseline/_ref <copy of flash_attn/cute>) and a GPU;
     prints {"impl": "fa4_bf16", "unavailable": ...} otherwise.  Timed like the main arm (resident
     inputs, warm-up 5, L2 flush between launches, CUDA events), one JSON line with a table."""
     import types
