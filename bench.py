@@ -816,6 +816,26 @@ def run_decode(args):
             fa.check_status(dev)
             row[name] = {"us": ms * 1e3, "kv_gbs": kv_bytes / ms / 1e6,
                          "frac_of_hbm_peak": kv_bytes / ms / 1e6 / peaks["hbm_gbs"]}
+            if variant == fa.VARIANT_DECODE:
+                # the same call captured in a CUDA graph and replayed back to back, as a serving loop
+                # runs its decode steps: no launch gap, no L2 flush (K and V exceed L2 on the first
+                # two shapes; on the smaller ones part of them stays cached, which is what such a loop sees)
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    step()
+                for _ in range(3):
+                    graph.replay()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(50):
+                    graph.replay()
+                e1.record(); e1.synchronize()
+                g_ms = e0.elapsed_time(e1) / 50
+                fa.check_status(dev)
+                row[name].update(graph_replay_us=g_ms * 1e3, graph_replay_kv_gbs=kv_bytes / g_ms / 1e6,
+                                 graph_replay_kv_fits_l2=bool(kv_bytes < 126 * 1000 * 1000))
+                del graph
         rows.append(row)
         del Q, K, V
     head = rows[0]

@@ -834,3 +834,52 @@ def test_varlen_many_short_sequences_cost_about_a_dense_call(cuda_device):
     t_d, t_p = best_ms(dense), best_ms(packed)
     assert t_p <= 1.5 * t_d, (t_p, t_d)
 
+
+
+@pytest.mark.parametrize("shape", [
+    # name, B, Sq, Sk, Hq, Hkv, causal
+    ("prefill", 2, 384, 384, 4, 2, True),
+    ("decode", 2, 1, 2048, 8, 2, True),
+], ids=lambda c: c[0])
+def test_calls_replay_from_a_cuda_graph(cuda_device, shape):
+    """A serving loop captures its steps in CUDA graphs: the prefill call and the decode call
+    (decode kernel + combine kernel, a programmatic dependent launch) are captured once after a
+    warm-up call and replayed on new operand CONTENTS in the same buffers; every replay gives the
+    bits of an eager call on those operands."""
+    _, B, Sq, Sk, Hq, Hkv, causal = shape
+    ops = []
+    for seed in (51, 52):
+        q, k, v = make_qkv(B, Sq, Sk, Hq, Hkv, 128, seed=seed, device=cuda_device)
+        Q, K, V = fa.quantize_qkv(q, k, v)
+        ops.append([t.to(cuda_device) for t in (Q.data, K.data, V.data, Q.tiled_sf(), K.tiled_sf(), V.tiled_sf())]
+                   + [Q.scale, K.scale, V.scale])
+    static = [t.clone() for t in ops[0][:6]]
+    out = torch.empty(B, Sq, Hq, 128, dtype=torch.bfloat16, device=cuda_device)
+    lse = torch.empty(B, Hq, Sq, dtype=torch.float32, device=cuda_device)
+    # per-tensor scales are host floats baked into the captured launch: both operand sets are
+    # dequantised with the first set's scales here, in the eager calls too
+    scales = ops[0][6:]
+
+    def call(bufs, o, l):
+        return fa.flash_attn_fp4_func(*bufs, *scales, causal=causal, return_lse=True, out=o, lse=l, sf_layout="tiled")
+
+    side = torch.cuda.Stream(cuda_device)
+    side.wait_stream(torch.cuda.current_stream(cuda_device))
+    with torch.cuda.stream(side):
+        call(static, out, lse)                      # warm-up outside the capture (kernel attributes are set here)
+    torch.cuda.current_stream(cuda_device).wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        call(static, out, lse)
+    for which in (1, 0, 1):
+        for dst, src in zip(static, ops[which][:6]):
+            dst.copy_(src)
+        out.zero_()
+        lse.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        fa.check_status(cuda_device)
+        want_o, want_l = call(ops[which][:6], torch.empty_like(out), torch.empty_like(lse))
+        torch.cuda.synchronize()
+        assert torch.equal(out, want_o) and torch.equal(lse, want_l), which
