@@ -7,9 +7,9 @@ from .interface import (flash_attn_func, flash_attn_fp4_func, check_status, meas
                         VARIANT_AUTO,
                         VARIANT_WS, VARIANT_WS64, VARIANT_DECODE)
 from .host_pipeline import HostPipeline, flash_attn_fp4_host
-from .varlen import flash_attn_varlen_fp4_func
+from .varlen import flash_attn_varlen_fp4_func, quantize_varlen_qkv, padded_key_offsets
 from .quant import NVFP4Tensor, quantize_qkv, quantize_qkv_fused, quantize_lastdim, dequantize_lastdim, sf_to_tiled
 
-__all__ = ["flash_attn_func", "flash_attn_fp4_func", "check_status", "HostPipeline", "flash_attn_fp4_host", "flash_attn_varlen_fp4_func", "measure_fp4_mma_rate", "measure_ex2_rate", "NVFP4Tensor", "quantize_qkv", "quantize_qkv_fused",
+__all__ = ["flash_attn_func", "flash_attn_fp4_func", "check_status", "HostPipeline", "flash_attn_fp4_host", "flash_attn_varlen_fp4_func", "quantize_varlen_qkv", "padded_key_offsets", "measure_fp4_mma_rate", "measure_ex2_rate", "NVFP4Tensor", "quantize_qkv", "quantize_qkv_fused",
            "quantize_lastdim", "dequantize_lastdim", "sf_to_tiled", "build", "lib", "LIB_PATH",
            "VARIANT_AUTO", "VARIANT_WS", "VARIANT_WS64", "VARIANT_DECODE"]

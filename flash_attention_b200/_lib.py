@@ -70,6 +70,7 @@ class Varlen(ctypes.Structure):
         ("max_seqlen_q", ctypes.c_int32), ("max_seqlen_k", ctypes.c_int32),
         ("window_left", ctypes.c_int32), ("window_right", ctypes.c_int32),
         ("sink", ctypes.c_void_p), ("softcap", ctypes.c_float), ("reserved", ctypes.c_uint32),
+        ("cu_seqlens_v", ctypes.c_void_p), ("total_v", ctypes.c_int32), ("reserved2", ctypes.c_int32),
     ]
 
 

@@ -136,7 +136,8 @@ struct CacheView {
   // packed variable-length batch (see fa4_nvfp4_varlen)
   const int32_t* cu_seqlens_q = nullptr;
   const int32_t* cu_seqlens_k = nullptr;
-  int total_q = 0, total_k = 0;
+  const int32_t* cu_seqlens_v = nullptr;   // starts inside V (multiples of 32); null: cu_seqlens_k
+  int total_q = 0, total_k = 0, total_v = 0;
 };
 int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint64_t workspace_bytes,
                int win_left, int win_right, const float* sink, float softcap, const CacheView& cache,
@@ -176,7 +177,10 @@ extern "C" int fa4_nvfp4_fwd_varlen(const fa4_nvfp4_params* p, const fa4_nvfp4_v
   if (v->num_seqs <= 0 || v->total_q <= 0 || v->total_k <= 0 || v->max_seqlen_q <= 0 || v->max_seqlen_k <= 0 ||
       v->max_seqlen_q > v->total_q || v->max_seqlen_k > v->total_k)
     return -FA4_E_SHAPE;
-  if (v->window_left < -1 || v->window_right < -1 || !(v->softcap >= 0.f) || v->softcap > 3.0e38f || v->reserved != 0u)
+  if (v->window_left < -1 || v->window_right < -1 || !(v->softcap >= 0.f) || v->softcap > 3.0e38f || v->reserved != 0u ||
+      v->reserved2 != 0)
+    return -FA4_E_SHAPE;
+  if (v->cu_seqlens_v != nullptr ? (v->total_v < v->total_k || v->total_v % 32 != 0) : v->total_v != 0)
     return -FA4_E_SHAPE;
   if (p->variant != FA4_VARIANT_AUTO && p->variant != FA4_VARIANT_WS64) return -FA4_E_VARIANT;
   // one launch over (sequence, m-block of the longest sequence, head): the grid of the dense call
@@ -192,6 +196,8 @@ extern "C" int fa4_nvfp4_fwd_varlen(const fa4_nvfp4_params* p, const fa4_nvfp4_v
   cache.cu_seqlens_k = v->cu_seqlens_k;
   cache.total_q = v->total_q;
   cache.total_k = v->total_k;
+  cache.cu_seqlens_v = v->cu_seqlens_v;
+  cache.total_v = v->cu_seqlens_v != nullptr ? v->total_v : v->total_k;
   return launch_fwd(&q, 1, nullptr, 0, v->window_left, v->window_right, v->sink, v->softcap, cache, cuda_stream);
 }
 
@@ -339,7 +345,8 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
     const uint64_t dk[4] = {(uint64_t)p->D / 2, (uint64_t)p->Hkv, k_rows, k_batch};
     const uint64_t sk[3] = {(uint64_t)p->k_stride_h, (uint64_t)p->k_stride_s, (uint64_t)p->k_stride_b};
     const uint32_t bk[4] = {qk_box, 1, (uint32_t)kBlockN, 1};
-    const uint64_t dv[4] = {(k_rows + 31) / 32 * 16, (uint64_t)p->Dv, (uint64_t)p->Hkv, k_batch};   // padded key axis
+    const uint64_t v_keys = packed ? (uint64_t)cache.total_v : k_rows;   // a packed V has its own, padded key axis
+    const uint64_t dv[4] = {(v_keys + 31) / 32 * 16, (uint64_t)p->Dv, (uint64_t)p->Hkv, k_batch};   // padded key axis
     const uint64_t sv[3] = {(uint64_t)p->v_stride_d, (uint64_t)p->v_stride_h, (uint64_t)p->v_stride_b};
     const uint32_t bv[4] = {64, (uint32_t)p->Dv, 1, 1};
     // a Q / K tile row is D / 2 bytes: 64-byte swizzle for D = 128, 32-byte for D = 64
@@ -386,6 +393,7 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
   kp.pages_per_seq = cache.pages_per_seq;
   kp.cu_seqlens_q = cache.cu_seqlens_q;
   kp.cu_seqlens_k = cache.cu_seqlens_k;
+  kp.cu_seqlens_v = cache.cu_seqlens_v;
   kp.total_q = cache.total_q;
   kp.sl2 = p->softmax_scale * p->q_scale * p->k_scale * 1.4426950408889634f;
   kp.softcap_c1 = 0.f;

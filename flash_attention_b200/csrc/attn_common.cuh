@@ -82,6 +82,7 @@ struct KernelParams {
   // scales stay per sequence, padded to that longest length.  LSE is (Hq, total_q).  NULL = dense.
   const int32_t* cu_seqlens_q;
   const int32_t* cu_seqlens_k;
+  const int32_t* cu_seqlens_v;   // starts of the sequences inside V (multiples of 32); null: cu_seqlens_k
   int total_q;
 };
 
@@ -97,6 +98,7 @@ struct Tile {
   int sk;        // valid keys of this batch entry (general instantiation; p.Sk otherwise)
   int sq;        // query rows of this batch entry (packed batches; p.Sq otherwise)
   int q0, k0;    // first packed query row / key of this entry (packed batches; 0 otherwise)
+  int v0;        // first key of this entry inside V (packed batches: V pads every sequence to 32 keys)
 };
 
 // Query length that masks, block ranges and stores see.
@@ -135,6 +137,7 @@ __device__ __forceinline__ Tile decode_tile(const KernelParams& p, int tile_idx)
   t.sq = p.Sq;
   t.q0 = 0;
   t.k0 = 0;
+  t.v0 = 0;
   int n = p.num_n_blocks;
   if constexpr (kGeneral) {
     if (p.cu_seqlens_q != nullptr) {
@@ -142,6 +145,7 @@ __device__ __forceinline__ Tile decode_tile(const KernelParams& p, int tile_idx)
       t.sq = p.cu_seqlens_q[t.b + 1] - t.q0;
       t.k0 = p.cu_seqlens_k[t.b];
       t.sk = p.cu_seqlens_k[t.b + 1] - t.k0;
+      t.v0 = p.cu_seqlens_v != nullptr ? p.cu_seqlens_v[t.b] : t.k0;
       n = (t.sk + kBlockN - 1) / kBlockN;
     }
     if (p.seqused_k != nullptr) {

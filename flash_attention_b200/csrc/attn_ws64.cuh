@@ -443,7 +443,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
             int kb, nbl;
             locate(nb, kb, nbl);
             tma_load_4d(base + kOffV + st * kTileBytes, &tm_v, bars.at(Bars::kVFull + st),
-                        (t.k0 + nbl * kBlockN) / 2, 0, t.hk, packed ? 0 : kb);
+                        (t.v0 + nbl * kBlockN) / 2, 0, t.hk, packed ? 0 : kb);
             bulk_load(base + kOffSFV + st * kSfBytes,
                       p.v_sf + kb * p.vsf_stride_b + t.hk * p.vsf_stride_h + (int64_t)nbl * kSfBytes,
                       kSfBytes, bars.at(Bars::kVFull + st));

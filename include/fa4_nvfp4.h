@@ -202,9 +202,13 @@ int fa4_nvfp4_fwd_ex(const fa4_nvfp4_params* p, const fa4_nvfp4_ext* x, void* cu
  * p->q_stride_s / q_stride_h etc. are the token and head strides (the batch strides must still be
  * positive multiples of 16 and are not used), p->B / Sq / Sk are ignored.  Sequence b owns query
  * rows cu_seqlens_q[b] .. cu_seqlens_q[b+1] and keys cu_seqlens_k[b] .. cu_seqlens_k[b+1] (device
- * arrays of num_seqs + 1 int32; no host read-back anywhere).  Every key-sequence start must be a
- * multiple of 32 (V's 16-key scale blocks and 16-byte rows); `seqused_k` (optional) gives the
- * valid keys of each slot.  The tile grid is (sequence, m-block of the LONGEST sequence, head):
+ * arrays of num_seqs + 1 int32; no host read-back anywhere).  V is key-contiguous and blocked by 16
+ * keys with 16-byte rows, so inside V (and v_sf) every sequence starts on a multiple of 32 keys:
+ * cu_seqlens_v gives those starts (slot i = cu_seqlens_v[i] .. cu_seqlens_v[i+1], at least as long
+ * as sequence i, a multiple of 32, its tail zero), total_v the length of V's key axis; with
+ * cu_seqlens_v = NULL V uses cu_seqlens_k, whose starts must then be multiples of 32 themselves.
+ * K is packed without padding in either case.  `seqused_k` (optional) gives the valid keys of
+ * each slot.  The tile grid is (sequence, m-block of the LONGEST sequence, head):
  * pass max_seqlen_q / max_seqlen_k as the reference's call does; tiles past a sequence's end
  * cost a few instructions.  The tiled scale factors are per sequence, padded to the longest:
  *   q_sf (num_seqs, Hq, ceil(max_seqlen_q/128), D/64, 512), k_sf (num_seqs, Hkv,
@@ -225,6 +229,9 @@ typedef struct fa4_nvfp4_varlen {
   const float* sink;             /* Hq logits or NULL */
   float softcap;                 /* 0 = off */
   uint32_t reserved;             /* 0 */
+  const int32_t* cu_seqlens_v;   /* device, num_seqs + 1, multiples of 32, or NULL (= cu_seqlens_k) */
+  int32_t total_v;               /* keys along V's axis (a multiple of 32); 0 with cu_seqlens_v = NULL */
+  int32_t reserved2;             /* 0 */
 } fa4_nvfp4_varlen;
 int fa4_nvfp4_fwd_varlen(const fa4_nvfp4_params* p, const fa4_nvfp4_varlen* v, void* cuda_stream);
 
@@ -233,7 +240,8 @@ int fa4_nvfp4_fwd_varlen(const fa4_nvfp4_params* p, const fa4_nvfp4_varlen* v, v
  * padded with zeros to max_rows x max_cols.  packed_rows = 1: src is (total, n_inner, cols) with
  * the packed axis on the rows (q / k scales; stride_row = n_inner * cols, stride_inner = cols);
  * packed_rows = 0: src is (n_inner, rows, total / 16) with the packed axis on the columns
- * (v scales; cu_seqlens in keys, stride_inner = rows * row length, stride_row = row length).
+ * (v scales; cu_seqlens in keys -- the starts inside V, i.e. cu_seqlens_v when that is given --
+ * stride_inner = rows * row length, stride_row = row length).
  * No counterpart in the reference (it has no scale factors).
  */
 int fa4_nvfp4_sf_linear_to_tiled_packed(const void* src, void* dst, const int32_t* cu_seqlens,

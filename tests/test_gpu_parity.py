@@ -883,3 +883,43 @@ def test_calls_replay_from_a_cuda_graph(cuda_device, shape):
         want_o, want_l = call(ops[which][:6], torch.empty_like(out), torch.empty_like(lse))
         torch.cuda.synchronize()
         assert torch.equal(out, want_o) and torch.equal(lse, want_l), which
+
+
+def test_varlen_arbitrary_key_lengths_through_padded_v_slots(cuda_device):
+    """A packed batch whose key sequences start anywhere (lengths 70, 129, 1, 333 -- the reference's
+    varlen call has no alignment rule): K stays packed, V puts every sequence into a slot of whole
+    32-key groups (quantize_varlen_qkv / cu_seqlens_v).  Each sequence gives the bits of the dense
+    call on its own operands and meets the oracle's tolerance."""
+    Hq, Hkv, D = 4, 2, 128
+    sq, sk = [70, 5, 1, 200], [70, 129, 1, 333]
+    cq = [0] + list(np.cumsum(sq))
+    ck = [0] + list(np.cumsum(sk))
+    g = torch.Generator().manual_seed(33)
+    q = torch.randn(cq[-1], Hq, D, generator=g).bfloat16().to(cuda_device)
+    k = torch.randn(ck[-1], Hkv, D, generator=g).bfloat16().to(cuda_device)
+    v = torch.randn(ck[-1], Hkv, D, generator=g).bfloat16().to(cuda_device)
+    cu_q = torch.tensor(cq, dtype=torch.int32, device=cuda_device)
+    cu_k = torch.tensor(ck, dtype=torch.int32, device=cuda_device)
+    Q, K, V, cu_v = fa.quantize_varlen_qkv(q, k, v, cu_k)
+    cv = [int(x) for x in cu_v.cpu()]
+    assert cv == [0, 96, 256, 288, 640] and V.data.shape == (1, Hkv, D, 320)
+    for causal in (True, False):
+        out, lse = fa.flash_attn_varlen_fp4_func(
+            Q.data[0], K.data[0], V.data[0], Q.sf[0], K.sf[0], V.sf[0], Q.scale, K.scale, V.scale,
+            cu_q, cu_k, cu_seqlens_v=cu_v, max_seqlen_q=max(sq), max_seqlen_k=max(sk), causal=causal, return_lse=True)
+        torch.cuda.synchronize()
+        fa.check_status(cuda_device)
+        for i in range(len(sq)):
+            q0, q1, k0, k1, v0 = cq[i], cq[i + 1], ck[i], ck[i + 1], cv[i]
+            v1 = v0 + (sk[i] + 31) // 32 * 32
+            Qi = fa.NVFP4Tensor(Q.data[:, q0:q1].contiguous(), Q.sf[:, q0:q1].contiguous(), Q.scale)
+            Ki = fa.NVFP4Tensor(K.data[:, k0:k1].contiguous(), K.sf[:, k0:k1].contiguous(), K.scale)
+            Vi = fa.NVFP4Tensor(V.data[..., v0 // 2:v1 // 2].contiguous(), V.sf[..., v0 // 16:v1 // 16].contiguous(),
+                                V.scale, is_v=True)
+            o_d, l_d = run(Qi, Ki, Vi, causal, fa.VARIANT_WS64)
+            assert torch.equal(out[q0:q1], o_d[0]) and torch.equal(lse[:, q0:q1], l_d[0]), (causal, i)
+            assert_parity(o_d, l_d, *oracles(Qi, Ki, Vi, causal, variant=fa.VARIANT_WS64))
+    # without cu_seqlens_v the unaligned starts are refused on the host
+    with pytest.raises(NotImplementedError):
+        fa.flash_attn_varlen_fp4_func(Q.data[0], K.data[0], V.data[0], Q.sf[0], K.sf[0], V.sf[0], Q.scale, K.scale,
+                                      V.scale, cq, ck, causal=True)

@@ -279,3 +279,46 @@ def test_varlen_surface_rejects_bad_offsets_before_any_launch():
         fa.flash_attn_varlen_fp4_func(*args, [0, 16, 40], [0, 32, 80])
     with pytest.raises(AssertionError):               # different batch sizes
         fa.flash_attn_varlen_fp4_func(*args, [0, 48], [0, 32, 80])
+
+
+def test_varlen_entry_point_checks_its_arguments_on_the_host():
+    """fa4_nvfp4_fwd_varlen without a GPU: every malformed description of the packed batch comes
+    back with a negative argument code before anything could be launched."""
+    import ctypes
+    from flash_attention_b200 import _lib
+    L = fa.lib()
+    p = _lib.Params()
+    p.struct_size = ctypes.sizeof(_lib.Params)
+    for f in ("q", "k", "v", "q_sf", "k_sf", "v_sf", "out"):
+        setattr(p, f, 0x1000)
+    p.B, p.Sq, p.Sk, p.Hq, p.Hkv, p.D, p.Dv = 1, 128, 128, 2, 1, 128, 128
+    p.q_scale = p.k_scale = p.v_scale = 1.0
+    p.softmax_scale = 0.088
+
+    def varlen(**kw):
+        x = _lib.Varlen()
+        x.struct_size = ctypes.sizeof(_lib.Varlen)
+        x.num_seqs, x.total_q, x.total_k, x.max_seqlen_q, x.max_seqlen_k = 2, 200, 200, 128, 128
+        x.cu_seqlens_q = x.cu_seqlens_k = 0x2000
+        x.window_left = x.window_right = -1
+        for k_, v_ in kw.items():
+            setattr(x, k_, v_)
+        return x
+
+    call = lambda x: L.fa4_nvfp4_fwd_varlen(ctypes.byref(p), ctypes.byref(x), None)
+    assert call(varlen(cu_seqlens_k=None)) == -1                       # NULL offsets
+    assert call(varlen(struct_size=8)) == -7
+    assert call(varlen(max_seqlen_k=300)) == -2                        # longer than the pack
+    assert call(varlen(reserved=1)) == -2 and call(varlen(reserved2=1)) == -2
+    assert call(varlen(total_v=224)) == -2                             # a V length without V offsets
+    assert call(varlen(cu_seqlens_v=0x3000, total_v=100)) == -2        # V shorter than the keys
+    assert call(varlen(cu_seqlens_v=0x3000, total_v=230)) == -2        # not a multiple of 32
+    assert call(varlen(window_left=-2)) == -2
+    p.variant = 2                                                      # the 128-key kernel has no packed form
+    assert call(varlen()) == -5
+
+
+def test_padded_key_offsets_of_a_packed_batch():
+    cu = torch.tensor([0, 70, 199, 200, 533, 533], dtype=torch.int32)
+    assert fa.padded_key_offsets(cu).tolist() == [0, 96, 256, 288, 640, 640]
+    assert fa.padded_key_offsets(torch.tensor([0, 64, 128], dtype=torch.int32)).tolist() == [0, 64, 128]
