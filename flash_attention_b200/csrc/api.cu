@@ -423,15 +423,16 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
     dp.num_splits = num_splits;
     dp.o_partial = kp.o_partial;
     dp.lse_partial = kp.lse_partial;
-    auto launch_dec = [&](auto kernel) -> int {
-      if (int e = ensure_smem(kernel, dec::kSmemRequest)) return e;
-      kernel<<<dim3((unsigned)num_splits, (unsigned)p->Hkv, (unsigned)p->B), dec::kThreads, dec::kSmemRequest,
-               stream>>>(tm_k, tm_v, kp, dp);
+    auto launch_dec = [&](auto kernel, uint32_t smem) -> int {
+      if (int e = ensure_smem(kernel, smem)) return e;
+      kernel<<<dim3((unsigned)num_splits, (unsigned)p->Hkv, (unsigned)p->B), dec::kThreads, smem, stream>>>(
+          tm_k, tm_v, kp, dp);
       return 0;
     };
-    const int rc = dec_rows <= 4 ? launch_dec(attn_decode_kernel<4>)
-                                 : (dec_rows <= 8 ? launch_dec(attn_decode_kernel<8>)
-                                                  : launch_dec(attn_decode_kernel<16>));
+    const int rc = dec_rows <= 4    ? launch_dec(attn_decode_kernel<4>, dec::kSmemRequest)
+                   : dec_rows <= 8  ? launch_dec(attn_decode_kernel<8>, dec::kSmemRequest)
+                   : dec_rows <= 16 ? launch_dec(attn_decode_kernel<16>, dec::kSmemRequest)
+                                    : launch_dec(attn_decode_kernel<32>, dec::kSmemRequestWide);
     if (rc != 0) return rc;
   } else {
     // persistent: one CTA per SM walks the tile list

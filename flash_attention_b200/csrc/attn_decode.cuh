@@ -4,14 +4,15 @@
 // token per sequence 127 of them are padding and the per-block latency chain (about 3000 clocks,
 // two blocks in flight) sets the pace: 0.7 TB/s of K/V.  Here the products are transposed, as
 // decode kernels usually do: the 128 KEYS of a block sit on the lanes and the query rows -- the
-// Sq x (query heads per kv head) rows that share this kv head, at most 16 -- on the N side:
+// Sq x (query heads per kv head) rows that share this kv head, at most 32 -- on the N side
+// (N = 16, or 32 for more than 16 rows):
 //
-//   S^T (128 keys x 16 rows)  = K (A operand, the tile as it is loaded) . Q^T (B operand)
-//   O^T (128 dv   x 16 rows) += V^T (A operand: V is stored key-contiguous, i.e. already as the
-//                                    K-major (dv, keys) matrix) . P^T (B operand)
+//   S^T (128 keys x N rows)  = K (A operand, the tile as it is loaded) . Q^T (B operand)
+//   O^T (128 dv   x N rows) += V^T (A operand: V is stored key-contiguous, i.e. already as the
+//                                   K-major (dv, keys) matrix) . P^T (B operand)
 //
-// so no lane is wasted, an S^T buffer is 16 tensor-memory columns (four blocks in flight cost 64),
-// and a softmax thread owns ONE key with its <= 16 scores.  The softmax statistics run across
+// so no lane is wasted, an S^T buffer is N tensor-memory columns, and tensor memory hands a
+// softmax thread ONE key with its <= N scores.  The softmax statistics run across
 // lanes: row maxima and sums by warp shuffles plus one exchange through shared memory per block,
 // the 16-key block maxima of the P scales by four shuffle steps.  P is quantised exactly as in
 // the prefill kernels (e2m1, power-of-two ue4m3 scale per row and 16 keys, lazy reference).
@@ -32,24 +33,25 @@ namespace fa4 {
 namespace dec {
 
 constexpr int kThreads = 224;
-// Three of everything: 65 KB of shared memory and 128 tensor-memory columns per CTA, so that THREE
-// CTAs share an SM -- the softmax chain of a block is latency-bound and one CTA has one in flight.
+// Three of everything: 70 KB of shared memory and 128 tensor-memory columns per CTA (256 in the
+// 32-row form), so that THREE CTAs share an SM (two in the 32-row form).
 constexpr int kStages = 3;   // K and V tiles in flight
-constexpr int kSBufs = 3;    // S^T buffers (16 columns each)
-constexpr int kPSlots = 3;   // P^T tiles (16 rows x 64 bytes) and their scale chunks
-constexpr int kMaxRows = 16; // query rows per kv head: Sq * group
+constexpr int kSBufs = 3;    // S^T buffers (N columns each)
+constexpr int kPSlots = 3;   // P^T tiles (N rows x 64 bytes) and their scale chunks
+constexpr int kMaxRows = 32; // query rows per kv head: Sq * group
 
 // shared memory
 constexpr uint32_t kOffK = 0;
 constexpr uint32_t kOffV = kOffK + kStages * kTileBytes;
 constexpr uint32_t kOffSFK = kOffV + kStages * kTileBytes;
 constexpr uint32_t kOffSFV = kOffSFK + kStages * kSfBytes;
-constexpr uint32_t kOffQ = kOffSFV + kStages * kSfBytes;   // 16 rows x 64 bytes, 64-byte swizzle
-constexpr uint32_t kOffSFQ = kOffQ + 1024;                 // two 512-byte chunks
-constexpr uint32_t kOffP = kOffSFQ + 1024;                 // kPSlots x 1024
-constexpr uint32_t kOffSFP = kOffP + kPSlots * 1024;       // kPSlots x 2 chunks x 512
-constexpr uint32_t kOffRed = kOffSFP + kPSlots * 1024;     // 2 x 4 warps x 16 floats
-constexpr uint32_t kOffBar = kOffRed + 2 * 4 * 16 * 4;
+constexpr uint32_t kQBytes = kMaxRows * 64;                // Q^T / P^T operand: up to 32 rows x 64 bytes
+constexpr uint32_t kOffQ = kOffSFV + kStages * kSfBytes;   // rows x 64 bytes, 64-byte swizzle
+constexpr uint32_t kOffSFQ = kOffQ + kQBytes;              // two 512-byte chunks
+constexpr uint32_t kOffP = kOffSFQ + 1024;                 // kPSlots x kQBytes
+constexpr uint32_t kOffSFP = kOffP + kPSlots * kQBytes;    // kPSlots x 2 chunks x 512
+constexpr uint32_t kOffRed = kOffSFP + kPSlots * 1024;     // 2 x 4 warps x 32 floats
+constexpr uint32_t kOffBar = kOffRed + 2 * 4 * kMaxRows * 4;
 struct Bars {
   uint32_t base;
   static constexpr uint32_t kKFull = 0, kVFull = kKFull + kStages, kKFree = kVFull + kStages,
@@ -62,13 +64,22 @@ struct Bars {
 };
 constexpr uint32_t kOffMisc = kOffBar + 8 * Bars::kCount;
 constexpr uint32_t kSmemRequest = kOffMisc + 16 + 1024;
+// The 32-row form allocates 256 tensor-memory columns: its request is padded so that only two CTAs
+// fit an SM (a third would sit inside tcgen05.alloc until one of them ends).
+constexpr uint32_t kSmemRequestWide = 100 * 1024;
+static_assert(kSmemRequest <= kSmemRequestWide && 3 * kSmemRequest <= 227 * 1024, "decode kernel shared memory");
 
-// tensor memory (128 columns allocated): S^T buffers, O^T, scale factors.  The K / V / P scale
-// slots alternate between two copies: the copy and the product that reads it are issued by one
-// thread to the in-order tensor pipe, the second copy keeps a copy from racing the product before.
-constexpr uint32_t kDTmemCols = 128;
-constexpr uint32_t kDTmS = 0 /* 3 x 16 */, kDTmO = 48, kDTmSFQ = 64, kDTmSFK = 72 /* 2 x 8 */,
-                   kDTmSFV = 88 /* 2 x 8 */, kDTmSFP = 104 /* 2 x 8 */;
+// tensor memory of the form with N columns per operand (N = 16: 128 columns allocated, N = 32:
+// 256): S^T buffers, O^T, scale factors.  The K / V / P scale slots alternate between two copies:
+// the copy and the product that reads it are issued by one thread to the in-order tensor pipe, the
+// second copy keeps a copy from racing the product before.
+template <int kN>
+struct Tm {
+  static constexpr uint32_t kCols = kN == 16 ? 128 : 256;
+  static constexpr uint32_t kS = 0 /* 3 x N */, kO = 3 * kN, kSFQ = 4 * kN, kSFK = kSFQ + 8 /* 2 x 8 */,
+                            kSFV = kSFK + 16 /* 2 x 8 */, kSFP = kSFV + 16 /* 2 x 8 */;
+  static_assert(kSFP + 16 <= kCols, "tensor-memory map of the decode kernel");
+};
 
 enum Site { kDKFull = 80, kDVFull, kDKFree, kDVFree, kDSFull, kDSFree, kDPFull, kDPvDone, kDQReady, kDSync };
 
@@ -118,8 +129,10 @@ __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t* r) {
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
                  : "r"(taddr)
                  : "memory");
-  } else {
+  } else if constexpr (kN == 16) {
     tmem_ld16(taddr, r);
+  } else {
+    tmem_ld32(taddr, r);
   }
 }
 template <int kN>
@@ -133,12 +146,14 @@ __device__ __forceinline__ void tmem_st_cols(uint32_t taddr, const uint32_t* r) 
                  ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
                  "r"(taddr)
                  : "memory");
-  } else {
+  } else if constexpr (kN == 16) {
     tmem_st16(taddr, r);
+  } else {
+    tmem_st32(taddr, r);
   }
 }
 
-// T x T transpose inside every group of T neighbouring lanes (T = 4, 8, 16): before, lane i of a
+// T x T transpose inside every group of T neighbouring lanes (T = 4, 8, 16, 32): before, lane i of a
 // group holds x[0..T) = its own column; after, x[j] is what lane j of the group held in x[i].
 // log2(T) butterfly rounds of T / 2 shuffles.
 template <int T>
@@ -183,11 +198,11 @@ struct DecodeParams {
   float* lse_partial;    // (splits, B, Hq, Sq) fp32
 };
 
-// kR: query rows the softmax code is unrolled for (4, 8 or 16 >= Sq * group).  The row loops are
-// fully unrolled, and sixteen rows of them no longer fit the instruction cache (measured: 10 000
-// clocks per block, instruction-fetch bound), so the common decode shapes get the short forms.
+// kR: query rows the softmax code is built for (4, 8, 16 or 32 >= Sq * group): the size of the
+// lane-group transpose and the number of keys a thread owns afterwards.  N (the MMA's N, the
+// columns of an S^T buffer) is 16 up to sixteen rows and 32 above.
 template <int kR>
-__global__ void __launch_bounds__(dec::kThreads, 3)
+__global__ void __launch_bounds__(dec::kThreads, kR <= 16 ? 3 : 2)
 attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                    const KernelParams p, const DecodeParams d) {
   using namespace dec;
@@ -197,28 +212,31 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   const Bars bars(base + kOffBar);
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + kOffMisc);
   volatile uint32_t* s_abort = reinterpret_cast<volatile uint32_t*>(gbase + kOffMisc + 4);
-  volatile float* s_red = reinterpret_cast<volatile float*>(gbase + kOffRed);  // [2][4][16]
+  volatile float* s_red = reinterpret_cast<volatile float*>(gbase + kOffRed);  // [2][4][32]
+  constexpr int kN = kR <= 16 ? 16 : 32;
+  using TM = Tm<kN>;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
   const WaitCtx wc{s_abort, p.status, p.budget_ns, p.epoch};
-  const int R = p.Sq * p.group;  // live query rows (<= 16)
+  const int R = p.Sq * p.group;  // live query rows (<= kR)
 
   // The query rows and their scale words go to registers first thing: their latency (a trip to
   // HBM while every CTA of the grid starts its K / V stream) then overlaps the set-up below
-  // instead of following it.  Threads 0-63: row tid / 4, 16-byte chunk tid % 4; threads 64-95: row
-  // (tid - 64) / 2, the scale word of 64-element step tid % 2.
+  // instead of following it.  Threads 0-127: row tid / 4, 16-byte chunk tid % 4; threads 0-63
+  // also: row tid / 2, the scale word of 64-element step tid % 2.
   uint4 q_pref = make_uint4(0u, 0u, 0u, 0u);
   uint32_t qsf_pref = 0u;
-  if (tid < 64) {
+  if (tid < 128) {
     const int r = tid >> 2, ch = tid & 3;
     if (r < R) {
       const int s = r / p.group, h = hk * p.group + r % p.group;
       q_pref = *reinterpret_cast<const uint4*>(d.q + b * d.q_stride_b + s * d.q_stride_s + h * d.q_stride_h +
                                                ch * 16);
     }
-  } else if (tid < 64 + 32) {
-    const int r = (tid - 64) >> 1, ks = tid & 1;
+  }
+  if (tid < 64) {
+    const int r = tid >> 1, ks = tid & 1;
     if (r < R) {
       const int s = r / p.group, h = hk * p.group + r % p.group;
       const uint8_t* chunk = d.q_sf + b * p.qsf_stride_b + h * p.qsf_stride_h + ((int64_t)(s / 128) * 2 + ks) * 512;
@@ -260,7 +278,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   if (warp == 4 && lane == 0) tma_prefetch_desc(&tm_k);
   if (warp == 6 && lane == 0) tma_prefetch_desc(&tm_v);
   if (warp == 5) {
-    tmem_alloc(base + kOffMisc, kDTmemCols);
+    tmem_alloc(base + kOffMisc, TM::kCols);
     tmem_relinquish();
   }
   tc_fence_before_sync();
@@ -270,7 +288,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   // this grid still runs (they wait for its completion before they read the partials)
   asm volatile("griddepcontrol.launch_dependents;");
   const uint32_t tmem = *tmem_slot;
-  constexpr uint32_t idesc = make_idesc_nvf4(128, 16);
+  constexpr uint32_t idesc = make_idesc_nvf4(128, kN);
   bool ok = true;
 
   if (warp == 4 || warp == 6) {
@@ -327,7 +345,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         tc_fence_after_sync();
 #pragma unroll
         for (int ks = 0; ks < 2; ++ks) {
-          tc_cp_sf(tmem + kDTmSFQ + 4 * ks, base + kOffSFQ + 512 * ks);
+          tc_cp_sf(tmem + TM::kSFQ + 4 * ks, base + kOffSFQ + 512 * ks);
           dq[ks] = make_desc_sw64(base + kOffQ + 32 * ks);
         }
       }
@@ -342,14 +360,14 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
             if (!ok) break;
           }
           tc_fence_after_sync();
-          const uint32_t sfk = tmem + kDTmSFK + 8 * (li & 1);
+          const uint32_t sfk = tmem + TM::kSFK + 8 * (li & 1);
           const uint32_t kt = base + kOffK + st * kTileBytes, ksf = base + kOffSFK + st * kSfBytes;
 #pragma unroll
           for (int ks = 0; ks < 2; ++ks) tc_cp_sf(sfk + 4 * ks, ksf + 512 * ks);
 #pragma unroll
           for (int ks = 0; ks < 2; ++ks) {
-            mma_nvf4(tmem + kDTmS + 16 * buf, make_desc_sw64(kt + 32 * ks), dq[ks], idesc, sfk + 4 * ks,
-                     tmem + kDTmSFQ + 4 * ks, ks > 0 ? 1u : 0u);
+            mma_nvf4(tmem + TM::kS + kN * buf, make_desc_sw64(kt + 32 * ks), dq[ks], idesc, sfk + 4 * ks,
+                     tmem + TM::kSFQ + 4 * ks, ks > 0 ? 1u : 0u);
           }
           tc_commit(bars.at(Bars::kSFull + buf));
           tc_commit(bars.at(Bars::kKFree + st));
@@ -362,9 +380,9 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
           ok = mbar_wait(bars.at(Bars::kPFull + slot), (li / kPSlots) & 1, wc, kDPFull);
           if (!ok) break;
           tc_fence_after_sync();
-          const uint32_t sfv = tmem + kDTmSFV + 8 * (li & 1), sfp = tmem + kDTmSFP + 8 * (li & 1);
+          const uint32_t sfv = tmem + TM::kSFV + 8 * (li & 1), sfp = tmem + TM::kSFP + 8 * (li & 1);
           const uint32_t vt = base + kOffV + st * kTileBytes, vsf = base + kOffSFV + st * kSfBytes;
-          const uint32_t pt = base + kOffP + slot * 1024, psf = base + kOffSFP + slot * 1024;
+          const uint32_t pt = base + kOffP + slot * kQBytes, psf = base + kOffSFP + slot * 1024;
 #pragma unroll
           for (int ks = 0; ks < 2; ++ks) {
             tc_cp_sf(sfv + 4 * ks, vsf + 512 * ks);
@@ -372,7 +390,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
           }
 #pragma unroll
           for (int ks = 0; ks < 2; ++ks) {
-            mma_nvf4(tmem + kDTmO, make_desc_sw64(vt + 32 * ks), make_desc_sw64(pt + 32 * ks), idesc,
+            mma_nvf4(tmem + TM::kO, make_desc_sw64(vt + 32 * ks), make_desc_sw64(pt + 32 * ks), idesc,
                      sfv + 4 * ks, sfp + 4 * ks, (li > 0 || ks > 0) ? 1u : 0u);
           }
           tc_commit(bars.at(Bars::kPvDone + slot));
@@ -395,19 +413,20 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   ok = __all_sync(0xffffffffu, mbar_wait(bars.at(Bars::kSync), sync_phase & 1, wc, kDSync));     \
   sync_phase += 1;
 
-    // ---- set-up: Q^T operand (16 rows x 64 bytes, rows past R zero), its scale chunks, zeroed
+    // ---- set-up: Q^T operand (rows x 64 bytes, rows past R zero), its scale chunks, zeroed
     //      P^T tiles and scale chunks (rows past R are never written again)
-    for (uint32_t i = tid; i < (kPSlots * 2048u + 2048u) / 16; i += 128) {
+    for (uint32_t i = tid; i < (kOffRed - kOffQ) / 16; i += 128) {
       *reinterpret_cast<uint4*>(gbase + kOffQ + i * 16) = make_uint4(0u, 0u, 0u, 0u);  // Q, SFQ, P, SFP are contiguous
     }
     ok = true;
     FA4_DEC_SYNC()
-    if (ok && tid < 64) {
+    if (ok) {
       const int r = tid >> 2, ch = tid & 3;
       if (r < R) *reinterpret_cast<uint4*>(gbase + kOffQ + sw64_offset(r, ch)) = q_pref;
-    } else if (ok && tid < 64 + 32) {
+    }
+    if (ok && tid < 64) {
       // scale bytes of row r: two words (one per 64-element step) of the tiled layout
-      const int r = (tid - 64) >> 1, ks = tid & 1;
+      const int r = tid >> 1, ks = tid & 1;
       if (r < R) *reinterpret_cast<uint32_t*>(gbase + kOffSFQ + 512 * ks + r * 16) = qsf_pref;
     }
     fence_proxy_async_smem();
@@ -435,7 +454,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       if (!ok) break;
       tc_fence_after_sync();
       float x[kR];
-      tmem_ld_cols<kR>(lane_addr + kDTmS + 16 * buf, reinterpret_cast<uint32_t*>(x));
+      tmem_ld_cols<kR>(lane_addr + TM::kS + kN * buf, reinterpret_cast<uint32_t*>(x));
       tc_wait_ld();
       tc_fence_before_sync();
       mbar_arrive(bars.at(Bars::kSFree + buf));
@@ -443,23 +462,36 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       // (key = lane, all rows) -> (row = lane % kR, kR keys): x[j] = score of key key_in_blk + j
       lane_group_transpose<kR>(x, lane);
       const int key0 = nb * kBlockN + key_in_blk;
-      float bm = kNegInf;
+      // kB 16-key blocks per thread: one (shared with neighbouring lanes) up to 16 rows, two of
+      // its own in the 32-row form, where a thread owns all 32 keys of its warp
+      constexpr int kB = kR <= 16 ? 1 : 2, kPer = kR / kB;
+      float bm[kB];
 #pragma unroll
-      for (int j = 0; j < kR; ++j) {
-        x[j] = (key0 + j <= lim) ? x[j] : kNegInf;
-        bm = fmaxf(bm, x[j]);
+      for (int q = 0; q < kB; ++q) {
+        bm[q] = kNegInf;
+#pragma unroll
+        for (int j = 0; j < kPer; ++j) {
+          x[q * kPer + j] = (key0 + q * kPer + j <= lim) ? x[q * kPer + j] : kNegInf;
+          bm[q] = fmaxf(bm[q], x[q * kPer + j]);
+        }
       }
       // maximum of the row's 16-key block (kept for the P scale), then of the warp's 32 keys
+      float wm;
+      if constexpr (kB == 1) {
 #pragma unroll
-      for (int o = kR; o < 16; o <<= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, o));
-      const float wm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 16));
-      volatile float* red = s_red + (li & 1) * 64;
-      if (lane < kR) red[warp * 16 + lane] = wm;
+        for (int o = kR; o < 16; o <<= 1) bm[0] = fmaxf(bm[0], __shfl_xor_sync(0xffffffffu, bm[0], o));
+        wm = fmaxf(bm[0], __shfl_xor_sync(0xffffffffu, bm[0], 16));
+      } else {
+        wm = fmaxf(bm[0], bm[kB - 1]);
+      }
+      volatile float* red = s_red + (li & 1) * (4 * kMaxRows);
+      if (lane < kR) red[warp * kMaxRows + lane] = wm;
       FA4_DEC_SYNC()
       if (!ok) break;
 
       // reference maximum of the row (CTA-uniform per row: every warp computes the same value)
-      const float m_loc = fmaxf(fmaxf(red[my_row], red[16 + my_row]), fmaxf(red[32 + my_row], red[48 + my_row]));
+      const float m_loc = fmaxf(fmaxf(red[my_row], red[kMaxRows + my_row]),
+                                fmaxf(red[2 * kMaxRows + my_row], red[3 * kMaxRows + my_row]));
       const float m_new = next_reference(m_ref, m_loc, p.sl2);
       float fac = 1.f;
       bool moved_row = false;
@@ -478,35 +510,52 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         if (!ok) break;
       }
       {
-        float noff;
-        uint32_t ue;
-        block_exponent1(bm, m_ref, p.sl2, noff, ue);
-        float pv[kR], psum = 0.f;
+        float noff[kB];
+        uint32_t ue[kB];
+        float pv[kR];
 #pragma unroll
-        for (int j = 0; j < kR; ++j) {
-          pv[j] = ex2_approx(fmaf(x[j], p.sl2, noff));
-          psum += pv[j];
+        for (int q = 0; q < kB; ++q) {
+          block_exponent1(bm[q], m_ref, p.sl2, noff[q], ue[q]);
+          float psum = 0.f;
+#pragma unroll
+          for (int j = 0; j < kPer; ++j) {
+            pv[q * kPer + j] = ex2_approx(fmaf(x[q * kPer + j], p.sl2, noff[q]));
+            psum += pv[q * kPer + j];
+          }
+          l_sum = fmaf(psum, __uint_as_float(ue[q] << 23), l_sum);
         }
-        l_sum = fmaf(psum, __uint_as_float(ue << 23), l_sum);
         if (my_row < R) {   // rows past R stay zero (written once at set-up)
           // kR keys = kR / 2 bytes of the row's 64, inside one 16-byte chunk of the swizzled tile
           const uint32_t col = static_cast<uint32_t>(key_in_blk) >> 1;
-          uint8_t* dst = gbase + kOffP + slot * 1024 + sw64_offset(my_row, col >> 4) + (col & 15);
+          uint8_t* dst = gbase + kOffP + slot * kQBytes + sw64_offset(my_row, col >> 4) + (col & 15);
+          // scale byte of 16-key block blk = key_in_blk / 16: chunk blk / 4, the row's word, byte blk % 4
+          uint8_t* sf_dst = gbase + kOffSFP + slot * 1024 + 512 * (key_in_blk >> 6) + my_row * 16 +
+                            ((key_in_blk >> 4) & 3);
           if constexpr (kR == 4) {
             *reinterpret_cast<uint16_t*>(dst) =
                 static_cast<uint16_t>(pack2_e2m1(pv[0], pv[1]) | (pack2_e2m1(pv[2], pv[3]) << 8));
           } else if constexpr (kR == 8) {
             *reinterpret_cast<uint32_t*>(dst) = pack8_e2m1(pv[0], pv[1], pv[2], pv[3], pv[4], pv[5], pv[6], pv[7]);
-          } else {
+          } else if constexpr (kR == 16) {
             *reinterpret_cast<uint2*>(dst) =
                 make_uint2(pack8_e2m1(pv[0], pv[1], pv[2], pv[3], pv[4], pv[5], pv[6], pv[7]),
                            pack8_e2m1(pv[8 % kR], pv[9 % kR], pv[10 % kR], pv[11 % kR], pv[12 % kR], pv[13 % kR],
                                       pv[14 % kR], pv[15 % kR]));
+          } else {
+            uint32_t w[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              w[c] = pack8_e2m1(pv[(8 * c) % kR], pv[(8 * c + 1) % kR], pv[(8 * c + 2) % kR], pv[(8 * c + 3) % kR],
+                                pv[(8 * c + 4) % kR], pv[(8 * c + 5) % kR], pv[(8 * c + 6) % kR], pv[(8 * c + 7) % kR]);
+            }
+            *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
           }
-          if ((key_in_blk & 15) == 0) {
-            const int blk = key_in_blk >> 4;  // 16-key block inside the 128 keys
-            gbase[kOffSFP + slot * 1024 + 512 * (blk >> 2) + my_row * 16 + (blk & 3)] =
-                static_cast<uint8_t>((ue - 0x78u) << 3);
+          if constexpr (kB == 2) {
+            // the thread's two blocks are neighbours in the scale word of its row
+            *reinterpret_cast<uint16_t*>(sf_dst) =
+                static_cast<uint16_t>(((ue[0] - 0x78u) << 3) | (((ue[kB - 1] - 0x78u) << 3) << 8));
+          } else if ((key_in_blk & 15) == 0) {
+            *sf_dst = static_cast<uint8_t>((ue[0] - 0x78u) << 3);
           }
         }
       }
@@ -519,11 +568,11 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         if (!ok) break;
         tc_fence_after_sync();
         float o[kR];
-        tmem_ld_cols<kR>(lane_addr + kDTmO, reinterpret_cast<uint32_t*>(o));
+        tmem_ld_cols<kR>(lane_addr + TM::kO, reinterpret_cast<uint32_t*>(o));
         tc_wait_ld();
 #pragma unroll
         for (int r = 0; r < kR; ++r) o[r] *= __shfl_sync(0xffffffffu, fac, r);
-        tmem_st_cols<kR>(lane_addr + kDTmO, reinterpret_cast<const uint32_t*>(o));
+        tmem_st_cols<kR>(lane_addr + TM::kO, reinterpret_cast<const uint32_t*>(o));
         tc_wait_st();
       }
       fence_proxy_async_smem();
@@ -533,15 +582,15 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
 
     // ---- epilogue: row sums over the 128 key lanes, then thread = dv lane of O^T --------------
     if (ok) {
-      volatile float* red = s_red + (n & 1) * 64;
+      volatile float* red = s_red + (n & 1) * (4 * kMaxRows);
       float v = l_sum;   // this thread's share of its row; the lanes of one row are kR apart
 #pragma unroll
       for (int o = kR; o < 32; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-      if (lane < kR) red[warp * 16 + lane] = v;
+      if (lane < kR) red[warp * kMaxRows + lane] = v;
       FA4_DEC_SYNC()
     }
     if (ok) {
-      volatile float* red = s_red + (n & 1) * 64;
+      volatile float* red = s_red + (n & 1) * (4 * kMaxRows);
       float o[kR];
 #pragma unroll
       for (int r = 0; r < kR; ++r) o[r] = 0.f;
@@ -550,7 +599,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
                                                ((n - 1) / kPSlots) & 1, wc, kDPvDone));
         if (ok) {
           tc_fence_after_sync();
-          tmem_ld_cols<kR>(lane_addr + kDTmO, reinterpret_cast<uint32_t*>(o));
+          tmem_ld_cols<kR>(lane_addr + TM::kO, reinterpret_cast<uint32_t*>(o));
           tc_wait_ld();
         }
       }
@@ -559,7 +608,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         for (int r = 0; r < kR; ++r) {
           if (r < R) {
             // fixed order over the four warps: the sum of a row does not depend on timing
-            const float l_tot = ((red[r] + red[16 + r]) + red[32 + r]) + red[48 + r];
+            const float l_tot = ((red[r] + red[kMaxRows + r]) + red[2 * kMaxRows + r]) + red[3 * kMaxRows + r];
             const int s = r / p.group, h = hk * p.group + r % p.group;
             const float scale = (l_tot > 0.f && n > 0) ? p.out_scale / l_tot : 0.f;
             d.o_partial[((((int64_t)split * p.B + b) * p.Sq + s) * p.Hq + h) * 128 + tid] = o[r] * scale;
@@ -576,7 +625,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
 
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 5) tmem_dealloc(tmem, dec::kDTmemCols);
+  if (warp == 5) tmem_dealloc(tmem, TM::kCols);
 }
 
 }  // namespace fa4

@@ -115,7 +115,7 @@ def flash_attn_fp4_func(
     ``num_splits``: 1 = one pass over K/V per query tile; k > 1 = split-KV with a combine kernel
     (the reference's ``num_splits``, interface.py:494-510), for short Sq against long Sk;
     0 = choose (split only when the query tiles alone leave most SMs idle).  Decode and append
-    shapes (D = Dv = 128, Sq * Hq / Hkv <= 16, no window / sink / softcap) run the transposed
+    shapes (D = Dv = 128, Sq * Hq / Hkv <= 32, no window / sink / softcap) run the transposed
     decode kernel (``VARIANT_DECODE``: keys on the tile's lanes, grid = splits x Hkv x B); there
     ``num_splits=0`` is what a serving loop wants (about two CTAs per SM).
 
@@ -235,10 +235,10 @@ def flash_attn_fp4_func(
     p.causal = 1 if causal else 0
     # A handful of query rows per kv head (decode, append): the transposed kernel, which always
     # splits the keys over CTAs and merges with the combine kernel.
-    decode_ok = (D == 128 and Dv == 128 and Sq * (Hq // Hkv) <= 16 and win_left is None
+    decode_ok = (D == 128 and Dv == 128 and Sq * (Hq // Hkv) <= 32 and win_left is None
                  and (win_right is None or win_right == 0) and learnable_sink is None and not softcap)
     if variant == VARIANT_DECODE and not decode_ok:
-        raise NotImplementedError("the decode kernel takes D = Dv = 128, Sq * (Hq / Hkv) <= 16, no window / "
+        raise NotImplementedError("the decode kernel takes D = Dv = 128, Sq * (Hq / Hkv) <= 32, no window / "
                                   "sink / softcap")
     if variant == VARIANT_AUTO and decode_ok:
         variant = VARIANT_DECODE

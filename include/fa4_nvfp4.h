@@ -88,7 +88,7 @@ enum {
                              windows, sinks, the soft cap and KV-cache views, but no split-KV
                              (-FA4_E_SHAPE) */
   FA4_VARIANT_DECODE = 4  /* transposed products for a handful of query rows: keys on the tile's
-                             lanes, the Sq * (Hq / Hkv) <= 16 query rows of a kv head on the N
+                             lanes, the Sq * (Hq / Hkv) <= 32 query rows of a kv head on the N
                              side; D = Dv = 128, causal or unmasked, seqused_k / page_table allowed;
                              through fa4_nvfp4_fwd_ex with num_splits >= 1 and the split-KV
                              workspace (grid = splits x Hkv x B) */

@@ -53,7 +53,7 @@ def kernel_model(D, num_splits=1, window=(None, None), sink=None, variant=0, sof
     64-key one, 4 the decode kernel's."""
     plain = num_splits == 1
     # decode / append shapes: the transposed kernel, 128-key steps upwards, any number of splits
-    decode_ok = (D == 128 and rows is not None and rows <= 16 and window in ((None, None), (None, 0))
+    decode_ok = (D == 128 and rows is not None and rows <= 32 and window in ((None, None), (None, 0))
                  and sink is None and not softcap)
     if variant == 4 or (variant == 0 and decode_ok):
         return {"step_keys": 128, "ascending": True}

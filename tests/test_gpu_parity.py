@@ -632,9 +632,13 @@ def test_softcap_parity(cuda_device, case):
     ("three_rows_of_four", 1, 3, 416, 2, 2, True, 2),
     ("six_rows_of_eight_noncausal", 2, 3, 300, 4, 2, False, 1),
     ("twelve_rows_of_sixteen", 1, 3, 1000, 8, 2, True, 3),
+    # more than sixteen rows: the 32-row form (N = 32), a thread owns a row with all 32 keys of its warp
+    ("thirty_two_rows", 2, 8, 1200, 8, 2, True, 3),
+    ("twenty_four_rows_of_thirty_two_noncausal", 1, 3, 700, 8, 1, False, 2),
+    ("seventeen_rows_mha", 1, 17, 400, 2, 2, True, 1),
 ], ids=lambda c: c[0])
 def test_decode_kernel_parity(cuda_device, case):
-    """The transposed decode kernel (keys on the lanes, the Sq * Hq / Hkv <= 16 query rows of a kv
+    """The transposed decode kernel (keys on the lanes, the Sq * Hq / Hkv <= 32 query rows of a kv
     head on the N side), which the automatic choice runs for these shapes: against the oracle's
     model of it (128-key steps upwards, contiguous shares of the blocks per split) at the usual
     tolerances, and deterministic."""
@@ -653,10 +657,10 @@ def test_decode_kernel_parity(cuda_device, case):
 
 
 def test_decode_kernel_refuses_other_shapes(cuda_device):
-    q, k, v = make_qkv(1, 17, 256, 2, 2, 128, seed=1, device=cuda_device)
+    q, k, v = make_qkv(1, 33, 256, 2, 2, 128, seed=1, device=cuda_device)
     Q, K, V = fa.quantize_qkv(q, k, v)
     with pytest.raises(NotImplementedError):
-        run(Q, K, V, True, fa.VARIANT_DECODE)                      # 17 rows
+        run(Q, K, V, True, fa.VARIANT_DECODE)                      # 33 rows
     q, k, v = make_qkv(1, 2, 256, 2, 2, 128, seed=1, device=cuda_device)
     Q, K, V = fa.quantize_qkv(q, k, v)
     for kw in ({"window_size": (64, 0)}, {"softcap": 2.0}, {"learnable_sink": torch.zeros(2)}):
@@ -682,7 +686,7 @@ def test_kv_cache_seqused_and_page_table(cuda_device, case):
     Q, K, V = fa.quantize_qkv(q, k, v)
     su = torch.tensor(used, dtype=torch.int32, device=cuda_device)
     # what the automatic choice runs for this shape: the decode kernel for a handful of rows
-    model = (fa.VARIANT_DECODE if (D == 128 and Sq * (Hq // Hkv) <= 16)
+    model = (fa.VARIANT_DECODE if (D == 128 and Sq * (Hq // Hkv) <= 32)
              else (fa.VARIANT_WS64 if splits == 1 else fa.VARIANT_WS))
     out, lse = run(Q, K, V, causal, seqused_k=su, num_splits=splits)
     for b, sk in enumerate(used):
