@@ -12,15 +12,18 @@
 //                                   K-major (dv, keys) matrix) . P^T (B operand)
 //
 // so no lane is wasted, an S^T buffer is N tensor-memory columns, and tensor memory hands a
-// softmax thread ONE key with its <= N scores.  The softmax statistics run across
-// lanes: row maxima and sums by warp shuffles plus one exchange through shared memory per block,
-// the 16-key block maxima of the P scales by four shuffle steps.  P is quantised exactly as in
-// the prefill kernels (e2m1, power-of-two ue4m3 scale per row and 16 keys, lazy reference).
+// softmax thread ONE key with its <= N scores.  The warp transposes that within groups of `rows`
+// lanes, after which a thread owns one query ROW with `rows` neighbouring keys: the per-row work
+// (mask limit, reference maximum, block exponent, running sum) is scalar per thread; block and
+// warp maxima take zero to three shuffles, the CTA maximum one exchange through shared memory per
+// block.  P is quantised exactly as in the prefill kernels (e2m1, power-of-two ue4m3 scale per
+// row and 16 keys, lazy reference).
 //
 // One CTA = one (split, kv head, batch entry): a contiguous share of the entry's 128-key blocks,
 // visited in ascending order; it writes a normalised fp32 partial O and a partial LSE for
 // combine_splits_kernel, like the split-KV path of attn_ws.cuh.  Grid = (splits, Hkv, B).
-//   warps 0-3  softmax / correction / epilogue (thread = key lane, later = dv lane)
+//   warps 0-3  softmax / correction / epilogue (thread = key lane, after the transpose a row; in the
+//              correction and the epilogue a dv lane)
 //   warp 4     TMA producer of K (ring of three tiles, through the page table if there is one)
 //   warp 5     MMA issuer (owns tensor memory)
 //   warp 6     TMA producer of V (its own ring, independent of K's)
