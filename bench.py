@@ -571,11 +571,26 @@ def run_gpu_arm(args, wl, rank, local_rank, world):
         dist.destroy_process_group()
 
 
+def kernel_source_hash():
+    """SHA-256 of the CUDA sources with `//` comments and blank lines removed: what identifies the
+    code an ncu capture was taken on (a reworded comment does not make the capture stale)."""
+    import hashlib
+    import re
+    h = hashlib.sha256()
+    csrc = os.path.join(ROOT, "flash_attention_b200", "csrc")
+    for name in sorted(os.listdir(csrc)):
+        h.update(name.encode())
+        for line in open(os.path.join(csrc, name), encoding="utf-8"):
+            code = re.sub(r"\s*//.*$", "", line.rstrip("\n")).rstrip()
+            if code:
+                h.update(code.encode() + b"\n")
+    return h.hexdigest()
+
+
 def traffic_record(workload):
     """DRAM bytes per launch of the attention kernel from the ncu capture recorded in
     profiles/traffic.json, with the hash of the kernel sources it was captured on; a capture of
     other sources is reported as stale."""
-    import hashlib
     path = os.path.join(ROOT, "profiles", "traffic.json")
     try:
         rec = json.load(open(path)).get(workload)
@@ -583,21 +598,8 @@ def traffic_record(workload):
         rec = None
     if not rec:
         return {"traffic": None}
-    h = hashlib.sha256()
-    csrc = os.path.join(ROOT, "flash_attention_b200", "csrc")
-    for name in sorted(os.listdir(csrc)):
-        h.update(open(os.path.join(csrc, name), "rb").read())
     return {"traffic": rec["bytes"], "traffic_note": rec.get("note"),
-            "traffic_stale": rec.get("source_sha256") != h.hexdigest()}
-
-
-def kernel_source_hash():
-    import hashlib
-    h = hashlib.sha256()
-    csrc = os.path.join(ROOT, "flash_attention_b200", "csrc")
-    for name in sorted(os.listdir(csrc)):
-        h.update(open(os.path.join(csrc, name), "rb").read())
-    return h.hexdigest()
+            "traffic_stale": rec.get("source_sha256") != kernel_source_hash()}
 
 
 def run_sweep(args):
