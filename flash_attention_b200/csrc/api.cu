@@ -370,6 +370,10 @@ int launch_fwd(const fa4_nvfp4_params* p, int num_splits, void* workspace, uint6
   kp.o_stride_h = p->o_stride_h;
   kp.B = p->B; kp.Sq = p->Sq; kp.Sk = p->Sk; kp.Hq = p->Hq; kp.Hkv = p->Hkv;
   kp.group = p->Hq / p->Hkv;
+  kp.div_tiles_per_m = make_fastdiv((uint32_t)p->Hq * (uint32_t)p->B);
+  kp.div_hq = make_fastdiv((uint32_t)p->Hq);
+  kp.div_group = make_fastdiv((uint32_t)kp.group);
+  kp.div_splits = make_fastdiv((uint32_t)num_splits);
   kp.num_m_blocks = (p->Sq + kBlockM - 1) / kBlockM;
   kp.num_n_blocks = (p->Sk + kBlockN - 1) / kBlockN;
   kp.causal = win_right >= 0 ? 1 : 0;

@@ -374,7 +374,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
       // ========================================= TMA producer ===================================
       uint32_t issued_k = 0, issued_v = 0, issued_q = 0;
       FA4_FOR_EACH_TILE {
-        const Tile t = decode_tile<kWindow || kCache>(p, tile);
+        const Tile t = decode_tile<kWindow || kCache, kWindow || kCache>(p, tile);
         const int n = t.n_blocks;
         if (n == 0) continue;
         if (status_poisoned(p.status, p.epoch)) {
@@ -472,7 +472,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
     } else if (warp == kIssuerWarp && lane == 0) {
       // ========================================= QK^T issuer ====================================
       FA4_FOR_EACH_TILE {
-        const Tile t = decode_tile<kWindow || kCache>(p, tile);
+        const Tile t = decode_tile<kWindow || kCache, kWindow || kCache>(p, tile);
         const int n = t.n_blocks;
         if (n == 0) continue;
         const uint32_t qb = ti & 1;
@@ -524,7 +524,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
     } else if (warp == kPvIssuerWarp && lane == 0) {
       // ========================================= P V issuer =====================================
       FA4_FOR_EACH_TILE {
-        const Tile t = decode_tile<kWindow || kCache>(p, tile);
+        const Tile t = decode_tile<kWindow || kCache, kWindow || kCache>(p, tile);
         const int n = t.n_blocks;
         if (n == 0) continue;
         for (int i = 0; ok && i < n; ++i) {
@@ -569,7 +569,7 @@ attn_fwd_ws64_kernel(const __grid_constant__ CUtensorMap tm_q,
       // A stage's tensor-memory slot is free when its shared-memory stage is: the producer
       // reloads the stage only after the products that used it have completed.
       FA4_FOR_EACH_TILE {
-        const Tile t = decode_tile<kWindow || kCache>(p, tile);
+        const Tile t = decode_tile<kWindow || kCache, kWindow || kCache>(p, tile);
         const int n = t.n_blocks;
         if (n == 0) continue;
         for (int step = 0; ok && step < n + 2; ++step) {

@@ -164,6 +164,22 @@ __device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity,
   }
 }
 
+// Division by a divisor fixed at launch, as multiply-high + shift (dividends below 2^31).
+struct FastDiv {
+  uint32_t mul, shr;
+};
+inline FastDiv make_fastdiv(uint32_t d) {
+  FastDiv f{0u, 0u};
+  if (d > 1) {
+    while ((1u << f.shr) < d) ++f.shr;
+    f.mul = static_cast<uint32_t>((((1ull << f.shr) - d) << 32) / d + 1);
+  }
+  return f;
+}
+__device__ __forceinline__ int fast_div(int n, FastDiv f) {
+  return static_cast<int>((__umulhi(static_cast<uint32_t>(n), f.mul) + static_cast<uint32_t>(n)) >> f.shr);
+}
+
 // ---------------------------------------------------------------------------------------------
 // proxy / tcgen05 fences
 // ---------------------------------------------------------------------------------------------

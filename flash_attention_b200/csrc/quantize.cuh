@@ -16,22 +16,6 @@
 
 namespace fa4 {
 
-// Division by a divisor fixed at launch, as multiply-high + shift (dividends below 2^31).
-struct FastDiv {
-  uint32_t mul, shr;
-};
-inline FastDiv make_fastdiv(uint32_t d) {
-  FastDiv f{0u, 0u};
-  if (d > 1) {
-    while ((1u << f.shr) < d) ++f.shr;
-    f.mul = static_cast<uint32_t>((((1ull << f.shr) - d) << 32) / d + 1);
-  }
-  return f;
-}
-__device__ __forceinline__ int fast_div(int n, FastDiv f) {
-  return static_cast<int>((__umulhi(static_cast<uint32_t>(n), f.mul) + static_cast<uint32_t>(n)) >> f.shr);
-}
-
 __device__ __forceinline__ float tensor_scale_of(float amax) {
   return amax > 0.f ? __fdiv_rn(amax, 6.f * 448.f) : 1.f;
 }
